@@ -1,0 +1,512 @@
+// Persistent, warp-specialised bf16/fp16 GEMM for sm_100a.
+//
+//   C[M,N] (+)= A * B  (+ bias[N]) (+ residual[M,N])
+//
+// * Operands are staged by TMA (128-byte swizzle, no multicast) into a 4-stage
+//   shared-memory ring; one elected thread issues tcgen05.mma (128x256x16 per
+//   instruction) with fp32 accumulators in tensor memory.
+// * TMEM holds two 128x256 accumulators, so the epilogue of tile i (tcgen05.ld
+//   -> registers -> swizzled smem -> TMA store) overlaps the main loop of tile i+1.
+// * Each operand may be K-major (reduction dim contiguous) or MN-major (output
+//   dim contiguous), which covers forward (x@W with W stored [in,out]), dgrad
+//   (dy@W^T) and wgrad (x^T@dy) without any transposing copy.
+// * Grouped forms for mixture-of-experts: group_mode 1 picks B (and bias) per
+//   128-row M tile from a lookup table; group_mode 2 computes one C per group
+//   over a K range taken from an offsets table (expert weight gradients).
+// * Every wait is bounded: on timeout a status word is set and the kernel drains.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA
+// issuer, warps 2-5 = epilogue (one TMEM lane quarter each).
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace icb {
+
+constexpr int kBM = 128;
+constexpr int kBN = 256;
+constexpr int kBK = 64;
+constexpr int kStages = 4;
+constexpr int kAStageBytes = kBM * kBK * 2;   // 16 KiB
+constexpr int kBStageBytes = kBN * kBK * 2;   // 32 KiB
+constexpr int kSlabBytes = kBM * 128;         // 128 rows x 128 B
+constexpr int kGemmThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kGroupM = 16;
+
+struct GemmSmem {
+  // offsets from the 1024-aligned base
+  static constexpr int a_off = 0;
+  static constexpr int b_off = kStages * kAStageBytes;
+  static constexpr int slab_off = b_off + kStages * kBStageBytes;
+  static constexpr int bar_off = slab_off + 2 * kSlabBytes;
+  static constexpr int total = bar_off + 256;
+};
+constexpr int kGemmSmemBytes = GemmSmem::total + 1024;  // slack for manual alignment
+
+struct GemmArgs {
+  int M, N, K;
+  int num_m_tiles, num_n_tiles, num_groups;
+  int group_mode;            // 0 none, 1 B chosen per m-tile, 2 per-group K range
+  const int* group_table;    // mode 1: [num_m_tiles] group of each m tile (-1 = skip tile); mode 2: [G+1] k offsets
+  const void* bias;          // [N] (mode 1: [G, N]) in input dtype, may be null
+  const void* residual;      // [M, ldr] in output dtype, may be null (may alias C)
+  long long ldr;
+  int in_fmt;                // 0 fp16, 1 bf16
+  int out_f32;               // 0: output dtype == input dtype, 1: fp32
+  int* status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& mt, int& nt) {
+  const int per_group = kGroupM * num_n;
+  const int g = tile / per_group;
+  const int first_m = g * kGroupM;
+  const int gsz = min(num_m - first_m, kGroupM);
+  const int r = tile - g * per_group;
+  mt = first_m + r % gsz;
+  nt = r / gsz;
+}
+
+template <int A_MAJOR, int B_MAJOR>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmC, const GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem + GemmSmem::a_off;
+  uint8_t* smem_b = smem + GemmSmem::b_off;
+  uint8_t* smem_slab = smem + GemmSmem::slab_off;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + GemmSmem::bar_off);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tfull_bar = empty_bar + kStages;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], 128);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmC);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_per_group = args.num_m_tiles * args.num_n_tiles;
+  const int total_tiles = (args.group_mode == 2 ? args.num_groups : 1) * tiles_per_group;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        int grp = 0, k_begin = 0, k_end = args.K;
+        int local = tile;
+        if (args.group_mode == 2) {
+          grp = tile / tiles_per_group;
+          local = tile - grp * tiles_per_group;
+          k_begin = args.group_table[grp];
+          k_end = args.group_table[grp + 1];
+        }
+        int mt, nt;
+        tile_coords(local, args.num_m_tiles, args.num_n_tiles, mt, nt);
+        if (args.group_mode == 1) {
+          grp = args.group_table[mt];
+          if (grp < 0) continue;
+        }
+        const int m0 = mt * kBM, n0 = nt * kBN;
+        const int bz = (args.group_mode == 1) ? grp : 0;
+        for (int k0 = k_begin; k0 < k_end; k0 += kBK, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, args.status, kTimeoutSmemEmpty);
+          mbar_expect_tx(&full_bar[s], kAStageBytes + kBStageBytes);
+          uint8_t* sa = smem_a + s * kAStageBytes;
+          uint8_t* sb = smem_b + s * kBStageBytes;
+          if (A_MAJOR == 0) {
+            tma_load_2d(sa, &tmA, &full_bar[s], k0, m0);
+          } else {
+            tma_load_2d(sa, &tmA, &full_bar[s], m0, k0);
+            tma_load_2d(sa + 8192, &tmA, &full_bar[s], m0 + 64, k0);
+          }
+          if (B_MAJOR == 0) {
+            tma_load_3d(sb, &tmB, &full_bar[s], k0, n0, bz);
+          } else {
+#pragma unroll
+            for (int c = 0; c < kBN / 64; ++c) tma_load_3d(sb + c * 8192, &tmB, &full_bar[s], n0 + c * 64, k0, bz);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(kBM, kBN, args.in_fmt, A_MAJOR, B_MAJOR);
+      uint32_t it = 0, tcount = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        int k_begin = 0, k_end = args.K;
+        int local = tile;
+        if (args.group_mode == 2) {
+          const int grp = tile / tiles_per_group;
+          local = tile - grp * tiles_per_group;
+          k_begin = args.group_table[grp];
+          k_end = args.group_table[grp + 1];
+        }
+        if (args.group_mode == 1) {
+          int mt, nt;
+          tile_coords(local, args.num_m_tiles, args.num_n_tiles, mt, nt);
+          if (args.group_table[mt] < 0) continue;
+        }
+        if (k_end <= k_begin) continue;  // the epilogue writes zeros (+residual) without an accumulator
+        const uint32_t acc = tcount & 1;
+        const uint32_t acc_ph = (tcount >> 1) & 1;
+        mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, args.status, kTimeoutTmemEmpty);
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * kBN;
+        uint32_t first = 1;
+        for (int k0 = k_begin; k0 < k_end; k0 += kBK, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          mbar_wait(&full_bar[s], ph, abort_flag, args.status, kTimeoutSmemFull);
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem_a + s * kAStageBytes);
+          const uint32_t b_addr = smem_u32(smem_b + s * kBStageBytes);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t adesc = (A_MAJOR == 0) ? umma_desc_sw128(a_addr + k * 32, 16, 1024)
+                                                  : umma_desc_sw128(a_addr + k * 2048, 8192, 1024);
+            const uint64_t bdesc = (B_MAJOR == 0) ? umma_desc_sw128(b_addr + k * 32, 16, 1024)
+                                                  : umma_desc_sw128(b_addr + k * 2048, 8192, 1024);
+            umma_ss(tmem_d, adesc, bdesc, idesc, first ? 0u : 1u);
+            first = 0;
+          }
+          umma_commit(&empty_bar[s]);
+        }
+        umma_commit(&tfull_bar[acc]);
+        ++tcount;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int et = threadIdx.x - 64;     // 0..127
+    const int q = warp & 3;              // TMEM lane quarter this warp may read
+    const int row = q * 32 + lane;
+    const int esz = args.out_f32 ? 4 : 2;
+    const int cols_per_slab = 128 / esz;  // 64 (16-bit) or 32 (fp32)
+    uint32_t tcount = 0, slab_count = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      int grp = 0, k_begin = 0, k_end = args.K;
+      int local = tile;
+      if (args.group_mode == 2) {
+        grp = tile / tiles_per_group;
+        local = tile - grp * tiles_per_group;
+        k_begin = args.group_table[grp];
+        k_end = args.group_table[grp + 1];
+      }
+      int mt, nt;
+      tile_coords(local, args.num_m_tiles, args.num_n_tiles, mt, nt);
+      if (args.group_mode == 1) {
+        grp = args.group_table[mt];
+        if (grp < 0) continue;
+      }
+      const bool empty_k = (k_end <= k_begin);
+      const int m0 = mt * kBM, n0 = nt * kBN;
+      const uint32_t acc = tcount & 1;
+      const uint32_t acc_ph = (tcount >> 1) & 1;
+      if (!empty_k) {
+        mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, args.status, kTimeoutTmemFull);
+        tc_fence_after();
+      }
+      const long long m_glob = m0 + row;
+      const bool row_ok = m_glob < args.M;
+      const int cz = (args.group_mode == 2) ? grp : 0;
+      const uint8_t* bias_base = nullptr;
+      if (args.bias != nullptr)
+        bias_base = reinterpret_cast<const uint8_t*>(args.bias) + (args.group_mode == 1 ? (size_t)grp * args.N * 2 : 0);
+
+#pragma unroll 1
+      for (int sub = 0; sub < kBN / 32; ++sub) {
+        const int col0 = sub * 32;
+        const int slab_sub = (esz == 2) ? (sub & 1) : 0;
+        const bool slab_start = (slab_sub == 0);
+        const bool slab_end = (esz == 4) || (sub & 1);
+        uint8_t* slab = smem_slab + (slab_count & 1) * kSlabBytes;
+        if (slab_start) {
+          if (et == 0) tma_store_wait_read<1>();
+          named_barrier(1, 128);
+        }
+        uint32_t r[32];
+        if (!empty_k) {
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN + col0, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (sub == kBN / 32 - 1 && !empty_k) {
+          tc_fence_before();
+          mbar_arrive(&tempty_bar[acc]);
+        }
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        const int n_glob = n0 + col0;
+        if (bias_base != nullptr) {
+          if (n_glob + 32 <= args.N) {
+            const uint4* bp = reinterpret_cast<const uint4*>(bias_base + (size_t)n_glob * 2);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const uint4 u = __ldg(bp + c);
+              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                float lo, hi;
+                if (args.in_fmt == 1) {
+                  const float2 f = unpack_bf16x2(w[t]);
+                  lo = f.x; hi = f.y;
+                } else {
+                  const __half2 h = *reinterpret_cast<const __half2*>(&w[t]);
+                  const float2 f = __half22float2(h);
+                  lo = f.x; hi = f.y;
+                }
+                v[c * 8 + t * 2] += lo;
+                v[c * 8 + t * 2 + 1] += hi;
+              }
+            }
+          } else {
+            for (int j = 0; j < 32; ++j) {
+              if (n_glob + j < args.N) {
+                const uint16_t raw = reinterpret_cast<const uint16_t*>(bias_base)[n_glob + j];
+                float b;
+                if (args.in_fmt == 1) b = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&raw));
+                else b = __half2float(*reinterpret_cast<const __half*>(&raw));
+                v[j] += b;
+              }
+            }
+          }
+        }
+        if (args.residual != nullptr && row_ok) {
+          const uint8_t* rp = reinterpret_cast<const uint8_t*>(args.residual) +
+                              ((size_t)cz * args.M * args.ldr + (size_t)m_glob * args.ldr + n_glob) * esz;
+          const bool vec_ok = (n_glob + 32 <= args.N) && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0);
+          if (esz == 4) {
+            if (vec_ok) {
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                const float4 f = *reinterpret_cast<const float4*>(rp + c * 16);
+                v[c * 4] += f.x; v[c * 4 + 1] += f.y; v[c * 4 + 2] += f.z; v[c * 4 + 3] += f.w;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (n_glob + j < args.N) v[j] += reinterpret_cast<const float*>(rp)[j];
+            }
+          } else {
+            if (vec_ok) {
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                const uint4 u = *reinterpret_cast<const uint4*>(rp + c * 16);
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                  float2 f;
+                  if (args.in_fmt == 1) f = unpack_bf16x2(w[t]);
+                  else f = __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
+                  v[c * 8 + t * 2] += f.x;
+                  v[c * 8 + t * 2 + 1] += f.y;
+                }
+              }
+            } else {
+              for (int j = 0; j < 32; ++j) {
+                if (n_glob + j < args.N) {
+                  const uint16_t raw = reinterpret_cast<const uint16_t*>(rp)[j];
+                  float b;
+                  if (args.in_fmt == 1) b = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&raw));
+                  else b = __half2float(*reinterpret_cast<const __half*>(&raw));
+                  v[j] += b;
+                }
+              }
+            }
+          }
+        }
+        // registers -> swizzled staging slab (row-major 128 B rows, 16 B chunks XOR row%8)
+        uint8_t* srow = slab + row * 128;
+        if (esz == 4) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const int pc = c ^ (row & 7);
+            *reinterpret_cast<float4*>(srow + pc * 16) = make_float4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int pc = (slab_sub * 4 + c) ^ (row & 7);
+            uint4 u;
+            if (args.in_fmt == 1) {
+              u.x = pack_bf16x2(v[c * 8], v[c * 8 + 1]);
+              u.y = pack_bf16x2(v[c * 8 + 2], v[c * 8 + 3]);
+              u.z = pack_bf16x2(v[c * 8 + 4], v[c * 8 + 5]);
+              u.w = pack_bf16x2(v[c * 8 + 6], v[c * 8 + 7]);
+            } else {
+              u.x = pack_f16x2(v[c * 8], v[c * 8 + 1]);
+              u.y = pack_f16x2(v[c * 8 + 2], v[c * 8 + 3]);
+              u.z = pack_f16x2(v[c * 8 + 4], v[c * 8 + 5]);
+              u.w = pack_f16x2(v[c * 8 + 6], v[c * 8 + 7]);
+            }
+            *reinterpret_cast<uint4*>(srow + pc * 16) = u;
+          }
+        }
+        if (slab_end) {
+          fence_proxy_async_smem();
+          named_barrier(1, 128);
+          if (et == 0) {
+            const int slab_col0 = n0 + col0 - slab_sub * 32;
+            if (slab_col0 < args.N) tma_store_3d(&tmC, slab, slab_col0, m0, cz);
+            tma_store_commit();
+          }
+          ++slab_count;
+        }
+      }
+      if (!empty_k) ++tcount;
+    }
+    if (et == 0) tma_store_wait<0>();
+  }
+
+  // Drain: nobody may exit while TMEM is allocated or copies are in flight.
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // Give outstanding TMA loads time to land before shared memory is released.
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) { __nanosleep(1000); }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int A_MAJOR, int B_MAJOR>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const GemmArgs& args,
+                       int grid, cudaStream_t stream) {
+  static bool configured = false;
+  auto kern = gemm_kernel<A_MAJOR, B_MAJOR>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+    if (e != cudaSuccess) {
+      fprintf(stderr, "[ironcore_b200] gemm smem attribute failed: %s\n", cudaGetErrorString(e));
+      return -(int)e;
+    }
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(tmA, tmB, tmC, args);
+  return check_launch("gemm_kernel");
+}
+
+}  // namespace icb
+
+using namespace icb;
+
+// C[M,N] (+)= A*B (+bias) (+residual).
+//   a_major 0: A is [M, lda] row-major (K contiguous);  1: A is [K, lda] row-major (M contiguous)
+//   b_major 0: B is [N, ldb] row-major (K contiguous);  1: B is [K, ldb] row-major (N contiguous)
+//   in_dtype 0 bf16 / 1 fp16; out_f32 selects fp32 output (residual, if any, has the output dtype)
+//   group_mode 0: plain. 1: B = B_base + group_table[m_tile]*b_group_stride (elements), bias row per group.
+//   group_mode 2: for g in [0,G): C_g[M,N] = A[:, k_g..k_g+1) * B[k range], C_g = C + g*M*ldc
+//                 (needs a_major = b_major = 1; K offsets multiples of 64 or zero-padded rows).
+// All pitches in elements; pitches * element size and base pointers must be multiples of 16 bytes.
+ICB_API int icb_gemm(const void* A, const void* B, void* C, const void* bias, const void* residual, int M, int N,
+                     int K, long long lda, long long ldb, long long ldc, long long ldr, int a_major, int b_major,
+                     int in_dtype, int out_f32, int group_mode, int num_groups, const int* group_table,
+                     long long b_group_stride, int* status, int max_ctas, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (in_dtype != kBF16 && in_dtype != kF16) return -2;
+  if (group_mode == 2 && !(a_major == 1 && b_major == 1)) return -3;
+  const int es = 2;
+  const int oes = out_f32 ? 4 : 2;
+  if ((lda * es) % 16 || (ldb * es) % 16 || (ldc * oes) % 16) return -4;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -5;
+  if (num_groups < 1) num_groups = 1;
+
+  CUtensorMap tmA, tmB, tmC;
+  int rc;
+  const uint64_t k_rows = (uint64_t)K;
+  if (a_major == 0) {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)lda * es};
+    uint32_t box[2] = {64, (uint32_t)kBM};
+    rc = make_tmap(&tmA, in_dtype, 2, A, dims, str, box, true);
+  } else {
+    uint64_t dims[2] = {(uint64_t)M, k_rows};
+    uint64_t str[1] = {(uint64_t)lda * es};
+    uint32_t box[2] = {64, (uint32_t)kBK};
+    rc = make_tmap(&tmA, in_dtype, 2, A, dims, str, box, true);
+  }
+  if (rc) return rc;
+  const uint64_t bgroups = (group_mode == 1) ? (uint64_t)num_groups : 1;
+  if (b_major == 0) {
+    uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, bgroups};
+    uint64_t str[2] = {(uint64_t)ldb * es, (uint64_t)(group_mode == 1 ? b_group_stride : (long long)N * ldb) * es};
+    uint32_t box[3] = {64, (uint32_t)kBN, 1};
+    rc = make_tmap(&tmB, in_dtype, 3, B, dims, str, box, true);
+  } else {
+    uint64_t dims[3] = {(uint64_t)N, k_rows, bgroups};
+    uint64_t str[2] = {(uint64_t)ldb * es, (uint64_t)(group_mode == 1 ? b_group_stride : (long long)K * ldb) * es};
+    uint32_t box[3] = {64, (uint32_t)kBK, 1};
+    rc = make_tmap(&tmB, in_dtype, 3, B, dims, str, box, true);
+  }
+  if (rc) return rc;
+  {
+    const uint64_t cgroups = (group_mode == 2) ? (uint64_t)num_groups : 1;
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, cgroups};
+    uint64_t str[2] = {(uint64_t)ldc * oes, (uint64_t)M * ldc * oes};
+    uint32_t box[3] = {(uint32_t)(128 / oes), (uint32_t)kBM, 1};
+    rc = make_tmap(&tmC, out_f32 ? kF32 : in_dtype, 3, C, dims, str, box, true);
+  }
+  if (rc) return rc;
+
+  GemmArgs args;
+  args.M = M; args.N = N; args.K = K;
+  args.num_m_tiles = (M + kBM - 1) / kBM;
+  args.num_n_tiles = (N + kBN - 1) / kBN;
+  args.num_groups = num_groups;
+  args.group_mode = group_mode;
+  args.group_table = group_table;
+  args.bias = bias;
+  args.residual = residual;
+  args.ldr = ldr;
+  args.in_fmt = (in_dtype == kBF16) ? 1 : 0;
+  args.out_f32 = out_f32;
+  args.status = status;
+
+  long long total = (long long)args.num_m_tiles * args.num_n_tiles * (group_mode == 2 ? num_groups : 1);
+  int grid = num_sms();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (total < grid) grid = (int)total;
+  if (grid < 1) grid = 1;
+
+  if (a_major == 0 && b_major == 0) return launch_gemm<0, 0>(tmA, tmB, tmC, args, grid, stream);
+  if (a_major == 0 && b_major == 1) return launch_gemm<0, 1>(tmA, tmB, tmC, args, grid, stream);
+  if (a_major == 1 && b_major == 0) return launch_gemm<1, 0>(tmA, tmB, tmC, args, grid, stream);
+  return launch_gemm<1, 1>(tmA, tmB, tmC, args, grid, stream);
+}

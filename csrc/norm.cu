@@ -1,0 +1,333 @@
+// RMSNorm / LayerNorm forward and backward for 16-bit activations (bf16/fp16),
+// fp32 statistics. One 128-thread CTA walks rows; each thread keeps its slice of
+// the row in registers, so every tensor is read once and written once.
+//
+// forward : (optionally h = x + residual, stored) ; y = norm(h) * (w + w_offset) (+ b)
+// backward: dx = d norm / dh (+ dres_in), per-CTA partial dw/db in fp32 scratch,
+//           then a second kernel reduces the partials (deterministic, no atomics).
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace icb {
+
+constexpr int kNormThreads = 128;
+
+template <bool BF16>
+__device__ __forceinline__ void load8(const void* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t;
+    if (BF16) t = unpack_bf16x2(w[i]);
+    else t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+template <bool BF16>
+__device__ __forceinline__ void store8(void* p, const float (&f)[8]) {
+  uint4 u;
+  if (BF16) {
+    u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
+    u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+  } else {
+    u.x = pack_f16x2(f[0], f[1]); u.y = pack_f16x2(f[2], f[3]);
+    u.z = pack_f16x2(f[4], f[5]); u.w = pack_f16x2(f[6], f[7]);
+  }
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+__device__ __forceinline__ float block_sum_128(float v, float* sh) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  return sh[0] + sh[1] + sh[2] + sh[3];
+}
+
+// VPT = 16-byte vectors per thread; D == VPT*128*8 is not required: tail vectors are masked.
+template <bool BF16, int VPT, bool RMS>
+__global__ void __launch_bounds__(kNormThreads)
+norm_fwd_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ res, const uint16_t* __restrict__ w,
+                const uint16_t* __restrict__ b, uint16_t* __restrict__ y, uint16_t* __restrict__ h_out,
+                float* __restrict__ mean_out, float* __restrict__ rstd_out, int M, int D, float eps, float w_offset) {
+  __shared__ float sh[4];
+  const int nvec = D >> 3;
+  float wv[VPT][8], bv[VPT][8];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = threadIdx.x + i * kNormThreads;
+    if (vi < nvec) {
+      load8<BF16>(w + vi * 8, wv[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) wv[i][j] += w_offset;
+      if (b != nullptr) load8<BF16>(b + vi * 8, bv[i]);
+    }
+  }
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    const size_t base = (size_t)row * D;
+    float xv[VPT][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = threadIdx.x + i * kNormThreads;
+      if (vi < nvec) {
+        load8<BF16>(x + base + vi * 8, xv[i]);
+        if (res != nullptr) {
+          float rv[8];
+          load8<BF16>(res + base + vi * 8, rv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) xv[i][j] += rv[j];
+          if (h_out != nullptr) {
+            store8<BF16>(h_out + base + vi * 8, xv[i]);
+            // keep the statistics consistent with the rounded value that backward will re-read
+            load8<BF16>(h_out + base + vi * 8, xv[i]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += RMS ? xv[i][j] * xv[i][j] : xv[i][j];
+      }
+    }
+    float mean = 0.f, rstd;
+    if (RMS) {
+      const float ss = block_sum_128(s, sh);
+      rstd = rsqrtf(ss / D + eps);
+    } else {
+      mean = block_sum_128(s, sh) / D;
+      float s2 = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int vi = threadIdx.x + i * kNormThreads;
+        if (vi < nvec) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { const float d = xv[i][j] - mean; s2 += d * d; }
+        }
+      }
+      rstd = rsqrtf(block_sum_128(s2, sh) / D + eps);
+    }
+    if (threadIdx.x == 0) {
+      if (mean_out != nullptr) mean_out[row] = mean;
+      rstd_out[row] = rstd;
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = threadIdx.x + i * kNormThreads;
+      if (vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o[j] = (xv[i][j] - mean) * rstd * wv[i][j];
+          if (b != nullptr) o[j] += bv[i][j];
+        }
+        store8<BF16>(y + base + vi * 8, o);
+      }
+    }
+  }
+}
+
+template <bool BF16, int VPT, bool RMS>
+__global__ void __launch_bounds__(kNormThreads)
+norm_bwd_kernel(const uint16_t* __restrict__ dy, const uint16_t* __restrict__ x, const uint16_t* __restrict__ w,
+                const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                const uint16_t* __restrict__ dres_in, uint16_t* __restrict__ dx, float* __restrict__ dw_part,
+                float* __restrict__ db_part, int M, int D, float w_offset) {
+  __shared__ float sh[4];
+  const int nvec = D >> 3;
+  float wv[VPT][8], dwv[VPT][8], dbv[VPT][8];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = threadIdx.x + i * kNormThreads;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { dwv[i][j] = 0.f; dbv[i][j] = 0.f; wv[i][j] = 0.f; }
+    if (vi < nvec) {
+      load8<BF16>(w + vi * 8, wv[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) wv[i][j] += w_offset;
+    }
+  }
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    const size_t base = (size_t)row * D;
+    const float mean = RMS ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float xh[VPT][8], g[VPT][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = threadIdx.x + i * kNormThreads;
+      if (vi < nvec) {
+        float dyv[8];
+        load8<BF16>(dy + base + vi * 8, dyv);
+        load8<BF16>(x + base + vi * 8, xh[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = (xh[i][j] - mean) * rstd;
+          g[i][j] = dyv[j] * wv[i][j];
+          s1 += g[i][j] * xh[i][j];
+          if (!RMS) s2 += g[i][j];
+          dwv[i][j] += dyv[j] * xh[i][j];
+          dbv[i][j] += dyv[j];
+        }
+      }
+    }
+    const float c1 = block_sum_128(s1, sh) / D;
+    const float c2 = RMS ? 0.f : block_sum_128(s2, sh) / D;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = threadIdx.x + i * kNormThreads;
+      if (vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - c2 - xh[i][j] * c1);
+        if (dres_in != nullptr) {
+          float a[8];
+          load8<BF16>(dres_in + base + vi * 8, a);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += a[j];
+        }
+        store8<BF16>(dx + base + vi * 8, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = threadIdx.x + i * kNormThreads;
+    if (vi < nvec) {
+      float* p = dw_part + (size_t)blockIdx.x * D + vi * 8;
+      *reinterpret_cast<float4*>(p) = make_float4(dwv[i][0], dwv[i][1], dwv[i][2], dwv[i][3]);
+      *reinterpret_cast<float4*>(p + 4) = make_float4(dwv[i][4], dwv[i][5], dwv[i][6], dwv[i][7]);
+      if (db_part != nullptr) {
+        float* q = db_part + (size_t)blockIdx.x * D + vi * 8;
+        *reinterpret_cast<float4*>(q) = make_float4(dbv[i][0], dbv[i][1], dbv[i][2], dbv[i][3]);
+        *reinterpret_cast<float4*>(q + 4) = make_float4(dbv[i][4], dbv[i][5], dbv[i][6], dbv[i][7]);
+      }
+    }
+  }
+}
+
+// out[d] (+)= sum_p part[p, d]; writes 16-bit or fp32 output.
+template <bool BF16>
+__global__ void reduce_partials_kernel(const float* __restrict__ part, int P, int D, void* __restrict__ out,
+                                       int out_f32, int accumulate) {
+  const int d = blockIdx.x * blockDim.x + threadIdx.x;
+  if (d >= D) return;
+  float s = 0.f;
+  for (int p = 0; p < P; ++p) s += part[(size_t)p * D + d];
+  if (out_f32) {
+    float* o = reinterpret_cast<float*>(out);
+    o[d] = accumulate ? o[d] + s : s;
+  } else if (BF16) {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
+    o[d] = __float2bfloat16(accumulate ? __bfloat162float(o[d]) + s : s);
+  } else {
+    __half* o = reinterpret_cast<__half*>(out);
+    o[d] = __float2half(accumulate ? __half2float(o[d]) + s : s);
+  }
+}
+
+template <bool BF16, bool RMS>
+static int norm_fwd_dispatch(int vpt, int grid, cudaStream_t st, const uint16_t* x, const uint16_t* res,
+                             const uint16_t* w, const uint16_t* b, uint16_t* y, uint16_t* h, float* mean, float* rstd,
+                             int M, int D, float eps, float woff) {
+#define ICB_NF(V) \
+  norm_fwd_kernel<BF16, V, RMS><<<grid, kNormThreads, 0, st>>>(x, res, w, b, y, h, mean, rstd, M, D, eps, woff)
+  switch (vpt) {
+    case 1: ICB_NF(1); break;
+    case 2: ICB_NF(2); break;
+    case 3: case 4: ICB_NF(4); break;
+    case 5: case 6: ICB_NF(6); break;
+    case 7: case 8: ICB_NF(8); break;
+    default: return -2;
+  }
+#undef ICB_NF
+  return check_launch("norm_fwd");
+}
+
+template <bool BF16, bool RMS>
+static int norm_bwd_dispatch(int vpt, int grid, cudaStream_t st, const uint16_t* dy, const uint16_t* x,
+                             const uint16_t* w, const float* mean, const float* rstd, const uint16_t* dres,
+                             uint16_t* dx, float* dwp, float* dbp, int M, int D, float woff) {
+#define ICB_NB(V) \
+  norm_bwd_kernel<BF16, V, RMS><<<grid, kNormThreads, 0, st>>>(dy, x, w, mean, rstd, dres, dx, dwp, dbp, M, D, woff)
+  switch (vpt) {
+    case 1: ICB_NB(1); break;
+    case 2: ICB_NB(2); break;
+    case 3: case 4: ICB_NB(4); break;
+    case 5: case 6: ICB_NB(6); break;
+    case 7: case 8: ICB_NB(8); break;
+    default: return -2;
+  }
+#undef ICB_NB
+  return check_launch("norm_bwd");
+}
+
+}  // namespace icb
+
+using namespace icb;
+
+// Number of CTAs (= rows of the partial-sum scratch) the backward kernel uses for M rows.
+ICB_API int icb_norm_bwd_parts(int M) {
+  int g = num_sms() * 4;
+  return M < g ? M : g;
+}
+
+// dtype: 0 bf16, 1 fp16. rms: 1 RMSNorm, 0 LayerNorm. D must be a multiple of 8 and <= 8192.
+// res/h_out/b/mean may be null. If res is given, h = x + res is normalised and (if h_out) stored.
+ICB_API int icb_norm_fwd(const void* x, const void* res, const void* w, const void* b, void* y, void* h_out,
+                         float* mean, float* rstd, int M, int D, float eps, float w_offset, int rms, int dtype,
+                         void* stream) {
+  if (M <= 0) return 0;
+  if (D % 8 != 0 || D > 8192) return -2;
+  const int vpt = (D / 8 + kNormThreads - 1) / kNormThreads;
+  int grid = num_sms() * 8;
+  if (M < grid) grid = M;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  auto X = reinterpret_cast<const uint16_t*>(x);
+  auto R = reinterpret_cast<const uint16_t*>(res);
+  auto W = reinterpret_cast<const uint16_t*>(w);
+  auto B = reinterpret_cast<const uint16_t*>(b);
+  auto Y = reinterpret_cast<uint16_t*>(y);
+  auto H = reinterpret_cast<uint16_t*>(h_out);
+  if (dtype == kBF16)
+    return rms ? norm_fwd_dispatch<true, true>(vpt, grid, st, X, R, W, B, Y, H, mean, rstd, M, D, eps, w_offset)
+               : norm_fwd_dispatch<true, false>(vpt, grid, st, X, R, W, B, Y, H, mean, rstd, M, D, eps, w_offset);
+  return rms ? norm_fwd_dispatch<false, true>(vpt, grid, st, X, R, W, B, Y, H, mean, rstd, M, D, eps, w_offset)
+             : norm_fwd_dispatch<false, false>(vpt, grid, st, X, R, W, B, Y, H, mean, rstd, M, D, eps, w_offset);
+}
+
+// scratch: fp32 [(db ? 2 : 1) * icb_norm_bwd_parts(M) * D]. dw/db are written (or accumulated into)
+// in the 16-bit dtype (grad_f32 = 0) or fp32 (grad_f32 = 1). dres_in (optional) is added to dx.
+ICB_API int icb_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                         const void* dres_in, void* dx, void* dw, void* db, float* scratch, int M, int D,
+                         float w_offset, int rms, int dtype, int grad_f32, int accumulate, void* stream) {
+  if (M <= 0) return 0;
+  if (D % 8 != 0 || D > 8192) return -2;
+  const int vpt = (D / 8 + kNormThreads - 1) / kNormThreads;
+  const int grid = icb_norm_bwd_parts(M);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  float* dwp = scratch;
+  float* dbp = (db != nullptr) ? scratch + (size_t)grid * D : nullptr;
+  auto DY = reinterpret_cast<const uint16_t*>(dy);
+  auto X = reinterpret_cast<const uint16_t*>(x);
+  auto W = reinterpret_cast<const uint16_t*>(w);
+  auto DR = reinterpret_cast<const uint16_t*>(dres_in);
+  auto DX = reinterpret_cast<uint16_t*>(dx);
+  int rc;
+  if (dtype == kBF16)
+    rc = rms ? norm_bwd_dispatch<true, true>(vpt, grid, st, DY, X, W, mean, rstd, DR, DX, dwp, dbp, M, D, w_offset)
+             : norm_bwd_dispatch<true, false>(vpt, grid, st, DY, X, W, mean, rstd, DR, DX, dwp, dbp, M, D, w_offset);
+  else
+    rc = rms ? norm_bwd_dispatch<false, true>(vpt, grid, st, DY, X, W, mean, rstd, DR, DX, dwp, dbp, M, D, w_offset)
+             : norm_bwd_dispatch<false, false>(vpt, grid, st, DY, X, W, mean, rstd, DR, DX, dwp, dbp, M, D, w_offset);
+  if (rc) return rc;
+  const int th = 256, bl = (D + th - 1) / th;
+  if (dtype == kBF16) {
+    reduce_partials_kernel<true><<<bl, th, 0, st>>>(dwp, grid, D, dw, grad_f32, accumulate);
+    if (db != nullptr) reduce_partials_kernel<true><<<bl, th, 0, st>>>(dbp, grid, D, db, grad_f32, accumulate);
+  } else {
+    reduce_partials_kernel<false><<<bl, th, 0, st>>>(dwp, grid, D, dw, grad_f32, accumulate);
+    if (db != nullptr) reduce_partials_kernel<false><<<bl, th, 0, st>>>(dbp, grid, D, db, grad_f32, accumulate);
+  }
+  return check_launch("norm_bwd_reduce");
+}

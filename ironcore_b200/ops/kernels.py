@@ -1,0 +1,294 @@
+"""Tensor-level wrappers around the native sm_100a kernels.
+
+Each function validates shapes/strides, allocates outputs with torch (so the
+caching allocator and stream semantics stay PyTorch's) and launches the kernel on
+the current CUDA stream. These wrappers have no autograd; see
+:mod:`ironcore_b200.ops.functional` for differentiable ops.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import native
+from .native import call, dtype_code, ptr, query, stream_ptr
+
+ACT_KINDS = {"relu": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3, "sigmoid": 4}
+# gated activations: name -> (kind, gate_is_act). y = act(f) * g, or f * act(g) when gate_is_act.
+GLU_KINDS = {
+    "swiglu": (3, 0),
+    "geglu": (2, 0),
+    "geglu_erf": (1, 0),
+    "reglu": (0, 0),
+    "glu": (4, 1),
+}
+
+
+def _check_2d(t: torch.Tensor, name: str) -> None:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be 2-D with a contiguous last dim, got shape {tuple(t.shape)} strides {t.stride()}")
+    if (t.stride(0) * t.element_size()) % 16 != 0 or t.data_ptr() % 16 != 0:
+        raise ValueError(f"{name}: row pitch and base address must be multiples of 16 bytes")
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_major: int,
+    b_major: int,
+    m: int,
+    n: int,
+    k: int,
+    out: Optional[torch.Tensor] = None,
+    bias: Optional[torch.Tensor] = None,
+    residual: Optional[torch.Tensor] = None,
+    out_dtype: Optional[torch.dtype] = None,
+    group_mode: int = 0,
+    num_groups: int = 1,
+    group_table: Optional[torch.Tensor] = None,
+    b_group_stride: int = 0,
+    max_ctas: int = 0,
+) -> torch.Tensor:
+    """C[m,n] = A*B (+bias) (+residual) on the tcgen05 GEMM.
+
+    a_major 0: ``a`` is [m, k] (k contiguous); 1: ``a`` is [k, m] (m contiguous).
+    b_major 0: ``b`` is [n, k] (k contiguous); 1: ``b`` is [k, n] (n contiguous).
+    ``residual`` must have the output dtype and may alias ``out`` (accumulation).
+    """
+    in_dt = a.dtype
+    if b.dtype != in_dt or in_dt not in (torch.bfloat16, torch.float16):
+        raise TypeError("gemm operands must both be bf16 or both fp16")
+    out_dtype = out_dtype or (out.dtype if out is not None else in_dt)
+    if out_dtype not in (in_dt, torch.float32):
+        raise TypeError("gemm output must be the input dtype or fp32")
+    if group_mode == 2:
+        out_shape = (num_groups, m, n)
+    else:
+        out_shape = (m, n)
+    if out is None:
+        out = torch.empty(out_shape, dtype=out_dtype, device=a.device)
+    ldc = out.stride(-2)
+    if out.stride(-1) != 1 or (ldc * out.element_size()) % 16 or out.data_ptr() % 16:
+        raise ValueError("gemm output must be row-major with 16-byte aligned rows")
+    _check_2d(a if a.dim() == 2 else a.reshape(-1, a.shape[-1]), "a")
+    lda = a.stride(-2)
+    ldb = b.stride(-2)
+    if b.stride(-1) != 1 or (ldb * 2) % 16 or b.data_ptr() % 16:
+        raise ValueError("gemm operand b must be row-major with 16-byte aligned rows")
+    ldr = 0
+    if residual is not None:
+        if residual.dtype != out_dtype or residual.stride(-1) != 1:
+            raise ValueError("residual must match the output dtype and be row-major")
+        ldr = residual.stride(-2)
+    if bias is not None and bias.dtype != in_dt:
+        bias = bias.to(in_dt)
+    if group_table is not None and group_table.dtype != torch.int32:
+        raise TypeError("group_table must be int32")
+    call(
+        "icb_gemm",
+        ptr(a), ptr(b), ptr(out), ptr(bias), ptr(residual),
+        int(m), int(n), int(k), int(lda), int(ldb), int(ldc), int(ldr),
+        int(a_major), int(b_major), dtype_code(in_dt), 1 if out_dtype == torch.float32 and in_dt != torch.float32 else 0,
+        int(group_mode), int(num_groups), ptr(group_table), int(b_group_stride),
+        ptr(native.status_tensor(a.device)), int(max_ctas), stream_ptr(),
+    )
+    return out
+
+
+def mm_nn(x: torch.Tensor, w: torch.Tensor, **kw) -> torch.Tensor:
+    """x[M,K] @ w[K,N] (weights stored [in, out])."""
+    return gemm(x, w, a_major=0, b_major=1, m=x.shape[0], n=w.shape[1], k=x.shape[1], **kw)
+
+
+def mm_nt(dy: torch.Tensor, w: torch.Tensor, **kw) -> torch.Tensor:
+    """dy[M,N] @ w[K,N]^T -> [M,K]."""
+    return gemm(dy, w, a_major=0, b_major=0, m=dy.shape[0], n=w.shape[0], k=dy.shape[1], **kw)
+
+
+def mm_tn(x: torch.Tensor, dy: torch.Tensor, **kw) -> torch.Tensor:
+    """x[M,K]^T @ dy[M,N] -> [K,N]."""
+    return gemm(x, dy, a_major=1, b_major=1, m=x.shape[1], n=dy.shape[1], k=x.shape[0], **kw)
+
+
+# ---------------------------------------------------------------------------
+# normalisation
+# ---------------------------------------------------------------------------
+def norm_fwd(x, weight, bias, eps: float, rms: bool, residual=None, w_offset: float = 0.0, store_sum: bool = True):
+    """Returns (y, h, mean, rstd). ``h`` is x+residual (or x itself when no residual)."""
+    d = x.shape[-1]
+    x2 = x.reshape(-1, d)
+    m = x2.shape[0]
+    y = torch.empty_like(x2)
+    rstd = torch.empty(m, dtype=torch.float32, device=x.device)
+    mean = None if rms else torch.empty(m, dtype=torch.float32, device=x.device)
+    h = None
+    r2 = None
+    if residual is not None:
+        r2 = residual.reshape(-1, d)
+        h = torch.empty_like(x2) if store_sum else None
+    call(
+        "icb_norm_fwd", ptr(x2), ptr(r2), ptr(weight), ptr(bias), ptr(y), ptr(h), ptr(mean), ptr(rstd),
+        m, d, float(eps), float(w_offset), 1 if rms else 0, dtype_code(x.dtype), stream_ptr(),
+    )
+    return y.view(x.shape), (h.view(x.shape) if h is not None else x), mean, rstd
+
+
+def norm_bwd(dy, x, weight, mean, rstd, rms: bool, has_bias: bool, dres_in=None, w_offset: float = 0.0):
+    """Returns (dx, dw, db). dres_in (optional) is added into dx inside the kernel."""
+    d = x.shape[-1]
+    x2 = x.reshape(-1, d)
+    dy2 = dy.reshape(-1, d)
+    m = x2.shape[0]
+    parts = query("icb_norm_bwd_parts", m)
+    scratch = torch.empty((2 if has_bias else 1) * parts * d, dtype=torch.float32, device=x.device)
+    dx = torch.empty_like(x2)
+    dw = torch.empty(d, dtype=torch.float32, device=x.device)
+    db = torch.empty(d, dtype=torch.float32, device=x.device) if has_bias else None
+    dr2 = dres_in.reshape(-1, d) if dres_in is not None else None
+    call(
+        "icb_norm_bwd", ptr(dy2), ptr(x2), ptr(weight), ptr(mean), ptr(rstd), ptr(dr2), ptr(dx), ptr(dw), ptr(db),
+        ptr(scratch), m, d, float(w_offset), 1 if rms else 0, dtype_code(x.dtype), 1, 0, stream_ptr(),
+    )
+    return dx.view(x.shape), dw, db
+
+
+# ---------------------------------------------------------------------------
+# rotary embedding
+# ---------------------------------------------------------------------------
+def rope(x: torch.Tensor, out: torch.Tensor, *, nheads: int, head_dim: int, tokens: int, seq_len: int,
+         base: float, scale: float = 1.0, offset: int = 0, interleaved: bool = True, inverse: bool = False,
+         pos_ids: Optional[torch.Tensor] = None, row_stride: Optional[int] = None,
+         out_stride: Optional[int] = None) -> torch.Tensor:
+    """Rotate ``nheads`` heads starting at x's data pointer in rows of pitch ``row_stride`` elements."""
+    rs = row_stride if row_stride is not None else nheads * head_dim
+    os_ = out_stride if out_stride is not None else rs
+    call(
+        "icb_rope", ptr(x), ptr(out), ptr(pos_ids), int(tokens), int(nheads), int(head_dim), int(rs), int(os_),
+        int(seq_len), float(base), float(scale), int(offset), 1 if interleaved else 0, 1 if inverse else 0,
+        dtype_code(x.dtype), stream_ptr(),
+    )
+    return out
+
+
+# ---------------------------------------------------------------------------
+# activations
+# ---------------------------------------------------------------------------
+def glu_fwd(x: torch.Tensor, name: str) -> torch.Tensor:
+    kind, gate_is_act = GLU_KINDS[name]
+    f = x.shape[-1] // 2
+    x2 = x.reshape(-1, 2 * f)
+    y = torch.empty((x2.shape[0], f), dtype=x.dtype, device=x.device)
+    call("icb_glu_fwd", ptr(x2), ptr(y), x2.shape[0], f, kind, gate_is_act, dtype_code(x.dtype), stream_ptr())
+    return y.view(*x.shape[:-1], f)
+
+
+def glu_bwd(dy: torch.Tensor, x: torch.Tensor, name: str) -> torch.Tensor:
+    kind, gate_is_act = GLU_KINDS[name]
+    f = x.shape[-1] // 2
+    x2 = x.reshape(-1, 2 * f)
+    dy2 = dy.reshape(-1, f)
+    if not dy2.is_contiguous():
+        dy2 = dy2.contiguous()
+    dx = torch.empty_like(x2)
+    call("icb_glu_bwd", ptr(dy2), ptr(x2), ptr(dx), x2.shape[0], f, kind, gate_is_act, dtype_code(x.dtype), stream_ptr())
+    return dx.view(x.shape)
+
+
+def act_fwd(x: torch.Tensor, name: str) -> torch.Tensor:
+    xc = x.contiguous()
+    y = torch.empty_like(xc)
+    call("icb_act_fwd", ptr(xc), ptr(y), xc.numel(), ACT_KINDS[name], dtype_code(x.dtype), stream_ptr())
+    return y
+
+
+def act_bwd(dy: torch.Tensor, x: torch.Tensor, name: str) -> torch.Tensor:
+    xc = x.contiguous()
+    dyc = dy.contiguous()
+    dx = torch.empty_like(xc)
+    call("icb_act_bwd", ptr(dyc), ptr(xc), ptr(dx), xc.numel(), ACT_KINDS[name], dtype_code(x.dtype), stream_ptr())
+    return dx
+
+
+# ---------------------------------------------------------------------------
+# embedding
+# ---------------------------------------------------------------------------
+def embedding_fwd(ids: torch.Tensor, weight: torch.Tensor, *, vocab_start: int = 0,
+                  pos_table: Optional[torch.Tensor] = None, pos_ids: Optional[torch.Tensor] = None,
+                  seq_len: int = 1) -> torch.Tensor:
+    flat = ids.reshape(-1)
+    if flat.dtype != torch.int64:
+        flat = flat.long()
+    t = flat.numel()
+    d = weight.shape[1]
+    out = torch.empty((t, d), dtype=weight.dtype, device=weight.device)
+    call(
+        "icb_embedding_fwd", ptr(flat), ptr(weight), ptr(pos_table), ptr(pos_ids), ptr(out), t, d, int(vocab_start),
+        weight.shape[0], int(seq_len), dtype_code(weight.dtype), stream_ptr(),
+    )
+    return out.view(*ids.shape, d)
+
+
+def embedding_bwd(rows: torch.Tensor, dy: torch.Tensor, num_rows: int, *, row_start: int = 0) -> torch.Tensor:
+    flat = rows.reshape(-1)
+    if flat.dtype != torch.int64:
+        flat = flat.long()
+    d = dy.shape[-1]
+    dy2 = dy.reshape(-1, d).contiguous()
+    dw = torch.zeros((num_rows, d), dtype=torch.float32, device=dy.device)
+    call("icb_embedding_bwd", ptr(flat), ptr(dy2), ptr(dw), flat.numel(), d, int(row_start), num_rows,
+         dtype_code(dy.dtype), stream_ptr())
+    return dw
+
+
+# ---------------------------------------------------------------------------
+# cross entropy
+# ---------------------------------------------------------------------------
+def ce_stats(logits: torch.Tensor, targets: torch.Tensor, *, vocab_start: int = 0, vocab_valid: Optional[int] = None):
+    t, v = logits.shape
+    vv = v if vocab_valid is None else vocab_valid
+    rmax = torch.empty(t, dtype=torch.float32, device=logits.device)
+    rsum = torch.empty_like(rmax)
+    rtgt = torch.empty_like(rmax)
+    call("icb_ce_stats", ptr(logits), ptr(targets), ptr(rmax), ptr(rsum), ptr(rtgt), t, v, logits.stride(0),
+         int(vocab_start), int(vv), dtype_code(logits.dtype), stream_ptr())
+    return rmax, rsum, rtgt
+
+
+def ce_grad_(logits: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor, gscale: torch.Tensor, *,
+             vocab_start: int = 0, vocab_valid: Optional[int] = None) -> torch.Tensor:
+    t, v = logits.shape
+    vv = v if vocab_valid is None else vocab_valid
+    call("icb_ce_grad", ptr(logits), ptr(targets), ptr(lse), ptr(gscale), t, v, logits.stride(0), int(vocab_start),
+         int(vv), dtype_code(logits.dtype), stream_ptr())
+    return logits
+
+
+# ---------------------------------------------------------------------------
+# optimizer helpers
+# ---------------------------------------------------------------------------
+def adam_step_(p, g, m, v, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0, grad_scale_dev=None):
+    bc1 = 1.0 - beta1 ** step
+    bc2 = 1.0 - beta2 ** step
+    step_size = lr * (bc2 ** 0.5) / bc1
+    call("icb_adam", ptr(p), ptr(g), ptr(m), ptr(v), p.numel(), float(lr), float(beta1), float(beta2), float(eps),
+         float(weight_decay), float(step_size), float(grad_scale), ptr(grad_scale_dev), dtype_code(p.dtype),
+         dtype_code(g.dtype), stream_ptr())
+
+
+def sumsq(g: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
+    """out[0] (+)= sum(g^2) on device; ``out`` is a 1-element fp32 tensor."""
+    n = g.numel()
+    parts = query("icb_sumsq_parts", n)
+    scratch = torch.empty(parts, dtype=torch.float32, device=g.device)
+    call("icb_sumsq", ptr(g), n, ptr(scratch), ptr(out), 1 if accumulate else 0, dtype_code(g.dtype), stream_ptr())
+    return out
+
+
+def clip_coef(total_sq: torch.Tensor, clip: float):
+    norm = torch.empty(1, dtype=torch.float32, device=total_sq.device)
+    coef = torch.empty(1, dtype=torch.float32, device=total_sq.device)
+    call("icb_clip_coef", ptr(total_sq), float(clip), ptr(norm), ptr(coef), stream_ptr())
+    return norm, coef

@@ -1,0 +1,109 @@
+"""tcgen05 GEMM against an fp32 PyTorch reference: every operand-major combination,
+ragged shapes, epilogue options and the grouped (mixture-of-experts) forms."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, a_major, b_major):
+    A = a.float() if a_major == 0 else a.float().t()
+    B = b.float().t() if b_major == 0 else b.float()
+    return A @ B
+
+
+def _mk(rows, cols, dtype=torch.bfloat16, scale=1.0):
+    return (torch.randn(rows, cols, device="cuda") * scale).to(dtype)
+
+
+def _check(out, ref, k, tol=2e-2):
+    err = (out.float() - ref).abs().max().item()
+    bound = tol * (k ** 0.5)
+    assert err <= bound, f"max abs err {err} > {bound}"
+
+
+@pytest.mark.parametrize("a_major,b_major", [(0, 1), (0, 0), (1, 1), (1, 0)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 256), (384, 1376, 520), (200, 264, 72), (4096, 1536, 1024)])
+def test_gemm_majors(a_major, b_major, m, n, k):
+    from ironcore_b200.ops import kernels, native
+
+    torch.manual_seed(0)
+    a = _mk(m, k) if a_major == 0 else _mk(k, m)
+    b = _mk(n, k) if b_major == 0 else _mk(k, n)
+    out = kernels.gemm(a, b, a_major=a_major, b_major=b_major, m=m, n=n, k=k)
+    torch.cuda.synchronize()
+    native.check_status()
+    _check(out, _ref(a, b, a_major, b_major), k)
+
+
+def test_gemm_epilogue_bias_residual_fp32():
+    from ironcore_b200.ops import kernels, native
+
+    torch.manual_seed(1)
+    m, n, k = 300, 520, 256
+    x, w = _mk(m, k), _mk(k, n)
+    bias = _mk(1, n).reshape(n)
+    res = _mk(m, n)
+    out = kernels.mm_nn(x, w, bias=bias, residual=res)
+    ref = x.float() @ w.float() + bias.float() + res.float()
+    _check(out, ref, k)
+    # fp32 output with in-place accumulation (C += A B)
+    acc = torch.randn(m, n, device="cuda")
+    ref2 = acc + x.float() @ w.float()
+    out2 = kernels.mm_nn(x, w, out=acc, residual=acc, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert out2.data_ptr() == acc.data_ptr()
+    _check(out2, ref2, k, tol=1e-2)
+
+
+def test_gemm_fp16():
+    from ironcore_b200.ops import kernels
+
+    torch.manual_seed(2)
+    m, n, k = 256, 256, 128
+    x, w = _mk(m, k, torch.float16), _mk(k, n, torch.float16)
+    out = kernels.mm_nn(x, w)
+    _check(out, x.float() @ w.float(), k, tol=5e-3)
+
+
+def test_gemm_backward_helpers():
+    from ironcore_b200.ops import kernels
+
+    torch.manual_seed(3)
+    m, k, n = 512, 264, 392
+    x, w, dy = _mk(m, k), _mk(k, n), _mk(m, n)
+    _check(kernels.mm_nt(dy, w), dy.float() @ w.float().t(), n)
+    _check(kernels.mm_tn(x, dy), x.float().t() @ dy.float(), m)
+
+
+def test_gemm_grouped_by_m_tile():
+    from ironcore_b200.ops import kernels
+
+    torch.manual_seed(4)
+    g, k, n = 3, 128, 320
+    rows = [256, 128, 384]
+    table = torch.tensor([0, 0, 1, 2, 2, 2], dtype=torch.int32, device="cuda")
+    m = sum(rows)
+    x = _mk(m, k)
+    w = (torch.randn(g, k, n, device="cuda")).to(torch.bfloat16)
+    out = kernels.gemm(x, w, a_major=0, b_major=1, m=m, n=n, k=k, group_mode=1, num_groups=g,
+                       group_table=table, b_group_stride=k * n)
+    ref = torch.cat([x[:256].float() @ w[0].float(), x[256:384].float() @ w[1].float(), x[384:].float() @ w[2].float()])
+    _check(out, ref, k)
+
+
+def test_gemm_grouped_by_k_range():
+    from ironcore_b200.ops import kernels
+
+    torch.manual_seed(5)
+    g, kin, n = 3, 200, 264
+    offs = torch.tensor([0, 128, 128, 448], dtype=torch.int32, device="cuda")  # middle group is empty
+    x = _mk(448, kin)
+    dy = _mk(448, n)
+    out = kernels.gemm(x, dy, a_major=1, b_major=1, m=kin, n=n, k=448, group_mode=2, num_groups=g, group_table=offs)
+    refs = [x[0:128].float().t() @ dy[0:128].float(), torch.zeros(kin, n, device="cuda"),
+            x[128:448].float().t() @ dy[128:448].float()]
+    for i in range(g):
+        _check(out[i], refs[i], 320)
