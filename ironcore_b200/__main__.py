@@ -1,0 +1,47 @@
+"""Command-line entry: ``ironcore {train,preprocess,rollout} ...`` (also ``python -m ironcore_b200``).
+(Behavioural reference: ironcore/__main__.py:16-89.)"""
+
+from __future__ import annotations
+
+import argparse
+import sys
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(prog="ironcore", description="ironcore_b200: B200-native LLM training framework")
+    sub = parser.add_subparsers(dest="command")
+
+    p_pre = sub.add_parser("preprocess", help="tokenize datasets into data.bin / data.idx.npy")
+    p_pre.add_argument("--config", required=True, help="dataset YAML (UniversalDataConfig)")
+    p_pre.add_argument("--inspect", action="store_true", help="inspect the outputs after preprocessing")
+    p_pre.add_argument("--only-inspect", action="store_true", help="inspect existing outputs, do not preprocess")
+    p_pre.add_argument("--preview", type=int, default=0, help="number of samples to preview")
+
+    p_train = sub.add_parser("train", help="run training from a YAML configuration")
+    p_train.add_argument("--config", required=True, help="training YAML")
+    p_train.add_argument("--rl", action="store_true", help="run the GRPO loop instead of pre-training")
+
+    p_roll = sub.add_parser("rollout", help="sample from a model on the paged KV cache")
+    p_roll.add_argument("--config", required=True)
+    p_roll.add_argument("--prompt", default=None)
+    p_roll.add_argument("--max-new-tokens", type=int, default=64)
+
+    args, extra = parser.parse_known_args(argv)
+    if args.command == "preprocess":
+        from .cli.preprocess import run_preprocess
+
+        return run_preprocess(args) or 0
+    if args.command == "train":
+        from .cli.train import run_train
+
+        return run_train(args, extra)
+    if args.command == "rollout":
+        from .cli.rollout import run_rollout
+
+        return run_rollout(args, extra)
+    parser.print_help()
+    return 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -143,7 +143,7 @@ class PositionalEmbeddingConfig(BaseConfig):
     scaling_factor: float = opt(1.0, "position scaling factor for rotary embeddings")
     offset: int = opt(0, "first position index of a sequence")
     interleaved: bool = opt(True, "rotate (2i, 2i+1) pairs (native layout); False = rotate-half (HF layout)")
-    rotary_fraction: float = opt(1.0, "fraction of each head that is rotated (Phi: 0.4 / 0.5)")
+    rotary_fraction: Optional[float] = opt(None, "fraction of each head that is rotated (None = family default; Phi: 0.4 / 0.5)")
 
 
 @dataclass
@@ -190,10 +190,11 @@ class ModelConfig(BaseConfig):
     fp16_lm_cross_entropy: bool = opt(False, "cross entropy in 16-bit")
     ln_type: str = opt("layernorm", "layernorm | rmsnorm")
     ln_eps: float = opt(1e-5, "norm epsilon")
-    norm_weight_offset: float = opt(0.0, "added to the norm gain (Gemma uses 1.0)")
+    norm_weight_offset: Optional[float] = opt(None, "added to the norm gain (None = family default; Gemma uses 1.0)")
     post_ln: bool = opt(False, "post-LN residual topology")
-    parallel_block: bool = opt(False, "attention and MLP read the same norm output (Phi)")
-    embed_scale: Optional[float] = opt(None, "multiply embeddings (Gemma: sqrt(d_model))")
+    parallel_block: Optional[bool] = opt(None, "attention and MLP read the same norm output (None = family default; Phi)")
+    embed_scale: Optional[float] = opt(None, "multiply embeddings (None = family default; Gemma: sqrt(d_model))")
+    lm_head_bias: Optional[bool] = opt(None, "bias on the LM head (None = family default; Phi)")
     activation_type: str = opt("gelu", "relu|gelu|gelu_tanh|silu|swiglu|geglu|reglu|glu")
     seq_len_q: Optional[int] = opt(None, "unused")
     seq_len_kv: Optional[int] = opt(None, "unused")
@@ -205,6 +206,8 @@ class ModelConfig(BaseConfig):
     merge_file_path: Optional[str] = opt(None, "merge file path")
     vocab_size: Optional[int] = opt(None, "set by the tokenizer (or directly for synthetic data)")
     padded_vocab_size: Optional[int] = opt(None, "vocab padded to vocab_padding_unit * tp")
+    eod_token_id: Optional[int] = opt(None, "end-of-document id (set by the tokenizer)")
+    pad_token_id: Optional[int] = opt(None, "padding id (set by the tokenizer)")
 
     def __post_init__(self):
         if self.ln_type not in ("layernorm", "rmsnorm"):
@@ -287,6 +290,7 @@ class OptimConfig(BaseConfig):
     muon_weight_decay: float = opt(0.0, "decoupled decay on Muon parameters")
     cpu_offload_optimizer: bool = opt(False, "keep Adam moments in pinned host memory")
     master_weights: bool = opt(False, "fp32 master copy of 16-bit parameters")
+    fp32_grad_accum: bool = opt(True, "accumulate gradients in an fp32 buffer (False = parameter dtype)")
 
 
 # --------------------------------------------------------------------------- parallel

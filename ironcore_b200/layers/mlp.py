@@ -1,0 +1,34 @@
+"""Feed-forward block: column-parallel up projection (gate|up fused for gated activations,
+each half sharded separately), activation, row-parallel down projection whose epilogue
+adds the residual. (Behavioural reference: ironcore/layers/mlp.py:19-54.)"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear
+from .activations import Activation
+
+
+class MLP(nn.Module):
+    def __init__(self, d_model: int, d_ffn: int, activation: str, bias: bool = True, dropout: float = 0.0,
+                 dtype=None, device=None, tp_group="default"):
+        super().__init__()
+        self.activation = Activation(activation)
+        mult = 2 if self.activation.gated else 1
+        self.up_proj = ColumnParallelLinear(d_model, d_ffn * mult, bias=bias, concatenated_weights=mult, dtype=dtype,
+                                            device=device, tp_group=tp_group)
+        self.down_proj = RowParallelLinear(d_ffn, d_model, bias=bias, input_is_parallel=True, dtype=dtype,
+                                           device=device, tp_group=tp_group)
+        self.dropout = dropout
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        h = self.activation(self.up_proj(x))
+        if self.dropout > 0 and self.training:
+            y = F.dropout(self.down_proj(h), self.dropout, True)
+            return y if residual is None else y + residual
+        return self.down_proj(h, residual=residual)

@@ -1,0 +1,300 @@
+"""Causal language model: embedding -> transformer stack -> final norm -> LM head ->
+vocab-parallel cross entropy -> masked mean.
+
+``forward(input_ids, labels=None, ...)`` returns the scalar loss when labels are given and
+the (vocab-sharded) logits ``[B, S, V/t]`` otherwise. Document boundaries (positions and
+attention restarting after an end-of-document token) are derived on the device and passed
+to the attention kernel as ``cu_seqlens`` — no ``[B,1,S,S]`` mask is ever built on the
+fused path. Labels equal to ``-100`` are excluded from the loss.
+(Behavioural reference: ironcore/language_model.py:21-234; parameter names follow the
+reference's live model so checkpoints interoperate: ironcore/models/transformer.py:47-72.)
+"""
+
+from __future__ import annotations
+
+import math
+from collections import OrderedDict
+from typing import Callable, Dict, Optional
+
+import torch
+import torch.nn as nn
+
+from ..layers.embedding import LanguageModelEmbedding
+from ..layers.module import BaseModule
+from ..layers.norm import get_norm
+from ..ops import functional as OF
+from ..parallel import collectives as C
+from ..parallel import mesh
+from ..parallel.tensor_parallel import (ColumnParallelLinear, init_linear_weight_, shard_tensor,
+                                        vocab_parallel_cross_entropy)
+from .families import family_of, resolve_family_defaults
+
+IGNORE_INDEX = -100
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float16": torch.float16, "fp16": torch.float16,
+           "half": torch.float16, "float32": torch.float32, "fp32": torch.float32, "float": torch.float32}
+
+
+def get_model_dtype(config) -> torch.dtype:
+    try:
+        return _DTYPES[str(config.model.precision).lower()]
+    except KeyError as exc:
+        raise ValueError(f"unknown precision {config.model.precision}") from exc
+
+
+def masked_mean_loss(per_token_loss: torch.Tensor, loss_mask: torch.Tensor) -> torch.Tensor:
+    """sum(loss * mask) / sum(mask) (reference: ironcore/training_utils.py:142-151)."""
+    mask = loss_mask.reshape(-1).float()
+    return (per_token_loss.reshape(-1).float() * mask).sum() / mask.sum().clamp_min(1.0)
+
+
+class _LinearT(torch.autograd.Function):
+    """y = x @ W^T for a weight stored [out, in] (the tied LM head reads the embedding table)."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        from ..ops import kernels
+
+        ctx.save_for_backward(x, weight)
+        return kernels.mm_nt(x, weight)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops import kernels
+
+        x, weight = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = kernels.mm_nn(dy, weight) if ctx.needs_input_grad[0] else None
+        dw = kernels.mm_tn(dy, x) if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+def linear_t(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    if OF.use_native(x):
+        return _LinearT.apply(x.contiguous(), weight)
+    return x @ weight.t()
+
+
+class LanguageModel(BaseModule):
+    def __init__(self, config, loss_fn: Optional[Callable] = None, device=None):
+        super().__init__(config)
+        m = config.model
+        self.family = resolve_family_defaults(m)
+        self.loss_fn = loss_fn or masked_mean_loss
+        dtype = get_model_dtype(config)
+        self.vocab_size = int(m.vocab_size if m.vocab_size is not None else config.data.vocab_size)
+        tp = mesh.get_tensor_model_parallel_world_size()
+        unit = config.trainer.vocab_padding_unit * tp
+        self.padded_vocab_size = int(m.padded_vocab_size or (math.ceil(self.vocab_size / unit) * unit))
+        m.vocab_size, m.padded_vocab_size = self.vocab_size, self.padded_vocab_size
+        self.tp_group = mesh.get_tensor_model_parallel_group()
+        self.tp_size = tp
+        self.sequence_parallel = mesh.sequence_parallel_enabled()
+        self.seq_len = m.max_seq_len
+        learned_pos = m.positional_embedding.type.lower() == "absolute"
+        if self.family == "DUMMY":
+            from .dummy import DummyModel
+
+            self.embedding = LanguageModelEmbedding(self.padded_vocab_size, self.vocab_size, m.d_model, m.max_seq_len,
+                                                    False, 0.0, None, dtype, device)
+            self.model = DummyModel(config, dtype, device)
+        else:
+            from .transformer import TransformerModel
+
+            self.embedding = LanguageModelEmbedding(self.padded_vocab_size, self.vocab_size, m.d_model,
+                                                    max(m.max_seq_len, 1), learned_pos, m.dropout_embd, m.embed_scale,
+                                                    dtype, device)
+            self.model = TransformerModel(config, dtype, device)
+        self.output_layernorm = get_norm(config, dtype, device)
+        self.untied = bool(m.untie_embed)
+        if self.untied:
+            self.output_layer = ColumnParallelLinear(m.d_model, self.padded_vocab_size, bias=bool(m.lm_head_bias),
+                                                     dtype=dtype, device=device)
+        self.reset_position_ids = m.reset_position_ids
+        self.reset_attention_mask = m.reset_attention_mask
+        self.eod_mask_loss = m.eod_mask_loss
+        self.init_weights()
+
+    # ------------------------------------------------------------------ initialisation
+    def init_weights(self):
+        """normal(0, init_std); residual projections (attn_output, down_proj) use
+        std / sqrt(2 * num_layers); biases zero; norm gains one (or 1 - offset); padded
+        vocabulary rows zero. Sharded weights are slices of the TP=1 tensor, drawn from a
+        CPU generator so every TP size sees the same full matrices.
+        (Behavioural reference: ironcore/layers/module.py:43-163.)"""
+        cfg = self.config
+        std = cfg.init.init_std
+        resid_std = std / math.sqrt(2.0 * max(cfg.model.num_layers, 1))
+        gen = torch.Generator(device="cpu")
+        gen.manual_seed(int(cfg.init.seed))
+        tp_rank, tp_size = mesh.get_tensor_model_parallel_rank(), self.tp_size
+        ep_rank = mesh.get_expert_model_parallel_rank()
+        ep_size = mesh.get_expert_model_parallel_world_size()
+        for name, p in self.named_parameters():
+            if name.endswith("bias"):
+                nn.init.zeros_(p)
+                continue
+            if "layernorm" in name:
+                continue  # gains were set at construction
+            shard_dim = getattr(p, "tp_shard_dim", None)
+            parts = getattr(p, "tp_parts", 1)
+            is_resid = name.endswith("attn_output.weight") or name.endswith("down_proj.weight") \
+                or name.endswith("experts_down")
+            s = resid_std if is_resid else std
+            if getattr(p, "expert_parallel", False):
+                # [E_local, in, out]: draw all experts, keep this rank's slice of the expert dim
+                e_local = p.shape[0]
+                full = torch.empty((e_local * ep_size,) + tuple(p.shape[1:]), dtype=torch.float32)
+                full.normal_(0.0, s, generator=gen)
+                with torch.no_grad():
+                    p.copy_(full[ep_rank * e_local:(ep_rank + 1) * e_local].to(p.dtype))
+                continue
+            full_shape = list(p.shape)
+            if shard_dim is not None and tp_size > 1:
+                full_shape[shard_dim] *= tp_size
+            if p.dim() < 2:
+                with torch.no_grad():
+                    p.copy_(torch.empty(full_shape).normal_(0.0, s, generator=gen).to(p.dtype))
+                continue
+            init_linear_weight_(p, full_shape, s, shard_dim, parts, tp_rank, tp_size, bool(cfg.init.xavier_init), gen)
+        # zero the padded vocabulary rows / columns
+        with torch.no_grad():
+            w = self.embedding.word_embeddings
+            lo = max(self.vocab_size - w.vocab_start, 0)
+            if lo < w.rows_per_partition:
+                w.weight[lo:].zero_()
+            if self.untied:
+                v_local = self.output_layer.out_per_partition
+                start = tp_rank * v_local
+                lo = max(self.vocab_size - start, 0)
+                if lo < v_local:
+                    self.output_layer.weight[:, lo:].zero_()
+
+    # ------------------------------------------------------------------ helpers
+    def _document_layout(self, input_ids: torch.Tensor):
+        """Positions restarting after every end-of-document token and the cumulative
+        document boundaries of the flat token stream (int32, includes batch-row ends)."""
+        eod = self.config.model.eod_token_id
+        b, s = input_ids.shape
+        if eod is None or not (self.reset_position_ids or self.reset_attention_mask):
+            return None, None
+        is_eod = input_ids == eod
+        pos_ids = None
+        if self.reset_position_ids:
+            idx = torch.arange(s, device=input_ids.device).expand(b, s)
+            # a new document starts *after* an EOD token
+            start = torch.where(is_eod, idx + 1, torch.zeros_like(idx))
+            start = torch.cummax(torch.roll(start, 1, dims=1).index_fill_(
+                1, torch.zeros(1, dtype=torch.long, device=input_ids.device), 0), dim=1).values
+            pos_ids = idx - start
+        cu = None
+        if self.reset_attention_mask:
+            flat_end = is_eod.clone()
+            flat_end[:, -1] = True
+            ends = torch.nonzero(flat_end.reshape(-1), as_tuple=False).squeeze(1) + 1
+            cu = torch.cat([torch.zeros(1, dtype=ends.dtype, device=ends.device), ends]).to(torch.int32)
+        return pos_ids, cu
+
+    def _loss_mask(self, input_ids, labels, loss_mask):
+        mask = (labels != IGNORE_INDEX)
+        if loss_mask is not None:
+            mask = mask & (loss_mask.to(torch.bool))
+        m = self.config.model
+        if self.eod_mask_loss and m.eod_token_id is not None:
+            mask = mask & (input_ids != m.eod_token_id)
+        return mask
+
+    def hidden_states(self, input_ids, position_ids=None, cu_seqlens=None, attn_mask=None):
+        """[B, S] ids -> normalised final hidden states, token-major (SP shard when enabled)."""
+        b, s = input_ids.shape
+        if position_ids is None and cu_seqlens is None:
+            position_ids, cu_seqlens = self._document_layout(input_ids)
+        pos_flat = position_ids.reshape(-1).to(torch.int32) if position_ids is not None else None
+        x = self.embedding(input_ids, position_ids)
+        x, aux = self.model(x, s, pos_flat, cu_seqlens, attn_mask)
+        x = self.output_layernorm(x)
+        return x, aux
+
+    def logits_from_hidden(self, x: torch.Tensor) -> torch.Tensor:
+        """token-major hidden [T(_local), d] -> vocab-sharded logits [T, V/t]."""
+        if self.untied:
+            return self.output_layer(x)
+        if self.tp_size > 1:
+            x = C.gather_from_sp(x, self.tp_group) if self.sequence_parallel else C.copy_to_tp(x, self.tp_group)
+        return linear_t(x, self.embedding.word_embeddings.weight)
+
+    def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None,
+                position_ids: Optional[torch.Tensor] = None, cu_seqlens: Optional[torch.Tensor] = None,
+                loss_mask: Optional[torch.Tensor] = None, attn_mask: Optional[torch.Tensor] = None):
+        dev = self.embedding.word_embeddings.weight.device
+        if input_ids.device != dev:
+            input_ids = input_ids.to(dev, non_blocking=True)
+        if labels is not None and labels.device != dev:
+            labels = labels.to(dev, non_blocking=True)
+        b, s = input_ids.shape
+        x, aux = self.hidden_states(input_ids, position_ids, cu_seqlens, attn_mask)
+        logits = self.logits_from_hidden(x)
+        if labels is None:
+            return logits.view(b, s, -1)
+        per_token = vocab_parallel_cross_entropy(logits, labels.reshape(-1).clamp_min(-1), self.vocab_size,
+                                                 tp_group=self.tp_group)
+        mask = self._loss_mask(input_ids, labels, loss_mask)
+        loss = self.loss_fn(per_token.view(b, s), mask)
+        if aux is not None:
+            loss = loss + aux
+        return loss
+
+    # ------------------------------------------------------------------ canonical (checkpoint) names
+    def canonical_state_dict(self) -> "OrderedDict[str, torch.Tensor]":
+        """Local shard under the reference's parameter names: the fused ``linear_qkv`` is split
+        into ``linear_q`` and ``linear_kv`` (K|V halves)."""
+        out = OrderedDict()
+        for name, t in self.state_dict().items():
+            if ".linear_qkv." in name:
+                layer = self.model.layers[int(name.split(".")[2])]
+                qn = layer.heads_local * layer.head_dim
+                q, kv = t.split([qn, t.shape[-1] - qn], dim=-1)
+                out[name.replace("linear_qkv", "linear_q")] = q
+                out[name.replace("linear_qkv", "linear_kv")] = kv
+            else:
+                out[name] = t
+        return out
+
+    def load_canonical_state_dict(self, sd: Dict[str, torch.Tensor], strict: bool = True):
+        fused = {}
+        plain = {}
+        for name, t in sd.items():
+            name = name[7:] if name.startswith("module.") else name
+            if ".linear_q." in name:
+                fused.setdefault(name.replace("linear_q", "linear_qkv"), {})["q"] = t
+            elif ".linear_kv." in name:
+                fused.setdefault(name.replace("linear_kv", "linear_qkv"), {})["kv"] = t
+            else:
+                plain[name] = t
+        for name, parts in fused.items():
+            plain[name] = torch.cat([parts["q"], parts["kv"]], dim=-1)
+        own = self.state_dict()
+        for k in list(plain.keys()):
+            if k in own and plain[k].shape != own[k].shape and plain[k].numel() == own[k].numel():
+                plain[k] = plain[k].reshape(own[k].shape)
+        return self.load_state_dict(plain, strict=strict)
+
+    def canonical_shard_info(self) -> Dict[str, tuple]:
+        """name -> (tp_shard_dim or None, parts) for every canonical tensor (used to merge /
+        split universal checkpoints across TP sizes)."""
+        info = {}
+        params = dict(self.named_parameters())
+        for name in self.canonical_state_dict().keys():
+            if ".linear_q." in name:
+                src = params[name.replace("linear_q", "linear_qkv")]
+                info[name] = (getattr(src, "tp_shard_dim", None), 1)
+            elif ".linear_kv." in name:
+                src = params[name.replace("linear_kv", "linear_qkv")]
+                info[name] = (getattr(src, "tp_shard_dim", None), 2)
+            elif name in params:
+                p = params[name]
+                parts = getattr(p, "tp_parts", 1)
+                info[name] = (getattr(p, "tp_shard_dim", None), parts if isinstance(parts, int) else 1)
+            else:
+                info[name] = (None, 1)
+        return info

@@ -1,0 +1,120 @@
+"""The unified decoder stack.
+
+One ``TransformerLayer`` class serves GPT-2 / Llama / Gemma / Qwen / Phi shapes through
+configuration: pre- or post-norm residual topology, LayerNorm or RMSNorm, MHA / GQA / MQA,
+rotary or learned positions, plain or gated MLP, optional parallel (Phi) block and a
+mixture-of-experts feed-forward. Activations are token-major ``[T, d]`` (``T = batch *
+seq``; a token shard under sequence parallelism), so norms, residuals and dropout run on
+shards and the column / row parallel projections own the gather / reduce-scatter.
+
+Internally q, k and v are one fused projection (``linear_qkv``: one gather, one GEMM);
+checkpoints use the canonical ``linear_q`` / ``linear_kv`` tensors.
+(Behavioural reference: ironcore/models/transformer.py:23-162.)
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+from ..layers.attention import Attention
+from ..layers.mlp import MLP
+from ..layers.norm import get_norm
+from ..layers.positional import RotaryPositionalEmbedding
+from ..parallel import mesh
+from ..parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear, divide
+
+
+class TransformerLayer(nn.Module):
+    def __init__(self, config, layer_idx: int, dtype=None, device=None):
+        super().__init__()
+        m = config.model
+        tp = mesh.get_tensor_model_parallel_world_size()
+        self.layer_idx = layer_idx
+        self.d_model = m.d_model
+        self.head_dim = m.head_dim
+        self.num_heads = m.num_attention_heads
+        self.num_kv_heads = m.num_attention_groups
+        self.heads_local = divide(self.num_heads, tp)
+        self.kv_heads_local = divide(self.num_kv_heads, tp)
+        self.post_ln = m.post_ln
+        self.parallel_block = bool(m.parallel_block)
+        self.dropout_attn = m.dropout_attn
+        q_out = self.num_heads * self.head_dim
+        kv_out = self.num_kv_heads * self.head_dim
+        self.input_layernorm = get_norm(config, dtype, device)
+        self.linear_qkv = ColumnParallelLinear(m.d_model, q_out + 2 * kv_out, bias=bool(m.qkv_bias),
+                                               concatenated_weights=[q_out, kv_out, kv_out], dtype=dtype, device=device)
+        self.attn_output = RowParallelLinear(q_out, m.d_model, bias=not m.no_bias, input_is_parallel=True,
+                                             dtype=dtype, device=device)
+        rotary = None
+        if m.positional_embedding.type.lower() == "rope":
+            pe = m.positional_embedding
+            rotary = RotaryPositionalEmbedding(self.head_dim, pe.base, pe.scaling_factor, pe.offset, pe.interleaved,
+                                               float(pe.rotary_fraction or 1.0))
+        self.rotary_pos_emb = rotary
+        self.attention = Attention(self.heads_local, self.kv_heads_local, self.head_dim, dropout=m.dropout_attn,
+                                   fused=config.trainer.use_flash_attn, causal=True, rotary=rotary)
+        if not self.parallel_block:
+            self.post_attn_layernorm = get_norm(config, dtype, device)
+        moe = m.moe
+        if moe.num_experts > 0 and (layer_idx % max(moe.layer_freq, 1) == 0):
+            from .moe import MoEBlock
+
+            self.mlp = MoEBlock(config, dtype=dtype, device=device)
+            self.is_moe = True
+        else:
+            self.mlp = MLP(m.d_model, m.d_ffn, m.activation_type, bias=not m.no_bias, dropout=m.dropout_mlp,
+                           dtype=dtype, device=device)
+            self.is_moe = False
+
+    def _attend(self, normed, seq_len, pos_ids, cu_seqlens, attn_mask, residual):
+        qkv = self.linear_qkv(normed)
+        ctx = self.attention(qkv, seq_len, pos_ids=pos_ids, cu_seqlens=cu_seqlens, attn_mask=attn_mask)
+        if self.dropout_attn > 0 and self.training:
+            out = F.dropout(self.attn_output(ctx), self.dropout_attn, True)
+            return out if residual is None else out + residual
+        return self.attn_output(ctx, residual=residual)
+
+    def forward(self, x: torch.Tensor, seq_len: int, pos_ids=None, cu_seqlens=None, attn_mask=None):
+        """x: [T_local, d]. Returns (x, aux_loss or None)."""
+        aux = None
+        n1 = self.input_layernorm(x)
+        if self.parallel_block:
+            a = self._attend(n1, seq_len, pos_ids, cu_seqlens, attn_mask, residual=x)
+            out = self.mlp(n1, residual=a)
+            if self.is_moe:
+                out, aux = out
+            return out, aux
+        res1 = n1 if self.post_ln else x
+        x = self._attend(n1, seq_len, pos_ids, cu_seqlens, attn_mask, residual=res1)
+        n2 = self.post_attn_layernorm(x)
+        res2 = n2 if self.post_ln else x
+        out = self.mlp(n2, residual=res2)
+        if self.is_moe:
+            out, aux = out
+        return out, aux
+
+
+class TransformerModel(nn.Module):
+    def __init__(self, config, dtype=None, device=None):
+        super().__init__()
+        self.config = config
+        self.layers = nn.ModuleList([TransformerLayer(config, i, dtype, device) for i in range(config.model.num_layers)])
+        self.recompute = config.operation.activation_recompute
+        self.use_reentrant = config.operation.recompute_strategy == "optimized"
+
+    def forward(self, x, seq_len: int, pos_ids=None, cu_seqlens=None, attn_mask=None):
+        aux_total = None
+        for layer in self.layers:
+            if self.recompute and self.training:
+                x, aux = checkpoint(layer, x, seq_len, pos_ids, cu_seqlens, attn_mask, use_reentrant=self.use_reentrant)
+            else:
+                x, aux = layer(x, seq_len, pos_ids, cu_seqlens, attn_mask)
+            if aux is not None:
+                aux_total = aux if aux_total is None else aux_total + aux
+        return x, aux_total

@@ -1,0 +1,203 @@
+"""Muon for 2-D hidden weight matrices, in distributed form.
+
+Per matrix:  m <- mu * m + g ;  u = g + mu * m (Nesterov) or m ;
+X = NewtonSchulz5(u)  (quintic iteration in bf16 on the normalised matrix, computed on the
+wide orientation):  A = X X^T ; B = b A + c A A ; X <- a X + B X   with
+(a, b, c) = (3.4445, -4.7750, 2.0315);  W <- W (1 - lr wd) - lr * sqrt(max(1, fan_out/fan_in)) * X.
+
+Fused tensors (q|k|v, gate|up) and stacked expert weights are orthogonalised per logical
+matrix. Distribution: every logical matrix has an owner rank in the data-parallel group
+(greedy balance by Newton-Schulz FLOPs); the owner keeps the momentum, runs the iteration
+on the (TP-gathered) matrix and publishes the update through a summed update buffer, so
+momentum memory and Newton-Schulz time divide by the number of ranks. On CUDA the three
+matrix products per iteration are the tcgen05 GEMM.
+(No counterpart in the reference; semantics follow the published Muon optimizer.)
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as OF
+from ..ops import kernels
+
+NS_COEFFS = (3.4445, -4.7750, 2.0315)
+
+
+def newton_schulz_reference(g: torch.Tensor, steps: int = 5, eps: float = 1e-7, dtype=torch.bfloat16) -> torch.Tensor:
+    """Plain PyTorch quintic Newton-Schulz orthogonalisation of a 2-D matrix."""
+    a, b, c = NS_COEFFS
+    x = g.to(dtype)
+    transposed = x.shape[0] > x.shape[1]
+    if transposed:
+        x = x.t()
+    x = x / (x.float().norm() + eps).to(dtype)
+    for _ in range(steps):
+        A = x @ x.t()
+        B = b * A + c * (A @ A)
+        x = a * x + B @ x
+    return x.t() if transposed else x
+
+
+def newton_schulz(g: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.Tensor:
+    """Newton-Schulz on the native GEMM (CUDA, dims multiples of 8) or the reference path."""
+    if not (g.is_cuda and g.shape[0] % 8 == 0 and g.shape[1] % 8 == 0):
+        return newton_schulz_reference(g, steps, eps, torch.bfloat16 if g.is_cuda else torch.float32).to(g.dtype)
+    a, b, c = NS_COEFFS
+    x = g.to(torch.bfloat16)
+    transposed = x.shape[0] > x.shape[1]
+    if transposed:
+        x = x.t().contiguous()
+    x = (x / (x.float().norm() + eps).to(torch.bfloat16)).contiguous()
+    for _ in range(steps):
+        A = kernels.mm_nt(x, x)                 # X X^T   (both operands K-major)
+        A2 = kernels.mm_nn(A, A)                # A A
+        B = (b * A + c * A2).contiguous()
+        x = kernels.mm_nn(B, x, residual=(a * x).contiguous())   # B X + a X in the GEMM epilogue
+    return (x.t() if transposed else x).to(g.dtype)
+
+
+class _Matrix:
+    __slots__ = ("slot", "group_idx", "expert", "col_lo", "col_hi", "full_shape", "owner", "momentum", "tp_dim")
+
+
+class MuonState:
+    def __init__(self, engine, config):
+        self.engine = engine
+        o = config.optim
+        self.momentum = o.muon_momentum
+        self.nesterov = o.nesterov
+        self.steps = o.muon_ns_steps
+        self.weight_decay = o.muon_weight_decay
+        self.tp_group = engine.tp_group
+        self.tp_size = engine.tp_size
+        self.matrices: List[_Matrix] = []
+        for gi, g in enumerate(engine.groups):
+            for s in g.slots:
+                if g.regions[s.region].kind != "muon":
+                    continue
+                p = s.param
+                parts = getattr(p, "tp_parts", 1)
+                tp_dim = getattr(p, "tp_shard_dim", None)
+                experts = range(p.shape[0]) if p.dim() == 3 else [None]
+                cols = p.shape[-1]
+                if isinstance(parts, int):
+                    sizes = [cols // parts] * parts
+                else:
+                    sizes = [x // self.tp_size if tp_dim is not None and self.tp_size > 1 else x for x in parts]
+                for e in experts:
+                    lo = 0
+                    for sz in sizes:
+                        mtx = _Matrix()
+                        mtx.slot, mtx.group_idx, mtx.expert = s, gi, e
+                        mtx.col_lo, mtx.col_hi = lo, lo + sz
+                        rows = p.shape[-2]
+                        fr, fc = rows, sz
+                        if tp_dim is not None and self.tp_size > 1 and p.dim() == 2:
+                            if tp_dim == 0:
+                                fr = rows * self.tp_size
+                            else:
+                                fc = sz * self.tp_size
+                        mtx.full_shape = (fr, fc)
+                        mtx.tp_dim = tp_dim if (self.tp_size > 1 and p.dim() == 2) else None
+                        mtx.owner, mtx.momentum = 0, None
+                        self.matrices.append(mtx)
+                        lo += sz
+        # greedy balance of Newton-Schulz cost over the reduction group of each flat group
+        for gi, g in enumerate(engine.groups):
+            mats = [m for m in self.matrices if m.group_idx == gi]
+            load = [0.0] * max(g.dp, 1)
+            for m in sorted(mats, key=lambda t: -self._cost(t.full_shape)):
+                r = min(range(len(load)), key=lambda i: load[i])
+                m.owner = r
+                load[r] += self._cost(m.full_shape)
+
+    @staticmethod
+    def _cost(shape) -> float:
+        r, c = min(shape), max(shape)
+        return 4.0 * r * r * c + 2.0 * r * r * r
+
+    def _view(self, buf: torch.Tensor, m: _Matrix) -> torch.Tensor:
+        s = m.slot
+        t = buf[s.offset:s.offset + s.numel].view(s.param.shape)
+        if m.expert is not None:
+            t = t[m.expert]
+        return t[:, m.col_lo:m.col_hi]
+
+    def _gather_tp(self, local: torch.Tensor, m: _Matrix) -> torch.Tensor:
+        if m.tp_dim is None:
+            return local
+        parts = [torch.empty_like(local) for _ in range(self.tp_size)]
+        dist.all_gather(parts, local.contiguous(), group=self.tp_group)
+        return torch.cat(parts, dim=m.tp_dim)
+
+    def _slice_tp(self, full: torch.Tensor, m: _Matrix) -> torch.Tensor:
+        if m.tp_dim is None:
+            return full
+        r = dist.get_rank(self.tp_group)
+        return full.chunk(self.tp_size, dim=m.tp_dim)[r]
+
+    @torch.no_grad()
+    def step(self, coef: torch.Tensor, lr: float):
+        eng = self.engine
+        upd_bufs = []
+        for g in eng.groups:
+            upd_bufs.append(torch.zeros_like(g.param_buf) if g.dp > 1 else None)
+        for m in self.matrices:
+            g = eng.groups[m.group_idx]
+            mine = (m.owner == g.dp_rank)
+            if not mine and m.tp_dim is None:
+                continue
+            grad_local = self._view(g.grad_buf, m)
+            if m.tp_dim is not None:
+                grad_full = self._gather_tp(grad_local.contiguous(), m)  # collective: every TP rank joins
+                if not mine:
+                    continue
+            else:
+                grad_full = grad_local
+            gf = grad_full.float() * (coef.to(grad_full.device) / g.dp)
+            if m.momentum is None:
+                m.momentum = torch.zeros_like(gf)
+            m.momentum.mul_(self.momentum).add_(gf)
+            u = gf.add(m.momentum, alpha=self.momentum) if self.nesterov else m.momentum
+            x = newton_schulz(u, self.steps)
+            fan_in, fan_out = m.full_shape
+            scale = math.sqrt(max(1.0, fan_out / fan_in))
+            delta = self._slice_tp((-lr * scale) * x.float(), m)
+            target = upd_bufs[m.group_idx]
+            if target is None:
+                w = self._view(g.param_buf, m)
+                if self.weight_decay:
+                    w.mul_(1 - lr * self.weight_decay)
+                w.add_(delta.to(w.dtype))
+            else:
+                self._view(target, m).copy_(delta.to(target.dtype))
+        for g, upd in zip(eng.groups, upd_bufs):
+            if upd is None:
+                continue
+            for r in g.regions:
+                if r.kind == "muon" and r.end > r.start:
+                    dist.all_reduce(upd[r.start:r.end], group=g.reduce_group)
+                    w = g.param_buf[r.start:r.end]
+                    if self.weight_decay:
+                        w.mul_(1 - lr * self.weight_decay)
+                    w.add_(upd[r.start:r.end])
+
+    def state_dict(self) -> Dict[str, torch.Tensor]:
+        out = {}
+        for i, m in enumerate(self.matrices):
+            if m.momentum is not None:
+                key = f"{m.slot.name}|{m.expert}|{m.col_lo}"
+                out[key] = m.momentum.detach().cpu()
+        return out
+
+    def load_state_dict(self, sd: Dict[str, torch.Tensor]):
+        for m in self.matrices:
+            key = f"{m.slot.name}|{m.expert}|{m.col_lo}"
+            if key in sd:
+                g = self.engine.groups[m.group_idx]
+                m.momentum = sd[key].to(g.device).float()
