@@ -1,0 +1,485 @@
+// Flash attention backward for sm_100a (causal / full, GQA, cu_seqlens, head_dim 64/128).
+//
+// One CTA owns a 128-row K/V tile of one KV head and walks every query head of the group
+// and every query tile that can see it. Per step five tcgen05 GEMMs run on tiles that are
+// loaded once: S = Q K^T and dP = dO V^T (K-major reads), then dV += P^T dO, dK += dS^T Q
+// and dQ = dS K, which read the *same* shared-memory bytes through MN-major descriptors,
+// so nothing is transposed or copied. TMEM holds S, dP, dV and dK (4 x 128 columns for
+// head_dim 128); dQ reuses the S columns once the softmax warps have consumed S.
+// Warps 2-5 own one query row each: P = exp2(S*scale - lse), dS = P (dP - delta) scale,
+// written as bf16 into 128-byte-swizzled tiles; the same threads drain dQ with fp32 vector
+// atomics into a zeroed scratch (converted to 16-bit by a follow-up kernel) and, at the
+// end, dK / dV (TMEM lane == kv row). dK/dV need no atomics: the group's heads are
+// accumulated in place. Every wait is bounded (status word + drain on timeout).
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace icb {
+
+constexpr int kFbThreads = 192;
+constexpr int kFbTmemCols = 512;
+
+int make_head_tmap(CUtensorMap* tm, const void* base, int hd, int heads, long long tokens, long long row_stride,
+                   int dtype);
+
+struct FlashBwdArgs {
+  int batch, seq_len, hq, hkv;
+  const int* cu_seqlens;
+  const float* lse;      // [hq, T]
+  const float* delta;    // [hq, T]  rowsum(dO * O)
+  float* dq_acc;         // [T, hq, HD] fp32, zero-initialised
+  void* dk;              // first element of dK inside rows of dkv_stride elements
+  void* dv;
+  long long dkv_stride;
+  long long total_tokens;
+  float scale, scale_log2;
+  int causal;
+  int in_fmt;
+  int* status;
+};
+
+template <int HD>
+struct FbSmem {
+  static constexpr int kChunks = HD / 64;
+  static constexpr int tile_bytes = 128 * HD * 2;
+  static constexpr int p_bytes = 128 * 128 * 2;
+  static constexpr int k_off = 0;
+  static constexpr int v_off = k_off + tile_bytes;
+  static constexpr int q_off = v_off + tile_bytes;
+  static constexpr int do_off = q_off + tile_bytes;
+  static constexpr int p_off = do_off + tile_bytes;
+  static constexpr int ds_off = p_off + p_bytes;
+  static constexpr int bar_off = ds_off + p_bytes;
+  static constexpr int total = bar_off + 256 + 1024;
+};
+
+__device__ __forceinline__ float fast_exp2_b(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kFbThreads, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                 const FlashBwdArgs args) {
+  using L = FbSmem<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem + L::k_off;
+  uint8_t* sV = smem + L::v_off;
+  uint8_t* sQ = smem + L::q_off;
+  uint8_t* sDO = smem + L::do_off;
+  uint8_t* sP = smem + L::p_off;
+  uint8_t* sDS = smem + L::ds_off;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::bar_off);
+  uint64_t* kv_full = bars;
+  uint64_t* q_full = bars + 1;
+  uint64_t* q_empty = bars + 2;
+  uint64_t* do_full = bars + 3;
+  uint64_t* do_empty = bars + 4;
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* pds_full = bars + 6;
+  uint64_t* dq_full = bars + 7;
+  uint64_t* dq_empty = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kv_head = blockIdx.y;
+  const int b = blockIdx.z;
+  const int group = args.hq / args.hkv;
+
+  int seq_start, seq_len;
+  if (args.cu_seqlens != nullptr) {
+    seq_start = args.cu_seqlens[b];
+    seq_len = args.cu_seqlens[b + 1] - seq_start;
+  } else {
+    seq_start = b * args.seq_len;
+    seq_len = args.seq_len;
+  }
+  const int n_tiles = (seq_len + 127) >> 7;
+  const int jt = blockIdx.x;  // kv tile; low tiles (most work under a causal mask) are scheduled first
+  if (jt >= n_tiles) return;
+  const int kv0 = jt * 128;
+  const int i_begin = args.causal ? jt : 0;
+  const int iters_per_head = n_tiles - i_begin;
+  const int n_iters = iters_per_head * group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
+    mbar_init(do_full, 1);
+    mbar_init(do_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 128);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_empty, 128);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmDO);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kFbTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tm_s = tmem_base;          // also dQ
+  const uint32_t tm_dp = tmem_base + 128;
+  const uint32_t tm_dv = tmem_base + 256;
+  const uint32_t tm_dk = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * L::tile_bytes);
+#pragma unroll
+      for (int c = 0; c < L::kChunks; ++c) {
+        tma_load_3d(sK + c * 16384, &tmK, kv_full, c * 64, kv_head, seq_start + kv0);
+        tma_load_3d(sV + c * 16384, &tmV, kv_full, c * 64, kv_head, seq_start + kv0);
+      }
+      for (int it = 0; it < n_iters; ++it) {
+        const uint32_t ph = it & 1;
+        const int head = kv_head * group + it / iters_per_head;
+        const int t0 = seq_start + (i_begin + it % iters_per_head) * 128;
+        mbar_wait(q_empty, ph ^ 1, abort_flag, args.status, kTimeoutSmemEmpty);
+        mbar_expect_tx(q_full, L::tile_bytes);
+#pragma unroll
+        for (int c = 0; c < L::kChunks; ++c) tma_load_3d(sQ + c * 16384, &tmQ, q_full, c * 64, head, t0);
+        mbar_wait(do_empty, ph ^ 1, abort_flag, args.status, kTimeoutSmemEmpty);
+        mbar_expect_tx(do_full, L::tile_bytes);
+#pragma unroll
+        for (int c = 0; c < L::kChunks; ++c) tma_load_3d(sDO + c * 16384, &tmDO, do_full, c * 64, head, t0);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_kk = umma_idesc(128, 128, args.in_fmt, 0, 0);   // S, dP
+      const uint32_t idesc_mm = umma_idesc(128, HD, args.in_fmt, 1, 1);    // dV, dK
+      const uint32_t idesc_km = umma_idesc(128, HD, args.in_fmt, 0, 1);    // dQ
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aDO = smem_u32(sDO);
+      const uint32_t aP = smem_u32(sP), aDS = smem_u32(sDS);
+      mbar_wait(kv_full, 0, abort_flag, args.status, kTimeoutSmemFull);
+      for (int it = 0; it < n_iters; ++it) {
+        const uint32_t ph = it & 1;
+        mbar_wait(q_full, ph, abort_flag, args.status, kTimeoutSmemFull);
+        mbar_wait(dq_empty, ph ^ 1, abort_flag, args.status, kTimeoutTmemEmpty);
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_ss(tm_s, umma_desc_sw128(aQ + off, 16, 1024), umma_desc_sw128(aK + off, 16, 1024), idesc_kk,
+                  k > 0 ? 1u : 0u);
+        }
+        mbar_wait(do_full, ph, abort_flag, args.status, kTimeoutSmemFull);
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_ss(tm_dp, umma_desc_sw128(aDO + off, 16, 1024), umma_desc_sw128(aV + off, 16, 1024), idesc_kk,
+                  k > 0 ? 1u : 0u);
+        }
+        umma_commit(sdp_full);
+        mbar_wait(pds_full, ph, abort_flag, args.status, kTimeoutLocalFlag);
+        tc_fence_after();
+        const uint32_t acc = it > 0 ? 1u : 0u;
+        // dV += P^T dO   (A = P read MN-major: M = kv, K = q rows; B = dO read MN-major)
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(tm_dv, umma_desc_sw128(aP + k * 2048, 16384, 1024), umma_desc_sw128(aDO + k * 2048, 16384, 1024),
+                  idesc_mm, (acc | (k > 0 ? 1u : 0u)));
+        umma_commit(do_empty);
+        // dK += dS^T Q
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(tm_dk, umma_desc_sw128(aDS + k * 2048, 16384, 1024), umma_desc_sw128(aQ + k * 2048, 16384, 1024),
+                  idesc_mm, (acc | (k > 0 ? 1u : 0u)));
+        umma_commit(q_empty);
+        // dQ = dS K   (A = dS read K-major: M = q rows, K = kv; B = K tile read MN-major)
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(tm_s, umma_desc_sw128(aDS + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                  umma_desc_sw128(aK + k * 2048, 16384, 1024), idesc_km, k > 0 ? 1u : 0u);
+        umma_commit(dq_full);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
+    const float log2e = 1.4426950408889634f;
+    for (int it = 0; it < n_iters; ++it) {
+      const uint32_t ph = it & 1;
+      const int head = kv_head * group + it / iters_per_head;
+      const int it_q = i_begin + it % iters_per_head;
+      const int q_idx = it_q * 128 + row;
+      const bool q_valid = q_idx < seq_len;
+      const long long tok = (long long)seq_start + q_idx;
+      float lse2 = 0.f, dlt = 0.f;
+      if (q_valid) {
+        lse2 = args.lse[(size_t)head * args.total_tokens + tok] * log2e;
+        dlt = args.delta[(size_t)head * args.total_tokens + tok];
+      }
+      const bool need_mask = (args.causal && it_q == jt) || (kv0 + 128 > seq_len);
+      mbar_wait(sdp_full, ph, abort_flag, args.status, kTimeoutTmemFull);
+      tc_fence_after();
+      uint8_t* prow = sP + row * 128;
+      uint8_t* dsrow = sDS + row * 128;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sr[32], dr[32];
+        tmem_ld_32x32(tm_s + lane_off + c * 32, sr);
+        tmem_ld_32x32(tm_dp + lane_off + c * 32, dr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float p[8], ds[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int col = c * 32 + g * 8 + i;
+            float pv = fast_exp2_b(__uint_as_float(sr[g * 8 + i]) * args.scale_log2 - lse2);
+            bool keep = q_valid;
+            if (need_mask) {
+              const int kv_idx = kv0 + col;
+              if (kv_idx >= seq_len || (args.causal && kv_idx > q_idx)) keep = false;
+            }
+            pv = keep ? pv : 0.f;
+            p[i] = pv;
+            ds[i] = pv * (__uint_as_float(dr[g * 8 + i]) - dlt) * args.scale;
+          }
+          uint4 up, ud;
+          if (args.in_fmt == 1) {
+            up.x = pack_bf16x2(p[0], p[1]); up.y = pack_bf16x2(p[2], p[3]);
+            up.z = pack_bf16x2(p[4], p[5]); up.w = pack_bf16x2(p[6], p[7]);
+            ud.x = pack_bf16x2(ds[0], ds[1]); ud.y = pack_bf16x2(ds[2], ds[3]);
+            ud.z = pack_bf16x2(ds[4], ds[5]); ud.w = pack_bf16x2(ds[6], ds[7]);
+          } else {
+            up.x = pack_f16x2(p[0], p[1]); up.y = pack_f16x2(p[2], p[3]);
+            up.z = pack_f16x2(p[4], p[5]); up.w = pack_f16x2(p[6], p[7]);
+            ud.x = pack_f16x2(ds[0], ds[1]); ud.y = pack_f16x2(ds[2], ds[3]);
+            ud.z = pack_f16x2(ds[4], ds[5]); ud.w = pack_f16x2(ds[6], ds[7]);
+          }
+          const int col0 = c * 32 + g * 8;
+          const int off = (col0 >> 6) * 16384 + ((((col0 & 63) >> 3) ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(prow + off) = up;
+          *reinterpret_cast<uint4*>(dsrow + off) = ud;
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(pds_full);
+      // drain dQ
+      mbar_wait(dq_full, ph, abort_flag, args.status, kTimeoutTmemFull);
+      tc_fence_after();
+      float* dqrow = args.dq_acc + ((size_t)tok * args.hq + head) * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32(tm_s + lane_off + c * 32, o);
+        tmem_ld_wait();
+        if (q_valid) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            float4 v4 = make_float4(__uint_as_float(o[g * 4]), __uint_as_float(o[g * 4 + 1]),
+                                    __uint_as_float(o[g * 4 + 2]), __uint_as_float(o[g * 4 + 3]));
+            atomicAdd(reinterpret_cast<float4*>(dqrow + c * 32 + g * 4), v4);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(dq_empty);
+    }
+    // ---- epilogue: dK, dV (lane == kv row). The last dq_full wait implies every MMA finished.
+    {
+      const int kv_idx = kv0 + row;
+      const bool valid = kv_idx < seq_len;
+      const long long tok = (long long)seq_start + kv_idx;
+      uint8_t* dkrow = reinterpret_cast<uint8_t*>(args.dk) + ((size_t)tok * args.dkv_stride + (size_t)kv_head * HD) * 2;
+      uint8_t* dvrow = reinterpret_cast<uint8_t*>(args.dv) + ((size_t)tok * args.dkv_stride + (size_t)kv_head * HD) * 2;
+      tc_fence_after();
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t tm = which == 0 ? tm_dk : tm_dv;
+        uint8_t* orow = which == 0 ? dkrow : dvrow;
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32(tm + lane_off + c * 32, o);
+          tmem_ld_wait();
+          if (valid) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(o[g * 8 + i]);
+              uint4 u;
+              if (args.in_fmt == 1) {
+                u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
+                u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+              } else {
+                u.x = pack_f16x2(f[0], f[1]); u.y = pack_f16x2(f[2], f[3]);
+                u.z = pack_f16x2(f[4], f[5]); u.w = pack_f16x2(f[6], f[7]);
+              }
+              *reinterpret_cast<uint4*>(orow + (c * 32 + g * 8) * 2) = u;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) { __nanosleep(1000); }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kFbTmemCols);
+  }
+}
+
+// delta[h, t] = sum_d dO[t,h,d] * O[t,h,d]; one warp per (token, head).
+template <bool BF16>
+__global__ void flash_delta_kernel(const uint16_t* __restrict__ dO, const uint16_t* __restrict__ O,
+                                   float* __restrict__ delta, long long T, int hq, int hd) {
+  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= T * hq) return;
+  const long long t = w / hq;
+  const int h = (int)(w - t * hq);
+  const size_t base = ((size_t)t * hq + h) * hd;
+  float s = 0.f;
+  for (int i = lane * 2; i < hd; i += 64) {
+    const uint32_t a = *reinterpret_cast<const uint32_t*>(dO + base + i);
+    const uint32_t b = *reinterpret_cast<const uint32_t*>(O + base + i);
+    float2 fa, fb;
+    if (BF16) { fa = unpack_bf16x2(a); fb = unpack_bf16x2(b); }
+    else {
+      fa = __half22float2(*reinterpret_cast<const __half2*>(&a));
+      fb = __half22float2(*reinterpret_cast<const __half2*>(&b));
+    }
+    s += fa.x * fb.x + fa.y * fb.y;
+  }
+  s = warp_sum(s);
+  if (lane == 0) delta[(size_t)h * T + t] = s;
+}
+
+// fp32 [T, width] -> 16-bit rows of pitch out_stride
+template <bool BF16>
+__global__ void flash_dq_convert_kernel(const float* __restrict__ acc, uint16_t* __restrict__ out, long long T,
+                                        int width, long long out_stride) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int vecs = width >> 3;
+  if (idx >= T * vecs) return;
+  const long long t = idx / vecs;
+  const int v = (int)(idx - t * vecs);
+  const float4 a = *reinterpret_cast<const float4*>(acc + (size_t)t * width + v * 8);
+  const float4 b = *reinterpret_cast<const float4*>(acc + (size_t)t * width + v * 8 + 4);
+  uint4 u;
+  if (BF16) {
+    u.x = pack_bf16x2(a.x, a.y); u.y = pack_bf16x2(a.z, a.w); u.z = pack_bf16x2(b.x, b.y); u.w = pack_bf16x2(b.z, b.w);
+  } else {
+    u.x = pack_f16x2(a.x, a.y); u.y = pack_f16x2(a.z, a.w); u.z = pack_f16x2(b.x, b.y); u.w = pack_f16x2(b.z, b.w);
+  }
+  *reinterpret_cast<uint4*>(out + (size_t)t * out_stride + v * 8) = u;
+}
+
+template <int HD>
+static int launch_flash_bwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                            const CUtensorMap& tmDO, const FlashBwdArgs& args, dim3 grid, cudaStream_t stream) {
+  static bool configured = false;
+  auto kern = flash_bwd_kernel<HD>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FbSmem<HD>::total);
+    if (e != cudaSuccess) return -(int)e;
+    configured = true;
+  }
+  kern<<<grid, kFbThreads, FbSmem<HD>::total, stream>>>(tmQ, tmK, tmV, tmDO, args);
+  return check_launch("flash_bwd_kernel");
+}
+
+}  // namespace icb
+
+using namespace icb;
+
+// Scratch: delta fp32 [hq * T] and dq_acc fp32 [T * hq * hd] (zeroed here). dq/dk/dv point at the
+// first element of each gradient inside rows of dqkv_stride elements (packed layout or separate).
+ICB_API int icb_flash_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out,
+                          const float* lse, void* dq, void* dk, void* dv, float* delta, float* dq_acc, int batch,
+                          int seq_len, long long total_tokens, int hq, int hkv, int hd, long long q_stride,
+                          long long kv_stride, long long dq_stride, long long dkv_stride, const int* cu_seqlens,
+                          int causal, float scale, int dtype, int* status, void* stream_) {
+  if (hd != 64 && hd != 128) return -2;
+  if (hq % hkv != 0) return -3;
+  if (batch <= 0 || seq_len <= 0) return 0;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const bool bf16 = dtype == kBF16;
+  {
+    const long long warps = total_tokens * hq;
+    const int th = 256;
+    const long long blocks = (warps * 32 + th - 1) / th;
+    if (bf16)
+      flash_delta_kernel<true><<<(unsigned)blocks, th, 0, stream>>>(reinterpret_cast<const uint16_t*>(dout),
+                                                                   reinterpret_cast<const uint16_t*>(out), delta,
+                                                                   total_tokens, hq, hd);
+    else
+      flash_delta_kernel<false><<<(unsigned)blocks, th, 0, stream>>>(reinterpret_cast<const uint16_t*>(dout),
+                                                                    reinterpret_cast<const uint16_t*>(out), delta,
+                                                                    total_tokens, hq, hd);
+    int rc = check_launch("flash_delta");
+    if (rc) return rc;
+  }
+  cudaError_t e = cudaMemsetAsync(dq_acc, 0, (size_t)total_tokens * hq * hd * sizeof(float), stream);
+  if (e != cudaSuccess) return -(int)e;
+
+  CUtensorMap tmQ, tmK, tmV, tmDO;
+  int rc = make_head_tmap(&tmQ, q, hd, hq, total_tokens, q_stride, dtype);
+  if (rc) return rc;
+  rc = make_head_tmap(&tmK, k, hd, hkv, total_tokens, kv_stride, dtype);
+  if (rc) return rc;
+  rc = make_head_tmap(&tmV, v, hd, hkv, total_tokens, kv_stride, dtype);
+  if (rc) return rc;
+  rc = make_head_tmap(&tmDO, dout, hd, hq, total_tokens, (long long)hq * hd, dtype);
+  if (rc) return rc;
+  FlashBwdArgs a;
+  a.batch = batch; a.seq_len = seq_len; a.hq = hq; a.hkv = hkv;
+  a.cu_seqlens = cu_seqlens;
+  a.lse = lse; a.delta = delta; a.dq_acc = dq_acc;
+  a.dk = dk; a.dv = dv; a.dkv_stride = dkv_stride;
+  a.total_tokens = total_tokens;
+  a.scale = scale;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.causal = causal;
+  a.in_fmt = bf16 ? 1 : 0;
+  a.status = status;
+  dim3 grid((seq_len + 127) / 128, hkv, batch);
+  rc = (hd == 64) ? launch_flash_bwd<64>(tmQ, tmK, tmV, tmDO, a, grid, stream)
+                  : launch_flash_bwd<128>(tmQ, tmK, tmV, tmDO, a, grid, stream);
+  if (rc) return rc;
+  {
+    const int width = hq * hd;
+    const long long n = total_tokens * (width / 8);
+    const int th = 256;
+    const long long blocks = (n + th - 1) / th;
+    if (bf16)
+      flash_dq_convert_kernel<true><<<(unsigned)blocks, th, 0, stream>>>(dq_acc, reinterpret_cast<uint16_t*>(dq),
+                                                                        total_tokens, width, dq_stride);
+    else
+      flash_dq_convert_kernel<false><<<(unsigned)blocks, th, 0, stream>>>(dq_acc, reinterpret_cast<uint16_t*>(dq),
+                                                                         total_tokens, width, dq_stride);
+  }
+  return check_launch("flash_dq_convert");
+}

@@ -18,6 +18,10 @@ class SyntheticTokenStream:
         self.pin = torch.cuda.is_available() if pin is None else pin
         self.num_batches = num_batches
         self._count = 0
+        # rotating pool of pinned staging buffers: a buffer is reused only after `depth` later
+        # batches were produced, by which time its asynchronous copy has long been consumed
+        self._pool = []
+        self._depth = 256
 
     def __iter__(self) -> Iterator[Dict[str, torch.Tensor]]:
         return self
@@ -26,8 +30,13 @@ class SyntheticTokenStream:
         if self.num_batches is not None and self._count >= self.num_batches:
             raise StopIteration
         self._count += 1
-        tokens = torch.randint(0, self.vocab_size, (self.micro_batch, self.seq_len + 1), generator=self.gen,
-                               dtype=torch.int64)
         if self.pin:
-            tokens = tokens.pin_memory()
+            slot = (self._count - 1) % self._depth
+            if slot >= len(self._pool):
+                self._pool.append(torch.empty((self.micro_batch, self.seq_len + 1), dtype=torch.int64).pin_memory())
+            tokens = self._pool[slot]
+            torch.randint(0, self.vocab_size, tokens.shape, generator=self.gen, dtype=torch.int64, out=tokens)
+        else:
+            tokens = torch.randint(0, self.vocab_size, (self.micro_batch, self.seq_len + 1), generator=self.gen,
+                                   dtype=torch.int64)
         return {"input_ids": tokens[:, :-1], "labels": tokens[:, 1:]}

