@@ -331,3 +331,79 @@ ICB_API int icb_norm_bwd(const void* dy, const void* x, const void* w, const flo
   }
   return check_launch("norm_bwd_reduce");
 }
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant of the backward pass (declared and documented in no_alloc.h).
+// ---------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+namespace icb {
+// Partial sums of dw (first half) and db (second half); lives in the library's device image.
+static __device__ __align__(256) float g_norm_bwd_scratch[2 * ICB_NOALLOC_PARTS * ICB_NOALLOC_MAX_D];
+
+// The array's name is only a host-side stand-in for the symbol: the device address has to be
+// asked for, once per device, with that device current.
+static float* noalloc_scratch_for_current_device(int* rc) {
+  static float* cache[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    *rc = ICB_NOALLOC_SETUP_FAILED;
+    return nullptr;
+  }
+  if (cache[dev] == nullptr) {
+    float* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_norm_bwd_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      fprintf(stderr, "[ironcore_b200] icb_norm_bwd_noalloc: cudaGetSymbolAddress failed: %s\n",
+              cudaGetErrorString(e));
+      *rc = ICB_NOALLOC_SETUP_FAILED;
+      return nullptr;
+    }
+    cache[dev] = p;
+  }
+  *rc = 0;
+  return cache[dev];
+}
+}  // namespace icb
+
+ICB_API int icb_norm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                                 const void* dres_in, void* dx, void* dw, void* db, int M, int D, float w_offset,
+                                 int rms, int dtype, int grad_f32, int accumulate, void* stream) {
+  if (M <= 0) return 0;
+  if (D % 8 != 0) return -2;
+  if (D > ICB_NOALLOC_MAX_D) {
+    fprintf(stderr,
+            "[ironcore_b200] icb_norm_bwd_noalloc: row length %d exceeds the built-in scratch limit of %d; "
+            "use icb_norm_bwd with a caller-provided scratch buffer\n", D, ICB_NOALLOC_MAX_D);
+    return ICB_NOALLOC_TOO_LARGE;
+  }
+  int rc = 0;
+  float* scratch = noalloc_scratch_for_current_device(&rc);
+  if (scratch == nullptr) return rc;
+  const int vpt = (D / 8 + kNormThreads - 1) / kNormThreads;
+  const int grid = M < ICB_NOALLOC_PARTS ? M : ICB_NOALLOC_PARTS;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  float* dwp = scratch;
+  float* dbp = (db != nullptr) ? scratch + (size_t)ICB_NOALLOC_PARTS * ICB_NOALLOC_MAX_D : nullptr;
+  auto DY = reinterpret_cast<const uint16_t*>(dy);
+  auto X = reinterpret_cast<const uint16_t*>(x);
+  auto W = reinterpret_cast<const uint16_t*>(w);
+  auto DR = reinterpret_cast<const uint16_t*>(dres_in);
+  auto DX = reinterpret_cast<uint16_t*>(dx);
+  if (dtype == kBF16)
+    rc = rms ? norm_bwd_dispatch<true, true>(vpt, grid, st, DY, X, W, mean, rstd, DR, DX, dwp, dbp, M, D, w_offset)
+             : norm_bwd_dispatch<true, false>(vpt, grid, st, DY, X, W, mean, rstd, DR, DX, dwp, dbp, M, D, w_offset);
+  else
+    rc = rms ? norm_bwd_dispatch<false, true>(vpt, grid, st, DY, X, W, mean, rstd, DR, DX, dwp, dbp, M, D, w_offset)
+             : norm_bwd_dispatch<false, false>(vpt, grid, st, DY, X, W, mean, rstd, DR, DX, dwp, dbp, M, D, w_offset);
+  if (rc) return rc;
+  const int th = 256, bl = (D + th - 1) / th;
+  if (dtype == kBF16) {
+    reduce_partials_kernel<true><<<bl, th, 0, st>>>(dwp, grid, D, dw, grad_f32, accumulate);
+    if (db != nullptr) reduce_partials_kernel<true><<<bl, th, 0, st>>>(dbp, grid, D, db, grad_f32, accumulate);
+  } else {
+    reduce_partials_kernel<false><<<bl, th, 0, st>>>(dwp, grid, D, dw, grad_f32, accumulate);
+    if (db != nullptr) reduce_partials_kernel<false><<<bl, th, 0, st>>>(dbp, grid, D, db, grad_f32, accumulate);
+  }
+  return check_launch("norm_bwd_noalloc_reduce");
+}
