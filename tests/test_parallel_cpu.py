@@ -1,0 +1,135 @@
+"""Multi-rank host logic on CPU ranks over Gloo: mesh layout, TP / SP equivalence with the
+single-rank model, ZeRO-1 equivalence with the replicated optimizer, universal checkpoints
+across TP sizes."""
+
+import os
+
+import pytest
+import torch
+
+from helpers import run_distributed, tiny_config
+
+
+def test_mesh_layout_matches_documented_example():
+    from ironcore_b200.parallel.mesh import mesh_layout
+
+    lay = mesh_layout(16, 4)
+    assert lay["tp"][0] == [0, 1, 2, 3] and lay["tp"][3] == [12, 13, 14, 15]
+    assert lay["dp"][0] == [0, 4, 8, 12] and lay["dp"][1] == [1, 5, 9, 13]
+    lay = mesh_layout(8, 1, ep=4)
+    assert lay["ep"] == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    assert lay["edp"] == [[0, 4], [1, 5], [2, 6], [3, 7]]
+
+
+def _reference_run(family, steps, accum=1):
+    """Single-process TP=1 run: returns losses and the final canonical state dict."""
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.trainer import Trainer
+
+    mesh.destroy_model_parallel()
+    cfg = tiny_config(family)
+    cfg.trainer(micro_batch_size=2, train_batch_size=2 * accum, gradient_accumulation_steps=None)
+    cfg.operation.train_steps = steps
+    validate_config(cfg)
+    tr = Trainer(cfg)
+    losses = [float(tr.train_step(s)[0]) for s in range(steps)]
+    sd = {k: v.clone() for k, v in tr.model.canonical_state_dict().items()}
+    return losses, sd
+
+
+def _tp_worker(rank, world, family, sp, steps, out_path):
+    from ironcore_b200.checkpoint.native import merge_model_parallel_state
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.trainer import Trainer
+
+    cfg = tiny_config(family)
+    cfg.trainer(micro_batch_size=2, train_batch_size=2, gradient_accumulation_steps=None,
+                tensor_model_parallel_size=world)
+    cfg.parallel(world_size=world, rank=rank, sequence_parallel=sp)
+    cfg.operation.train_steps = steps
+    validate_config(cfg)
+    tr = Trainer(cfg)
+    losses = [float(tr.train_step(s)[0]) for s in range(steps)]
+    merged = merge_model_parallel_state(dict(tr.model.canonical_state_dict()), tr.model.canonical_shard_info())
+    if rank == 0:
+        torch.save({"losses": losses, "sd": merged}, out_path)
+
+
+@pytest.mark.parametrize("family,sp", [("gpt2", False), ("llama", False), ("llama", True), ("gpt2", True)])
+def test_tp2_matches_tp1(tmp_path, family, sp):
+    steps = 3
+    ref_losses, ref_sd = _reference_run(family, steps)
+    out = str(tmp_path / "tp.pt")
+    run_distributed(_tp_worker, 2, family, sp, steps, out)
+    got = torch.load(out)
+    for a, b in zip(ref_losses, got["losses"]):
+        assert abs(a - b) < 2e-4, (ref_losses, got["losses"])
+    for k, v in ref_sd.items():
+        assert torch.allclose(v, got["sd"][k], atol=2e-4, rtol=1e-3), k
+
+
+def _zero_worker(rank, world, zero, steps, out_path):
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.trainer import Trainer
+
+    cfg = tiny_config("llama")
+    cfg.trainer(micro_batch_size=2, train_batch_size=4, gradient_accumulation_steps=None)
+    cfg.parallel(world_size=world, rank=rank, zero_stage=zero)
+    cfg.operation.train_steps = steps
+    validate_config(cfg)
+    tr = Trainer(cfg)
+    losses = [float(tr.train_step(s)[0]) for s in range(steps)]
+    sd = {k: v.clone() for k, v in tr.model.canonical_state_dict().items()}
+    opt = tr.optimizer.state_dict()
+    if rank == 0:
+        torch.save({"losses": losses, "sd": sd, "opt": opt["state"]}, out_path)
+
+
+def test_zero1_matches_replicated_optimizer(tmp_path):
+    a, b = str(tmp_path / "z0.pt"), str(tmp_path / "z1.pt")
+    run_distributed(_zero_worker, 2, 0, 3, a)
+    run_distributed(_zero_worker, 2, 1, 3, b)
+    r0, r1 = torch.load(a), torch.load(b)
+    for k in r0["sd"]:
+        assert torch.allclose(r0["sd"][k], r1["sd"][k], atol=1e-6), k
+    for k in r0["opt"]:
+        assert torch.allclose(r0["opt"][k]["exp_avg"], r1["opt"][k]["exp_avg"], atol=1e-7), k
+
+
+def _ckpt_save_worker(rank, world, path):
+    from ironcore_b200.checkpoint import save_checkpoint
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.trainer import Trainer
+
+    cfg = tiny_config("llama")
+    cfg.trainer(micro_batch_size=2, train_batch_size=2, gradient_accumulation_steps=None,
+                tensor_model_parallel_size=world, model_path=path)
+    cfg.parallel(world_size=world, rank=rank, sequence_parallel=True)
+    cfg.operation.train_steps = 2
+    validate_config(cfg)
+    tr = Trainer(cfg)
+    for s in range(2):
+        tr.train_step(s)
+    save_checkpoint(cfg, tr.model, tr.optimizer, tr.lr_scheduler, 1)
+
+
+def test_universal_checkpoint_tp2_to_tp1(tmp_path):
+    from ironcore_b200.checkpoint import load_checkpoint
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.trainer import Trainer
+
+    path = str(tmp_path / "ck")
+    run_distributed(_ckpt_save_worker, 2, path)
+    ref_losses, ref_sd = _reference_run("llama", 2)
+    mesh.destroy_model_parallel()
+    cfg = tiny_config("llama")
+    cfg.trainer(micro_batch_size=2, train_batch_size=2, gradient_accumulation_steps=None, model_path=path)
+    cfg.operation.train_steps = 2
+    validate_config(cfg)
+    tr = Trainer(cfg)
+    assert load_checkpoint(cfg, tr.model, tr.optimizer, tr.lr_scheduler) == 1
+    for k, v in tr.model.canonical_state_dict().items():
+        assert torch.allclose(v, ref_sd[k], atol=2e-4, rtol=1e-3), k
+    assert tr.optimizer.step_count == 2
