@@ -108,7 +108,7 @@ def build_config(world: int, steps: int):
             clip_grad=1.0, warmup_steps=0)
     c.init(init_std=0.02, seed=1234)
     c.parallel(world_size=world, rank=int(os.environ.get("RANK", "0")), local_rank=int(os.environ.get("LOCAL_RANK", "0")),
-               sequence_parallel=world > 1, zero_stage=1)
+               sequence_parallel=world > 1, zero_stage=1, fused_comm=os.environ.get("ICB_FUSED_COMM", "1") != "0")
     c.utils(report_memory_usage=False)
     validate_config(c)
     return c
@@ -214,6 +214,8 @@ def run_ours(args):
             "config": {"model": "llama-7b-shape (32L, d4096, 32h x 128, ffn 11008 swiglu, vocab 32000)",
                        "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN, "micro_batch": 1,
                        "parallelism": f"tp{world}" + ("+sp" if world > 1 else "") + "+zero1",
+                       "tp_comm": ("fused in-kernel P2P (all-gather->GEMM, GEMM->reduce-scatter)"
+                                   if (world > 1 and cfg.parallel.fused_comm) else ("nccl" if world > 1 else "none")),
                        "optimizer": "adam(0.9,0.95) lr 3e-4, clip 1.0, fp32 grad accumulation",
                        "l2": "no flush needed: every pass streams 13.5 GB of weights, far larger than the 126 MB L2"},
             "clocks": clocks,

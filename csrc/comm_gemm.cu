@@ -1,0 +1,368 @@
+// Fused GEMM -> reduce-scatter over a tensor-parallel group (sequence parallelism), sm_100a.
+//
+//   partial[M, N] = A_local[M, K_local] * B_local          (tcgen05, same pipeline as gemm.cu)
+//   out_shard[M/t, N] = sum_ranks partial[rows of this rank] (+ bias) (+ residual)
+//
+// One kernel does both. The epilogue of every 128 x 256 tile converts the accumulator to
+// 16-bit and stores it straight into the *owner's* receive buffer (slot of the sending rank)
+// with peer-to-peer stores over NVLink, then bumps the owner's per-tile arrival counter with
+// a system-scope release. Tiles destined for other ranks are computed first (ring order
+// starting at rank+1), the rank's own rows last, so the wire is busy while the tensor core
+// still has work. When a CTA runs out of GEMM tiles its warps turn into reducers: they wait
+// (bounded, acquire) until all t partials of a 16-row x 256-column unit of this rank's shard
+// have arrived, sum them in fp32, add bias / residual and write the output shard.
+// Counters are cumulative (target = t * epoch), receive buffers alternate by call parity on
+// the host side, so nothing is ever re-zeroed.
+#include "gemm_common.cuh"
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace icb {
+
+struct RsArgs {
+  int M, N, K;
+  int num_m_tiles, num_n_tiles;
+  int rank, world;
+  int rows_per_rank;               // M / world, multiple of 128
+  uint8_t* const* peer_recv;       // device array [world]: every rank's receive buffer [world][rows_per_rank][N] (16-bit)
+  int* const* peer_flags;          // device array [world]: every rank's arrival counters [rows_per_rank/128][num_n_tiles]
+  const uint8_t* recv;             // this rank's receive buffer
+  const int* flags;                // this rank's arrival counters
+  void* out;                       // [rows_per_rank, ldo] 16-bit
+  long long ldo;
+  const void* bias;                // [N] or null
+  const void* residual;            // [rows_per_rank, ldr] or null
+  long long ldr;
+  int epoch;
+  int in_fmt;
+  int* status;
+};
+
+template <int B_MAJOR>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const RsArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem + GemmSmem::a_off;
+  uint8_t* smem_b = smem + GemmSmem::b_off;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + GemmSmem::bar_off);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tfull_bar = empty_bar + kStages;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], 128);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = args.num_m_tiles * args.num_n_tiles;
+  const int mtiles_per_shard = args.rows_per_rank >> 7;
+  // tile -> (m tile, n tile): remote owners first in ring order, own shard last
+  auto coords = [&](int tile, int& mt, int& nt) {
+    tile_coords(tile, args.num_m_tiles, args.num_n_tiles, mt, nt);
+    mt = (mt + (args.rank + 1) * mtiles_per_shard) % args.num_m_tiles;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        int mt, nt;
+        coords(tile, mt, nt);
+        const int m0 = mt * kBM, n0 = nt * kBN;
+        for (int k0 = 0; k0 < args.K; k0 += kBK, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, args.status, kTimeoutSmemEmpty);
+          mbar_expect_tx(&full_bar[s], kAStageBytes + kBStageBytes);
+          uint8_t* sa = smem_a + s * kAStageBytes;
+          uint8_t* sb = smem_b + s * kBStageBytes;
+          tma_load_2d(sa, &tmA, &full_bar[s], k0, m0);
+          if (B_MAJOR == 0) {
+            tma_load_2d(sb, &tmB, &full_bar[s], k0, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < kBN / 64; ++c) tma_load_2d(sb + c * 8192, &tmB, &full_bar[s], n0 + c * 64, k0);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(kBM, kBN, args.in_fmt, 0, B_MAJOR);
+      uint32_t it = 0, tcount = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        const uint32_t acc = tcount & 1;
+        const uint32_t acc_ph = (tcount >> 1) & 1;
+        mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, args.status, kTimeoutTmemEmpty);
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * kBN;
+        uint32_t first = 1;
+        for (int k0 = 0; k0 < args.K; k0 += kBK, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          mbar_wait(&full_bar[s], ph, abort_flag, args.status, kTimeoutSmemFull);
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem_a + s * kAStageBytes);
+          const uint32_t b_addr = smem_u32(smem_b + s * kBStageBytes);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t adesc = umma_desc_sw128(a_addr + k * 32, 16, 1024);
+            const uint64_t bdesc = (B_MAJOR == 0) ? umma_desc_sw128(b_addr + k * 32, 16, 1024)
+                                                  : umma_desc_sw128(b_addr + k * 2048, 8192, 1024);
+            umma_ss(tmem_d, adesc, bdesc, idesc, first ? 0u : 1u);
+            first = 0;
+          }
+          umma_commit(&empty_bar[s]);
+        }
+        umma_commit(&tfull_bar[acc]);
+        ++tcount;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue: accumulator -> owner's receive slot (P2P stores) ----------------
+    const int et = threadIdx.x - 64;
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    uint32_t tcount = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      int mt, nt;
+      coords(tile, mt, nt);
+      const int owner = mt / mtiles_per_shard;
+      const int lm = mt - owner * mtiles_per_shard;
+      const int n0 = nt * kBN;
+      const uint32_t acc = tcount & 1;
+      const uint32_t acc_ph = (tcount >> 1) & 1;
+      mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, args.status, kTimeoutTmemFull);
+      tc_fence_after();
+      const size_t slot_row = (size_t)args.rank * args.rows_per_rank + (size_t)lm * 128 + row;
+      uint8_t* dst_row = args.peer_recv[owner] + slot_row * args.N * 2;
+#pragma unroll 1
+      for (int sub = 0; sub < kBN / 32; ++sub) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN + sub * 32, r);
+        tmem_ld_wait();
+        if (sub == kBN / 32 - 1) {
+          tc_fence_before();
+          mbar_arrive(&tempty_bar[acc]);
+        }
+        const int n_glob = n0 + sub * 32;
+        if (n_glob + 32 <= args.N) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint4 u;
+            if (args.in_fmt == 1) {
+              u.x = pack_bf16x2(__uint_as_float(r[c * 8]), __uint_as_float(r[c * 8 + 1]));
+              u.y = pack_bf16x2(__uint_as_float(r[c * 8 + 2]), __uint_as_float(r[c * 8 + 3]));
+              u.z = pack_bf16x2(__uint_as_float(r[c * 8 + 4]), __uint_as_float(r[c * 8 + 5]));
+              u.w = pack_bf16x2(__uint_as_float(r[c * 8 + 6]), __uint_as_float(r[c * 8 + 7]));
+            } else {
+              u.x = pack_f16x2(__uint_as_float(r[c * 8]), __uint_as_float(r[c * 8 + 1]));
+              u.y = pack_f16x2(__uint_as_float(r[c * 8 + 2]), __uint_as_float(r[c * 8 + 3]));
+              u.z = pack_f16x2(__uint_as_float(r[c * 8 + 4]), __uint_as_float(r[c * 8 + 5]));
+              u.w = pack_f16x2(__uint_as_float(r[c * 8 + 6]), __uint_as_float(r[c * 8 + 7]));
+            }
+            *reinterpret_cast<uint4*>(dst_row + ((size_t)n_glob + c * 8) * 2) = u;
+          }
+        } else {
+          for (int j = 0; j < 32; ++j) {
+            if (n_glob + j < args.N) {
+              const float f = __uint_as_float(r[j]);
+              uint16_t h;
+              if (args.in_fmt == 1) { __nv_bfloat16 b = __float2bfloat16(f); h = *reinterpret_cast<uint16_t*>(&b); }
+              else { __half b = __float2half(f); h = *reinterpret_cast<uint16_t*>(&b); }
+              reinterpret_cast<uint16_t*>(dst_row)[n_glob + j] = h;
+            }
+          }
+        }
+      }
+      // publish the tile: all 128 rows are written -> one arrival on the owner's counter
+      __threadfence_system();
+      named_barrier(1, 128);
+      if (et == 0) red_release_sys_add(args.peer_flags[owner] + lm * args.num_n_tiles + nt, 1);
+      ++tcount;
+    }
+  }
+
+  // ---------------- reduce phase: every warp of the CTA sums arrived partials ----------------
+  {
+    const int nwarps = kGemmThreads / 32;
+    const int gw = blockIdx.x * nwarps + warp;
+    const int n_gw = gridDim.x * nwarps;
+    const int units = mtiles_per_shard * args.num_n_tiles * 8;   // 16 rows x 256 columns each
+    const int target = args.world * args.epoch;
+    for (int u = gw; u < units; u += n_gw) {
+      const int rg = u & 7;
+      const int tn = u >> 3;
+      const int nt = tn % args.num_n_tiles;
+      const int lm = tn / args.num_n_tiles;
+      int ok = 1;
+      if (lane == 0)
+        ok = wait_flag_sys(args.flags + lm * args.num_n_tiles + nt, target, args.status, kTimeoutPeerFlag) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) continue;
+      const int col = nt * kBN + lane * 8;
+      if (col >= args.N) continue;
+      float bias_v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) bias_v[j] = 0.f;
+      if (args.bias != nullptr) {
+        const uint4 ub = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(args.bias) + (size_t)col * 2);
+        const uint32_t w[4] = {ub.x, ub.y, ub.z, ub.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          float2 f = args.in_fmt == 1 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
+          bias_v[2 * t] = f.x; bias_v[2 * t + 1] = f.y;
+        }
+      }
+#pragma unroll 1
+      for (int i = 0; i < 16; ++i) {
+        const int lrow = lm * 128 + rg * 16 + i;
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = bias_v[j];
+        for (int src = 0; src < args.world; ++src) {
+          const uint8_t* p = args.recv + (((size_t)src * args.rows_per_rank + lrow) * args.N + col) * 2;
+          const uint4 v = __ldcv(reinterpret_cast<const uint4*>(p));
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            float2 f = args.in_fmt == 1 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
+            acc[2 * t] += f.x; acc[2 * t + 1] += f.y;
+          }
+        }
+        if (args.residual != nullptr) {
+          const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(args.residual) +
+                                                          ((size_t)lrow * args.ldr + col) * 2);
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            float2 f = args.in_fmt == 1 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
+            acc[2 * t] += f.x; acc[2 * t + 1] += f.y;
+          }
+        }
+        uint4 o;
+        if (args.in_fmt == 1) {
+          o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+          o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+        } else {
+          o.x = pack_f16x2(acc[0], acc[1]); o.y = pack_f16x2(acc[2], acc[3]);
+          o.z = pack_f16x2(acc[4], acc[5]); o.w = pack_f16x2(acc[6], acc[7]);
+        }
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(args.out) + ((size_t)lrow * args.ldo + col) * 2) = o;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) { __nanosleep(1000); }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int B_MAJOR>
+static int launch_gemm_rs(const CUtensorMap& tmA, const CUtensorMap& tmB, const RsArgs& args, int grid,
+                          cudaStream_t stream) {
+  static bool configured = false;
+  auto kern = gemm_rs_kernel<B_MAJOR>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+    if (e != cudaSuccess) return -(int)e;
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(tmA, tmB, args);
+  return check_launch("gemm_rs_kernel");
+}
+
+}  // namespace icb
+
+using namespace icb;
+
+// out_shard[rows_per_rank, N] = reduce_scatter_rows(A[M, K] * B) (+bias) (+residual), M = world * rows_per_rank.
+//   A: [M, lda] row-major (K contiguous). b_major 0: B [N, ldb] (K contiguous); 1: B [K, ldb] (N contiguous).
+//   peer_recv / peer_flags: device arrays [world] of peer pointers to every rank's receive buffer
+//   ([world][rows_per_rank][N] 16-bit) and arrival counters ([rows_per_rank/128][ceil(N/256)] int).
+//   N must be a multiple of 8; rows_per_rank a multiple of 128; epoch = 1, 2, ... per call on this
+//   pair of buffers (same on every rank).
+ICB_API int icb_gemm_rs(const void* A, const void* B, void* out, const void* bias, const void* residual, int M, int N,
+                        int K, long long lda, long long ldb, long long ldo, long long ldr, int b_major, int in_dtype,
+                        const void* const* peer_recv, int* const* peer_flags, const void* recv, const int* flags,
+                        int rank, int world, int epoch, int* status, void* stream_) {
+  if (world < 1 || M % world != 0) return -2;
+  const int rows_per_rank = M / world;
+  if (rows_per_rank % 128 != 0 || N % 8 != 0) return -7;
+  if ((lda * 2) % 16 || (ldb * 2) % 16 || (ldo * 2) % 16) return -4;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  CUtensorMap tmA, tmB;
+  int rc;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {64, (uint32_t)kBM};
+    rc = make_tmap(&tmA, in_dtype, 2, A, dims, str, box, true);
+    if (rc) return rc;
+  }
+  if (b_major == 0) {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {64, (uint32_t)kBN};
+    rc = make_tmap(&tmB, in_dtype, 2, B, dims, str, box, true);
+  } else {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {64, (uint32_t)kBK};
+    rc = make_tmap(&tmB, in_dtype, 2, B, dims, str, box, true);
+  }
+  if (rc) return rc;
+  RsArgs a;
+  a.M = M; a.N = N; a.K = K;
+  a.num_m_tiles = M / kBM;
+  a.num_n_tiles = (N + kBN - 1) / kBN;
+  a.rank = rank; a.world = world; a.rows_per_rank = rows_per_rank;
+  a.peer_recv = reinterpret_cast<uint8_t* const*>(const_cast<void* const*>(reinterpret_cast<const void* const*>(peer_recv)));
+  a.peer_flags = peer_flags;
+  a.recv = reinterpret_cast<const uint8_t*>(recv);
+  a.flags = flags;
+  a.out = out; a.ldo = ldo;
+  a.bias = bias; a.residual = residual; a.ldr = ldr;
+  a.epoch = epoch;
+  a.in_fmt = (in_dtype == kBF16) ? 1 : 0;
+  a.status = status;
+  int grid = num_sms();
+  const int total = a.num_m_tiles * a.num_n_tiles;
+  if (total < grid) grid = total;
+  if (b_major == 0) return launch_gemm_rs<0>(tmA, tmB, a, grid, stream);
+  return launch_gemm_rs<1>(tmA, tmB, a, grid, stream);
+}

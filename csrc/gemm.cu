@@ -13,35 +13,20 @@
 // * Grouped forms for mixture-of-experts: group_mode 1 picks B (and bias) per
 //   128-row M tile from a lookup table; group_mode 2 computes one C per group
 //   over a K range taken from an offsets table (expert weight gradients).
+// * Fused all-gather -> GEMM (template flag AG): A lives in a gathered buffer whose remote
+//   row blocks are pulled from the peers' copies over NVLink (plain P2P loads) by two extra
+//   copy warps per CTA while the tensor core works on row blocks that already arrived
+//   (local shard first, then peers in ring order). Per-128-row flags (release/acquire,
+//   cumulative sequence numbers) gate the TMA producer.
 // * Every wait is bounded: on timeout a status word is set and the kernel drains.
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA
 // issuer, warps 2-5 = epilogue (one TMEM lane quarter each).
 #include "host_common.h"
 #include "ptx.cuh"
+#include "gemm_common.cuh"
 
 namespace icb {
-
-constexpr int kBM = 128;
-constexpr int kBN = 256;
-constexpr int kBK = 64;
-constexpr int kStages = 4;
-constexpr int kAStageBytes = kBM * kBK * 2;   // 16 KiB
-constexpr int kBStageBytes = kBN * kBK * 2;   // 32 KiB
-constexpr int kSlabBytes = kBM * 128;         // 128 rows x 128 B
-constexpr int kGemmThreads = 192;
-constexpr int kTmemCols = 512;
-constexpr int kGroupM = 16;
-
-struct GemmSmem {
-  // offsets from the 1024-aligned base
-  static constexpr int a_off = 0;
-  static constexpr int b_off = kStages * kAStageBytes;
-  static constexpr int slab_off = b_off + kStages * kBStageBytes;
-  static constexpr int bar_off = slab_off + 2 * kSlabBytes;
-  static constexpr int total = bar_off + 256;
-};
-constexpr int kGemmSmemBytes = GemmSmem::total + 1024;  // slack for manual alignment
 
 struct GemmArgs {
   int M, N, K;
@@ -54,20 +39,22 @@ struct GemmArgs {
   int in_fmt;                // 0 fp16, 1 bf16
   int out_f32;               // 0: output dtype == input dtype, 1: fp32
   int* status;
+  // ---- fused all-gather (AG kernels only) ----
+  int ag_rank, ag_world;            // this rank / group size
+  int ag_rows_per_rank;             // token rows per shard (multiple of 128)
+  long long ag_row_bytes;           // bytes per token row of the gathered buffer
+  uint8_t* ag_local;                // this rank's gathered buffer [world * rows_per_rank, row_bytes]
+  uint8_t* const* ag_peers;         // device array [world]: every rank's gathered buffer (peer pointers)
+  int* const* ag_peer_signal;       // device array [world]: every rank's shard_ready[world] array
+  const int* ag_signal;             // this rank's shard_ready[world] (written by the peers)
+  int* ag_ready;                    // this rank's per-128-row-block arrival counters
+  int ag_epoch;                     // call sequence number (flags are cumulative)
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& mt, int& nt) {
-  const int per_group = kGroupM * num_n;
-  const int g = tile / per_group;
-  const int first_m = g * kGroupM;
-  const int gsz = min(num_m - first_m, kGroupM);
-  const int r = tile - g * per_group;
-  mt = first_m + r % gsz;
-  nt = r / gsz;
-}
+constexpr int kAgSubChunks = 8;     // a 128-row block is copied as 8 units of 16 rows
 
-template <int A_MAJOR, int B_MAJOR>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int A_MAJOR, int B_MAJOR, bool AG>
+__global__ void __launch_bounds__(AG ? kGemmThreads + 64 : kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const GemmArgs args) {
   extern __shared__ uint8_t smem_raw[];
@@ -109,6 +96,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  if (AG) {
+    // Tell every peer that this rank's shard (written before this kernel in stream order) is readable.
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+      __threadfence_system();
+      for (int q = 0; q < args.ag_world; ++q)
+        if (q != args.ag_rank) st_release_sys(args.ag_peer_signal[q] + args.ag_rank, args.ag_epoch);
+    }
+  }
+  const int ag_mtiles_per_shard = AG ? max(args.ag_rows_per_rank >> 7, 1) : 1;
+
   const int tiles_per_group = args.num_m_tiles * args.num_n_tiles;
   const int total_tiles = (args.group_mode == 2 ? args.num_groups : 1) * tiles_per_group;
 
@@ -131,9 +128,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           grp = args.group_table[mt];
           if (grp < 0) continue;
         }
+        if (AG && A_MAJOR == 0) {
+          // local shard first, then the peers in ring order (the order the copy warps fetch them)
+          mt = (mt + args.ag_rank * ag_mtiles_per_shard) % args.num_m_tiles;
+          if (mt / ag_mtiles_per_shard != args.ag_rank) {
+            wait_flag_gpu(args.ag_ready + mt, args.ag_epoch * kAgSubChunks, args.status, kTimeoutLocalFlag);
+            fence_proxy_async_all();
+          }
+        }
         const int m0 = mt * kBM, n0 = nt * kBN;
         const int bz = (args.group_mode == 1) ? grp : 0;
-        for (int k0 = k_begin; k0 < k_end; k0 += kBK, ++it) {
+        for (int kseq = k_begin; kseq < k_end; kseq += kBK, ++it) {
+          int k0 = kseq;
+          if (AG && A_MAJOR == 1) {
+            // the reduction runs over token rows: start with the local shard's rows
+            k0 = (kseq + args.ag_rank * args.ag_rows_per_rank) % args.K;
+            if ((k0 & 127) == 0) {
+              const int rb = k0 >> 7;
+              if (rb / ag_mtiles_per_shard != args.ag_rank) {
+                wait_flag_gpu(args.ag_ready + rb, args.ag_epoch * kAgSubChunks, args.status, kTimeoutLocalFlag);
+                fence_proxy_async_all();
+              }
+            }
+          }
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, args.status, kTimeoutSmemEmpty);
@@ -205,7 +222,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp < 6) {
     // ------------------------------ epilogue ----------------------------------
     const int et = threadIdx.x - 64;     // 0..127
     const int q = warp & 3;              // TMEM lane quarter this warp may read
@@ -228,6 +245,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         grp = args.group_table[mt];
         if (grp < 0) continue;
       }
+      if (AG && A_MAJOR == 0) mt = (mt + args.ag_rank * ag_mtiles_per_shard) % args.num_m_tiles;
       const bool empty_k = (k_end <= k_begin);
       const int m0 = mt * kBM, n0 = nt * kBN;
       const uint32_t acc = tcount & 1;
@@ -390,6 +408,53 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (et == 0) tma_store_wait<0>();
   }
 
+  if (AG && warp >= 6) {
+    // ------------------------------ all-gather copy warps ----------------------
+    // Unit = 16 token rows of one remote 128-row block. Units are visited peer by peer in ring
+    // order (rank+1 first) so that every rank pulls from a different peer at the same time.
+    const int cw = blockIdx.x * 2 + (warp - 6);
+    const int n_cw = gridDim.x * 2;
+    const int units_per_shard = ag_mtiles_per_shard * kAgSubChunks;
+    const int total_units = (args.ag_world - 1) * units_per_shard;
+    const long long unit_bytes = 16LL * args.ag_row_bytes;
+    int checked_peer = -1;
+    bool peer_ok = true;
+    for (int u = cw; u < total_units; u += n_cw) {
+      const int step = u / units_per_shard + 1;
+      const int within = u - (step - 1) * units_per_shard;
+      const int q = (args.ag_rank + step) % args.ag_world;
+      if (q != checked_peer) {
+        int ok = 1;
+        if (lane == 0) ok = wait_flag_sys(args.ag_signal + q, args.ag_epoch, args.status, kTimeoutPeerFlag) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        peer_ok = ok != 0;
+        checked_peer = q;
+      }
+      const int rb = q * ag_mtiles_per_shard + within / kAgSubChunks;           // 128-row block index
+      const long long off = ((long long)rb * 128 + (within % kAgSubChunks) * 16) * args.ag_row_bytes;
+      if (peer_ok) {
+        const uint4* src = reinterpret_cast<const uint4*>(args.ag_peers[q] + off);
+        uint4* dst = reinterpret_cast<uint4*>(args.ag_local + off);
+        const long long nvec = unit_bytes >> 4;
+        long long i = lane;
+        for (; i + 7 * 32 < nvec; i += 8 * 32) {
+          uint4 v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = __ldcv(src + i + j * 32);   // volatile load: never from a stale cache line
+#pragma unroll
+          for (int j = 0; j < 8; ++j) dst[i + j * 32] = v[j];
+        }
+        for (; i < nvec; i += 32) dst[i] = __ldcv(src + i);
+      }
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) {
+        fence_proxy_async_all();
+        red_release_gpu_add(args.ag_ready + rb, 1);
+      }
+    }
+  }
+
   // Drain: nobody may exit while TMEM is allocated or copies are in flight.
   tc_fence_before();
   __syncthreads();
@@ -405,11 +470,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   }
 }
 
-template <int A_MAJOR, int B_MAJOR>
+template <int A_MAJOR, int B_MAJOR, bool AG = false>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const GemmArgs& args,
                        int grid, cudaStream_t stream) {
   static bool configured = false;
-  auto kern = gemm_kernel<A_MAJOR, B_MAJOR>;
+  auto kern = gemm_kernel<A_MAJOR, B_MAJOR, AG>;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
     if (e != cudaSuccess) {
@@ -418,7 +483,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
     }
     configured = true;
   }
-  kern<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(tmA, tmB, tmC, args);
+  kern<<<grid, AG ? kGemmThreads + 64 : kGemmThreads, kGemmSmemBytes, stream>>>(tmA, tmB, tmC, args);
   return check_launch("gemm_kernel");
 }
 
@@ -434,10 +499,10 @@ using namespace icb;
 //   group_mode 2: for g in [0,G): C_g[M,N] = A[:, k_g..k_g+1) * B[k range], C_g = C + g*M*ldc
 //                 (needs a_major = b_major = 1; K offsets multiples of 64 or zero-padded rows).
 // All pitches in elements; pitches * element size and base pointers must be multiples of 16 bytes.
-ICB_API int icb_gemm(const void* A, const void* B, void* C, const void* bias, const void* residual, int M, int N,
+static int gemm_impl(const void* A, const void* B, void* C, const void* bias, const void* residual, int M, int N,
                      int K, long long lda, long long ldb, long long ldc, long long ldr, int a_major, int b_major,
                      int in_dtype, int out_f32, int group_mode, int num_groups, const int* group_table,
-                     long long b_group_stride, int* status, int max_ctas, void* stream_) {
+                     long long b_group_stride, int* status, int max_ctas, void* stream_, const GemmArgs* ag) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0) return 0;
   if (in_dtype != kBF16 && in_dtype != kF16) return -2;
@@ -486,6 +551,12 @@ ICB_API int icb_gemm(const void* A, const void* B, void* C, const void* bias, co
   if (rc) return rc;
 
   GemmArgs args;
+  if (ag != nullptr) args = *ag;
+  else {
+    args.ag_rank = 0; args.ag_world = 1; args.ag_rows_per_rank = 0; args.ag_row_bytes = 0;
+    args.ag_local = nullptr; args.ag_peers = nullptr; args.ag_peer_signal = nullptr; args.ag_signal = nullptr;
+    args.ag_ready = nullptr; args.ag_epoch = 0;
+  }
   args.M = M; args.N = N; args.K = K;
   args.num_m_tiles = (M + kBM - 1) / kBM;
   args.num_n_tiles = (N + kBN - 1) / kBN;
@@ -505,8 +576,55 @@ ICB_API int icb_gemm(const void* A, const void* B, void* C, const void* bias, co
   if (total < grid) grid = (int)total;
   if (grid < 1) grid = 1;
 
+  if (ag != nullptr) {
+    if (a_major == 0 && b_major == 0) return launch_gemm<0, 0, true>(tmA, tmB, tmC, args, grid, stream);
+    if (a_major == 0 && b_major == 1) return launch_gemm<0, 1, true>(tmA, tmB, tmC, args, grid, stream);
+    if (a_major == 1 && b_major == 1) return launch_gemm<1, 1, true>(tmA, tmB, tmC, args, grid, stream);
+    return -6;
+  }
   if (a_major == 0 && b_major == 0) return launch_gemm<0, 0>(tmA, tmB, tmC, args, grid, stream);
   if (a_major == 0 && b_major == 1) return launch_gemm<0, 1>(tmA, tmB, tmC, args, grid, stream);
   if (a_major == 1 && b_major == 0) return launch_gemm<1, 0>(tmA, tmB, tmC, args, grid, stream);
   return launch_gemm<1, 1>(tmA, tmB, tmC, args, grid, stream);
+}
+
+ICB_API int icb_gemm(const void* A, const void* B, void* C, const void* bias, const void* residual, int M, int N,
+                     int K, long long lda, long long ldb, long long ldc, long long ldr, int a_major, int b_major,
+                     int in_dtype, int out_f32, int group_mode, int num_groups, const int* group_table,
+                     long long b_group_stride, int* status, int max_ctas, void* stream_) {
+  return gemm_impl(A, B, C, bias, residual, M, N, K, lda, ldb, ldc, ldr, a_major, b_major, in_dtype, out_f32,
+                   group_mode, num_groups, group_table, b_group_stride, status, max_ctas, stream_, nullptr);
+}
+
+// Fused all-gather -> GEMM over a tensor-parallel group (sequence parallelism).
+//   gathered : this rank's gathered activation buffer [world * rows_per_rank, width] (16-bit, contiguous);
+//              the local shard's rows must already be in place (stream order).
+//   peers    : device array [world] of every rank's gathered buffer (symmetric-memory peer pointers).
+//   peer_signal : device array [world] of every rank's shard_ready[world] int array; signal = this rank's own.
+//   ready    : this rank's int array [world * rows_per_rank / 128] of cumulative arrival counters.
+//   epoch    : 1, 2, 3, ... per call on this workspace (same on every rank).
+//   a_major 0: C[M = world*rows_per_rank, N] = gathered[M, K = width] * B        (forward / dgrad of a row-parallel layer)
+//   a_major 1: C[M = width, N] = gathered^T * B[K = world*rows_per_rank, N]      (wgrad: reduction over gathered rows)
+// Remote rows are pulled with plain P2P loads by copy warps inside the same kernel; the tensor core
+// starts with the local shard and follows the peers in ring order.
+ICB_API int icb_ag_gemm(void* gathered, const void* const* peers, int* const* peer_signal, const int* signal,
+                        int* ready, int rank, int world, int rows_per_rank, int width, int epoch, const void* B,
+                        void* C, const void* bias, const void* residual, int N, long long ldb, long long ldc,
+                        long long ldr, int a_major, int b_major, int in_dtype, int out_f32, int* status,
+                        void* stream_) {
+  if (rows_per_rank % 128 != 0 || width % 8 != 0) return -7;
+  GemmArgs ag;
+  ag.ag_rank = rank; ag.ag_world = world; ag.ag_rows_per_rank = rows_per_rank;
+  ag.ag_row_bytes = (long long)width * 2;
+  ag.ag_local = reinterpret_cast<uint8_t*>(gathered);
+  ag.ag_peers = reinterpret_cast<uint8_t* const*>(const_cast<void* const*>(reinterpret_cast<const void* const*>(peers)));
+  ag.ag_peer_signal = peer_signal;
+  ag.ag_signal = signal;
+  ag.ag_ready = ready;
+  ag.ag_epoch = epoch;
+  const int rows = world * rows_per_rank;
+  const int M = a_major == 0 ? rows : width;
+  const int K = a_major == 0 ? width : rows;
+  return gemm_impl(gathered, B, C, bias, residual, M, N, K, width, ldb, ldc, ldr, a_major, b_major, in_dtype, out_f32,
+                   0, 1, nullptr, 0, status, 0, stream_, &ag);
 }

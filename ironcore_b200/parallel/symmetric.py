@@ -1,0 +1,59 @@
+"""Symmetric-memory workspaces for the fused compute+collective kernels.
+
+A workspace is one allocation of PyTorch's symmetric-memory allocator, made by every rank of
+a process group with the same size and exchanged with ``rendezvous``; afterwards each rank
+knows the device address of every peer's copy (NVLink peer pointers through NVSwitch). The
+kernels read / write those addresses directly (plain P2P loads and stores, release/acquire
+flags); no TMA multicast and no library kernel ever sees a peer pointer.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def symmetric_memory_available() -> bool:
+    if not (torch.cuda.is_available() and dist.is_initialized()):
+        return False
+    try:
+        import torch.distributed._symmetric_memory as _sm  # noqa: F401
+
+        return True
+    except Exception:
+        return False
+
+
+class SymmetricBuffer:
+    """``nbytes`` of zero-initialised symmetric memory over ``group``."""
+
+    def __init__(self, nbytes: int, group):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        nbytes = (nbytes + 255) // 256 * 256
+        self.nbytes = nbytes
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.local = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
+        self.handle = symm_mem.rendezvous(self.local, group)
+        self.local.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+        self.peer_ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        if self.peer_ptrs[self.rank] != self.local.data_ptr():
+            raise RuntimeError("symmetric memory: local pointer does not match the rendezvous table")
+
+    def view(self, offset: int, shape, dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= s
+        nb = n * torch.empty((), dtype=dtype).element_size()
+        return self.local[offset:offset + nb].view(dtype).view(*shape)
+
+    def peer_table(self, offset: int) -> torch.Tensor:
+        """int64 device tensor [world] with every rank's address of the region at ``offset``."""
+        return torch.tensor([p + offset for p in self.peer_ptrs], dtype=torch.int64, device=self.local.device)

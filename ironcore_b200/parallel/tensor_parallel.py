@@ -70,7 +70,7 @@ class ColumnParallelLinear(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.tp_size > 1:
             if self.sequence_parallel:
-                if self.fused is not None and OF.use_native(x):
+                if self.fused is not None and OF.use_native(x) and x.dim() == 2 and x.shape[0] == self.fused.rows:
                     y = self.fused.allgather_linear(x, self.weight, self.bias)
                     return C.gather_last_dim(y, self.tp_group) if self.gather_output else y
                 x = C.gather_from_sp(x, self.tp_group)
@@ -114,7 +114,8 @@ class RowParallelLinear(nn.Module):
             return OF.linear(x, self.weight, self.bias, residual)
         if not self.input_is_parallel:
             x = C.scatter_last_dim(x, self.tp_group)
-        if self.sequence_parallel and self.fused is not None and OF.use_native(x):
+        if self.sequence_parallel and self.fused is not None and OF.use_native(x) and x.dim() == 2 \
+                and x.shape[0] == self.fused.tokens:
             return self.fused.linear_reduce_scatter(x, self.weight, self.bias, residual)
         y = OF.linear(x, self.weight, None)
         if self.sequence_parallel:

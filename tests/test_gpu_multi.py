@@ -1,0 +1,135 @@
+"""Fused compute+collective kernels on 2 GPUs against the NCCL + GEMM composition.
+Skipped when fewer than two CUDA devices are visible."""
+
+import os
+
+import pytest
+import torch
+
+from helpers import free_port
+
+pytestmark = pytest.mark.gpu
+
+
+def _need_two():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+
+
+def _worker(rank, world, port, fn_name, out_q):
+    import traceback
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    try:
+        import torch.distributed as dist
+
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        globals()[fn_name](rank, world)
+        torch.cuda.synchronize()
+        from ironcore_b200.ops import native
+
+        native.check_status()
+        dist.barrier()
+        dist.destroy_process_group()
+        out_q.put((rank, "ok"))
+    except Exception:
+        out_q.put((rank, traceback.format_exc()))
+
+
+def _spawn(fn_name, world=2):
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fn_name, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    results = []
+    while not q.empty():
+        results.append(q.get())
+    bad = [r for r in results if r[1] != "ok"]
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            bad.append((-1, "timeout"))
+    assert not bad and len(results) == world, "\n".join(f"[rank {r}] {m}" for r, m in bad)
+
+
+def _close(a, b, k):
+    err = (a.float() - b.float()).abs().max().item()
+    assert err <= 3e-2 * (k ** 0.5), err
+
+
+def check_raw_kernels(rank, world):
+    import torch.distributed as dist
+
+    from ironcore_b200.parallel.fused_comm import FusedTP
+
+    torch.manual_seed(100 + rank)
+    tokens, d, n = 1024, 512, 768
+    ws = FusedTP(tokens, d, dist.group.WORLD)
+    rows = tokens // world
+    for it in range(3):   # several epochs: flags are cumulative, buffers alternate
+        x = torch.randn(rows, d, device="cuda").bfloat16()
+        w = torch.randn(d, n, device="cuda").bfloat16()
+        dist.broadcast(w, 0)
+        full = torch.empty(tokens, d, device="cuda", dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(full, x)
+        y = ws.ag_gemm(x, w, a_major=0, b_major=1, n=n)
+        _close(y, full.float() @ w.float(), d)
+        # wgrad form: gathered^T @ dy
+        dy = torch.randn(tokens, n, device="cuda").bfloat16()
+        dw = ws.ag_gemm(x, dy, a_major=1, b_major=1, n=n)
+        _close(dw, full.float().t() @ dy.float(), tokens)
+        # GEMM -> reduce-scatter with bias and residual
+        a = torch.randn(tokens, 384, device="cuda").bfloat16()
+        b = torch.randn(384, d, device="cuda").bfloat16()
+        bias = torch.randn(d, device="cuda").bfloat16()
+        res = torch.randn(rows, d, device="cuda").bfloat16()
+        out = ws.gemm_rs(a, b, b_major=1, bias=bias, residual=res)
+        part = (a.float() @ b.float()).contiguous()
+        ref = torch.empty(rows, d, device="cuda")
+        dist.reduce_scatter_tensor(ref, part)
+        _close(out, ref + bias.float() + res.float(), 384 * world)
+
+
+def check_tp2_model_fused_matches_nccl(rank, world):
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.trainer import Trainer
+    from helpers import tiny_config
+
+    def run(fused):
+        mesh.destroy_model_parallel()
+        cfg = tiny_config("llama", d_model=256, d_ffn=512, num_layers=2, num_attention_heads=4, head_dim=64,
+                          max_seq_len=256, max_position_embeddings=256, precision="bf16", vocab_size=1024)
+        cfg.data.vocab_size = 1024
+        cfg.trainer(micro_batch_size=2, train_batch_size=2, gradient_accumulation_steps=None,
+                    tensor_model_parallel_size=world)
+        cfg.parallel(world_size=world, rank=rank, local_rank=rank, sequence_parallel=True, fused_comm=fused)
+        cfg.operation.train_steps = 3
+        validate_config(cfg)
+        tr = Trainer(cfg)
+        if fused:
+            assert any(getattr(m, "fused", None) is not None for m in tr.model.modules())
+        return [float(tr.train_step(s)[0]) for s in range(3)]
+
+    a = run(False)
+    b = run(True)
+    for x, y in zip(a, b):
+        assert abs(x - y) < 5e-2, (a, b)
+
+
+def test_fused_tp_kernels_two_gpus():
+    _need_two()
+    _spawn("check_raw_kernels")
+
+
+def test_tp2_sp_model_fused_vs_nccl():
+    _need_two()
+    _spawn("check_tp2_model_fused_matches_nccl")
