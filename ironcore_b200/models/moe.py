@@ -1,0 +1,234 @@
+"""Mixture-of-experts feed-forward block with expert parallelism.
+
+Semantics (no counterpart in the reference; standard top-k softmax routing):
+  probs = softmax(x W_r) over E experts; the k largest are selected and weight the expert
+  outputs (optionally renormalised); routed experts are gated MLPs of hidden ``expert_d_ffn``;
+  ``num_shared_experts`` always-on experts are one dense gated MLP of hidden
+  ``num_shared * shared_d_ffn`` applied to every token;
+  out = shared(x) + sum_k w_k * expert_k(x) (+ residual);
+  aux = coeff * E * sum_e f_e * P_e with f_e the fraction of token slots routed to e and P_e the
+  mean router probability of e.
+
+Execution. Token slots are sorted by expert into a buffer whose per-expert segments are padded
+to the GEMM's 128-row tile, so the grouped tcgen05 GEMM picks the expert weight per M tile
+from a small device table (no host synchronisation when experts are local). With expert
+parallelism the slots first cross the EP group with an all-to-all whose split sizes are the
+per-rank expert counts; the inverse all-to-all brings expert outputs back, and the slot
+outputs are combined with the router weights. Dropless (no capacity factor).
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..layers.activations import Activation
+from ..layers.mlp import MLP
+from ..ops import functional as OF
+from ..ops import kernels
+from ..parallel import collectives as C
+from ..parallel import mesh
+
+TILE = 128
+
+
+class _GroupedLinear(torch.autograd.Function):
+    """y[rows of expert e] = x[rows of expert e] @ W[e] on the padded, expert-sorted layout."""
+
+    @staticmethod
+    def forward(ctx, xp, weight, tile_expert, k_offsets):
+        e, k, n = weight.shape
+        y = kernels.gemm(xp, weight, a_major=0, b_major=1, m=xp.shape[0], n=n, k=k, group_mode=1, num_groups=e,
+                         group_table=tile_expert, b_group_stride=k * n)
+        ctx.save_for_backward(xp, weight, tile_expert, k_offsets)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xp, weight, tile_expert, k_offsets = ctx.saved_tensors
+        e, k, n = weight.shape
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = kernels.gemm(dy, weight, a_major=0, b_major=0, m=dy.shape[0], n=k, k=n, group_mode=1, num_groups=e,
+                              group_table=tile_expert, b_group_stride=k * n)
+        if ctx.needs_input_grad[1]:
+            main_grad = getattr(weight, "main_grad", None)
+            if main_grad is not None:
+                kernels.gemm(xp, dy, a_major=1, b_major=1, m=k, n=n, k=xp.shape[0], group_mode=2, num_groups=e,
+                             group_table=k_offsets, out=main_grad, residual=main_grad, out_dtype=main_grad.dtype)
+                weight.grad_ready = True
+            else:
+                dw = kernels.gemm(xp, dy, a_major=1, b_major=1, m=k, n=n, k=xp.shape[0], group_mode=2, num_groups=e,
+                                  group_table=k_offsets)
+        return dx, dw, None, None
+
+
+def grouped_linear(xp: torch.Tensor, weight: torch.Tensor, tile_expert: torch.Tensor, seg_offsets: torch.Tensor,
+                   counts: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """xp: [P, K] expert-sorted rows with 128-padded segments; weight: [E, K, N];
+    tile_expert: int32 [P/128] expert of each tile (-1 = unused tile); seg_offsets: int32 [E+1]."""
+    if OF.use_native(xp):
+        return _GroupedLinear.apply(xp, weight, tile_expert, seg_offsets)
+    outs = torch.zeros((xp.shape[0], weight.shape[2]), dtype=xp.dtype, device=xp.device)
+    off = seg_offsets.tolist()
+    for e in range(weight.shape[0]):
+        lo, hi = off[e], off[e + 1]
+        if hi > lo:
+            outs[lo:hi] = xp[lo:hi] @ weight[e]
+    return outs
+
+
+def padded_layout(expert_ids: torch.Tensor, num_experts: int, capacity_rows: int):
+    """For slot->expert ids (any order) compute the destination row of every slot in the
+    expert-sorted, 128-padded buffer. Returns (dest_row [S], seg_offsets int32 [E+1],
+    tile_expert int32 [capacity_rows/128], counts [E]). All on device, no synchronisation."""
+    s = expert_ids.numel()
+    counts = torch.bincount(expert_ids, minlength=num_experts)
+    padded = (counts + TILE - 1) // TILE * TILE
+    seg_end = torch.cumsum(padded, 0)
+    seg_start = seg_end - padded
+    order = torch.argsort(expert_ids, stable=True)
+    sorted_e = expert_ids[order]
+    first_of_expert = torch.cumsum(counts, 0) - counts
+    rank_in_expert = torch.arange(s, device=expert_ids.device) - first_of_expert[sorted_e]
+    dest_sorted = seg_start[sorted_e] + rank_in_expert
+    dest = torch.empty_like(dest_sorted)
+    dest[order] = dest_sorted
+    seg_offsets = torch.cat([seg_start[:1] * 0, seg_end]).to(torch.int32)
+    tiles = capacity_rows // TILE
+    tile_start = torch.arange(tiles, device=expert_ids.device) * TILE
+    tile_expert = torch.bucketize(tile_start, seg_end, right=True)
+    tile_expert = torch.where(tile_expert < num_experts, tile_expert, torch.full_like(tile_expert, -1))
+    # tiles inside an expert's segment but beyond its real rows still belong to it (padding rows are zero)
+    return dest, seg_offsets, tile_expert.to(torch.int32), counts
+
+
+class MoEBlock(nn.Module):
+    def __init__(self, config, dtype=None, device=None):
+        super().__init__()
+        m = config.model
+        moe = m.moe
+        self.d_model = m.d_model
+        self.num_experts = moe.num_experts
+        self.top_k = moe.top_k
+        self.aux_coeff = moe.aux_loss_coeff
+        self.normalize = moe.normalize_topk
+        self.ffn = moe.expert_d_ffn or m.d_ffn
+        self.ep_group = mesh.get_expert_model_parallel_group()
+        self.ep = mesh.get_expert_model_parallel_world_size()
+        self.ep_rank = mesh.get_expert_model_parallel_rank()
+        if self.num_experts % self.ep:
+            raise ValueError("num_experts must be divisible by the expert parallel size")
+        self.e_local = self.num_experts // self.ep
+        self.activation = Activation(m.activation_type)
+        mult = 2 if self.activation.gated else 1
+        self.router = nn.Linear(m.d_model, self.num_experts, bias=False, dtype=dtype, device=device)
+        # stored [in, out] like every other linear: router.weight is [E, d] (nn.Linear) and applied as x @ W^T
+        self.experts_up = nn.Parameter(torch.empty(self.e_local, m.d_model, self.ffn * mult, dtype=dtype, device=device))
+        self.experts_down = nn.Parameter(torch.empty(self.e_local, self.ffn, m.d_model, dtype=dtype, device=device))
+        self.experts_up.expert_parallel = True
+        self.experts_down.expert_parallel = True
+        self.shared = None
+        if moe.num_shared_experts > 0:
+            s_ffn = (moe.shared_expert_d_ffn or self.ffn) * moe.num_shared_experts
+            self.shared = MLP(m.d_model, s_ffn, m.activation_type, bias=False, dropout=0.0, dtype=dtype, device=device)
+
+    # ------------------------------------------------------------------ routing
+    def route(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        logits = F.linear(x, self.router.weight).float()
+        probs = torch.softmax(logits, dim=-1)
+        w, idx = torch.topk(probs, self.top_k, dim=-1)
+        if self.normalize:
+            w = w / w.sum(-1, keepdim=True).clamp_min(1e-20)
+        t = x.shape[0]
+        f = torch.bincount(idx.reshape(-1), minlength=self.num_experts).float() / float(t * self.top_k)
+        p_mean = probs.mean(0)
+        aux = self.aux_coeff * self.num_experts * (f.detach() * p_mean).sum()
+        return w, idx, aux
+
+    # ------------------------------------------------------------------ expert compute on sorted slots
+    def _experts(self, xs: torch.Tensor, local_expert: torch.Tensor) -> torch.Tensor:
+        """xs: [S, d] slot inputs, local_expert: [S] ids in [0, e_local). Returns [S, d]."""
+        s = xs.shape[0]
+        cap = (s + self.e_local * (TILE - 1) + TILE - 1) // TILE * TILE
+        dest, seg_offsets, tile_expert, _counts = padded_layout(local_expert, self.e_local, cap)
+        xp = torch.zeros((cap, xs.shape[1]), dtype=xs.dtype, device=xs.device)
+        xp = xp.index_copy(0, dest, xs)
+        h = grouped_linear(xp, self.experts_up, tile_expert, seg_offsets)
+        if OF.use_native(h):
+            # rows of unused tiles are never written by the grouped GEMM: define them for the activation
+            used = seg_offsets[-1].to(torch.long)
+            row = torch.arange(cap, device=h.device)
+            h = torch.where((row < used)[:, None], h, torch.zeros((), dtype=h.dtype, device=h.device))
+        h = self.activation(h)
+        yp = grouped_linear(h, self.experts_down, tile_expert, seg_offsets)
+        return yp.index_select(0, dest)
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None):
+        """x: [T, d] -> ([T, d], aux loss)."""
+        t, d = x.shape
+        w, idx, aux = self.route(x)
+        slots_expert = idx.reshape(-1)                                   # [T*k]
+        token_of_slot = torch.arange(t, device=x.device).repeat_interleave(self.top_k)
+        xs = x.index_select(0, token_of_slot)
+        if self.ep == 1:
+            ys = self._experts(xs, slots_expert)
+        else:
+            # sort slots by destination rank, exchange, run local experts, exchange back
+            dest_rank = slots_expert // self.e_local
+            order = torch.argsort(dest_rank, stable=True)
+            send_counts = torch.bincount(dest_rank, minlength=self.ep)
+            recv_counts = torch.empty_like(send_counts)
+            if x.is_cuda:
+                dist.all_to_all_single(recv_counts, send_counts, group=self.ep_group)
+            else:
+                self._exchange_counts(send_counts, recv_counts)
+            in_splits = send_counts.tolist()
+            out_splits = recv_counts.tolist()
+            xs_sorted = xs.index_select(0, order)
+            e_sorted = (slots_expert.index_select(0, order) % self.e_local)
+            xr = C.all_to_all(xs_sorted, out_splits, in_splits, self.ep_group)
+            er = C.all_to_all_single(e_sorted.contiguous(), out_splits, in_splits, self.ep_group)
+            yr = self._experts(xr, er)
+            ys_sorted = C.all_to_all(yr, in_splits, out_splits, self.ep_group)
+            ys = torch.empty_like(ys_sorted)
+            ys = ys.index_copy(0, order, ys_sorted)
+        out = (ys.view(t, self.top_k, d) * w.to(ys.dtype).unsqueeze(-1)).sum(1)
+        if self.shared is not None:
+            out = out + self.shared(x)
+        if residual is not None:
+            out = out + residual
+        return out, aux
+
+    def _exchange_counts(self, send_counts, recv_counts):
+        gathered = [torch.empty_like(send_counts) for _ in range(self.ep)]
+        dist.all_gather(gathered, send_counts, group=self.ep_group)
+        for r in range(self.ep):
+            recv_counts[r] = gathered[r][self.ep_rank]
+
+
+def moe_reference(x, router_w, experts_up, experts_down, top_k, activation: str, normalize: bool = False):
+    """Dense per-token restatement (every token through its k experts one by one); oracle for tests."""
+    from ..ops.reference import act_reference, glu_reference
+    from ..ops.functional import is_gated
+
+    probs = torch.softmax((x @ router_w.t()).float(), dim=-1)
+    w, idx = torch.topk(probs, top_k, dim=-1)
+    if normalize:
+        w = w / w.sum(-1, keepdim=True)
+    out = torch.zeros_like(x, dtype=torch.float32)
+    for e in range(experts_up.shape[0]):
+        mask = (idx == e)
+        if not mask.any():
+            continue
+        tok, slot = mask.nonzero(as_tuple=True)
+        h = x[tok].float() @ experts_up[e].float()
+        h = glu_reference(h, activation) if is_gated(activation) else act_reference(h, activation)
+        y = h @ experts_down[e].float()
+        out.index_add_(0, tok, y * w[tok, slot].unsqueeze(-1))
+    return out

@@ -146,6 +146,10 @@ class DistributedOptimizer:
         self.edp_group = mesh.get_expert_data_parallel_group() if edp_group == "default" else edp_group
         self.tp_group = mesh.get_tensor_model_parallel_group() if tp_group == "default" else tp_group
         self.tp_size = _gsize(self.tp_group)
+        # every gradient (dense or expert) is a sum over all data-parallel ranks' losses once its
+        # reduction group has been summed (expert gradients already contain the tokens of the
+        # whole EP group), so the mean divides by the full data-parallel size
+        self.grad_div = float(_gsize(self.dp_group))
         self.sequence_parallel = mesh.sequence_parallel_enabled()
         self.zero = int(config.parallel.zero_stage) >= 1
         self.lr = o.max_lr
@@ -262,7 +266,7 @@ class DistributedOptimizer:
         total = torch.zeros(1, dtype=torch.float32, device=dev)
         for g in self.groups:
             lo, hi = g.shard_range(self.zero)
-            inv = 1.0 / (g.dp * g.dp)
+            inv = 1.0 / (self.grad_div * self.grad_div)
             for r in g.regions:
                 a, b = max(r.start, lo), min(r.end, hi)
                 if b <= a:
@@ -286,7 +290,7 @@ class DistributedOptimizer:
                     # expert shards differ across EP ranks: add the other ranks' expert parts
                     dense_total = torch.zeros_like(total)
                     g0 = self.groups[0]
-                    inv0 = 1.0 / (g0.dp * g0.dp)
+                    inv0 = 1.0 / (self.grad_div * self.grad_div)
                     for r in g0.regions:
                         w = inv0 / self.tp_size if r.tp_replicated else inv0
                         self._sumsq(g0.grad_buf[r.start:r.end], dense_total, w)
@@ -307,7 +311,7 @@ class DistributedOptimizer:
         p = g.param_buf[a:b]
         gr = g.grad_buf[a:b]
         b1, b2 = self.betas
-        gscale = 1.0 / g.dp
+        gscale = 1.0 / self.grad_div
         if self.offload:
             self._adam_offloaded(p, gr, mom, a - lo, b - lo, wd, coef, lr, gscale)
             return

@@ -159,7 +159,7 @@ class MuonState:
                     continue
             else:
                 grad_full = grad_local
-            gf = grad_full.float() * (coef.to(grad_full.device) / g.dp)
+            gf = grad_full.float() * (coef.to(grad_full.device) / eng.grad_div)
             if m.momentum is None:
                 m.momentum = torch.zeros_like(gf)
             m.momentum.mul_(self.momentum).add_(gf)

@@ -73,3 +73,34 @@ def test_trainer_native_loss_falls_and_matches_cpu():
 
     losses = run("bf16", True)
     assert losses[-1] < losses[0] - 0.3, losses
+
+
+def test_moe_block_native_matches_dense_restatement():
+    from ironcore_b200.models.moe import MoEBlock, moe_reference
+    from ironcore_b200.ops import native
+    from ironcore_b200.parallel import mesh
+
+    mesh.destroy_model_parallel()
+    cfg = _cfg("llama", "bf16")
+    cfg.model.moe(num_experts=8, top_k=2, expert_d_ffn=256, num_shared_experts=1, aux_loss_coeff=0.01)
+    torch.manual_seed(5)
+    blk = MoEBlock(cfg, dtype=torch.bfloat16, device=torch.device("cuda"))
+    for p in blk.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    x = (0.5 * torch.randn(700, 256, device="cuda")).bfloat16().requires_grad_(True)
+    out, aux = blk(x)
+    torch.cuda.synchronize()
+    native.check_status()
+    xf = x.detach().float().requires_grad_(True)
+    up = blk.experts_up.detach().float().requires_grad_(True)
+    down = blk.experts_down.detach().float().requires_grad_(True)
+    ref = moe_reference(xf, blk.router.weight.float(), up, down, 2, "swiglu")
+    shared = blk.shared(x.detach()).float()
+    assert (out.float() - (ref + shared)).abs().max().item() < 5e-2
+    dy = torch.randn_like(out)
+    out.backward(dy)
+    ref.backward(dy.float())
+    gu = blk.experts_up.grad.float()
+    assert (gu - up.grad).abs().max().item() < 5e-2 * max(up.grad.abs().max().item(), 1.0)
+    gd = blk.experts_down.grad.float()
+    assert (gd - down.grad).abs().max().item() < 5e-2 * max(down.grad.abs().max().item(), 1.0)
