@@ -70,6 +70,10 @@ class HFConfigManager:
 
 
 def _base_model(model):
+    """The object exposing canonical_state_dict(): the FSDP wrapper itself (it gathers shards
+    around the call) or the plain language model."""
+    if getattr(model, "is_fsdp_wrapper", False):
+        return model
     return model.module if hasattr(model, "module") else model
 
 
@@ -150,7 +154,8 @@ def save_checkpoint(config, model, optimizer=None, lr_scheduler=None, step: int 
             merged_state = {}
             canon = _canonical_optimizer_state(base, opt_sd["state"])
             for key in ("exp_avg", "exp_avg_sq"):
-                flat = {n: st[key].to(next(base.parameters()).device) for n, st in canon.items()}
+                dev0 = next(base.parameters()).device
+                flat = {n: st[key].to(dev0) for n, st in canon.items()}
                 merged = merge_model_parallel_state(flat, info, expert_names)
                 for n, t in merged.items():
                     merged_state.setdefault(n, {"step": canon[n]["step"]})[key] = t
@@ -198,7 +203,8 @@ def _canonical_optimizer_state(base, state: Dict[str, dict]) -> Dict[str, dict]:
     for name, st in state.items():
         name = name[7:] if name.startswith("module.") else name
         if ".linear_qkv." in name:
-            layer = base.model.layers[int(name.split(".")[2])]
+            inner = base.module if getattr(base, "is_fsdp_wrapper", False) else base
+            layer = inner.model.layers[int(name.split(".")[2])]
             qn = layer.heads_local * layer.head_dim
             q = {"step": st["step"]}
             kv = {"step": st["step"]}
