@@ -49,9 +49,10 @@ struct GemmArgs {
   const int* ag_signal;             // this rank's shard_ready[world] (written by the peers)
   int* ag_ready;                    // this rank's per-128-row-block arrival counters
   int ag_epoch;                     // call sequence number (flags are cumulative)
+  int ag_chunks_per_block;          // 8 KiB chunks in one 128-row block
 };
 
-constexpr int kAgSubChunks = 8;     // a 128-row block is copied as 8 units of 16 rows
+constexpr int kAgChunkBytes = 8192;  // copy granularity of the all-gather (one warp iteration)
 
 template <int A_MAJOR, int B_MAJOR, bool AG>
 __global__ void __launch_bounds__(AG ? kGemmThreads + 64 : kGemmThreads, 1)
@@ -132,7 +133,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           // local shard first, then the peers in ring order (the order the copy warps fetch them)
           mt = (mt + args.ag_rank * ag_mtiles_per_shard) % args.num_m_tiles;
           if (mt / ag_mtiles_per_shard != args.ag_rank) {
-            wait_flag_gpu(args.ag_ready + mt, args.ag_epoch * kAgSubChunks, args.status, kTimeoutLocalFlag);
+            wait_flag_gpu(args.ag_ready + mt, args.ag_epoch * args.ag_chunks_per_block, args.status, kTimeoutLocalFlag);
             fence_proxy_async_all();
           }
         }
@@ -146,7 +147,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if ((k0 & 127) == 0) {
               const int rb = k0 >> 7;
               if (rb / ag_mtiles_per_shard != args.ag_rank) {
-                wait_flag_gpu(args.ag_ready + rb, args.ag_epoch * kAgSubChunks, args.status, kTimeoutLocalFlag);
+                wait_flag_gpu(args.ag_ready + rb, args.ag_epoch * args.ag_chunks_per_block, args.status, kTimeoutLocalFlag);
                 fence_proxy_async_all();
               }
             }
@@ -410,18 +411,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   if (AG && warp >= 6) {
     // ------------------------------ all-gather copy warps ----------------------
-    // Unit = 16 token rows of one remote 128-row block. Units are visited peer by peer in ring
-    // order (rank+1 first) so that every rank pulls from a different peer at the same time.
+    // The remote shards are streamed as 8 KiB chunks, interleaved over all copy warps of the grid
+    // (2 per CTA) so that ~2 MiB of loads are in flight — enough to cover the NVLink round trip at
+    // full link bandwidth. Chunks are visited peer by peer in ring order (rank+1 first), so every
+    // rank pulls from a different peer at any time. Each finished chunk bumps the arrival counter
+    // of its 128-row block; a block is complete at epoch * chunks_per_block.
     const int cw = blockIdx.x * 2 + (warp - 6);
     const int n_cw = gridDim.x * 2;
-    const int units_per_shard = ag_mtiles_per_shard * kAgSubChunks;
-    const int total_units = (args.ag_world - 1) * units_per_shard;
-    const long long unit_bytes = 16LL * args.ag_row_bytes;
+    const long long shard_bytes = (long long)args.ag_rows_per_rank * args.ag_row_bytes;
+    const long long block_bytes = 128LL * args.ag_row_bytes;
+    const int chunks_per_shard = (int)(shard_bytes / kAgChunkBytes);
+    const int total_chunks = (args.ag_world - 1) * chunks_per_shard;
     int checked_peer = -1;
     bool peer_ok = true;
-    for (int u = cw; u < total_units; u += n_cw) {
-      const int step = u / units_per_shard + 1;
-      const int within = u - (step - 1) * units_per_shard;
+    for (int c = cw; c < total_chunks; c += n_cw) {
+      const int step = c / chunks_per_shard + 1;
+      const int within = c - (step - 1) * chunks_per_shard;
       const int q = (args.ag_rank + step) % args.ag_world;
       if (q != checked_peer) {
         int ok = 1;
@@ -430,27 +435,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         peer_ok = ok != 0;
         checked_peer = q;
       }
-      const int rb = q * ag_mtiles_per_shard + within / kAgSubChunks;           // 128-row block index
-      const long long off = ((long long)rb * 128 + (within % kAgSubChunks) * 16) * args.ag_row_bytes;
+      const long long off = (long long)q * shard_bytes + (long long)within * kAgChunkBytes;
       if (peer_ok) {
         const uint4* src = reinterpret_cast<const uint4*>(args.ag_peers[q] + off);
         uint4* dst = reinterpret_cast<uint4*>(args.ag_local + off);
-        const long long nvec = unit_bytes >> 4;
-        long long i = lane;
-        for (; i + 7 * 32 < nvec; i += 8 * 32) {
-          uint4 v[8];
+        uint4 v[16];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = __ldcv(src + i + j * 32);   // volatile load: never from a stale cache line
+        for (int j = 0; j < 16; ++j) v[j] = __ldcv(src + lane + j * 32);   // volatile: never a stale cache line
 #pragma unroll
-          for (int j = 0; j < 8; ++j) dst[i + j * 32] = v[j];
-        }
-        for (; i < nvec; i += 32) dst[i] = __ldcv(src + i);
+        for (int j = 0; j < 16; ++j) dst[lane + j * 32] = v[j];
       }
       __threadfence();
       __syncwarp();
       if (lane == 0) {
         fence_proxy_async_all();
-        red_release_gpu_add(args.ag_ready + rb, 1);
+        red_release_gpu_add(args.ag_ready + (int)(off / block_bytes), 1);
       }
     }
   }
@@ -555,7 +554,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, co
   else {
     args.ag_rank = 0; args.ag_world = 1; args.ag_rows_per_rank = 0; args.ag_row_bytes = 0;
     args.ag_local = nullptr; args.ag_peers = nullptr; args.ag_peer_signal = nullptr; args.ag_signal = nullptr;
-    args.ag_ready = nullptr; args.ag_epoch = 0;
+    args.ag_ready = nullptr; args.ag_epoch = 0; args.ag_chunks_per_block = 1;
   }
   args.M = M; args.N = N; args.K = K;
   args.num_m_tiles = (M + kBM - 1) / kBM;
@@ -612,7 +611,7 @@ ICB_API int icb_ag_gemm(void* gathered, const void* const* peers, int* const* pe
                         void* C, const void* bias, const void* residual, int N, long long ldb, long long ldc,
                         long long ldr, int a_major, int b_major, int in_dtype, int out_f32, int* status,
                         void* stream_) {
-  if (rows_per_rank % 128 != 0 || width % 8 != 0) return -7;
+  if (rows_per_rank % 128 != 0 || width % 32 != 0) return -7;   // 128-row blocks must be whole 8 KiB chunks
   GemmArgs ag;
   ag.ag_rank = rank; ag.ag_world = world; ag.ag_rows_per_rank = rows_per_rank;
   ag.ag_row_bytes = (long long)width * 2;
@@ -622,6 +621,7 @@ ICB_API int icb_ag_gemm(void* gathered, const void* const* peers, int* const* pe
   ag.ag_signal = signal;
   ag.ag_ready = ready;
   ag.ag_epoch = epoch;
+  ag.ag_chunks_per_block = (int)(128LL * width * 2 / kAgChunkBytes);
   const int rows = world * rows_per_rank;
   const int M = a_major == 0 ? rows : width;
   const int K = a_major == 0 ? width : rows;

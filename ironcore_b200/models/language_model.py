@@ -244,6 +244,19 @@ class LanguageModel(BaseModule):
             loss = loss + aux
         return loss
 
+    def token_logprobs(self, input_ids: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+        """log pi(labels[b, s] | input_ids[b, :s+1]) for every position, fp32 [B, S] (differentiable).
+        The log-prob is the negative of the fused vocab-parallel cross entropy, so the
+        ``[tokens, vocab]`` matrix is never expanded to fp32."""
+        dev = self.embedding.word_embeddings.weight.device
+        input_ids, labels = input_ids.to(dev), labels.to(dev)
+        b, s = input_ids.shape
+        x, _aux = self.hidden_states(input_ids)
+        logits = self.logits_from_hidden(x)
+        ce = vocab_parallel_cross_entropy(logits, labels.reshape(-1).clamp_min(-1), self.vocab_size,
+                                          tp_group=self.tp_group)
+        return -ce.view(b, s)
+
     # ------------------------------------------------------------------ canonical (checkpoint) names
     def canonical_state_dict(self) -> "OrderedDict[str, torch.Tensor]":
         """Local shard under the reference's parameter names: the fused ``linear_qkv`` is split

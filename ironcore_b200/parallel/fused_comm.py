@@ -44,8 +44,8 @@ class FusedTP:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.tokens, self.width, self.dtype = tokens, width, dtype
-        if tokens % self.world or (tokens // self.world) % 128 or width % 8:
-            raise ValueError("fused TP needs tokens/world to be a multiple of 128 and width a multiple of 8")
+        if tokens % self.world or (tokens // self.world) % 128 or width % 32:
+            raise ValueError("fused TP needs tokens/world to be a multiple of 128 and width a multiple of 32")
         self.rows = tokens // self.world
         es = 2
         self.max_n_tiles = (width + 255) // 256
@@ -215,7 +215,7 @@ def attach_fused_tp(model, config) -> Optional[FusedTP]:
     t = mesh.get_tensor_model_parallel_world_size()
     tokens = config.trainer.micro_batch_size * config.model.max_seq_len
     width = config.model.d_model
-    if t < 2 or tokens % t or (tokens // t) % 128 or width % 8:
+    if t < 2 or tokens % t or (tokens // t) % 128 or width % 32:
         return None
     from ..models.language_model import get_model_dtype
 

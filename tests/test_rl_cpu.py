@@ -1,0 +1,110 @@
+"""Rollout engine and GRPO on CPU: the paged-cache decode path must reproduce the cache-less
+full-prefix forward, sampling must be exact, the loss must match its formula."""
+
+import torch
+
+from helpers import tiny_config
+
+
+def _model(family="llama"):
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.models import LanguageModel
+    from ironcore_b200.parallel import mesh
+
+    mesh.destroy_model_parallel()
+    cfg = tiny_config(family, max_seq_len=64, max_position_embeddings=64)
+    cfg.trainer.use_flash_attn = False
+    validate_config(cfg)
+    torch.manual_seed(0)
+    return cfg, LanguageModel(cfg).eval()
+
+
+def test_paged_decode_matches_full_prefix_forward():
+    from ironcore_b200.rl import RolloutEngine
+
+    for family in ("llama", "gpt2"):
+        cfg, model = _model(family)
+        eng = RolloutEngine(model, cfg, max_seqs=3, max_seq_len=64, block_size=16, use_cuda_graph=False)
+        prompts = torch.randint(0, 512, (3, 20))
+        toks, logps = eng.generate(prompts, 12, temperature=0.0)
+        # greedy continuation with the cache-less model must give the same tokens
+        cur = prompts.clone()
+        for i in range(12):
+            logits = model(cur)[:, -1, :512]
+            nxt = logits.argmax(-1)
+            assert torch.equal(nxt, toks[:, 20 + i]), (family, i)
+            cur = torch.cat([cur, nxt[:, None]], dim=1)
+        # log-probs of the sampled tokens
+        full = model(toks[:, :-1])[:, 19:, :512].float()
+        ref_lp = torch.log_softmax(full, -1).gather(-1, toks[:, 20:, None]).squeeze(-1)
+        assert torch.allclose(logps, ref_lp, atol=1e-4)
+
+
+def test_kv_cache_allocation_and_free():
+    from ironcore_b200.rl import BlockKVCache
+
+    c = BlockKVCache(1, 2, 8, num_blocks=10, block_size=16, max_seqs=4, max_seq_len=64, dtype=torch.float32, device="cpu")
+    c.reserve(0, 17)
+    c.reserve(1, 16)
+    assert c.free_blocks == 7
+    assert len(set(c.block_table[0, :2].tolist()) | set(c.block_table[1, :1].tolist())) == 3
+    c.free(0)
+    assert c.free_blocks == 9
+    c.reserve_all(4, 32)
+    assert c.free_blocks == 9 - 2 * 4 + 1  # sequence 1 already owned one page... re-reserved consistently
+    
+
+def test_sampling_distribution_and_logprob():
+    from ironcore_b200.rl import sample_tokens
+
+    g = torch.Generator().manual_seed(0)
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0]]).repeat(20000, 1)
+    tok, lp = sample_tokens(logits, 1.0, generator=g)
+    freq = torch.bincount(tok, minlength=4).float() / 20000
+    assert torch.allclose(freq, torch.softmax(logits[0], -1), atol=0.015)
+    assert torch.allclose(lp, torch.log_softmax(logits, -1).gather(1, tok[:, None]).squeeze(1), atol=1e-5)
+    tok2, _ = sample_tokens(logits, 1.0, top_k=2, generator=g)
+    assert int(tok2.max()) <= 1
+    tok3, _ = sample_tokens(logits, 1.0, top_p=0.6, generator=g)
+    assert int(tok3.max()) == 0
+
+
+def test_grpo_loss_formula_and_advantages():
+    from ironcore_b200.rl import group_advantages, grpo_loss
+
+    torch.manual_seed(1)
+    r = torch.tensor([1.0, 0.0, 0.5, 0.5, 2.0, 2.0, 2.0, 2.0])
+    adv = group_advantages(r, 4)
+    assert abs(adv[:4].mean().item()) < 1e-6 and torch.allclose(adv[4:], torch.zeros(4), atol=1e-3)
+    lp = torch.randn(8, 5, requires_grad=True)
+    old = lp.detach() + 0.3 * torch.randn(8, 5)
+    ref = lp.detach() + 0.1 * torch.randn(8, 5)
+    a = torch.randn(8)
+    mask = torch.ones(8, 5)
+    loss, stats = grpo_loss(lp, old, ref, a, mask, 0.2, 0.04)
+    ratio = torch.exp(lp - old)
+    pg = -torch.minimum(ratio * a[:, None], ratio.clamp(0.8, 1.2) * a[:, None])
+    d = ref - lp
+    expect = (pg + 0.04 * (torch.exp(d) - d - 1)).mean()
+    assert torch.allclose(loss, expect, atol=1e-6)
+    loss.backward()
+    assert torch.isfinite(lp.grad).all()
+
+
+def test_grpo_trainer_runs_and_improves_reward_signal():
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.rl.trainer import GRPOTrainer
+
+    mesh.destroy_model_parallel()
+    cfg = tiny_config("llama", max_seq_len=48, max_position_embeddings=48)
+    cfg.trainer.use_flash_attn = False
+    cfg.rl(num_prompts=2, prompt_len=8, group_size=4, max_new_tokens=8, reward_vocab_subset=64)
+    cfg.trainer(micro_batch_size=4, train_batch_size=4, gradient_accumulation_steps=None)
+    cfg.operation.train_steps = 2
+    validate_config(cfg)
+    tr = GRPOTrainer(cfg)
+    st = tr.train_step(0)
+    assert st["rollout_tokens_per_s"] > 0 and abs(st["ratio_mean"] - 1.0) < 1e-3
+    st2 = tr.train_step(1)
+    assert st2["kl_mean"] >= 0.0
