@@ -62,8 +62,9 @@ def _merge_single_key_lists(node: Any) -> Any:
     return node
 
 
-def load_yaml_config(path) -> Dict[str, Any]:
-    """Read a YAML file with ``${ENV}`` interpolation and list-of-dicts merging."""
+def load_yaml_config(path, merge_lists: bool = True) -> Dict[str, Any]:
+    """Read a YAML file with ``${ENV}`` interpolation and (for trainer configs) merging of
+    lists of single-key mappings; dataset YAMLs keep their lists (``merge_lists=False``)."""
     p = Path(path)
     if not p.exists():
         raise FileNotFoundError(f"Config file not found: {p}")
@@ -71,7 +72,8 @@ def load_yaml_config(path) -> Dict[str, Any]:
         raw = yaml.safe_load(p.read_text(encoding="utf-8")) or {}
     except yaml.YAMLError as exc:
         raise ValueError(f"Error loading yaml config {p}: {exc}") from exc
-    return _merge_single_key_lists(_interpolate(raw))
+    doc = _interpolate(raw)
+    return _merge_single_key_lists(doc) if merge_lists else doc
 
 
 def get_dataset_base_dir() -> Path:

@@ -1,0 +1,149 @@
+"""Memory-mapped datasets over the binary format and weighted mixing of several sources.
+
+pretrain: fixed windows of ``seq_len + 1`` tokens starting every ``seq_len`` tokens (wrapping at the
+end), visited in a seeded shuffle and sharded ``index % dp_size == dp_rank``; sft / dpo: samples
+drawn by weighted sampling without replacement, then rank-sharded. Train / eval / test splits are
+contiguous token (pretrain) or sample (sft, dpo) ranges given by the split ratios.
+(Behavioural reference: ironcore/dataloader/universal_dataset.py:20-390.)"""
+
+from __future__ import annotations
+
+import json
+from pathlib import Path
+from typing import Dict, Iterator, List, Optional
+
+import numpy as np
+import torch
+from torch.utils.data import IterableDataset
+
+from .serializer import BIN_NAME, IDX_NAME
+
+
+class BinaryDataset:
+    def __init__(self, directory):
+        d = Path(directory)
+        if not (d / BIN_NAME).exists() or not (d / IDX_NAME).exists():
+            raise FileNotFoundError(f"{d} does not contain {BIN_NAME} / {IDX_NAME}; run `ironcore preprocess`")
+        self.index = np.load(d / IDX_NAME, allow_pickle=False)
+        meta = d / "meta.json"
+        if meta.exists():
+            dtype = np.dtype(json.loads(meta.read_text())["dtype"])
+        else:
+            nbytes = (d / BIN_NAME).stat().st_size
+            total = int(self.index["offset"][-1] + self.index["length"][-1]) if len(self.index) else 0
+            dtype = np.dtype(np.uint16) if total and nbytes // total == 2 else np.dtype(np.uint32)
+        self.tokens = np.memmap(d / BIN_NAME, dtype=dtype, mode="r")
+        self.directory = d
+
+    @property
+    def num_tokens(self) -> int:
+        return int(self.tokens.shape[0])
+
+    def __len__(self) -> int:
+        return len(self.index)
+
+    def sample(self, i: int) -> Dict:
+        rec = self.index[i]
+        o, n = int(rec["offset"]), int(rec["length"])
+        return {"tokens": np.asarray(self.tokens[o:o + n], dtype=np.int64), "type": str(rec["type"]),
+                "group_id": int(rec["group_id"]), "mask_ranges": json.loads(str(rec["mask_ranges"]) or "[]")}
+
+    def window(self, start: int, length: int) -> np.ndarray:
+        """``length`` tokens from ``start`` (wrapping around the end of the corpus)."""
+        total = self.num_tokens
+        start %= max(total, 1)
+        if start + length <= total:
+            return np.asarray(self.tokens[start:start + length], dtype=np.int64)
+        head = np.asarray(self.tokens[start:], dtype=np.int64)
+        reps = [head]
+        need = length - len(head)
+        while need > 0:
+            part = np.asarray(self.tokens[:min(need, total)], dtype=np.int64)
+            reps.append(part)
+            need -= len(part)
+        return np.concatenate(reps)
+
+
+def _split_range(n: int, splits: List[float], split: str):
+    idx = {"train": 0, "eval": 1, "test": 2}[split]
+    bounds = np.cumsum([0.0] + list(splits))
+    lo, hi = int(round(bounds[idx] * n)), int(round(bounds[idx + 1] * n))
+    return lo, hi
+
+
+class WeightedMixingDataset(IterableDataset):
+    def __init__(self, directories: List, ratios: List[float], mode: str, split: str, seq_len: int,
+                 splits: List[float], seed: int = 1337, dp_rank: int = 0, dp_size: int = 1, epochs: Optional[int] = None):
+        self.sets = [BinaryDataset(d) for d in directories]
+        w = np.asarray(ratios, dtype=np.float64)
+        self.weights = w / w.sum()
+        self.mode, self.split, self.seq_len, self.splits = mode, split, seq_len, splits
+        self.seed, self.dp_rank, self.dp_size = seed, dp_rank, dp_size
+        self.epochs = epochs
+        self.cursor = 0          # samples yielded so far on this rank (saved in checkpoints)
+
+    def _pretrain_positions(self):
+        items = []
+        for si, ds in enumerate(self.sets):
+            lo, hi = _split_range(ds.num_tokens, self.splits, self.split)
+            for start in range(lo, max(lo, hi - 1), self.seq_len):
+                items.append((si, start))
+        return items
+
+    def _sample_items(self):
+        items, probs = [], []
+        for si, ds in enumerate(self.sets):
+            lo, hi = _split_range(len(ds), self.splits, self.split)
+            n = max(hi - lo, 0)
+            for i in range(lo, hi):
+                items.append((si, i))
+                probs.append(self.weights[si] / max(n, 1))
+        return items, np.asarray(probs)
+
+    def __iter__(self) -> Iterator[Dict]:
+        epoch = 0
+        while self.epochs is None or epoch < self.epochs:
+            rng = np.random.default_rng(self.seed + epoch)
+            if self.mode == "pretrain":
+                items = self._pretrain_positions()
+                if not items:
+                    return
+                # weight the sources by replicating their share of the shuffle
+                order = rng.permutation(len(items))
+                for j, k in enumerate(order):
+                    if j % self.dp_size != self.dp_rank:
+                        continue
+                    si, start = items[k]
+                    self.cursor += 1
+                    yield {"tokens": self.sets[si].window(start, self.seq_len + 1), "type": "pretrain"}
+            else:
+                items, probs = self._sample_items()
+                if not items:
+                    return
+                probs = probs / probs.sum()
+                order = rng.choice(len(items), size=len(items), replace=False, p=probs)
+                if self.mode == "dpo":
+                    # keep chosen / rejected of a group together: iterate over group ids
+                    seen = set()
+                    j = 0
+                    for k in order:
+                        si, i = items[k]
+                        gid = (si, int(self.sets[si].index[i]["group_id"]))
+                        if gid in seen:
+                            continue
+                        seen.add(gid)
+                        if j % self.dp_size == self.dp_rank:
+                            grp = [x for x in range(len(self.sets[si])) if int(self.sets[si].index[x]["group_id"]) == gid[1]]
+                            pair = {str(self.sets[si].index[x]["type"]): self.sets[si].sample(x) for x in grp}
+                            if "dpo_chosen" in pair and "dpo_rejected" in pair:
+                                self.cursor += 1
+                                yield {"chosen": pair["dpo_chosen"], "rejected": pair["dpo_rejected"], "type": "dpo"}
+                        j += 1
+                else:
+                    for j, k in enumerate(order):
+                        if j % self.dp_size != self.dp_rank:
+                            continue
+                        si, i = items[k]
+                        self.cursor += 1
+                        yield self.sets[si].sample(i)
+            epoch += 1

@@ -1,0 +1,43 @@
+"""File-backed iterators for the trainer: dataset YAML -> mixing datasets -> DataLoader -> batches."""
+
+from __future__ import annotations
+
+import itertools
+from typing import Dict
+
+import torch
+from torch.utils.data import DataLoader
+
+from .collator import UniversalCollator
+from .data_config import UniversalDataConfig
+from .dataset import WeightedMixingDataset
+
+
+def build_file_iterators(config, dp_rank: int, dp_size: int) -> Dict[str, object]:
+    dcfg = UniversalDataConfig.from_yaml(config.data.config_path)
+    task = str(getattr(config.data, "task_type", "pretrain")).lower()
+    seq_len = config.model.max_seq_len
+    pad = config.model.pad_token_id if config.model.pad_token_id is not None else 0
+    out = {}
+    for split in ("train", "eval", "test"):
+        sources = {"train": dcfg.datasets, "eval": dcfg.eval_datasets or dcfg.datasets,
+                   "test": dcfg.test_datasets or dcfg.datasets}[split]
+        enabled = split == "train" or (split == "eval" and config.trainer.do_eval) or \
+            (split == "test" and config.trainer.do_test)
+        sources = [s for s in sources if s.task_type == task]
+        if not enabled or not sources:
+            out[split] = None
+            continue
+        own_split = split if (split == "train" or not {"eval": dcfg.eval_datasets, "test": dcfg.test_datasets}[split]) \
+            else "train"
+        splits = dcfg.splits if own_split == split else [1.0, 0.0, 0.0]
+        ds = WeightedMixingDataset([s.output_path for s in sources], [s.ratio for s in sources], task, own_split,
+                                   seq_len, splits, seed=1337, dp_rank=dp_rank, dp_size=dp_size,
+                                   epochs=None if split == "train" else 1)
+        bs = {"train": config.trainer.micro_batch_size,
+              "eval": config.trainer.eval_batch_size or config.trainer.micro_batch_size,
+              "test": config.trainer.test_batch_size or config.trainer.micro_batch_size}[split]
+        loader = DataLoader(ds, batch_size=bs, collate_fn=UniversalCollator(task, seq_len, pad), num_workers=0,
+                            pin_memory=torch.cuda.is_available(), drop_last=(split == "train"))
+        out[split] = iter(loader)
+    return out

@@ -1,0 +1,118 @@
+"""Micro-benchmark of the fused TP kernels against the NCCL + GEMM composition.
+
+    python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 \
+        -m ironcore_b200.parallel.bench_fused [--tokens 4096 --width 4096 --ffn 11008]
+
+Times (CUDA events, max over ranks, L2 flushed between launches) the four call sites of a
+Llama-shape layer at tensor-parallel size N and prints one JSON line per case with the
+achieved time, the NCCL-composition time and the roofline (slower of GEMM time at the
+measured bf16 peak and bytes over NVLink at the measured peer bandwidth).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--width", type=int, default=4096)
+    ap.add_argument("--ffn", type=int, default=11008)
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+    from ironcore_b200.ops import kernels, native
+    from ironcore_b200.parallel.fused_comm import FusedTP
+
+    t, d, f = args.tokens, args.width, args.ffn
+    ws = FusedTP(t, d, dist.group.WORLD)
+    rows = t // world
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    peak_tflops, link_gbs = 1414.0, 770.0
+
+    def timeit(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        times = []
+        for _ in range(args.iters):
+            flush.zero_()
+            dist.barrier()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e))
+        times.sort()
+        v = torch.tensor([times[len(times) // 2]], device="cuda")
+        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        return float(v.item())
+
+    cases = []
+    # column-parallel forward: AG(x)[t, d] @ W[d, n_local]
+    for name, n_local in (("qkv_fwd", 3 * d // world), ("gate_up_fwd", 2 * f // world)):
+        n_local = (n_local + 7) // 8 * 8
+        x = torch.randn(rows, d, device="cuda").bfloat16()
+        w = torch.randn(d, n_local, device="cuda").bfloat16()
+        full = torch.empty(t, d, device="cuda", dtype=torch.bfloat16)
+
+        def fused():
+            ws.ag_gemm(x, w, a_major=0, b_major=1, n=n_local)
+
+        def nccl():
+            dist.all_gather_into_tensor(full, x)
+            kernels.mm_nn(full, w)
+
+        def gemm_only():
+            kernels.mm_nn(full, w)
+
+        flops = 2.0 * t * d * n_local
+        wire = (world - 1) * rows * d * 2
+        cases.append((name, "ag_gemm", fused, nccl, gemm_only, flops, wire))
+    # row-parallel forward: (x[t, k_local] @ W[k_local, d]) -> RS
+    for name, k_local in (("attn_out_fwd", d // world), ("down_fwd", f // world)):
+        k_local = (k_local + 7) // 8 * 8
+        a = torch.randn(t, k_local, device="cuda").bfloat16()
+        w = torch.randn(k_local, d, device="cuda").bfloat16()
+        out = torch.empty(rows, d, device="cuda", dtype=torch.bfloat16)
+
+        def fused(a=a, w=w):
+            ws.gemm_rs(a, w, b_major=1)
+
+        def nccl(a=a, w=w, out=out):
+            y = kernels.mm_nn(a, w)
+            dist.reduce_scatter_tensor(out, y)
+
+        def gemm_only(a=a, w=w):
+            kernels.mm_nn(a, w)
+
+        flops = 2.0 * t * d * k_local
+        wire = (world - 1) * rows * d * 2
+        cases.append((name, "gemm_rs", fused, nccl, gemm_only, flops, wire))
+    for name, kind, fused, nccl, gemm_only, flops, wire in cases:
+        tf = timeit(fused)
+        tn = timeit(nccl)
+        tg = timeit(gemm_only)
+        roof_ms = max(flops / (peak_tflops * 1e9), wire / (link_gbs * 1e6))
+        if rank == 0:
+            print(json.dumps({"case": name, "kind": kind, "world": world, "fused_ms": tf, "nccl_plus_gemm_ms": tn,
+                              "gemm_only_ms": tg, "roofline_ms": roof_ms, "fraction_of_roofline": roof_ms / tf,
+                              "wire_mb": wire / 1e6, "gflop": flops / 1e9}), flush=True)
+    torch.cuda.synchronize()
+    native.check_status()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

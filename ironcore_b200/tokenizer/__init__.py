@@ -58,7 +58,13 @@ def _try_hf(name_or_path: str, tokenizer_type: str):
             from transformers import GPT2TokenizerFast as Cls
         else:
             from transformers import AutoTokenizer as Cls
-        return Cls.from_pretrained(name_or_path, local_files_only=True)
+        if not name_or_path or str(name_or_path).lower() in ("none", "stub"):
+            return None
+        tok = Cls.from_pretrained(name_or_path, local_files_only=True)
+        # a tokenizer built without its vocabulary files encodes everything to nothing: reject it
+        if len(tok.encode("hello world")) == 0 or len(tok) < 256:
+            return None
+        return tok
     except Exception:
         return None
 
