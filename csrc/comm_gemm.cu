@@ -45,6 +45,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem + GemmSmem::a_off;
   uint8_t* smem_b = smem + GemmSmem::b_off;
+  uint8_t* smem_slab = smem + GemmSmem::slab_off;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + GemmSmem::bar_off);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tfull_bar = empty_bar + kStages;
@@ -160,19 +161,24 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t acc_ph = (tcount >> 1) & 1;
       mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, args.status, kTimeoutTmemFull);
       tc_fence_after();
-      const size_t slot_row = (size_t)args.rank * args.rows_per_rank + (size_t)lm * 128 + row;
-      uint8_t* dst_row = args.peer_recv[owner] + slot_row * args.N * 2;
+      // Rows of this tile inside the owner's receive slot of the sending rank.
+      const size_t slot_row0 = (size_t)args.rank * args.rows_per_rank + (size_t)lm * 128;
+      uint8_t* dst_tile = args.peer_recv[owner] + slot_row0 * args.N * 2;
+      // The accumulator leaves in two halves of 128 columns. Each half is staged in shared memory
+      // (two 128-byte-swizzled slabs) and then written out cooperatively so that every warp store
+      // covers two rows x 256 contiguous bytes: NVLink sees full-line writes instead of 16-byte pieces.
 #pragma unroll 1
-      for (int sub = 0; sub < kBN / 32; ++sub) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN + sub * 32, r);
-        tmem_ld_wait();
-        if (sub == kBN / 32 - 1) {
-          tc_fence_before();
-          mbar_arrive(&tempty_bar[acc]);
-        }
-        const int n_glob = n0 + sub * 32;
-        if (n_glob + 32 <= args.N) {
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+        for (int sub = 0; sub < 4; ++sub) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN + half * 128 + sub * 32, r);
+          tmem_ld_wait();
+          if (half == 1 && sub == 3) {
+            tc_fence_before();
+            mbar_arrive(&tempty_bar[acc]);
+          }
+          uint8_t* srow = smem_slab + (sub >> 1) * kSlabBytes + row * 128;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             uint4 u;
@@ -187,24 +193,33 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               u.z = pack_f16x2(__uint_as_float(r[c * 8 + 4]), __uint_as_float(r[c * 8 + 5]));
               u.w = pack_f16x2(__uint_as_float(r[c * 8 + 6]), __uint_as_float(r[c * 8 + 7]));
             }
-            *reinterpret_cast<uint4*>(dst_row + ((size_t)n_glob + c * 8) * 2) = u;
-          }
-        } else {
-          for (int j = 0; j < 32; ++j) {
-            if (n_glob + j < args.N) {
-              const float f = __uint_as_float(r[j]);
-              uint16_t h;
-              if (args.in_fmt == 1) { __nv_bfloat16 b = __float2bfloat16(f); h = *reinterpret_cast<uint16_t*>(&b); }
-              else { __half b = __float2half(f); h = *reinterpret_cast<uint16_t*>(&b); }
-              reinterpret_cast<uint16_t*>(dst_row)[n_glob + j] = h;
-            }
+            const int piece = (sub & 1) * 4 + c;
+            *reinterpret_cast<uint4*>(srow + ((piece ^ (row & 7)) << 4)) = u;
           }
         }
+        named_barrier(1, 128);
+        const int col_base = n0 + half * 128;
+#pragma unroll 4
+        for (int k = 0; k < 16; ++k) {
+          const int idx = k * 128 + et;
+          const int rr = idx >> 4;            // row of the tile
+          const int p16 = idx & 15;           // 16-byte piece inside the 256-byte half row
+          const int col = col_base + p16 * 8;
+          if (col < args.N) {
+            const uint4 u = *reinterpret_cast<const uint4*>(smem_slab + (p16 >> 3) * kSlabBytes + rr * 128 +
+                                                            (((p16 & 7) ^ (rr & 7)) << 4));
+            *reinterpret_cast<uint4*>(dst_tile + ((size_t)rr * args.N + col) * 2) = u;
+          }
+        }
+        named_barrier(1, 128);
       }
-      // publish the tile: all 128 rows are written -> one arrival on the owner's counter
-      __threadfence_system();
+      // publish the tile: all 128 rows are written -> one arrival on the owner's counter. The barrier
+      // orders every thread's stores before thread 0, whose system-scope fence + release are cumulative.
       named_barrier(1, 128);
-      if (et == 0) red_release_sys_add(args.peer_flags[owner] + lm * args.num_n_tiles + nt, 1);
+      if (et == 0) {
+        __threadfence_system();
+        red_release_sys_add(args.peer_flags[owner] + lm * args.num_n_tiles + nt, 1);
+      }
       ++tcount;
     }
   }
@@ -240,41 +255,62 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           bias_v[2 * t] = f.x; bias_v[2 * t + 1] = f.y;
         }
       }
+      // four rows per pass: all partial loads of the pass are issued before any is consumed
 #pragma unroll 1
-      for (int i = 0; i < 16; ++i) {
-        const int lrow = lm * 128 + rg * 16 + i;
-        float acc[8];
+      for (int i0 = 0; i0 < 16; i0 += 4) {
+        float acc[4][8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = bias_v[j];
-        for (int src = 0; src < args.world; ++src) {
-          const uint8_t* p = args.recv + (((size_t)src * args.rows_per_rank + lrow) * args.N + col) * 2;
-          const uint4 v = __ldcv(reinterpret_cast<const uint4*>(p));
-          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        for (int r = 0; r < 4; ++r)
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            float2 f = args.in_fmt == 1 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
-            acc[2 * t] += f.x; acc[2 * t + 1] += f.y;
-          }
-        }
+          for (int j = 0; j < 8; ++j) acc[r][j] = bias_v[j];
+        uint4 resv[4];
         if (args.residual != nullptr) {
-          const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(args.residual) +
-                                                          ((size_t)lrow * args.ldr + col) * 2);
-          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            float2 f = args.in_fmt == 1 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
-            acc[2 * t] += f.x; acc[2 * t + 1] += f.y;
+          for (int r = 0; r < 4; ++r) {
+            const int lrow = lm * 128 + rg * 16 + i0 + r;
+            resv[r] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(args.residual) +
+                                                      ((size_t)lrow * args.ldr + col) * 2);
           }
         }
-        uint4 o;
-        if (args.in_fmt == 1) {
-          o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-          o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
-        } else {
-          o.x = pack_f16x2(acc[0], acc[1]); o.y = pack_f16x2(acc[2], acc[3]);
-          o.z = pack_f16x2(acc[4], acc[5]); o.w = pack_f16x2(acc[6], acc[7]);
+        for (int src = 0; src < args.world; ++src) {
+          uint4 v[4];
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const int lrow = lm * 128 + rg * 16 + i0 + r;
+            v[r] = __ldcv(reinterpret_cast<const uint4*>(
+                args.recv + (((size_t)src * args.rows_per_rank + lrow) * args.N + col) * 2));
+          }
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const uint32_t w[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              float2 f = args.in_fmt == 1 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
+              acc[r][2 * t] += f.x; acc[r][2 * t + 1] += f.y;
+            }
+          }
         }
-        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(args.out) + ((size_t)lrow * args.ldo + col) * 2) = o;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int lrow = lm * 128 + rg * 16 + i0 + r;
+          if (args.residual != nullptr) {
+            const uint32_t w[4] = {resv[r].x, resv[r].y, resv[r].z, resv[r].w};
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              float2 f = args.in_fmt == 1 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
+              acc[r][2 * t] += f.x; acc[r][2 * t + 1] += f.y;
+            }
+          }
+          uint4 o;
+          if (args.in_fmt == 1) {
+            o.x = pack_bf16x2(acc[r][0], acc[r][1]); o.y = pack_bf16x2(acc[r][2], acc[r][3]);
+            o.z = pack_bf16x2(acc[r][4], acc[r][5]); o.w = pack_bf16x2(acc[r][6], acc[r][7]);
+          } else {
+            o.x = pack_f16x2(acc[r][0], acc[r][1]); o.y = pack_f16x2(acc[r][2], acc[r][3]);
+            o.z = pack_f16x2(acc[r][4], acc[r][5]); o.w = pack_f16x2(acc[r][6], acc[r][7]);
+          }
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(args.out) + ((size_t)lrow * args.ldo + col) * 2) = o;
+        }
       }
     }
   }

@@ -13,11 +13,12 @@
 // * Grouped forms for mixture-of-experts: group_mode 1 picks B (and bias) per
 //   128-row M tile from a lookup table; group_mode 2 computes one C per group
 //   over a K range taken from an offsets table (expert weight gradients).
-// * Fused all-gather -> GEMM (template flag AG): A lives in a gathered buffer whose remote
-//   row blocks are pulled from the peers' copies over NVLink (plain P2P loads) by two extra
-//   copy warps per CTA while the tensor core works on row blocks that already arrived
-//   (local shard first, then peers in ring order). Per-128-row flags (release/acquire,
-//   cumulative sequence numbers) gate the TMA producer.
+// * Fused all-gather -> GEMM (template flag AG): A lives in a gathered buffer. Two extra copy
+//   warps per CTA push this rank's shard into every peer's buffer over NVLink (plain P2P
+//   stores, fire-and-forget, peers visited in ring order) and bump the peer's per-128-row
+//   arrival counters with system-scope releases, while the tensor core works on the row
+//   blocks that are already there (local shard first, then the shards in the order they
+//   arrive). The TMA producer waits (acquire, bounded) on the counters of remote blocks.
 // * Every wait is bounded: on timeout a status word is set and the kernel drains.
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA
@@ -47,12 +48,21 @@ struct GemmArgs {
   uint8_t* const* ag_peers;         // device array [world]: every rank's gathered buffer (peer pointers)
   int* const* ag_peer_signal;       // device array [world]: every rank's shard_ready[world] array
   const int* ag_signal;             // this rank's shard_ready[world] (written by the peers)
-  int* ag_ready;                    // this rank's per-128-row-block arrival counters
+  int* ag_ready;                    // this rank's per-128-row-block arrival counters (bumped by the peers)
+  int* const* ag_peer_ready;        // device array [world]: every rank's arrival counters
   int ag_epoch;                     // call sequence number (flags are cumulative)
   int ag_chunks_per_block;          // 8 KiB chunks in one 128-row block
 };
 
 constexpr int kAgChunkBytes = 8192;  // copy granularity of the all-gather (one warp iteration)
+
+// Position `seq` of the visiting order -> index in rank-major order: shard 0 of the visiting order is
+// this rank's own, shard s belongs to rank - s (mod world).
+__device__ __forceinline__ int ag_rotate(int seq, int per_shard, int rank, int world) {
+  const int s = seq / per_shard;
+  const int owner = (rank - s + world) % world;
+  return owner * per_shard + (seq - s * per_shard);
+}
 
 template <int A_MAJOR, int B_MAJOR, bool AG>
 __global__ void __launch_bounds__(AG ? kGemmThreads + 64 : kGemmThreads, 1)
@@ -97,14 +107,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (AG) {
-    // Tell every peer that this rank's shard (written before this kernel in stream order) is readable.
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
-      __threadfence_system();
-      for (int q = 0; q < args.ag_world; ++q)
-        if (q != args.ag_rank) st_release_sys(args.ag_peer_signal[q] + args.ag_rank, args.ag_epoch);
-    }
-  }
   const int ag_mtiles_per_shard = AG ? max(args.ag_rows_per_rank >> 7, 1) : 1;
 
   const int tiles_per_group = args.num_m_tiles * args.num_n_tiles;
@@ -130,10 +132,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (grp < 0) continue;
         }
         if (AG && A_MAJOR == 0) {
-          // local shard first, then the peers in ring order (the order the copy warps fetch them)
-          mt = (mt + args.ag_rank * ag_mtiles_per_shard) % args.num_m_tiles;
+          // local shard first, then rank-1, rank-2, ... (the order in which the peers' pushes land)
+          mt = ag_rotate(mt, ag_mtiles_per_shard, args.ag_rank, args.ag_world);
           if (mt / ag_mtiles_per_shard != args.ag_rank) {
-            wait_flag_gpu(args.ag_ready + mt, args.ag_epoch * args.ag_chunks_per_block, args.status, kTimeoutLocalFlag);
+            wait_flag_sys(args.ag_ready + mt, args.ag_epoch * args.ag_chunks_per_block, args.status, kTimeoutPeerFlag);
             fence_proxy_async_all();
           }
         }
@@ -143,11 +145,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           int k0 = kseq;
           if (AG && A_MAJOR == 1) {
             // the reduction runs over token rows: start with the local shard's rows
-            k0 = (kseq + args.ag_rank * args.ag_rows_per_rank) % args.K;
+            k0 = ag_rotate(kseq, args.ag_rows_per_rank, args.ag_rank, args.ag_world);
             if ((k0 & 127) == 0) {
               const int rb = k0 >> 7;
               if (rb / ag_mtiles_per_shard != args.ag_rank) {
-                wait_flag_gpu(args.ag_ready + rb, args.ag_epoch * args.ag_chunks_per_block, args.status, kTimeoutLocalFlag);
+                wait_flag_sys(args.ag_ready + rb, args.ag_epoch * args.ag_chunks_per_block, args.status, kTimeoutPeerFlag);
                 fence_proxy_async_all();
               }
             }
@@ -246,7 +248,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         grp = args.group_table[mt];
         if (grp < 0) continue;
       }
-      if (AG && A_MAJOR == 0) mt = (mt + args.ag_rank * ag_mtiles_per_shard) % args.num_m_tiles;
+      if (AG && A_MAJOR == 0) mt = ag_rotate(mt, ag_mtiles_per_shard, args.ag_rank, args.ag_world);
       const bool empty_k = (k_end <= k_begin);
       const int m0 = mt * kBM, n0 = nt * kBN;
       const uint32_t acc = tcount & 1;
@@ -411,45 +413,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   if (AG && warp >= 6) {
     // ------------------------------ all-gather copy warps ----------------------
-    // The remote shards are streamed as 8 KiB chunks, interleaved over all copy warps of the grid
-    // (2 per CTA) so that ~2 MiB of loads are in flight — enough to cover the NVLink round trip at
-    // full link bandwidth. Chunks are visited peer by peer in ring order (rank+1 first), so every
-    // rank pulls from a different peer at any time. Each finished chunk bumps the arrival counter
-    // of its 128-row block; a block is complete at epoch * chunks_per_block.
+    // Push model: this rank's shard is streamed as 8 KiB chunks, interleaved over all copy warps of
+    // the grid (2 per CTA), into every peer's gathered buffer. Stores need no round trip, so a few
+    // warps saturate the link. Peers are visited in ring order (rank+1 first): at any moment every
+    // rank writes to a different peer. Each finished chunk bumps the arrival counter of its 128-row
+    // block on the *peer* (release at system scope, cumulative over the warp's stores); a block is
+    // complete at epoch * chunks_per_block.
     const int cw = blockIdx.x * 2 + (warp - 6);
     const int n_cw = gridDim.x * 2;
     const long long shard_bytes = (long long)args.ag_rows_per_rank * args.ag_row_bytes;
     const long long block_bytes = 128LL * args.ag_row_bytes;
     const int chunks_per_shard = (int)(shard_bytes / kAgChunkBytes);
     const int total_chunks = (args.ag_world - 1) * chunks_per_shard;
-    int checked_peer = -1;
-    bool peer_ok = true;
     for (int c = cw; c < total_chunks; c += n_cw) {
       const int step = c / chunks_per_shard + 1;
       const int within = c - (step - 1) * chunks_per_shard;
       const int q = (args.ag_rank + step) % args.ag_world;
-      if (q != checked_peer) {
-        int ok = 1;
-        if (lane == 0) ok = wait_flag_sys(args.ag_signal + q, args.ag_epoch, args.status, kTimeoutPeerFlag) ? 1 : 0;
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        peer_ok = ok != 0;
-        checked_peer = q;
-      }
-      const long long off = (long long)q * shard_bytes + (long long)within * kAgChunkBytes;
-      if (peer_ok) {
-        const uint4* src = reinterpret_cast<const uint4*>(args.ag_peers[q] + off);
-        uint4* dst = reinterpret_cast<uint4*>(args.ag_local + off);
-        uint4 v[16];
+      const long long off = (long long)args.ag_rank * shard_bytes + (long long)within * kAgChunkBytes;
+      const uint4* src = reinterpret_cast<const uint4*>(args.ag_local + off);
+      uint4* dst = reinterpret_cast<uint4*>(args.ag_peers[q] + off);
+      uint4 v[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = __ldcv(src + lane + j * 32);   // volatile: never a stale cache line
+      for (int j = 0; j < 16; ++j) v[j] = src[lane + j * 32];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) dst[lane + j * 32] = v[j];
-      }
-      __threadfence();
+      for (int j = 0; j < 16; ++j) dst[lane + j * 32] = v[j];
       __syncwarp();
       if (lane == 0) {
-        fence_proxy_async_all();
-        red_release_gpu_add(args.ag_ready + (int)(off / block_bytes), 1);
+        __threadfence_system();
+        red_release_sys_add(args.ag_peer_ready[q] + (int)(off / block_bytes), 1);
       }
     }
   }
@@ -554,7 +545,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, co
   else {
     args.ag_rank = 0; args.ag_world = 1; args.ag_rows_per_rank = 0; args.ag_row_bytes = 0;
     args.ag_local = nullptr; args.ag_peers = nullptr; args.ag_peer_signal = nullptr; args.ag_signal = nullptr;
-    args.ag_ready = nullptr; args.ag_epoch = 0; args.ag_chunks_per_block = 1;
+    args.ag_ready = nullptr; args.ag_epoch = 0; args.ag_chunks_per_block = 1; args.ag_peer_ready = nullptr;
   }
   args.M = M; args.N = N; args.K = K;
   args.num_m_tiles = (M + kBM - 1) / kBM;
@@ -599,14 +590,14 @@ ICB_API int icb_gemm(const void* A, const void* B, void* C, const void* bias, co
 //   gathered : this rank's gathered activation buffer [world * rows_per_rank, width] (16-bit, contiguous);
 //              the local shard's rows must already be in place (stream order).
 //   peers    : device array [world] of every rank's gathered buffer (symmetric-memory peer pointers).
-//   peer_signal : device array [world] of every rank's shard_ready[world] int array; signal = this rank's own.
+//   peer_ready : device array [world] of every rank's arrival-counter array; `signal` is unused (reserved).
 //   ready    : this rank's int array [world * rows_per_rank / 128] of cumulative arrival counters.
 //   epoch    : 1, 2, 3, ... per call on this workspace (same on every rank).
 //   a_major 0: C[M = world*rows_per_rank, N] = gathered[M, K = width] * B        (forward / dgrad of a row-parallel layer)
 //   a_major 1: C[M = width, N] = gathered^T * B[K = world*rows_per_rank, N]      (wgrad: reduction over gathered rows)
-// Remote rows are pulled with plain P2P loads by copy warps inside the same kernel; the tensor core
-// starts with the local shard and follows the peers in ring order.
-ICB_API int icb_ag_gemm(void* gathered, const void* const* peers, int* const* peer_signal, const int* signal,
+// The local shard is pushed to every peer with plain P2P stores by copy warps inside the same kernel;
+// the tensor core starts with the local shard and follows the other shards in arrival order.
+ICB_API int icb_ag_gemm(void* gathered, const void* const* peers, int* const* peer_ready, const int* signal,
                         int* ready, int rank, int world, int rows_per_rank, int width, int epoch, const void* B,
                         void* C, const void* bias, const void* residual, int N, long long ldb, long long ldc,
                         long long ldr, int a_major, int b_major, int in_dtype, int out_f32, int* status,
@@ -617,7 +608,8 @@ ICB_API int icb_ag_gemm(void* gathered, const void* const* peers, int* const* pe
   ag.ag_row_bytes = (long long)width * 2;
   ag.ag_local = reinterpret_cast<uint8_t*>(gathered);
   ag.ag_peers = reinterpret_cast<uint8_t* const*>(const_cast<void* const*>(reinterpret_cast<const void* const*>(peers)));
-  ag.ag_peer_signal = peer_signal;
+  ag.ag_peer_signal = nullptr;
+  ag.ag_peer_ready = peer_ready;
   ag.ag_signal = signal;
   ag.ag_ready = ready;
   ag.ag_epoch = epoch;

@@ -66,14 +66,14 @@ def main():
         w = torch.randn(d, n_local, device="cuda").bfloat16()
         full = torch.empty(t, d, device="cuda", dtype=torch.bfloat16)
 
-        def fused():
+        def fused(x=x, w=w, n_local=n_local):
             ws.ag_gemm(x, w, a_major=0, b_major=1, n=n_local)
 
-        def nccl():
+        def nccl(x=x, w=w, full=full):
             dist.all_gather_into_tensor(full, x)
             kernels.mm_nn(full, w)
 
-        def gemm_only():
+        def gemm_only(w=w, full=full):
             kernels.mm_nn(full, w)
 
         flops = 2.0 * t * d * n_local

@@ -3,8 +3,8 @@
 ``FusedTP`` owns two symmetric-memory workspaces shared by every layer of a model:
 
 * gather workspace  : two (call-parity) gathered activation buffers ``[M, d]`` plus the
-  per-128-row arrival counters and the per-peer "shard ready" words used by
-  ``icb_ag_gemm`` (all-gather -> GEMM in one kernel);
+  per-128-row arrival counters that the peers bump when their pushed shard chunks have
+  landed, used by ``icb_ag_gemm`` (all-gather -> GEMM in one kernel);
 * scatter workspace : two receive buffers ``[t][M/t][d]`` plus per-tile arrival counters used
   by ``icb_gemm_rs`` (GEMM -> reduce-scatter in one kernel).
 
@@ -59,6 +59,7 @@ class FusedTP:
         self.g_views = [self.gbuf.view(self._g_off[p], (tokens, width), dtype) for p in range(2)]
         self.g_peers = [self.gbuf.peer_table(self._g_off[p]) for p in range(2)]
         self.g_peer_signal = self.gbuf.peer_table(self._g_signal_off)
+        self.g_peer_ready = self.gbuf.peer_table(self._g_ready_off)
         self.g_ready = self.gbuf.view(self._g_ready_off, (tokens // 128,), torch.int32)
         self.g_signal = self.gbuf.view(self._g_signal_off, (self.world,), torch.int32)
         self.g_epoch = 0
@@ -91,7 +92,7 @@ class FusedTP:
         if out is None:
             out = torch.empty((m, n), dtype=out_dtype, device=x_shard.device)
         ldr = residual.stride(0) if residual is not None else 0
-        call("icb_ag_gemm", ptr(gathered), ptr(self.g_peers[par]), ptr(self.g_peer_signal), ptr(self.g_signal),
+        call("icb_ag_gemm", ptr(gathered), ptr(self.g_peers[par]), ptr(self.g_peer_ready), ptr(self.g_signal),
              ptr(self.g_ready), self.rank, self.world, self.rows, self.width, self.g_epoch, ptr(b), ptr(out),
              ptr(bias), ptr(residual), int(n), b.stride(0), out.stride(0), ldr, int(a_major), int(b_major),
              dtype_code(self.dtype), 1 if out_dtype == torch.float32 else 0,
