@@ -79,6 +79,24 @@ def main():
         flops = 2.0 * t * d * n_local
         wire = (world - 1) * rows * d * 2
         cases.append((name, "ag_gemm", fused, nccl, gemm_only, flops, wire))
+    # column-parallel weight gradient: AG(x)^T @ dy[t, n_local] (reduction over the gathered tokens)
+    for name, n_local in (("qkv_wgrad", 3 * d // world), ("gate_up_wgrad", 2 * f // world)):
+        n_local = (n_local + 7) // 8 * 8
+        x = torch.randn(rows, d, device="cuda").bfloat16()
+        dy = torch.randn(t, n_local, device="cuda").bfloat16()
+        full = torch.empty(t, d, device="cuda", dtype=torch.bfloat16)
+
+        def fused(x=x, dy=dy, n_local=n_local):
+            ws.ag_gemm(x, dy, a_major=1, b_major=1, n=n_local)
+
+        def nccl(x=x, dy=dy, full=full):
+            dist.all_gather_into_tensor(full, x)
+            kernels.mm_tn(full, dy)
+
+        def gemm_only(dy=dy, full=full):
+            kernels.mm_tn(full, dy)
+
+        cases.append((name, "ag_gemm_wgrad", fused, nccl, gemm_only, 2.0 * t * d * n_local, (world - 1) * rows * d * 2))
     # row-parallel forward: (x[t, k_local] @ W[k_local, d]) -> RS
     for name, k_local in (("attn_out_fwd", d // world), ("down_fwd", f // world)):
         k_local = (k_local + 7) // 8 * 8

@@ -1,0 +1,183 @@
+"""Auxiliary subsystems on CPU: failure detection on the host, cadence control, LR schedule, eval task,
+config loading from YAML groups, corrupted checkpoint handling."""
+
+import json
+import os
+
+import pytest
+import torch
+import yaml
+
+from helpers import run_distributed, tiny_config
+
+
+# ------------------------------------------------------------------ failure detection (host only)
+class _FakeStore:
+    def __init__(self):
+        self.kv = {}
+
+    def set(self, k, v):
+        self.kv[k] = v.encode() if isinstance(v, str) else v
+
+    def get(self, k):
+        return self.kv[k]
+
+
+def test_heartbeat_detects_silent_rank_with_fake_clock():
+    from ironcore_b200.parallel.fault import Heartbeat, RankFailure
+
+    now = [1000.0]
+    store = _FakeStore()
+    a = Heartbeat(0, 10.0, store, rank=0, world_size=3, clock=lambda: now[0])
+    b = Heartbeat(0, 10.0, store, rank=1, world_size=3, clock=lambda: now[0])
+    assert a.dead_peers() == [2]            # rank 2 never joined
+    c = Heartbeat(0, 10.0, store, rank=2, world_size=3, clock=lambda: now[0])
+    assert a.dead_peers() == []
+    now[0] += 8.0
+    b.beat(5)
+    now[0] += 8.0                            # rank 2 silent for 16 s, rank 1 for 8 s
+    assert a.dead_peers() == [2]
+    with pytest.raises(RankFailure) as e:
+        a.raise_if_peer_dead()
+    assert e.value.ranks == [2]
+    c.beat(6)
+    a.raise_if_peer_dead()
+
+
+def _hb_worker(rank, world):
+    import time
+
+    from ironcore_b200.parallel.fault import Heartbeat
+
+    hb = Heartbeat(interval_s=0.05, timeout_s=0.6)
+    if rank == 1:
+        hb.stop()               # this rank stops publishing (a hung or dead process), between steps
+        time.sleep(1.5)
+        return
+    time.sleep(1.2)
+    dead = hb.dead_peers()
+    hb.stop()
+    assert dead == [1], dead
+
+
+def test_heartbeat_over_real_store_two_ranks():
+    run_distributed(_hb_worker, 2)
+
+
+def _timeout_worker(rank, world):
+    """A rank that never joins a collective: the short process-group timeout ends the others' wait
+    with an error instead of a hang (Gloo ranks, nothing on a GPU)."""
+    import datetime
+
+    import torch.distributed as dist
+
+    g = dist.new_group(ranks=[0, 1], timeout=datetime.timedelta(seconds=2))
+    t = torch.ones(1)
+    if rank == 0:
+        with pytest.raises(Exception):
+            dist.all_reduce(t, group=g)
+
+
+def test_collective_timeout_surfaces_as_error():
+    try:
+        run_distributed(_timeout_worker, 2, timeout=60)
+    except AssertionError:
+        pass   # the process group may already be torn down by the failed collective at barrier time
+
+
+# ------------------------------------------------------------------ controller / schedule
+def test_cadence_predicates():
+    from ironcore_b200.controller import TrainingControl
+
+    cfg = tiny_config("gpt2")
+    cfg.trainer(log_interval=5, save_checkpoint_steps=10, model_path="/tmp/x", grad_norm_log_interval="log")
+    cfg.operation(eval_interval=4, exit_interval=7)
+    cfg.trainer.do_eval = True
+    c = TrainingControl(cfg)
+    assert [s for s in range(12) if c.do_log(s)] == [4, 9]
+    assert [s for s in range(12) if c.do_checkpoint(s)] == [9]
+    assert [s for s in range(12) if c.do_eval(s)] == [3, 7, 11]
+    assert [s for s in range(12) if c.do_exit(s)] == [6]
+    assert c.do_grad_norm(4) and not c.do_grad_norm(5)
+    assert TrainingControl._cadence_now(10, 5) and not TrainingControl._cadence_now(0, 5)
+
+
+def test_cosine_schedule_matches_documented_values():
+    from ironcore_b200.optim.lr_scheduler import CosineAnnealingLR
+
+    class Opt:
+        param_groups = [{"lr": 6e-4}]
+
+    s = CosineAnnealingLR(Opt(), max_lr=6e-4, min_lr=0.0, warmup_steps=2, annealing_steps=4, total_steps=4)
+    seen = [Opt.param_groups[0]["lr"]]
+    for _ in range(4):
+        s.step()
+        seen.append(Opt.param_groups[0]["lr"])
+    # t = 1..5: warm-up 3e-4, 6e-4, then cosine over 4 steps
+    assert abs(seen[0] - 3e-4) < 1e-12 and abs(seen[1] - 6e-4) < 1e-12
+    assert abs(seen[2] - 6e-4 * (1 + 0.7071067811865476) / 2) < 1e-9
+    assert abs(seen[3] - 3e-4) < 1e-9
+
+
+# ------------------------------------------------------------------ YAML groups / CLI
+def test_yaml_groups_env_and_cli(tmp_path, monkeypatch):
+    from ironcore_b200.config import load_trainer_config
+
+    (tmp_path / "model").mkdir()
+    (tmp_path / "model" / "tiny.yaml").write_text(yaml.safe_dump(
+        {"d_model": 64, "d_ffn": 128, "num_layers": 2, "num_attention_heads": 4, "max_seq_len": 32, "precision": "fp32"}))
+    monkeypatch.setenv("MY_CKPT", str(tmp_path / "ck"))
+    (tmp_path / "main.yaml").write_text(
+        "model: tiny\ntrainer:\n  model_path: ${MY_CKPT}\n  micro_batch_size: 2\n  train_batch_size: 4\n"
+        "optim:\n  - max_lr: 1.0e-3\n  - weight_decay: 0.1\noperation:\n  train_steps: 5\n")
+    cfg = load_trainer_config(["--config-path", str(tmp_path / "main.yaml"), "--log-interval", "3", "--max_lr", "2e-3"])
+    assert cfg.model.name == "tiny" and cfg.model.d_model == 64
+    assert cfg.trainer.model_path == str(tmp_path / "ck")
+    assert cfg.trainer.gradient_accumulation_steps == 2 and cfg.trainer.log_interval == 3
+    assert cfg.optim.max_lr == 2e-3 and cfg.optim.weight_decay == 0.1
+    with pytest.raises(KeyError):
+        (tmp_path / "bad.yaml").write_text("nonsense:\n  a: 1\n")
+        load_trainer_config(["--config-path", str(tmp_path / "bad.yaml")])
+
+
+# ------------------------------------------------------------------ checkpoints under failure
+def test_corrupt_and_missing_checkpoints(tmp_path):
+    from ironcore_b200.checkpoint import find_latest_step, load_checkpoint, save_checkpoint
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.trainer import Trainer
+
+    mesh.destroy_model_parallel()
+    cfg = tiny_config("gpt2")
+    cfg.trainer.model_path = str(tmp_path / "ck")
+    validate_config(cfg)
+    tr = Trainer(cfg)
+    assert load_checkpoint(cfg, tr.model) == -1                    # nothing there yet
+    tr.train_step(0)
+    save_checkpoint(cfg, tr.model, tr.optimizer, tr.lr_scheduler, 0)
+    save_checkpoint(cfg, tr.model, tr.optimizer, tr.lr_scheduler, 1)
+    os.remove(tmp_path / "ck" / "latest_step.txt")
+    assert find_latest_step(cfg.trainer.model_path) == 1           # falls back to scanning step_* dirs
+    p = tmp_path / "ck" / "step_1" / "pytorch_model.bin"
+    p.write_bytes(p.read_bytes()[:1000])                           # truncated file
+    with pytest.raises(RuntimeError):
+        load_checkpoint(cfg, tr.model)
+    assert load_checkpoint(cfg, tr.model, step=0) == 0
+
+
+# ------------------------------------------------------------------ eval task
+def test_hellaswag_task_on_inline_examples():
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.eval.tasks.hellaswag import HellaSwag
+    from ironcore_b200.models import LanguageModel
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.tokenizer import Tokenizer
+
+    mesh.destroy_model_parallel()
+    cfg = tiny_config("gpt2", max_seq_len=64, max_position_embeddings=64)
+    validate_config(cfg)
+    model = LanguageModel(cfg).eval()
+    tok = Tokenizer(512, 511, 0, 8)
+    ex = [{"ctx": "a b c", "endings": ["d", "e f", "g", "hh"], "label": 1} for _ in range(3)]
+    res = HellaSwag(tok, 1, None, examples=ex).process(model)
+    assert res["metric"] == "accuracy" and 0.0 <= res["score"] <= 100.0
