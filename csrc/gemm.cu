@@ -428,23 +428,36 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const long long block_bytes = 128LL * args.ag_row_bytes;
     const int chunks_per_shard = (int)(shard_bytes / kAgChunkBytes);
     const int total_chunks = (args.ag_world - 1) * chunks_per_shard;
-    for (int c = cw; c < total_chunks; c += n_cw) {
-      const int step = c / chunks_per_shard + 1;
-      const int within = c - (step - 1) * chunks_per_shard;
-      const int q = (args.ag_rank + step) % args.ag_world;
-      const long long off = (long long)args.ag_rank * shard_bytes + (long long)within * kAgChunkBytes;
-      const uint4* src = reinterpret_cast<const uint4*>(args.ag_local + off);
-      uint4* dst = reinterpret_cast<uint4*>(args.ag_peers[q] + off);
-      uint4 v[16];
+    // A system-scope fence waits for the acknowledgement of every remote store, i.e. a full NVLink
+    // round trip: issue it once per batch of chunks (up to kAgBatch), then publish the batch.
+    constexpr int kAgBatch = 16;
+    int c = cw;
+    while (c < total_chunks) {
+      int done_q[kAgBatch], done_rb[kAgBatch];
+      int n_done = 0;
+#pragma unroll 1
+      for (; c < total_chunks && n_done < kAgBatch; c += n_cw) {
+        const int step = c / chunks_per_shard + 1;
+        const int within = c - (step - 1) * chunks_per_shard;
+        const int q = (args.ag_rank + step) % args.ag_world;
+        const long long off = (long long)args.ag_rank * shard_bytes + (long long)within * kAgChunkBytes;
+        const uint4* src = reinterpret_cast<const uint4*>(args.ag_local + off);
+        uint4* dst = reinterpret_cast<uint4*>(args.ag_peers[q] + off);
+        uint4 v[16];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) v[j] = src[lane + j * 32];
+        for (int j = 0; j < 16; ++j) v[j] = src[lane + j * 32];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) dst[lane + j * 32] = v[j];
+        for (int j = 0; j < 16; ++j) dst[lane + j * 32] = v[j];
+        done_q[n_done] = q;
+        done_rb[n_done] = (int)(off / block_bytes);
+        ++n_done;
+      }
       __syncwarp();
       if (lane == 0) {
         __threadfence_system();
-        red_release_sys_add(args.ag_peer_ready[q] + (int)(off / block_bytes), 1);
+        for (int i = 0; i < n_done; ++i) red_release_sys_add(args.ag_peer_ready[done_q[i]] + done_rb[i], 1);
       }
+      __syncwarp();
     }
   }
 

@@ -75,6 +75,9 @@ class FusedTP:
         self.r_peer_flags = self.rbuf.peer_table(self._r_flags_off)
         self.r_flags = self.rbuf.view(self._r_flags_off, (n_flags,), torch.int32)
         self.r_epoch = 0
+        # True: forward keeps the gathered activations (32 MiB at 4096 x 4096) for the weight gradient;
+        # False: backward re-gathers inside the wgrad kernel (less memory, exposed transfer).
+        self.save_gathered = True
 
     # ------------------------------------------------------------------ raw kernels
     def ag_gemm(self, x_shard: torch.Tensor, b: torch.Tensor, *, a_major: int, b_major: int, n: int,
@@ -144,7 +147,11 @@ class _AllGatherLinear(torch.autograd.Function):
     def forward(ctx, x_shard, weight, bias, ws: FusedTP):
         x2 = x_shard.reshape(-1, x_shard.shape[-1]).contiguous()
         y = ws.ag_gemm(x2, weight, a_major=0, b_major=1, n=weight.shape[1], bias=bias)
-        ctx.save_for_backward(x2, weight)
+        # Keep the gathered activations for the weight gradient (the workspace buffer is reused two
+        # calls later). A re-gather inside the wgrad kernel cannot hide its transfer: the reduction
+        # runs over the gathered rows, so every output tile needs all of them at once.
+        x_full = ws.last_gathered.clone() if ws.save_gathered else x2
+        ctx.save_for_backward(x_full, weight)
         ctx.ws = ws
         ctx.has_bias = bias is not None
         return y
@@ -160,6 +167,10 @@ class _AllGatherLinear(torch.autograd.Function):
             n = weight.shape[1]
 
             def compute(acc):
+                if ws.save_gathered:
+                    if acc is not None:
+                        return kernels.mm_tn(x2, dy, out=acc, residual=acc, out_dtype=acc.dtype)
+                    return kernels.mm_tn(x2, dy)
                 if acc is not None:
                     return ws.ag_gemm(x2, dy, a_major=1, b_major=1, n=n, out=acc, residual=acc, out_dtype=acc.dtype)
                 return ws.ag_gemm(x2, dy, a_major=1, b_major=1, n=n)
