@@ -206,14 +206,30 @@ norm_bwd_kernel(const uint16_t* __restrict__ dy, const uint16_t* __restrict__ x,
   }
 }
 
-// out[d] (+)= sum_p part[p, d]; writes 16-bit or fp32 output.
+// out[d] (+)= sum_p part[p, d]; writes 16-bit or fp32 output. blockDim = (32, 8): 32 columns per CTA,
+// the partial rows are split over 8 thread rows (4 loads in flight each) and folded through smem.
 template <bool BF16>
 __global__ void reduce_partials_kernel(const float* __restrict__ part, int P, int D, void* __restrict__ out,
                                        int out_f32, int accumulate) {
-  const int d = blockIdx.x * blockDim.x + threadIdx.x;
-  if (d >= D) return;
+  __shared__ float sh[8][33];
+  const int d = blockIdx.x * 32 + threadIdx.x;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (d < D) {
+    int p = threadIdx.y;
+    for (; p + 24 < P; p += 32) {
+      s0 += part[(size_t)p * D + d];
+      s1 += part[(size_t)(p + 8) * D + d];
+      s2 += part[(size_t)(p + 16) * D + d];
+      s3 += part[(size_t)(p + 24) * D + d];
+    }
+    for (; p < P; p += 8) s0 += part[(size_t)p * D + d];
+  }
+  sh[threadIdx.y][threadIdx.x] = (s0 + s1) + (s2 + s3);
+  __syncthreads();
+  if (threadIdx.y != 0 || d >= D) return;
   float s = 0.f;
-  for (int p = 0; p < P; ++p) s += part[(size_t)p * D + d];
+#pragma unroll
+  for (int y = 0; y < 8; ++y) s += sh[y][threadIdx.x];
   if (out_f32) {
     float* o = reinterpret_cast<float*>(out);
     o[d] = accumulate ? o[d] + s : s;
@@ -321,7 +337,7 @@ ICB_API int icb_norm_bwd(const void* dy, const void* x, const void* w, const flo
     rc = rms ? norm_bwd_dispatch<false, true>(vpt, grid, st, DY, X, W, mean, rstd, DR, DX, dwp, dbp, M, D, w_offset)
              : norm_bwd_dispatch<false, false>(vpt, grid, st, DY, X, W, mean, rstd, DR, DX, dwp, dbp, M, D, w_offset);
   if (rc) return rc;
-  const int th = 256, bl = (D + th - 1) / th;
+  const dim3 th(32, 8); const int bl = (D + 31) / 32;
   if (dtype == kBF16) {
     reduce_partials_kernel<true><<<bl, th, 0, st>>>(dwp, grid, D, dw, grad_f32, accumulate);
     if (db != nullptr) reduce_partials_kernel<true><<<bl, th, 0, st>>>(dbp, grid, D, db, grad_f32, accumulate);
@@ -397,7 +413,7 @@ ICB_API int icb_norm_bwd_noalloc(const void* dy, const void* x, const void* w, c
     rc = rms ? norm_bwd_dispatch<false, true>(vpt, grid, st, DY, X, W, mean, rstd, DR, DX, dwp, dbp, M, D, w_offset)
              : norm_bwd_dispatch<false, false>(vpt, grid, st, DY, X, W, mean, rstd, DR, DX, dwp, dbp, M, D, w_offset);
   if (rc) return rc;
-  const int th = 256, bl = (D + th - 1) / th;
+  const dim3 th(32, 8); const int bl = (D + 31) / 32;
   if (dtype == kBF16) {
     reduce_partials_kernel<true><<<bl, th, 0, st>>>(dwp, grid, D, dw, grad_f32, accumulate);
     if (db != nullptr) reduce_partials_kernel<true><<<bl, th, 0, st>>>(dbp, grid, D, db, grad_f32, accumulate);

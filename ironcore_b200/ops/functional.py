@@ -185,12 +185,20 @@ class _Embedding(torch.autograd.Function):
         ctx.rows = weight.shape[0]
         ctx.w_dtype = weight.dtype
         ctx.pos_rows = pos_table.shape[0] if pos_table is not None else 0
+        ctx.weight_ref = weight
         return out
 
     @staticmethod
     def backward(ctx, dy):
         ids, pos_saved = ctx.saved_tensors
-        dw = kernels.embedding_bwd(ids, dy, ctx.rows, row_start=ctx.vocab_start).to(ctx.w_dtype)
+        main_grad = getattr(ctx.weight_ref, "main_grad", None)
+        if main_grad is not None and main_grad.dtype == torch.float32:
+            # scatter-add straight into the flat fp32 gradient buffer: no [V, d] temporary, no conversion
+            kernels.embedding_bwd(ids, dy, ctx.rows, row_start=ctx.vocab_start, out=main_grad)
+            ctx.weight_ref.grad_ready = True
+            dw = None
+        else:
+            dw = kernels.embedding_bwd(ids, dy, ctx.rows, row_start=ctx.vocab_start).to(ctx.w_dtype)
         dpos = None
         if ctx.pos_rows:
             if ctx.has_pos_ids:

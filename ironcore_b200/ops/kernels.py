@@ -231,13 +231,15 @@ def embedding_fwd(ids: torch.Tensor, weight: torch.Tensor, *, vocab_start: int =
     return out.view(*ids.shape, d)
 
 
-def embedding_bwd(rows: torch.Tensor, dy: torch.Tensor, num_rows: int, *, row_start: int = 0) -> torch.Tensor:
+def embedding_bwd(rows: torch.Tensor, dy: torch.Tensor, num_rows: int, *, row_start: int = 0,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """dW[rows[t] - row_start] += dy[t] (fp32 atomics). ``out`` (fp32 [num_rows, d]) is accumulated into."""
     flat = rows.reshape(-1)
     if flat.dtype != torch.int64:
         flat = flat.long()
     d = dy.shape[-1]
     dy2 = dy.reshape(-1, d).contiguous()
-    dw = torch.zeros((num_rows, d), dtype=torch.float32, device=dy.device)
+    dw = out if out is not None else torch.zeros((num_rows, d), dtype=torch.float32, device=dy.device)
     call("icb_embedding_bwd", ptr(flat), ptr(dy2), ptr(dw), flat.numel(), d, int(row_start), num_rows,
          dtype_code(dy.dtype), stream_ptr())
     return dw
