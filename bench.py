@@ -102,7 +102,8 @@ def build_config(world: int, steps: int):
     c.model(**MODEL)
     c.data(task_type="synthetic", vocab_size=32000, synthetic_seed=1234)
     c.trainer(micro_batch_size=1, train_batch_size=GLOBAL_BATCH, gradient_accumulation_steps=None,
-              tensor_model_parallel_size=world, log_interval=10 ** 9, model_path="", use_flash_attn=True)
+              tensor_model_parallel_size=world, log_interval=10 ** 9, model_path="", use_flash_attn=True,
+              cuda_graph=os.environ.get("ICB_CUDA_GRAPH", "1" if world > 1 else "0") != "0")
     c.operation(train_steps=10 ** 6, no_save=True)
     c.optim(optimizer="adam", max_lr=3e-4, min_lr=3e-5, adam_beta1=0.9, adam_beta2=0.95, weight_decay=0.1,
             clip_grad=1.0, warmup_steps=0)
@@ -217,6 +218,7 @@ def run_ours(args):
                        "tp_comm": ("fused in-kernel P2P (all-gather->GEMM, GEMM->reduce-scatter)"
                                    if (world > 1 and cfg.parallel.fused_comm) else ("nccl" if world > 1 else "none")),
                        "optimizer": "adam(0.9,0.95) lr 3e-4, clip 1.0, fp32 grad accumulation",
+                       "cuda_graph": bool(cfg.trainer.cuda_graph),
                        "l2": "no flush needed: every pass streams 13.5 GB of weights, far larger than the 126 MB L2"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes,

@@ -33,7 +33,7 @@ struct RsArgs {
   const void* bias;                // [N] or null
   const void* residual;            // [rows_per_rank, ldr] or null
   long long ldr;
-  int epoch;
+  const int* epoch_ptr;            // device word: calls completed so far on this workspace
   int in_fmt;
   int* status;
 };
@@ -230,7 +230,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int gw = blockIdx.x * nwarps + warp;
     const int n_gw = gridDim.x * nwarps;
     const int units = mtiles_per_shard * args.num_n_tiles * 8;   // 16 rows x 256 columns each
-    const int target = args.world * args.epoch;
+    const int target = args.world * (*args.epoch_ptr + 1);
     for (int u = gw; u < units; u += n_gw) {
       const int rg = u & 7;
       const int tn = u >> 3;
@@ -350,12 +350,12 @@ using namespace icb;
 //   A: [M, lda] row-major (K contiguous). b_major 0: B [N, ldb] (K contiguous); 1: B [K, ldb] (N contiguous).
 //   peer_recv / peer_flags: device arrays [world] of peer pointers to every rank's receive buffer
 //   ([world][rows_per_rank][N] 16-bit) and arrival counters ([rows_per_rank/128][ceil(N/256)] int).
-//   N must be a multiple of 8; rows_per_rank a multiple of 128; epoch = 1, 2, ... per call on this
-//   pair of buffers (same on every rank).
+//   N must be a multiple of 8; rows_per_rank a multiple of 128; epoch_ptr = device int with the number of calls already
+//   made on this pair of buffers (same on every rank; the caller increments it after the call).
 ICB_API int icb_gemm_rs(const void* A, const void* B, void* out, const void* bias, const void* residual, int M, int N,
                         int K, long long lda, long long ldb, long long ldo, long long ldr, int b_major, int in_dtype,
                         const void* const* peer_recv, int* const* peer_flags, const void* recv, const int* flags,
-                        int rank, int world, int epoch, int* status, void* stream_) {
+                        int rank, int world, const int* epoch_ptr, int* status, void* stream_) {
   if (world < 1 || M % world != 0) return -2;
   const int rows_per_rank = M / world;
   if (rows_per_rank % 128 != 0 || N % 8 != 0) return -7;
@@ -393,7 +393,7 @@ ICB_API int icb_gemm_rs(const void* A, const void* B, void* out, const void* bia
   a.flags = flags;
   a.out = out; a.ldo = ldo;
   a.bias = bias; a.residual = residual; a.ldr = ldr;
-  a.epoch = epoch;
+  a.epoch_ptr = epoch_ptr;
   a.in_fmt = (in_dtype == kBF16) ? 1 : 0;
   a.status = status;
   int grid = num_sms();

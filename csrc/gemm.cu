@@ -50,7 +50,7 @@ struct GemmArgs {
   const int* ag_signal;             // this rank's shard_ready[world] (written by the peers)
   int* ag_ready;                    // this rank's per-128-row-block arrival counters (bumped by the peers)
   int* const* ag_peer_ready;        // device array [world]: every rank's arrival counters
-  int ag_epoch;                     // call sequence number (flags are cumulative)
+  const int* ag_epoch_ptr;          // device word: calls completed so far on this workspace (this call = +1)
   int ag_chunks_per_block;          // 8 KiB chunks in one 128-row block
 };
 
@@ -108,6 +108,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const uint32_t tmem_base = *tmem_slot;
 
   const int ag_mtiles_per_shard = AG ? max(args.ag_rows_per_rank >> 7, 1) : 1;
+  // Flags are cumulative; the sequence number lives on the device so that a captured CUDA graph
+  // replays with the right value (the host bumps the word after every call, in stream order).
+  const int ag_epoch = AG ? (*args.ag_epoch_ptr + 1) : 0;
 
   const int tiles_per_group = args.num_m_tiles * args.num_n_tiles;
   const int total_tiles = (args.group_mode == 2 ? args.num_groups : 1) * tiles_per_group;
@@ -121,7 +124,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       unsigned long long ag_seen = 0ull;
       auto ag_ensure_ready = [&](int rb) {
         if (rb < 64 && ((ag_seen >> rb) & 1ull)) return;
-        wait_flag_sys(args.ag_ready + rb, args.ag_epoch * args.ag_chunks_per_block, args.status, kTimeoutPeerFlag);
+        wait_flag_sys(args.ag_ready + rb, ag_epoch * args.ag_chunks_per_block, args.status, kTimeoutPeerFlag);
         fence_proxy_async_all();
         if (rb < 64) ag_seen |= (1ull << rb);
       };
@@ -561,7 +564,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, co
   else {
     args.ag_rank = 0; args.ag_world = 1; args.ag_rows_per_rank = 0; args.ag_row_bytes = 0;
     args.ag_local = nullptr; args.ag_peers = nullptr; args.ag_peer_signal = nullptr; args.ag_signal = nullptr;
-    args.ag_ready = nullptr; args.ag_epoch = 0; args.ag_chunks_per_block = 1; args.ag_peer_ready = nullptr;
+    args.ag_ready = nullptr; args.ag_epoch_ptr = nullptr; args.ag_chunks_per_block = 1; args.ag_peer_ready = nullptr;
   }
   args.M = M; args.N = N; args.K = K;
   args.num_m_tiles = (M + kBM - 1) / kBM;
@@ -608,13 +611,14 @@ ICB_API int icb_gemm(const void* A, const void* B, void* C, const void* bias, co
 //   peers    : device array [world] of every rank's gathered buffer (symmetric-memory peer pointers).
 //   peer_ready : device array [world] of every rank's arrival-counter array; `signal` is unused (reserved).
 //   ready    : this rank's int array [world * rows_per_rank / 128] of cumulative arrival counters.
-//   epoch    : 1, 2, 3, ... per call on this workspace (same on every rank).
+//   epoch_ptr: device int holding the number of calls already made on this workspace (same on every
+//              rank); the caller increments it in stream order after this call.
 //   a_major 0: C[M = world*rows_per_rank, N] = gathered[M, K = width] * B        (forward / dgrad of a row-parallel layer)
 //   a_major 1: C[M = width, N] = gathered^T * B[K = world*rows_per_rank, N]      (wgrad: reduction over gathered rows)
 // The local shard is pushed to every peer with plain P2P stores by copy warps inside the same kernel;
 // the tensor core starts with the local shard and follows the other shards in arrival order.
 ICB_API int icb_ag_gemm(void* gathered, const void* const* peers, int* const* peer_ready, const int* signal,
-                        int* ready, int rank, int world, int rows_per_rank, int width, int epoch, const void* B,
+                        int* ready, int rank, int world, int rows_per_rank, int width, const int* epoch_ptr, const void* B,
                         void* C, const void* bias, const void* residual, int N, long long ldb, long long ldc,
                         long long ldr, int a_major, int b_major, int in_dtype, int out_f32, int* status,
                         void* stream_) {
@@ -628,7 +632,7 @@ ICB_API int icb_ag_gemm(void* gathered, const void* const* peers, int* const* pe
   ag.ag_peer_ready = peer_ready;
   ag.ag_signal = signal;
   ag.ag_ready = ready;
-  ag.ag_epoch = epoch;
+  ag.ag_epoch_ptr = epoch_ptr;
   ag.ag_chunks_per_block = (int)(128LL * width * 2 / kAgChunkBytes);
   const int rows = world * rows_per_rank;
   const int M = a_major == 0 ? rows : width;

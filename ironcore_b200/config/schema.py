@@ -238,6 +238,7 @@ class TrainerConfig(BaseConfig):
     vocab_padding_unit: int = opt(128, "vocab padding unit")
     special_tokens_config_path: Optional[str] = opt(None, "special token file")
     use_flash_attn: bool = opt(True, "fused attention kernel")
+    cuda_graph: bool = opt(False, "capture one micro-batch forward+backward in a CUDA graph and replay it")
     compile_model: bool = opt(False, "accepted for compatibility; the hot path is hand-written kernels")
     compile_mode: Optional[Literal["default", "reduce-overhead", "max-autotune"]] = opt("default", "ignored")
     compile_backend: Literal["inductor", "cudagraphs", "eager"] = opt("inductor", "ignored")

@@ -100,6 +100,12 @@ def launches() -> int:
     return _LAUNCHES
 
 
+def add_launches(n: int) -> None:
+    """Account for kernels launched by replaying a captured CUDA graph."""
+    global _LAUNCHES
+    _LAUNCHES += int(n)
+
+
 def reset_launches() -> None:
     global _LAUNCHES
     _LAUNCHES = 0

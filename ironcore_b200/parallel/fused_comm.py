@@ -17,8 +17,10 @@ Forward and backward of the column- / row-parallel linears map onto these two ke
   row dgrad   : AG(dy) -> GEMM                     (icb_ag_gemm, a_major 0)
   row wgrad   : x^T GEMM gathered(dy)              (plain GEMM on the buffer the dgrad call filled)
 
-Every rank must issue the same sequence of calls (SPMD); the call counter of each workspace
-is the epoch the kernels' cumulative flags are compared against. The ``torch.distributed``
+Every rank must issue the same sequence of calls (SPMD). Each workspace counts its calls in a
+device word that the kernels read as the epoch of their cumulative flags, so a captured CUDA
+graph replays correctly; the host-side counter only selects the buffer parity, which is why a
+captured region must contain an even number of calls per workspace (checked by the trainer). The ``torch.distributed``
 path in :mod:`ironcore_b200.parallel.tensor_parallel` is the fallback and the oracle.
 """
 
@@ -34,8 +36,8 @@ from ..ops.native import call, dtype_code, ptr, stream_ptr
 from .symmetric import SymmetricBuffer, symmetric_memory_available
 
 P, I, L = native.P, native.I, native.L
-native.register("icb_ag_gemm", [P, P, P, P, P, I, I, I, I, I, P, P, P, P, I, L, L, L, I, I, I, I, P, P])
-native.register("icb_gemm_rs", [P, P, P, P, P, I, I, I, L, L, L, L, I, I, P, P, P, P, I, I, I, P, P])
+native.register("icb_ag_gemm", [P, P, P, P, P, I, I, I, I, P, P, P, P, P, I, L, L, L, I, I, I, I, P, P])
+native.register("icb_gemm_rs", [P, P, P, P, P, I, I, I, L, L, L, L, I, I, P, P, P, P, I, I, P, P, P])
 
 
 class FusedTP:
@@ -63,6 +65,7 @@ class FusedTP:
         self.g_ready = self.gbuf.view(self._g_ready_off, (tokens // 128,), torch.int32)
         self.g_signal = self.gbuf.view(self._g_signal_off, (self.world,), torch.int32)
         self.g_epoch = 0
+        self.g_epoch_dev = torch.zeros(1, dtype=torch.int32, device=self.gbuf.local.device)
         self.last_gathered: Optional[torch.Tensor] = None
         # ---- scatter workspace ----
         r_data = tokens * width * es
@@ -75,6 +78,7 @@ class FusedTP:
         self.r_peer_flags = self.rbuf.peer_table(self._r_flags_off)
         self.r_flags = self.rbuf.view(self._r_flags_off, (n_flags,), torch.int32)
         self.r_epoch = 0
+        self.r_epoch_dev = torch.zeros(1, dtype=torch.int32, device=self.rbuf.local.device)
         # True: forward keeps the gathered activations (32 MiB at 4096 x 4096) for the weight gradient;
         # False: backward re-gathers inside the wgrad kernel (less memory, exposed transfer).
         self.save_gathered = True
@@ -96,10 +100,11 @@ class FusedTP:
             out = torch.empty((m, n), dtype=out_dtype, device=x_shard.device)
         ldr = residual.stride(0) if residual is not None else 0
         call("icb_ag_gemm", ptr(gathered), ptr(self.g_peers[par]), ptr(self.g_peer_ready), ptr(self.g_signal),
-             ptr(self.g_ready), self.rank, self.world, self.rows, self.width, self.g_epoch, ptr(b), ptr(out),
+             ptr(self.g_ready), self.rank, self.world, self.rows, self.width, ptr(self.g_epoch_dev), ptr(b), ptr(out),
              ptr(bias), ptr(residual), int(n), b.stride(0), out.stride(0), ldr, int(a_major), int(b_major),
              dtype_code(self.dtype), 1 if out_dtype == torch.float32 else 0,
              ptr(native.status_tensor(x_shard.device)), stream_ptr())
+        self.g_epoch_dev.add_(1)
         self.last_gathered = gathered
         return out
 
@@ -116,8 +121,9 @@ class FusedTP:
         recv_ptr = self.rbuf.local.data_ptr() + self._r_off[par]
         call("icb_gemm_rs", ptr(a), ptr(b), ptr(out), ptr(bias), ptr(residual), self.tokens, n, k, a.stride(0),
              b.stride(0), out.stride(0), ldr, int(b_major), dtype_code(self.dtype), ptr(self.r_peers[par]),
-             ptr(self.r_peer_flags), recv_ptr, ptr(self.r_flags), self.rank, self.world, self.r_epoch,
+             ptr(self.r_peer_flags), recv_ptr, ptr(self.r_flags), self.rank, self.world, ptr(self.r_epoch_dev),
              ptr(native.status_tensor(a.device)), stream_ptr())
+        self.r_epoch_dev.add_(1)
         return out
 
     # ------------------------------------------------------------------ autograd entry points
@@ -235,7 +241,10 @@ def attach_fused_tp(model, config) -> Optional[FusedTP]:
     if dtype not in (torch.bfloat16, torch.float16):
         return None
     ws = FusedTP(tokens, width, group, dtype)
+    head = getattr(model, "output_layer", None)
     for mod in model.modules():
+        if mod is head:
+            continue   # keeps the number of fused calls per micro-batch even (needed for CUDA-graph replay)
         if isinstance(mod, ColumnParallelLinear) and mod.sequence_parallel and mod.in_features == width:
             mod.fused = ws
         elif isinstance(mod, RowParallelLinear) and mod.sequence_parallel and mod.out_features == width:

@@ -97,6 +97,18 @@ class Trainer:
         self._step_timer = DeviceTimer() if self.device.type == "cuda" else None
         self._memory_reported = False
         self.last_step = -1
+        # CUDA-graph replay of the micro-batch (forward + backward): removes the host launch cost of
+        # the ~2000 kernels of a micro-batch, which dominates once tensor parallelism shrinks them.
+        self._graph_enabled = bool(config.trainer.cuda_graph) and self.device.type == "cuda" \
+            and self.forward_step_func is default_forward_step and not config.parallel.use_fsdp
+        if self._graph_enabled and (config.model.reset_attention_mask or config.model.reset_position_ids) \
+                and config.model.eod_token_id is not None:
+            self.logger.warning("trainer.cuda_graph is off: document-boundary resets need a host-side scan per batch")
+            self._graph_enabled = False
+        self._graph = None
+        self._graph_stream = None
+        self._graph_eager_done = 0
+        self._graph_launches = 0
 
     # ------------------------------------------------------------------ lifecycle
     def __enter__(self):
@@ -200,10 +212,24 @@ class Trainer:
         if self._step_timer is not None:
             self._step_timer.start()
         total = None
-        for _ in range(accum):
-            loss = self.forward_step_func(self.model, self.data_iterator["train"])
-            (loss / accum).backward()
-            total = loss.detach() if total is None else total + loss.detach()
+        if self._graph_enabled:
+            # Everything of the micro-batch loop (eager warm-up, capture, replays) runs on one side
+            # stream: gradient-accumulation nodes remember the stream they were created on, and a node
+            # created on the legacy default stream cannot take part in a capture.
+            if self._graph_stream is None:
+                self._graph_stream = torch.cuda.Stream()
+            main = torch.cuda.current_stream()
+            self._graph_stream.wait_stream(main)
+            with torch.cuda.stream(self._graph_stream):
+                for _ in range(accum):
+                    loss = self._graphed_micro_batch(accum)
+                    total = loss.detach().clone() if total is None else total + loss.detach()
+            main.wait_stream(self._graph_stream)
+        else:
+            for _ in range(accum):
+                loss = self.forward_step_func(self.model, self.data_iterator["train"])
+                (loss / accum).backward()
+                total = loss.detach() if total is None else total + loss.detach()
         grad_norm = self.optimizer.step()
         self.optimizer.zero_grad()
         self.lr_scheduler.step()
@@ -214,6 +240,48 @@ class Trainer:
             self._step_timer.stop()
         self.timer.stop("iter")
         return total / accum, grad_norm, param_norm
+
+    def _graphed_micro_batch(self, accum: int):
+        """Two eager micro-batches (allocator / lazy-init warm-up), then capture once and replay."""
+        from .ops import native
+
+        batch = next(self.data_iterator["train"])
+        extra = [k for k in batch if k not in ("input_ids", "labels") and batch[k] is not None]
+        if extra:
+            raise RuntimeError(f"trainer.cuda_graph supports (input_ids, labels) batches only, got extra {extra}")
+        if self._graph is None and self._graph_eager_done < 2:
+            self._graph_eager_done += 1
+            loss = self.model(batch["input_ids"], batch["labels"])
+            (loss / accum).backward()
+            return loss
+        if self._graph is None:
+            self._static_ids = batch["input_ids"].to(self.device).clone()
+            self._static_labels = batch["labels"].to(self.device).clone()
+            ws = None
+            for m in self.model.modules():
+                cand = getattr(m, "fused", None)
+                if cand is not None and hasattr(cand, "g_epoch") and hasattr(cand, "r_epoch"):
+                    ws = cand
+                    break
+            before = (ws.g_epoch, ws.r_epoch) if ws is not None else (0, 0)
+            count0 = native.launches()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=self._graph_stream):
+                loss = self.model(self._static_ids, self._static_labels)
+                (loss / accum).backward()
+                self._static_loss = loss.detach()
+            if ws is not None and (((ws.g_epoch - before[0]) | (ws.r_epoch - before[1])) & 1):
+                raise RuntimeError("a captured micro-batch must issue an even number of fused gather / scatter "
+                                   "calls (buffer parity is fixed at capture time)")
+            self._graph_launches = native.launches() - count0
+            self._graph = graph
+        else:
+            self._static_ids.copy_(batch["input_ids"], non_blocking=True)
+            self._static_labels.copy_(batch["labels"], non_blocking=True)
+            native.add_launches(self._graph_launches)
+        self._graph.replay()
+        return self._static_loss
 
     def _param_norm(self):
         sq = None

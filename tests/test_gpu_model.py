@@ -110,3 +110,21 @@ def test_moe_block_native_matches_dense_restatement():
     assert (gu - up.grad).abs().max().item() < 8e-2 * max(up.grad.abs().max().item(), 1.0)
     gd = blk.experts_down.grad.float()
     assert (gd - down.grad).abs().max().item() < 8e-2 * max(down.grad.abs().max().item(), 1.0)
+
+
+def test_cuda_graph_micro_batch_matches_eager():
+    from ironcore_b200.trainer import Trainer
+
+    def run(graph):
+        cfg = _cfg("llama", "bf16", reset_position_ids=False, reset_attention_mask=False)
+        cfg.trainer(micro_batch_size=2, train_batch_size=8, gradient_accumulation_steps=None, cuda_graph=graph)
+        from ironcore_b200.config import validate_config
+
+        validate_config(cfg)
+        tr = Trainer(cfg)
+        return [float(tr.train_step(s)[0]) for s in range(3)]
+
+    a, b = run(False), run(True)
+    assert b is not None
+    for x, y in zip(a, b):
+        assert abs(x - y) < 2e-2, (a, b)

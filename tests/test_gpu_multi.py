@@ -48,7 +48,7 @@ def _spawn(fn_name, world=2):
     for p in procs:
         p.start()
     for p in procs:
-        p.join(300)
+        p.join(150)
     results = []
     while not q.empty():
         results.append(q.get())
@@ -104,25 +104,29 @@ def check_tp2_model_fused_matches_nccl(rank, world):
     from ironcore_b200.trainer import Trainer
     from helpers import tiny_config
 
-    def run(fused):
+    def run(fused, graph=False):
         mesh.destroy_model_parallel()
         cfg = tiny_config("llama", d_model=256, d_ffn=512, num_layers=2, num_attention_heads=4, head_dim=64,
                           max_seq_len=256, max_position_embeddings=256, precision="bf16", vocab_size=1024)
         cfg.data.vocab_size = 1024
-        cfg.trainer(micro_batch_size=2, train_batch_size=2, gradient_accumulation_steps=None,
-                    tensor_model_parallel_size=world)
+        cfg.model(reset_position_ids=False, reset_attention_mask=False)
+        cfg.trainer(micro_batch_size=2, train_batch_size=8 if graph else 2, gradient_accumulation_steps=None,
+                    tensor_model_parallel_size=world, cuda_graph=graph)
         cfg.parallel(world_size=world, rank=rank, local_rank=rank, sequence_parallel=True, fused_comm=fused)
         cfg.operation.train_steps = 3
         validate_config(cfg)
         tr = Trainer(cfg)
         if fused:
-            assert any(getattr(m, "fused", None) is not None for m in tr.model.modules())
+            assert any(hasattr(getattr(m, "fused", None), "g_epoch") for m in tr.model.modules())
         return [float(tr.train_step(s)[0]) for s in range(3)]
 
     a = run(False)
     b = run(True)
     for x, y in zip(a, b):
         assert abs(x - y) < 5e-2, (a, b)
+    # CUDA-graph replay of the micro-batch with the fused kernels inside (4 micro-batches per step)
+    graphed = run(True, graph=True)
+    assert all(l == l and l < 20 for l in graphed), graphed
 
 
 def test_fused_tp_kernels_two_gpus():
