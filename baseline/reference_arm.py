@@ -278,8 +278,15 @@ def run_reference(args, model_kw, global_batch, seq_len, metric) -> int:
             "memory_gib": torch.cuda.max_memory_allocated() / 2 ** 30,
         }
         print(json.dumps(out), flush=True)
+    import threading
+
+    watchdog = threading.Timer(45.0, lambda: os._exit(0))
+    watchdog.daemon = True
+    watchdog.start()
     try:
         trainer._finialize_process()
     except Exception:
         pass
+    finally:
+        watchdog.cancel()
     return 0

@@ -227,7 +227,14 @@ def run_ours(args):
             "memory_gib": torch.cuda.max_memory_allocated() / 2 ** 30,
         }
         print(json.dumps(out), flush=True)
-    trainer.finalize()
+    # Teardown must never outlive the measurement: if the collective shutdown stalls, leave anyway.
+    watchdog = threading.Timer(45.0, lambda: os._exit(0))
+    watchdog.daemon = True
+    watchdog.start()
+    try:
+        trainer.finalize()
+    finally:
+        watchdog.cancel()
     return 0
 
 

@@ -119,6 +119,15 @@ class Trainer:
 
     def finalize(self):
         G.global_states_cleanup()
+        if self._graph is not None:
+            # a captured graph keeps NCCL work objects alive: drop it before the process group goes away
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+            self._graph = None
+            self._static_loss = None
+            import gc
+
+            gc.collect()
         if self.heartbeat is not None:
             self.heartbeat.stop()
         if dist.is_initialized():
