@@ -131,6 +131,7 @@ def run_ours(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     trainer = Trainer(cfg)
     dev = trainer.device
+    fused_ws = getattr(trainer, "fused_tp", None)
     accum = cfg.trainer.gradient_accumulation_steps
     tokens_per_step = GLOBAL_BATCH * SEQ_LEN
 
@@ -215,8 +216,9 @@ def run_ours(args):
             "config": {"model": "llama-7b-shape (32L, d4096, 32h x 128, ffn 11008 swiglu, vocab 32000)",
                        "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN, "micro_batch": 1,
                        "parallelism": f"tp{world}" + ("+sp" if world > 1 else "") + "+zero1",
-                       "tp_comm": ("fused in-kernel P2P (all-gather->GEMM, GEMM->reduce-scatter)"
-                                   if (world > 1 and cfg.parallel.fused_comm) else ("nccl" if world > 1 else "none")),
+                       "tp_comm": (("fused in-kernel NVLS multimem" if getattr(fused_ws, "nvls", False)
+                                    else "fused in-kernel P2P") + " (all-gather->GEMM, GEMM->reduce-scatter)"
+                                   if (world > 1 and fused_ws is not None) else ("nccl" if world > 1 else "none")),
                        "optimizer": "adam(0.9,0.95) lr 3e-4, clip 1.0, fp32 grad accumulation",
                        "cuda_graph": bool(cfg.trainer.cuda_graph),
                        "l2": "no flush needed: every pass streams 13.5 GB of weights, far larger than the 126 MB L2"},

@@ -34,6 +34,7 @@ struct RsArgs {
   const void* residual;            // [rows_per_rank, ldr] or null
   long long ldr;
   const int* epoch_ptr;            // device word: calls completed so far on this workspace
+  const uint8_t* mc_recv;          // multicast (NVLS) address of the receive buffer, or null (see below)
   int in_fmt;
   int* status;
 };
@@ -162,8 +163,13 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, args.status, kTimeoutTmemFull);
       tc_fence_after();
       // Rows of this tile inside the owner's receive slot of the sending rank.
-      const size_t slot_row0 = (size_t)args.rank * args.rows_per_rank + (size_t)lm * 128;
-      uint8_t* dst_tile = args.peer_recv[owner] + slot_row0 * args.N * 2;
+      // NVLS form: the partial tile stays in this rank's own buffer, laid out [M][N]; the owner sums all
+      // ranks' copies with one multimem.ld_reduce per 16 bytes, so only the arrival counter crosses NVLink
+      // from here and the owner's ingress is 1x instead of world x.
+      const size_t slot_row0 = args.mc_recv != nullptr
+                                   ? (size_t)owner * args.rows_per_rank + (size_t)lm * 128
+                                   : (size_t)args.rank * args.rows_per_rank + (size_t)lm * 128;
+      uint8_t* dst_tile = args.peer_recv[args.mc_recv != nullptr ? args.rank : owner] + slot_row0 * args.N * 2;
       // The accumulator leaves in two halves of 128 columns. Each half is staged in shared memory
       // (two 128-byte-swizzled slabs) and then written out cooperatively so that every warp store
       // covers two rows x 256 contiguous bytes: NVLink sees full-line writes instead of 16-byte pieces.
@@ -272,6 +278,24 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                                       ((size_t)lrow * args.ldr + col) * 2);
           }
         }
+        if (args.mc_recv != nullptr) {
+          uint4 v[4];
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const int lrow = lm * 128 + rg * 16 + i0 + r;
+            const uint8_t* p = args.mc_recv + (((size_t)args.rank * args.rows_per_rank + lrow) * args.N + col) * 2;
+            v[r] = args.in_fmt == 1 ? multimem_ld_reduce_bf16x8(p) : multimem_ld_reduce_f16x8(p);
+          }
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const uint32_t w[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              float2 f = args.in_fmt == 1 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
+              acc[r][2 * t] += f.x; acc[r][2 * t + 1] += f.y;
+            }
+          }
+        } else
         for (int src = 0; src < args.world; ++src) {
           uint4 v[4];
 #pragma unroll
@@ -350,12 +374,14 @@ using namespace icb;
 //   A: [M, lda] row-major (K contiguous). b_major 0: B [N, ldb] (K contiguous); 1: B [K, ldb] (N contiguous).
 //   peer_recv / peer_flags: device arrays [world] of peer pointers to every rank's receive buffer
 //   ([world][rows_per_rank][N] 16-bit) and arrival counters ([rows_per_rank/128][ceil(N/256)] int).
+//   mc_recv: multicast (NVLS) address of the receive buffer or null. With it partial tiles stay local ([M][N]) and the
+//   owner reduces them through the switch (multimem.ld_reduce); same form on every call and rank of a workspace.
 //   N must be a multiple of 8; rows_per_rank a multiple of 128; epoch_ptr = device int with the number of calls already
 //   made on this pair of buffers (same on every rank; the caller increments it after the call).
 ICB_API int icb_gemm_rs(const void* A, const void* B, void* out, const void* bias, const void* residual, int M, int N,
                         int K, long long lda, long long ldb, long long ldo, long long ldr, int b_major, int in_dtype,
                         const void* const* peer_recv, int* const* peer_flags, const void* recv, const int* flags,
-                        int rank, int world, const int* epoch_ptr, int* status, void* stream_) {
+                        int rank, int world, const int* epoch_ptr, int* status, void* stream_, const void* mc_recv) {
   if (world < 1 || M % world != 0) return -2;
   const int rows_per_rank = M / world;
   if (rows_per_rank % 128 != 0 || N % 8 != 0) return -7;
@@ -394,6 +420,7 @@ ICB_API int icb_gemm_rs(const void* A, const void* B, void* out, const void* bia
   a.out = out; a.ldo = ldo;
   a.bias = bias; a.residual = residual; a.ldr = ldr;
   a.epoch_ptr = epoch_ptr;
+  a.mc_recv = reinterpret_cast<const uint8_t*>(mc_recv);
   a.in_fmt = (in_dtype == kBF16) ? 1 : 0;
   a.status = status;
   int grid = num_sms();

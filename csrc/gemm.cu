@@ -52,6 +52,7 @@ struct GemmArgs {
   int* const* ag_peer_ready;        // device array [world]: every rank's arrival counters
   const int* ag_epoch_ptr;          // device word: calls completed so far on this workspace (this call = +1)
   int ag_chunks_per_block;          // 8 KiB chunks in one 128-row block
+  uint8_t* ag_mc;                   // multicast (NVLS) address of the gathered buffer, or null: plain P2P stores
 };
 
 constexpr int kAgChunkBytes = 8192;  // copy granularity of the all-gather (one warp iteration)
@@ -430,37 +431,68 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const long long shard_bytes = (long long)args.ag_rows_per_rank * args.ag_row_bytes;
     const long long block_bytes = 128LL * args.ag_row_bytes;
     const int chunks_per_shard = (int)(shard_bytes / kAgChunkBytes);
-    const int total_chunks = (args.ag_world - 1) * chunks_per_shard;
     // A system-scope fence waits for the acknowledgement of every remote store, i.e. a full NVLink
     // round trip: issue it once per batch of chunks (up to kAgBatch), then publish the batch.
     constexpr int kAgBatch = 16;
-    int c = cw;
-    while (c < total_chunks) {
-      int done_q[kAgBatch], done_rb[kAgBatch];
-      int n_done = 0;
+    if (args.ag_mc != nullptr) {
+      // NVLS form: one multimem.st per 16 bytes lands in every rank's buffer (the switch replicates),
+      // so the shard leaves this GPU once instead of world-1 times. The arrival counters are still
+      // bumped per peer, by lanes 0..world-2 in parallel.
+      int c = cw;
+      while (c < chunks_per_shard) {
+        int done_rb[kAgBatch];
+        int n_done = 0;
 #pragma unroll 1
-      for (; c < total_chunks && n_done < kAgBatch; c += n_cw) {
-        const int step = c / chunks_per_shard + 1;
-        const int within = c - (step - 1) * chunks_per_shard;
-        const int q = (args.ag_rank + step) % args.ag_world;
-        const long long off = (long long)args.ag_rank * shard_bytes + (long long)within * kAgChunkBytes;
-        const uint4* src = reinterpret_cast<const uint4*>(args.ag_local + off);
-        uint4* dst = reinterpret_cast<uint4*>(args.ag_peers[q] + off);
-        uint4 v[16];
+        for (; c < chunks_per_shard && n_done < kAgBatch; c += n_cw) {
+          const long long off = (long long)args.ag_rank * shard_bytes + (long long)c * kAgChunkBytes;
+          const uint4* src = reinterpret_cast<const uint4*>(args.ag_local + off);
+          uint4* dst = reinterpret_cast<uint4*>(args.ag_mc + off);
+          uint4 v[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = src[lane + j * 32];
+          for (int j = 0; j < 16; ++j) v[j] = src[lane + j * 32];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) dst[lane + j * 32] = v[j];
-        done_q[n_done] = q;
-        done_rb[n_done] = (int)(off / block_bytes);
-        ++n_done;
+          for (int j = 0; j < 16; ++j) multimem_st_v4(dst + lane + j * 32, v[j]);
+          done_rb[n_done] = (int)(off / block_bytes);
+          ++n_done;
+        }
+        __syncwarp();
+        for (int p = lane; p < args.ag_world - 1; p += 32) {
+          const int q = (args.ag_rank + 1 + p) % args.ag_world;
+          __threadfence_system();
+          for (int i = 0; i < n_done; ++i) red_release_sys_add(args.ag_peer_ready[q] + done_rb[i], 1);
+        }
+        __syncwarp();
       }
-      __syncwarp();
-      if (lane == 0) {
-        __threadfence_system();
-        for (int i = 0; i < n_done; ++i) red_release_sys_add(args.ag_peer_ready[done_q[i]] + done_rb[i], 1);
+    } else {
+      const int total_chunks = (args.ag_world - 1) * chunks_per_shard;
+      int c = cw;
+      while (c < total_chunks) {
+        int done_q[kAgBatch], done_rb[kAgBatch];
+        int n_done = 0;
+#pragma unroll 1
+        for (; c < total_chunks && n_done < kAgBatch; c += n_cw) {
+          const int step = c / chunks_per_shard + 1;
+          const int within = c - (step - 1) * chunks_per_shard;
+          const int q = (args.ag_rank + step) % args.ag_world;
+          const long long off = (long long)args.ag_rank * shard_bytes + (long long)within * kAgChunkBytes;
+          const uint4* src = reinterpret_cast<const uint4*>(args.ag_local + off);
+          uint4* dst = reinterpret_cast<uint4*>(args.ag_peers[q] + off);
+          uint4 v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = src[lane + j * 32];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) dst[lane + j * 32] = v[j];
+          done_q[n_done] = q;
+          done_rb[n_done] = (int)(off / block_bytes);
+          ++n_done;
+        }
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_system();
+          for (int i = 0; i < n_done; ++i) red_release_sys_add(args.ag_peer_ready[done_q[i]] + done_rb[i], 1);
+        }
+        __syncwarp();
       }
-      __syncwarp();
     }
   }
 
@@ -565,6 +597,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, co
     args.ag_rank = 0; args.ag_world = 1; args.ag_rows_per_rank = 0; args.ag_row_bytes = 0;
     args.ag_local = nullptr; args.ag_peers = nullptr; args.ag_peer_signal = nullptr; args.ag_signal = nullptr;
     args.ag_ready = nullptr; args.ag_epoch_ptr = nullptr; args.ag_chunks_per_block = 1; args.ag_peer_ready = nullptr;
+    args.ag_mc = nullptr;
   }
   args.M = M; args.N = N; args.K = K;
   args.num_m_tiles = (M + kBM - 1) / kBM;
@@ -615,13 +648,15 @@ ICB_API int icb_gemm(const void* A, const void* B, void* C, const void* bias, co
 //              rank); the caller increments it in stream order after this call.
 //   a_major 0: C[M = world*rows_per_rank, N] = gathered[M, K = width] * B        (forward / dgrad of a row-parallel layer)
 //   a_major 1: C[M = width, N] = gathered^T * B[K = world*rows_per_rank, N]      (wgrad: reduction over gathered rows)
+//   gathered_mc: multicast (NVLS) address of `gathered` or null. With it the shard is pushed once with multimem.st
+//              and replicated by the NVSwitch; a workspace must use the same form on every call and rank.
 // The local shard is pushed to every peer with plain P2P stores by copy warps inside the same kernel;
 // the tensor core starts with the local shard and follows the other shards in arrival order.
 ICB_API int icb_ag_gemm(void* gathered, const void* const* peers, int* const* peer_ready, const int* signal,
                         int* ready, int rank, int world, int rows_per_rank, int width, const int* epoch_ptr, const void* B,
                         void* C, const void* bias, const void* residual, int N, long long ldb, long long ldc,
                         long long ldr, int a_major, int b_major, int in_dtype, int out_f32, int* status,
-                        void* stream_) {
+                        void* stream_, void* gathered_mc) {
   if (rows_per_rank % 128 != 0 || width % 32 != 0) return -7;   // 128-row blocks must be whole 8 KiB chunks
   GemmArgs ag;
   ag.ag_rank = rank; ag.ag_world = world; ag.ag_rows_per_rank = rows_per_rank;
@@ -633,6 +668,7 @@ ICB_API int icb_ag_gemm(void* gathered, const void* const* peers, int* const* pe
   ag.ag_signal = signal;
   ag.ag_ready = ready;
   ag.ag_epoch_ptr = epoch_ptr;
+  ag.ag_mc = reinterpret_cast<uint8_t*>(gathered_mc);
   ag.ag_chunks_per_block = (int)(128LL * width * 2 / kAgChunkBytes);
   const int rows = world * rows_per_rank;
   const int M = a_major == 0 ? rows : width;

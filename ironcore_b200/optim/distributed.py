@@ -88,7 +88,8 @@ class Slot:
 class FlatGroup:
     """One contiguous parameter buffer + gradient buffer reduced over ``group``."""
 
-    def __init__(self, named_params, reduce_group, weight_decay: float, decay_fn, muon_fn, grad_dtype, pad_to: int):
+    def __init__(self, named_params, reduce_group, weight_decay: float, decay_fn, muon_fn, grad_dtype, pad_to: int,
+                 alloc=None):
         self.reduce_group = reduce_group
         self.dp = _gsize(reduce_group)
         self.dp_rank = _grank(reduce_group)
@@ -119,8 +120,13 @@ class FlatGroup:
         first = self.slots[0].param if self.slots else None
         self.dtype = first.dtype if first is not None else torch.float32
         self.device = first.device if first is not None else torch.device("cpu")
-        self.param_buf = torch.zeros(self.total, dtype=self.dtype, device=self.device)
-        self.grad_buf = torch.zeros(self.total, dtype=grad_dtype or self.dtype, device=self.device)
+        # ``alloc(group, param_dtype, grad_dtype)`` may place both buffers in symmetric memory (fused ZeRO step)
+        bufs = alloc(self, self.dtype, grad_dtype or self.dtype) if (alloc is not None and self.total > 0) else None
+        if bufs is not None:
+            self.param_buf, self.grad_buf = bufs
+        else:
+            self.param_buf = torch.zeros(self.total, dtype=self.dtype, device=self.device)
+            self.grad_buf = torch.zeros(self.total, dtype=grad_dtype or self.dtype, device=self.device)
         for s in self.slots:
             view = self.param_buf[s.offset:s.offset + s.numel].view(s.param.shape)
             view.copy_(s.param.data)
@@ -179,8 +185,19 @@ class DistributedOptimizer:
         dense = [it for it in uniq if not getattr(it[3], "expert_parallel", False)]
         expert = [it for it in uniq if getattr(it[3], "expert_parallel", False)]
         self.groups: List[FlatGroup] = []
+        self.fused_zero = None
+        alloc = None
+        if self.zero and not expert and not self.use_muon and not self.offload and self.tp_size == 1 \
+                and _gsize(self.dp_group) > 1 and getattr(config.parallel, "fused_comm", True) \
+                and grad_dtype == torch.float32 and dense and dense[0][3].is_cuda \
+                and dense[0][3].dtype in (torch.bfloat16, torch.float16):
+            from .fused_zero import FusedZeroStep
+
+            self.fused_zero = FusedZeroStep.create(self.dp_group)
+            alloc = self.fused_zero.allocate if self.fused_zero is not None else None
         if dense:
-            self.groups.append(FlatGroup(dense, self.dp_group, o.weight_decay, decay_fn, muon_fn, grad_dtype, 128))
+            self.groups.append(FlatGroup(dense, self.dp_group, o.weight_decay, decay_fn, muon_fn, grad_dtype, 128,
+                                         alloc=alloc))
         if expert:
             self.groups.append(FlatGroup(expert, self.edp_group, o.weight_decay, decay_fn, muon_fn, grad_dtype, 128))
         self.param_groups = [{"lr": o.max_lr, "initial_lr": o.max_lr, "name": "adam"}]
@@ -351,9 +368,30 @@ class DistributedOptimizer:
                 hv.copy_(dv, non_blocking=True)
         torch.cuda.current_stream().wait_stream(side)
 
+    def _fused_zero_step(self):
+        """Gradient reduce-scatter, global norm, Adam and parameter all-gather in two kernels that talk
+        to the peers' buffers directly (pure data parallelism, one flat group)."""
+        g, mom = self.groups[0], self.moments[0]
+        lo, hi = g.shard_range(True)
+        inv = 1.0 / (self.grad_div * self.grad_div)
+        regions = []
+        for r in g.regions:
+            a, b = max(r.start, lo), min(r.end, hi)
+            if b > a:
+                regions.append((a, b, inv, r.weight_decay, 1.0 if r.kind == "adam" else 0.0))
+        b1, b2 = self.betas
+        bc1, bc2 = 1.0 - b1 ** self.step_count, 1.0 - b2 ** self.step_count
+        lr = self.param_groups[0]["lr"]
+        return self.fused_zero.step(regions, lo, mom["exp_avg"], mom["exp_avg_sq"], lr=lr, beta1=b1, beta2=b2,
+                                    eps=self.eps, step_size=lr * (bc2 ** 0.5) / bc1, grad_scale=1.0 / self.grad_div,
+                                    clip=self.clip)
+
     @torch.no_grad()
     def step(self):
         self.step_count += 1
+        if self.fused_zero is not None and self.fused_zero.ready:
+            self._norm = self._fused_zero_step()
+            return self._norm
         for g in self.groups:
             self._tp_sync_replicated(g)
             self._reduce_grads(g)

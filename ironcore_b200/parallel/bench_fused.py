@@ -33,7 +33,8 @@ def main():
     from ironcore_b200.parallel.fused_comm import FusedTP
 
     t, d, f = args.tokens, args.width, args.ffn
-    ws = FusedTP(t, d, dist.group.WORLD)
+    ws = FusedTP(t, d, dist.group.WORLD)                 # NVLS form when the fabric offers multicast
+    ws_p2p = FusedTP(t, d, dist.group.WORLD, nvls=False) if ws.nvls else ws   # plain P2P stores / loads
     rows = t // world
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     peak_tflops, link_gbs = 1414.0, 770.0
@@ -66,12 +67,12 @@ def main():
         w = torch.randn(d, n_local, device="cuda").bfloat16()
         full = torch.empty(t, d, device="cuda", dtype=torch.bfloat16)
 
-        def fused(x=x, w=w, n_local=n_local):
-            ws.ag_gemm(x, w, a_major=0, b_major=1, n=n_local)
+        def fused(ws=ws, x=x, w=w, n_local=n_local):
+            return ws.ag_gemm(x, w, a_major=0, b_major=1, n=n_local)
 
         def nccl(x=x, w=w, full=full):
             dist.all_gather_into_tensor(full, x)
-            kernels.mm_nn(full, w)
+            return kernels.mm_nn(full, w)
 
         def gemm_only(w=w, full=full):
             kernels.mm_nn(full, w)
@@ -86,12 +87,12 @@ def main():
         dy = torch.randn(t, n_local, device="cuda").bfloat16()
         full = torch.empty(t, d, device="cuda", dtype=torch.bfloat16)
 
-        def fused(x=x, dy=dy, n_local=n_local):
-            ws.ag_gemm(x, dy, a_major=1, b_major=1, n=n_local)
+        def fused(ws=ws, x=x, dy=dy, n_local=n_local):
+            return ws.ag_gemm(x, dy, a_major=1, b_major=1, n=n_local)
 
         def nccl(x=x, dy=dy, full=full):
             dist.all_gather_into_tensor(full, x)
-            kernels.mm_tn(full, dy)
+            return kernels.mm_tn(full, dy)
 
         def gemm_only(dy=dy, full=full):
             kernels.mm_tn(full, dy)
@@ -104,12 +105,13 @@ def main():
         w = torch.randn(k_local, d, device="cuda").bfloat16()
         out = torch.empty(rows, d, device="cuda", dtype=torch.bfloat16)
 
-        def fused(a=a, w=w):
-            ws.gemm_rs(a, w, b_major=1)
+        def fused(ws=ws, a=a, w=w):
+            return ws.gemm_rs(a, w, b_major=1)
 
         def nccl(a=a, w=w, out=out):
             y = kernels.mm_nn(a, w)
             dist.reduce_scatter_tensor(out, y)
+            return out
 
         def gemm_only(a=a, w=w):
             kernels.mm_nn(a, w)
@@ -118,18 +120,27 @@ def main():
         wire = (world - 1) * rows * d * 2
         cases.append((name, "gemm_rs", fused, nccl, gemm_only, flops, wire))
     for name, kind, fused, nccl, gemm_only, flops, wire in cases:
+        ref = nccl().float()
+        err = max(float((fused(ws=w_).float() - ref).abs().max()) for w_ in {id(ws): ws, id(ws_p2p): ws_p2p}.values())
+        scale = float(ref.abs().max())
         tf = timeit(fused)
+        tp = timeit(lambda: fused(ws=ws_p2p)) if ws_p2p is not ws else tf
         tn = timeit(nccl)
         tg = timeit(gemm_only)
         roof_ms = max(flops / (peak_tflops * 1e9), wire / (link_gbs * 1e6))
         if rank == 0:
-            print(json.dumps({"case": name, "kind": kind, "world": world, "fused_ms": tf, "nccl_plus_gemm_ms": tn,
+            print(json.dumps({"case": name, "kind": kind, "world": world, "nvls": ws.nvls, "fused_ms": tf,
+                              "fused_p2p_ms": tp, "max_abs_err_vs_nccl": err, "ref_abs_max": scale, "nccl_plus_gemm_ms": tn,
                               "gemm_only_ms": tg, "roofline_ms": roof_ms, "fraction_of_roofline": roof_ms / tf,
                               "wire_mb": wire / 1e6, "gflop": flops / 1e9}), flush=True)
     torch.cuda.synchronize()
     native.check_status()
     dist.barrier()
+    import threading
+
+    threading.Timer(30.0, lambda: os._exit(0)).start()   # never let a stuck communicator teardown hold the GPUs
     dist.destroy_process_group()
+    os._exit(0)
 
 
 if __name__ == "__main__":

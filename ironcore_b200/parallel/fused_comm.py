@@ -28,6 +28,8 @@ from __future__ import annotations
 
 from typing import Optional
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -36,12 +38,23 @@ from ..ops.native import call, dtype_code, ptr, stream_ptr
 from .symmetric import SymmetricBuffer, symmetric_memory_available
 
 P, I, L = native.P, native.I, native.L
-native.register("icb_ag_gemm", [P, P, P, P, P, I, I, I, I, P, P, P, P, P, I, L, L, L, I, I, I, I, P, P])
-native.register("icb_gemm_rs", [P, P, P, P, P, I, I, I, L, L, L, L, I, I, P, P, P, P, I, I, P, P, P])
+native.register("icb_ag_gemm", [P, P, P, P, P, I, I, I, I, P, P, P, P, P, I, L, L, L, I, I, I, I, P, P, P])
+native.register("icb_gemm_rs", [P, P, P, P, P, I, I, I, L, L, L, L, I, I, P, P, P, P, I, I, P, P, P, P])
+
+
+def _nvls_requested(world: int) -> bool:
+    """ICB_NVLS=1 / 0 forces the multicast form on / off; by default it is used from 4 ranks up, where
+    pushing a shard once instead of world-1 times pays (at 2 ranks plain P2P stores are faster)."""
+    v = os.environ.get("ICB_NVLS", "auto").lower()
+    if v in ("0", "false", "off"):
+        return False
+    if v in ("1", "true", "on"):
+        return True
+    return world >= 4
 
 
 class FusedTP:
-    def __init__(self, tokens: int, width: int, group, dtype=torch.bfloat16):
+    def __init__(self, tokens: int, width: int, group, dtype=torch.bfloat16, nvls: Optional[bool] = None):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -82,6 +95,14 @@ class FusedTP:
         # True: forward keeps the gathered activations (32 MiB at 4096 x 4096) for the weight gradient;
         # False: backward re-gathers inside the wgrad kernel (less memory, exposed transfer).
         self.save_gathered = True
+        # NVLS: push the gathered shard once with multimem.st and reduce the scattered partials with
+        # multimem.ld_reduce when the symmetric allocations have a multicast mapping on every rank.
+        want = _nvls_requested(self.world) if nvls is None else bool(nvls)
+        have = torch.tensor([1 if (self.gbuf.multicast_ptr and self.rbuf.multicast_ptr) else 0],
+                            dtype=torch.int32, device=self.gbuf.local.device)
+        if self.world > 1:
+            dist.all_reduce(have, op=dist.ReduceOp.MIN, group=group)
+        self.nvls = bool(want and self.world > 1 and int(have.item()) == 1)
 
     # ------------------------------------------------------------------ raw kernels
     def ag_gemm(self, x_shard: torch.Tensor, b: torch.Tensor, *, a_major: int, b_major: int, n: int,
@@ -103,7 +124,8 @@ class FusedTP:
              ptr(self.g_ready), self.rank, self.world, self.rows, self.width, ptr(self.g_epoch_dev), ptr(b), ptr(out),
              ptr(bias), ptr(residual), int(n), b.stride(0), out.stride(0), ldr, int(a_major), int(b_major),
              dtype_code(self.dtype), 1 if out_dtype == torch.float32 else 0,
-             ptr(native.status_tensor(x_shard.device)), stream_ptr())
+             ptr(native.status_tensor(x_shard.device)), stream_ptr(),
+             (self.gbuf.multicast_ptr + self._g_off[par]) if self.nvls else None)
         self.g_epoch_dev.add_(1)
         self.last_gathered = gathered
         return out
@@ -122,7 +144,8 @@ class FusedTP:
         call("icb_gemm_rs", ptr(a), ptr(b), ptr(out), ptr(bias), ptr(residual), self.tokens, n, k, a.stride(0),
              b.stride(0), out.stride(0), ldr, int(b_major), dtype_code(self.dtype), ptr(self.r_peers[par]),
              ptr(self.r_peer_flags), recv_ptr, ptr(self.r_flags), self.rank, self.world, ptr(self.r_epoch_dev),
-             ptr(native.status_tensor(a.device)), stream_ptr())
+             ptr(native.status_tensor(a.device)), stream_ptr(),
+             (self.rbuf.multicast_ptr + self._r_off[par]) if self.nvls else None)
         self.r_epoch_dev.add_(1)
         return out
 

@@ -3,8 +3,9 @@
 A workspace is one allocation of PyTorch's symmetric-memory allocator, made by every rank of
 a process group with the same size and exchanged with ``rendezvous``; afterwards each rank
 knows the device address of every peer's copy (NVLink peer pointers through NVSwitch). The
-kernels read / write those addresses directly (plain P2P loads and stores, release/acquire
-flags); no TMA multicast and no library kernel ever sees a peer pointer.
+kernels read / write those addresses directly (plain P2P loads and stores, ``multimem`` stores and
+reductions through the NVSwitch multicast mapping, release/acquire flags); no TMA multicast and no
+library kernel ever sees a peer pointer.
 """
 
 from __future__ import annotations
@@ -46,6 +47,12 @@ class SymmetricBuffer:
         self.peer_ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
         if self.peer_ptrs[self.rank] != self.local.data_ptr():
             raise RuntimeError("symmetric memory: local pointer does not match the rendezvous table")
+        # Multicast (NVLS) mapping of the same allocation: a store to it lands in every rank's copy, a
+        # multimem.ld_reduce returns the sum over the copies. 0 when the fabric has no multicast support.
+        try:
+            self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        except Exception:
+            self.multicast_ptr = 0
 
     def view(self, offset: int, shape, dtype) -> torch.Tensor:
         n = 1

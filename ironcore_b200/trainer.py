@@ -161,7 +161,7 @@ class Trainer:
                 and mesh.sequence_parallel_enabled():
             from .parallel.fused_comm import attach_fused_tp
 
-            attach_fused_tp(model, cfg)
+            self.fused_tp = attach_fused_tp(model, cfg)
         if cfg.utils.profile_torch or cfg.utils.profile_nsys:
             base = model.module if hasattr(model, "module") else model
             if hasattr(base, "register_profile_hooks"):

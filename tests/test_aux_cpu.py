@@ -181,3 +181,25 @@ def test_hellaswag_task_on_inline_examples():
     ex = [{"ctx": "a b c", "endings": ["d", "e f", "g", "hh"], "label": 1} for _ in range(3)]
     res = HellaSwag(tok, 1, None, examples=ex).process(model)
     assert res["metric"] == "accuracy" and 0.0 <= res["score"] <= 100.0
+
+
+def test_gpt2_loss_curve_matches_reference_cpu():
+    """Same weights, same batches, same optimizer settings: the loss curve of the unmodified reference
+    trainer and ours agree step by step (fp32, CPU). Runs in a child process because the reference
+    owns its own process group and global state."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if not os.path.isdir(os.path.join(root, "baseline", "_ref", "ironcore")):
+        pytest.skip("reference is not installed under baseline/_ref")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    out = subprocess.run([sys.executable, "-m", "baseline.parity_gpt2", "--layers", "2", "--d-model", "64", "--heads",
+                          "4", "--vocab", "512", "--seq", "32", "--micro-batch", "2", "--steps", "8"],
+                         cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    res = json.loads(out.stdout.strip().splitlines()[-1])
+    assert res["missing_in_ours"] == [] and res["not_in_ours"] == []
+    assert res["max_abs_diff"] < 1e-4, res
