@@ -133,6 +133,9 @@ class MoEBlock(nn.Module):
         self.experts_down = nn.Parameter(torch.empty(self.e_local, self.ffn, m.d_model, dtype=dtype, device=device))
         self.experts_up.expert_parallel = True
         self.experts_down.expert_parallel = True
+        self.fused_ep = None          # set lazily on the first CUDA forward (symmetric-memory workspace)
+        self._fused_ep_tried = False
+        self._max_tokens = config.trainer.micro_batch_size * m.max_seq_len
         self.shared = None
         if moe.num_shared_experts > 0:
             s_ffn = (moe.shared_expert_d_ffn or self.ffn) * moe.num_shared_experts
@@ -169,10 +172,43 @@ class MoEBlock(nn.Module):
         yp = grouped_linear(h, self.experts_down, tile_expert, seg_offsets)
         return yp.index_select(0, dest)
 
+    def _experts_on_layout(self, xp, seg_offsets, tile_expert):
+        """Expert MLPs on rows that already sit in the padded, expert-sorted layout."""
+        h = grouped_linear(xp, self.experts_up, tile_expert, seg_offsets)
+        used = seg_offsets[-1].to(torch.long)
+        row = torch.arange(xp.shape[0], device=h.device)
+        h = torch.where((row < used)[:, None], h, torch.zeros((), dtype=h.dtype, device=h.device))
+        h = self.activation(h)
+        return grouped_linear(h, self.experts_down, tile_expert, seg_offsets)
+
+    def _fused_workspace(self, x):
+        if not self._fused_ep_tried:
+            self._fused_ep_tried = True
+            if x.is_cuda and self.ep > 1 and OF.use_native(x):
+                from ..parallel.fused_moe import get_fused_ep
+
+                self.fused_ep = get_fused_ep(self.ep_group, self.num_experts, self.top_k,
+                                             max(self._max_tokens, x.shape[0]), self.d_model, x.dtype)
+        return self.fused_ep
+
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None):
         """x: [T, d] -> ([T, d], aux loss)."""
         t, d = x.shape
         w, idx, aux = self.route(x)
+        ws = self._fused_workspace(x) if self.ep > 1 else None
+        if ws is not None and t <= ws.max_tokens:
+            # dispatch, expert GEMMs and combine without leaving the device: the exchange runs inside kernels
+            from ..parallel.fused_moe import fused_combine, fused_dispatch
+
+            expert = idx.reshape(-1).to(torch.int32)
+            xp, dest, seg, tile_expert, counts = fused_dispatch(x, expert, ws)
+            yp = self._experts_on_layout(xp, seg, tile_expert)
+            out = fused_combine(yp, w, expert, dest, counts, ws)
+            if self.shared is not None:
+                out = out + self.shared(x)
+            if residual is not None:
+                out = out + residual
+            return out, aux
         slots_expert = idx.reshape(-1)                                   # [T*k]
         token_of_slot = torch.arange(t, device=x.device).repeat_interleave(self.top_k)
         xs = x.index_select(0, token_of_slot)

@@ -175,6 +175,70 @@ def check_dp2_fused_zero_matches_nccl(rank, world):
         assert (pa - pb).abs().max().item() < 2e-2, (pa - pb).abs().max().item()
 
 
+def check_ep2_fused_moe_matches_nccl(rank, world):
+    """Expert parallelism over 2 GPUs: dispatch / combine inside kernels (P2P stores and loads into the
+    grouped GEMM's layout) against the all-to-all composition, block level (output and gradients) and
+    three trainer steps."""
+    import os
+
+    import torch.distributed as dist
+
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.models.moe import MoEBlock
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.parallel.fused_moe import release_workspaces
+    from ironcore_b200.trainer import Trainer
+    from helpers import tiny_config
+
+    def cfg_for():
+        cfg = tiny_config("llama", d_model=256, d_ffn=512, num_layers=2, num_attention_heads=4, head_dim=64,
+                          num_attention_groups=2, max_seq_len=128, max_position_embeddings=128, precision="bf16",
+                          vocab_size=1024)
+        cfg.data.vocab_size = 1024
+        cfg.model(reset_position_ids=False, reset_attention_mask=False)
+        cfg.model.moe(num_experts=8, top_k=2, expert_d_ffn=128, num_shared_experts=1, aux_loss_coeff=0.01)
+        cfg.trainer(micro_batch_size=2, train_batch_size=4, gradient_accumulation_steps=None,
+                    tensor_model_parallel_size=1)
+        cfg.parallel(world_size=world, rank=rank, local_rank=rank, expert_model_parallel_size=world)
+        cfg.operation.train_steps = 3
+        validate_config(cfg)
+        return cfg
+
+    def block_run(fused):
+        os.environ["ICB_FUSED_MOE"] = "1" if fused else "0"
+        release_workspaces()
+        mesh.destroy_model_parallel()
+        cfg = cfg_for()
+        mesh.initialize_model_parallel(1, world)
+        torch.manual_seed(5)
+        blk = MoEBlock(cfg, dtype=torch.bfloat16, device=torch.device("cuda"))
+        for p in blk.parameters():
+            torch.nn.init.normal_(p, std=0.05)
+        torch.manual_seed(11 + rank)
+        x = torch.randn(256, 256, device="cuda").bfloat16().requires_grad_(True)
+        out, aux = blk(x)
+        assert (blk.fused_ep is not None) == fused
+        g = torch.randn_like(out)
+        (out * g).sum().backward()
+        return out.detach().float(), x.grad.float(), blk.experts_up.grad.float(), blk.router.weight.grad.float()
+
+    a = block_run(False)
+    b = block_run(True)
+    for u, v, tol in zip(a, b, (3e-2, 3e-2, 1e-1, 1e-1)):
+        assert (u - v).abs().max().item() <= tol * max(1.0, u.abs().max().item()), (u - v).abs().max().item()
+
+    def train_run(fused):
+        os.environ["ICB_FUSED_MOE"] = "1" if fused else "0"
+        release_workspaces()
+        mesh.destroy_model_parallel()
+        tr = Trainer(cfg_for())
+        return [float(tr.train_step(s)[0]) for s in range(3)]
+
+    la, lb = train_run(False), train_run(True)
+    for x, y in zip(la, lb):
+        assert abs(x - y) < 5e-2, (la, lb)
+
+
 def test_fused_tp_kernels_two_gpus():
     _need_two()
     _spawn("check_raw_kernels")
@@ -183,6 +247,11 @@ def test_fused_tp_kernels_two_gpus():
 def test_dp2_fused_zero_step_vs_nccl():
     _need_two()
     _spawn("check_dp2_fused_zero_matches_nccl")
+
+
+def test_ep2_fused_moe_vs_nccl():
+    _need_two()
+    _spawn("check_ep2_fused_moe_matches_nccl")
 
 
 def test_tp2_sp_model_fused_vs_nccl():
