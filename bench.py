@@ -216,8 +216,11 @@ def run_ours(args):
             "config": {"model": "llama-7b-shape (32L, d4096, 32h x 128, ffn 11008 swiglu, vocab 32000)",
                        "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN, "micro_batch": 1,
                        "parallelism": f"tp{world}" + ("+sp" if world > 1 else "") + "+zero1",
-                       "tp_comm": (("fused in-kernel NVLS multimem" if getattr(fused_ws, "nvls", False)
-                                    else "fused in-kernel P2P") + " (all-gather->GEMM, GEMM->reduce-scatter)"
+                       "tp_comm": ("fused in-kernel (all-gather->GEMM: "
+                                   + ("NVLS multimem.st" if getattr(fused_ws, "nvls_ag", False) else "P2P stores")
+                                   + ", GEMM->reduce-scatter: "
+                                   + ("NVLS multimem.ld_reduce" if getattr(fused_ws, "nvls_rs", False) else "P2P stores")
+                                   + ")"
                                    if (world > 1 and fused_ws is not None) else ("nccl" if world > 1 else "none")),
                        "optimizer": "adam(0.9,0.95) lr 3e-4, clip 1.0, fp32 grad accumulation",
                        "cuda_graph": bool(cfg.trainer.cuda_graph),

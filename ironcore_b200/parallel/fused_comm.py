@@ -42,15 +42,18 @@ native.register("icb_ag_gemm", [P, P, P, P, P, I, I, I, I, P, P, P, P, P, I, L, 
 native.register("icb_gemm_rs", [P, P, P, P, P, I, I, I, L, L, L, L, I, I, P, P, P, P, I, I, P, P, P, P])
 
 
-def _nvls_requested(world: int) -> bool:
-    """ICB_NVLS=1 / 0 forces the multicast form on / off; by default it is used from 4 ranks up, where
-    pushing a shard once instead of world-1 times pays (at 2 ranks plain P2P stores are faster)."""
+def _nvls_requested(world: int, op: str) -> bool:
+    """Whether ``op`` ("ag" or "rs") uses the NVSwitch multicast form. ``ICB_NVLS=1`` / ``0`` forces it on /
+    off for both. By default the all-gather push uses it from 4 ranks up (one multimem.st instead of world-1
+    P2P stores: measured 13 % faster at 4 ranks, slower at 2), and the reduce-scatter stays on P2P stores:
+    pushing partial tiles while the tensor core still works overlaps better than pulling the sums through
+    the switch after the last tile (measured at 2 and 4 ranks)."""
     v = os.environ.get("ICB_NVLS", "auto").lower()
     if v in ("0", "false", "off"):
         return False
     if v in ("1", "true", "on"):
         return True
-    return world >= 4
+    return op == "ag" and world >= 4
 
 
 class FusedTP:
@@ -97,12 +100,14 @@ class FusedTP:
         self.save_gathered = True
         # NVLS: push the gathered shard once with multimem.st and reduce the scattered partials with
         # multimem.ld_reduce when the symmetric allocations have a multicast mapping on every rank.
-        want = _nvls_requested(self.world) if nvls is None else bool(nvls)
         have = torch.tensor([1 if (self.gbuf.multicast_ptr and self.rbuf.multicast_ptr) else 0],
                             dtype=torch.int32, device=self.gbuf.local.device)
         if self.world > 1:
             dist.all_reduce(have, op=dist.ReduceOp.MIN, group=group)
-        self.nvls = bool(want and self.world > 1 and int(have.item()) == 1)
+        have = self.world > 1 and int(have.item()) == 1
+        self.nvls_ag = bool(have and (_nvls_requested(self.world, "ag") if nvls is None else nvls))
+        self.nvls_rs = bool(have and (_nvls_requested(self.world, "rs") if nvls is None else nvls))
+        self.nvls = self.nvls_ag or self.nvls_rs
 
     # ------------------------------------------------------------------ raw kernels
     def ag_gemm(self, x_shard: torch.Tensor, b: torch.Tensor, *, a_major: int, b_major: int, n: int,
@@ -125,7 +130,7 @@ class FusedTP:
              ptr(bias), ptr(residual), int(n), b.stride(0), out.stride(0), ldr, int(a_major), int(b_major),
              dtype_code(self.dtype), 1 if out_dtype == torch.float32 else 0,
              ptr(native.status_tensor(x_shard.device)), stream_ptr(),
-             (self.gbuf.multicast_ptr + self._g_off[par]) if self.nvls else None)
+             (self.gbuf.multicast_ptr + self._g_off[par]) if self.nvls_ag else None)
         self.g_epoch_dev.add_(1)
         self.last_gathered = gathered
         return out
@@ -145,7 +150,7 @@ class FusedTP:
              b.stride(0), out.stride(0), ldr, int(b_major), dtype_code(self.dtype), ptr(self.r_peers[par]),
              ptr(self.r_peer_flags), recv_ptr, ptr(self.r_flags), self.rank, self.world, ptr(self.r_epoch_dev),
              ptr(native.status_tensor(a.device)), stream_ptr(),
-             (self.rbuf.multicast_ptr + self._r_off[par]) if self.nvls else None)
+             (self.rbuf.multicast_ptr + self._r_off[par]) if self.nvls_rs else None)
         self.r_epoch_dev.add_(1)
         return out
 
