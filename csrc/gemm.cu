@@ -25,6 +25,8 @@
 // issuer, warps 2-5 = epilogue (one TMEM lane quarter each).
 #include "host_common.h"
 #include "ptx.cuh"
+#include <cstdlib>
+
 #include "gemm_common.cuh"
 
 namespace icb {
@@ -53,6 +55,7 @@ struct GemmArgs {
   const int* ag_epoch_ptr;          // device word: calls completed so far on this workspace (this call = +1)
   int ag_chunks_per_block;          // 8 KiB chunks in one 128-row block
   uint8_t* ag_mc;                   // multicast (NVLS) address of the gathered buffer, or null: plain P2P stores
+  int ag_batch;                     // chunks a copy warp pushes between two fence + publish steps (1..16)
 };
 
 constexpr int kAgChunkBytes = 8192;  // copy granularity of the all-gather (one warp iteration)
@@ -443,7 +446,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         int done_rb[kAgBatch];
         int n_done = 0;
 #pragma unroll 1
-        for (; c < chunks_per_shard && n_done < kAgBatch; c += n_cw) {
+        for (; c < chunks_per_shard && n_done < args.ag_batch; c += n_cw) {
           const long long off = (long long)args.ag_rank * shard_bytes + (long long)c * kAgChunkBytes;
           const uint4* src = reinterpret_cast<const uint4*>(args.ag_local + off);
           uint4* dst = reinterpret_cast<uint4*>(args.ag_mc + off);
@@ -459,7 +462,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         for (int p = lane; p < args.ag_world - 1; p += 32) {
           const int q = (args.ag_rank + 1 + p) % args.ag_world;
           __threadfence_system();
-          for (int i = 0; i < n_done; ++i) red_release_sys_add(args.ag_peer_ready[q] + done_rb[i], 1);
+          for (int i = 0; i < n_done; ++i) red_relaxed_sys_add(args.ag_peer_ready[q] + done_rb[i], 1);
         }
         __syncwarp();
       }
@@ -470,7 +473,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         int done_q[kAgBatch], done_rb[kAgBatch];
         int n_done = 0;
 #pragma unroll 1
-        for (; c < total_chunks && n_done < kAgBatch; c += n_cw) {
+        for (; c < total_chunks && n_done < args.ag_batch; c += n_cw) {
           const int step = c / chunks_per_shard + 1;
           const int within = c - (step - 1) * chunks_per_shard;
           const int q = (args.ag_rank + step) % args.ag_world;
@@ -489,7 +492,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         __syncwarp();
         if (lane == 0) {
           __threadfence_system();
-          for (int i = 0; i < n_done; ++i) red_release_sys_add(args.ag_peer_ready[done_q[i]] + done_rb[i], 1);
+          for (int i = 0; i < n_done; ++i) red_relaxed_sys_add(args.ag_peer_ready[done_q[i]] + done_rb[i], 1);
         }
         __syncwarp();
       }
@@ -597,7 +600,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, co
     args.ag_rank = 0; args.ag_world = 1; args.ag_rows_per_rank = 0; args.ag_row_bytes = 0;
     args.ag_local = nullptr; args.ag_peers = nullptr; args.ag_peer_signal = nullptr; args.ag_signal = nullptr;
     args.ag_ready = nullptr; args.ag_epoch_ptr = nullptr; args.ag_chunks_per_block = 1; args.ag_peer_ready = nullptr;
-    args.ag_mc = nullptr;
+    args.ag_mc = nullptr; args.ag_batch = 16;
   }
   args.M = M; args.N = N; args.K = K;
   args.num_m_tiles = (M + kBM - 1) / kBM;
@@ -669,6 +672,17 @@ ICB_API int icb_ag_gemm(void* gathered, const void* const* peers, int* const* pe
   ag.ag_ready = ready;
   ag.ag_epoch_ptr = epoch_ptr;
   ag.ag_mc = reinterpret_cast<uint8_t*>(gathered_mc);
+  {
+    // Publishing granularity: fewer chunks per fence make the first remote tiles ready earlier, more chunks
+    // amortise the system-scope fence. ICB_AG_BATCH overrides the default for experiments.
+    static int batch = -1;
+    if (batch < 0) {
+      const char* e = getenv("ICB_AG_BATCH");
+      int v = e != nullptr ? atoi(e) : 0;
+      batch = (v >= 1 && v <= 16) ? v : 0;
+    }
+    ag.ag_batch = batch > 0 ? batch : 16;
+  }
   ag.ag_chunks_per_block = (int)(128LL * width * 2 / kAgChunkBytes);
   const int rows = world * rows_per_rank;
   const int M = a_major == 0 ? rows : width;

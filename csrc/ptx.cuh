@@ -334,6 +334,11 @@ __device__ __forceinline__ uint4 multimem_ld_reduce_f16x8(const void* mc) {
                : "memory");
   return v;
 }
+// Relaxed form: publishes nothing by itself; a preceding fence.acq_rel.sys (__threadfence_system) by the same
+// thread makes the pair a release. One fence can cover many of these, a release per counter cannot.
+__device__ __forceinline__ void red_relaxed_sys_add(int* p, int v) {
+  asm volatile("red.relaxed.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
   asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }

@@ -25,6 +25,7 @@ def main():
     ap.add_argument("--width", type=int, default=4096)
     ap.add_argument("--ffn", type=int, default=11008)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--cases", default="", help="comma-separated case names to run (default: all)")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -119,7 +120,10 @@ def main():
         flops = 2.0 * t * d * k_local
         wire = (world - 1) * rows * d * 2
         cases.append((name, "gemm_rs", fused, nccl, gemm_only, flops, wire))
+    wanted = {c for c in args.cases.split(",") if c}
     for name, kind, fused, nccl, gemm_only, flops, wire in cases:
+        if wanted and name not in wanted:
+            continue
         ref = nccl().float()
         err = max(float((fused(ws=w_).float() - ref).abs().max()) for w_ in {id(ws): ws, id(ws_p2p): ws_p2p}.values())
         scale = float(ref.abs().max())
@@ -129,7 +133,7 @@ def main():
         tg = timeit(gemm_only)
         roof_ms = max(flops / (peak_tflops * 1e9), wire / (link_gbs * 1e6))
         if rank == 0:
-            print(json.dumps({"case": name, "kind": kind, "world": world, "nvls": ws.nvls, "fused_ms": tf,
+            print(json.dumps({"case": name, "kind": kind, "world": world, "nvls": ws.nvls, "ag_batch": os.environ.get("ICB_AG_BATCH", "default"), "fused_ms": tf,
                               "fused_p2p_ms": tp, "max_abs_err_vs_nccl": err, "ref_abs_max": scale, "nccl_plus_gemm_ms": tn,
                               "gemm_only_ms": tg, "roofline_ms": roof_ms, "fraction_of_roofline": roof_ms / tf,
                               "wire_mb": wire / 1e6, "gflop": flops / 1e9}), flush=True)
