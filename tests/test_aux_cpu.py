@@ -203,3 +203,34 @@ def test_gpt2_loss_curve_matches_reference_cpu():
     res = json.loads(out.stdout.strip().splitlines()[-1])
     assert res["missing_in_ours"] == [] and res["not_in_ours"] == []
     assert res["max_abs_diff"] < 1e-4, res
+
+
+def test_examples_run_on_cpu(tmp_path):
+    """The flag-driven training example and the text-generation example run end to end on CPU."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_PORT"):
+        env.pop(k, None)
+    flags = ("--model_name tiny --name llama --d_model 64 --d_ffn 128 --num_layers 2 --num_attention_heads 4 "
+             "--max_seq_len 32 --max_position_embeddings 32 --precision fp32 --ln_type rmsnorm --activation_type swiglu "
+             "--task_type synthetic --vocab_size 512 --train_steps 2 --no_save true --micro_batch_size 2 "
+             "--train_batch_size 4 --log_interval 1 --dist_backend gloo").split()
+    out = subprocess.run([sys.executable, os.path.join(root, "examples", "train.py"), *flags], cwd=tmp_path, env=env,
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "step      2" in out.stdout + out.stderr
+    cfg = tmp_path / "gen.yaml"
+    cfg.write_text("trainer: {micro_batch_size: 1, train_batch_size: 1, model_path: ''}\noperation: {no_save: true}\n"
+                   "model: {name: llama, d_model: 64, d_ffn: 128, num_layers: 2, num_attention_heads: 4, max_seq_len: 64,\n"
+                   "  max_position_embeddings: 64, precision: fp32, ln_type: rmsnorm, activation_type: swiglu, vocab_size: 300,\n"
+                   "  tokenizer_type: byte, vocab_name_or_path: none, positional_embedding: {type: rope}}\n"
+                   "data: {task_type: synthetic, vocab_size: 300}\nparallel: {dist_backend: gloo}\n")
+    out = subprocess.run([sys.executable, os.path.join(root, "examples", "generate_text.py"), "--config", str(cfg),
+                          "--prompt", "hello", "--max-new-tokens", "6"], cwd=tmp_path, env=env, capture_output=True,
+                         text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "--- sample 0 ---" in out.stdout
