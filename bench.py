@@ -244,7 +244,7 @@ def run_ours(args):
 
 
 def _published_baseline():
-    """BASELINE.md publishes no tokens/s figure for this model/config on any hardware."""
+    """The reference publishes no tokens/s figure for this model and configuration on any hardware."""
     return None
 
 

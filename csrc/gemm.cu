@@ -56,6 +56,7 @@ struct GemmArgs {
   int ag_chunks_per_block;          // 8 KiB chunks in one 128-row block
   uint8_t* ag_mc;                   // multicast (NVLS) address of the gathered buffer, or null: plain P2P stores
   int ag_batch;                     // chunks a copy warp pushes between two fence + publish steps (1..16)
+  unsigned long long* ag_debug;     // optional [grid][4] timestamps (ns): start, push done, first remote block ready, end
 };
 
 constexpr int kAgChunkBytes = 8192;  // copy granularity of the all-gather (one warp iteration)
@@ -126,10 +127,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       // Row blocks already seen complete: a system-scope acquire costs about a microsecond, far more
       // than the few hundred nanoseconds of work the 4-stage ring buffers, so each block is polled once.
       unsigned long long ag_seen = 0ull;
+      if (AG && args.ag_debug != nullptr) args.ag_debug[blockIdx.x * 4 + 0] = globaltimer_ns();
       auto ag_ensure_ready = [&](int rb) {
         if (rb < 64 && ((ag_seen >> rb) & 1ull)) return;
         wait_flag_sys(args.ag_ready + rb, ag_epoch * args.ag_chunks_per_block, args.status, kTimeoutPeerFlag);
         fence_proxy_async_all();
+        if (args.ag_debug != nullptr && ag_seen == 0ull) args.ag_debug[blockIdx.x * 4 + 2] = globaltimer_ns();
         if (rb < 64) ag_seen |= (1ull << rb);
       };
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
@@ -499,6 +502,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
   }
 
+  if (AG && args.ag_debug != nullptr) {
+    if (warp == 6 && lane == 0) args.ag_debug[blockIdx.x * 4 + 1] = globaltimer_ns();
+    if (warp == 2 && lane == 0) args.ag_debug[blockIdx.x * 4 + 3] = globaltimer_ns();
+  }
   // Drain: nobody may exit while TMEM is allocated or copies are in flight.
   tc_fence_before();
   __syncthreads();
@@ -600,7 +607,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, co
     args.ag_rank = 0; args.ag_world = 1; args.ag_rows_per_rank = 0; args.ag_row_bytes = 0;
     args.ag_local = nullptr; args.ag_peers = nullptr; args.ag_peer_signal = nullptr; args.ag_signal = nullptr;
     args.ag_ready = nullptr; args.ag_epoch_ptr = nullptr; args.ag_chunks_per_block = 1; args.ag_peer_ready = nullptr;
-    args.ag_mc = nullptr; args.ag_batch = 16;
+    args.ag_mc = nullptr; args.ag_batch = 4; args.ag_debug = nullptr;
   }
   args.M = M; args.N = N; args.K = K;
   args.num_m_tiles = (M + kBM - 1) / kBM;
@@ -639,6 +646,14 @@ ICB_API int icb_gemm(const void* A, const void* B, void* C, const void* bias, co
                      long long b_group_stride, int* status, int max_ctas, void* stream_) {
   return gemm_impl(A, B, C, bias, residual, M, N, K, lda, ldb, ldc, ldr, a_major, b_major, in_dtype, out_f32,
                    group_mode, num_groups, group_table, b_group_stride, status, max_ctas, stream_, nullptr);
+}
+
+// Optional instrumentation of the fused all-gather kernels: a device buffer of [148][4] 64-bit nanosecond
+// timestamps per CTA (producer start, copy warps done, first remote row block ready, epilogue done); null = off.
+static unsigned long long* g_ag_debug = nullptr;
+ICB_API int icb_set_ag_debug(void* buf) {
+  g_ag_debug = reinterpret_cast<unsigned long long*>(buf);
+  return 0;
 }
 
 // Fused all-gather -> GEMM over a tensor-parallel group (sequence parallelism).
@@ -681,8 +696,9 @@ ICB_API int icb_ag_gemm(void* gathered, const void* const* peers, int* const* pe
       int v = e != nullptr ? atoi(e) : 0;
       batch = (v >= 1 && v <= 16) ? v : 0;
     }
-    ag.ag_batch = batch > 0 ? batch : 16;
+    ag.ag_batch = batch > 0 ? batch : 4;
   }
+  ag.ag_debug = g_ag_debug;
   ag.ag_chunks_per_block = (int)(128LL * width * 2 / kAgChunkBytes);
   const int rows = world * rows_per_rank;
   const int M = a_major == 0 ? rows : width;

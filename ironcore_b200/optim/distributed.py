@@ -259,7 +259,9 @@ class DistributedOptimizer:
             return
         if self.zero:
             lo, hi = g.shard_range(True)
-            if g.device.type == "cpu":
+            # Muon owners need the whole gradient of their matrices, which lie outside their Adam shard:
+            # with Muon the buffer is all-reduced (the optimizer state stays sharded either way).
+            if g.device.type == "cpu" or self.use_muon:
                 dist.all_reduce(g.grad_buf, group=g.reduce_group)
             else:
                 dist.reduce_scatter_tensor(g.grad_buf[lo:hi], g.grad_buf, group=g.reduce_group)

@@ -25,6 +25,7 @@ def main():
     ap.add_argument("--width", type=int, default=4096)
     ap.add_argument("--ffn", type=int, default=11008)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--trace", action="store_true", help="per-CTA timestamps of the fused all-gather kernel")
     ap.add_argument("--cases", default="", help="comma-separated case names to run (default: all)")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -127,6 +128,29 @@ def main():
         ref = nccl().float()
         err = max(float((fused(ws=w_).float() - ref).abs().max()) for w_ in {id(ws): ws, id(ws_p2p): ws_p2p}.values())
         scale = float(ref.abs().max())
+        if args.trace and kind.startswith("ag_gemm"):
+            native.register("icb_set_ag_debug", [native.P])
+            dbg = torch.zeros(148 * 4, dtype=torch.int64, device="cuda")
+            for w_ in ({id(ws): ws, id(ws_p2p): ws_p2p}.values()):
+                for _ in range(3):
+                    fused(ws=w_)
+                torch.cuda.synchronize()
+                flush.zero_()
+                dist.barrier()
+                torch.cuda.synchronize()
+                native.call("icb_set_ag_debug", dbg.data_ptr())
+                fused(ws=w_)
+                torch.cuda.synchronize()
+                native.call("icb_set_ag_debug", None)
+                t = dbg.view(148, 4).cpu().double()
+                t0 = t[:, 0].min()
+                def stat(col):
+                    v = (t[:, col][t[:, col] > 0] - t0) / 1e3
+                    return [round(float(v.min()), 1), round(float(v.median()), 1), round(float(v.max()), 1)] if v.numel() else None
+                print(json.dumps({"trace": name, "rank": rank, "nvls_ag": w_.nvls_ag, "us_since_first_cta_start": {
+                    "cta_start": stat(0), "push_done": stat(1), "first_remote_block_ready": stat(2), "epilogue_done": stat(3)}}),
+                    flush=True)
+                dbg.zero_()
         tf = timeit(fused)
         tp = timeit(lambda: fused(ws=ws_p2p)) if ws_p2p is not ws else tf
         tn = timeit(nccl)
