@@ -11,14 +11,19 @@
 // while the softmax of the current one runs. The accumulator is only rescaled when
 // the running max grows by more than 2^8 (exact: the final normalisation uses the
 // same reference max), which keeps TMEM read-modify-write off the steady state.
+// Two tilings: BN = 128 key rows per step with one CTA per SM (double-buffered P), and BN = 64 with two
+// CTAs per SM (half the shared memory and TMEM each, single P buffer): two independent pipelines per SM
+// give every warp scheduler two softmax warps, which hides the latency of the row-wise exp / max / sum
+// chain that one warp per scheduler cannot.
 // Every wait is bounded; on timeout the status word is set and the CTA drains.
+#include <cstdlib>
+
 #include "host_common.h"
 #include "ptx.cuh"
 
 namespace icb {
 
 constexpr int kFaThreads = 192;
-constexpr int kFaTmemCols = 512;
 
 struct FlashFwdArgs {
   int batch, seq_len, hq, hkv;        // seq_len: tokens per sequence (max when cu_seqlens is used)
@@ -38,27 +43,39 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-template <int HD>
+template <int HD, int BN>
 struct FaSmem {
   static constexpr int kChunks = HD / 64;            // 64-element (128 B) column chunks per row
+  static constexpr int kPStages = BN == 128 ? 2 : 1;
   static constexpr int q_bytes = 128 * HD * 2;
-  static constexpr int kv_bytes = 128 * HD * 2;
-  static constexpr int p_bytes = 128 * 128 * 2;
+  static constexpr int kv_bytes = BN * HD * 2;
+  static constexpr int kv_chunk = BN * 128;          // bytes of one 64-column chunk of a K / V tile
+  static constexpr int p_bytes = 128 * BN * 2;
   static constexpr int q_off = 0;
   static constexpr int k_off = q_off + q_bytes;
   static constexpr int v_off = k_off + 2 * kv_bytes;
   static constexpr int p_off = v_off + 2 * kv_bytes;
-  static constexpr int bar_off = p_off + 2 * p_bytes;
-  static constexpr int total = bar_off + 256 + 1024;
+  static constexpr int bar_off = p_off + kPStages * p_bytes;
+  // BN = 128: manual 1 KiB alignment slack. BN = 64: the declaration is 1 KiB aligned (checked in the
+  // kernel), so that two CTAs fit into one SM's shared memory.
+  static constexpr int total = bar_off + 256 + (BN == 128 ? 1024 : 0);
+  static constexpr int tmem_cols = BN == 128 ? 512 : 256;
+  static constexpr int tmem_o = 2 * BN;
 };
 
-template <int HD>
-__global__ void __launch_bounds__(kFaThreads, 1)
+template <int HD, int BN>
+__global__ void __launch_bounds__(kFaThreads, BN == 128 ? 1 : 2)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FlashFwdArgs args) {
-  using L = FaSmem<HD>;
-  extern __shared__ uint8_t smem_raw[];
+  using L = FaSmem<HD, BN>;
+  constexpr int PS = L::kPStages;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  if (BN != 128 && smem != smem_raw) {
+    // the two-CTA layout has no room for alignment slack
+    if (threadIdx.x == 0 && args.status != nullptr) atomicCAS(args.status, 0, kBadArgument);
+    return;
+  }
   uint8_t* sQ = smem + L::q_off;
   uint8_t* sK = smem + L::k_off;
   uint8_t* sV = smem + L::v_off;
@@ -95,8 +112,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;
   if (qt >= num_q_tiles) return;
   const int q0 = qt * 128;
-  const int n_kv_total = (seq_len + 127) >> 7;
-  const int n_kv = args.causal ? min(qt + 1, n_kv_total) : n_kv_total;
+  const int n_kv_total = (seq_len + BN - 1) / BN;
+  const int n_kv = args.causal ? min((q0 + 128 + BN - 1) / BN, n_kv_total) : n_kv_total;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -117,14 +134,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tma_prefetch_desc(&tmV);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, kFaTmemCols);
+    tmem_alloc(tmem_slot, L::tmem_cols);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 256;
+  const uint32_t tmem_o = tmem_base + L::tmem_o;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -134,23 +151,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int j = 0; j < n_kv; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        const int t0 = seq_start + j * 128;
+        const int t0 = seq_start + j * BN;
         mbar_wait(&k_empty[s], ph ^ 1, abort_flag, args.status, kTimeoutSmemEmpty);
         mbar_expect_tx(&k_full[s], L::kv_bytes);
 #pragma unroll
         for (int c = 0; c < L::kChunks; ++c)
-          tma_load_3d(sK + s * L::kv_bytes + c * 16384, &tmK, &k_full[s], c * 64, kv_head, t0);
+          tma_load_3d(sK + s * L::kv_bytes + c * L::kv_chunk, &tmK, &k_full[s], c * 64, kv_head, t0);
         mbar_wait(&v_empty[s], ph ^ 1, abort_flag, args.status, kTimeoutSmemEmpty);
         mbar_expect_tx(&v_full[s], L::kv_bytes);
 #pragma unroll
         for (int c = 0; c < L::kChunks; ++c)
-          tma_load_3d(sV + s * L::kv_bytes + c * 16384, &tmV, &v_full[s], c * 64, kv_head, t0);
+          tma_load_3d(sV + s * L::kv_bytes + c * L::kv_chunk, &tmV, &v_full[s], c * 64, kv_head, t0);
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc_s = umma_idesc(128, 128, args.in_fmt, 0, 0);
+      const uint32_t idesc_s = umma_idesc(128, BN, args.in_fmt, 0, 0);
       const uint32_t idesc_pv = umma_idesc(128, HD, args.in_fmt, 0, 1);
       const uint32_t q_addr = smem_u32(sQ);
       auto issue_s = [&](int j) {
@@ -158,9 +175,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t k_addr = smem_u32(sK + s * L::kv_bytes);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-          umma_ss(tmem_base + s * 128, umma_desc_sw128(q_addr + off, 16, 1024), umma_desc_sw128(k_addr + off, 16, 1024),
-                  idesc_s, k > 0 ? 1u : 0u);
+          const uint32_t q_off = (k >> 2) * 16384 + (k & 3) * 32;
+          const uint32_t k_off = (k >> 2) * L::kv_chunk + (k & 3) * 32;
+          umma_ss(tmem_base + s * BN, umma_desc_sw128(q_addr + q_off, 16, 1024),
+                  umma_desc_sw128(k_addr + k_off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[s]);
         umma_commit(&k_empty[s]);
@@ -180,18 +198,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tc_fence_after();
           issue_s(j + 1);
         }
+        const int sp = j % PS;
+        const uint32_t php = (j / PS) & 1;
         mbar_wait(&v_full[s], ph, abort_flag, args.status, kTimeoutSmemFull);
-        mbar_wait(&p_full[s], ph, abort_flag, args.status, kTimeoutLocalFlag);
+        mbar_wait(&p_full[sp], php, abort_flag, args.status, kTimeoutLocalFlag);
         tc_fence_after();
-        const uint32_t p_addr = smem_u32(sP + s * L::p_bytes);
+        const uint32_t p_addr = smem_u32(sP + sp * L::p_bytes);
         const uint32_t v_addr = smem_u32(sV + s * L::kv_bytes);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int k = 0; k < BN / 16; ++k) {
           const uint64_t adesc = umma_desc_sw128(p_addr + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
-          const uint64_t bdesc = umma_desc_sw128(v_addr + k * 2048, 16384, 1024);
+          const uint64_t bdesc = umma_desc_sw128(v_addr + k * 2048, L::kv_chunk, 1024);
           umma_ss(tmem_o, adesc, bdesc, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
         }
-        umma_commit(&p_empty[s]);
+        umma_commit(&p_empty[sp]);
         umma_commit(&v_empty[s]);
       }
     }
@@ -209,17 +229,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t ph = (j >> 1) & 1;
       mbar_wait(&s_full[s], ph, abort_flag, args.status, kTimeoutTmemFull);
       tc_fence_after();
-      uint32_t r[4][32];
+      constexpr int NC = BN / 32;
+      uint32_t r[NC][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_base + lane_off + s * 128 + c * 32, r[c]);
+      for (int c = 0; c < NC; ++c) tmem_ld_32x32(tmem_base + lane_off + s * BN + c * 32, r[c]);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&s_empty[s]);
-      const int kv0 = j * 128;
-      const bool need_mask = (args.causal && j == qt) || (kv0 + 128 > seq_len);
+      const int kv0 = j * BN;
+      const bool need_mask = (args.causal && kv0 + BN > q0) || (kv0 + BN > seq_len);
       float m_tile = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < NC; ++c) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           float x = __uint_as_float(r[c][i]) * args.scale_log2;
@@ -243,8 +264,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         if (j > 0) {
           // the accumulator must be complete up to P_{j-1} V_{j-1} before it is rescaled
-          const int sp = (j - 1) & 1;
-          mbar_wait(&p_empty[sp], ((j - 1) >> 1) & 1, abort_flag, args.status, kTimeoutTmemFull);
+          const int spp = (j - 1) % PS;
+          mbar_wait(&p_empty[spp], ((j - 1) / PS) & 1, abort_flag, args.status, kTimeoutTmemFull);
           tc_fence_after();
 #pragma unroll
           for (int c = 0; c < HD / 32; ++c) {
@@ -259,12 +280,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tc_fence_before();
         }
       }
-      // P buffer s was last read by P_{j-2} V_{j-2}
-      if (j >= 2) mbar_wait(&p_empty[s], ph ^ 1, abort_flag, args.status, kTimeoutLocalFlag);
-      uint8_t* prow = sP + s * L::p_bytes + row * 128;
+      // P buffer sp was last read by P_{j-PS} V_{j-PS}
+      const int sp = j % PS;
+      const uint32_t php = (j / PS) & 1;
+      if (j >= PS) mbar_wait(&p_empty[sp], php ^ 1, abort_flag, args.status, kTimeoutLocalFlag);
+      uint8_t* prow = sP + sp * L::p_bytes + row * 128;
       float lsum_tile = 0.f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < NC; ++c) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           float p[8];
@@ -289,12 +312,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       l_sum += lsum_tile;
       fence_proxy_async_smem();
-      mbar_arrive(&p_full[s]);
+      mbar_arrive(&p_full[sp]);
     }
     // ---- epilogue: O / l, log-sum-exp ----
     {
       const int last = n_kv - 1;
-      mbar_wait(&p_empty[last & 1], (last >> 1) & 1, abort_flag, args.status, kTimeoutTmemFull);
+      mbar_wait(&p_empty[last % PS], (last / PS) & 1, abort_flag, args.status, kTimeoutTmemFull);
       tc_fence_after();
       const float inv_l = l_sum > 0.f ? 1.0f / l_sum : 0.f;
       const bool valid = q_idx < seq_len;
@@ -336,31 +359,46 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kFaTmemCols);
+    tmem_dealloc(tmem_base, L::tmem_cols);
   }
 }
 
-template <int HD>
+template <int HD, int BN>
 static int launch_flash_fwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
                             const FlashFwdArgs& args, dim3 grid, cudaStream_t stream) {
   static bool configured = false;
-  auto kern = flash_fwd_kernel<HD>;
+  auto kern = flash_fwd_kernel<HD, BN>;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSmem<HD>::total);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSmem<HD, BN>::total);
     if (e != cudaSuccess) return -(int)e;
     configured = true;
   }
-  kern<<<grid, kFaThreads, FaSmem<HD>::total, stream>>>(tmQ, tmK, tmV, args);
+  kern<<<grid, kFaThreads, FaSmem<HD, BN>::total, stream>>>(tmQ, tmK, tmV, args);
   return check_launch("flash_fwd_kernel");
 }
 
 // 3-D view (head_dim, heads, tokens) of a [T, row_stride] matrix whose heads start at `base`.
-int make_head_tmap(CUtensorMap* tm, const void* base, int hd, int heads, long long tokens, long long row_stride,
-                   int dtype) {
+int make_head_tmap_rows(CUtensorMap* tm, const void* base, int hd, int heads, long long tokens, long long row_stride,
+                        int dtype, int box_rows) {
   uint64_t dims[3] = {(uint64_t)hd, (uint64_t)heads, (uint64_t)tokens};
   uint64_t str[2] = {(uint64_t)hd * 2, (uint64_t)row_stride * 2};
-  uint32_t box[3] = {64, 1, 128};
+  uint32_t box[3] = {64, 1, (uint32_t)box_rows};
   return make_tmap(tm, dtype, 3, base, dims, str, box, true);
+}
+int make_head_tmap(CUtensorMap* tm, const void* base, int hd, int heads, long long tokens, long long row_stride,
+                   int dtype) {
+  return make_head_tmap_rows(tm, base, hd, heads, tokens, row_stride, dtype, 128);
+}
+
+// Key rows per step: 128 (one CTA per SM) or 64 (two CTAs per SM). ICB_FLASH_BN overrides the default.
+static int flash_fwd_bn() {
+  static int bn = 0;
+  if (bn == 0) {
+    const char* e = getenv("ICB_FLASH_BN");
+    const int v = e != nullptr ? atoi(e) : 0;
+    bn = (v == 64 || v == 128) ? v : 128;
+  }
+  return bn;
 }
 
 }  // namespace icb
@@ -380,9 +418,10 @@ ICB_API int icb_flash_fwd(const void* q, const void* k, const void* v, void* out
   CUtensorMap tmQ, tmK, tmV;
   int rc = make_head_tmap(&tmQ, q, hd, hq, total_tokens, q_stride, dtype);
   if (rc) return rc;
-  rc = make_head_tmap(&tmK, k, hd, hkv, total_tokens, kv_stride, dtype);
+  const int bn = flash_fwd_bn();
+  rc = make_head_tmap_rows(&tmK, k, hd, hkv, total_tokens, kv_stride, dtype, bn);
   if (rc) return rc;
-  rc = make_head_tmap(&tmV, v, hd, hkv, total_tokens, kv_stride, dtype);
+  rc = make_head_tmap_rows(&tmV, v, hd, hkv, total_tokens, kv_stride, dtype, bn);
   if (rc) return rc;
   FlashFwdArgs a;
   a.batch = batch; a.seq_len = seq_len; a.hq = hq; a.hkv = hkv;
@@ -393,6 +432,10 @@ ICB_API int icb_flash_fwd(const void* q, const void* k, const void* v, void* out
   a.in_fmt = (dtype == kBF16) ? 1 : 0;
   a.status = status;
   dim3 grid((seq_len + 127) / 128, hq, batch);
-  if (hd == 64) return launch_flash_fwd<64>(tmQ, tmK, tmV, a, grid, stream);
-  return launch_flash_fwd<128>(tmQ, tmK, tmV, a, grid, stream);
+  if (bn == 64) {
+    if (hd == 64) return launch_flash_fwd<64, 64>(tmQ, tmK, tmV, a, grid, stream);
+    return launch_flash_fwd<128, 64>(tmQ, tmK, tmV, a, grid, stream);
+  }
+  if (hd == 64) return launch_flash_fwd<64, 128>(tmQ, tmK, tmV, a, grid, stream);
+  return launch_flash_fwd<128, 128>(tmQ, tmK, tmV, a, grid, stream);
 }

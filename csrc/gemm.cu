@@ -69,7 +69,7 @@ __device__ __forceinline__ int ag_rotate(int seq, int per_shard, int rank, int w
   return owner * per_shard + (seq - s * per_shard);
 }
 
-template <int A_MAJOR, int B_MAJOR, bool AG>
+template <int A_MAJOR, int B_MAJOR, bool AG, int BN>
 __global__ void __launch_bounds__(AG ? kGemmThreads + 64 : kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const GemmArgs args) {
@@ -155,7 +155,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           mt = ag_rotate(mt, ag_mtiles_per_shard, args.ag_rank, args.ag_world);
           if (mt / ag_mtiles_per_shard != args.ag_rank) ag_ensure_ready(mt);
         }
-        const int m0 = mt * kBM, n0 = nt * kBN;
+        const int m0 = mt * kBM, n0 = nt * BN;
         const int bz = (args.group_mode == 1) ? grp : 0;
         for (int kseq = k_begin; kseq < k_end; kseq += kBK, ++it) {
           int k0 = kseq;
@@ -170,7 +170,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, args.status, kTimeoutSmemEmpty);
-          mbar_expect_tx(&full_bar[s], kAStageBytes + kBStageBytes);
+          mbar_expect_tx(&full_bar[s], kAStageBytes + BN * kBK * 2);
           uint8_t* sa = smem_a + s * kAStageBytes;
           uint8_t* sb = smem_b + s * kBStageBytes;
           if (A_MAJOR == 0) {
@@ -183,7 +183,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             tma_load_3d(sb, &tmB, &full_bar[s], k0, n0, bz);
           } else {
 #pragma unroll
-            for (int c = 0; c < kBN / 64; ++c) tma_load_3d(sb + c * 8192, &tmB, &full_bar[s], n0 + c * 64, k0, bz);
+            for (int c = 0; c < BN / 64; ++c) tma_load_3d(sb + c * 8192, &tmB, &full_bar[s], n0 + c * 64, k0, bz);
           }
         }
       }
@@ -192,7 +192,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc(kBM, kBN, args.in_fmt, A_MAJOR, B_MAJOR);
+      const uint32_t idesc = umma_idesc(kBM, BN, args.in_fmt, A_MAJOR, B_MAJOR);
       uint32_t it = 0, tcount = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         int k_begin = 0, k_end = args.K;
@@ -213,7 +213,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const uint32_t acc_ph = (tcount >> 1) & 1;
         mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, args.status, kTimeoutTmemEmpty);
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + acc * kBN;
+        const uint32_t tmem_d = tmem_base + acc * BN;
         uint32_t first = 1;
         for (int k0 = k_begin; k0 < k_end; k0 += kBK, ++it) {
           const int s = it % kStages;
@@ -263,7 +263,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       if (AG && A_MAJOR == 0) mt = ag_rotate(mt, ag_mtiles_per_shard, args.ag_rank, args.ag_world);
       const bool empty_k = (k_end <= k_begin);
-      const int m0 = mt * kBM, n0 = nt * kBN;
+      const int m0 = mt * kBM, n0 = nt * BN;
       const uint32_t acc = tcount & 1;
       const uint32_t acc_ph = (tcount >> 1) & 1;
       if (!empty_k) {
@@ -278,7 +278,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         bias_base = reinterpret_cast<const uint8_t*>(args.bias) + (args.group_mode == 1 ? (size_t)grp * args.N * 2 : 0);
 
 #pragma unroll 1
-      for (int sub = 0; sub < kBN / 32; ++sub) {
+      for (int sub = 0; sub < BN / 32; ++sub) {
         const int col0 = sub * 32;
         const int slab_sub = (esz == 2) ? (sub & 1) : 0;
         const bool slab_start = (slab_sub == 0);
@@ -290,13 +290,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         uint32_t r[32];
         if (!empty_k) {
-          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN + col0, r);
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + col0, r);
           tmem_ld_wait();
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-        if (sub == kBN / 32 - 1 && !empty_k) {
+        if (sub == BN / 32 - 1 && !empty_k) {
           tc_fence_before();
           mbar_arrive(&tempty_bar[acc]);
         }
@@ -521,11 +521,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   }
 }
 
-template <int A_MAJOR, int B_MAJOR, bool AG = false>
-static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const GemmArgs& args,
-                       int grid, cudaStream_t stream) {
+template <int A_MAJOR, int B_MAJOR, bool AG, int BN>
+static int launch_gemm_bn(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const GemmArgs& args,
+                          int grid, cudaStream_t stream) {
   static bool configured = false;
-  auto kern = gemm_kernel<A_MAJOR, B_MAJOR, AG>;
+  auto kern = gemm_kernel<A_MAJOR, B_MAJOR, AG, BN>;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
     if (e != cudaSuccess) {
@@ -536,6 +536,29 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   }
   kern<<<grid, AG ? kGemmThreads + 64 : kGemmThreads, kGemmSmemBytes, stream>>>(tmA, tmB, tmC, args);
   return check_launch("gemm_kernel");
+}
+template <int A_MAJOR, int B_MAJOR, bool AG = false>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const GemmArgs& args,
+                       int grid, cudaStream_t stream, int bn) {
+  if (bn == 128) return launch_gemm_bn<A_MAJOR, B_MAJOR, AG, 128>(tmA, tmB, tmC, args, grid, stream);
+  return launch_gemm_bn<A_MAJOR, B_MAJOR, AG, 256>(tmA, tmB, tmC, args, grid, stream);
+}
+
+// Tile width for a problem: 256 columns keep the tensor core fed best, but a grid of few tiles leaves a
+// ragged last wave on 148 SMs; 128-column tiles cost roughly a quarter more per flop (less operand reuse) and halve the quantum.
+static int pick_bn(long long m_tiles, int N, int groups, int sms) {
+  static int forced = -1;
+  if (forced < 0) {
+    const char* e = getenv("ICB_GEMM_BN");
+    const int v = e != nullptr ? atoi(e) : 0;
+    forced = (v == 128 || v == 256) ? v : 0;
+  }
+  if (forced) return forced;
+  const long long t256 = m_tiles * ((N + 255) / 256) * groups;
+  const long long t128 = m_tiles * ((N + 127) / 128) * groups;
+  const double c256 = (double)((t256 + sms - 1) / sms);
+  const double c128 = (double)((t128 + sms - 1) / sms) * 0.62;
+  return (c128 < c256 * 0.97) ? 128 : 256;
 }
 
 }  // namespace icb
@@ -564,6 +587,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, co
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -5;
   if (num_groups < 1) num_groups = 1;
 
+  const int bn = pick_bn((M + kBM - 1) / kBM, N, group_mode == 2 ? num_groups : 1, num_sms());
   CUtensorMap tmA, tmB, tmC;
   int rc;
   const uint64_t k_rows = (uint64_t)K;
@@ -583,7 +607,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, co
   if (b_major == 0) {
     uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, bgroups};
     uint64_t str[2] = {(uint64_t)ldb * es, (uint64_t)(group_mode == 1 ? b_group_stride : (long long)N * ldb) * es};
-    uint32_t box[3] = {64, (uint32_t)kBN, 1};
+    uint32_t box[3] = {64, (uint32_t)bn, 1};
     rc = make_tmap(&tmB, in_dtype, 3, B, dims, str, box, true);
   } else {
     uint64_t dims[3] = {(uint64_t)N, k_rows, bgroups};
@@ -611,7 +635,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, co
   }
   args.M = M; args.N = N; args.K = K;
   args.num_m_tiles = (M + kBM - 1) / kBM;
-  args.num_n_tiles = (N + kBN - 1) / kBN;
+  args.num_n_tiles = (N + bn - 1) / bn;
   args.num_groups = num_groups;
   args.group_mode = group_mode;
   args.group_table = group_table;
@@ -629,15 +653,15 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, co
   if (grid < 1) grid = 1;
 
   if (ag != nullptr) {
-    if (a_major == 0 && b_major == 0) return launch_gemm<0, 0, true>(tmA, tmB, tmC, args, grid, stream);
-    if (a_major == 0 && b_major == 1) return launch_gemm<0, 1, true>(tmA, tmB, tmC, args, grid, stream);
-    if (a_major == 1 && b_major == 1) return launch_gemm<1, 1, true>(tmA, tmB, tmC, args, grid, stream);
+    if (a_major == 0 && b_major == 0) return launch_gemm<0, 0, true>(tmA, tmB, tmC, args, grid, stream, bn);
+    if (a_major == 0 && b_major == 1) return launch_gemm<0, 1, true>(tmA, tmB, tmC, args, grid, stream, bn);
+    if (a_major == 1 && b_major == 1) return launch_gemm<1, 1, true>(tmA, tmB, tmC, args, grid, stream, bn);
     return -6;
   }
-  if (a_major == 0 && b_major == 0) return launch_gemm<0, 0>(tmA, tmB, tmC, args, grid, stream);
-  if (a_major == 0 && b_major == 1) return launch_gemm<0, 1>(tmA, tmB, tmC, args, grid, stream);
-  if (a_major == 1 && b_major == 0) return launch_gemm<1, 0>(tmA, tmB, tmC, args, grid, stream);
-  return launch_gemm<1, 1>(tmA, tmB, tmC, args, grid, stream);
+  if (a_major == 0 && b_major == 0) return launch_gemm<0, 0>(tmA, tmB, tmC, args, grid, stream, bn);
+  if (a_major == 0 && b_major == 1) return launch_gemm<0, 1>(tmA, tmB, tmC, args, grid, stream, bn);
+  if (a_major == 1 && b_major == 0) return launch_gemm<1, 0>(tmA, tmB, tmC, args, grid, stream, bn);
+  return launch_gemm<1, 1>(tmA, tmB, tmC, args, grid, stream, bn);
 }
 
 ICB_API int icb_gemm(const void* A, const void* B, void* C, const void* bias, const void* residual, int M, int N,

@@ -239,6 +239,37 @@ def check_ep2_fused_moe_matches_nccl(rank, world):
         assert abs(x - y) < 5e-2, (la, lb)
 
 
+def check_dp2_muon_sharded_state_matches_replicated(rank, world):
+    """Muon under data parallelism: with the optimizer state sharded (ZeRO-1) the matrix owners must still see
+    whole, fully reduced gradient matrices; the run has to match the replicated-state run."""
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.trainer import Trainer
+    from helpers import tiny_config
+
+    def run(zero):
+        mesh.destroy_model_parallel()
+        cfg = tiny_config("llama", d_model=256, d_ffn=512, num_layers=2, num_attention_heads=4, head_dim=64,
+                          max_seq_len=128, max_position_embeddings=128, precision="bf16", vocab_size=1024)
+        cfg.data.vocab_size = 1024
+        cfg.model(reset_position_ids=False, reset_attention_mask=False)
+        cfg.trainer(micro_batch_size=2, train_batch_size=4, gradient_accumulation_steps=None,
+                    tensor_model_parallel_size=1)
+        cfg.parallel(world_size=world, rank=rank, local_rank=rank, zero_stage=zero)
+        cfg.optim(optimizer="muon", muon_lr=0.02, max_lr=1e-3, clip_grad=1.0)
+        cfg.operation.train_steps = 3
+        validate_config(cfg)
+        tr = Trainer(cfg)
+        losses = [float(tr.train_step(s)[0]) for s in range(3)]
+        return losses, tr.optimizer.groups[0].param_buf.float().clone()
+
+    la, pa = run(0)
+    lb, pb = run(1)
+    for x, y in zip(la, lb):
+        assert abs(x - y) < 2e-2, (la, lb)
+    assert (pa - pb).abs().max().item() < 2e-2, (pa - pb).abs().max().item()
+
+
 def test_fused_tp_kernels_two_gpus():
     _need_two()
     _spawn("check_raw_kernels")
@@ -247,6 +278,11 @@ def test_fused_tp_kernels_two_gpus():
 def test_dp2_fused_zero_step_vs_nccl():
     _need_two()
     _spawn("check_dp2_fused_zero_matches_nccl")
+
+
+def test_dp2_muon_sharded_state():
+    _need_two()
+    _spawn("check_dp2_muon_sharded_state_matches_replicated")
 
 
 def test_ep2_fused_moe_vs_nccl():
