@@ -550,7 +550,7 @@ static int pick_bn(long long m_tiles, int N, int groups, int sms) {
   static int forced = -1;
   if (forced < 0) {
     const char* e = getenv("ICB_GEMM_BN");
-    const int v = e != nullptr ? atoi(e) : 0;
+    const int v = e != nullptr ? atoi(e) : 256;   // 0 = choose per problem (wave fit), 128 / 256 = fixed
     forced = (v == 128 || v == 256) ? v : 0;
   }
   if (forced) return forced;
