@@ -95,7 +95,7 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def build_config(world: int, steps: int):
+def build_config(world: int, steps: int, fused=None, graph=None):
     from ironcore_b200.config import default_config, validate_config
 
     c = default_config()
@@ -103,13 +103,14 @@ def build_config(world: int, steps: int):
     c.data(task_type="synthetic", vocab_size=32000, synthetic_seed=1234)
     c.trainer(micro_batch_size=1, train_batch_size=GLOBAL_BATCH, gradient_accumulation_steps=None,
               tensor_model_parallel_size=world, log_interval=10 ** 9, model_path="", use_flash_attn=True,
-              cuda_graph=os.environ.get("ICB_CUDA_GRAPH", "1" if world > 1 else "0") != "0")
+              cuda_graph=(os.environ.get("ICB_CUDA_GRAPH", "1" if world > 1 else "0") != "0") if graph is None else graph)
     c.operation(train_steps=10 ** 6, no_save=True)
     c.optim(optimizer="adam", max_lr=3e-4, min_lr=3e-5, adam_beta1=0.9, adam_beta2=0.95, weight_decay=0.1,
             clip_grad=1.0, warmup_steps=0)
     c.init(init_std=0.02, seed=1234)
     c.parallel(world_size=world, rank=int(os.environ.get("RANK", "0")), local_rank=int(os.environ.get("LOCAL_RANK", "0")),
-               sequence_parallel=world > 1, zero_stage=1, fused_comm=os.environ.get("ICB_FUSED_COMM", "1") != "0")
+               sequence_parallel=world > 1, zero_stage=1,
+               fused_comm=(os.environ.get("ICB_FUSED_COMM", "1") != "0") if fused is None else fused)
     c.utils(report_memory_usage=False)
     validate_config(c)
     return c
@@ -159,6 +160,43 @@ def run_ours(args):
             self.i += 1
             return b
 
+    # Probe step: if the in-kernel collectives report a failed wait (status word) or produce a non-finite
+    # loss on any rank, every rank rebuilds the trainer on the NCCL collectives, so that the run still
+    # measures the step; the JSON line says which path was timed.
+    fallback = None
+    if world > 1 and fused_ws is not None:
+        keep = trainer.data_iterator["train"]
+        trainer.data_iterator["train"] = Cycle(resident)
+        ok = 1
+        try:
+            loss, _, _ = trainer.train_step(0)
+            torch.cuda.synchronize()
+            code = int(native.status_tensor(dev)[0].item())
+            if code != 0 or not bool(torch.isfinite(loss).all()):
+                ok = 0
+                fallback = f"probe step: status {code}, loss {float(loss)}"
+        except Exception as exc:  # noqa: BLE001 - any failure of the fused path triggers the fallback
+            ok = 0
+            fallback = f"probe step raised {type(exc).__name__}: {str(exc)[:120]}"
+        flag = torch.tensor([ok], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            fallback = fallback or "another rank failed the probe step"
+            native.status_tensor(dev).zero_()
+            trainer._graph = None
+            trainer._static_loss = None
+            del trainer, keep
+            import gc
+
+            gc.collect()
+            torch.cuda.empty_cache()
+            mesh.destroy_model_parallel()
+            cfg = build_config(world, args.steps, fused=False, graph=False)
+            trainer = Trainer(cfg)
+            fused_ws = None
+        else:
+            fallback = None
+            trainer.data_iterator["train"] = keep
     host_iter = trainer.data_iterator["train"]
     trainer.data_iterator["train"] = Cycle(resident)
     for s in range(args.warmup):
@@ -229,6 +267,7 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes,
                     "d2h_bytes_per_step": d2h_bytes, "last_loss": last_loss},
             "gpu_launches": launches,
+            "fallback": fallback,
             "memory_gib": torch.cuda.max_memory_allocated() / 2 ** 30,
         }
         print(json.dumps(out), flush=True)
