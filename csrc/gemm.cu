@@ -56,6 +56,7 @@ struct GemmArgs {
   int ag_chunks_per_block;          // 8 KiB chunks in one 128-row block
   uint8_t* ag_mc;                   // multicast (NVLS) address of the gathered buffer, or null: plain P2P stores
   int ag_batch;                     // chunks a copy warp pushes between two fence + publish steps (1..16)
+  int ag_helpers;                   // 1: the four epilogue warps push chunks too before their first tile
   unsigned long long* ag_debug;     // optional [grid][4] timestamps (ns): start, push done, first remote block ready, end
 };
 
@@ -67,6 +68,81 @@ __device__ __forceinline__ int ag_rotate(int seq, int per_shard, int rank, int w
   const int s = seq / per_shard;
   const int owner = (rank - s + world) % world;
   return owner * per_shard + (seq - s * per_shard);
+}
+
+// Push this rank's shard into every peer's gathered buffer. The shard is streamed as 8 KiB chunks,
+// interleaved over `n_cw` warps of the grid (`cw` = this warp's index). Stores need no round trip, so a few
+// warps saturate the link. Peers are visited in ring order (rank+1 first): at any moment every rank writes
+// to a different peer. Each finished chunk bumps the arrival counter of its 128-row block on the *peer*
+// (one system-scope fence per batch, then relaxed reductions); a block is complete at
+// epoch * chunks_per_block.
+__device__ __noinline__ void ag_push_shard(const GemmArgs& args, int cw, int n_cw, int lane) {
+    const long long shard_bytes = (long long)args.ag_rows_per_rank * args.ag_row_bytes;
+    const long long block_bytes = 128LL * args.ag_row_bytes;
+    const int chunks_per_shard = (int)(shard_bytes / kAgChunkBytes);
+    // A system-scope fence waits for the acknowledgement of every remote store, i.e. a full NVLink
+    // round trip: issue it once per batch of chunks (up to kAgBatch), then publish the batch.
+    constexpr int kAgBatch = 16;
+    if (args.ag_mc != nullptr) {
+      // NVLS form: one multimem.st per 16 bytes lands in every rank's buffer (the switch replicates),
+      // so the shard leaves this GPU once instead of world-1 times. The arrival counters are still
+      // bumped per peer, by lanes 0..world-2 in parallel.
+      int c = cw;
+      while (c < chunks_per_shard) {
+        int done_rb[kAgBatch];
+        int n_done = 0;
+#pragma unroll 1
+        for (; c < chunks_per_shard && n_done < args.ag_batch; c += n_cw) {
+          const long long off = (long long)args.ag_rank * shard_bytes + (long long)c * kAgChunkBytes;
+          const uint4* src = reinterpret_cast<const uint4*>(args.ag_local + off);
+          uint4* dst = reinterpret_cast<uint4*>(args.ag_mc + off);
+          uint4 v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = src[lane + j * 32];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) multimem_st_v4(dst + lane + j * 32, v[j]);
+          done_rb[n_done] = (int)(off / block_bytes);
+          ++n_done;
+        }
+        __syncwarp();
+        for (int p = lane; p < args.ag_world - 1; p += 32) {
+          const int q = (args.ag_rank + 1 + p) % args.ag_world;
+          __threadfence_system();
+          for (int i = 0; i < n_done; ++i) red_relaxed_sys_add(args.ag_peer_ready[q] + done_rb[i], 1);
+        }
+        __syncwarp();
+      }
+    } else {
+      const int total_chunks = (args.ag_world - 1) * chunks_per_shard;
+      int c = cw;
+      while (c < total_chunks) {
+        int done_q[kAgBatch], done_rb[kAgBatch];
+        int n_done = 0;
+#pragma unroll 1
+        for (; c < total_chunks && n_done < args.ag_batch; c += n_cw) {
+          const int step = c / chunks_per_shard + 1;
+          const int within = c - (step - 1) * chunks_per_shard;
+          const int q = (args.ag_rank + step) % args.ag_world;
+          const long long off = (long long)args.ag_rank * shard_bytes + (long long)within * kAgChunkBytes;
+          const uint4* src = reinterpret_cast<const uint4*>(args.ag_local + off);
+          uint4* dst = reinterpret_cast<uint4*>(args.ag_peers[q] + off);
+          uint4 v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = src[lane + j * 32];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) dst[lane + j * 32] = v[j];
+          done_q[n_done] = q;
+          done_rb[n_done] = (int)(off / block_bytes);
+          ++n_done;
+        }
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_system();
+          for (int i = 0; i < n_done; ++i) red_relaxed_sys_add(args.ag_peer_ready[done_q[i]] + done_rb[i], 1);
+        }
+        __syncwarp();
+      }
+    }
 }
 
 template <int A_MAJOR, int B_MAJOR, bool AG, int BN>
@@ -240,6 +316,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     __syncwarp();
   } else if (warp < 6) {
     // ------------------------------ epilogue ----------------------------------
+    if (AG && args.ag_helpers) ag_push_shard(args, blockIdx.x * 6 + (warp - 2), gridDim.x * 6, lane);
     const int et = threadIdx.x - 64;     // 0..127
     const int q = warp & 3;              // TMEM lane quarter this warp may read
     const int row = q * 32 + lane;
@@ -426,80 +503,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   if (AG && warp >= 6) {
     // ------------------------------ all-gather copy warps ----------------------
-    // Push model: this rank's shard is streamed as 8 KiB chunks, interleaved over all copy warps of
-    // the grid (2 per CTA), into every peer's gathered buffer. Stores need no round trip, so a few
-    // warps saturate the link. Peers are visited in ring order (rank+1 first): at any moment every
-    // rank writes to a different peer. Each finished chunk bumps the arrival counter of its 128-row
-    // block on the *peer* (release at system scope, cumulative over the warp's stores); a block is
-    // complete at epoch * chunks_per_block.
-    const int cw = blockIdx.x * 2 + (warp - 6);
-    const int n_cw = gridDim.x * 2;
-    const long long shard_bytes = (long long)args.ag_rows_per_rank * args.ag_row_bytes;
-    const long long block_bytes = 128LL * args.ag_row_bytes;
-    const int chunks_per_shard = (int)(shard_bytes / kAgChunkBytes);
-    // A system-scope fence waits for the acknowledgement of every remote store, i.e. a full NVLink
-    // round trip: issue it once per batch of chunks (up to kAgBatch), then publish the batch.
-    constexpr int kAgBatch = 16;
-    if (args.ag_mc != nullptr) {
-      // NVLS form: one multimem.st per 16 bytes lands in every rank's buffer (the switch replicates),
-      // so the shard leaves this GPU once instead of world-1 times. The arrival counters are still
-      // bumped per peer, by lanes 0..world-2 in parallel.
-      int c = cw;
-      while (c < chunks_per_shard) {
-        int done_rb[kAgBatch];
-        int n_done = 0;
-#pragma unroll 1
-        for (; c < chunks_per_shard && n_done < args.ag_batch; c += n_cw) {
-          const long long off = (long long)args.ag_rank * shard_bytes + (long long)c * kAgChunkBytes;
-          const uint4* src = reinterpret_cast<const uint4*>(args.ag_local + off);
-          uint4* dst = reinterpret_cast<uint4*>(args.ag_mc + off);
-          uint4 v[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = src[lane + j * 32];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) multimem_st_v4(dst + lane + j * 32, v[j]);
-          done_rb[n_done] = (int)(off / block_bytes);
-          ++n_done;
-        }
-        __syncwarp();
-        for (int p = lane; p < args.ag_world - 1; p += 32) {
-          const int q = (args.ag_rank + 1 + p) % args.ag_world;
-          __threadfence_system();
-          for (int i = 0; i < n_done; ++i) red_relaxed_sys_add(args.ag_peer_ready[q] + done_rb[i], 1);
-        }
-        __syncwarp();
-      }
-    } else {
-      const int total_chunks = (args.ag_world - 1) * chunks_per_shard;
-      int c = cw;
-      while (c < total_chunks) {
-        int done_q[kAgBatch], done_rb[kAgBatch];
-        int n_done = 0;
-#pragma unroll 1
-        for (; c < total_chunks && n_done < args.ag_batch; c += n_cw) {
-          const int step = c / chunks_per_shard + 1;
-          const int within = c - (step - 1) * chunks_per_shard;
-          const int q = (args.ag_rank + step) % args.ag_world;
-          const long long off = (long long)args.ag_rank * shard_bytes + (long long)within * kAgChunkBytes;
-          const uint4* src = reinterpret_cast<const uint4*>(args.ag_local + off);
-          uint4* dst = reinterpret_cast<uint4*>(args.ag_peers[q] + off);
-          uint4 v[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = src[lane + j * 32];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) dst[lane + j * 32] = v[j];
-          done_q[n_done] = q;
-          done_rb[n_done] = (int)(off / block_bytes);
-          ++n_done;
-        }
-        __syncwarp();
-        if (lane == 0) {
-          __threadfence_system();
-          for (int i = 0; i < n_done; ++i) red_relaxed_sys_add(args.ag_peer_ready[done_q[i]] + done_rb[i], 1);
-        }
-        __syncwarp();
-      }
-    }
+    // Two dedicated warps per CTA; with ag_helpers the four epilogue warps have already taken their share
+    // of the chunks before their first accumulator was ready (warp slots 0..3), these are slots 4 and 5.
+    const int per_cta = args.ag_helpers ? 6 : 2;
+    ag_push_shard(args, blockIdx.x * per_cta + (per_cta - 2) + (warp - 6), gridDim.x * per_cta, lane);
   }
 
   if (AG && args.ag_debug != nullptr) {
@@ -631,7 +638,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, co
     args.ag_rank = 0; args.ag_world = 1; args.ag_rows_per_rank = 0; args.ag_row_bytes = 0;
     args.ag_local = nullptr; args.ag_peers = nullptr; args.ag_peer_signal = nullptr; args.ag_signal = nullptr;
     args.ag_ready = nullptr; args.ag_epoch_ptr = nullptr; args.ag_chunks_per_block = 1; args.ag_peer_ready = nullptr;
-    args.ag_mc = nullptr; args.ag_batch = 4; args.ag_debug = nullptr;
+    args.ag_mc = nullptr; args.ag_batch = 4; args.ag_debug = nullptr; args.ag_helpers = 0;
   }
   args.M = M; args.N = N; args.K = K;
   args.num_m_tiles = (M + kBM - 1) / kBM;
@@ -723,6 +730,14 @@ ICB_API int icb_ag_gemm(void* gathered, const void* const* peers, int* const* pe
     ag.ag_batch = batch > 0 ? batch : 4;
   }
   ag.ag_debug = g_ag_debug;
+  {
+    static int helpers = -1;
+    if (helpers < 0) {
+      const char* e = getenv("ICB_AG_HELPERS");
+      helpers = (e != nullptr && atoi(e) != 0) ? 1 : 0;
+    }
+    ag.ag_helpers = helpers;
+  }
   ag.ag_chunks_per_block = (int)(128LL * width * 2 / kAgChunkBytes);
   const int rows = world * rows_per_rank;
   const int M = a_major == 0 ? rows : width;
