@@ -390,13 +390,13 @@ int make_head_tmap(CUtensorMap* tm, const void* base, int hd, int heads, long lo
   return make_head_tmap_rows(tm, base, hd, heads, tokens, row_stride, dtype, 128);
 }
 
-// Key rows per step: 128 (one CTA per SM) or 64 (two CTAs per SM). ICB_FLASH_BN overrides the default.
+// Key rows per step: 64 (two CTAs per SM, the default) or 128 (one CTA per SM). ICB_FLASH_BN overrides it.
 static int flash_fwd_bn() {
   static int bn = 0;
   if (bn == 0) {
     const char* e = getenv("ICB_FLASH_BN");
     const int v = e != nullptr ? atoi(e) : 0;
-    bn = (v == 64 || v == 128) ? v : 128;
+    bn = (v == 64 || v == 128) ? v : 64;   // measured: 0.270 ms vs 0.452 ms at s=4096, 32 heads x 128
   }
   return bn;
 }

@@ -551,8 +551,9 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   return launch_gemm_bn<A_MAJOR, B_MAJOR, AG, 256>(tmA, tmB, tmC, args, grid, stream);
 }
 
-// Tile width for a problem: 256 columns keep the tensor core fed best, but a grid of few tiles leaves a
-// ragged last wave on 148 SMs; 128-column tiles cost roughly a quarter more per flop (less operand reuse) and halve the quantum.
+// Tile width for a problem. Measured on B200: a 128-column tile costs 0.79 of a 256-column tile (the operand
+// feed, not the tensor pipe, bounds it), so it loses even on shapes with a ragged last wave (4096 x 1536 x 4096:
+// 0.083 ms vs 0.071 ms); 256 is the default, ICB_GEMM_BN=128 / 0 (per-problem choice) remain for experiments.
 static int pick_bn(long long m_tiles, int N, int groups, int sms) {
   static int forced = -1;
   if (forced < 0) {
@@ -564,7 +565,7 @@ static int pick_bn(long long m_tiles, int N, int groups, int sms) {
   const long long t256 = m_tiles * ((N + 255) / 256) * groups;
   const long long t128 = m_tiles * ((N + 127) / 128) * groups;
   const double c256 = (double)((t256 + sms - 1) / sms);
-  const double c128 = (double)((t128 + sms - 1) / sms) * 0.62;
+  const double c128 = (double)((t128 + sms - 1) / sms) * 0.79;
   return (c128 < c256 * 0.97) ? 128 : 256;
 }
 

@@ -1,8 +1,8 @@
 """Launch one native kernel a few times on a small (but larger-than-L2) case, for ``ncu``.
 
-    python -m ironcore_b200.ops.profile_kernels --kernel gemm|gemm_wgrad|flash_fwd|flash_bwd|rmsnorm|swiglu|adam|ag_gemm|gemm_rs
+    python -m ironcore_b200.ops.profile_kernels --kernel gemm|gemm_wgrad|flash_fwd|flash_bwd|rmsnorm|swiglu|adam|ag_gemm|gemm_rs|zero_step|moe_dispatch
 
-``ag_gemm`` / ``gemm_rs`` run the fused tensor-parallel kernels on a one-rank group (the peer table
+``ag_gemm`` / ``gemm_rs`` / ``zero_step`` / ``moe_dispatch`` run the fused compute+collective kernels on a one-rank group (the peer table
 points at this GPU's own buffers), which exercises the same code path — copy warps, flags, P2P
 epilogue, in-kernel reduction — inside a single process that a profiler can wrap."""
 
@@ -70,6 +70,40 @@ def main(argv=None):
             w = torch.randn(2048, d, device=dev).bfloat16()
             res = torch.randn(t, d, device=dev).bfloat16()
             fn = lambda: ws.gemm_rs(a, w, b_major=1, residual=res)
+    elif k in ("zero_step", "moe_dispatch"):
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29578")
+        torch.cuda.set_device(0)
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+        if k == "zero_step":
+            from ..optim.fused_zero import FusedZeroStep
+
+            n = 128 * 1024 * 1024      # 256 MiB of bf16 parameters, 512 MiB of fp32 gradients
+
+            class _Group:
+                total = n
+
+            fz = FusedZeroStep(dist.group.WORLD)
+            pbuf, gbuf = fz.allocate(_Group, torch.bfloat16, torch.float32)
+            gbuf.normal_()
+            m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+            regions = [(0, n, 1.0, 0.1, 1.0)]
+            fn = lambda: fz.step(regions, 0, m, v, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, step_size=1e-3,
+                                 grad_scale=1.0, clip=1.0)
+        else:
+            from ..parallel.fused_moe import FusedEP
+
+            t, d, e, kk = 8192, 2048, 64, 6
+            ws = FusedEP(dist.group.WORLD, e, kk, t, d, torch.bfloat16, 1.0)
+            x = torch.randn(t, d, device=dev).bfloat16()
+            expert = torch.randint(0, e, (t * kk,), device=dev, dtype=torch.int32)
+            w = torch.rand(t, kk, device=dev)
+
+            def fn():
+                xp, dest, seg, tile_expert, counts = ws.dispatch(x, expert)
+                ws.pull(xp, expert, dest, t, weight=w.reshape(-1).contiguous())
     else:
         raise SystemExit(f"unknown kernel {k}")
     for _ in range(args.iters):
