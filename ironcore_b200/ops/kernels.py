@@ -8,6 +8,8 @@ the current CUDA stream. These wrappers have no autograd; see
 
 from __future__ import annotations
 
+import os
+
 from typing import Optional
 
 import torch
@@ -31,6 +33,10 @@ def _check_2d(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"{name} must be 2-D with a contiguous last dim, got shape {tuple(t.shape)} strides {t.stride()}")
     if (t.stride(0) * t.element_size()) % 16 != 0 or t.data_ptr() % 16 != 0:
         raise ValueError(f"{name}: row pitch and base address must be multiples of 16 bytes")
+
+
+_USE_2SM = os.environ.get("ICB_GEMM_2SM", "0") == "1"
+native.register("icb_gemm_2sm", [native.P] * 5 + [native.I] * 3 + [native.L] * 4 + [native.I] * 4 + [native.P] * 2)
 
 
 def gemm(
@@ -87,6 +93,12 @@ def gemm(
         bias = bias.to(in_dt)
     if group_table is not None and group_table.dtype != torch.int32:
         raise TypeError("group_table must be int32")
+    if group_mode == 0 and _USE_2SM:
+        # experimental: 256 x 256 tiles on CTA pairs (tcgen05.mma.cta_group::2), ICB_GEMM_2SM=1
+        call("icb_gemm_2sm", ptr(a), ptr(b), ptr(out), ptr(bias), ptr(residual), int(m), int(n), int(k), int(lda),
+             int(ldb), int(ldc), int(ldr), int(a_major), int(b_major), dtype_code(in_dt),
+             1 if out_dtype == torch.float32 else 0, ptr(native.status_tensor(a.device)), stream_ptr())
+        return out
     call(
         "icb_gemm",
         ptr(a), ptr(b), ptr(out), ptr(bias), ptr(residual),

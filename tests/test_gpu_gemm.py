@@ -1,6 +1,8 @@
 """tcgen05 GEMM against an fp32 PyTorch reference: every operand-major combination,
 ragged shapes, epilogue options and the grouped (mixture-of-experts) forms."""
 
+import os
+
 import pytest
 import torch
 
@@ -107,3 +109,29 @@ def test_gemm_grouped_by_k_range():
             x[128:448].float().t() @ dy[128:448].float()]
     for i in range(g):
         _check(out[i], refs[i], 320)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(os.environ.get("ICB_TEST_2SM", "0") != "1",
+                    reason="experimental CTA-pair GEMM: run explicitly with ICB_TEST_2SM=1")
+@pytest.mark.parametrize("a_major,b_major", [(0, 1), (0, 0), (1, 1), (1, 0)])
+def test_gemm_2sm_matches_reference(a_major, b_major):
+    """256 x 256 tiles on CTA pairs (tcgen05.mma.cta_group::2) against fp32 matmul, ragged edges included."""
+    from ironcore_b200.ops import native
+    from ironcore_b200.ops.native import call, dtype_code, ptr, stream_ptr
+    from ironcore_b200.ops import kernels  # noqa: F401  (registers icb_gemm_2sm)
+
+    torch.manual_seed(3)
+    for (m, n, k) in [(256, 256, 64), (512, 768, 256), (384, 320, 192), (4096, 1536, 1024)]:
+        a = torch.randn((m, k) if a_major == 0 else (k, m), device="cuda").bfloat16()
+        b = torch.randn((n, k) if b_major == 0 else (k, n), device="cuda").bfloat16()
+        out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        call("icb_gemm_2sm", ptr(a), ptr(b), ptr(out), None, None, m, n, k, a.stride(0), b.stride(0), out.stride(0), 0,
+             a_major, b_major, dtype_code(torch.bfloat16), 0, ptr(native.status_tensor(a.device)), stream_ptr())
+        torch.cuda.synchronize()
+        native.check_status()
+        af = a.float() if a_major == 0 else a.float().t()
+        bf = b.float().t() if b_major == 0 else b.float()
+        ref = af @ bf
+        err = (out.float() - ref).abs().max().item()
+        assert err <= 2e-2 * (k ** 0.5) + 2.0 ** -7 * ref.abs().max().item(), (m, n, k, err)
