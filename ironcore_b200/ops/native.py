@@ -91,9 +91,10 @@ def register(name: str, argtypes) -> None:
     """Declare one more exported symbol (used by modules that own extra kernels)."""
     _SIGNATURES[name] = argtypes
     if _LIB is not None:
-        fn = getattr(_LIB, name)
-        fn.argtypes = argtypes
-        fn.restype = I
+        fn = getattr(_LIB, name, None)   # an optional entry point may be absent from an older build
+        if fn is not None:
+            fn.argtypes = argtypes
+            fn.restype = I
 
 
 def launches() -> int:
