@@ -113,7 +113,10 @@ class FSDPUnit:
             return self.shard_host.to(self.device, non_blocking=True)
         return self.shard
 
-    def gather(self, stream=None):
+    def gather(self, async_op: bool = False):
+        """Re-materialise the full buffer. With ``async_op`` the all-gather is only enqueued (it runs on the
+        communication stream of the backend, overlapping whatever the compute stream does next); ``wait_gather``
+        makes the compute stream wait for it right before the unit's parameters are used."""
         if self.materialised or not self.shard_params:
             return
         nbytes = self.total * self.full.element_size()
@@ -124,12 +127,22 @@ class FSDPUnit:
             dist.all_gather(parts, shard, group=self.group)
             self.full.copy_(torch.cat(parts))
         else:
-            dist.all_gather_into_tensor(self.full, shard, group=self.group)
+            work = dist.all_gather_into_tensor(self.full, shard, group=self.group, async_op=async_op)
+            self._gather_work = work if async_op else None
+            self._gather_src = shard if async_op else None   # keep the source alive until the wait
         self.materialised = True
+
+    def wait_gather(self):
+        work = getattr(self, "_gather_work", None)
+        if work is not None:
+            work.wait()
+            self._gather_work = None
+            self._gather_src = None
 
     def release(self):
         if not self.shard_params or not self.materialised:
             return
+        self.wait_gather()
         self.full.untyped_storage().resize_(0)
         self.materialised = False
 
@@ -165,15 +178,27 @@ class FSDPUnit:
                 if self.device.type == "cpu":
                     dist.all_reduce(fg, group=self.group)
                     out.copy_(fg[self.rank * self.shard_size:(self.rank + 1) * self.shard_size])
+                    self.grad_shard.add_(out.float())
                 else:
-                    dist.reduce_scatter_tensor(out, fg, group=self.group)
-                self.grad_shard.add_(out.float())
+                    # enqueue only: the reduce-scatter overlaps the backward pass of the next unit; the sum
+                    # is folded into the fp32 shard by ``finish_reduction`` (next unit's reduction / optimizer)
+                    self.finish_reduction()   # a reduction of an earlier micro-batch may still be pending
+                    work = dist.reduce_scatter_tensor(out, fg, group=self.group, async_op=True)
+                    self._pending_rs = (work, out, fg)
             else:
                 dist.all_reduce(fg, group=self.group)
                 self.grad_shard.add_(fg.float())
         else:
             self.grad_shard.add_(fg.float())
         self.release()
+
+    def finish_reduction(self):
+        pending = getattr(self, "_pending_rs", None)
+        if pending is not None:
+            work, out, _fg = pending
+            work.wait()
+            self.grad_shard.add_(out.float())
+            self._pending_rs = None
 
     def shard_range(self):
         if self.shard_params:
@@ -237,12 +262,15 @@ class FullyShardedModel(nn.Module):
 
     # ---- hooks ----
     def _prefetch(self, idx: int):
+        """Enqueue the next unit's all-gather without waiting for it: it overlaps the current unit's compute."""
         if 0 < idx < len(self.units):
-            self.units[idx].gather()
+            self.units[idx].gather(async_op=True)
 
     def _pre_forward(self, idx):
         def hook(_m, _inp):
-            self.units[idx].gather()
+            u = self.units[idx]
+            u.gather()
+            u.wait_gather()
             self._prefetch(idx + 1)
         return hook
 
@@ -258,6 +286,7 @@ class FullyShardedModel(nn.Module):
         def hook(_m, _gout):
             u = self.units[idx]
             u.gather()
+            u.wait_gather()
             if u._flat_grad is None:
                 u.begin_backward()
             self._prefetch(idx - 1 if idx - 1 >= 1 else -1)
@@ -265,8 +294,20 @@ class FullyShardedModel(nn.Module):
 
     def _grad_hook(self, unit: FSDPUnit, idx: int):
         def hook(_p):
+            if unit._pending == 1:
+                # this is the unit's last gradient: its reduction is about to be issued, so fold the
+                # previous one first (at most one unit-sized reduction buffer stays in flight)
+                prev = getattr(self, "_last_reduced", None)
+                if prev is not None and prev is not unit:
+                    prev.finish_reduction()
+                self._last_reduced = unit
             unit.grad_ready(idx)
         return hook
+
+    def finish_reductions(self):
+        for u in self.units:
+            u.finish_reduction()
+        self._last_reduced = None
 
     # ---- nn.Module surface ----
     def forward(self, *a, **k):
@@ -278,6 +319,7 @@ class FullyShardedModel(nn.Module):
     def gather_all(self):
         for u in self.units:
             u.gather()
+            u.wait_gather()
 
     def release_all(self):
         for u in self.units:
@@ -367,6 +409,7 @@ class FSDPOptimizer:
         from ..optim.muon import newton_schulz
 
         fs = self.fsdp
+        fs.finish_reductions()
         self.step_count += 1
         dp = float(max(fs.dp, 1))
         dev = fs.units[0].device

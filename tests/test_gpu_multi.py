@@ -270,6 +270,40 @@ def check_dp2_muon_sharded_state_matches_replicated(rank, world):
     assert (pa - pb).abs().max().item() < 2e-2, (pa - pb).abs().max().item()
 
 
+def check_fsdp2_matches_dp2(rank, world):
+    """Full-shard FSDP on 2 GPUs (asynchronous parameter gathers and gradient reduce-scatters) against the
+    replicated data-parallel run, with Adam and with Muon."""
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.trainer import Trainer
+    from helpers import tiny_config
+
+    def run(fsdp, optimizer):
+        mesh.destroy_model_parallel()
+        cfg = tiny_config("llama", d_model=256, d_ffn=512, num_layers=3, num_attention_heads=4, head_dim=64,
+                          max_seq_len=128, max_position_embeddings=128, precision="bf16", vocab_size=1024)
+        cfg.data.vocab_size = 1024
+        cfg.model(reset_position_ids=False, reset_attention_mask=False)
+        cfg.trainer(micro_batch_size=2, train_batch_size=8, gradient_accumulation_steps=None,
+                    tensor_model_parallel_size=1)
+        cfg.parallel(world_size=world, rank=rank, local_rank=rank, use_fsdp=fsdp, fsdp_mixed_precision="mixed")
+        cfg.optim(optimizer=optimizer, muon_lr=0.02, max_lr=1e-3, clip_grad=1.0)
+        cfg.operation.train_steps = 3
+        validate_config(cfg)
+        tr = Trainer(cfg)
+        losses = [float(tr.train_step(s)[0]) for s in range(3)]
+        sd = {k: v.float().clone() for k, v in tr.model.canonical_state_dict().items()}
+        return losses, sd
+
+    for optimizer in ("adam", "muon"):
+        la, sa = run(False, optimizer)
+        lb, sb = run(True, optimizer)
+        for x, y in zip(la, lb):
+            assert abs(x - y) < 3e-2, (optimizer, la, lb)
+        worst = max((sa[k] - sb[k]).abs().max().item() for k in sa)
+        assert worst < 3e-2, (optimizer, worst)
+
+
 def test_fused_tp_kernels_two_gpus():
     _need_two()
     _spawn("check_raw_kernels")
@@ -278,6 +312,11 @@ def test_fused_tp_kernels_two_gpus():
 def test_dp2_fused_zero_step_vs_nccl():
     _need_two()
     _spawn("check_dp2_fused_zero_matches_nccl")
+
+
+def test_fsdp2_matches_dp2():
+    _need_two()
+    _spawn("check_fsdp2_matches_dp2")
 
 
 def test_dp2_muon_sharded_state():
