@@ -234,3 +234,23 @@ def test_examples_run_on_cpu(tmp_path):
                          text=True, timeout=300)
     assert out.returncode == 0, out.stderr[-2000:]
     assert "--- sample 0 ---" in out.stdout
+
+
+def test_constructed_baselines_run_tiny_on_cpu():
+    """The plain-PyTorch baselines of the MoE, FSDP+Muon and GRPO workloads execute end to end (tiny shapes)."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_PORT"):
+        env.pop(k, None)
+    for workload in ("moe", "fsdp_muon", "grpo"):
+        out = subprocess.run([sys.executable, "-m", "baseline.constructed", "--workload", workload, "--tiny",
+                              "--steps", "1", "--warmup", "1"], cwd=root, env=env, capture_output=True, text=True,
+                             timeout=300)
+        assert out.returncode == 0, out.stderr[-1500:]
+        line = json.loads(out.stdout.strip().splitlines()[-1])
+        assert line["workload"] == workload and line["value"] > 0
