@@ -15,7 +15,6 @@ import argparse
 import json
 import math
 import os
-import sys
 import threading
 import time
 

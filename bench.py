@@ -23,7 +23,6 @@ import statistics
 import subprocess
 import sys
 import threading
-import time
 
 REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)

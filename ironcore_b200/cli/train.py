@@ -4,7 +4,6 @@ such as ``--tensor-model-parallel-size 2`` are accepted after ``--config``.)"""
 
 from __future__ import annotations
 
-import sys
 import traceback
 from pathlib import Path
 

@@ -10,7 +10,7 @@ dpo     : a ``chosen_`` and a ``rejected_`` SFT batch.
 
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Dict, List
 
 import numpy as np
 import torch

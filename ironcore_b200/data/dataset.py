@@ -13,7 +13,6 @@ from pathlib import Path
 from typing import Dict, Iterator, List, Optional
 
 import numpy as np
-import torch
 from torch.utils.data import IterableDataset
 
 from .serializer import BIN_NAME, IDX_NAME

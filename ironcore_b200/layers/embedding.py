@@ -10,7 +10,6 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..parallel import collectives as C
 from ..parallel.tensor_parallel import VocabParallelEmbedding
 
 

@@ -4,7 +4,7 @@ residual add that precedes the norm). Parameter path is ``<name>.layernorm.weigh
 
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Optional
 
 import torch
 import torch.nn as nn

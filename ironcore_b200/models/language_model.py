@@ -27,7 +27,7 @@ from ..parallel import collectives as C
 from ..parallel import mesh
 from ..parallel.tensor_parallel import (ColumnParallelLinear, init_linear_weight_, shard_tensor,
                                         vocab_parallel_cross_entropy)
-from .families import family_of, resolve_family_defaults
+from .families import resolve_family_defaults
 
 IGNORE_INDEX = -100
 

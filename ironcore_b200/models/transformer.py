@@ -14,7 +14,6 @@ checkpoints use the canonical ``linear_q`` / ``linear_kv`` tensors.
 
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.nn as nn

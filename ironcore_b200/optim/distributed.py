@@ -20,9 +20,8 @@ The update rule is the reference's (see :mod:`ironcore_b200.optim.adam`).
 
 from __future__ import annotations
 
-import math
-from dataclasses import dataclass, field
-from typing import Dict, List, Optional
+from dataclasses import dataclass
+from typing import Dict, List
 
 import torch
 import torch.distributed as dist

@@ -17,12 +17,11 @@ matrix products per iteration are the tcgen05 GEMM.
 from __future__ import annotations
 
 import math
-from typing import Dict, List, Optional
+from typing import Dict, List
 
 import torch
 import torch.distributed as dist
 
-from ..ops import functional as OF
 from ..ops import kernels
 
 NS_COEFFS = (3.4445, -4.7750, 2.0315)

@@ -10,7 +10,7 @@ library kernel ever sees a peer pointer.
 
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import List
 
 import torch
 import torch.distributed as dist

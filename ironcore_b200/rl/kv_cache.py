@@ -7,7 +7,7 @@ CUDA graph of the decode step keeps reading the current state)."""
 
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import List
 
 import torch
 

@@ -12,7 +12,6 @@ examples/generate_text.py:12-46.)
 
 from __future__ import annotations
 
-import math
 from typing import Optional, Tuple
 
 import torch

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import copy
 import time
-from typing import Dict, Optional
+from typing import Dict
 
 import torch
 import torch.distributed as dist

@@ -11,12 +11,10 @@ is averaged over the data-parallel group size.)
 
 from __future__ import annotations
 
-import contextlib
 import json
 import math
 import os
 import random
-import time
 from typing import Callable, Dict, Optional
 
 import numpy as np
