@@ -304,6 +304,34 @@ def check_fsdp2_matches_dp2(rank, world):
         assert worst < 3e-2, (optimizer, worst)
 
 
+def check_fsdp_comm_kernels(rank, world):
+    """Parameter gather and gradient reduce-scatter kernels over symmetric memory against NCCL."""
+    import torch.distributed as dist
+
+    from ironcore_b200.parallel.fsdp_comm import FsdpCommPool
+
+    torch.manual_seed(50 + rank)
+    n = 8 * world * 4096
+    for reduce_dtype in (torch.float32, torch.bfloat16):
+        pool = FsdpCommPool(dist.group.WORLD, n, torch.bfloat16, reduce_dtype)
+        for it in range(3):
+            slot = it % 2
+            shard = torch.randn(n // world, device="cuda").bfloat16()
+            ref = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+            dist.all_gather_into_tensor(ref, shard)
+            full = pool.gather(shard, slot)
+            torch.cuda.synchronize()
+            assert torch.equal(full, ref)
+            flat = torch.randn(n, device="cuda").to(reduce_dtype)
+            pool.flat_view(slot, n).copy_(flat)
+            acc = torch.ones(n // world, device="cuda")
+            pool.reduce_scatter(slot, acc, 0.5)
+            want = torch.empty(n // world, device="cuda")
+            dist.reduce_scatter_tensor(want, flat.float())
+            torch.cuda.synchronize()
+            assert (acc - (1.0 + 0.5 * want)).abs().max().item() < 2e-2
+
+
 def test_fused_tp_kernels_two_gpus():
     _need_two()
     _spawn("check_raw_kernels")
@@ -317,6 +345,13 @@ def test_dp2_fused_zero_step_vs_nccl():
 def test_fsdp2_matches_dp2():
     _need_two()
     _spawn("check_fsdp2_matches_dp2")
+
+
+@pytest.mark.skipif(os.environ.get("ICB_TEST_EXPERIMENTAL", "0") != "1",
+                    reason="opt-in kernels: run explicitly with ICB_TEST_EXPERIMENTAL=1")
+def test_fsdp_comm_kernels_two_gpus():
+    _need_two()
+    _spawn("check_fsdp_comm_kernels")
 
 
 def test_dp2_muon_sharded_state():
