@@ -15,7 +15,6 @@ import argparse
 import json
 import math
 import os
-import threading
 import time
 
 import torch
@@ -433,10 +432,14 @@ def main(argv=None):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "dtype": "bf16",
             "data": "synthetic", "config": {k: v for k, v in c.items() if not isinstance(v, (list, dict))},
             "memory_gib": torch.cuda.max_memory_allocated() / 2 ** 30 if cuda else None}), flush=True)
-    threading.Timer(30.0, lambda: os._exit(0)).start()
+    import faulthandler
+
+    # a stalled teardown is reported (stacks on stderr, exit status 1), never passed off as success
+    faulthandler.dump_traceback_later(45.0, exit=True)
     if world > 1:
         dist.destroy_process_group()
-    os._exit(0)
+    faulthandler.cancel_dump_traceback_later()
+    faulthandler.dump_traceback_later(45.0, exit=True)
 
 
 if __name__ == "__main__":

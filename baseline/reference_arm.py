@@ -272,21 +272,14 @@ def run_reference(args, model_kw, global_batch, seq_len, metric) -> int:
                        "shims": "offline tokenizer stub, synthetic data iterator, RMSNorm bias kwarg, "
                                 "device property of parameter-free modules"},
             "clocks": clocks,
+            "ms_per_step_x_sm_mhz": (ms_per_step * clocks["sm_mhz"]) if clocks and clocks.get("sm_mhz") else None,
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": accum * 2 * seq_len * 8,
                     "d2h_bytes_per_step": 4, "last_loss": last},
             "gpu_launches": 0,
             "memory_gib": torch.cuda.max_memory_allocated() / 2 ** 30,
         }
         print(json.dumps(out), flush=True)
-    import threading
+    from bench import guarded_teardown
 
-    watchdog = threading.Timer(45.0, lambda: os._exit(0))
-    watchdog.daemon = True
-    watchdog.start()
-    try:
-        trainer._finialize_process()
-    except Exception:
-        pass
-    finally:
-        watchdog.cancel()
+    guarded_teardown(trainer._finialize_process)
     return 0

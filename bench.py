@@ -263,6 +263,9 @@ def run_ours(args):
                        "cuda_graph": bool(cfg.trainer.cuda_graph),
                        "l2": "no flush needed: every pass streams 13.5 GB of weights, far larger than the 126 MB L2"},
             "clocks": clocks,
+            # time x clock: compares the work per cycle of two arms that settled at different SM clocks
+            # under the same power cap
+            "ms_per_step_x_sm_mhz": (ms_per_step * clocks["sm_mhz"]) if clocks and clocks.get("sm_mhz") else None,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes,
                     "d2h_bytes_per_step": d2h_bytes, "last_loss": last_loss},
             "gpu_launches": launches,
@@ -270,15 +273,23 @@ def run_ours(args):
             "memory_gib": torch.cuda.max_memory_allocated() / 2 ** 30,
         }
         print(json.dumps(out), flush=True)
-    # Teardown must never outlive the measurement: if the collective shutdown stalls, leave anyway.
-    watchdog = threading.Timer(45.0, lambda: os._exit(0))
-    watchdog.daemon = True
-    watchdog.start()
-    try:
-        trainer.finalize()
-    finally:
-        watchdog.cancel()
+    guarded_teardown(trainer.finalize)
     return 0
+
+
+def guarded_teardown(finalize, limit_s: float = 45.0):
+    """Run ``finalize`` under a watchdog. A teardown that stalls (a collective shutdown waiting for a rank
+    that is gone) is not a success: after ``limit_s`` the watchdog prints every thread's stack to stderr
+    and ends the process with exit status 1. A second watchdog covers interpreter shutdown."""
+    import faulthandler
+
+    sys.stdout.flush()
+    faulthandler.dump_traceback_later(limit_s, exit=True)
+    try:
+        finalize()
+    finally:
+        faulthandler.cancel_dump_traceback_later()
+    faulthandler.dump_traceback_later(limit_s, exit=True)
 
 
 def _published_baseline():

@@ -18,7 +18,6 @@ import argparse
 import json
 import os
 import sys
-import threading
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 PRESET = {"moe": "configs/baseline_moe_ep8.yaml", "fsdp_muon": "configs/baseline_llama13b_fsdp_muon.yaml",
@@ -119,8 +118,7 @@ def main(argv=None):
     for s in range(args.steps):
         last = trainer.train_step(args.warmup + s)
         if args.workload == "grpo":
-            rollout_s += trainer.num_seqs * cfg.rl.max_new_tokens / max(last["rollout_tokens_per_s"] /
-                                                                        mesh.get_data_parallel_world_size(), 1e-9)
+            rollout_s += last["rollout_s"]       # device-timed, already the maximum over ranks
     e1.record()
     barrier_sync()
     t = torch.tensor([e0.elapsed_time(e1), rollout_s * 1e3], device=dev)
@@ -153,12 +151,9 @@ def main(argv=None):
                        "optimizer": cfg.optim.optimizer, "zero_stage": cfg.parallel.zero_stage},
             "clocks": clocks, "gpu_launches": native.launches(),
             "memory_gib": torch.cuda.max_memory_allocated() / 2 ** 30, **extra}), flush=True)
-    threading.Timer(45.0, lambda: os._exit(0)).start()
-    try:
-        trainer.finalize()
-    except Exception:
-        pass
-    os._exit(0)
+    from bench import guarded_teardown
+
+    guarded_teardown(trainer.finalize)
 
 
 if __name__ == "__main__":

@@ -1,7 +1,9 @@
 """Memory-mapped datasets over the binary format and weighted mixing of several sources.
 
 pretrain: fixed windows of ``seq_len + 1`` tokens starting every ``seq_len`` tokens (wrapping at the
-end), visited in a seeded shuffle and sharded ``index % dp_size == dp_rank``; sft / dpo: samples
+end); an epoch draws ``round(N * ratio_i)`` windows from source ``i`` (N = windows of all sources; a
+source smaller than its share is revisited, a larger one is subsampled without replacement), in a
+seeded shuffle sharded ``index % dp_size == dp_rank``; sft / dpo: samples
 drawn by weighted sampling without replacement, then rank-sharded. Train / eval / test splits are
 contiguous token (pretrain) or sample (sft, dpo) ranges given by the split ratios.
 (Behavioural reference: ironcore/dataloader/universal_dataset.py:20-390.)"""
@@ -15,7 +17,7 @@ from typing import Dict, Iterator, List, Optional
 import numpy as np
 from torch.utils.data import IterableDataset
 
-from .serializer import BIN_NAME, IDX_NAME
+from .serializer import BIN_NAME, IDX_NAME, RANGES_NAME, decode_mask_ranges
 
 
 class BinaryDataset:
@@ -32,6 +34,7 @@ class BinaryDataset:
             total = int(self.index["offset"][-1] + self.index["length"][-1]) if len(self.index) else 0
             dtype = np.dtype(np.uint16) if total and nbytes // total == 2 else np.dtype(np.uint32)
         self.tokens = np.memmap(d / BIN_NAME, dtype=dtype, mode="r")
+        self.ranges = np.load(d / RANGES_NAME, allow_pickle=False) if (d / RANGES_NAME).exists() else None
         self.directory = d
 
     @property
@@ -45,7 +48,7 @@ class BinaryDataset:
         rec = self.index[i]
         o, n = int(rec["offset"]), int(rec["length"])
         return {"tokens": np.asarray(self.tokens[o:o + n], dtype=np.int64), "type": str(rec["type"]),
-                "group_id": int(rec["group_id"]), "mask_ranges": json.loads(str(rec["mask_ranges"]) or "[]")}
+                "group_id": int(rec["group_id"]), "mask_ranges": decode_mask_ranges(rec["mask_ranges"], self.ranges)}
 
     def window(self, start: int, length: int) -> np.ndarray:
         """``length`` tokens from ``start`` (wrapping around the end of the corpus)."""
@@ -89,6 +92,26 @@ class WeightedMixingDataset(IterableDataset):
                 items.append((si, start))
         return items
 
+    def _weighted_pretrain_order(self, items, rng) -> np.ndarray:
+        """Indices into ``items`` for one epoch: every source contributes its ratio's share of the epoch."""
+        src = np.asarray([si for si, _ in items])
+        total = len(items)
+        if len(self.sets) == 1:
+            return rng.permutation(total)
+        picks = []
+        for si in range(len(self.sets)):
+            own = np.flatnonzero(src == si)
+            want = int(round(total * float(self.weights[si])))
+            if len(own) == 0 or want == 0:
+                continue
+            full, rest = divmod(want, len(own))
+            for _ in range(full):
+                picks.append(rng.permutation(own))
+            if rest:
+                picks.append(rng.choice(own, size=rest, replace=False))
+        order = np.concatenate(picks) if picks else np.zeros(0, dtype=np.int64)
+        return order[rng.permutation(len(order))]
+
     def _sample_items(self):
         items, probs = [], []
         for si, ds in enumerate(self.sets):
@@ -107,8 +130,7 @@ class WeightedMixingDataset(IterableDataset):
                 items = self._pretrain_positions()
                 if not items:
                     return
-                # weight the sources by replicating their share of the shuffle
-                order = rng.permutation(len(items))
+                order = self._weighted_pretrain_order(items, rng)
                 for j, k in enumerate(order):
                     if j % self.dp_size != self.dp_rank:
                         continue

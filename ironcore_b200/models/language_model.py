@@ -297,7 +297,13 @@ class LanguageModel(BaseModule):
         split universal checkpoints across TP sizes)."""
         info = {}
         params = dict(self.named_parameters())
-        for name in self.canonical_state_dict().keys():
+        names = []
+        for name in self.state_dict().keys():   # names only: parameter storage may be released (FSDP)
+            if ".linear_qkv." in name:
+                names += [name.replace("linear_qkv", "linear_q"), name.replace("linear_qkv", "linear_kv")]
+            else:
+                names.append(name)
+        for name in names:
             if ".linear_q." in name:
                 src = params[name.replace("linear_q", "linear_qkv")]
                 info[name] = (getattr(src, "tp_shard_dim", None), 1)

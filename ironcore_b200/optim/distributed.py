@@ -66,6 +66,15 @@ def is_muon_param(name: str, p: torch.Tensor) -> bool:
     return True
 
 
+def muon_param_group(o) -> dict:
+    """Param group of the Muon matrices. The schedule is computed on the Adam scale (``initial_lr`` =
+    ``max_lr``, floor ``min_lr``) and multiplied by ``lr_mult = muon_lr / max_lr`` exactly once, so the
+    Muon rate follows the same warm-up / decay shape and peaks at ``muon_lr``."""
+    mult = o.muon_lr / o.max_lr if o.max_lr else 1.0
+    base = o.max_lr if o.max_lr else o.muon_lr
+    return {"lr": o.muon_lr, "initial_lr": base, "name": "muon", "lr_mult": mult}
+
+
 @dataclass
 class Region:
     start: int
@@ -201,8 +210,7 @@ class DistributedOptimizer:
             self.groups.append(FlatGroup(expert, self.edp_group, o.weight_decay, decay_fn, muon_fn, grad_dtype, 128))
         self.param_groups = [{"lr": o.max_lr, "initial_lr": o.max_lr, "name": "adam"}]
         if self.use_muon:
-            self.param_groups.append({"lr": o.muon_lr, "initial_lr": o.muon_lr, "name": "muon",
-                                      "lr_mult": o.muon_lr / o.max_lr if o.max_lr else 1.0})
+            self.param_groups.append(muon_param_group(o))
         # optimizer state: fp32 moments for the adam regions of the local shard
         self.moments = []
         for g in self.groups:
@@ -367,7 +375,9 @@ class DistributedOptimizer:
                                    weight_decay=wd, step=self.step_count, grad_scale=gscale, grad_scale_dev=coef)
                 hm.copy_(dm, non_blocking=True)
                 hv.copy_(dv, non_blocking=True)
-        torch.cuda.current_stream().wait_stream(side)
+        # step() joins the side stream after the Muon matrices were updated on the main stream: the
+        # host <-> device traffic of the moments overlaps the Newton-Schulz GEMMs (disjoint parameters)
+        self._side_pending = True
 
     def _fused_zero_step(self):
         """Gradient reduce-scatter, global norm, Adam and parameter all-gather in two kernels that talk
@@ -409,6 +419,9 @@ class DistributedOptimizer:
                     self._adam_range(g, mom, lo, a, b, r.weight_decay, coef, lr)
         if self.use_muon and self.muon is not None:
             self.muon.step(coef, self.param_groups[1]["lr"])
+        if getattr(self, "_side_pending", False):
+            torch.cuda.current_stream().wait_stream(self._side_stream)
+            self._side_pending = False
         if self.zero:
             for g in self.groups:
                 if g.dp > 1:

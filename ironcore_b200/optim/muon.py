@@ -23,6 +23,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import kernels
+from ..parallel import mesh as _mesh
 
 NS_COEFFS = (3.4445, -4.7750, 2.0315)
 
@@ -61,12 +62,14 @@ def newton_schulz(g: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.T
 
 
 class _Matrix:
-    __slots__ = ("slot", "group_idx", "expert", "col_lo", "col_hi", "full_shape", "owner", "momentum", "tp_dim")
+    __slots__ = ("slot", "group_idx", "expert", "col_lo", "col_hi", "full_shape", "owner", "momentum", "tp_dim",
+                 "part", "key")
 
 
 class MuonState:
     def __init__(self, engine, config):
         self.engine = engine
+        self.config = config
         o = config.optim
         self.momentum = o.muon_momentum
         self.nesterov = o.nesterov
@@ -88,11 +91,18 @@ class MuonState:
                     sizes = [cols // parts] * parts
                 else:
                     sizes = [x // self.tp_size if tp_dim is not None and self.tp_size > 1 else x for x in parts]
+                # checkpoint key: independent of the TP and EP layout (part index of a fused tensor, global
+                # expert index), because the momentum is kept for the whole logical matrix
+                e_base = 0
+                if p.dim() == 3 and getattr(p, "expert_parallel", False):
+                    e_base = _mesh.get_expert_model_parallel_rank() * p.shape[0]
                 for e in experts:
                     lo = 0
-                    for sz in sizes:
+                    for part, sz in enumerate(sizes):
                         mtx = _Matrix()
                         mtx.slot, mtx.group_idx, mtx.expert = s, gi, e
+                        mtx.part = part
+                        mtx.key = f"{s.name}|{None if e is None else e + e_base}|{part}"
                         mtx.col_lo, mtx.col_hi = lo, lo + sz
                         rows = p.shape[-2]
                         fr, fc = rows, sz
@@ -187,16 +197,46 @@ class MuonState:
                     w.add_(upd[r.start:r.end])
 
     def state_dict(self) -> Dict[str, torch.Tensor]:
-        out = {}
-        for i, m in enumerate(self.matrices):
-            if m.momentum is not None:
-                key = f"{m.slot.name}|{m.expert}|{m.col_lo}"
-                out[key] = m.momentum.detach().cpu()
+        """Momentum of every logical matrix by layout-independent key. Collective: each momentum lives on
+        its owner in the reduction group and is broadcast from there; data-parallel rank 0 (the checkpoint
+        writer) keeps a host copy, the other ranks keep nothing. With expert parallelism and a merged
+        (non-distributed) checkpoint the expert ranks' dictionaries are then collected on expert rank 0."""
+        out: Dict[str, torch.Tensor] = {}
+        eng = self.engine
+        for m in self.matrices:
+            g = eng.groups[m.group_idx]
+            mine = m.owner == g.dp_rank
+            t = m.momentum if mine else None
+            if g.dp > 1:
+                buf = torch.zeros(m.full_shape, dtype=torch.float32, device=g.device)
+                if t is not None:
+                    buf.copy_(t)
+                dist.broadcast(buf, src=_mesh.global_rank_of(g.reduce_group, m.owner), group=g.reduce_group)
+                t = buf
+            if t is not None and g.dp_rank == 0:
+                out[m.key] = t.detach().float().cpu()
+        ep = _mesh.get_expert_model_parallel_world_size()
+        if ep > 1 and not getattr(self.config.operation, "save_dist_ckpt", False):
+            group = _mesh.get_expert_model_parallel_group()
+            dst = _mesh.global_rank_of(group, 0)
+            expert_keys = {m.key for m in self.matrices if m.expert is not None}
+            mine_exp = {k: v for k, v in out.items() if k in expert_keys}
+            parts = [None] * ep if dist.get_rank() == dst else None
+            dist.gather_object(mine_exp, parts, dst=dst, group=group)
+            if parts is not None:
+                for d in parts:
+                    out.update(d)
         return out
 
     def load_state_dict(self, sd: Dict[str, torch.Tensor]):
+        """Owners take the momenta of their matrices; everything else in ``sd`` is ignored."""
         for m in self.matrices:
-            key = f"{m.slot.name}|{m.expert}|{m.col_lo}"
-            if key in sd:
-                g = self.engine.groups[m.group_idx]
-                m.momentum = sd[key].to(g.device).float()
+            g = self.engine.groups[m.group_idx]
+            if m.owner != g.dp_rank:
+                m.momentum = None
+                continue
+            t = sd.get(m.key)
+            if t is None:      # files written before keys became layout independent
+                t = sd.get(f"{m.slot.name}|{m.expert}|{m.col_lo}")
+            if t is not None and tuple(t.shape) == tuple(m.full_shape):
+                m.momentum = t.to(g.device).float().clone()

@@ -1,8 +1,9 @@
 """Host-side failure detection.
 
-Every rank publishes ``(step, wall clock)`` to the process group's key-value store on a background
-thread; each rank watches the others and declares a peer dead when its heartbeat is older than the
-timeout. The trainer asks between steps (never while kernels or collectives are in flight), so a
+Every rank publishes ``(step, beat counter)`` to the process group's key-value store on a background
+thread; each rank watches the others and declares a peer dead when that peer's counter has not moved
+for longer than the timeout, measured on the watcher's own clock (clocks of different hosts are never
+compared, and a key that is not there yet is probed with ``check`` instead of a blocking ``get``). The trainer asks between steps (never while kernels or collectives are in flight), so a
 lost rank surfaces as a Python exception before the next launch instead of a collective that
 blocks until the process-group timeout. Recovery is restart-from-latest-checkpoint, driven by the
 launcher. Device-side waits are bounded separately (status word written by the kernels).
@@ -36,6 +37,10 @@ class Heartbeat:
             store = _get_default_store()
         self.store = store
         self.step = -1
+        self._seq = 0
+        self._seen: Dict[int, tuple] = {}       # peer -> (last counter value, local time it was first seen)
+        self._born = self.clock()
+        self._lock = threading.Lock()
         self._stop = threading.Event()
         self._thread = None
         self._publish()
@@ -47,12 +52,14 @@ class Heartbeat:
         return f"{self.prefix}/{rank}"
 
     def _publish(self):
-        self.store.set(self._key(self.rank), f"{self.step}:{self.clock():.3f}")
+        self._seq += 1
+        self.store.set(self._key(self.rank), f"{self.step}:{self._seq}")
 
     def _run(self):
         while not self._stop.wait(self.interval_s):
             try:
                 self._publish()
+                self.peer_ages()        # keep the "last change" times current between the trainer's questions
             except Exception:
                 return
 
@@ -60,17 +67,46 @@ class Heartbeat:
         self.step = step
         self._publish()
 
+    def _read(self, rank: int) -> Optional[str]:
+        """The peer's record, or None when it has not published yet. Never blocks on a missing key."""
+        key = self._key(rank)
+        check = getattr(self.store, "check", None)
+        try:
+            if check is not None and not check([key]):
+                return None
+            raw = self.store.get(key)
+        except Exception:
+            return None
+        return raw.decode() if isinstance(raw, (bytes, bytearray)) else str(raw)
+
+    def peer_steps(self) -> Dict[int, int]:
+        """Last optimizer step each peer reported (-1 before its first step or when it never published)."""
+        out = {}
+        for r in range(self.world):
+            if r != self.rank:
+                raw = self._read(r)
+                out[r] = int(raw.split(":")[0]) if raw else -1
+        return out
+
     def peer_ages(self) -> Dict[int, float]:
-        now = self.clock()
+        """Seconds, on this rank's clock, since each peer's beat counter last changed (since this watcher
+        started, for a peer that never published)."""
         ages = {}
         for r in range(self.world):
             if r == self.rank:
                 continue
-            try:
-                raw = self.store.get(self._key(r)).decode()
-                ages[r] = now - float(raw.split(":")[1])
-            except Exception:
-                ages[r] = float("inf")
+            raw = self._read(r)
+            now = self.clock()
+            if raw is None:
+                ages[r] = now - self._born
+                continue
+            with self._lock:
+                seen = self._seen.get(r)
+                if seen is None or seen[0] != raw:
+                    self._seen[r] = (raw, now)
+                    ages[r] = 0.0
+                else:
+                    ages[r] = now - seen[1]
         return ages
 
     def dead_peers(self) -> List[int]:

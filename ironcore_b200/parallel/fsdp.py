@@ -32,7 +32,7 @@ import torch.nn as nn
 
 from ..ops import kernels
 from ..optim.adam import adam_update_reference
-from ..optim.distributed import is_muon_param, is_no_decay
+from ..optim.distributed import is_muon_param, is_no_decay, muon_param_group
 from . import mesh
 
 _ALIGN = 64
@@ -363,8 +363,7 @@ class FSDPOptimizer:
         self.use_muon = fsdp.use_muon
         self.param_groups = [{"lr": o.max_lr, "initial_lr": o.max_lr, "name": "adam"}]
         if self.use_muon:
-            self.param_groups.append({"lr": o.muon_lr, "initial_lr": o.muon_lr, "name": "muon",
-                                      "lr_mult": o.muon_lr / o.max_lr if o.max_lr else 1.0})
+            self.param_groups.append(muon_param_group(o))
         self.muon_momentum: Dict[str, torch.Tensor] = {}
         self._norm = None
         self._owners: Dict[str, int] = {}
@@ -531,7 +530,35 @@ class FSDPOptimizer:
                             "exp_avg": m[off:off + p.numel()].view(p.shape).clone().cpu(),
                             "exp_avg_sq": v[off:off + p.numel()].view(p.shape).clone().cpu()}
         return {"step": self.step_count, "param_groups": [dict(g) for g in self.param_groups], "state": state,
-                "muon": {repr(k): t.cpu() for k, t in self.muon_momentum.items()}}
+                "muon": self._muon_state()}
+
+    @staticmethod
+    def _muon_key(key) -> str:
+        name, e, c0, _ = key
+        return f"{name}|{e}|{c0}"
+
+    def _muon_state(self):
+        """Momentum of every Muon matrix, broadcast from its owner (collective over the shard group);
+        only shard rank 0, the checkpoint writer, keeps the host copies."""
+        out = {}
+        if not self.use_muon:
+            return out
+        for u in self.fsdp.units:
+            for n, p, k in zip(u.names, u.params, u.kinds):
+                if k != 2:
+                    continue
+                for key, shape in self._logical_matrices(n, p):
+                    owner = self._owners.get(key, 0) if (u.dp > 1 and u.shard_params) else u.rank
+                    t = self.muon_momentum.get(key) if owner == u.rank else None
+                    if u.dp > 1 and u.shard_params:
+                        buf = torch.zeros(shape, dtype=torch.float32, device=u.device)
+                        if t is not None:
+                            buf.copy_(t)
+                        dist.broadcast(buf, src=mesh.global_rank_of(u.group, owner), group=u.group)
+                        t = buf
+                    if t is not None and u.rank == 0:
+                        out[self._muon_key(key)] = t.detach().float().cpu()
+        return out
 
     def load_state_dict(self, sd):
         self.step_count = int(sd.get("step", 0))
@@ -546,4 +573,19 @@ class FSDPOptimizer:
                 if b > a:
                     u.exp_avg[a - lo:b - lo].copy_(st["exp_avg"].reshape(-1)[a - off:b - off])
                     u.exp_avg_sq[a - lo:b - lo].copy_(st["exp_avg_sq"].reshape(-1)[a - off:b - off])
+        for pg, saved in zip(self.param_groups, sd.get("param_groups", [])):
+            pg.update({k: v for k, v in saved.items() if k in ("lr", "initial_lr")})
+        muon = sd.get("muon") or {}
+        self.muon_momentum.clear()
+        if self.use_muon and muon:
+            for u in self.fsdp.units:
+                for n, p, k in zip(u.names, u.params, u.kinds):
+                    if k != 2:
+                        continue
+                    for key, shape in self._logical_matrices(n, p):
+                        if self._owners.get(key, 0) != u.rank and u.dp > 1 and u.shard_params:
+                            continue
+                        t = muon.get(self._muon_key(key))
+                        if t is not None and tuple(t.shape) == tuple(shape):
+                            self.muon_momentum[key] = t.to(u.device).float().clone()
         return self

@@ -214,3 +214,10 @@ def get_world_size() -> int:
 
 def is_rank_zero() -> bool:
     return get_rank() == 0
+
+
+def global_rank_of(group, group_rank: int) -> int:
+    """Global rank of ``group_rank`` within ``group`` (the default group maps to itself)."""
+    if group is None or not dist.is_initialized() or group is dist.group.WORLD:
+        return int(group_rank)
+    return int(dist.get_global_rank(group, group_rank))

@@ -7,7 +7,6 @@ optimizer engine). Reported throughput = generated tokens per second of rollout 
 
 from __future__ import annotations
 
-import copy
 import time
 from typing import Dict
 
@@ -37,12 +36,23 @@ class GRPOTrainer(Trainer):
         # frozen reference policy: same weights at construction time, never updated
         self.ref_model = None
         if rl.kl_beta > 0:
-            self.ref_model = copy.deepcopy(self.model)
+            # a second model of the same layout with the policy's initial weights (modules hold
+            # process-group handles, so the policy object itself cannot be deep-copied)
+            from ..models.language_model import LanguageModel
+
+            rng_cpu = torch.get_rng_state()
+            rng_dev = torch.cuda.get_rng_state() if self.device.type == "cuda" else None
+            self.ref_model = LanguageModel(config, self.loss_fn, device=self.device)
+            torch.set_rng_state(rng_cpu)
+            if rng_dev is not None:
+                torch.cuda.set_rng_state(rng_dev)
+            with torch.no_grad():
+                for dst, src in zip(self.ref_model.parameters(), self.model.parameters()):
+                    dst.copy_(src)
+                for dst, src in zip(self.ref_model.buffers(), self.model.buffers()):
+                    dst.copy_(src)
             for p in self.ref_model.parameters():
                 p.requires_grad_(False)
-                for attr in ("main_grad",):
-                    if hasattr(p, attr):
-                        delattr(p, attr)
             self.ref_model.eval()
         self.prompt_gen = torch.Generator(device="cpu").manual_seed(int(rl.reward_seed) + 1000 * mesh.get_data_parallel_rank())
         self.sample_gen = None
@@ -65,14 +75,22 @@ class GRPOTrainer(Trainer):
     def rollout(self) -> Dict[str, torch.Tensor]:
         rl = self.config.rl
         prompts = self._prompts()
-        if self.device.type == "cuda":
+        # rollout time is measured on the device (CUDA events on the launching stream); the slowest
+        # replica defines the throughput (train_step reduces it with MAX over all ranks)
+        cuda = self.device.type == "cuda"
+        if cuda:
             torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
         t0 = time.perf_counter()
         tokens, logp_old = self.engine.generate(prompts, rl.max_new_tokens, rl.temperature, rl.top_k, rl.top_p,
                                                 self.sample_gen)
-        if self.device.type == "cuda":
-            torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
+        if cuda:
+            e1.record()
+            e1.synchronize()
+            dt = e0.elapsed_time(e1) / 1e3
+        else:
+            dt = time.perf_counter() - t0
         generated = tokens[:, rl.prompt_len:]
         rewards = self.reward_fn(generated)
         adv = group_advantages(rewards, rl.group_size, rl.adv_eps)
@@ -116,7 +134,12 @@ class GRPOTrainer(Trainer):
         rl = self.config.rl
         gen_tokens = self.num_seqs * rl.max_new_tokens * mesh.get_data_parallel_world_size()
         stats["reward_mean"] = float(batch["rewards"].mean())
-        stats["rollout_tokens_per_s"] = gen_tokens / batch["rollout_s"]
+        slowest = torch.tensor([batch["rollout_s"]], dtype=torch.float64, device=self.device)
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            slowest = slowest.float() if self.device.type == "cuda" else slowest
+            dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+        stats["rollout_s"] = float(slowest)
+        stats["rollout_tokens_per_s"] = gen_tokens / max(stats["rollout_s"], 1e-9)
         return stats
 
     def train(self):

@@ -20,7 +20,12 @@ class _FakeStore:
         self.kv[k] = v.encode() if isinstance(v, str) else v
 
     def get(self, k):
+        if k not in self.kv:
+            raise AssertionError("a get() of a missing key blocks on a real store")
         return self.kv[k]
+
+    def check(self, keys):
+        return all(k in self.kv for k in keys)
 
 
 def test_heartbeat_detects_silent_rank_with_fake_clock():
@@ -30,13 +35,18 @@ def test_heartbeat_detects_silent_rank_with_fake_clock():
     store = _FakeStore()
     a = Heartbeat(0, 10.0, store, rank=0, world_size=3, clock=lambda: now[0])
     b = Heartbeat(0, 10.0, store, rank=1, world_size=3, clock=lambda: now[0])
-    assert a.dead_peers() == [2]            # rank 2 never joined
+    assert a.dead_peers() == []             # rank 2 has not joined yet, but the timeout has not passed either
+    now[0] += 11.0
+    b.beat(0)
+    assert a.dead_peers() == [2]            # ... now it has: a rank that never publishes is reported
     c = Heartbeat(0, 10.0, store, rank=2, world_size=3, clock=lambda: now[0])
     assert a.dead_peers() == []
     now[0] += 8.0
     b.beat(5)
+    assert a.dead_peers() == []
     now[0] += 8.0                            # rank 2 silent for 16 s, rank 1 for 8 s
     assert a.dead_peers() == [2]
+    assert a.peer_steps() == {1: 5, 2: -1}
     with pytest.raises(RankFailure) as e:
         a.raise_if_peer_dead()
     assert e.value.ranks == [2]

@@ -109,3 +109,89 @@ def test_trainer_on_preprocessed_files(tmp_path):
     tr = Trainer(cfg)
     losses = [float(tr.train_step(s)[0]) for s in range(2)]
     assert all(np.isfinite(losses))
+
+
+def test_long_conversation_masks_survive_serialisation(tmp_path):
+    """A 70-turn conversation has more mask ranges than the 500-character index field holds: they go to
+    the side table, every user turn stays masked, and the record reads back identical."""
+    from ironcore_b200.data.data_config import DatasetConfig, UniversalDataConfig
+    from ironcore_b200.data.dataset import BinaryDataset
+    from ironcore_b200.data.serializer import RANGES_NAME, DataSerializer
+    from ironcore_b200.tokenizer import Tokenizer
+
+    msgs = []
+    for i in range(70):
+        msgs.append({"role": "user", "content": f"question number {i} with some padding text"})
+        msgs.append({"role": "assistant", "content": f"reply {i}"})
+    short = [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "hello"}]
+    src = tmp_path / "long.jsonl"
+    src.write_text(json.dumps({"messages": msgs}) + "\n" + json.dumps({"messages": short}) + "\n")
+    ds_cfg = DatasetConfig(name="long", source=str(src), task_type="sft", output_path=tmp_path / "out")
+    tok = Tokenizer(50257, 50256, None)
+    ser = DataSerializer(UniversalDataConfig(datasets=[ds_cfg]), tok)
+    want_tokens, want_masks = ser._chat_tokens(msgs)
+    assert len(want_masks) == 70 and len(json.dumps(want_masks)) > 500
+    ser.serialize(ds_cfg, force=True)
+    assert (tmp_path / "out" / RANGES_NAME).exists()
+    ds = BinaryDataset(tmp_path / "out")
+    rec = ds.sample(0)
+    assert rec["mask_ranges"] == want_masks and rec["tokens"].tolist() == want_tokens
+    assert str(ds.index[0]["mask_ranges"]).startswith("@")
+    assert ds.sample(1)["mask_ranges"] == ser._chat_tokens(short)[1]      # short ones stay inline JSON
+    assert str(ds.index[1]["mask_ranges"]).startswith("[")
+
+
+def test_chat_template_of_the_tokenizer_is_used(tmp_path):
+    """With a tokenizer that carries a chat template the serializer renders through it and masks the
+    non-assistant turns by prefix rendering."""
+    from ironcore_b200.data.data_config import DatasetConfig, UniversalDataConfig
+    from ironcore_b200.data.serializer import DataSerializer
+
+    class TemplateTok:
+        eos_token_id = 1
+        vocab_size = 300
+        chat_template = "stub"
+
+        def encode(self, text):
+            return [ord(c) % 256 for c in text]
+
+        def apply_chat_template(self, messages, tokenize=True, add_generation_prompt=False, chat_template=None):
+            tag = chat_template or self.chat_template
+            text = "<bos>" + "".join(f"[{tag}:{m['role']}]{m['content']}</s>" for m in messages)
+            return self.encode(text)
+
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "2+2?"},
+            {"role": "assistant", "content": "4"}, {"role": "user", "content": "3+3?"},
+            {"role": "assistant", "content": "6"}]
+    dummy = DatasetConfig(name="d", source=str(tmp_path), task_type="sft")
+    ser = DataSerializer(UniversalDataConfig(datasets=[dummy]), TemplateTok())
+    tokens, masks = ser._chat_tokens(msgs)
+    text = "".join(chr(t) for t in tokens)
+    assert text.startswith("<bos>[stub:system]")
+    kept = "".join(c for i, c in enumerate(text) if not any(a <= i < b for a, b in masks))
+    assert kept == "[stub:assistant]4</s>[stub:assistant]6</s>"
+    # a per-dataset template overrides the tokenizer's
+    tokens2, _ = ser._chat_tokens(msgs, template="custom")
+    assert "[custom:user]" in "".join(chr(t) for t in tokens2)
+
+
+def test_pretrain_mixing_follows_the_ratios(tmp_path):
+    from ironcore_b200.data.dataset import WeightedMixingDataset
+    from ironcore_b200.data.serializer import BIN_NAME, IDX_DTYPE, IDX_NAME
+
+    dirs = []
+    for name, fill in (("a", 7), ("b", 9)):
+        d = tmp_path / name
+        d.mkdir()
+        np.full(16 * 400, fill, dtype=np.uint16).tofile(d / BIN_NAME)
+        np.save(d / IDX_NAME, np.array([(0, 16 * 400, "pretrain", 0, "[]")], dtype=IDX_DTYPE))
+        dirs.append(d)
+    ds = WeightedMixingDataset(dirs, [0.9, 0.1], "pretrain", "train", 16, [1.0, 0.0, 0.0], epochs=1)
+    firsts = [int(x["tokens"][0]) for x in ds]
+    assert len(firsts) == 800
+    share_a = firsts.count(7) / len(firsts)
+    assert abs(share_a - 0.9) < 0.01, share_a
+    # both ranks together see the same multiset, split evenly
+    r0 = list(WeightedMixingDataset(dirs, [0.9, 0.1], "pretrain", "train", 16, [1.0, 0.0, 0.0], dp_rank=0, dp_size=2, epochs=1))
+    r1 = list(WeightedMixingDataset(dirs, [0.9, 0.1], "pretrain", "train", 16, [1.0, 0.0, 0.0], dp_rank=1, dp_size=2, epochs=1))
+    assert len(r0) + len(r1) == 800 and abs(len(r0) - len(r1)) <= 1
