@@ -181,7 +181,7 @@ def run_ours(args):
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if int(flag.item()) == 0:
             fallback = fallback or "another rank failed the probe step"
-            native.status_tensor(dev).zero_()
+            native.clear_status(dev)
             trainer._graph = None
             trainer._static_loss = None
             del trainer, keep

@@ -8,8 +8,8 @@ import torch
 
 
 def bench_attention(results, quick: bool = False):
-    from . import attention
-    from .bench_kernels import _flush_buffer, time_cuda
+    from ironcore_b200.ops import attention
+    from .kernels import _flush_buffer, time_cuda
 
     flush = _flush_buffer()
     cases = [("llama7b", 1, 4096, 32, 32, 128), ("llama7b_tp8", 1, 4096, 4, 4, 128), ("gqa", 2, 4096, 16, 4, 128),

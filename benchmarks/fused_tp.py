@@ -1,7 +1,7 @@
 """Micro-benchmark of the fused TP kernels against the NCCL + GEMM composition.
 
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 \
-        -m ironcore_b200.parallel.bench_fused [--tokens 4096 --width 4096 --ffn 11008]
+        -m benchmarks.fused_tp [--tokens 4096 --width 4096 --ffn 11008]
 
 Times (CUDA events, max over ranks, L2 flushed between launches) the four call sites of a
 Llama-shape layer at tensor-parallel size N and prints one JSON line per case with the
@@ -35,8 +35,8 @@ def main():
     from ironcore_b200.parallel.fused_comm import FusedTP
 
     t, d, f = args.tokens, args.width, args.ffn
-    ws = FusedTP(t, d, dist.group.WORLD)                 # NVLS form when the fabric offers multicast
-    ws_p2p = FusedTP(t, d, dist.group.WORLD, nvls=False) if ws.nvls else ws   # plain P2P stores / loads
+    ws = FusedTP(t, d, dist.group.WORLD, num_slots=1)    # NVLS form when the fabric offers multicast
+    ws_p2p = FusedTP(t, d, dist.group.WORLD, nvls=False, num_slots=1) if ws.nvls else ws   # plain P2P stores / loads
     rows = t // world
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     peak_tflops, link_gbs = 1414.0, 770.0
@@ -121,6 +121,46 @@ def main():
         flops = 2.0 * t * d * k_local
         wire = (world - 1) * rows * d * 2
         cases.append((name, "gemm_rs", fused, nccl, gemm_only, flops, wire))
+    # chains across a norm boundary: row-parallel GEMM -> reduce-scatter (+residual) -> RMSNorm -> all-gather ->
+    # column-parallel GEMM. "fused": one producer kernel (GEMM + reduce + norm + push) and one consumer kernel that
+    # only waits; "separate": the two fused GEMM+collective kernels with a norm kernel between them.
+    for name, k_local, n_local in (("attn_out_norm_gate_up", d // world, 2 * f // world),
+                                   ("down_norm_qkv", f // world, 3 * d // world)):
+        k_local, n_local = (k_local + 7) // 8 * 8, (n_local + 7) // 8 * 8
+        a = torch.randn(t, k_local, device="cuda").bfloat16()
+        w = (torch.randn(k_local, d, device="cuda") / (k_local * world) ** 0.5).bfloat16()
+        res = torch.randn(rows, d, device="cuda").bfloat16()
+        gamma = torch.ones(d, device="cuda").bfloat16()
+        w2 = torch.randn(d, n_local, device="cuda").bfloat16()
+        out = torch.empty(rows, d, device="cuda", dtype=torch.bfloat16)
+        full = torch.empty(t, d, device="cuda", dtype=torch.bfloat16)
+
+        def fused(ws=ws, a=a, w=w, res=res, gamma=gamma, w2=w2, n_local=n_local):
+            slot = ws.slots[0]
+            ws.gemm_rs(a, w, b_major=1, residual=res, norm=(gamma, 1e-5, 0.0, slot))
+            return ws.ag_gemm(slot.local, w2, a_major=0, b_major=1, n=n_local, slot=slot, pushed=True)
+
+        def separate(ws=ws, a=a, w=w, res=res, gamma=gamma, w2=w2, n_local=n_local):
+            h = ws.gemm_rs(a, w, b_major=1, residual=res)
+            y = kernels.norm_fwd(h, gamma, None, 1e-5, True)[0]
+            return ws.ag_gemm(y, w2, a_major=0, b_major=1, n=n_local)
+
+        def nccl(a=a, w=w, res=res, gamma=gamma, w2=w2, out=out, full=full):
+            y = kernels.mm_nn(a, w)
+            dist.reduce_scatter_tensor(out, y)
+            yn = kernels.norm_fwd(out, gamma, None, 1e-5, True, residual=res)[0]
+            dist.all_gather_into_tensor(full, yn)
+            return kernels.mm_nn(full, w2)
+
+        def gemm_only(a=a, w=w, gamma=gamma, w2=w2, full=full, out=out):
+            kernels.mm_nn(a, w)
+            kernels.norm_fwd(out, gamma, None, 1e-5, True)
+            kernels.mm_nn(full, w2)
+
+        flops = 2.0 * t * d * (k_local + n_local)
+        wire = 2 * (world - 1) * rows * d * 2
+        cases.append((name, "rs_norm_ag_chain", fused, nccl, gemm_only, flops, wire))
+        cases.append((name + "_separate_kernels", "rs_norm_ag_chain", separate, nccl, gemm_only, flops, wire))
     wanted = {c for c in args.cases.split(",") if c}
     for name, kind, fused, nccl, gemm_only, flops, wire in cases:
         if wanted and name not in wanted:
@@ -157,18 +197,18 @@ def main():
         tg = timeit(gemm_only)
         roof_ms = max(flops / (peak_tflops * 1e9), wire / (link_gbs * 1e6))
         if rank == 0:
-            print(json.dumps({"case": name, "kind": kind, "world": world, "nvls": ws.nvls, "ag_batch": os.environ.get("ICB_AG_BATCH", "default"), "fused_ms": tf,
+            print(json.dumps({"case": name, "kind": kind, "world": world, "nvls": ws.nvls, "fused_ms": tf,
                               "fused_p2p_ms": tp, "max_abs_err_vs_nccl": err, "ref_abs_max": scale, "nccl_plus_gemm_ms": tn,
                               "gemm_only_ms": tg, "roofline_ms": roof_ms, "fraction_of_roofline": roof_ms / tf,
                               "wire_mb": wire / 1e6, "gflop": flops / 1e9}), flush=True)
     torch.cuda.synchronize()
     native.check_status()
     dist.barrier()
-    import threading
+    import faulthandler
 
-    threading.Timer(30.0, lambda: os._exit(0)).start()   # never let a stuck communicator teardown hold the GPUs
+    faulthandler.dump_traceback_later(45.0, exit=True)   # a stuck communicator teardown ends with exit status 1
     dist.destroy_process_group()
-    os._exit(0)
+    faulthandler.cancel_dump_traceback_later()
 
 
 if __name__ == "__main__":

@@ -1,6 +1,6 @@
 """Micro-benchmarks of the native kernels against their library counterparts.
 
-``python -m ironcore_b200.ops.bench_kernels [--out FILE] [--quick]`` times each kernel
+``python -m benchmarks.kernels [--out FILE] [--quick]`` times each kernel
 with CUDA events (3 warm-up launches, L2 flushed between timed launches by writing a
 256 MiB buffer) and prints one JSON line per case with achieved TFLOP/s or GB/s.
 """
@@ -38,7 +38,7 @@ def time_cuda(fn, iters: int = 10, warmup: int = 3, flush=None) -> float:
 
 
 def bench_gemm(results, quick: bool):
-    from . import kernels
+    from ironcore_b200.ops import kernels
 
     shapes = [
         ("qkv_7b", 4096, 12288, 4096), ("out_7b", 4096, 4096, 4096), ("gateup_7b", 4096, 22016, 4096),
@@ -66,7 +66,7 @@ def bench_gemm(results, quick: bool):
 
 
 def bench_elementwise(results, quick: bool):
-    from . import kernels
+    from ironcore_b200.ops import kernels
 
     flush = _flush_buffer()
     m, d = 16384, 4096
@@ -111,7 +111,7 @@ def main(argv=None):
         bench_elementwise(results, args.quick)
     if only is None or "attention" in only:
         try:
-            from .bench_attention import bench_attention
+            from .attention import bench_attention
         except ImportError:
             bench_attention = None
         if bench_attention is not None:

@@ -1,6 +1,6 @@
 """Launch one native kernel a few times on a small (but larger-than-L2) case, for ``ncu``.
 
-    python -m ironcore_b200.ops.profile_kernels --kernel gemm|gemm_wgrad|flash_fwd|flash_bwd|rmsnorm|swiglu|adam|ag_gemm|gemm_rs|zero_step|moe_dispatch
+    python -m benchmarks.profile_kernels --kernel gemm|gemm_wgrad|flash_fwd|flash_bwd|rmsnorm|swiglu|adam|ag_gemm|gemm_rs|zero_step|moe_dispatch
 
 ``ag_gemm`` / ``gemm_rs`` / ``zero_step`` / ``moe_dispatch`` run the fused compute+collective kernels on a one-rank group (the peer table
 points at this GPU's own buffers), which exercises the same code path — copy warps, flags, P2P
@@ -19,7 +19,7 @@ def main(argv=None):
     ap.add_argument("--kernel", required=True)
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args(argv)
-    from . import attention, kernels, native
+    from ironcore_b200.ops import attention, kernels, native
 
     dev = "cuda"
     torch.manual_seed(0)
@@ -57,7 +57,7 @@ def main(argv=None):
         os.environ.setdefault("MASTER_PORT", "29577")
         torch.cuda.set_device(0)
         dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
-        from ..parallel.fused_comm import FusedTP
+        from ironcore_b200.parallel.fused_comm import FusedTP
 
         t, d = 8192, 4096
         ws = FusedTP(t, d, dist.group.WORLD)
@@ -78,7 +78,7 @@ def main(argv=None):
         torch.cuda.set_device(0)
         dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
         if k == "zero_step":
-            from ..optim.fused_zero import FusedZeroStep
+            from ironcore_b200.optim.fused_zero import FusedZeroStep
 
             n = 128 * 1024 * 1024      # 256 MiB of bf16 parameters, 512 MiB of fp32 gradients
 
@@ -93,7 +93,7 @@ def main(argv=None):
             fn = lambda: fz.step(regions, 0, m, v, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, step_size=1e-3,
                                  grad_scale=1.0, clip=1.0)
         else:
-            from ..parallel.fused_moe import FusedEP
+            from ironcore_b200.parallel.fused_moe import FusedEP
 
             t, d, e, kk = 8192, 2048, 64, 6
             ws = FusedEP(dist.group.WORLD, e, kk, t, d, torch.bfloat16, 1.0)

@@ -1,7 +1,7 @@
 """Small driver for profilers: a few layers of a named model shape, a couple of micro-batch
 forward + backward passes and one optimizer step on one GPU.
 
-    python -m ironcore_b200.utils.profile_step --layers 2 --iters 2 [--shape llama7b|qwen1p5b|gpt2]
+    python -m benchmarks.profile_step --layers 2 --iters 2 [--shape llama7b|qwen1p5b|gpt2]
 
 Meant to be wrapped by ``ncu --metrics gpu__time_duration.sum`` (one pass, every launch) or by
 ``ncu --set full -k regex:<kernel> -c 3`` for one kernel; it keeps the device footprint to a few GB."""
@@ -31,9 +31,9 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=2)
     ap.add_argument("--micro-batch", type=int, default=1)
     args = ap.parse_args(argv)
-    from ..config import default_config, validate_config
-    from ..ops import native
-    from ..trainer import Trainer
+    from ironcore_b200.config import default_config, validate_config
+    from ironcore_b200.ops import native
+    from ironcore_b200.trainer import Trainer
 
     c = default_config()
     c.model(name="llama" if args.shape != "gpt2" else "gpt2", num_layers=args.layers, precision="bf16", dropout_embd=0.0,

@@ -13,6 +13,14 @@
 // have arrived, sum them in fp32, add bias / residual and write the output shard.
 // Counters are cumulative (target = t * epoch), receive buffers alternate by call parity on
 // the host side, so nothing is ever re-zeroed.
+//
+// Fused follow-up (norm_gamma != null): under sequence parallelism the reduced rows are the residual
+// stream, and what comes next is RMSNorm -> all-gather -> column-parallel GEMM. In this mode a reducer
+// warp owns whole rows: it sums the partials (+ bias + residual), stores the residual-stream row,
+// normalises it (fp32 statistics, gain applied) and stores the normalised row straight into every
+// rank's gather buffer of the next GEMM (P2P stores, or one multimem.st through the NVSwitch), then
+// bumps the per-128-row arrival counters that the all-gather GEMM kernel polls. The norm kernel, the
+// copy into the gather buffer and the push phase of the following all-gather GEMM disappear.
 #include "gemm_common.cuh"
 #include "host_common.h"
 #include "ptx.cuh"
@@ -37,11 +45,213 @@ struct RsArgs {
   const uint8_t* mc_recv;          // multicast (NVLS) address of the receive buffer, or null (see below)
   int in_fmt;
   int* status;
+  // ---- fused RMSNorm + all-gather push of the reduced rows (norm_gamma == null: off) ----
+  const void* norm_gamma;          // [N] gain, 16-bit
+  float norm_eps, norm_w_offset;   // y = h * rsqrt(mean(h^2) + eps) * (gamma + w_offset)
+  float* norm_rstd;                // [rows_per_rank] fp32, kept for the backward pass
+  uint8_t* const* ag_peers;        // device array [world]: every rank's gather buffer [world * rows_per_rank][N]
+  uint8_t* ag_mc;                  // multicast address of the gather buffer or null (P2P stores)
+  int* const* ag_peer_ready;       // device array [world]: every rank's per-128-row arrival counters
+  int ag_rows_per_unit;            // consecutive rows a warp finishes before it publishes once
+  int ag_add_per_unit;             // counter increment per unit (a 128-row block totals 128 * N * 2 / 8192)
 };
+
+template <bool BF16>
+__device__ __forceinline__ void rs_acc8(float (&a)[8], const uint4& u) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const float2 f = BF16 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
+    a[2 * t] += f.x;
+    a[2 * t + 1] += f.y;
+  }
+}
+template <bool BF16>
+__device__ __forceinline__ uint4 rs_pack8(const float (&a)[8]) {
+  uint4 o;
+  if (BF16) {
+    o.x = pack_bf16x2(a[0], a[1]); o.y = pack_bf16x2(a[2], a[3]);
+    o.z = pack_bf16x2(a[4], a[5]); o.w = pack_bf16x2(a[6], a[7]);
+  } else {
+    o.x = pack_f16x2(a[0], a[1]); o.y = pack_f16x2(a[2], a[3]);
+    o.z = pack_f16x2(a[4], a[5]); o.w = pack_f16x2(a[6], a[7]);
+  }
+  return o;
+}
+
+// Row-owning reduce phase with the norm and the all-gather push fused in (see the header comment).
+// One warp per unit of `ag_rows_per_unit` consecutive rows; a lane covers 8 columns of every
+// 256-column stripe. kCU stripes of kSB source ranks are loaded together, so each lane keeps
+// kCU * kSB 16-byte loads in flight (the phase is latency bound: a warp owns only a few rows).
+// The counters of a finished unit are published after the loads of the next unit have been issued:
+// by then the unit's remote stores have been acknowledged and the system-scope fence is cheap.
+template <bool BF16, int kCU, int kSB>
+__device__ __noinline__ void rs_reduce_norm_push(const RsArgs& args, int warp, int lane) {
+  const int nwarps = kGemmThreads / 32;
+  const int gw = blockIdx.x * nwarps + warp;
+  const int n_gw = gridDim.x * nwarps;
+  const int N = args.N;
+  const int units = args.rows_per_rank / args.ag_rows_per_unit;
+  const int target = args.world * (*args.epoch_ptr + 1);
+  const size_t slot_stride = (size_t)args.rows_per_rank * N * 2;   // bytes between two source ranks' slots
+  int checked_lm = -1, checked_ok = 0;
+  int pending_rb = -1;                                             // unit whose counters are not yet published
+  auto publish = [&](int rb) {
+    __syncwarp();
+    for (int p = lane; p < args.world - 1; p += 32) {
+      const int q = (args.rank + 1 + p) % args.world;
+      __threadfence_system();
+      red_relaxed_sys_add(args.ag_peer_ready[q] + rb, args.ag_add_per_unit);
+    }
+    __syncwarp();
+  };
+  for (int u = gw; u < units; u += n_gw) {
+    const int row0 = u * args.ag_rows_per_unit;
+    const int lm = row0 >> 7;
+    if (lm != checked_lm) {
+      // all column tiles of this 128-row block must have arrived from every rank
+      int ok = 1;
+      for (int nt = lane; nt < args.num_n_tiles; nt += 32)
+        ok &= wait_flag_sys(args.flags + lm * args.num_n_tiles + nt, target, args.status, kTimeoutPeerFlag,
+                            lm * args.num_n_tiles + nt) ? 1 : 0;
+      checked_ok = __all_sync(0xffffffffu, ok);
+      checked_lm = lm;
+    }
+    if (!checked_ok) continue;
+    for (int r = 0; r < args.ag_rows_per_unit; ++r) {
+      const int lrow = row0 + r;
+      uint8_t* out_row = reinterpret_cast<uint8_t*>(args.out) + (size_t)lrow * args.ldo * 2;
+      const uint8_t* res_row = args.residual != nullptr
+                                   ? reinterpret_cast<const uint8_t*>(args.residual) + (size_t)lrow * args.ldr * 2
+                                   : nullptr;
+      // ---- pass 1: sum of the partials (+ bias + residual) -> residual-stream row, sum of squares
+      float ss = 0.f;
+      for (int c0 = lane * 8; c0 < N; c0 += 256 * kCU) {
+        float acc[kCU][8];
+#pragma unroll
+        for (int i = 0; i < kCU; ++i) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+        }
+        uint4 rv[kCU];
+        if (res_row != nullptr) {
+#pragma unroll
+          for (int i = 0; i < kCU; ++i) {
+            const int col = c0 + i * 256;
+            if (col < N) rv[i] = *reinterpret_cast<const uint4*>(res_row + (size_t)col * 2);
+          }
+        }
+        if (args.mc_recv != nullptr) {
+          uint4 v[kCU];
+#pragma unroll
+          for (int i = 0; i < kCU; ++i) {
+            const int col = c0 + i * 256;
+            if (col < N) {
+              const uint8_t* p = args.mc_recv + (((size_t)args.rank * args.rows_per_rank + lrow) * N + col) * 2;
+              v[i] = BF16 ? multimem_ld_reduce_bf16x8(p) : multimem_ld_reduce_f16x8(p);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < kCU; ++i)
+            if (c0 + i * 256 < N) rs_acc8<BF16>(acc[i], v[i]);
+        } else {
+          const uint8_t* base = args.recv + ((size_t)lrow * N) * 2;
+          for (int s0 = 0; s0 < args.world; s0 += kSB) {
+            uint4 v[kSB][kCU];
+#pragma unroll
+            for (int sb = 0; sb < kSB; ++sb) {
+              if (s0 + sb < args.world) {
+#pragma unroll
+                for (int i = 0; i < kCU; ++i) {
+                  const int col = c0 + i * 256;
+                  if (col < N)
+                    v[sb][i] = __ldcv(reinterpret_cast<const uint4*>(base + (s0 + sb) * slot_stride + (size_t)col * 2));
+                }
+              }
+            }
+#pragma unroll
+            for (int sb = 0; sb < kSB; ++sb) {
+              if (s0 + sb < args.world) {
+#pragma unroll
+                for (int i = 0; i < kCU; ++i)
+                  if (c0 + i * 256 < N) rs_acc8<BF16>(acc[i], v[sb][i]);
+              }
+            }
+          }
+        }
+        if (pending_rb >= 0) {      // the previous unit's stores have had a whole load round trip to land
+          publish(pending_rb);
+          pending_rb = -1;
+        }
+#pragma unroll
+        for (int i = 0; i < kCU; ++i) {
+          const int col = c0 + i * 256;
+          if (col < N) {
+            if (args.bias != nullptr)
+              rs_acc8<BF16>(acc[i], *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(args.bias) +
+                                                                     (size_t)col * 2));
+            if (res_row != nullptr) rs_acc8<BF16>(acc[i], rv[i]);
+            const uint4 o = rs_pack8<BF16>(acc[i]);
+            *reinterpret_cast<uint4*>(out_row + (size_t)col * 2) = o;
+            // statistics of the rounded values: the backward pass re-reads exactly these
+            float hr[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) hr[j] = 0.f;
+            rs_acc8<BF16>(hr, o);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss += hr[j] * hr[j];
+          }
+        }
+      }
+      ss = warp_sum(ss);
+      const float rstd = rsqrtf(ss / N + args.norm_eps);
+      if (lane == 0 && args.norm_rstd != nullptr) args.norm_rstd[lrow] = rstd;
+      // ---- pass 2: normalise (this lane re-reads its own stores) and push into every gather buffer
+      const size_t g_row = ((size_t)args.rank * args.rows_per_rank + lrow) * N * 2;
+      for (int c0 = lane * 8; c0 < N; c0 += 256 * kCU) {
+        uint4 y[kCU];
+#pragma unroll
+        for (int i = 0; i < kCU; ++i) {
+          const int col = c0 + i * 256;
+          if (col < N) {
+            float h[8], g[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { h[j] = 0.f; g[j] = args.norm_w_offset; }
+            rs_acc8<BF16>(h, *reinterpret_cast<const uint4*>(out_row + (size_t)col * 2));
+            rs_acc8<BF16>(g, *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(args.norm_gamma) +
+                                                             (size_t)col * 2));
+#pragma unroll
+            for (int j = 0; j < 8; ++j) h[j] = h[j] * rstd * g[j];
+            y[i] = rs_pack8<BF16>(h);
+          }
+        }
+        if (args.ag_mc != nullptr) {
+#pragma unroll
+          for (int i = 0; i < kCU; ++i) {
+            const int col = c0 + i * 256;
+            if (col < N) multimem_st_v4(args.ag_mc + g_row + (size_t)col * 2, y[i]);
+          }
+        } else {
+          for (int q = 0; q < args.world; ++q) {
+            uint8_t* dst = args.ag_peers[(args.rank + q) % args.world] + g_row;
+#pragma unroll
+            for (int i = 0; i < kCU; ++i) {
+              const int col = c0 + i * 256;
+              if (col < N) *reinterpret_cast<uint4*>(dst + (size_t)col * 2) = y[i];
+            }
+          }
+        }
+      }
+    }
+    pending_rb = (args.rank * args.rows_per_rank + row0) >> 7;
+  }
+  if (pending_rb >= 0) publish(pending_rb);
+}
 
 template <int B_MAJOR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const RsArgs args) {
+gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ RsArgs args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem + GemmSmem::a_off;
@@ -231,7 +441,16 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 
   // ---------------- reduce phase: every warp of the CTA sums arrived partials ----------------
-  {
+  if (args.norm_gamma != nullptr) {
+    // 16 loads per lane in flight whatever the group size: two source ranks x 8 stripes, or four x 4
+    if (args.in_fmt == 1) {
+      if (args.world <= 2) rs_reduce_norm_push<true, 8, 2>(args, warp, lane);
+      else rs_reduce_norm_push<true, 4, 4>(args, warp, lane);
+    } else {
+      if (args.world <= 2) rs_reduce_norm_push<false, 8, 2>(args, warp, lane);
+      else rs_reduce_norm_push<false, 4, 4>(args, warp, lane);
+    }
+  } else {
     const int nwarps = kGemmThreads / 32;
     const int gw = blockIdx.x * nwarps + warp;
     const int n_gw = gridDim.x * nwarps;
@@ -378,10 +597,11 @@ using namespace icb;
 //   owner reduces them through the switch (multimem.ld_reduce); same form on every call and rank of a workspace.
 //   N must be a multiple of 8; rows_per_rank a multiple of 128; epoch_ptr = device int with the number of calls already
 //   made on this pair of buffers (same on every rank; the caller increments it after the call).
-ICB_API int icb_gemm_rs(const void* A, const void* B, void* out, const void* bias, const void* residual, int M, int N,
+static int gemm_rs_impl(const void* A, const void* B, void* out, const void* bias, const void* residual, int M, int N,
                         int K, long long lda, long long ldb, long long ldo, long long ldr, int b_major, int in_dtype,
                         const void* const* peer_recv, int* const* peer_flags, const void* recv, const int* flags,
-                        int rank, int world, const int* epoch_ptr, int* status, void* stream_, const void* mc_recv) {
+                        int rank, int world, const int* epoch_ptr, int* status, void* stream_, const void* mc_recv,
+                        const RsArgs* fused) {
   if (world < 1 || M % world != 0) return -2;
   const int rows_per_rank = M / world;
   if (rows_per_rank % 128 != 0 || N % 8 != 0) return -7;
@@ -408,7 +628,8 @@ ICB_API int icb_gemm_rs(const void* A, const void* B, void* out, const void* bia
     rc = make_tmap(&tmB, in_dtype, 2, B, dims, str, box, true);
   }
   if (rc) return rc;
-  RsArgs a;
+  RsArgs a{};
+  if (fused != nullptr) a = *fused;
   a.M = M; a.N = N; a.K = K;
   a.num_m_tiles = M / kBM;
   a.num_n_tiles = (N + kBN - 1) / kBN;
@@ -428,4 +649,46 @@ ICB_API int icb_gemm_rs(const void* A, const void* B, void* out, const void* bia
   if (total < grid) grid = total;
   if (b_major == 0) return launch_gemm_rs<0>(tmA, tmB, a, grid, stream);
   return launch_gemm_rs<1>(tmA, tmB, a, grid, stream);
+}
+
+ICB_API int icb_gemm_rs(const void* A, const void* B, void* out, const void* bias, const void* residual, int M, int N,
+                        int K, long long lda, long long ldb, long long ldo, long long ldr, int b_major, int in_dtype,
+                        const void* const* peer_recv, int* const* peer_flags, const void* recv, const int* flags,
+                        int rank, int world, const int* epoch_ptr, int* status, void* stream_, const void* mc_recv) {
+  return gemm_rs_impl(A, B, out, bias, residual, M, N, K, lda, ldb, ldo, ldr, b_major, in_dtype, peer_recv, peer_flags,
+                      recv, flags, rank, world, epoch_ptr, status, stream_, mc_recv, nullptr);
+}
+
+// icb_gemm_rs followed, inside the same kernel, by RMSNorm of the reduced rows and their all-gather:
+//   out[rows_per_rank, N]     = reduce_scatter_rows(A * B) (+ bias) (+ residual)        (the residual stream)
+//   gather_r[rank rows, N]    = out * rsqrt(mean(out^2) + eps) * (gamma + w_offset)      on every rank r
+//   rstd[rows_per_rank]       = the reciprocal root mean squares (fp32), for the backward pass
+// ag_peers / ag_peer_ready are the gather buffers ([world * rows_per_rank, N], 16-bit) and per-128-row arrival
+// counters of the all-gather GEMM that consumes the rows (icb_ag_gemm with flags bit 0); ag_mc is the multicast
+// address of that gather buffer or null. N * 2 bytes must divide 8192 or be a multiple of it (the counters
+// count 8 KiB chunks, as the push of icb_ag_gemm does).
+ICB_API int icb_gemm_rs_norm_ag(const void* A, const void* B, void* out, const void* bias, const void* residual, int M,
+                                int N, int K, long long lda, long long ldb, long long ldo, long long ldr, int b_major,
+                                int in_dtype, const void* const* peer_recv, int* const* peer_flags, const void* recv,
+                                const int* flags, int rank, int world, const int* epoch_ptr, int* status, void* stream_,
+                                const void* mc_recv, const void* gamma, float eps, float w_offset, float* rstd,
+                                void* const* ag_peers, void* ag_mc, int* const* ag_peer_ready) {
+  if (gamma == nullptr || ag_peers == nullptr || ag_peer_ready == nullptr) return -2;
+  const long long row_bytes = (long long)N * 2;
+  RsArgs f{};
+  if (row_bytes >= 8192) {
+    if (row_bytes % 8192) return -8;
+    f.ag_rows_per_unit = 1;
+    f.ag_add_per_unit = (int)(row_bytes / 8192);
+  } else {
+    if (8192 % row_bytes) return -8;
+    f.ag_rows_per_unit = (int)(8192 / row_bytes);
+    f.ag_add_per_unit = 1;
+  }
+  f.norm_gamma = gamma; f.norm_eps = eps; f.norm_w_offset = w_offset; f.norm_rstd = rstd;
+  f.ag_peers = reinterpret_cast<uint8_t* const*>(ag_peers);
+  f.ag_mc = reinterpret_cast<uint8_t*>(ag_mc);
+  f.ag_peer_ready = ag_peer_ready;
+  return gemm_rs_impl(A, B, out, bias, residual, M, N, K, lda, ldb, ldo, ldr, b_major, in_dtype, peer_recv, peer_flags,
+                      recv, flags, rank, world, epoch_ptr, status, stream_, mc_recv, &f);
 }

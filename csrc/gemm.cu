@@ -25,7 +25,6 @@
 // issuer, warps 2-5 = epilogue (one TMEM lane quarter each).
 #include "host_common.h"
 #include "ptx.cuh"
-#include <cstdlib>
 
 #include "gemm_common.cuh"
 
@@ -57,6 +56,7 @@ struct GemmArgs {
   uint8_t* ag_mc;                   // multicast (NVLS) address of the gathered buffer, or null: plain P2P stores
   int ag_batch;                     // chunks a copy warp pushes between two fence + publish steps (1..16)
   int ag_helpers;                   // 1: the four epilogue warps push chunks too before their first tile
+  int ag_push;                      // 0: the shards arrive from their producers, this kernel only waits
   unsigned long long* ag_debug;     // optional [grid][4] timestamps (ns): start, push done, first remote block ready, end
 };
 
@@ -204,9 +204,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       // than the few hundred nanoseconds of work the 4-stage ring buffers, so each block is polled once.
       unsigned long long ag_seen = 0ull;
       if (AG && args.ag_debug != nullptr) args.ag_debug[blockIdx.x * 4 + 0] = globaltimer_ns();
+      bool ag_gave_up = false;   // after one wait ran out the remaining tiles are not waited for
       auto ag_ensure_ready = [&](int rb) {
-        if (rb < 64 && ((ag_seen >> rb) & 1ull)) return;
-        wait_flag_sys(args.ag_ready + rb, ag_epoch * args.ag_chunks_per_block, args.status, kTimeoutPeerFlag);
+        if (ag_gave_up || (rb < 64 && ((ag_seen >> rb) & 1ull))) return;
+        if (!wait_flag_sys(args.ag_ready + rb, ag_epoch * args.ag_chunks_per_block, args.status, kTimeoutPeerFlag,
+                           rb)) {
+          ag_gave_up = true;
+          return;
+        }
         fence_proxy_async_all();
         if (args.ag_debug != nullptr && ag_seen == 0ull) args.ag_debug[blockIdx.x * 4 + 2] = globaltimer_ns();
         if (rb < 64) ag_seen |= (1ull << rb);
@@ -316,7 +321,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     __syncwarp();
   } else if (warp < 6) {
     // ------------------------------ epilogue ----------------------------------
-    if (AG && args.ag_helpers) ag_push_shard(args, blockIdx.x * 6 + (warp - 2), gridDim.x * 6, lane);
+    if (AG && args.ag_push && args.ag_helpers) ag_push_shard(args, blockIdx.x * 6 + (warp - 2), gridDim.x * 6, lane);
     const int et = threadIdx.x - 64;     // 0..127
     const int q = warp & 3;              // TMEM lane quarter this warp may read
     const int row = q * 32 + lane;
@@ -501,7 +506,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (et == 0) tma_store_wait<0>();
   }
 
-  if (AG && warp >= 6) {
+  if (AG && warp >= 6 && args.ag_push) {
     // ------------------------------ all-gather copy warps ----------------------
     // Two dedicated warps per CTA; with ag_helpers the four epilogue warps have already taken their share
     // of the chunks before their first accumulator was ready (warp slots 0..3), these are slots 4 and 5.
@@ -528,11 +533,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   }
 }
 
-template <int A_MAJOR, int B_MAJOR, bool AG, int BN>
-static int launch_gemm_bn(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const GemmArgs& args,
-                          int grid, cudaStream_t stream) {
+template <int A_MAJOR, int B_MAJOR, bool AG = false>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const GemmArgs& args,
+                       int grid, cudaStream_t stream) {
   static bool configured = false;
-  auto kern = gemm_kernel<A_MAJOR, B_MAJOR, AG, BN>;
+  auto kern = gemm_kernel<A_MAJOR, B_MAJOR, AG, kBN>;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
     if (e != cudaSuccess) {
@@ -543,30 +548,6 @@ static int launch_gemm_bn(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   }
   kern<<<grid, AG ? kGemmThreads + 64 : kGemmThreads, kGemmSmemBytes, stream>>>(tmA, tmB, tmC, args);
   return check_launch("gemm_kernel");
-}
-template <int A_MAJOR, int B_MAJOR, bool AG = false>
-static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const GemmArgs& args,
-                       int grid, cudaStream_t stream, int bn) {
-  if (bn == 128) return launch_gemm_bn<A_MAJOR, B_MAJOR, AG, 128>(tmA, tmB, tmC, args, grid, stream);
-  return launch_gemm_bn<A_MAJOR, B_MAJOR, AG, 256>(tmA, tmB, tmC, args, grid, stream);
-}
-
-// Tile width for a problem. Measured on B200: a 128-column tile costs 0.79 of a 256-column tile (the operand
-// feed, not the tensor pipe, bounds it), so it loses even on shapes with a ragged last wave (4096 x 1536 x 4096:
-// 0.083 ms vs 0.071 ms); 256 is the default, ICB_GEMM_BN=128 / 0 (per-problem choice) remain for experiments.
-static int pick_bn(long long m_tiles, int N, int groups, int sms) {
-  static int forced = -1;
-  if (forced < 0) {
-    const char* e = getenv("ICB_GEMM_BN");
-    const int v = e != nullptr ? atoi(e) : 256;   // 0 = choose per problem (wave fit), 128 / 256 = fixed
-    forced = (v == 128 || v == 256) ? v : 0;
-  }
-  if (forced) return forced;
-  const long long t256 = m_tiles * ((N + 255) / 256) * groups;
-  const long long t128 = m_tiles * ((N + 127) / 128) * groups;
-  const double c256 = (double)((t256 + sms - 1) / sms);
-  const double c128 = (double)((t128 + sms - 1) / sms) * 0.79;
-  return (c128 < c256 * 0.97) ? 128 : 256;
 }
 
 }  // namespace icb
@@ -595,7 +576,9 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, co
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -5;
   if (num_groups < 1) num_groups = 1;
 
-  const int bn = pick_bn((M + kBM - 1) / kBM, N, group_mode == 2 ? num_groups : 1, num_sms());
+  // 128 x 256 tiles throughout: a 128-column tile costs 0.79 of a 256-column one on B200 (the operand feed,
+  // not the tensor pipe, bounds it), so it loses even on shapes with a ragged last wave.
+  const int bn = kBN;
   CUtensorMap tmA, tmB, tmC;
   int rc;
   const uint64_t k_rows = (uint64_t)K;
@@ -639,7 +622,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, co
     args.ag_rank = 0; args.ag_world = 1; args.ag_rows_per_rank = 0; args.ag_row_bytes = 0;
     args.ag_local = nullptr; args.ag_peers = nullptr; args.ag_peer_signal = nullptr; args.ag_signal = nullptr;
     args.ag_ready = nullptr; args.ag_epoch_ptr = nullptr; args.ag_chunks_per_block = 1; args.ag_peer_ready = nullptr;
-    args.ag_mc = nullptr; args.ag_batch = 4; args.ag_debug = nullptr; args.ag_helpers = 0;
+    args.ag_mc = nullptr; args.ag_batch = 4; args.ag_debug = nullptr; args.ag_helpers = 0; args.ag_push = 0;
   }
   args.M = M; args.N = N; args.K = K;
   args.num_m_tiles = (M + kBM - 1) / kBM;
@@ -661,15 +644,15 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, co
   if (grid < 1) grid = 1;
 
   if (ag != nullptr) {
-    if (a_major == 0 && b_major == 0) return launch_gemm<0, 0, true>(tmA, tmB, tmC, args, grid, stream, bn);
-    if (a_major == 0 && b_major == 1) return launch_gemm<0, 1, true>(tmA, tmB, tmC, args, grid, stream, bn);
-    if (a_major == 1 && b_major == 1) return launch_gemm<1, 1, true>(tmA, tmB, tmC, args, grid, stream, bn);
+    if (a_major == 0 && b_major == 0) return launch_gemm<0, 0, true>(tmA, tmB, tmC, args, grid, stream);
+    if (a_major == 0 && b_major == 1) return launch_gemm<0, 1, true>(tmA, tmB, tmC, args, grid, stream);
+    if (a_major == 1 && b_major == 1) return launch_gemm<1, 1, true>(tmA, tmB, tmC, args, grid, stream);
     return -6;
   }
-  if (a_major == 0 && b_major == 0) return launch_gemm<0, 0>(tmA, tmB, tmC, args, grid, stream, bn);
-  if (a_major == 0 && b_major == 1) return launch_gemm<0, 1>(tmA, tmB, tmC, args, grid, stream, bn);
-  if (a_major == 1 && b_major == 0) return launch_gemm<1, 0>(tmA, tmB, tmC, args, grid, stream, bn);
-  return launch_gemm<1, 1>(tmA, tmB, tmC, args, grid, stream, bn);
+  if (a_major == 0 && b_major == 0) return launch_gemm<0, 0>(tmA, tmB, tmC, args, grid, stream);
+  if (a_major == 0 && b_major == 1) return launch_gemm<0, 1>(tmA, tmB, tmC, args, grid, stream);
+  if (a_major == 1 && b_major == 0) return launch_gemm<1, 0>(tmA, tmB, tmC, args, grid, stream);
+  return launch_gemm<1, 1>(tmA, tmB, tmC, args, grid, stream);
 }
 
 ICB_API int icb_gemm(const void* A, const void* B, void* C, const void* bias, const void* residual, int M, int N,
@@ -698,6 +681,9 @@ ICB_API int icb_set_ag_debug(void* buf) {
 //              rank); the caller increments it in stream order after this call.
 //   a_major 0: C[M = world*rows_per_rank, N] = gathered[M, K = width] * B        (forward / dgrad of a row-parallel layer)
 //   a_major 1: C[M = width, N] = gathered^T * B[K = world*rows_per_rank, N]      (wgrad: reduction over gathered rows)
+//   flags    : bit 0 = the shards are pushed by their producers (the fused reduce-scatter + norm kernel of
+//              every rank writes its normalised rows into all gather buffers and bumps the same counters):
+//              this kernel pushes nothing and only waits; bit 1 = the epilogue warps help pushing.
 //   gathered_mc: multicast (NVLS) address of `gathered` or null. With it the shard is pushed once with multimem.st
 //              and replicated by the NVSwitch; a workspace must use the same form on every call and rank.
 // The local shard is pushed to every peer with plain P2P stores by copy warps inside the same kernel;
@@ -706,7 +692,7 @@ ICB_API int icb_ag_gemm(void* gathered, const void* const* peers, int* const* pe
                         int* ready, int rank, int world, int rows_per_rank, int width, const int* epoch_ptr, const void* B,
                         void* C, const void* bias, const void* residual, int N, long long ldb, long long ldc,
                         long long ldr, int a_major, int b_major, int in_dtype, int out_f32, int* status,
-                        void* stream_, void* gathered_mc) {
+                        void* stream_, void* gathered_mc, int flags) {
   if (rows_per_rank % 128 != 0 || width % 32 != 0) return -7;   // 128-row blocks must be whole 8 KiB chunks
   GemmArgs ag;
   ag.ag_rank = rank; ag.ag_world = world; ag.ag_rows_per_rank = rows_per_rank;
@@ -719,26 +705,12 @@ ICB_API int icb_ag_gemm(void* gathered, const void* const* peers, int* const* pe
   ag.ag_ready = ready;
   ag.ag_epoch_ptr = epoch_ptr;
   ag.ag_mc = reinterpret_cast<uint8_t*>(gathered_mc);
-  {
-    // Publishing granularity: fewer chunks per fence make the first remote tiles ready earlier, more chunks
-    // amortise the system-scope fence. ICB_AG_BATCH overrides the default for experiments.
-    static int batch = -1;
-    if (batch < 0) {
-      const char* e = getenv("ICB_AG_BATCH");
-      int v = e != nullptr ? atoi(e) : 0;
-      batch = (v >= 1 && v <= 16) ? v : 0;
-    }
-    ag.ag_batch = batch > 0 ? batch : 4;
-  }
+  // Publishing granularity of the push: 4 chunks per fence (fewer make the first remote tiles ready earlier,
+  // more amortise the system-scope fence; 4 measured best at 2 ranks).
+  ag.ag_batch = 4;
   ag.ag_debug = g_ag_debug;
-  {
-    static int helpers = -1;
-    if (helpers < 0) {
-      const char* e = getenv("ICB_AG_HELPERS");
-      helpers = (e != nullptr && atoi(e) != 0) ? 1 : 0;
-    }
-    ag.ag_helpers = helpers;
-  }
+  ag.ag_push = (flags & 1) ? 0 : 1;
+  ag.ag_helpers = (flags & 2) ? 1 : 0;
   ag.ag_chunks_per_block = (int)(128LL * width * 2 / kAgChunkBytes);
   const int rows = world * rows_per_rank;
   const int M = a_major == 0 ? rows : width;

@@ -27,16 +27,33 @@ enum StatusCode : int {
   kBadArgument = 7,
 };
 
-// Roughly two seconds at ~1.9 GHz. Long enough for any legitimate wait inside
-// one kernel, short enough that a lost signal ends the kernel instead of the GPU.
-#ifndef ICB_WAIT_CYCLES
-#define ICB_WAIT_CYCLES (4000000000LL)
-#endif
+// The status block is a small int array in device memory, one per device:
+//   [0] code    first StatusCode a kernel reported (0 = none); set with atomicCAS, cleared by the host
+//   [1] limit   how long one wait may last, in microseconds; 0 selects the default below. Host-settable,
+//               so a test can make a wait run out in milliseconds
+//   [2] detail  what the first failing wait was waiting for (flag index), informational
+// Default limit: two seconds. Long enough for any legitimate wait inside one kernel, short enough
+// that a lost signal ends the kernel instead of the GPU.
+constexpr long long kDefaultWaitNs = 2000000000LL;
 
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
+}
+
+__device__ __forceinline__ long long wait_budget_ns(const int* status) {
+  if (status != nullptr) {
+    const int us = *reinterpret_cast<const volatile int*>(status + 1);
+    if (us > 0) return static_cast<long long>(us) * 1000LL;
+  }
+  return kDefaultWaitNs;
+}
+__device__ __forceinline__ bool status_is_set(const int* status) {
+  return status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0;
+}
+__device__ __forceinline__ void status_report(int* status, int code, int detail) {
+  if (status != nullptr && atomicCAS(status, 0, code) == 0) status[2] = detail;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -93,16 +110,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
                                           int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   if (*abort_flag) return false;
-  const long long t0 = clock64();
+  const unsigned long long t0 = globaltimer_ns();
+  // Twice the limit of a flag wait (plus a millisecond): the roles of a CTA wait on one another through
+  // mbarriers, so when the producer is held up by a peer flag every mbarrier wait downstream of it is held up
+  // for as long. The flag wait must be the one that runs out and names the cause; it then lets the pipeline
+  // move on, and the mbarrier waits complete.
+  const long long budget = 2 * wait_budget_ns(status) + 1000000LL;
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 32; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
     }
     if (*abort_flag) return false;
-    if (clock64() - t0 > ICB_WAIT_CYCLES) {
+    if (static_cast<long long>(globaltimer_ns() - t0) > budget) {
       *abort_flag = 1;
-      if (status != nullptr) atomicCAS(status, 0, code);
+      status_report(status, code, 0);
       return false;
     }
   }
@@ -349,34 +371,42 @@ __device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
   asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// Wait until *p >= target (system scope). Bounded; returns false on timeout
-// after writing `code` to the status word.
-__device__ __forceinline__ bool wait_flag_sys(const int* p, int target, int* status, int code) {
+// Wait until *p >= target (system scope). Bounded by the status block's limit; returns false after
+// writing `code` to the status word. Fails fast: once any wait has given up (status word non-zero), every
+// later flag wait on this device returns false at once, so a step with a silent peer costs one limit in
+// total, not one per wait. `detail` identifies the flag in the status block.
+__device__ __forceinline__ bool wait_flag_sys(const int* p, int target, int* status, int code, int detail = 0) {
   if (ld_acquire_sys(p) - target >= 0) return true;
-  const long long t0 = clock64();
+  if (status_is_set(status)) return false;
+  const unsigned long long t0 = globaltimer_ns();
+  const long long budget = wait_budget_ns(status);
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 16; ++i) {
       if (ld_acquire_sys(p) - target >= 0) return true;
       __nanosleep(64);
     }
-    if (clock64() - t0 > ICB_WAIT_CYCLES) {
-      if (status != nullptr) atomicCAS(status, 0, code);
+    if (status_is_set(status)) return false;
+    if (static_cast<long long>(globaltimer_ns() - t0) > budget) {
+      status_report(status, code, detail);
       return false;
     }
   }
 }
-__device__ __forceinline__ bool wait_flag_gpu(const int* p, int target, int* status, int code) {
+__device__ __forceinline__ bool wait_flag_gpu(const int* p, int target, int* status, int code, int detail = 0) {
   if (ld_acquire_gpu(p) - target >= 0) return true;
-  const long long t0 = clock64();
+  if (status_is_set(status)) return false;
+  const unsigned long long t0 = globaltimer_ns();
+  const long long budget = wait_budget_ns(status);
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 16; ++i) {
       if (ld_acquire_gpu(p) - target >= 0) return true;
       __nanosleep(32);
     }
-    if (clock64() - t0 > ICB_WAIT_CYCLES) {
-      if (status != nullptr) atomicCAS(status, 0, code);
+    if (status_is_set(status)) return false;
+    if (static_cast<long long>(globaltimer_ns() - t0) > budget) {
+      status_report(status, code, detail);
       return false;
     }
   }

@@ -26,9 +26,19 @@ class MLP(nn.Module):
                                            device=device, tp_group=tp_group)
         self.dropout = dropout
 
-    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-        h = self.activation(self.up_proj(x))
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, pregathered: bool = False,
+                next_norm=None, next_consumer=None):
+        """``pregathered``: ``x`` already sits in ``up_proj``'s gather slot on every rank. ``next_norm`` /
+        ``next_consumer``: the norm and column-parallel linear that follow this block; when given (and
+        fusable) the down projection also normalises its output into the consumer's gather slot and the
+        result is ``(out, normed)`` instead of ``out``."""
+        h = self.activation(self.up_proj(x, pregathered=pregathered) if pregathered else self.up_proj(x))
         if self.dropout > 0 and self.training:
             y = F.dropout(self.down_proj(h), self.dropout, True)
-            return y if residual is None else y + residual
+            y = y if residual is None else y + residual
+            return (y, None) if next_norm is not None else y
+        if next_norm is not None:
+            if self.down_proj.can_fuse_norm(h, next_norm, next_consumer):
+                return self.down_proj.forward_norm(h, residual, next_norm, next_consumer)
+            return self.down_proj(h, residual=residual), None
         return self.down_proj(h, residual=residual)

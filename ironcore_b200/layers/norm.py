@@ -30,9 +30,10 @@ class Norm(nn.Module):
         self.dim, self.eps, self.rms, self.weight_offset = dim, eps, rms, weight_offset
         self.layernorm = _NormParams(dim, bias and not rms, 1.0 - weight_offset, dtype, device)
 
-    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, return_sum: bool = False):
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, return_sum: bool = False,
+                out: Optional[torch.Tensor] = None):
         y, h = OF.norm(x, self.layernorm.weight, self.layernorm.bias, self.eps, self.rms, residual=residual,
-                       w_offset=self.weight_offset)
+                       w_offset=self.weight_offset, out=out)
         return (y, h) if return_sum else y
 
 

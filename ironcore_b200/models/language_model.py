@@ -257,6 +257,12 @@ class LanguageModel(BaseModule):
                                           tp_group=self.tp_group)
         return -ce.view(b, s)
 
+    def link_fused_norm_gather(self) -> int:
+        """See ``TransformerModel.link_fused_norm_gather``; called once the fused tensor-parallel
+        workspace has been attached to the parallel linears."""
+        fn = getattr(self.model, "link_fused_norm_gather", None)
+        return fn() if fn is not None else 0
+
     # ------------------------------------------------------------------ canonical (checkpoint) names
     def canonical_state_dict(self) -> "OrderedDict[str, torch.Tensor]":
         """Local shard under the reference's parameter names: the fused ``linear_qkv`` is split

@@ -71,32 +71,71 @@ class TransformerLayer(nn.Module):
                            dtype=dtype, device=device)
             self.is_moe = False
 
-    def _attend(self, normed, seq_len, pos_ids, cu_seqlens, attn_mask, residual):
-        qkv = self.linear_qkv(normed)
+        # set by ``LanguageModel.link_fused_norm_gather``: fuse reduce-scatter + norm + gather across the
+        # two norm boundaries this layer owns (attention output -> MLP, MLP output -> next layer)
+        self.fuse_norm_gather = False
+        self._next_layer = None
+
+    def _attend(self, normed, seq_len, pos_ids, cu_seqlens, attn_mask, residual, pregathered=False):
+        qkv = self.linear_qkv(normed, pregathered=True) if pregathered else self.linear_qkv(normed)
         ctx = self.attention(qkv, seq_len, pos_ids=pos_ids, cu_seqlens=cu_seqlens, attn_mask=attn_mask)
         if self.dropout_attn > 0 and self.training:
             out = F.dropout(self.attn_output(ctx), self.dropout_attn, True)
             return out if residual is None else out + residual
         return self.attn_output(ctx, residual=residual)
 
-    def forward(self, x: torch.Tensor, seq_len: int, pos_ids=None, cu_seqlens=None, attn_mask=None):
-        """x: [T_local, d]. Returns (x, aux_loss or None)."""
+    def set_next_layer(self, layer):
+        object.__setattr__(self, "_next_layer", layer)   # a plain reference, not a registered submodule
+
+    def _forward_fused(self, x, seq_len, pos_ids, cu_seqlens, attn_mask, prenormed):
+        """Pre-norm dense layer with both norm boundaries fused into the preceding row-parallel GEMM:
+        attention output -> (reduce-scatter + residual + post-attention norm + gather) -> MLP, and
+        MLP output -> (reduce-scatter + residual + next layer's input norm + gather) -> next layer."""
+        if prenormed is None:
+            n1, pushed = self.input_layernorm(x, out=self.linear_qkv.gather_target(x)), False
+        else:
+            n1, pushed = prenormed, True
+        qkv = self.linear_qkv(n1, pregathered=True) if pushed else self.linear_qkv(n1)
+        ctx = self.attention(qkv, seq_len, pos_ids=pos_ids, cu_seqlens=cu_seqlens, attn_mask=attn_mask)
+        up = self.mlp.up_proj
+        if self.attn_output.can_fuse_norm(ctx, self.post_attn_layernorm, up):
+            h, n2 = self.attn_output.forward_norm(ctx, x, self.post_attn_layernorm, up)
+            pushed2 = True
+        else:
+            h = self.attn_output(ctx, residual=x)
+            n2, pushed2 = self.post_attn_layernorm(h, out=up.gather_target(h)), False
+        nxt = self._next_layer
+        if nxt is not None and nxt.fuse_norm_gather:
+            out, next_normed = self.mlp(n2, residual=h, pregathered=pushed2, next_norm=nxt.input_layernorm,
+                                        next_consumer=nxt.linear_qkv)
+        else:
+            out, next_normed = self.mlp(n2, residual=h, pregathered=pushed2), None
+        return out, None, next_normed
+
+    def forward(self, x: torch.Tensor, seq_len: int, pos_ids=None, cu_seqlens=None, attn_mask=None, prenormed=None):
+        """x: [T_local, d]. Returns (x, aux_loss or None, normed_for_next_layer or None). ``prenormed``:
+        this layer's input norm of ``x``, already delivered into ``linear_qkv``'s gather slot by the
+        previous layer."""
+        if self.fuse_norm_gather and self.dropout_attn == 0:
+            return self._forward_fused(x, seq_len, pos_ids, cu_seqlens, attn_mask, prenormed)
         aux = None
-        n1 = self.input_layernorm(x)
+        # (not under post-norm, where the normalised tensor lives on as the residual)
+        n1 = self.input_layernorm(x, out=None if self.post_ln else self.linear_qkv.gather_target(x))
         if self.parallel_block:
             a = self._attend(n1, seq_len, pos_ids, cu_seqlens, attn_mask, residual=x)
             out = self.mlp(n1, residual=a)
             if self.is_moe:
                 out, aux = out
-            return out, aux
+            return out, aux, None
         res1 = n1 if self.post_ln else x
         x = self._attend(n1, seq_len, pos_ids, cu_seqlens, attn_mask, residual=res1)
-        n2 = self.post_attn_layernorm(x)
+        up = getattr(self.mlp, "up_proj", None)
+        n2 = self.post_attn_layernorm(x, out=up.gather_target(x) if (up is not None and not self.post_ln) else None)
         res2 = n2 if self.post_ln else x
         out = self.mlp(n2, residual=res2)
         if self.is_moe:
             out, aux = out
-        return out, aux
+        return out, aux, None
 
 
 class TransformerModel(nn.Module):
@@ -107,13 +146,36 @@ class TransformerModel(nn.Module):
         self.recompute = config.operation.activation_recompute
         self.use_reentrant = config.operation.recompute_strategy == "optimized"
 
+    def link_fused_norm_gather(self) -> int:
+        """Mark the layers whose norm boundaries can run inside the preceding row-parallel GEMM kernel
+        (pre-norm dense layers with RMSNorm, no dropout, fused workspace attached, no activation
+        recompute) and chain them. Returns the number of marked layers."""
+        n = 0
+        prev = None
+        for layer in self.layers:
+            ok = (not self.recompute and not layer.is_moe and not layer.parallel_block and not layer.post_ln
+                  and layer.dropout_attn == 0 and getattr(layer.mlp, "dropout", 0) == 0
+                  and getattr(layer.input_layernorm, "rms", False) and layer.input_layernorm.layernorm.bias is None
+                  and getattr(layer.linear_qkv, "gather_slot", None) is not None
+                  and getattr(layer.mlp.up_proj, "gather_slot", None) is not None
+                  and getattr(layer.attn_output, "fused", None) is not None)
+            layer.fuse_norm_gather = bool(ok)
+            layer.set_next_layer(None)
+            if prev is not None and prev.fuse_norm_gather:
+                prev.set_next_layer(layer)
+            prev = layer
+            n += int(ok)
+        return n
+
     def forward(self, x, seq_len: int, pos_ids=None, cu_seqlens=None, attn_mask=None):
         aux_total = None
+        prenormed = None
         for layer in self.layers:
             if self.recompute and self.training:
-                x, aux = checkpoint(layer, x, seq_len, pos_ids, cu_seqlens, attn_mask, use_reentrant=self.use_reentrant)
+                x, aux, prenormed = checkpoint(layer, x, seq_len, pos_ids, cu_seqlens, attn_mask,
+                                               use_reentrant=self.use_reentrant)
             else:
-                x, aux = layer(x, seq_len, pos_ids, cu_seqlens, attn_mask)
+                x, aux, prenormed = layer(x, seq_len, pos_ids, cu_seqlens, attn_mask, prenormed)
             if aux is not None:
                 aux_total = aux if aux_total is None else aux_total + aux
         return x, aux_total

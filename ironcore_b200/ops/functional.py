@@ -83,8 +83,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 # --------------------------------------------------------------------------- norm
 class _Norm(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, residual, eps, rms, w_offset):
-        y, h, mean, rstd = kernels.norm_fwd(x, weight, bias, eps, rms, residual=residual, w_offset=w_offset)
+    def forward(ctx, x, weight, bias, residual, eps, rms, w_offset, out=None):
+        y, h, mean, rstd = kernels.norm_fwd(x, weight, bias, eps, rms, residual=residual, w_offset=w_offset, out=out)
         ctx.save_for_backward(h, weight, mean if mean is not None else rstd, rstd)
         ctx.rms = rms
         ctx.has_bias = bias is not None
@@ -104,22 +104,26 @@ class _Norm(torch.autograd.Function):
         dwt = dw.to(weight.dtype)
         dbt = db.to(weight.dtype) if db is not None else None
         if ctx.has_res:
-            return dx, dwt, dbt, dx, None, None, None
+            return dx, dwt, dbt, dx, None, None, None, None
         if dh is not None:
             dx = dx + dh
-        return dx, dwt, dbt, None, None, None, None
+        return dx, dwt, dbt, None, None, None, None, None
 
 
 def norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float, rms: bool,
-         residual: Optional[torch.Tensor] = None, w_offset: float = 0.0) -> Tuple[torch.Tensor, torch.Tensor]:
+         residual: Optional[torch.Tensor] = None, w_offset: float = 0.0,
+         out: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Returns ``(normalised, h)`` with ``h = x + residual`` (or ``x`` when no residual):
-    the (fused) residual add and the norm that follows it."""
+    the (fused) residual add and the norm that follows it. ``out`` (native path, 2-D input only): where the
+    normalised rows are written, e.g. this rank's rows of the gather buffer of the next linear."""
     if use_native(x) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192:
         xc = x if x.is_contiguous() else x.contiguous()
         rc = residual
         if rc is not None and not rc.is_contiguous():
             rc = rc.contiguous()
-        return _Norm.apply(xc, weight, bias, rc, eps, rms, w_offset)
+        if out is not None and (xc.dim() != 2 or out.shape != xc.shape or out.dtype != xc.dtype):
+            out = None
+        return _Norm.apply(xc, weight, bias, rc, eps, rms, w_offset, out)
     h = x if residual is None else x + residual
     if rms:
         y = reference.rms_norm_reference(h, weight, eps, w_offset)

@@ -128,12 +128,16 @@ def mm_tn(x: torch.Tensor, dy: torch.Tensor, **kw) -> torch.Tensor:
 # ---------------------------------------------------------------------------
 # normalisation
 # ---------------------------------------------------------------------------
-def norm_fwd(x, weight, bias, eps: float, rms: bool, residual=None, w_offset: float = 0.0, store_sum: bool = True):
-    """Returns (y, h, mean, rstd). ``h`` is x+residual (or x itself when no residual)."""
+def norm_fwd(x, weight, bias, eps: float, rms: bool, residual=None, w_offset: float = 0.0, store_sum: bool = True,
+             out=None):
+    """Returns (y, h, mean, rstd). ``h`` is x+residual (or x itself when no residual). ``out``: contiguous
+    tensor of x's shape and dtype that receives ``y`` (e.g. this rank's rows of a gather buffer)."""
     d = x.shape[-1]
     x2 = x.reshape(-1, d)
     m = x2.shape[0]
-    y = torch.empty_like(x2)
+    if out is not None and (out.shape != x2.shape or out.dtype != x2.dtype or not out.is_contiguous()):
+        raise ValueError("norm_fwd: `out` must be a contiguous tensor of the input's 2-D shape and dtype")
+    y = out if out is not None else torch.empty_like(x2)
     rstd = torch.empty(m, dtype=torch.float32, device=x.device)
     mean = None if rms else torch.empty(m, dtype=torch.float32, device=x.device)
     h = None

@@ -180,10 +180,24 @@ def status_tensor(device=None) -> torch.Tensor:
     return t
 
 
+def set_wait_limit_us(microseconds: int, device=None) -> None:
+    """How long one device-side wait (mbarrier phase, peer flag, tile counter) may last before the
+    kernel gives up, writes a status code and returns. 0 restores the default of two seconds."""
+    status_tensor(device)[1] = int(microseconds)
+
+
+def clear_status(device=None) -> None:
+    """Reset the status code and detail; the configured wait limit stays."""
+    t = status_tensor(device)
+    t[0] = 0
+    t[2] = 0
+
+
 def check_status(device=None) -> None:
     """Synchronising check of the device status word; raises if any kernel reported an error."""
     t = status_tensor(device)
-    code = int(t[0].item())
+    code, _limit, detail, _ = (int(v) for v in t.tolist())
     if code != 0:
-        t.zero_()
-        raise RuntimeError(f"native kernel reported status {code}: {STATUS_NAMES.get(code, 'unknown')}")
+        clear_status(device)
+        raise RuntimeError(f"native kernel reported status {code}: {STATUS_NAMES.get(code, 'unknown')} "
+                           f"(detail {detail})")

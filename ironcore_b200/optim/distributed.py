@@ -332,6 +332,30 @@ class DistributedOptimizer:
             coef = torch.clamp(self.clip / (norm + 1e-6), max=1.0) if self.clip > 0 else torch.ones_like(norm)
         return norm, coef
 
+    @torch.no_grad()
+    def param_norm(self) -> torch.Tensor:
+        """L2 norm of all parameters of the model (not only this rank's): one sum-of-squares kernel per
+        region of the flat parameter buffer instead of a loop over tensors; regions replicated over the
+        tensor-parallel group are counted once, sharded ones are summed over TP (and expert regions over
+        the expert-parallel group). (Reference: the per-parameter loop of ironcore/trainer.py:335-340.)"""
+        dev = self.groups[0].device if self.groups else torch.device("cpu")
+        dense = torch.zeros(1, dtype=torch.float32, device=dev)
+        expert = torch.zeros(1, dtype=torch.float32, device=dev)
+        for gi, g in enumerate(self.groups):
+            is_expert = gi > 0
+            for r in g.regions:
+                if r.end <= r.start:
+                    continue
+                w = 1.0 / self.tp_size if r.tp_replicated and not is_expert else 1.0
+                self._sumsq(g.param_buf[r.start:r.end], expert if is_expert else dense, w)
+        if dist.is_initialized():
+            if self.tp_size > 1:
+                dist.all_reduce(dense, group=self.tp_group)
+            ep_group = mesh.get_expert_model_parallel_group()
+            if len(self.groups) > 1 and _gsize(ep_group) > 1:
+                dist.all_reduce(expert, group=ep_group)
+        return (dense + expert).sqrt().squeeze(0)
+
     def _adam_range(self, g: FlatGroup, mom, lo: int, a: int, b: int, wd: float, coef, lr: float):
         """Adam on flat range [a, b) of group g; moments are indexed relative to ``lo``."""
         p = g.param_buf[a:b]

@@ -13,7 +13,6 @@ norm, Adam kernel, all-gather) is the fallback and the oracle.
 from __future__ import annotations
 
 import ctypes as C
-import os
 from typing import Optional
 
 import torch
@@ -40,9 +39,9 @@ class FusedZeroStep:
 
     @staticmethod
     def create(group) -> Optional["FusedZeroStep"]:
-        from ..parallel.symmetric import symmetric_memory_available
+        from ..parallel.symmetric import POLICY, symmetric_memory_available
 
-        if os.environ.get("ICB_FUSED_ZERO", "1") in ("0", "false", "off"):
+        if not POLICY.fused_zero:
             return None
         if not symmetric_memory_available() or dist.get_world_size(group) > 16:
             return None
@@ -74,8 +73,9 @@ class FusedZeroStep:
         self.scratch = torch.zeros(2, dtype=torch.int32, device=dev)
         self.norm_out = torch.zeros(1, dtype=torch.float32, device=dev)
         self.coef_out = torch.ones(1, dtype=torch.float32, device=dev)
-        want = os.environ.get("ICB_NVLS", "auto").lower()
-        use_mc = b.multicast_ptr != 0 and (want in ("1", "true", "on") or (want == "auto" and self.world >= 4))
+        from ..parallel.symmetric import nvls_requested
+
+        use_mc = b.multicast_ptr != 0 and nvls_requested(self.world, "ag")
         flag = torch.tensor([1 if use_mc else 0], dtype=torch.int32, device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
         self.nvls = bool(int(flag.item()))

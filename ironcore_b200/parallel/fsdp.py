@@ -404,6 +404,26 @@ class FSDPOptimizer:
         return self._norm
 
     @torch.no_grad()
+    def param_norm(self) -> torch.Tensor:
+        """L2 norm of all parameters: one sum-of-squares kernel per unit shard, summed over the shard group."""
+        fs = self.fsdp
+        dev = fs.units[0].device
+        total = torch.zeros(1, dtype=torch.float32, device=dev)
+        sharded = False
+        for u in fs.units:
+            t = (u._local_shard() if u.shard_params else u.full)
+            sharded = sharded or u.shard_params
+            if t.is_cuda:
+                tmp = torch.zeros(1, dtype=torch.float32, device=dev)
+                kernels.sumsq(t, tmp)
+                total += tmp
+            else:
+                total += t.float().pow(2).sum()
+        if sharded and fs.dp > 1:
+            dist.all_reduce(total, group=fs.group)
+        return total.sqrt().squeeze(0)
+
+    @torch.no_grad()
     def step(self):
         from ..optim.muon import newton_schulz
 

@@ -15,7 +15,6 @@ scale and the accumulation into the fp32 gradient shard. The NCCL calls in
 
 from __future__ import annotations
 
-import os
 
 import torch
 import torch.distributed as dist
@@ -54,8 +53,9 @@ class FsdpCommPool:
         self.gather_epoch = torch.zeros(1, dtype=torch.int32, device=dev)
         self.reduce_epoch = torch.zeros(1, dtype=torch.int32, device=dev)
         self.ticket = torch.zeros(2, dtype=torch.int32, device=dev)
-        want = os.environ.get("ICB_NVLS", "auto").lower()
-        use_mc = self.buf.multicast_ptr != 0 and (want in ("1", "true", "on") or (want == "auto" and self.world >= 4))
+        from .symmetric import nvls_requested
+
+        use_mc = self.buf.multicast_ptr != 0 and nvls_requested(self.world, "ag")
         flag = torch.tensor([1 if use_mc else 0], dtype=torch.int32, device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
         self.nvls = bool(int(flag.item()))

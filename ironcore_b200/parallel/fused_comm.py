@@ -1,63 +1,83 @@
 """Fused compute+collective paths of tensor parallelism with sequence parallelism.
 
-``FusedTP`` owns two symmetric-memory workspaces shared by every layer of a model:
+``FusedTP`` owns the symmetric-memory workspaces shared by every layer of a model:
 
-* gather workspace  : two (call-parity) gathered activation buffers ``[M, d]`` plus the
-  per-128-row arrival counters that the peers bump when their pushed shard chunks have
-  landed, used by ``icb_ag_gemm`` (all-gather -> GEMM in one kernel);
-* scatter workspace : two receive buffers ``[t][M/t][d]`` plus per-tile arrival counters used
-  by ``icb_gemm_rs`` (GEMM -> reduce-scatter in one kernel).
+* gather scratch    : two (call-parity) gathered activation buffers ``[M, d]`` plus the per-128-row
+  arrival counters that the peers bump when their pushed shard chunks have landed, used by
+  ``icb_ag_gemm`` (all-gather -> GEMM in one kernel) for gathers that live for one call (the output
+  gradients of row-parallel layers);
+* gather slots      : one persistent gathered buffer ``[M, d]`` with its own counters per column-parallel
+  call site. The forward gather of a call site stays in its slot until the weight gradient of the same
+  call site has used it, so nothing is cloned; and a slot can be filled by the *producer* of its rows;
+* scatter workspace : two receive buffers ``[t][M/t][d]`` plus per-tile arrival counters used by
+  ``icb_gemm_rs`` (GEMM -> reduce-scatter in one kernel).
 
-Forward and backward of the column- / row-parallel linears map onto these two kernels:
+Forward and backward of the column- / row-parallel linears map onto these kernels:
 
   column fwd  : AG(x) -> GEMM                      (icb_ag_gemm, a_major 0)
+  column wgrad: gathered(x)^T GEMM dy              (plain GEMM on the slot the forward filled; runs before
+                                                    the dgrad so that no peer can refill the slot early)
   column dgrad: GEMM(dy, W^T) -> RS                (icb_gemm_rs)
-  column wgrad: AG(x)^T GEMM dy                    (icb_ag_gemm, a_major 1, accumulates into main_grad)
   row fwd     : GEMM -> RS (+bias +residual)       (icb_gemm_rs)
-  row dgrad   : AG(dy) -> GEMM                     (icb_ag_gemm, a_major 0)
-  row wgrad   : x^T GEMM gathered(dy)              (plain GEMM on the buffer the dgrad call filled)
+  row fwd + next norm : GEMM -> RS -> RMSNorm -> push into the next column call site's slot
+                                                   (icb_gemm_rs_norm_ag; the consumer runs icb_ag_gemm with
+                                                    the "pushed by the producers" flag and only waits)
+  row dgrad   : AG(dy) -> GEMM                     (icb_ag_gemm, a_major 0, scratch buffer)
+  row wgrad   : x^T GEMM gathered(dy)              (plain GEMM on the scratch buffer the dgrad call filled)
 
-Every rank must issue the same sequence of calls (SPMD). Each workspace counts its calls in a
-device word that the kernels read as the epoch of their cumulative flags, so a captured CUDA
-graph replays correctly; the host-side counter only selects the buffer parity, which is why a
-captured region must contain an even number of calls per workspace (checked by the trainer). The ``torch.distributed``
-path in :mod:`ironcore_b200.parallel.tensor_parallel` is the fallback and the oracle.
+Every rank must issue the same sequence of calls (SPMD). Each buffer counts its calls in a device word
+that the kernels read as the epoch of their cumulative flags, so a captured CUDA graph replays
+correctly; the host-side counter only selects the parity of the scratch / receive buffers, which is
+why a captured region must contain an even number of calls per parity workspace (checked by the
+trainer). The ``torch.distributed`` path in :mod:`ironcore_b200.parallel.tensor_parallel` is the
+fallback and the oracle.
 """
 
 from __future__ import annotations
 
-from typing import Optional
-
-import os
+from typing import List, Optional
 
 import torch
 import torch.distributed as dist
 
 from ..ops import kernels, native
 from ..ops.native import call, dtype_code, ptr, stream_ptr
-from .symmetric import SymmetricBuffer, symmetric_memory_available
+from .symmetric import SymmetricBuffer, nvls_requested, symmetric_memory_available
 
-P, I, L = native.P, native.I, native.L
-native.register("icb_ag_gemm", [P, P, P, P, P, I, I, I, I, P, P, P, P, P, I, L, L, L, I, I, I, I, P, P, P])
+P, I, L, F = native.P, native.I, native.L, native.F
+native.register("icb_ag_gemm", [P, P, P, P, P, I, I, I, I, P, P, P, P, P, I, L, L, L, I, I, I, I, P, P, P, I])
 native.register("icb_gemm_rs", [P, P, P, P, P, I, I, I, L, L, L, L, I, I, P, P, P, P, I, I, P, P, P, P])
+native.register("icb_gemm_rs_norm_ag", [P, P, P, P, P, I, I, I, L, L, L, L, I, I, P, P, P, P, I, I, P, P, P, P,
+                                        P, F, F, P, P, P, P])
 
 
-def _nvls_requested(world: int, op: str) -> bool:
-    """Whether ``op`` ("ag" or "rs") uses the NVSwitch multicast form. ``ICB_NVLS=1`` / ``0`` forces it on /
-    off for both. By default the all-gather push uses it from 4 ranks up (one multimem.st instead of world-1
-    P2P stores: measured 13 % faster at 4 ranks, slower at 2), and the reduce-scatter stays on P2P stores:
-    pushing partial tiles while the tensor core still works overlaps better than pulling the sums through
-    the switch after the last tile (measured at 2 and 4 ranks)."""
-    v = os.environ.get("ICB_NVLS", "auto").lower()
-    if v in ("0", "false", "off"):
-        return False
-    if v in ("1", "true", "on"):
-        return True
-    return op == "ag" and world >= 4
+class GatherSlot:
+    """One gathered activation buffer ``[tokens, width]`` of a symmetric allocation with the arrival
+    counters of its 128-row blocks and the device word that counts its completed gathers."""
+
+    def __init__(self, sbuf: SymmetricBuffer, data_off: int, ready_off: int, tokens: int, width: int, dtype, rank: int,
+                 rows: int, index: int):
+        self.index = index
+        self.data_off = data_off
+        self.buf = sbuf.view(data_off, (tokens, width), dtype)
+        self.local = self.buf[rank * rows:(rank + 1) * rows]
+        self.peers = sbuf.peer_table(data_off)
+        self.peer_ready = sbuf.peer_table(ready_off)
+        self.ready = sbuf.view(ready_off, (tokens // 128,), torch.int32)
+        self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=sbuf.local.device)
+        self.mc = (sbuf.multicast_ptr + data_off) if sbuf.multicast_ptr else 0
+
+
+def row_width_supported(width: int) -> bool:
+    """The fused reduce-scatter + norm producer publishes whole 8 KiB chunks: a row must divide a chunk
+    or be a multiple of it."""
+    row_bytes = width * 2
+    return row_bytes % 8192 == 0 if row_bytes >= 8192 else 8192 % row_bytes == 0
 
 
 class FusedTP:
-    def __init__(self, tokens: int, width: int, group, dtype=torch.bfloat16, nvls: Optional[bool] = None):
+    def __init__(self, tokens: int, width: int, group, dtype=torch.bfloat16, nvls: Optional[bool] = None,
+                 num_slots: int = 0):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -67,21 +87,24 @@ class FusedTP:
         self.rows = tokens // self.world
         es = 2
         self.max_n_tiles = (width + 255) // 256
-        # ---- gather workspace ----
+        # ---- gather workspace: two scratch buffers by call parity, then the persistent slots ----
         g_data = tokens * width * es
-        self._g_off = [0, g_data]
-        self._g_ready_off = 2 * g_data
-        self._g_signal_off = self._g_ready_off + (tokens // 128) * 4
-        g_total = self._g_signal_off + self.world * 4
+        ready_bytes = ((tokens // 128) * 4 + 255) // 256 * 256
+        n_bufs = 2 + num_slots
+        self._g_off = [i * g_data for i in range(n_bufs)]
+        ready_off = [n_bufs * g_data + i * ready_bytes for i in range(1 + num_slots)]   # scratch shares one array
+        g_total = ready_off[-1] + ready_bytes
         self.gbuf = SymmetricBuffer(g_total, group)
+        dev = self.gbuf.local.device
         self.g_views = [self.gbuf.view(self._g_off[p], (tokens, width), dtype) for p in range(2)]
         self.g_peers = [self.gbuf.peer_table(self._g_off[p]) for p in range(2)]
-        self.g_peer_signal = self.gbuf.peer_table(self._g_signal_off)
-        self.g_peer_ready = self.gbuf.peer_table(self._g_ready_off)
-        self.g_ready = self.gbuf.view(self._g_ready_off, (tokens // 128,), torch.int32)
-        self.g_signal = self.gbuf.view(self._g_signal_off, (self.world,), torch.int32)
+        self.g_peer_ready = self.gbuf.peer_table(ready_off[0])
+        self.g_ready = self.gbuf.view(ready_off[0], (tokens // 128,), torch.int32)
         self.g_epoch = 0
-        self.g_epoch_dev = torch.zeros(1, dtype=torch.int32, device=self.gbuf.local.device)
+        self.g_epoch_dev = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.slots: List[GatherSlot] = [
+            GatherSlot(self.gbuf, self._g_off[2 + i], ready_off[1 + i], tokens, width, dtype, self.rank, self.rows, i)
+            for i in range(num_slots)]
         self.last_gathered: Optional[torch.Tensor] = None
         # ---- scatter workspace ----
         r_data = tokens * width * es
@@ -94,49 +117,68 @@ class FusedTP:
         self.r_peer_flags = self.rbuf.peer_table(self._r_flags_off)
         self.r_flags = self.rbuf.view(self._r_flags_off, (n_flags,), torch.int32)
         self.r_epoch = 0
-        self.r_epoch_dev = torch.zeros(1, dtype=torch.int32, device=self.rbuf.local.device)
+        self.r_epoch_dev = torch.zeros(1, dtype=torch.int32, device=dev)
         # True: forward keeps the gathered activations (32 MiB at 4096 x 4096) for the weight gradient;
         # False: backward re-gathers inside the wgrad kernel (less memory, exposed transfer).
         self.save_gathered = True
         # NVLS: push the gathered shard once with multimem.st and reduce the scattered partials with
         # multimem.ld_reduce when the symmetric allocations have a multicast mapping on every rank.
         have = torch.tensor([1 if (self.gbuf.multicast_ptr and self.rbuf.multicast_ptr) else 0],
-                            dtype=torch.int32, device=self.gbuf.local.device)
+                            dtype=torch.int32, device=dev)
         if self.world > 1:
             dist.all_reduce(have, op=dist.ReduceOp.MIN, group=group)
         have = self.world > 1 and int(have.item()) == 1
-        self.nvls_ag = bool(have and (_nvls_requested(self.world, "ag") if nvls is None else nvls))
-        self.nvls_rs = bool(have and (_nvls_requested(self.world, "rs") if nvls is None else nvls))
+        self.nvls_ag = bool(have and (nvls_requested(self.world, "ag") if nvls is None else nvls))
+        self.nvls_rs = bool(have and (nvls_requested(self.world, "rs") if nvls is None else nvls))
         self.nvls = self.nvls_ag or self.nvls_rs
+        self.norm_fusable = row_width_supported(width)
 
     # ------------------------------------------------------------------ raw kernels
     def ag_gemm(self, x_shard: torch.Tensor, b: torch.Tensor, *, a_major: int, b_major: int, n: int,
-                bias=None, out=None, residual=None, out_dtype=None) -> torch.Tensor:
+                bias=None, out=None, residual=None, out_dtype=None, slot: Optional[GatherSlot] = None,
+                pushed: bool = False) -> torch.Tensor:
         """AG(x_shard) (x) b. a_major 0: [tokens, width] @ b -> [tokens, n];
-        a_major 1: gathered^T @ b[tokens, n] -> [width, n]."""
+        a_major 1: gathered^T @ b[tokens, n] -> [width, n].
+        ``slot``: gather into this persistent buffer instead of the parity scratch. ``pushed``: every rank's
+        rows were (or are being) written into the slot by their producers (``gemm_rs(..., norm=...)``); the
+        kernel pushes nothing and waits for the slot's counters."""
         if x_shard.shape != (self.rows, self.width) or x_shard.dtype != self.dtype:
             raise ValueError(f"fused gather expects a [{self.rows}, {self.width}] {self.dtype} shard")
-        self.g_epoch += 1
-        par = self.g_epoch & 1
-        gathered = self.g_views[par]
-        gathered[self.rank * self.rows:(self.rank + 1) * self.rows].copy_(x_shard)
+        if slot is None:
+            if pushed:
+                raise ValueError("a producer-pushed gather needs a slot")
+            self.g_epoch += 1
+            par = self.g_epoch & 1
+            gathered, peers, peer_ready, ready, epoch_dev = (self.g_views[par], self.g_peers[par], self.g_peer_ready,
+                                                             self.g_ready, self.g_epoch_dev)
+            mc = (self.gbuf.multicast_ptr + self._g_off[par]) if self.nvls_ag else None
+        else:
+            gathered, peers, peer_ready, ready, epoch_dev = slot.buf, slot.peers, slot.peer_ready, slot.ready, \
+                slot.epoch_dev
+            mc = slot.mc if (self.nvls_ag and slot.mc) else None
+        if not pushed:
+            local = gathered[self.rank * self.rows:(self.rank + 1) * self.rows]
+            if local.data_ptr() != x_shard.data_ptr():
+                local.copy_(x_shard)
         m = self.tokens if a_major == 0 else self.width
         out_dtype = out_dtype or (out.dtype if out is not None else self.dtype)
         if out is None:
             out = torch.empty((m, n), dtype=out_dtype, device=x_shard.device)
         ldr = residual.stride(0) if residual is not None else 0
-        call("icb_ag_gemm", ptr(gathered), ptr(self.g_peers[par]), ptr(self.g_peer_ready), ptr(self.g_signal),
-             ptr(self.g_ready), self.rank, self.world, self.rows, self.width, ptr(self.g_epoch_dev), ptr(b), ptr(out),
-             ptr(bias), ptr(residual), int(n), b.stride(0), out.stride(0), ldr, int(a_major), int(b_major),
-             dtype_code(self.dtype), 1 if out_dtype == torch.float32 else 0,
-             ptr(native.status_tensor(x_shard.device)), stream_ptr(),
-             (self.gbuf.multicast_ptr + self._g_off[par]) if self.nvls_ag else None)
-        self.g_epoch_dev.add_(1)
+        call("icb_ag_gemm", ptr(gathered), ptr(peers), ptr(peer_ready), None, ptr(ready), self.rank, self.world,
+             self.rows, self.width, ptr(epoch_dev), ptr(b), ptr(out), ptr(bias), ptr(residual), int(n), b.stride(0),
+             out.stride(0), ldr, int(a_major), int(b_major), dtype_code(self.dtype),
+             1 if out_dtype == torch.float32 else 0, ptr(native.status_tensor(x_shard.device)), stream_ptr(), mc,
+             1 if pushed else 0)
+        epoch_dev.add_(1)
         self.last_gathered = gathered
         return out
 
-    def gemm_rs(self, a: torch.Tensor, b: torch.Tensor, *, b_major: int, bias=None, residual=None) -> torch.Tensor:
-        """reduce_scatter_rows(a[tokens, k] (x) b) -> [tokens / world, width]."""
+    def gemm_rs(self, a: torch.Tensor, b: torch.Tensor, *, b_major: int, bias=None, residual=None, norm=None):
+        """reduce_scatter_rows(a[tokens, k] (x) b) -> [tokens / world, width].
+        ``norm = (gamma, eps, w_offset, slot)``: the same kernel also RMS-normalises the reduced rows and stores
+        them into every rank's copy of ``slot``; returns ``(out, rstd)`` and ``slot.local`` holds this rank's
+        normalised rows."""
         if a.shape[0] != self.tokens or a.dtype != self.dtype:
             raise ValueError("fused reduce-scatter expects the full token dimension")
         n = self.width
@@ -146,20 +188,37 @@ class FusedTP:
         out = torch.empty((self.rows, n), dtype=self.dtype, device=a.device)
         ldr = residual.stride(0) if residual is not None else 0
         recv_ptr = self.rbuf.local.data_ptr() + self._r_off[par]
-        call("icb_gemm_rs", ptr(a), ptr(b), ptr(out), ptr(bias), ptr(residual), self.tokens, n, k, a.stride(0),
-             b.stride(0), out.stride(0), ldr, int(b_major), dtype_code(self.dtype), ptr(self.r_peers[par]),
-             ptr(self.r_peer_flags), recv_ptr, ptr(self.r_flags), self.rank, self.world, ptr(self.r_epoch_dev),
-             ptr(native.status_tensor(a.device)), stream_ptr(),
-             (self.rbuf.multicast_ptr + self._r_off[par]) if self.nvls_rs else None)
+        common = (ptr(a), ptr(b), ptr(out), ptr(bias), ptr(residual), self.tokens, n, k, a.stride(0),
+                  b.stride(0), out.stride(0), ldr, int(b_major), dtype_code(self.dtype), ptr(self.r_peers[par]),
+                  ptr(self.r_peer_flags), recv_ptr, ptr(self.r_flags), self.rank, self.world, ptr(self.r_epoch_dev),
+                  ptr(native.status_tensor(a.device)), stream_ptr(),
+                  (self.rbuf.multicast_ptr + self._r_off[par]) if self.nvls_rs else None)
+        if norm is None:
+            call("icb_gemm_rs", *common)
+            self.r_epoch_dev.add_(1)
+            return out
+        gamma, eps, w_offset, slot = norm
+        if not self.norm_fusable:
+            raise ValueError(f"width {self.width} is not supported by the fused reduce-scatter + norm kernel")
+        rstd = torch.empty(self.rows, dtype=torch.float32, device=a.device)
+        call("icb_gemm_rs_norm_ag", *common, ptr(gamma), float(eps), float(w_offset), ptr(rstd), ptr(slot.peers),
+             slot.mc if (self.nvls_ag and slot.mc) else None, ptr(slot.peer_ready))
         self.r_epoch_dev.add_(1)
-        return out
+        return out, rstd
 
     # ------------------------------------------------------------------ autograd entry points
-    def allgather_linear(self, x_shard, weight, bias=None):
-        return _AllGatherLinear.apply(x_shard, weight, bias, self)
+    def allgather_linear(self, x_shard, weight, bias=None, slot: Optional[GatherSlot] = None, pushed: bool = False):
+        return _AllGatherLinear.apply(x_shard, weight, bias, self, slot, pushed)
 
     def linear_reduce_scatter(self, x, weight, bias=None, residual=None):
         return _LinearReduceScatter.apply(x, weight, bias, residual, self)
+
+    def linear_reduce_scatter_norm(self, x, weight, bias, residual, gamma, eps: float, w_offset: float,
+                                   slot: GatherSlot):
+        """Row-parallel linear + residual, then RMSNorm of the result pushed into ``slot`` on every rank.
+        Returns ``(h, normed)``: the residual-stream shard and this rank's normalised rows (a view of the slot,
+        to be handed to the column-parallel linear that owns the slot with ``pushed=True``)."""
+        return _LinearRSNorm.apply(x, weight, bias, residual, gamma, self, slot, float(eps), float(w_offset))
 
     def supports(self, x: torch.Tensor) -> bool:
         return x.dtype == self.dtype and x.is_cuda
@@ -178,13 +237,29 @@ def _accumulate_or_return(weight, compute):
 
 class _AllGatherLinear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x_shard, weight, bias, ws: FusedTP):
-        x2 = x_shard.reshape(-1, x_shard.shape[-1]).contiguous()
-        y = ws.ag_gemm(x2, weight, a_major=0, b_major=1, n=weight.shape[1], bias=bias)
-        # Keep the gathered activations for the weight gradient (the workspace buffer is reused two
-        # calls later). A re-gather inside the wgrad kernel cannot hide its transfer: the reduction
-        # runs over the gathered rows, so every output tile needs all of them at once.
-        x_full = ws.last_gathered.clone() if ws.save_gathered else x2
+    def forward(ctx, x_shard, weight, bias, ws: FusedTP, slot, pushed):
+        x2 = x_shard.reshape(-1, x_shard.shape[-1])
+        if not pushed:
+            x2 = x2.contiguous()
+        y = ws.ag_gemm(x2, weight, a_major=0, b_major=1, n=weight.shape[1], bias=bias, slot=slot, pushed=pushed)
+        # The weight gradient needs the gathered activations. A slot keeps them until this call site runs
+        # again; what protects it from an early refill by a fast peer is the reduce-scatter of the input
+        # gradient, issued after the weight gradient below: a peer cannot finish its backward pass, and
+        # start the next forward, before it has received this rank's partial tiles. Without an input
+        # gradient there is no such reduce-scatter, and the scratch buffer is reused two calls later:
+        # both cases keep a private copy. (A re-gather inside the wgrad kernel cannot hide its transfer:
+        # the reduction runs over the gathered rows, so every output tile needs all of them at once.)
+        # The slot is kept as a plain attribute, not through save_for_backward: every buffer of the
+        # workspace is a view of one symmetric allocation and shares its version counter, so autograd
+        # would take any later gather into a neighbouring buffer for a modification of this one.
+        ctx.slot_gathered = None
+        if not ws.save_gathered:
+            x_full = x2
+        elif slot is not None and ctx.needs_input_grad[0]:
+            ctx.slot_gathered = slot.buf
+            x_full = None
+        else:
+            x_full = ws.last_gathered.clone()
         ctx.save_for_backward(x_full, weight)
         ctx.ws = ws
         ctx.has_bias = bias is not None
@@ -193,9 +268,10 @@ class _AllGatherLinear(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x2, weight = ctx.saved_tensors
+        if ctx.slot_gathered is not None:
+            x2 = ctx.slot_gathered
         ws: FusedTP = ctx.ws
         dy = dy.contiguous()
-        dx = ws.gemm_rs(dy, weight, b_major=0) if ctx.needs_input_grad[0] else None
         dw = None
         if ctx.needs_input_grad[1]:
             n = weight.shape[1]
@@ -210,8 +286,25 @@ class _AllGatherLinear(torch.autograd.Function):
                 return ws.ag_gemm(x2, dy, a_major=1, b_major=1, n=n)
 
             dw = _accumulate_or_return(weight, compute)
+        dx = ws.gemm_rs(dy, weight, b_major=0) if ctx.needs_input_grad[0] else None
         db = dy.sum(0, dtype=torch.float32).to(dy.dtype) if ctx.has_bias and ctx.needs_input_grad[2] else None
-        return dx, dw, db, None
+        return dx, dw, db, None, None, None
+
+
+def _row_parallel_backward(ctx, x2, weight, dy_shard, ws: FusedTP):
+    """dX_local = AG(dy) @ W^T ; the gathered dy stays in the scratch buffer for the weight gradient."""
+    dx = ws.ag_gemm(dy_shard, weight, a_major=0, b_major=0, n=weight.shape[0])
+    dy_full = ws.last_gathered
+    dw = None
+    if ctx.needs_input_grad[1]:
+        def compute(acc):
+            if acc is not None:
+                return kernels.mm_tn(x2, dy_full, out=acc, residual=acc, out_dtype=acc.dtype)
+            return kernels.mm_tn(x2, dy_full)
+
+        dw = _accumulate_or_return(weight, compute)
+    db = dy_shard.sum(0, dtype=torch.float32).to(dy_shard.dtype) if ctx.has_bias and ctx.needs_input_grad[2] else None
+    return dx, dw, db
 
 
 class _LinearReduceScatter(torch.autograd.Function):
@@ -229,29 +322,50 @@ class _LinearReduceScatter(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy_shard):
         x2, weight = ctx.saved_tensors
-        ws: FusedTP = ctx.ws
         dy_shard = dy_shard.contiguous()
-        # dX_local = AG(dy) @ W^T ; the gathered dy stays in the workspace for the weight gradient
-        dx = ws.ag_gemm(dy_shard, weight, a_major=0, b_major=0, n=weight.shape[0])
-        dy_full = ws.last_gathered
-        dw = None
-        if ctx.needs_input_grad[1]:
-            def compute(acc):
-                if acc is not None:
-                    return kernels.mm_tn(x2, dy_full, out=acc, residual=acc, out_dtype=acc.dtype)
-                return kernels.mm_tn(x2, dy_full)
-
-            dw = _accumulate_or_return(weight, compute)
-        db = dy_shard.sum(0, dtype=torch.float32).to(dy_shard.dtype) if ctx.has_bias and ctx.needs_input_grad[2] \
-            else None
+        dx, dw, db = _row_parallel_backward(ctx, x2, weight, dy_shard, ctx.ws)
         dres = dy_shard if ctx.has_res and ctx.needs_input_grad[3] else None
         return dx, dw, db, dres, None
 
 
+class _LinearRSNorm(torch.autograd.Function):
+    """h = reduce_scatter(x @ W) + bias + residual ; normed = rmsnorm(h) * (gamma + w_offset), written into the
+    gather slot of the following column-parallel linear on every rank by the same kernel."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual, gamma, ws: FusedTP, slot, eps, w_offset):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        res2 = residual.reshape(-1, weight.shape[1]).contiguous() if residual is not None else None
+        h, rstd = ws.gemm_rs(x2, weight, b_major=1, bias=bias, residual=res2, norm=(gamma, eps, w_offset, slot))
+        ctx.save_for_backward(x2, weight, h, rstd, gamma)
+        ctx.ws = ws
+        ctx.has_bias = bias is not None
+        ctx.has_res = residual is not None
+        ctx.w_offset = w_offset
+        return h, slot.buf.narrow(0, ws.rank * ws.rows, ws.rows)
+
+    @staticmethod
+    def backward(ctx, dh, dnormed):
+        x2, weight, h, rstd, gamma = ctx.saved_tensors
+        dgamma = None
+        if dnormed is not None:
+            dres_in = dh.contiguous() if dh is not None else None
+            dh, dg, _ = kernels.norm_bwd(dnormed.contiguous(), h, gamma, None, rstd, True, False, dres_in=dres_in,
+                                         w_offset=ctx.w_offset)
+            dgamma = dg.to(gamma.dtype)
+        dh = dh.contiguous()
+        dx, dw, db = _row_parallel_backward(ctx, x2, weight, dh, ctx.ws)
+        dres = dh if ctx.has_res and ctx.needs_input_grad[3] else None
+        return dx, dw, db, dres, dgamma, None, None, None, None
+
+
 def attach_fused_tp(model, config) -> Optional[FusedTP]:
-    """Create the shared workspaces and hand them to every sequence-parallel column / row
-    parallel linear of ``model``. Returns None (and leaves the NCCL path active) when
-    symmetric memory is unavailable or the shapes do not fit the kernels' tiling."""
+    """Create the shared workspaces and hand them to every sequence-parallel column / row parallel
+    linear of ``model``; every fused column-parallel linear gets its own gather slot, and where a
+    row-parallel linear is followed by RMSNorm and a fused column-parallel linear the pair is linked so
+    that one kernel reduces, normalises and gathers (``parallel.fused_norm_gather``). Returns None (and
+    leaves the NCCL path active) when symmetric memory is unavailable or the shapes do not fit the
+    kernels' tiling."""
     from . import mesh
     from .tensor_parallel import ColumnParallelLinear, RowParallelLinear
 
@@ -268,13 +382,27 @@ def attach_fused_tp(model, config) -> Optional[FusedTP]:
     dtype = get_model_dtype(config)
     if dtype not in (torch.bfloat16, torch.float16):
         return None
-    ws = FusedTP(tokens, width, group, dtype)
     head = getattr(model, "output_layer", None)
+    columns, rows = [], []
     for mod in model.modules():
         if mod is head:
             continue   # keeps the number of fused calls per micro-batch even (needed for CUDA-graph replay)
         if isinstance(mod, ColumnParallelLinear) and mod.sequence_parallel and mod.in_features == width:
-            mod.fused = ws
+            columns.append(mod)
         elif isinstance(mod, RowParallelLinear) and mod.sequence_parallel and mod.out_features == width:
-            mod.fused = ws
+            rows.append(mod)
+    ws = FusedTP(tokens, width, group, dtype, num_slots=len(columns))
+    for i, mod in enumerate(columns):
+        mod.fused = ws
+        mod.gather_slot = ws.slots[i]
+    for mod in rows:
+        mod.fused = ws
+    link = getattr(model, "link_fused_norm_gather", None)
+    want = str(getattr(config.parallel, "fused_norm_gather", "auto")).lower()
+    # "auto": from 4 ranks up. At 2 ranks half of the consumer's tiles are local and hide its own push, and
+    # the separate kernels measured 11 % faster on the Llama-7B layer shapes; from 4 ranks up little of the
+    # push can hide behind local tiles and the producer form removes it together with the norm kernel.
+    on = want in ("on", "true", "1") or (want == "auto" and t >= 4)
+    if link is not None and on and ws.norm_fusable:
+        link()
     return ws

@@ -19,7 +19,6 @@ of ``d(xp)``. Nothing on this path synchronises with the host. The ``all_to_all`
 
 from __future__ import annotations
 
-import os
 from typing import Optional
 
 import torch
@@ -168,7 +167,9 @@ _WORKSPACES = {}
 
 def get_fused_ep(group, num_experts, top_k, max_tokens, d_model, dtype, factor: float = 2.0) -> Optional[FusedEP]:
     """Shared workspace for all MoE layers with the same geometry; None when the fused path cannot run."""
-    if os.environ.get("ICB_FUSED_MOE", "1") in ("0", "false", "off"):
+    from .symmetric import POLICY
+
+    if not POLICY.fused_moe:
         return None
     if not symmetric_memory_available() or dtype not in (torch.bfloat16, torch.float16):
         return None

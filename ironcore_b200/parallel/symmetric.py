@@ -10,10 +10,48 @@ library kernel ever sees a peer pointer.
 
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import List
 
 import torch
 import torch.distributed as dist
+
+
+@dataclass
+class CommPolicy:
+    """Process-wide choices for the in-kernel collectives, set from ``config.parallel`` by the trainer.
+
+    nvls: "auto" | "on" | "off". Whether kernels use the NVSwitch multicast mapping (``multimem.st`` /
+    ``multimem.ld_reduce``) where the fabric offers one. "auto": broadcast-type transfers (all-gather push,
+    parameter broadcast) from 4 ranks up (one store instead of world-1: measured 13 % faster at 4 ranks,
+    slower at 2); reduce-type transfers of the tensor-parallel GEMMs stay on P2P stores, which overlap the
+    transfer with the remaining tiles (pulling sums through the switch after the last tile measured slower
+    at 2 and 4 ranks)."""
+
+    nvls: str = "auto"
+    fused_zero: bool = True
+    fused_moe: bool = True
+    fused_norm_gather: str = "auto"
+
+
+POLICY = CommPolicy()
+
+
+def configure(parallel_config) -> CommPolicy:
+    for name in ("nvls", "fused_zero", "fused_moe", "fused_norm_gather"):
+        if hasattr(parallel_config, name):
+            setattr(POLICY, name, getattr(parallel_config, name))
+    return POLICY
+
+
+def nvls_requested(world: int, op: str) -> bool:
+    """``op``: "ag" (broadcast-type) or "rs" (reduce-type); see :class:`CommPolicy`."""
+    v = str(POLICY.nvls).lower()
+    if v in ("0", "false", "off"):
+        return False
+    if v in ("1", "true", "on"):
+        return True
+    return op == "ag" and world >= 4
 
 
 def symmetric_memory_available() -> bool:

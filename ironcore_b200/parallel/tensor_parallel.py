@@ -65,13 +65,28 @@ class ColumnParallelLinear(nn.Module):
         if self.bias is not None:
             self.bias.tp_shard_dim = 0
             self.bias.tp_parts = concatenated_weights
-        self.fused = None  # optional fused gather+GEMM workspace
+        self.fused = None        # optional fused gather+GEMM workspace
+        self.gather_slot = None  # this call site's persistent gathered buffer inside that workspace
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def gather_target(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """This rank's rows of the gather slot, when ``self(x')`` for an ``x'`` shaped like ``x`` will run the
+        fused gather: the producer of ``x'`` can write there directly and spare the copy into the slot."""
+        ws, slot = self.fused, self.gather_slot
+        if ws is None or slot is None or not self.sequence_parallel or not OF.use_native(x):
+            return None
+        if x.dim() != 2 or x.shape[0] != ws.rows or x.shape[1] != ws.width or x.dtype != ws.dtype:
+            return None
+        return slot.local
+
+    def forward(self, x: torch.Tensor, pregathered: bool = False) -> torch.Tensor:
+        """``pregathered``: ``x`` is this rank's part of ``gather_slot`` and every rank's part was written
+        there by the kernel that produced it (``RowParallelLinear.forward_norm``): nothing is pushed."""
+        if pregathered and (self.fused is None or self.gather_slot is None):
+            raise RuntimeError("a pregathered input needs the fused workspace and a gather slot")
         if self.tp_size > 1:
             if self.sequence_parallel:
                 if self.fused is not None and OF.use_native(x) and x.dim() == 2 and x.shape[0] == self.fused.rows:
-                    y = self.fused.allgather_linear(x, self.weight, self.bias)
+                    y = self.fused.allgather_linear(x, self.weight, self.bias, self.gather_slot, pregathered)
                     return C.gather_last_dim(y, self.tp_group) if self.gather_output else y
                 x = C.gather_from_sp(x, self.tp_group)
             else:
@@ -107,6 +122,23 @@ class RowParallelLinear(nn.Module):
             # replicated parameter that sees different tokens per rank under sequence parallelism
             self.bias.sp_replicated = True
         self.fused = None
+
+    def can_fuse_norm(self, x: torch.Tensor, norm, consumer) -> bool:
+        """Whether ``forward_norm`` can run as one kernel: fused workspace on both ends, RMSNorm without
+        bias, a row width the producer kernel supports."""
+        ws = self.fused
+        return (ws is not None and self.sequence_parallel and getattr(consumer, "fused", None) is ws
+                and getattr(consumer, "gather_slot", None) is not None and ws.norm_fusable
+                and getattr(norm, "rms", False) and norm.layernorm.bias is None and OF.use_native(x)
+                and x.dim() == 2 and x.shape[0] == ws.tokens and self.input_is_parallel)
+
+    def forward_norm(self, x: torch.Tensor, residual: Optional[torch.Tensor], norm, consumer):
+        """``h = self(x, residual)`` followed by ``norm(h)``, with the normalised rows delivered into the
+        gather slot of ``consumer`` (the column-parallel linear that reads them next) on every rank by the
+        same kernel that reduces the partial products. Returns ``(h, normed)``; pass ``normed`` to
+        ``consumer(normed, pregathered=True)``. Callers check ``can_fuse_norm`` first."""
+        return self.fused.linear_reduce_scatter_norm(x, self.weight, self.bias, residual, norm.layernorm.weight,
+                                                     norm.eps, norm.weight_offset, consumer.gather_slot)
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``residual`` (optional, already in the output layout) is added after the reduction."""

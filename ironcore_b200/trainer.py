@@ -144,6 +144,9 @@ class Trainer:
     def _build_model_and_optimizer(self):
         cfg = self.config
         self._seed_everything()
+        from .parallel.symmetric import configure as configure_comm_policy
+
+        configure_comm_policy(cfg.parallel)
         dtype = get_model_dtype(cfg)
         if self.device.type == "cpu" and dtype != torch.float32:
             self.logger.warning("16-bit precision on CPU runs the PyTorch reference path")
@@ -291,6 +294,9 @@ class Trainer:
         return self._static_loss
 
     def _param_norm(self):
+        fused = getattr(self.optimizer, "param_norm", None)
+        if fused is not None:
+            return fused()
         sq = None
         for p in self.model.parameters():
             v = p.detach().float().pow(2).sum()

@@ -79,3 +79,50 @@ def run_distributed(fn, world: int, *args, timeout: float = 240.0):
     if failed or msgs:
         raise AssertionError("distributed run failed: " + "; ".join(failed) + "\n" +
                              "\n".join(f"[rank {r}]\n{tb}" for r, tb in msgs))
+
+
+# ------------------------------------------------------------------ GPU ranks as child processes
+def _gpu_worker(rank, world, port, module_name, fn_name, out_q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    try:
+        import importlib
+
+        import torch.distributed as dist
+
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        fn = getattr(importlib.import_module(module_name), fn_name)
+        fn(rank, world)
+        torch.cuda.synchronize()
+        from ironcore_b200.ops import native
+
+        native.check_status()
+        dist.barrier()
+        dist.destroy_process_group()
+        out_q.put((rank, "ok"))
+    except Exception:
+        out_q.put((rank, traceback.format_exc()))
+
+
+def spawn_gpu_ranks(module_name: str, fn_name: str, world: int = 2, timeout: float = 150.0):
+    """Run ``module.fn(rank, world)`` as ``world`` child processes, one CUDA device and one NCCL rank each
+    (``world = 1`` gives a one-rank group whose peer tables point at the GPU's own buffers)."""
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = free_port()
+    procs = [ctx.Process(target=_gpu_worker, args=(r, world, port, module_name, fn_name, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout)
+    results = []
+    while not q.empty():
+        results.append(q.get())
+    bad = [r for r in results if r[1] != "ok"]
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            bad.append((-1, "timeout"))
+    assert not bad and len(results) == world, "\n".join(f"[rank {r}] {m}" for r, m in bad)

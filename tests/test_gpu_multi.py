@@ -16,6 +16,13 @@ def _need_two():
         pytest.skip("needs 2 GPUs")
 
 
+def _worlds():
+    """Rank counts to run the raw-kernel checks at: 2, and 4 / 8 when the box has them (the NVSwitch
+    multicast forms are the default from 4 ranks up)."""
+    n = torch.cuda.device_count()
+    return [w for w in (2, 4, 8) if w <= n]
+
+
 def _worker(rank, world, port, fn_name, out_q):
     import traceback
 
@@ -73,11 +80,11 @@ def check_raw_kernels(rank, world):
     from ironcore_b200.parallel.fused_comm import FusedTP
 
     torch.manual_seed(100 + rank)
-    tokens, d, n = 1024, 512, 768
+    tokens, d, n = 1024 * max(1, world // 2), 512, 768
     rows = tokens // world
     for it in range(6):   # several epochs: flags are cumulative, buffers alternate
         if it % 3 == 0:   # plain P2P form first, then the NVLS (multimem) form where the fabric has multicast
-            ws = FusedTP(tokens, d, dist.group.WORLD, nvls=(it >= 3))
+            ws = FusedTP(tokens, d, dist.group.WORLD, nvls=(it >= 3), num_slots=2)
         x = torch.randn(rows, d, device="cuda").bfloat16()
         w = torch.randn(d, n, device="cuda").bfloat16()
         dist.broadcast(w, 0)
@@ -99,6 +106,22 @@ def check_raw_kernels(rank, world):
         ref = torch.empty(rows, d, device="cuda")
         dist.reduce_scatter_tensor(ref, part)
         _close(out, ref + bias.float() + res.float(), 384 * world)
+        # GEMM -> reduce-scatter -> RMSNorm -> gather into a slot, consumed by a gather GEMM that only waits
+        gamma = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16()
+        dist.broadcast(gamma, 0)
+        slot = ws.slots[it % 2]
+        h, rstd = ws.gemm_rs(a, b, b_major=1, bias=bias, residual=res, norm=(gamma, 1e-5, 0.0, slot))
+        y2 = ws.ag_gemm(slot.local, w, a_major=0, b_major=1, n=n, slot=slot, pushed=True)
+        _close(h, ref + bias.float() + res.float(), 384 * world)
+        hf = h.float()
+        normed = (hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-5) * gamma.float()).bfloat16()
+        assert torch.allclose(rstd, torch.rsqrt(hf.pow(2).mean(-1) + 1e-5), rtol=1e-4, atol=1e-6)
+        full_n = torch.empty(tokens, d, device="cuda", dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(full_n, normed)
+        torch.cuda.synchronize()
+        dist.barrier()
+        assert (slot.buf.float() - full_n.float()).abs().max().item() <= 2.0 ** -6 * full_n.float().abs().max().item()
+        _close(y2, full_n.float() @ w.float(), d)
 
 
 def check_tp2_model_fused_matches_nccl(rank, world):
@@ -107,26 +130,32 @@ def check_tp2_model_fused_matches_nccl(rank, world):
     from ironcore_b200.trainer import Trainer
     from helpers import tiny_config
 
-    def run(fused, graph=False):
+    def run(fused, graph=False, norm_gather="on"):
         mesh.destroy_model_parallel()
-        cfg = tiny_config("llama", d_model=256, d_ffn=512, num_layers=2, num_attention_heads=4, head_dim=64,
+        cfg = tiny_config("llama", d_model=256, d_ffn=512, num_layers=3, num_attention_heads=4, head_dim=64,
                           max_seq_len=256, max_position_embeddings=256, precision="bf16", vocab_size=1024)
         cfg.data.vocab_size = 1024
         cfg.model(reset_position_ids=False, reset_attention_mask=False)
         cfg.trainer(micro_batch_size=2, train_batch_size=8 if graph else 2, gradient_accumulation_steps=None,
                     tensor_model_parallel_size=world, cuda_graph=graph)
-        cfg.parallel(world_size=world, rank=rank, local_rank=rank, sequence_parallel=True, fused_comm=fused)
+        cfg.parallel(world_size=world, rank=rank, local_rank=rank, sequence_parallel=True, fused_comm=fused,
+                     fused_norm_gather=norm_gather)
         cfg.operation.train_steps = 3
         validate_config(cfg)
         tr = Trainer(cfg)
         if fused:
             assert any(hasattr(getattr(m, "fused", None), "g_epoch") for m in tr.model.modules())
+            linked = sum(int(l.fuse_norm_gather) for l in tr.model.model.layers)
+            assert linked == (3 if norm_gather == "on" else 0), linked
         return [float(tr.train_step(s)[0]) for s in range(3)]
 
     a = run(False)
     b = run(True)
     for x, y in zip(a, b):
         assert abs(x - y) < 5e-2, (a, b)
+    c = run(True, norm_gather="off")      # fused GEMM+collective kernels, separate norm kernels
+    for x, y in zip(a, c):
+        assert abs(x - y) < 5e-2, (a, c)
     # CUDA-graph replay of the micro-batch with the fused kernels inside (4 micro-batches per step)
     graphed = run(True, graph=True)
     assert all(l == l and l < 20 for l in graphed), graphed
@@ -142,17 +171,16 @@ def check_dp2_fused_zero_matches_nccl(rank, world):
     from ironcore_b200.trainer import Trainer
     from helpers import tiny_config
 
-    def run(fused, nvls="0"):
+    def run(fused, nvls="off"):
         mesh.destroy_model_parallel()
-        os.environ["ICB_FUSED_ZERO"] = "1" if fused else "0"
-        os.environ["ICB_NVLS"] = nvls
         cfg = tiny_config("llama", d_model=256, d_ffn=512, num_layers=2, num_attention_heads=4, head_dim=64,
                           max_seq_len=128, max_position_embeddings=128, precision="bf16", vocab_size=1024)
         cfg.data.vocab_size = 1024
         cfg.model(reset_position_ids=False, reset_attention_mask=False)
         cfg.trainer(micro_batch_size=2, train_batch_size=8, gradient_accumulation_steps=None,
                     tensor_model_parallel_size=1)
-        cfg.parallel(world_size=world, rank=rank, local_rank=rank, zero_stage=1, fused_comm=True)
+        cfg.parallel(world_size=world, rank=rank, local_rank=rank, zero_stage=1, fused_comm=True, fused_zero=fused,
+                     nvls=nvls)
         cfg.optim(max_lr=1e-3, clip_grad=0.5, weight_decay=0.1)
         cfg.operation.train_steps = 4
         validate_config(cfg)
@@ -162,11 +190,10 @@ def check_dp2_fused_zero_matches_nccl(rank, world):
         losses = [float(o[0]) for o in out]
         norms = [float(o[1]) for o in out]
         flat = tr.optimizer.groups[0].param_buf.float().clone()
-        os.environ.pop("ICB_NVLS", None)
         return losses, norms, flat
 
     la, na, pa = run(False)
-    for nvls in ("0", "1"):
+    for nvls in ("off", "on"):
         lb, nb, pb = run(True, nvls)
         for x, y in zip(la, lb):
             assert abs(x - y) < 2e-2, (la, lb)
@@ -205,7 +232,9 @@ def check_ep2_fused_moe_matches_nccl(rank, world):
         return cfg
 
     def block_run(fused):
-        os.environ["ICB_FUSED_MOE"] = "1" if fused else "0"
+        from ironcore_b200.parallel.symmetric import POLICY
+
+        POLICY.fused_moe = fused
         release_workspaces()
         mesh.destroy_model_parallel()
         cfg = cfg_for()
@@ -228,10 +257,11 @@ def check_ep2_fused_moe_matches_nccl(rank, world):
         assert (u - v).abs().max().item() <= tol * max(1.0, u.abs().max().item()), (u - v).abs().max().item()
 
     def train_run(fused):
-        os.environ["ICB_FUSED_MOE"] = "1" if fused else "0"
         release_workspaces()
         mesh.destroy_model_parallel()
-        tr = Trainer(cfg_for())
+        cfg = cfg_for()
+        cfg.parallel.fused_moe = fused
+        tr = Trainer(cfg)
         return [float(tr.train_step(s)[0]) for s in range(3)]
 
     la, lb = train_run(False), train_run(True)
@@ -334,7 +364,8 @@ def check_fsdp_comm_kernels(rank, world):
 
 def test_fused_tp_kernels_two_gpus():
     _need_two()
-    _spawn("check_raw_kernels")
+    for world in _worlds():
+        _spawn("check_raw_kernels", world)
 
 
 def test_dp2_fused_zero_step_vs_nccl():
@@ -347,8 +378,6 @@ def test_fsdp2_matches_dp2():
     _spawn("check_fsdp2_matches_dp2")
 
 
-@pytest.mark.skipif(os.environ.get("ICB_TEST_EXPERIMENTAL", "0") != "1",
-                    reason="opt-in kernels: run explicitly with ICB_TEST_EXPERIMENTAL=1")
 def test_fsdp_comm_kernels_two_gpus():
     _need_two()
     _spawn("check_fsdp_comm_kernels")

@@ -83,3 +83,18 @@ def test_batch_derivation_and_validation():
     cfg.trainer(micro_batch_size=3)
     with pytest.raises(ValueError):
         validate_config(cfg)
+
+
+def test_param_norm_over_flat_buffers_matches_per_tensor_loop():
+    from helpers import tiny_config
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.trainer import Trainer
+
+    mesh.destroy_model_parallel()
+    cfg = tiny_config("llama")
+    validate_config(cfg)
+    tr = Trainer(cfg)
+    want = torch.sqrt(sum(p.detach().float().pow(2).sum() for p in tr.model.parameters()))
+    got = tr._param_norm()
+    assert torch.allclose(got, want, rtol=1e-5), (float(got), float(want))
