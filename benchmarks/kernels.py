@@ -37,7 +37,7 @@ def time_cuda(fn, iters: int = 10, warmup: int = 3, flush=None) -> float:
     return times[len(times) // 2]
 
 
-def bench_gemm(results, quick: bool):
+def bench_gemm(results, quick: bool, two_sm: bool = False):
     from ironcore_b200.ops import kernels
 
     shapes = [
@@ -48,20 +48,23 @@ def bench_gemm(results, quick: bool):
     if quick:
         shapes = shapes[:2]
     flush = _flush_buffer()
+    two_sm_ok = two_sm and kernels.two_sm_available()
     for name, m, n, k in shapes:
         x = torch.randn(m, k, device="cuda").bfloat16()
         w = torch.randn(k, n, device="cuda").bfloat16()
         dy = torch.randn(m, n, device="cuda").bfloat16()
         flops = 2.0 * m * n * k
         for label, fn, ref in (
-            ("fwd", lambda: kernels.mm_nn(x, w), lambda: torch.matmul(x, w)),
-            ("dgrad", lambda: kernels.mm_nt(dy, w), lambda: torch.matmul(dy, w.t())),
-            ("wgrad", lambda: kernels.mm_tn(x, dy), lambda: torch.matmul(x.t(), dy)),
+            ("fwd", lambda **kw: kernels.mm_nn(x, w, **kw), lambda: torch.matmul(x, w)),
+            ("dgrad", lambda **kw: kernels.mm_nt(dy, w, **kw), lambda: torch.matmul(dy, w.t())),
+            ("wgrad", lambda **kw: kernels.mm_tn(x, dy, **kw), lambda: torch.matmul(x.t(), dy)),
         ):
             ours = time_cuda(fn, flush=flush)
             lib = time_cuda(ref, flush=flush)
+            pair = time_cuda(lambda: fn(two_sm=True), flush=flush) if two_sm_ok else None
             results.append({"kernel": "gemm", "case": f"{name}_{label}", "m": m, "n": n, "k": k, "ms": ours,
-                            "tflops": flops / ours / 1e9, "cublas_ms": lib, "cublas_tflops": flops / lib / 1e9})
+                            "tflops": flops / ours / 1e9, "cublas_ms": lib, "cublas_tflops": flops / lib / 1e9,
+                            "two_sm_ms": pair, "two_sm_tflops": (flops / pair / 1e9) if pair else None})
             print(json.dumps(results[-1]), flush=True)
 
 
@@ -98,6 +101,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=None)
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--two-sm", dest="two_sm", action="store_true", help="also time the CTA-pair (cta_group::2) GEMM")
     ap.add_argument("--only", default=None, help="comma separated subset: gemm,elementwise,attention")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
@@ -106,7 +110,7 @@ def main(argv=None):
     results = []
     only = set(args.only.split(",")) if args.only else None
     if only is None or "gemm" in only:
-        bench_gemm(results, args.quick)
+        bench_gemm(results, args.quick, args.two_sm)
     if only is None or "elementwise" in only:
         bench_elementwise(results, args.quick)
     if only is None or "attention" in only:

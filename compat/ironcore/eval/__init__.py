@@ -1,0 +1,3 @@
+"""Evaluation tasks (reference: ironcore/eval/evaluator.py:20-64)."""
+
+from ironcore_b200.eval import get_evaluators  # noqa: F401

@@ -1,0 +1,12 @@
+"""Tensor-parallel layers, collectives and loss (reference: ironcore/parallel/tensor_parallel/__init__.py)."""
+
+from ironcore_b200.parallel.tensor_parallel import (ColumnParallelLinear, RowParallelLinear,  # noqa: F401
+                                                    VocabParallelEmbedding, vocab_parallel_cross_entropy)
+
+from .comm import (copy_inputs_to_model_parallel_workers, gather_from_model_parallel_workers,  # noqa: F401
+                   reduce_inputs_from_model_parallel_workers, scatter_input_to_model_parallel_workers,
+                   split_to_model_parallel_workers)
+
+__all__ = ["ColumnParallelLinear", "RowParallelLinear", "VocabParallelEmbedding",
+           "copy_inputs_to_model_parallel_workers", "reduce_inputs_from_model_parallel_workers",
+           "scatter_input_to_model_parallel_workers", "vocab_parallel_cross_entropy"]

@@ -1,4 +1,4 @@
-"""Command-line entry: ``ironcore {train,preprocess,rollout} ...`` (also ``python -m ironcore_b200``).
+"""Command-line entry: ``ironcore {train,preprocess,inspect,rollout} ...`` (also ``python -m ironcore_b200``).
 (Behavioural reference: ironcore/__main__.py:16-89.)"""
 
 from __future__ import annotations
@@ -17,6 +17,10 @@ def main(argv=None) -> int:
     p_pre.add_argument("--only-inspect", action="store_true", help="inspect existing outputs, do not preprocess")
     p_pre.add_argument("--preview", type=int, default=0, help="number of samples to preview")
 
+    p_ins = sub.add_parser("inspect", help="integrity checks, statistics and previews of preprocessed data")
+    p_ins.add_argument("--config", required=True, help="dataset YAML (UniversalDataConfig)")
+    p_ins.add_argument("--preview", type=int, default=0, help="number of samples to preview")
+
     p_train = sub.add_parser("train", help="run training from a YAML configuration")
     p_train.add_argument("--config", required=True, help="training YAML")
     p_train.add_argument("--rl", action="store_true", help="run the GRPO loop instead of pre-training")
@@ -30,6 +34,11 @@ def main(argv=None) -> int:
     if args.command == "preprocess":
         from .cli.preprocess import run_preprocess
 
+        return run_preprocess(args) or 0
+    if args.command == "inspect":
+        from .cli.preprocess import run_preprocess
+
+        args.only_inspect, args.inspect = True, True       # same code path as `preprocess --only-inspect`
         return run_preprocess(args) or 0
     if args.command == "train":
         from .cli.train import run_train

@@ -52,12 +52,17 @@ class HellaSwag(Task):
         for i, r in enumerate(rows):
             ids[i, :len(r)] = torch.tensor(r)
         ids = ids.to(dev)
-        logits = model(ids[:, :-1]).float()
-        vocab = getattr(model, "vocab_size", logits.shape[-1])
-        logits = logits[..., :vocab]
-        logp = torch.log_softmax(logits, dim=-1)
         tgt = ids[:, 1:]
-        tok_lp = logp.gather(-1, tgt.unsqueeze(-1)).squeeze(-1)
+        scorer = getattr(getattr(model, "module", model), "token_logprobs", None)
+        if scorer is not None:
+            # vocab-parallel cross entropy: correct under tensor parallelism (every rank holds a vocabulary
+            # shard of the logits and the three per-token scalars are exchanged), and no [rows, vocab] softmax
+            tok_lp = scorer(ids[:, :-1], tgt).float()
+        else:
+            logits = model(ids[:, :-1]).float()
+            vocab = getattr(model, "vocab_size", logits.shape[-1])
+            logp = torch.log_softmax(logits[..., :vocab], dim=-1)
+            tok_lp = logp.gather(-1, tgt.unsqueeze(-1)).squeeze(-1)
         out = []
         for i, (a, b) in enumerate(spans):
             out.append(-tok_lp[i, a - 1:b - 1].mean())

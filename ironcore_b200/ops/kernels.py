@@ -8,7 +8,6 @@ the current CUDA stream. These wrappers have no autograd; see
 
 from __future__ import annotations
 
-import os
 
 from typing import Optional
 
@@ -35,8 +34,28 @@ def _check_2d(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"{name}: row pitch and base address must be multiples of 16 bytes")
 
 
-_USE_2SM = os.environ.get("ICB_GEMM_2SM", "0") == "1"
 native.register("icb_gemm_2sm", [native.P] * 5 + [native.I] * 3 + [native.L] * 4 + [native.I] * 4 + [native.P] * 2)
+
+# Which plain (ungrouped) problems run on the CTA-pair kernel (256 x 256 tiles, tcgen05.mma.cta_group::2):
+# "off" none, "on" all, "auto" those for which ``_two_sm_wins`` says so. Set by ``set_gemm_policy``.
+_TWO_SM_POLICY = "off"
+
+
+def set_gemm_policy(two_sm: str) -> None:
+    global _TWO_SM_POLICY
+    if two_sm not in ("off", "on", "auto"):
+        raise ValueError("two_sm policy must be off, on or auto")
+    _TWO_SM_POLICY = two_sm
+
+
+def two_sm_available() -> bool:
+    lib = native.load()
+    return lib is not None and hasattr(lib, "icb_gemm_2sm")
+
+
+def _two_sm_wins(m: int, n: int, k: int) -> bool:
+    """Large problems only: a CTA pair needs whole 256 x 256 tiles to pay off and at least a few waves."""
+    return m >= 1024 and n >= 1024 and k >= 256
 
 
 def gemm(
@@ -57,12 +76,14 @@ def gemm(
     group_table: Optional[torch.Tensor] = None,
     b_group_stride: int = 0,
     max_ctas: int = 0,
+    two_sm: Optional[bool] = None,
 ) -> torch.Tensor:
     """C[m,n] = A*B (+bias) (+residual) on the tcgen05 GEMM.
 
     a_major 0: ``a`` is [m, k] (k contiguous); 1: ``a`` is [k, m] (m contiguous).
     b_major 0: ``b`` is [n, k] (k contiguous); 1: ``b`` is [k, n] (n contiguous).
     ``residual`` must have the output dtype and may alias ``out`` (accumulation).
+    ``two_sm``: run on CTA pairs (None = the policy set with ``set_gemm_policy``).
     """
     in_dt = a.dtype
     if b.dtype != in_dt or in_dt not in (torch.bfloat16, torch.float16):
@@ -93,8 +114,9 @@ def gemm(
         bias = bias.to(in_dt)
     if group_table is not None and group_table.dtype != torch.int32:
         raise TypeError("group_table must be int32")
-    if group_mode == 0 and _USE_2SM:
-        # experimental: 256 x 256 tiles on CTA pairs (tcgen05.mma.cta_group::2), ICB_GEMM_2SM=1
+    if two_sm is None:
+        two_sm = _TWO_SM_POLICY == "on" or (_TWO_SM_POLICY == "auto" and _two_sm_wins(m, n, k))
+    if group_mode == 0 and two_sm and max_ctas == 0:
         call("icb_gemm_2sm", ptr(a), ptr(b), ptr(out), ptr(bias), ptr(residual), int(m), int(n), int(k), int(lda),
              int(ldb), int(ldc), int(ldr), int(a_major), int(b_major), dtype_code(in_dt),
              1 if out_dtype == torch.float32 else 0, ptr(native.status_tensor(a.device)), stream_ptr())

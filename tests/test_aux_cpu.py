@@ -193,6 +193,36 @@ def test_hellaswag_task_on_inline_examples():
     assert res["metric"] == "accuracy" and 0.0 <= res["score"] <= 100.0
 
 
+def _hellaswag_tp_worker(rank, world, out_path):
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.eval.tasks.hellaswag import HellaSwag
+    from ironcore_b200.models import LanguageModel
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.tokenizer import Tokenizer
+
+    cfg = tiny_config("llama", max_seq_len=64, max_position_embeddings=64)
+    cfg.trainer.tensor_model_parallel_size = world
+    cfg.parallel(world_size=world, rank=rank)
+    validate_config(cfg)
+    mesh.initialize_model_parallel(world)
+    torch.manual_seed(3)
+    model = LanguageModel(cfg).eval()
+    task = HellaSwag(Tokenizer(512, 511, 0, 8), 1, None, examples=[])
+    losses = task.score_example(model, "a b c d", ["e", "f g", "hh", "i j k"])
+    if rank == 0:
+        torch.save(losses, out_path)
+
+
+def test_hellaswag_scores_do_not_depend_on_tensor_parallel_size(tmp_path):
+    """The ending losses are a softmax over the whole vocabulary: with the logits sharded over two ranks
+    they must equal the single-rank values (a softmax over the local shard would not)."""
+    a, b = str(tmp_path / "tp1.pt"), str(tmp_path / "tp2.pt")
+    run_distributed(_hellaswag_tp_worker, 1, a)
+    run_distributed(_hellaswag_tp_worker, 2, b)
+    la, lb = torch.load(a), torch.load(b)
+    assert torch.allclose(la, lb, atol=1e-4), (la, lb)
+
+
 def test_gpt2_loss_curve_matches_reference_cpu():
     """Same weights, same batches, same optimizer settings: the loss curve of the unmodified reference
     trainer and ours agree step by step (fp32, CPU). Runs in a child process because the reference

@@ -122,6 +122,7 @@ def test_gemm_2sm_matches_reference(a_major, b_major):
     from ironcore_b200.ops import kernels  # noqa: F401  (registers icb_gemm_2sm)
 
     torch.manual_seed(3)
+    native.set_wait_limit_us(200000)     # a protocol mistake in the pair ends after 0.2 s per wait, not 2 s
     for (m, n, k) in [(256, 256, 64), (512, 768, 256), (384, 320, 192), (4096, 1536, 1024)]:
         a = torch.randn((m, k) if a_major == 0 else (k, m), device="cuda").bfloat16()
         b = torch.randn((n, k) if b_major == 0 else (k, n), device="cuda").bfloat16()
@@ -135,3 +136,4 @@ def test_gemm_2sm_matches_reference(a_major, b_major):
         ref = af @ bf
         err = (out.float() - ref).abs().max().item()
         assert err <= 2e-2 * (k ** 0.5) + 2.0 ** -7 * ref.abs().max().item(), (m, n, k, err)
+    native.set_wait_limit_us(0)
