@@ -343,6 +343,7 @@ def run_grpo(args, shape, world, rank, dev):
     prompt = torch.randint(0, c["vocab"], (per_rank // c["group"], c["prompt_len"]), generator=g).to(dev)
     prompt = prompt.repeat_interleave(c["group"], 0)
 
+    @torch.no_grad()      # (a decorator on run_grpo alone would not cover this closure, which runs later)
     def step():
         caches = [(torch.empty(per_rank, c["kv_heads"], total, c["hd"], dtype=torch.bfloat16, device=dev),
                    torch.empty(per_rank, c["kv_heads"], total, c["hd"], dtype=torch.bfloat16, device=dev), 0)

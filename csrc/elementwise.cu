@@ -398,6 +398,38 @@ __global__ void clip_coef_kernel(const float* __restrict__ total_sq, float clip,
   *coef_out = c;
 }
 
+template <bool BF16>
+__global__ void cast_add_kernel(const float* __restrict__ acc, const uint16_t* __restrict__ residual,
+                                uint16_t* __restrict__ out, long long M, int N, long long ldr, long long ldo) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int vec_per_row = N >> 3;
+  if (i >= M * vec_per_row) return;
+  const long long row = i / vec_per_row;
+  const int col = (int)(i - row * vec_per_row) * 8;
+  const float4 a = *reinterpret_cast<const float4*>(acc + row * N + col);
+  const float4 b = *reinterpret_cast<const float4*>(acc + row * N + col + 4);
+  float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  if (residual != nullptr) {
+    const uint4 u = *reinterpret_cast<const uint4*>(residual + row * ldr + col);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 f = BF16 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
+      v[2 * t] += f.x;
+      v[2 * t + 1] += f.y;
+    }
+  }
+  uint4 o;
+  if (BF16) {
+    o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+    o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+  } else {
+    o.x = pack_f16x2(v[0], v[1]); o.y = pack_f16x2(v[2], v[3]);
+    o.z = pack_f16x2(v[4], v[5]); o.w = pack_f16x2(v[6], v[7]);
+  }
+  *reinterpret_cast<uint4*>(out + row * ldo + col) = o;
+}
+
 }  // namespace icb
 
 using namespace icb;
@@ -447,6 +479,25 @@ ICB_API int icb_glu_bwd(const void* dy, const void* x, void* dx, long long M, in
     glu_bwd_kernel<false><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(dy), ICB_U16(x), ICB_U16M(dx), M, F, kind, gate_is_act);
   return check_launch("glu_bwd");
 }
+// out[M, N] (16-bit, pitch ldo) = acc[M, N] (fp32, contiguous) (+ residual[M, N], 16-bit, pitch ldr): the closing
+// step of a split-K product, whose partial tiles were summed in fp32. N a multiple of 8; 16-byte aligned rows.
+ICB_API int icb_cast_add(const float* acc, const void* residual, void* out, long long M, int N, long long ldr,
+                         long long ldo, int dtype, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (N % 8 || (dtype != kBF16 && dtype != kF16)) return -2;
+  const long long nvec = M * (N / 8);
+  const int threads = 256;
+  const int blocks = (int)((nvec + threads - 1) / threads);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == kBF16)
+    cast_add_kernel<true><<<blocks, threads, 0, st>>>(acc, reinterpret_cast<const uint16_t*>(residual),
+                                                      reinterpret_cast<uint16_t*>(out), M, N, ldr, ldo);
+  else
+    cast_add_kernel<false><<<blocks, threads, 0, st>>>(acc, reinterpret_cast<const uint16_t*>(residual),
+                                                       reinterpret_cast<uint16_t*>(out), M, N, ldr, ldo);
+  return check_launch("cast_add_kernel");
+}
+
 ICB_API int icb_act_fwd(const void* x, void* y, long long n, int kind, int dtype, void* stream) {
   if (n <= 0) return 0;
   if (n % 8) return -2;

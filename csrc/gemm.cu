@@ -19,6 +19,10 @@
 //   arrival counters with system-scope releases, while the tensor core works on the row
 //   blocks that are already there (local shard first, then the shards in the order they
 //   arrive). The TMA producer waits (acquire, bounded) on the counters of remote blocks.
+// * Split-K (plain problems with few output tiles, e.g. decode steps with a handful of token rows): the
+//   work items are (tile, K range) pairs, so a 64 x 2048 x 1536 product runs on 48 CTAs instead of 8 and
+//   streams the weights at memory bandwidth; partial tiles are added into a zeroed fp32 C by TMA
+//   reduce-add, bias and residual by the first K range only.
 // * Every wait is bounded: on timeout a status word is set and the kernel drains.
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA
@@ -40,6 +44,8 @@ struct GemmArgs {
   long long ldr;
   int in_fmt;                // 0 fp16, 1 bf16
   int out_f32;               // 0: output dtype == input dtype, 1: fp32
+  int split_k;               // >1: every output tile is computed by split_k CTAs over disjoint K ranges of
+  int k_per_split;           //     k_per_split elements each, accumulated into a zeroed fp32 C with TMA reduce-add
   int* status;
   // ---- fused all-gather (AG kernels only) ----
   int ag_rank, ag_world;            // this rank / group size
@@ -195,6 +201,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   const int tiles_per_group = args.num_m_tiles * args.num_n_tiles;
   const int total_tiles = (args.group_mode == 2 ? args.num_groups : 1) * tiles_per_group;
+  const int total_work = total_tiles * (args.split_k > 1 ? args.split_k : 1);
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -216,8 +223,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (args.ag_debug != nullptr && ag_seen == 0ull) args.ag_debug[blockIdx.x * 4 + 2] = globaltimer_ns();
         if (rb < 64) ag_seen |= (1ull << rb);
       };
-      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      for (int work = blockIdx.x; work < total_work; work += gridDim.x) {
         int grp = 0, k_begin = 0, k_end = args.K;
+        int tile = work;
+        if (args.split_k > 1) {
+          tile = work / args.split_k;
+          k_begin = (work - tile * args.split_k) * args.k_per_split;
+          k_end = min(args.K, k_begin + args.k_per_split);
+        }
         int local = tile;
         if (args.group_mode == 2) {
           grp = tile / tiles_per_group;
@@ -275,8 +288,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(kBM, BN, args.in_fmt, A_MAJOR, B_MAJOR);
       uint32_t it = 0, tcount = 0;
-      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      for (int work = blockIdx.x; work < total_work; work += gridDim.x) {
         int k_begin = 0, k_end = args.K;
+        int tile = work;
+        if (args.split_k > 1) {
+          tile = work / args.split_k;
+          k_begin = (work - tile * args.split_k) * args.k_per_split;
+          k_end = min(args.K, k_begin + args.k_per_split);
+        }
         int local = tile;
         if (args.group_mode == 2) {
           const int grp = tile / tiles_per_group;
@@ -328,8 +347,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int esz = args.out_f32 ? 4 : 2;
     const int cols_per_slab = 128 / esz;  // 64 (16-bit) or 32 (fp32)
     uint32_t tcount = 0, slab_count = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    for (int work = blockIdx.x; work < total_work; work += gridDim.x) {
       int grp = 0, k_begin = 0, k_end = args.K;
+      int tile = work;
+      bool first_split = true;     // bias and residual are added by the first K range only
+      if (args.split_k > 1) {
+        tile = work / args.split_k;
+        const int ks = work - tile * args.split_k;
+        k_begin = ks * args.k_per_split;
+        k_end = min(args.K, k_begin + args.k_per_split);
+        first_split = ks == 0;
+      }
       int local = tile;
       if (args.group_mode == 2) {
         grp = tile / tiles_per_group;
@@ -386,7 +414,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
         const int n_glob = n0 + col0;
-        if (bias_base != nullptr) {
+        if (bias_base != nullptr && first_split) {
           if (n_glob + 32 <= args.N) {
             const uint4* bp = reinterpret_cast<const uint4*>(bias_base + (size_t)n_glob * 2);
 #pragma unroll
@@ -420,7 +448,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
           }
         }
-        if (args.residual != nullptr && row_ok) {
+        if (args.residual != nullptr && row_ok && first_split) {
           const uint8_t* rp = reinterpret_cast<const uint8_t*>(args.residual) +
                               ((size_t)cz * args.M * args.ldr + (size_t)m_glob * args.ldr + n_glob) * esz;
           const bool vec_ok = (n_glob + 32 <= args.N) && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0);
@@ -495,7 +523,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           named_barrier(1, 128);
           if (et == 0) {
             const int slab_col0 = n0 + col0 - slab_sub * 32;
-            if (slab_col0 < args.N) tma_store_3d(&tmC, slab, slab_col0, m0, cz);
+            if (slab_col0 < args.N) {
+              if (args.split_k > 1) tma_reduce_add_3d(&tmC, slab, slab_col0, m0, cz);
+              else tma_store_3d(&tmC, slab, slab_col0, m0, cz);
+            }
             tma_store_commit();
           }
           ++slab_count;
@@ -565,9 +596,11 @@ using namespace icb;
 static int gemm_impl(const void* A, const void* B, void* C, const void* bias, const void* residual, int M, int N,
                      int K, long long lda, long long ldb, long long ldc, long long ldr, int a_major, int b_major,
                      int in_dtype, int out_f32, int group_mode, int num_groups, const int* group_table,
-                     long long b_group_stride, int* status, int max_ctas, void* stream_, const GemmArgs* ag) {
+                     long long b_group_stride, int* status, int max_ctas, void* stream_, const GemmArgs* ag,
+                     int split_k = 1) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0) return 0;
+  if (split_k > 1 && (group_mode != 0 || ag != nullptr || !out_f32)) return -8;
   if (in_dtype != kBF16 && in_dtype != kF16) return -2;
   if (group_mode == 2 && !(a_major == 1 && b_major == 1)) return -3;
   const int es = 2;
@@ -636,8 +669,17 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, co
   args.in_fmt = (in_dtype == kBF16) ? 1 : 0;
   args.out_f32 = out_f32;
   args.status = status;
+  args.split_k = 1;
+  args.k_per_split = K;
+  if (split_k > 1) {
+    const int kblocks = (K + kBK - 1) / kBK;
+    const int per = (kblocks + split_k - 1) / split_k;
+    args.k_per_split = per * kBK;
+    args.split_k = (kblocks + per - 1) / per;      // no empty K range
+  }
 
-  long long total = (long long)args.num_m_tiles * args.num_n_tiles * (group_mode == 2 ? num_groups : 1);
+  long long total = (long long)args.num_m_tiles * args.num_n_tiles * (group_mode == 2 ? num_groups : 1) *
+                    args.split_k;
   int grid = num_sms();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (total < grid) grid = (int)total;
@@ -661,6 +703,17 @@ ICB_API int icb_gemm(const void* A, const void* B, void* C, const void* bias, co
                      long long b_group_stride, int* status, int max_ctas, void* stream_) {
   return gemm_impl(A, B, C, bias, residual, M, N, K, lda, ldb, ldc, ldr, a_major, b_major, in_dtype, out_f32,
                    group_mode, num_groups, group_table, b_group_stride, status, max_ctas, stream_, nullptr);
+}
+
+// icb_gemm with every output tile split over `split_k` CTAs along K. C must be fp32 (out_f32 = 1) and zeroed by the
+// caller (stream order): the partial tiles are accumulated into it with TMA reduce-add; bias and residual (fp32,
+// must not alias C) enter once. Plain problems only. For a few token rows against a wide weight matrix this turns
+// a handful of CTAs into a grid that streams the weights at memory bandwidth.
+ICB_API int icb_gemm_splitk(const void* A, const void* B, void* C, const void* bias, const void* residual, int M, int N,
+                            int K, long long lda, long long ldb, long long ldc, long long ldr, int a_major, int b_major,
+                            int in_dtype, int split_k, int* status, void* stream_) {
+  return gemm_impl(A, B, C, bias, residual, M, N, K, lda, ldb, ldc, ldr, a_major, b_major, in_dtype, 1, 0, 1, nullptr,
+                   0, status, 0, stream_, nullptr, split_k);
 }
 
 // Optional instrumentation of the fused all-gather kernels: a device buffer of [148][4] 64-bit nanosecond

@@ -1,4 +1,4 @@
-// Two-SM tcgen05 GEMM for sm_100a (experimental; selected with ICB_GEMM_2SM=1, off by default).
+// Two-SM tcgen05 GEMM for sm_100a: the default kernel for large plain problems (see ops/kernels.py).
 //
 // A thread-block cluster of two CTAs on neighbouring SMs computes one 256 x 256 output tile with
 // tcgen05.mma.cta_group::2: each CTA stages its own 128 rows of A and its own 128 columns of B
@@ -14,7 +14,6 @@
 //   tfull[a]  (own): commit to both CTAs when a tile's accumulator is complete.
 //   tempty[a] (leader's): all 256 epilogue threads of the pair arrive (the peer's remotely).
 // No TMA load is multicast; every wait is bounded (status word, drain, TMEM freed).
-#include <cstdlib>
 
 #include "gemm_common.cuh"
 #include "host_common.h"

@@ -8,7 +8,10 @@
 //                     whole GQA group from one pass over that head's pages, so K and V are read once
 //                     per group (decode is bound by KV bytes, not FLOPs). Each warp walks pages with
 //                     an online softmax (two lanes per token for the q.k dot products, four output
-//                     dims per lane for p.V), and the four warps are merged through shared memory.
+//                     dims per lane for p.V), and the eight warps are merged through shared memory.
+//                     All loads of a 16-token step (the K half rows, then the 16 V rows) are issued
+//                     before they are consumed: a warp owns only a few steps, so the kernel is bound
+//                     by load latency unless a step keeps many loads in flight.
 #include "host_common.h"
 #include "ptx.cuh"
 
@@ -38,7 +41,7 @@ __global__ void kv_append_kernel(const uint16_t* __restrict__ k, const uint16_t*
   }
 }
 
-constexpr int kPdWarps = 4;
+constexpr int kPdWarps = 8;
 constexpr int kPdMaxGroup = 8;
 
 template <int HD, bool BF16>
@@ -80,6 +83,18 @@ paged_decode_kernel(const uint16_t* __restrict__ q, long long q_stride, const ui
     const int blk = block_table[(size_t)seq * max_blocks + page];
     const int tok0 = page * block_size + (step - page * steps_per_page) * 16;
     const int in_blk0 = tok0 - page * block_size;
+    // ---- the step's 16 V rows (4 output dims per lane) are requested before anything is computed ----
+    const int n_tok = min(16, ctx - tok0);
+    const uint16_t* vbase = v_cache + ((size_t)blk * block_size + in_blk0) * row_elems + kvh * HD + lane * OD;
+    uint2 vu[16];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      vu[t] = make_uint2(0u, 0u);
+      if (t < n_tok) {
+        if (OD == 4) vu[t] = *reinterpret_cast<const uint2*>(vbase + (size_t)t * row_elems);
+        else vu[t].x = *reinterpret_cast<const uint32_t*>(vbase + (size_t)t * row_elems);
+      }
+    }
     // ---- scores for 16 tokens x G heads ----
     const int my_tok = tok0 + tok_in_pair;
     const bool tok_ok = my_tok < ctx;
@@ -88,10 +103,12 @@ paged_decode_kernel(const uint16_t* __restrict__ q, long long q_stride, const ui
     for (int g = 0; g < kPdMaxGroup; ++g) s[g] = 0.f;
     if (tok_ok) {
       const uint16_t* kr = k_cache + ((size_t)blk * block_size + in_blk0 + tok_in_pair) * row_elems + kvh * HD + half * HALF;
+      uint4 ku[HALF / 8];
+#pragma unroll
+      for (int c = 0; c < HALF / 8; ++c) ku[c] = *reinterpret_cast<const uint4*>(kr + c * 8);
 #pragma unroll
       for (int c = 0; c < HALF / 8; ++c) {
-        const uint4 u = *reinterpret_cast<const uint4*>(kr + c * 8);
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+        const uint32_t w[4] = {ku[c].x, ku[c].y, ku[c].z, ku[c].w};
         float kf[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -135,25 +152,22 @@ paged_decode_kernel(const uint16_t* __restrict__ q, long long q_stride, const ui
         for (int d = 0; d < OD; ++d) o[g][d] *= corr;
       }
     }
-    // ---- O += P V : lane owns OD output dims, loops over the 16 tokens ----
-    const int n_tok = min(16, ctx - tok0);
-    for (int t = 0; t < n_tok; ++t) {
-      const uint16_t* vr = v_cache + ((size_t)blk * block_size + in_blk0 + t) * row_elems + kvh * HD + lane * OD;
+    // ---- O += P V : lane owns OD output dims of the 16 rows fetched above ----
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
       float vf[OD];
       if (OD == 4) {
-        const uint2 u = *reinterpret_cast<const uint2*>(vr);
-        float2 a = BF16 ? unpack_bf16x2(u.x) : __half22float2(*reinterpret_cast<const __half2*>(&u.x));
-        float2 b = BF16 ? unpack_bf16x2(u.y) : __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+        float2 a = BF16 ? unpack_bf16x2(vu[t].x) : __half22float2(*reinterpret_cast<const __half2*>(&vu[t].x));
+        float2 b = BF16 ? unpack_bf16x2(vu[t].y) : __half22float2(*reinterpret_cast<const __half2*>(&vu[t].y));
         vf[0] = a.x; vf[1] = a.y; vf[2 % OD] = b.x; vf[3 % OD] = b.y;
       } else {
-        const uint32_t u = *reinterpret_cast<const uint32_t*>(vr);
-        float2 a = BF16 ? unpack_bf16x2(u) : __half22float2(*reinterpret_cast<const __half2*>(&u));
+        float2 a = BF16 ? unpack_bf16x2(vu[t].x) : __half22float2(*reinterpret_cast<const __half2*>(&vu[t].x));
         vf[0] = a.x; vf[1 % OD] = a.y;
       }
 #pragma unroll
       for (int g = 0; g < kPdMaxGroup; ++g) {
         if (g < G) {
-          const float pt = __shfl_sync(0xffffffffu, p[g], 2 * t);
+          const float pt = __shfl_sync(0xffffffffu, p[g], 2 * t);   // 0 for tokens past the context
 #pragma unroll
           for (int d = 0; d < OD; ++d) o[g][d] += pt * vf[d];
         }

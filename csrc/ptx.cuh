@@ -188,6 +188,13 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* tm, const void* 
       "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
+// Element-wise add of a shared-memory tile into global memory (fp32 / 16-bit, per the tensor map's dtype).
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* tm, const void* src, int x, int y, int z) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(tm)),
+               "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {

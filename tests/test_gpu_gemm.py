@@ -1,8 +1,6 @@
 """tcgen05 GEMM against an fp32 PyTorch reference: every operand-major combination,
 ragged shapes, epilogue options and the grouped (mixture-of-experts) forms."""
 
-import os
-
 import pytest
 import torch
 
@@ -60,6 +58,29 @@ def test_gemm_epilogue_bias_residual_fp32():
     _check(out2, ref2, k, tol=1e-2)
 
 
+@pytest.mark.parametrize("m,n,k", [(64, 2048, 1536), (64, 1536, 8960), (8, 17920, 1536), (130, 520, 1000)])
+def test_gemm_split_k_small_m(m, n, k):
+    """Decode-shaped products (a few token rows against a wide weight matrix) take the split-K path: the K
+    ranges of one output tile are computed by different CTAs and accumulated with TMA reduce-add."""
+    from ironcore_b200.ops import kernels, native
+
+    torch.manual_seed(2)
+    assert kernels._split_k_for(m, n, k) > 1
+    x, w = _mk(m, k), _mk(k, n, scale=k ** -0.5)
+    bias = _mk(1, n).reshape(n)
+    res = _mk(m, n)
+    ref = x.float() @ w.float()
+    _check(kernels.mm_nn(x, w), ref, k)
+    _check(kernels.mm_nn(x, w, bias=bias, residual=res), ref + bias.float() + res.float(), k)
+    wt = w.t().contiguous()                               # [n, k]: the dgrad / tied-head orientation
+    _check(kernels.mm_nt(x, wt), ref, k)
+    # run to run the accumulation order of the K ranges may differ: results agree to fp32 rounding
+    a, b = kernels.mm_nn(x, w), kernels.mm_nn(x, w)
+    assert (a.float() - b.float()).abs().max().item() <= 2.0 ** -7 * ref.abs().max().item()
+    torch.cuda.synchronize()
+    native.check_status()
+
+
 def test_gemm_fp16():
     from ironcore_b200.ops import kernels
 
@@ -111,9 +132,6 @@ def test_gemm_grouped_by_k_range():
         _check(out[i], refs[i], 320)
 
 
-@pytest.mark.gpu
-@pytest.mark.skipif(os.environ.get("ICB_TEST_2SM", "0") != "1",
-                    reason="experimental CTA-pair GEMM: run explicitly with ICB_TEST_2SM=1")
 @pytest.mark.parametrize("a_major,b_major", [(0, 1), (0, 0), (1, 1), (1, 0)])
 def test_gemm_2sm_matches_reference(a_major, b_major):
     """256 x 256 tiles on CTA pairs (tcgen05.mma.cta_group::2) against fp32 matmul, ragged edges included."""
@@ -137,3 +155,30 @@ def test_gemm_2sm_matches_reference(a_major, b_major):
         err = (out.float() - ref).abs().max().item()
         assert err <= 2e-2 * (k ** 0.5) + 2.0 ** -7 * ref.abs().max().item(), (m, n, k, err)
     native.set_wait_limit_us(0)
+
+
+def test_gemm_2sm_epilogue_and_policy():
+    """Bias, residual and in-place fp32 accumulation on the CTA-pair kernel, and the automatic choice:
+    large plain problems take the pair kernel, small and grouped ones the single-CTA kernel; both agree."""
+    from ironcore_b200.ops import kernels, native
+
+    torch.manual_seed(8)
+    m, n, k = 1024, 1280, 512
+    x, w = _mk(m, k), _mk(k, n)
+    bias, res = _mk(1, n).reshape(n), _mk(m, n)
+    ref = x.float() @ w.float() + bias.float() + res.float()
+    assert kernels._two_sm_wins(m, n, k) and not kernels._two_sm_wins(256, 256, 64)
+    a = kernels.mm_nn(x, w, bias=bias, residual=res, two_sm=True)
+    b = kernels.mm_nn(x, w, bias=bias, residual=res, two_sm=False)
+    c = kernels.mm_nn(x, w, bias=bias, residual=res)            # policy: auto
+    _check(a, ref, k)
+    _check(b, ref, k)
+    assert torch.equal(a, c)
+    acc = torch.randn(k, n, device="cuda")
+    dy = _mk(m, n)
+    ref2 = acc + x.float().t() @ dy.float()
+    out = kernels.mm_tn(x, dy, out=acc, residual=acc, out_dtype=torch.float32, two_sm=True)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert out.data_ptr() == acc.data_ptr()
+    _check(out, ref2, m, tol=1e-2)

@@ -91,3 +91,35 @@ def test_rollout_engine_with_cuda_graph_matches_eager():
     # decode path agrees with the cache-less training forward on the chosen tokens' log-probs
     full = model.token_logprobs(t1[:, :-1], t1[:, 1:])[:, 31:]
     assert (full - lp1).abs().max().item() < 0.15
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_gumbel_sampling_kernel(dtype):
+    """One-pass sampling kernel: the reported log-prob is log_softmax at the sampled token, padded columns are
+    never drawn, the same (seed, draw) reproduces the sample, and the draws follow softmax(logits / T)."""
+    from ironcore_b200.rl.sampling import sample_tokens
+
+    torch.manual_seed(4)
+    s, v, valid, temp = 33, 5000, 4931, 0.7
+    logits = (torch.randn(s, v, device="cuda") * 3).to(dtype)
+    g1, g2 = (torch.Generator(device="cuda") for _ in range(2))
+    g1.manual_seed(11), g2.manual_seed(11)
+    tok, lp = sample_tokens(logits, temp, generator=g1, vocab_start=100, vocab_valid=valid)
+    tok2, lp2 = sample_tokens(logits, temp, generator=g2, vocab_start=100, vocab_valid=valid)
+    assert torch.equal(tok, tok2) and torch.equal(lp, lp2)
+    local = tok - 100
+    assert int(local.min()) >= 0 and int(local.max()) < valid
+    ref = torch.log_softmax(logits.float()[:, :valid] / temp, dim=-1).gather(1, local[:, None]).squeeze(1)
+    assert torch.allclose(lp, ref, atol=2e-3, rtol=1e-4), (lp - ref).abs().max().item()
+    # a second draw from the same generator differs
+    tok3, _ = sample_tokens(logits, temp, generator=g1, vocab_start=100, vocab_valid=valid)
+    assert not torch.equal(tok, tok3)
+    # distribution: 40 000 rows of the same 12 logits
+    base = torch.tensor([2.0, 1.0, 0.0, -1.0, 0.5, 1.5, -2.0, 0.2, 0.9, -0.5, 1.2, 0.0], device="cuda")
+    n = 40000
+    many = base.to(dtype).repeat(n, 1)
+    draws, _ = sample_tokens(many, 1.0, generator=g1)
+    freq = torch.bincount(draws, minlength=12).float() / n
+    want = torch.softmax(base.to(dtype).float(), -1)
+    sigma = torch.sqrt(want * (1 - want) / n)
+    assert ((freq - want).abs() < 5 * sigma + 1e-4).all(), (freq, want)
