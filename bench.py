@@ -94,7 +94,7 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def build_config(world: int, steps: int, fused=None, graph=None):
+def build_config(world: int, steps: int, fused=None, graph=None, norm_gather: str = "auto"):
     from ironcore_b200.config import default_config, validate_config
 
     c = default_config()
@@ -102,14 +102,14 @@ def build_config(world: int, steps: int, fused=None, graph=None):
     c.data(task_type="synthetic", vocab_size=32000, synthetic_seed=1234)
     c.trainer(micro_batch_size=1, train_batch_size=GLOBAL_BATCH, gradient_accumulation_steps=None,
               tensor_model_parallel_size=world, log_interval=10 ** 9, model_path="", use_flash_attn=True,
-              cuda_graph=(os.environ.get("ICB_CUDA_GRAPH", "1" if world > 1 else "0") != "0") if graph is None else graph)
+              cuda_graph=(world > 1) if graph is None else graph)
     c.operation(train_steps=10 ** 6, no_save=True)
     c.optim(optimizer="adam", max_lr=3e-4, min_lr=3e-5, adam_beta1=0.9, adam_beta2=0.95, weight_decay=0.1,
             clip_grad=1.0, warmup_steps=0)
     c.init(init_std=0.02, seed=1234)
     c.parallel(world_size=world, rank=int(os.environ.get("RANK", "0")), local_rank=int(os.environ.get("LOCAL_RANK", "0")),
                sequence_parallel=world > 1, zero_stage=1,
-               fused_comm=(os.environ.get("ICB_FUSED_COMM", "1") != "0") if fused is None else fused)
+               fused_comm=True if fused is None else fused, fused_norm_gather=norm_gather)
     c.utils(report_memory_usage=False)
     validate_config(c)
     return c
@@ -126,7 +126,7 @@ def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
-    cfg = build_config(world, args.steps)
+    cfg = build_config(world, args.steps, norm_gather=args.norm_gather)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     trainer = Trainer(cfg)
@@ -259,6 +259,8 @@ def run_ours(args):
                                    + ("NVLS multimem.ld_reduce" if getattr(fused_ws, "nvls_rs", False) else "P2P stores")
                                    + ")"
                                    if (world > 1 and fused_ws is not None) else ("nccl" if world > 1 else "none")),
+                       "norm_boundaries_fused": sum(int(getattr(l, "fuse_norm_gather", False))
+                                                    for l in trainer.model.model.layers),
                        "optimizer": "adam(0.9,0.95) lr 3e-4, clip 1.0, fp32 grad accumulation",
                        "cuda_graph": bool(cfg.trainer.cuda_graph),
                        "l2": "no flush needed: every pass streams 13.5 GB of weights, far larger than the 126 MB L2"},
@@ -303,6 +305,8 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ironcore_b200", choices=["ironcore_b200", "ours", "reference"])
+    ap.add_argument("--norm-gather", dest="norm_gather", default="auto", choices=["auto", "on", "off"],
+                    help="fuse reduce-scatter + RMSNorm + all-gather across the norm boundaries (auto: TP >= 4)")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         from baseline.reference_arm import run_reference

@@ -48,7 +48,11 @@ struct RsArgs {
   // ---- fused RMSNorm + all-gather push of the reduced rows (norm_gamma == null: off) ----
   const void* norm_gamma;          // [N] gain, 16-bit
   float norm_eps, norm_w_offset;   // y = h * rsqrt(mean(h^2) + eps) * (gamma + w_offset)
-  float* norm_rstd;                // [rows_per_rank] fp32, kept for the backward pass
+  float* norm_rstd;                // [rows_per_rank] fp32: written by the forward form, read by the backward form
+  int norm_bwd;                    // 0: forward (normalise the reduced rows); 1: backward (see rs_reduce_norm_push)
+  const void* norm_x;              // backward: the norm's input rows [rows_per_rank, norm_ldx], 16-bit
+  long long norm_ldx;
+  void* aux_out;                   // backward: the reduced rows themselves [rows_per_rank, N], 16-bit
   uint8_t* const* ag_peers;        // device array [world]: every rank's gather buffer [world * rows_per_rank][N]
   uint8_t* ag_mc;                  // multicast address of the gather buffer or null (P2P stores)
   int* const* ag_peer_ready;       // device array [world]: every rank's per-128-row arrival counters
@@ -85,7 +89,13 @@ __device__ __forceinline__ uint4 rs_pack8(const float (&a)[8]) {
 // kCU * kSB 16-byte loads in flight (the phase is latency bound: a warp owns only a few rows).
 // The counters of a finished unit are published after the loads of the next unit have been issued:
 // by then the unit's remote stores have been acknowledged and the system-scope fence is cheap.
-template <bool BF16, int kCU, int kSB>
+//
+// BWD = false (forward):  h = sum(partials) + bias + residual  -> out ;  push  h * rstd * (gamma + off)
+// BWD = true  (backward of the same boundary): the reduced rows are dn, the gradient of the normalised
+//   activations. dn -> aux_out (kept for the gain's gradient); with xh = x * rstd and g = dn * (gamma + off):
+//   dx = rstd * (g - xh * mean(g * xh)) + residual  -> out and pushed (the input gradient of the
+//   row-parallel layer that produced x, gathered for that layer's dgrad and wgrad).
+template <bool BF16, int kCU, int kSB, bool BWD>
 __device__ __noinline__ void rs_reduce_norm_push(const RsArgs& args, int warp, int lane) {
   const int nwarps = kGemmThreads / 32;
   const int gw = blockIdx.x * nwarps + warp;
@@ -94,6 +104,7 @@ __device__ __noinline__ void rs_reduce_norm_push(const RsArgs& args, int warp, i
   const int units = args.rows_per_rank / args.ag_rows_per_unit;
   const int target = args.world * (*args.epoch_ptr + 1);
   const size_t slot_stride = (size_t)args.rows_per_rank * N * 2;   // bytes between two source ranks' slots
+  const uint8_t* gamma = reinterpret_cast<const uint8_t*>(args.norm_gamma);
   int checked_lm = -1, checked_ok = 0;
   int pending_rb = -1;                                             // unit whose counters are not yet published
   auto publish = [&](int rb) {
@@ -121,10 +132,15 @@ __device__ __noinline__ void rs_reduce_norm_push(const RsArgs& args, int warp, i
     for (int r = 0; r < args.ag_rows_per_unit; ++r) {
       const int lrow = row0 + r;
       uint8_t* out_row = reinterpret_cast<uint8_t*>(args.out) + (size_t)lrow * args.ldo * 2;
+      // forward: the reduced row itself is the first output; backward: it goes to the auxiliary output
+      uint8_t* red_row = BWD ? reinterpret_cast<uint8_t*>(args.aux_out) + (size_t)lrow * N * 2 : out_row;
       const uint8_t* res_row = args.residual != nullptr
                                    ? reinterpret_cast<const uint8_t*>(args.residual) + (size_t)lrow * args.ldr * 2
                                    : nullptr;
-      // ---- pass 1: sum of the partials (+ bias + residual) -> residual-stream row, sum of squares
+      const uint8_t* x_row = BWD ? reinterpret_cast<const uint8_t*>(args.norm_x) + (size_t)lrow * args.norm_ldx * 2
+                                 : nullptr;
+      const float rstd_in = BWD ? args.norm_rstd[lrow] : 0.f;
+      // ---- pass 1: sum of the partials -> reduced row; row statistic (sum of squares / <g, xh>)
       float ss = 0.f;
       for (int c0 = lane * 8; c0 < N; c0 += 256 * kCU) {
         float acc[kCU][8];
@@ -133,12 +149,13 @@ __device__ __noinline__ void rs_reduce_norm_push(const RsArgs& args, int warp, i
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
         }
-        uint4 rv[kCU];
-        if (res_row != nullptr) {
+        uint4 rv[kCU];     // forward: residual; backward: x (the norm's input)
+        const uint8_t* side_row = BWD ? x_row : res_row;
+        if (side_row != nullptr) {
 #pragma unroll
           for (int i = 0; i < kCU; ++i) {
             const int col = c0 + i * 256;
-            if (col < N) rv[i] = *reinterpret_cast<const uint4*>(res_row + (size_t)col * 2);
+            if (col < N) rv[i] = *reinterpret_cast<const uint4*>(side_row + (size_t)col * 2);
           }
         }
         if (args.mc_recv != nullptr) {
@@ -190,23 +207,34 @@ __device__ __noinline__ void rs_reduce_norm_push(const RsArgs& args, int warp, i
             if (args.bias != nullptr)
               rs_acc8<BF16>(acc[i], *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(args.bias) +
                                                                      (size_t)col * 2));
-            if (res_row != nullptr) rs_acc8<BF16>(acc[i], rv[i]);
+            if (!BWD && res_row != nullptr) rs_acc8<BF16>(acc[i], rv[i]);
             const uint4 o = rs_pack8<BF16>(acc[i]);
-            *reinterpret_cast<uint4*>(out_row + (size_t)col * 2) = o;
-            // statistics of the rounded values: the backward pass re-reads exactly these
+            *reinterpret_cast<uint4*>(red_row + (size_t)col * 2) = o;
+            // statistics of the rounded values: what a separate norm kernel would read back
             float hr[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) hr[j] = 0.f;
             rs_acc8<BF16>(hr, o);
+            if (!BWD) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) ss += hr[j] * hr[j];
+              for (int j = 0; j < 8; ++j) ss += hr[j] * hr[j];
+            } else {
+              float xv[8], g[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { xv[j] = 0.f; g[j] = args.norm_w_offset; }
+              rs_acc8<BF16>(xv, rv[i]);
+              rs_acc8<BF16>(g, *reinterpret_cast<const uint4*>(gamma + (size_t)col * 2));
+#pragma unroll
+              for (int j = 0; j < 8; ++j) ss += hr[j] * g[j] * (xv[j] * rstd_in);
+            }
           }
         }
       }
       ss = warp_sum(ss);
-      const float rstd = rsqrtf(ss / N + args.norm_eps);
-      if (lane == 0 && args.norm_rstd != nullptr) args.norm_rstd[lrow] = rstd;
-      // ---- pass 2: normalise (this lane re-reads its own stores) and push into every gather buffer
+      const float rstd = BWD ? rstd_in : rsqrtf(ss / N + args.norm_eps);
+      const float c1 = ss / N;                                   // backward: mean(g * xh)
+      if (!BWD && lane == 0 && args.norm_rstd != nullptr) args.norm_rstd[lrow] = rstd;
+      // ---- pass 2: normalise / norm backward (this lane re-reads its own stores) and push into every gather buffer
       const size_t g_row = ((size_t)args.rank * args.rows_per_rank + lrow) * N * 2;
       for (int c0 = lane * 8; c0 < N; c0 += 256 * kCU) {
         uint4 y[kCU];
@@ -217,12 +245,22 @@ __device__ __noinline__ void rs_reduce_norm_push(const RsArgs& args, int warp, i
             float h[8], g[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) { h[j] = 0.f; g[j] = args.norm_w_offset; }
-            rs_acc8<BF16>(h, *reinterpret_cast<const uint4*>(out_row + (size_t)col * 2));
-            rs_acc8<BF16>(g, *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(args.norm_gamma) +
-                                                             (size_t)col * 2));
+            rs_acc8<BF16>(h, *reinterpret_cast<const uint4*>(red_row + (size_t)col * 2));
+            rs_acc8<BF16>(g, *reinterpret_cast<const uint4*>(gamma + (size_t)col * 2));
+            if (!BWD) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) h[j] = h[j] * rstd * g[j];
+              for (int j = 0; j < 8; ++j) h[j] = h[j] * rstd * g[j];
+            } else {
+              float xv[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) xv[j] = 0.f;
+              rs_acc8<BF16>(xv, *reinterpret_cast<const uint4*>(x_row + (size_t)col * 2));
+#pragma unroll
+              for (int j = 0; j < 8; ++j) h[j] = rstd * (h[j] * g[j] - xv[j] * rstd * c1);
+              if (res_row != nullptr) rs_acc8<BF16>(h, *reinterpret_cast<const uint4*>(res_row + (size_t)col * 2));
+            }
             y[i] = rs_pack8<BF16>(h);
+            if (BWD) *reinterpret_cast<uint4*>(out_row + (size_t)col * 2) = y[i];
           }
         }
         if (args.ag_mc != nullptr) {
@@ -246,6 +284,13 @@ __device__ __noinline__ void rs_reduce_norm_push(const RsArgs& args, int warp, i
     pending_rb = (args.rank * args.rows_per_rank + row0) >> 7;
   }
   if (pending_rb >= 0) publish(pending_rb);
+}
+
+template <bool BF16, bool BWD>
+__device__ __forceinline__ void rs_reduce_norm_dispatch(const RsArgs& args, int warp, int lane) {
+  // 16 loads per lane in flight whatever the group size: two source ranks x 8 stripes, or four x 4
+  if (args.world <= 2) rs_reduce_norm_push<BF16, 8, 2, BWD>(args, warp, lane);
+  else rs_reduce_norm_push<BF16, 4, 4, BWD>(args, warp, lane);
 }
 
 template <int B_MAJOR>
@@ -442,13 +487,12 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   // ---------------- reduce phase: every warp of the CTA sums arrived partials ----------------
   if (args.norm_gamma != nullptr) {
-    // 16 loads per lane in flight whatever the group size: two source ranks x 8 stripes, or four x 4
     if (args.in_fmt == 1) {
-      if (args.world <= 2) rs_reduce_norm_push<true, 8, 2>(args, warp, lane);
-      else rs_reduce_norm_push<true, 4, 4>(args, warp, lane);
+      if (args.norm_bwd) rs_reduce_norm_dispatch<true, true>(args, warp, lane);
+      else rs_reduce_norm_dispatch<true, false>(args, warp, lane);
     } else {
-      if (args.world <= 2) rs_reduce_norm_push<false, 8, 2>(args, warp, lane);
-      else rs_reduce_norm_push<false, 4, 4>(args, warp, lane);
+      if (args.norm_bwd) rs_reduce_norm_dispatch<false, true>(args, warp, lane);
+      else rs_reduce_norm_dispatch<false, false>(args, warp, lane);
     }
   } else {
     const int nwarps = kGemmThreads / 32;
@@ -691,4 +735,42 @@ ICB_API int icb_gemm_rs_norm_ag(const void* A, const void* B, void* out, const v
   f.ag_peer_ready = ag_peer_ready;
   return gemm_rs_impl(A, B, out, bias, residual, M, N, K, lda, ldb, ldo, ldr, b_major, in_dtype, peer_recv, peer_flags,
                       recv, flags, rank, world, epoch_ptr, status, stream_, mc_recv, &f);
+}
+
+// Backward of the same boundary: the column-parallel layer's input gradient is reduced, taken through the RMSNorm
+// backward and gathered for the row-parallel layer's backward, in the kernel that computes the partial products.
+//   dn[rows_per_rank, N]   = reduce_scatter_rows(A * B)                       (gradient of the normalised rows)
+//   out[rows_per_rank, N]  = rstd * (dn * g - xh * mean(dn * g * xh)) (+ residual),  xh = x * rstd, g = gamma + w_offset
+//   every rank's gather buffer receives `out` at this rank's rows (P2P stores / multimem.st) and the arrival
+//   counters are bumped, as in icb_gemm_rs_norm_ag. x / rstd: the norm's input rows and the statistics its forward
+//   wrote; residual: the gradient arriving over the residual path. dn is kept for the gain's gradient.
+ICB_API int icb_gemm_rs_norm_bwd_ag(const void* A, const void* B, void* out, const void* residual, int M, int N, int K,
+                                    long long lda, long long ldb, long long ldo, long long ldr, int b_major,
+                                    int in_dtype, const void* const* peer_recv, int* const* peer_flags,
+                                    const void* recv, const int* flags, int rank, int world, const int* epoch_ptr,
+                                    int* status, void* stream_, const void* mc_recv, const void* gamma, float w_offset,
+                                    const float* rstd, const void* x, long long ldx, void* dn, void* const* ag_peers,
+                                    void* ag_mc, int* const* ag_peer_ready) {
+  if (gamma == nullptr || ag_peers == nullptr || ag_peer_ready == nullptr || rstd == nullptr || x == nullptr ||
+      dn == nullptr)
+    return -2;
+  const long long row_bytes = (long long)N * 2;
+  RsArgs f{};
+  if (row_bytes >= 8192) {
+    if (row_bytes % 8192) return -8;
+    f.ag_rows_per_unit = 1;
+    f.ag_add_per_unit = (int)(row_bytes / 8192);
+  } else {
+    if (8192 % row_bytes) return -8;
+    f.ag_rows_per_unit = (int)(8192 / row_bytes);
+    f.ag_add_per_unit = 1;
+  }
+  f.norm_gamma = gamma; f.norm_eps = 0.f; f.norm_w_offset = w_offset;
+  f.norm_rstd = const_cast<float*>(rstd);
+  f.norm_bwd = 1; f.norm_x = x; f.norm_ldx = ldx; f.aux_out = dn;
+  f.ag_peers = reinterpret_cast<uint8_t* const*>(ag_peers);
+  f.ag_mc = reinterpret_cast<uint8_t*>(ag_mc);
+  f.ag_peer_ready = ag_peer_ready;
+  return gemm_rs_impl(A, B, out, nullptr, residual, M, N, K, lda, ldb, ldo, ldr, b_major, in_dtype, peer_recv,
+                      peer_flags, recv, flags, rank, world, epoch_ptr, status, stream_, mc_recv, &f);
 }

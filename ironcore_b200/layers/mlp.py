@@ -26,19 +26,19 @@ class MLP(nn.Module):
                                            device=device, tp_group=tp_group)
         self.dropout = dropout
 
-    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, pregathered: bool = False,
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, up_out: Optional[torch.Tensor] = None,
                 next_norm=None, next_consumer=None):
-        """``pregathered``: ``x`` already sits in ``up_proj``'s gather slot on every rank. ``next_norm`` /
-        ``next_consumer``: the norm and column-parallel linear that follow this block; when given (and
-        fusable) the down projection also normalises its output into the consumer's gather slot and the
-        result is ``(out, normed)`` instead of ``out``."""
-        h = self.activation(self.up_proj(x, pregathered=pregathered) if pregathered else self.up_proj(x))
+        """``up_out``: the up projection of ``x`` when the caller already computed it (fused norm boundary).
+        ``next_norm`` / ``next_consumer``: the norm and column-parallel linear that follow this block; when
+        given the result is ``(out, y_next)`` with ``y_next = next_consumer(next_norm(out))`` computed inside
+        the fused boundary kernels, or ``(out, None)`` when that is not possible."""
+        h = self.activation(self.up_proj(x) if up_out is None else up_out)
         if self.dropout > 0 and self.training:
             y = F.dropout(self.down_proj(h), self.dropout, True)
             y = y if residual is None else y + residual
             return (y, None) if next_norm is not None else y
         if next_norm is not None:
             if self.down_proj.can_fuse_norm(h, next_norm, next_consumer):
-                return self.down_proj.forward_norm(h, residual, next_norm, next_consumer)
+                return self.down_proj.forward_norm_linear(h, residual, next_norm, next_consumer)
             return self.down_proj(h, residual=residual), None
         return self.down_proj(h, residual=residual)

@@ -87,35 +87,32 @@ class TransformerLayer(nn.Module):
     def set_next_layer(self, layer):
         object.__setattr__(self, "_next_layer", layer)   # a plain reference, not a registered submodule
 
-    def _forward_fused(self, x, seq_len, pos_ids, cu_seqlens, attn_mask, prenormed):
-        """Pre-norm dense layer with both norm boundaries fused into the preceding row-parallel GEMM:
-        attention output -> (reduce-scatter + residual + post-attention norm + gather) -> MLP, and
-        MLP output -> (reduce-scatter + residual + next layer's input norm + gather) -> next layer."""
-        if prenormed is None:
-            n1, pushed = self.input_layernorm(x, out=self.linear_qkv.gather_target(x)), False
-        else:
-            n1, pushed = prenormed, True
-        qkv = self.linear_qkv(n1, pregathered=True) if pushed else self.linear_qkv(n1)
+    def _forward_fused(self, x, seq_len, pos_ids, cu_seqlens, attn_mask, qkv):
+        """Pre-norm dense layer with both norm boundaries fused into the GEMM kernels around them:
+        attention output -> (reduce-scatter + residual + post-attention norm + gather) -> MLP up projection, and
+        MLP down projection -> (reduce-scatter + residual + next layer's input norm + gather) -> next layer's
+        qkv projection, which this layer hands over."""
+        if qkv is None:
+            qkv = self.linear_qkv(self.input_layernorm(x, out=self.linear_qkv.gather_target(x)))
         ctx = self.attention(qkv, seq_len, pos_ids=pos_ids, cu_seqlens=cu_seqlens, attn_mask=attn_mask)
         up = self.mlp.up_proj
         if self.attn_output.can_fuse_norm(ctx, self.post_attn_layernorm, up):
-            h, n2 = self.attn_output.forward_norm(ctx, x, self.post_attn_layernorm, up)
-            pushed2 = True
+            h, up_out = self.attn_output.forward_norm_linear(ctx, x, self.post_attn_layernorm, up)
         else:
             h = self.attn_output(ctx, residual=x)
-            n2, pushed2 = self.post_attn_layernorm(h, out=up.gather_target(h)), False
+            up_out = up(self.post_attn_layernorm(h, out=up.gather_target(h)))
         nxt = self._next_layer
         if nxt is not None and nxt.fuse_norm_gather:
-            out, next_normed = self.mlp(n2, residual=h, pregathered=pushed2, next_norm=nxt.input_layernorm,
-                                        next_consumer=nxt.linear_qkv)
+            out, next_qkv = self.mlp(None, residual=h, up_out=up_out, next_norm=nxt.input_layernorm,
+                                     next_consumer=nxt.linear_qkv)
         else:
-            out, next_normed = self.mlp(n2, residual=h, pregathered=pushed2), None
-        return out, None, next_normed
+            out, next_qkv = self.mlp(None, residual=h, up_out=up_out), None
+        return out, None, next_qkv
 
     def forward(self, x: torch.Tensor, seq_len: int, pos_ids=None, cu_seqlens=None, attn_mask=None, prenormed=None):
-        """x: [T_local, d]. Returns (x, aux_loss or None, normed_for_next_layer or None). ``prenormed``:
-        this layer's input norm of ``x``, already delivered into ``linear_qkv``'s gather slot by the
-        previous layer."""
+        """x: [T_local, d]. Returns (x, aux_loss or None, qkv_for_next_layer or None). ``prenormed``:
+        this layer's qkv projection of its input norm of ``x``, computed by the previous layer inside its
+        fused output boundary."""
         if self.fuse_norm_gather and self.dropout_attn == 0:
             return self._forward_fused(x, seq_len, pos_ids, cu_seqlens, attn_mask, prenormed)
         aux = None

@@ -22,6 +22,9 @@ Forward and backward of the column- / row-parallel linears map onto these kernel
   row fwd + next norm : GEMM -> RS -> RMSNorm -> push into the next column call site's slot
                                                    (icb_gemm_rs_norm_ag; the consumer runs icb_ag_gemm with
                                                     the "pushed by the producers" flag and only waits)
+  column dgrad + norm bwd : GEMM(dy, W^T) -> RS -> RMSNorm backward (+ residual gradient) -> push into the scratch
+                                                   gather buffer of the row-parallel dgrad that follows
+                                                   (icb_gemm_rs_norm_bwd_ag; mirror of the forward boundary)
   row dgrad   : AG(dy) -> GEMM                     (icb_ag_gemm, a_major 0, scratch buffer)
   row wgrad   : x^T GEMM gathered(dy)              (plain GEMM on the scratch buffer the dgrad call filled)
 
@@ -49,6 +52,8 @@ native.register("icb_ag_gemm", [P, P, P, P, P, I, I, I, I, P, P, P, P, P, I, L, 
 native.register("icb_gemm_rs", [P, P, P, P, P, I, I, I, L, L, L, L, I, I, P, P, P, P, I, I, P, P, P, P])
 native.register("icb_gemm_rs_norm_ag", [P, P, P, P, P, I, I, I, L, L, L, L, I, I, P, P, P, P, I, I, P, P, P, P,
                                         P, F, F, P, P, P, P])
+native.register("icb_gemm_rs_norm_bwd_ag", [P, P, P, P, I, I, I, L, L, L, L, I, I, P, P, P, P, I, I, P, P, P, P,
+                                            P, F, P, P, L, P, P, P, P])
 
 
 class GatherSlot:
@@ -145,8 +150,6 @@ class FusedTP:
         if x_shard.shape != (self.rows, self.width) or x_shard.dtype != self.dtype:
             raise ValueError(f"fused gather expects a [{self.rows}, {self.width}] {self.dtype} shard")
         if slot is None:
-            if pushed:
-                raise ValueError("a producer-pushed gather needs a slot")
             self.g_epoch += 1
             par = self.g_epoch & 1
             gathered, peers, peer_ready, ready, epoch_dev = (self.g_views[par], self.g_peers[par], self.g_peer_ready,
@@ -206,7 +209,41 @@ class FusedTP:
         self.r_epoch_dev.add_(1)
         return out, rstd
 
+    def gemm_rs_norm_bwd(self, a: torch.Tensor, b: torch.Tensor, *, b_major: int, residual, gamma, w_offset: float,
+                         rstd: torch.Tensor, x: torch.Tensor):
+        """Backward of a ``gemm_rs(..., norm=...)`` boundary: ``dn = reduce_scatter_rows(a @ b)`` is the gradient
+        of the normalised rows; returns ``(dx, dn)`` with ``dx = rmsnorm_backward(dn; x, rstd, gamma) + residual``
+        and leaves every rank's ``dx`` rows in the scratch gather buffer that the NEXT scratch ``ag_gemm`` call
+        uses (call it with ``pushed=True``)."""
+        if a.shape[0] != self.tokens or a.dtype != self.dtype or not self.norm_fusable:
+            raise ValueError("fused reduce-scatter + norm backward: unsupported operand")
+        n, k = self.width, a.shape[1]
+        self.r_epoch += 1
+        par = self.r_epoch & 1
+        gpar = (self.g_epoch + 1) & 1          # parity of the scratch gather buffer the next ag_gemm call takes
+        out = torch.empty((self.rows, n), dtype=self.dtype, device=a.device)
+        dn = torch.empty((self.rows, n), dtype=self.dtype, device=a.device)
+        ldr = residual.stride(0) if residual is not None else 0
+        recv_ptr = self.rbuf.local.data_ptr() + self._r_off[par]
+        mc = (self.gbuf.multicast_ptr + self._g_off[gpar]) if self.nvls_ag else None
+        call("icb_gemm_rs_norm_bwd_ag", ptr(a), ptr(b), ptr(out), ptr(residual), self.tokens, n, k, a.stride(0),
+             b.stride(0), out.stride(0), ldr, int(b_major), dtype_code(self.dtype), ptr(self.r_peers[par]),
+             ptr(self.r_peer_flags), recv_ptr, ptr(self.r_flags), self.rank, self.world, ptr(self.r_epoch_dev),
+             ptr(native.status_tensor(a.device)), stream_ptr(),
+             (self.rbuf.multicast_ptr + self._r_off[par]) if self.nvls_rs else None, ptr(gamma), float(w_offset),
+             ptr(rstd), ptr(x), x.stride(0), ptr(dn), ptr(self.g_peers[gpar]), mc, ptr(self.g_peer_ready))
+        self.r_epoch_dev.add_(1)
+        return out, dn
+
     # ------------------------------------------------------------------ autograd entry points
+    def row_norm_column(self, x, w_row, b_row, residual, gamma, eps: float, w_offset: float, w_col, b_col,
+                        slot: GatherSlot):
+        """``h = reduce_scatter(x @ w_row) + b_row + residual`` ; ``y = all_gather(rmsnorm(h)) @ w_col + b_col``
+        as two kernels in forward (producer pushes, consumer only waits) and the mirrored pair in backward.
+        Returns ``(h, y)``."""
+        return _RowNormColumn.apply(x, w_row, b_row, residual, gamma, w_col, b_col, self, slot, float(eps),
+                                    float(w_offset))
+
     def allgather_linear(self, x_shard, weight, bias=None, slot: Optional[GatherSlot] = None, pushed: bool = False):
         return _AllGatherLinear.apply(x_shard, weight, bias, self, slot, pushed)
 
@@ -357,6 +394,68 @@ class _LinearRSNorm(torch.autograd.Function):
         dx, dw, db = _row_parallel_backward(ctx, x2, weight, dh, ctx.ws)
         dres = dh if ctx.has_res and ctx.needs_input_grad[3] else None
         return dx, dw, db, dres, dgamma, None, None, None, None
+
+
+class _RowNormColumn(torch.autograd.Function):
+    """A whole norm boundary of the sequence-parallel layer: row-parallel linear (+ residual) -> RMSNorm ->
+    column-parallel linear. Forward: ``icb_gemm_rs_norm_ag`` then ``icb_ag_gemm`` (pushed). Backward: the column
+    layer's weight gradient from the slot, ``icb_gemm_rs_norm_bwd_ag`` (column dgrad -> reduce-scatter -> norm
+    backward + residual gradient -> gather), the gain's gradient, then the row layer's ``icb_ag_gemm`` (pushed)
+    and weight gradient. The residual stream ``h`` passes through the node, so its gradient from later layers
+    is an input of the fused backward kernel."""
+
+    @staticmethod
+    def forward(ctx, x, w_row, b_row, residual, gamma, w_col, b_col, ws: FusedTP, slot, eps, w_offset):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        res2 = residual.reshape(-1, w_row.shape[1]).contiguous() if residual is not None else None
+        h, rstd = ws.gemm_rs(x2, w_row, b_major=1, bias=b_row, residual=res2, norm=(gamma, eps, w_offset, slot))
+        y = ws.ag_gemm(slot.local, w_col, a_major=0, b_major=1, n=w_col.shape[1], bias=b_col, slot=slot, pushed=True)
+        ctx.save_for_backward(x2, w_row, h, rstd, gamma, w_col)
+        ctx.ws, ctx.slot_gathered, ctx.w_offset = ws, slot.buf, w_offset
+        ctx.has_bias = b_row is not None          # name used by _row_parallel_backward
+        ctx.has_col_bias = b_col is not None
+        ctx.has_res = residual is not None
+        return h, y
+
+    @staticmethod
+    def backward(ctx, dh_later, dy):
+        x2, w_row, h, rstd, gamma, w_col = ctx.saved_tensors
+        ws: FusedTP = ctx.ws
+        dy = dy.contiguous()
+        # column-parallel weight gradient first: it reads the slot, which a peer may refill once it has
+        # received this rank's partial tiles of the reduce-scatter below
+        dw_col = None
+        if ctx.needs_input_grad[5]:
+            gathered = ctx.slot_gathered
+
+            def compute_col(acc):
+                if acc is not None:
+                    return kernels.mm_tn(gathered, dy, out=acc, residual=acc, out_dtype=acc.dtype)
+                return kernels.mm_tn(gathered, dy)
+
+            dw_col = _accumulate_or_return(w_col, compute_col)
+        db_col = dy.sum(0, dtype=torch.float32).to(dy.dtype) if ctx.has_col_bias and ctx.needs_input_grad[6] else None
+        dres_in = dh_later.contiguous() if dh_later is not None else None
+        dh, dn = ws.gemm_rs_norm_bwd(dy, w_col, b_major=0, residual=dres_in, gamma=gamma, w_offset=ctx.w_offset,
+                                     rstd=rstd, x=h)
+        dgamma = None
+        if ctx.needs_input_grad[4]:
+            _, dg, _ = kernels.norm_bwd(dn, h, gamma, None, rstd, True, False, w_offset=ctx.w_offset)
+            dgamma = dg.to(gamma.dtype)
+        # row-parallel backward on the rows the kernel above has already gathered on every rank
+        dx = ws.ag_gemm(dh, w_row, a_major=0, b_major=0, n=w_row.shape[0], pushed=True)
+        dh_full = ws.last_gathered
+        dw_row = None
+        if ctx.needs_input_grad[1]:
+            def compute_row(acc):
+                if acc is not None:
+                    return kernels.mm_tn(x2, dh_full, out=acc, residual=acc, out_dtype=acc.dtype)
+                return kernels.mm_tn(x2, dh_full)
+
+            dw_row = _accumulate_or_return(w_row, compute_row)
+        db_row = dh.sum(0, dtype=torch.float32).to(dh.dtype) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        dres = dh if ctx.has_res and ctx.needs_input_grad[3] else None
+        return dx, dw_row, db_row, dres, dgamma, dw_col, db_col, None, None, None, None
 
 
 def attach_fused_tp(model, config) -> Optional[FusedTP]:

@@ -130,7 +130,8 @@ class RowParallelLinear(nn.Module):
         return (ws is not None and self.sequence_parallel and getattr(consumer, "fused", None) is ws
                 and getattr(consumer, "gather_slot", None) is not None and ws.norm_fusable
                 and getattr(norm, "rms", False) and norm.layernorm.bias is None and OF.use_native(x)
-                and x.dim() == 2 and x.shape[0] == ws.tokens and self.input_is_parallel)
+                and x.dim() == 2 and x.shape[0] == ws.tokens and self.input_is_parallel
+                and not getattr(consumer, "gather_output", False))
 
     def forward_norm(self, x: torch.Tensor, residual: Optional[torch.Tensor], norm, consumer):
         """``h = self(x, residual)`` followed by ``norm(h)``, with the normalised rows delivered into the
@@ -139,6 +140,12 @@ class RowParallelLinear(nn.Module):
         ``consumer(normed, pregathered=True)``. Callers check ``can_fuse_norm`` first."""
         return self.fused.linear_reduce_scatter_norm(x, self.weight, self.bias, residual, norm.layernorm.weight,
                                                      norm.eps, norm.weight_offset, consumer.gather_slot)
+
+    def forward_norm_linear(self, x: torch.Tensor, residual: Optional[torch.Tensor], norm, consumer):
+        """``h = self(x, residual)``; ``y = consumer(norm(h))`` with the whole boundary fused in both
+        directions (see ``fused_comm._RowNormColumn``). Returns ``(h, y)``. Callers check ``can_fuse_norm``."""
+        return self.fused.row_norm_column(x, self.weight, self.bias, residual, norm.layernorm.weight, norm.eps,
+                                          norm.weight_offset, consumer.weight, consumer.bias, consumer.gather_slot)
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``residual`` (optional, already in the output layout) is added after the reduction."""

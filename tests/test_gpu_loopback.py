@@ -79,6 +79,42 @@ def check_rs_norm_autograd_one_rank(rank, world):
         assert (a - b).abs().max().item() < 0.05 * scale, (name, (a - b).abs().max().item(), scale)
 
 
+def check_row_norm_column_one_rank(rank, world):
+    """The whole fused boundary (forward pair and mirrored backward pair of kernels) against the unfused ops:
+    outputs and all six gradients, with the residual stream also feeding the loss directly."""
+    import torch.distributed as dist
+
+    from ironcore_b200.ops import functional as OF
+    from ironcore_b200.parallel.fused_comm import FusedTP
+
+    torch.manual_seed(13)
+    for tokens, d, k, n in ((256, 512, 256, 384), (256, 4096, 128, 256)):
+        ws = FusedTP(tokens, d, dist.group.WORLD, num_slots=1)
+        slot = ws.slots[0]
+        mk = lambda *s, sc=1.0: (torch.randn(*s, device="cuda") * sc).bfloat16().requires_grad_(True)
+        x, w, res, w2 = mk(tokens, k), mk(k, d, sc=k ** -0.5), mk(tokens, d), mk(d, n, sc=d ** -0.5)
+        gamma = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16().requires_grad_(True)
+        probe = torch.randn(tokens, d, device="cuda").bfloat16()
+        for step in range(2):      # twice: cumulative counters, receive-buffer and scratch parity
+            for t in (x, w, res, gamma, w2):
+                t.grad = None
+            h, y = ws.row_norm_column(x, w, None, res, gamma, 1e-5, 0.0, w2, None, slot)
+            (y.float().pow(2).mean() + (h.float() * probe.float()).mean()).backward()
+            got = [t.grad.float().clone() for t in (x, w, res, gamma, w2)]
+            for t in (x, w, res, gamma, w2):
+                t.grad = None
+            h2 = OF.linear(x, w, None, res)
+            n2, _ = OF.norm(h2, gamma, None, 1e-5, True)
+            y2 = OF.linear(n2, w2, None)
+            (y2.float().pow(2).mean() + (h2.float() * probe.float()).mean()).backward()
+            want = [t.grad.float() for t in (x, w, res, gamma, w2)]
+            assert (y.float() - y2.float()).abs().max().item() < 0.05
+            assert (h.float() - h2.float()).abs().max().item() < 0.05
+            for name, a, b in zip(("x", "w", "res", "gamma", "w2"), got, want):
+                scale = b.abs().max().item() + 1e-6
+                assert (a - b).abs().max().item() < 0.05 * scale, (step, name, (a - b).abs().max().item(), scale)
+
+
 def check_withheld_peer_flag_times_out(rank, world):
     """A gather over "two ranks" of which only this one exists: the arrival counters of the other rank's
     row blocks never move. With a limit of a few milliseconds the kernel gives up, reports
@@ -167,3 +203,7 @@ def test_rs_norm_autograd_one_rank():
 
 def test_withheld_peer_flag_times_out():
     spawn_gpu_ranks("test_gpu_loopback", "check_withheld_peer_flag_times_out", world=1)
+
+
+def test_row_norm_column_one_rank():
+    spawn_gpu_ranks("test_gpu_loopback", "check_row_norm_column_one_rank", world=1)

@@ -122,6 +122,26 @@ def check_raw_kernels(rank, world):
         dist.barrier()
         assert (slot.buf.float() - full_n.float()).abs().max().item() <= 2.0 ** -6 * full_n.float().abs().max().item()
         _close(y2, full_n.float() @ w.float(), d)
+        # the mirrored backward kernel: reduce-scatter -> RMSNorm backward (+ residual gradient) -> gather into
+        # the scratch buffer of the next (pushed) gather GEMM
+        from ironcore_b200.ops import kernels
+
+        xin = torch.randn(rows, d, device="cuda").bfloat16()
+        _, _, _, rstd_x = kernels.norm_fwd(xin, gamma, None, 1e-5, True)
+        dres = torch.randn(rows, d, device="cuda").bfloat16()
+        dx, dn = ws.gemm_rs_norm_bwd(a, b, b_major=1, residual=dres, gamma=gamma, w_offset=0.0, rstd=rstd_x, x=xin)
+        wt = torch.randn(n, d, device="cuda").bfloat16()
+        dist.broadcast(wt, 0)
+        y3 = ws.ag_gemm(dx, wt, a_major=0, b_major=0, n=n, pushed=True)
+        dn_ref = ref.bfloat16()
+        _close(dn, ref, 384 * world)
+        dx_ref, _, _ = kernels.norm_bwd(dn, xin, gamma, None, rstd_x, True, False, dres_in=dres)
+        assert (dx.float() - dx_ref.float()).abs().max().item() <= 2.0 ** -6 * max(1.0, dx_ref.float().abs().max().item())
+        full_dx = torch.empty(tokens, d, device="cuda", dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(full_dx, dx)
+        assert torch.equal(ws.last_gathered, full_dx)
+        _close(y3, full_dx.float() @ wt.float().t(), d)
+        del dn_ref
 
 
 def check_tp2_model_fused_matches_nccl(rank, world):
