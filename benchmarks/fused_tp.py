@@ -161,6 +161,47 @@ def main():
         wire = 2 * (world - 1) * rows * d * 2
         cases.append((name, "rs_norm_ag_chain", fused, nccl, gemm_only, flops, wire))
         cases.append((name + "_separate_kernels", "rs_norm_ag_chain", separate, nccl, gemm_only, flops, wire))
+    # the same boundaries in backward: column-parallel dgrad -> reduce-scatter -> RMSNorm backward (+ residual
+    # gradient) -> all-gather -> row-parallel dgrad
+    for name, n_col, k_row in (("gate_up_dgrad_normbwd_attn_out_dgrad", 2 * f // world, d // world),
+                               ("qkv_dgrad_normbwd_down_dgrad", 3 * d // world, f // world)):
+        n_col, k_row = (n_col + 7) // 8 * 8, (k_row + 7) // 8 * 8
+        dy = torch.randn(t, n_col, device="cuda").bfloat16()
+        w_col = (torch.randn(d, n_col, device="cuda") / (n_col * world) ** 0.5).bfloat16()   # [in = d, out]
+        w_row = torch.randn(k_row, d, device="cuda").bfloat16()                              # [in, out = d]
+        xin = torch.randn(rows, d, device="cuda").bfloat16()
+        gamma = torch.ones(d, device="cuda").bfloat16()
+        rstd = kernels.norm_fwd(xin, gamma, None, 1e-5, True)[3]
+        dres = torch.randn(rows, d, device="cuda").bfloat16()
+        out = torch.empty(rows, d, device="cuda", dtype=torch.bfloat16)
+        full = torch.empty(t, d, device="cuda", dtype=torch.bfloat16)
+
+        def fused(ws=ws, dy=dy, w_col=w_col, w_row=w_row, xin=xin, gamma=gamma, rstd=rstd, dres=dres, k_row=k_row):
+            dx, _dn = ws.gemm_rs_norm_bwd(dy, w_col, b_major=0, residual=dres, gamma=gamma, w_offset=0.0, rstd=rstd,
+                                          x=xin)
+            return ws.ag_gemm(dx, w_row, a_major=0, b_major=0, n=k_row, pushed=True)
+
+        def separate(ws=ws, dy=dy, w_col=w_col, w_row=w_row, xin=xin, gamma=gamma, rstd=rstd, dres=dres, k_row=k_row):
+            dn = ws.gemm_rs(dy, w_col, b_major=0)
+            dx = kernels.norm_bwd(dn, xin, gamma, None, rstd, True, False, dres_in=dres)[0]
+            return ws.ag_gemm(dx, w_row, a_major=0, b_major=0, n=k_row)
+
+        def nccl(dy=dy, w_col=w_col, w_row=w_row, xin=xin, gamma=gamma, rstd=rstd, dres=dres, out=out, full=full):
+            y = kernels.mm_nt(dy, w_col)
+            dist.reduce_scatter_tensor(out, y)
+            dx = kernels.norm_bwd(out, xin, gamma, None, rstd, True, False, dres_in=dres)[0]
+            dist.all_gather_into_tensor(full, dx)
+            return kernels.mm_nt(full, w_row)
+
+        def gemm_only(dy=dy, w_col=w_col, w_row=w_row, xin=xin, gamma=gamma, rstd=rstd, out=out, full=full):
+            kernels.mm_nt(dy, w_col)
+            kernels.norm_bwd(out, xin, gamma, None, rstd, True, False)
+            kernels.mm_nt(full, w_row)
+
+        flops = 2.0 * t * d * (n_col + k_row)
+        wire = 2 * (world - 1) * rows * d * 2
+        cases.append((name, "rs_normbwd_ag_chain", fused, nccl, gemm_only, flops, wire))
+        cases.append((name + "_separate_kernels", "rs_normbwd_ag_chain", separate, nccl, gemm_only, flops, wire))
     wanted = {c for c in args.cases.split(",") if c}
     for name, kind, fused, nccl, gemm_only, flops, wire in cases:
         if wanted and name not in wanted:

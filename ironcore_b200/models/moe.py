@@ -29,7 +29,7 @@ import torch.nn.functional as F
 from ..layers.activations import Activation
 from ..layers.mlp import MLP
 from ..ops import functional as OF
-from ..ops import kernels
+from ..ops import kernels, native
 from ..parallel import collectives as C
 from ..parallel import mesh
 
@@ -108,6 +108,52 @@ def padded_layout(expert_ids: torch.Tensor, num_experts: int, capacity_rows: int
     return dest, seg_offsets, tile_expert.to(torch.int32), counts
 
 
+native.register("icb_router_fwd", [native.P, native.I, native.I, native.I, native.I, native.P, native.P, native.P,
+                                   native.P, native.P, native.P])
+native.register("icb_router_bwd", [native.P, native.P, native.P, native.P, native.P, native.F, native.I, native.I,
+                                   native.I, native.I, native.P, native.P])
+
+
+class _Router(torch.autograd.Function):
+    """Router on the native kernels: logits from the tcgen05 GEMM (fp32 output), then one kernel for softmax,
+    top-k, the expert-load histogram and the mean routing probabilities; backward is one kernel plus the two
+    small GEMMs of the router weight. Returns (weights [T, k] fp32, expert ids [T, k] int64, aux loss)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, top_k: int, normalize: bool, aux_coeff: float):
+        t, e = x.shape[0], weight.shape[0]
+        logits = kernels.mm_nt(x, weight, out_dtype=torch.float32)
+        probs = torch.empty((t, e), dtype=torch.float32, device=x.device)
+        w = torch.empty((t, top_k), dtype=torch.float32, device=x.device)
+        idx = torch.empty((t, top_k), dtype=torch.int32, device=x.device)
+        counts = torch.zeros(e, dtype=torch.int32, device=x.device)
+        psum = torch.zeros(e, dtype=torch.float32, device=x.device)
+        native.call("icb_router_fwd", native.ptr(logits), t, e, int(top_k), 1 if normalize else 0, native.ptr(probs),
+                    native.ptr(w), native.ptr(idx), native.ptr(counts), native.ptr(psum), native.stream_ptr())
+        aux = (aux_coeff * e / (float(t) * top_k * t)) * (counts.float() * psum).sum()
+        ctx.save_for_backward(x, weight, probs, idx, counts)
+        ctx.cfg = (int(top_k), bool(normalize), float(aux_coeff))
+        idx64 = idx.long()
+        ctx.mark_non_differentiable(idx64)
+        return w, idx64, aux
+
+    @staticmethod
+    def backward(ctx, dw, _didx, daux):
+        x, weight, probs, idx, counts = ctx.saved_tensors
+        top_k, normalize, aux_coeff = ctx.cfg
+        t, e = probs.shape
+        dw = torch.zeros((t, top_k), dtype=torch.float32, device=x.device) if dw is None else dw.contiguous().float()
+        daux_t = daux.reshape(1).float().contiguous() if daux is not None else None
+        dlogits = torch.empty_like(probs)
+        native.call("icb_router_bwd", native.ptr(probs), native.ptr(dw), native.ptr(idx), native.ptr(counts),
+                    native.ptr(daux_t), aux_coeff * e / (float(t) * t * top_k), t, e, top_k, 1 if normalize else 0,
+                    native.ptr(dlogits), native.stream_ptr())
+        dl = dlogits.to(x.dtype)
+        dx = kernels.mm_nn(dl, weight) if ctx.needs_input_grad[0] else None       # [T, E] @ [E, d]
+        dwt = kernels.mm_tn(dl, x) if ctx.needs_input_grad[1] else None           # [T, E]^T @ [T, d]
+        return dx, dwt, None, None, None
+
+
 class MoEBlock(nn.Module):
     def __init__(self, config, dtype=None, device=None):
         super().__init__()
@@ -143,6 +189,10 @@ class MoEBlock(nn.Module):
 
     # ------------------------------------------------------------------ routing
     def route(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        e = self.num_experts
+        if OF.use_native(x) and x.dim() == 2 and e <= 256 and e % 8 == 0 and self.top_k <= 8 and x.shape[1] % 8 == 0 \
+                and self.router.weight.dtype == x.dtype:
+            return _Router.apply(x.contiguous(), self.router.weight, self.top_k, self.normalize, self.aux_coeff)
         logits = F.linear(x, self.router.weight).float()
         probs = torch.softmax(logits, dim=-1)
         w, idx = torch.topk(probs, self.top_k, dim=-1)

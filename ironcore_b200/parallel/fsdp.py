@@ -12,9 +12,13 @@ produced they are packed into a flat buffer and reduce-scattered (in fp32 for ``
 accumulates over micro-batches.
 
 Optimizer. Adam runs on the shard ranges (decay / no-decay split); the global gradient norm is
-the all-reduced sum of shard norms. With Muon, the reduced gradient shards of a unit are
-gathered once per step, the owner of each logical matrix runs Newton-Schulz, and the updates
-return through a reduce-scatter — momentum and orthogonalisation work are divided by ``dp``.
+the all-reduced sum of shard norms; with ``optim.cpu_offload_optimizer`` the Adam moments live in
+pinned host memory and stream through the device on a side stream while the Muon matrices are
+updated. With Muon every logical matrix has an owner rank: each rank sends the pieces of its
+gradient shard to the owners of the matrices they belong to (one all-to-all of 4 bytes per local
+Muon parameter), the owner runs Newton-Schulz on the assembled matrix and returns the update pieces
+in the parameter dtype to the shard holders (a second all-to-all of 2 bytes per parameter) —
+momentum, orthogonalisation work and wire bytes are all divided by ``dp``.
 Strategies: ``full`` (default), ``hybrid`` (same as full inside one node) and ``no_shard``
 (parameters stay whole; gradients are all-reduced).
 (The reference's FSDP branch — ironcore/parallel/parallel.py:82-115 — never shards anything;
@@ -48,7 +52,7 @@ def _grank(g):
 
 class FSDPUnit:
     def __init__(self, name: str, named_params, group, weight_decay: float, no_decay_on_embedding: bool,
-                 use_muon: bool, reduce_dtype, shard: bool, offload: bool):
+                 use_muon: bool, reduce_dtype, shard: bool, offload: bool, offload_state: bool = False):
         self.name = name
         self.group = group
         self.dp, self.rank = _gsize(group), _grank(group)
@@ -99,8 +103,14 @@ class FSDPUnit:
         self.materialised = True
         self.grad_shard = torch.zeros(self.shard_size if self.shard_params else self.total, dtype=torch.float32,
                                       device=self.device)
-        self.exp_avg = torch.zeros_like(self.grad_shard)
-        self.exp_avg_sq = torch.zeros_like(self.grad_shard)
+        # Adam moments: on the device, or (``optim.cpu_offload_optimizer``) in pinned host memory
+        self.offload_state = bool(offload_state) and self.device.type == "cuda"
+        if self.offload_state:
+            self.exp_avg = torch.zeros(self.grad_shard.shape, dtype=torch.float32).pin_memory()
+            self.exp_avg_sq = torch.zeros(self.grad_shard.shape, dtype=torch.float32).pin_memory()
+        else:
+            self.exp_avg = torch.zeros_like(self.grad_shard)
+            self.exp_avg_sq = torch.zeros_like(self.grad_shard)
         self._flat_grad: Optional[torch.Tensor] = None
         self._pending = 0
         self.gather_event = None
@@ -238,7 +248,8 @@ class FullyShardedModel(nn.Module):
             for pn, prm in mod.named_parameters(recurse=False):
                 root_named.append((f"{mn}.{pn}" if mn else pn, mod, pn, prm))
         mk = lambda name, named: FSDPUnit(name, named, self.group, o.weight_decay, o.no_decay_on_embedding,
-                                          self.use_muon, reduce_dtype, shard, p.fsdp_offload_params)
+                                          self.use_muon, reduce_dtype, shard, p.fsdp_offload_params,
+                                          bool(o.cpu_offload_optimizer))
         self.root_unit = mk("root", root_named)
         self.units.append(self.root_unit)
         for i, (name, layer) in enumerate(unit_modules):
@@ -365,6 +376,9 @@ class FSDPOptimizer:
         if self.use_muon:
             self.param_groups.append(muon_param_group(o))
         self.muon_momentum: Dict[str, torch.Tensor] = {}
+        self._side_stream = None
+        self._side_pending = False
+        self._muon_plans: Dict[str, dict] = {}
         self._norm = None
         self._owners: Dict[str, int] = {}
         if self.use_muon:
@@ -461,7 +475,9 @@ class FSDPOptimizer:
                     continue
                 sl = slice(a2 - lo, b2_ - lo)
                 kw = dict(lr=lr, beta1=b1, beta2=b2, eps=self.eps, weight_decay=wd, step=self.step_count)
-                if pshard.is_cuda:
+                if pshard.is_cuda and u.offload_state:
+                    self._adam_offloaded(pshard[sl], u.grad_shard[sl], u.exp_avg[sl], u.exp_avg_sq[sl], coef, dp, kw)
+                elif pshard.is_cuda:
                     kernels.adam_step_(pshard[sl], u.grad_shard[sl], u.exp_avg[sl], u.exp_avg_sq[sl], grad_scale=1.0 / dp,
                                        grad_scale_dev=coef, **kw)
                 else:
@@ -469,61 +485,148 @@ class FSDPOptimizer:
                                           grad_scale=float(coef) / dp, **kw)
             if self.use_muon and u.bounds[3] > u.bounds[2]:
                 self._muon_unit(u, pshard, lo, hi, coef, dp, newton_schulz)
+            if self._side_pending:
+                # the offloaded Adam ranges of this unit ran on the side stream, overlapping its Muon matrices
+                torch.cuda.current_stream().wait_stream(self._side_stream)
+                self._side_pending = False
             if u.shard_params:
                 u.write_back_shard(pshard)
         return norm
 
-    def _muon_unit(self, u: FSDPUnit, pshard, lo, hi, coef, dp, newton_schulz):
-        o = self.config.optim
-        lr = self.param_groups[1]["lr"]
-        # 1. every rank needs the full reduced gradient of the matrices it owns
-        if u.shard_params:
-            gfull = torch.empty(u.total, dtype=torch.float32, device=u.device)
-            if u.device.type == "cpu":
-                parts = [torch.empty_like(u.grad_shard) for _ in range(u.dp)]
-                dist.all_gather(parts, u.grad_shard, group=u.group)
-                gfull.copy_(torch.cat(parts))
-            else:
-                dist.all_gather_into_tensor(gfull, u.grad_shard, group=u.group)
-        else:
-            gfull = u.grad_shard
-        upd = torch.zeros(u.total, dtype=torch.float32, device=u.device)
+    def _adam_offloaded(self, p, g, hm, hv, coef, dp, kw, chunk: int = 1 << 24):
+        """Adam on a parameter range whose moments live in pinned host memory: the moments stream through the
+        device in chunks on a side stream (H2D, update, D2H); ``step`` joins the stream after the unit's Muon
+        matrices, which are disjoint parameters updated on the main stream meanwhile."""
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream()
+        side = self._side_stream
+        side.wait_stream(torch.cuda.current_stream())
+        n = p.numel()
+        with torch.cuda.stream(side):
+            for c0 in range(0, n, chunk):
+                c1 = min(n, c0 + chunk)
+                dm = hm[c0:c1].to(p.device, non_blocking=True)
+                dv = hv[c0:c1].to(p.device, non_blocking=True)
+                kernels.adam_step_(p[c0:c1], g[c0:c1], dm, dv, grad_scale=1.0 / dp, grad_scale_dev=coef, **kw)
+                hm[c0:c1].copy_(dm, non_blocking=True)
+                hv[c0:c1].copy_(dv, non_blocking=True)
+        self._side_pending = True
+
+    def _muon_plan(self, u: FSDPUnit) -> dict:
+        """Static exchange plan of a unit. A logical matrix (one expert, one fused part) is a set of rows of the
+        flat buffer, each row a contiguous run of ``c1 - c0`` elements, cut wherever a shard boundary falls.
+        Elements are ordered by (owner, matrix, row, column), which both sides can compute, so nothing but the
+        payload is exchanged.
+          send[r]  : pieces of MY shard that belong to matrices owned by rank r      (gradient: me -> r)
+          recv[s]  : pieces of rank s's shard that belong to matrices I own          (gradient: s -> me)
+        The update travels the same pieces in the opposite direction."""
+        plan = self._muon_plans.get(u.name)
+        if plan is not None:
+            return plan
+        dpn, me, ss = u.dp, u.rank, u.shard_size
+        dev = u.device
+        send_parts = [[] for _ in range(dpn)]     # per owner: indices into my shard (matrix, row, column order)
+        recv_parts = [[] for _ in range(dpn)]     # per source: positions in my packed matrices, same order
+        mats, mat_base, total = [], [], 0
         for n, p, k, off in zip(u.names, u.params, u.kinds, u.offsets):
             if k != 2:
                 continue
-            g = gfull[off:off + p.numel()].view(p.shape)
-            d = upd[off:off + p.numel()].view(p.shape)
             for key, shape in self._logical_matrices(n, p):
-                if self._owners.get(key, 0) != u.rank and u.dp > 1 and u.shard_params:
-                    continue
+                owner = self._owners.get(key, 0)
                 _, e, c0, c1 = key
-                gm = (g[e] if e is not None else g)[:, c0:c1] * (coef / dp)
-                mom = self.muon_momentum.get(key)
-                if mom is None:
-                    mom = torch.zeros_like(gm)
-                    self.muon_momentum[key] = mom
-                mom.mul_(o.muon_momentum).add_(gm)
-                upd_dir = gm.add(mom, alpha=o.muon_momentum) if o.nesterov else mom
-                x = newton_schulz(upd_dir.contiguous(), o.muon_ns_steps).float()
-                fan_in, fan_out = shape
-                scale = math.sqrt(max(1.0, fan_out / fan_in))
-                (d[e] if e is not None else d)[:, c0:c1].copy_(x * (-lr * scale))
-        # 2. updates go back to the shard owners
-        if u.shard_params:
-            ushard = torch.empty(u.shard_size, dtype=torch.float32, device=u.device)
-            if u.device.type == "cpu":
-                dist.all_reduce(upd, group=u.group)
-                ushard.copy_(upd[lo:hi])
-            else:
-                dist.reduce_scatter_tensor(ushard, upd, group=u.group)
-        else:
-            ushard = upd
-        a, b = max(u.bounds[2], lo), min(u.bounds[3], hi)
+                rows, cols, width = p.shape[-2], p.shape[-1], c1 - c0
+                base = off + (e * rows * cols if e is not None else 0) + c0
+                flat = (base + torch.arange(rows, device=dev, dtype=torch.long)[:, None] * cols
+                        + torch.arange(width, device=dev, dtype=torch.long)[None, :]).reshape(-1)
+                holder = torch.div(flat, ss, rounding_mode="floor")
+                send_parts[owner].append(flat[holder == me] - me * ss)
+                if owner == me:
+                    mats.append((key, shape, rows * width))
+                    mat_base.append(total)
+                    pos = torch.arange(rows * width, device=dev, dtype=torch.long) + total
+                    for s_ in range(dpn):
+                        recv_parts[s_].append(pos[holder == s_])
+                    total += rows * width
+        # 32-bit positions: the cached plans of a 13B model hold one index per Muon parameter of the shard, twice
+        empty = torch.zeros(0, dtype=torch.int32, device=dev)
+        cat = lambda parts: torch.cat([t.to(torch.int32) for t in parts]) if parts else empty
+        per_owner = [cat(send_parts[r]) for r in range(dpn)]
+        per_source = [cat(recv_parts[s_]) for s_ in range(dpn)]
+        send_index, recv_index = cat(per_owner), cat(per_source)
+        # gathers only (index_select takes 32-bit indices, the scatter forms do not): the inverse permutation
+        # unpacks the receive buffer into the matrices, and a map over the shard's Muon range (padding -> a
+        # trailing zero) applies the returned update
+        recv_inverse = torch.argsort(recv_index.long()).to(torch.int32) if recv_index.numel() else empty
+        a_, b_ = max(u.bounds[2], me * ss), min(u.bounds[3], (me + 1) * ss)
+        span = max(0, b_ - a_)
+        apply_map = torch.full((span,), send_index.numel(), dtype=torch.int32, device=dev)
+        if send_index.numel():
+            apply_map[(send_index.long() - (a_ - me * ss))] = torch.arange(send_index.numel(), device=dev, dtype=torch.int32)
+        plan = {
+            "recv_inverse": recv_inverse, "apply_map": apply_map, "apply_range": (a_ - me * ss, b_ - me * ss),
+            "mats": mats, "mat_base": mat_base, "owned_numel": total,
+            "send_splits": [int(t.numel()) for t in per_owner],
+            "recv_splits": [int(t.numel()) for t in per_source],
+            "send_index": send_index,          # gather from my gradient shard -> send buffer (owner-major)
+            "recv_index": recv_index,          # packed matrices I own -> return buffer (source-major)
+        }
+        self._muon_plans[u.name] = plan
+        return plan
+
+    def _muon_unit(self, u: FSDPUnit, pshard, lo, hi, coef, dp, newton_schulz):
+        from . import collectives as C
+
+        o = self.config.optim
+        lr = self.param_groups[1]["lr"]
+        sharded = u.shard_params and u.dp > 1
+        if not sharded:
+            # whole gradients are local: orthogonalise every matrix in place
+            for n, p, k, off in zip(u.names, u.params, u.kinds, u.offsets):
+                if k != 2:
+                    continue
+                g = u.grad_shard[off:off + p.numel()].view(p.shape)
+                w = pshard[off:off + p.numel()].view(p.shape)
+                for key, shape in self._logical_matrices(n, p):
+                    _, e, c0, c1 = key
+                    gm = (g[e] if e is not None else g)[:, c0:c1] * (coef / dp)
+                    x = self._muon_direction(key, gm, o, newton_schulz)
+                    scale = math.sqrt(max(1.0, shape[1] / shape[0]))
+                    wm = (w[e] if e is not None else w)[:, c0:c1]
+                    if o.muon_weight_decay:
+                        wm.mul_(1 - lr * o.muon_weight_decay)
+                    wm.add_((x * (-lr * scale)).to(wm.dtype))
+            return
+        plan = self._muon_plan(u)
+        # 1. gradient pieces travel to the owners of their matrices (fp32, 4 bytes per local Muon parameter)
+        send = u.grad_shard.index_select(0, plan["send_index"])
+        got = C.all_to_all_single(send, plan["recv_splits"], plan["send_splits"], u.group)
+        packed = got.index_select(0, plan["recv_inverse"])
+        # 2. the owner orthogonalises its matrices
+        upd = torch.empty(plan["owned_numel"], dtype=pshard.dtype, device=u.device)
+        for (key, shape, numel), base in zip(plan["mats"], plan["mat_base"]):
+            gm = packed[base:base + numel].view(shape) * (coef / dp)
+            x = self._muon_direction(key, gm, o, newton_schulz)
+            scale = math.sqrt(max(1.0, shape[1] / shape[0]))
+            upd[base:base + numel].copy_((x * (-lr * scale)).reshape(-1))
+        # 3. update pieces return to the shard holders in the parameter dtype (2 bytes per parameter)
+        back = C.all_to_all_single(upd.index_select(0, plan["recv_index"]), plan["send_splits"], plan["recv_splits"],
+                                   u.group)
+        a, b = plan["apply_range"]
         if b > a:
-            sl = slice(a - lo, b - lo)
             if o.muon_weight_decay:
-                pshard[sl].mul_(1 - lr * o.muon_weight_decay)
-            pshard[sl].add_(ushard[sl].to(pshard.dtype))
+                pshard[a:b].mul_(1 - lr * o.muon_weight_decay)
+            padded = torch.cat([back.to(pshard.dtype), torch.zeros(1, dtype=pshard.dtype, device=u.device)])
+            pshard[a:b].add_(padded.index_select(0, plan["apply_map"]))
+
+    def _muon_direction(self, key, gm, o, newton_schulz):
+        """Momentum update and Newton-Schulz orthogonalisation of one matrix gradient (fp32 in, fp32 out)."""
+        mom = self.muon_momentum.get(key)
+        if mom is None:
+            mom = torch.zeros_like(gm)
+            self.muon_momentum[key] = mom
+        mom.mul_(o.muon_momentum).add_(gm)
+        direction = gm.add(mom, alpha=o.muon_momentum) if o.nesterov else mom
+        return newton_schulz(direction.contiguous(), o.muon_ns_steps).float()
 
     # ---- checkpoint state (sharded: each rank saves its own moments) ----
     def _full_moment(self, u: FSDPUnit, t: torch.Tensor) -> torch.Tensor:

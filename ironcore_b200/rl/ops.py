@@ -11,7 +11,18 @@ from ..ops.native import call, dtype_code, ptr, stream_ptr
 
 P, I, L, F = native.P, native.I, native.L, native.F
 native.register("icb_kv_append", [P, P, P, P, P, I, I, L, L, P])
-native.register("icb_paged_decode", [P, L, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P])
+native.register("icb_paged_decode", [P, L, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P, I])
+_SMS = None
+
+
+def _decode_splits(num_seqs: int, hkv: int, max_tokens: int) -> int:
+    """Context ranges per (sequence, kv head) for the tensor-core decode kernel: enough CTAs for two per SM,
+    at least four 16-token steps per range."""
+    global _SMS
+    if _SMS is None:
+        _SMS = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    want = -(-2 * _SMS // max(1, num_seqs * hkv))
+    return max(1, min(want, 8, max(1, max_tokens // 64)))
 native.register("icb_grpo_loss", [P, P, P, P, P, P, P, P, P, L, F, F, P])
 
 
@@ -58,9 +69,14 @@ def paged_decode(q: torch.Tensor, k_cache, v_cache, block_table, seq_lens, hq: i
     s = q.shape[0]
     if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and hd in (64, 128) and hq // hkv <= 8:
         out = torch.empty((s, hq * hd), dtype=q.dtype, device=q.device)
+        scratch, nsplit = None, 0
+        if hd == 128 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
+            # tensor-core kernel (mma.sync over the GQA group), the context split over several CTAs
+            nsplit = _decode_splits(s, hkv, block_table.shape[1] * k_cache.shape[1])
+            scratch = torch.empty(max(1, s * hq * nsplit * (hd + 2)), dtype=torch.float32, device=q.device)
         call("icb_paged_decode", ptr(q), q.stride(0), ptr(k_cache), ptr(v_cache), ptr(block_table), ptr(seq_lens),
              ptr(out), None, s, hq, hkv, hd, k_cache.shape[1], block_table.shape[1], float(scale),
-             dtype_code(q.dtype), stream_ptr())
+             dtype_code(q.dtype), stream_ptr(), ptr(scratch), int(nsplit))
         return out
     return paged_decode_reference(q, k_cache, v_cache, block_table, seq_lens, hq, hkv, hd, scale)
 

@@ -128,3 +128,41 @@ def test_cuda_graph_micro_batch_matches_eager():
     assert b is not None
     for x, y in zip(a, b):
         assert abs(x - y) < 2e-2, (a, b)
+
+
+@pytest.mark.parametrize("experts,top_k,normalize", [(64, 6, False), (8, 2, True), (16, 1, False)])
+def test_router_kernel_matches_eager(experts, top_k, normalize):
+    """Router kernels (GEMM logits -> softmax / top-k / histogram / aux loss, and the backward) against the same
+    computation in fp32 PyTorch on the logits the kernel saw."""
+    from ironcore_b200.models.moe import _Router
+    from ironcore_b200.ops import kernels, native
+
+    torch.manual_seed(21)
+    t, d, coeff = 1000, 256, 0.01
+    x = torch.randn(t, d, device="cuda").bfloat16().requires_grad_(True)
+    wr = (torch.randn(experts, d, device="cuda") * 0.3).bfloat16().requires_grad_(True)
+    w, idx, aux = _Router.apply(x, wr, top_k, normalize, coeff)
+    gw = torch.randn_like(w)
+    ((w * gw).sum() + 3.0 * aux).backward()
+    torch.cuda.synchronize()
+    native.check_status()
+    # reference from the same fp32 logits
+    logits = kernels.mm_nt(x.detach(), wr.detach(), out_dtype=torch.float32).requires_grad_(True)
+    probs = torch.softmax(logits, -1)
+    rw, ridx = torch.topk(probs, top_k, -1)
+    if normalize:
+        rw = rw / rw.sum(-1, keepdim=True)
+    f = torch.bincount(ridx.reshape(-1), minlength=experts).float() / (t * top_k)
+    raux = coeff * experts * (f * probs.mean(0)).sum()
+    assert torch.equal(idx.sort(-1).values, ridx.sort(-1).values)
+    order = idx.argsort(-1)
+    rorder = ridx.argsort(-1)
+    assert torch.allclose(w.gather(-1, order), rw.gather(-1, rorder), atol=1e-6, rtol=1e-5)
+    assert torch.allclose(aux, raux, rtol=1e-4, atol=1e-8)
+    rgw = torch.zeros_like(rw).scatter(-1, rorder, gw.gather(-1, order))   # same upstream gradient per expert
+    ((rw * rgw).sum() + 3.0 * raux).backward()
+    dl = logits.grad
+    dx_ref = dl @ wr.detach().float()
+    dw_ref = dl.t() @ x.detach().float()
+    assert (x.grad.float() - dx_ref).abs().max().item() < 2e-2 * max(1.0, dx_ref.abs().max().item())
+    assert (wr.grad.float() - dw_ref).abs().max().item() < 2e-2 * max(1.0, dw_ref.abs().max().item())

@@ -20,7 +20,7 @@ def _worlds():
     """Rank counts to run the raw-kernel checks at: 2, and 4 / 8 when the box has them (the NVSwitch
     multicast forms are the default from 4 ranks up)."""
     n = torch.cuda.device_count()
-    return [w for w in (2, 4, 8) if w <= n]
+    return sorted({2, max(w for w in (2, 4, 8) if w <= n)})
 
 
 def _worker(rank, world, port, fn_name, out_q):
