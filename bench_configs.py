@@ -1,6 +1,6 @@
 """Throughput of the other named workloads (the flagship Llama-7B TP benchmark is ``bench.py``).
 
-    python bench_configs.py --workload moe|fsdp_muon|grpo|gpt2 [--gpus N --steps K --warmup W --layers L]
+    python bench_configs.py --workload moe|fsdp_muon|grpo|gpt2|llama7b [--gpus N --steps K --warmup W --layers L]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         bench_configs.py --workload moe --gpus N
 
@@ -8,8 +8,10 @@ Each workload loads its preset from ``configs/`` and adapts only what depends on
 (expert-parallel size = min(8, N); FSDP over N ranks; GRPO TP2 x DP(N/2), TP1 on one GPU); the global
 batch stays the preset's unless ``--global-batch`` is given. ``--layers``
 runs a shallower model of the same layer shape when the full depth does not fit the GPUs given, and
-is reported in the JSON line. Synthetic uniform tokens, random-init weights, device timing with CUDA
-events (max over ranks), one JSON line on rank 0.
+is reported in the JSON line. ``llama7b --tp T`` is the headline model on a TP x DP mesh (T-way tensor +
+sequence parallel inside each replica, data parallel with ZeRO-1 optimizer-state sharding across replicas:
+e.g. TP2 x DP4 on 8 GPUs), next to ``bench.py``'s TP = N layout. Synthetic uniform tokens, random-init
+weights, device timing with CUDA events (max over ranks), one JSON line on rank 0.
 """
 
 from __future__ import annotations
@@ -21,13 +23,30 @@ import sys
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 PRESET = {"moe": "configs/baseline_moe_ep8.yaml", "fsdp_muon": "configs/baseline_llama13b_fsdp_muon.yaml",
-          "grpo": "configs/baseline_grpo_qwen.yaml", "gpt2": "configs/example.yaml"}
+          "grpo": "configs/baseline_grpo_qwen.yaml", "gpt2": "configs/example.yaml", "llama7b": None}
 
 
 def build_config(args, world: int):
     from ironcore_b200.config import apply_env_ranks, apply_yaml, default_config, validate_config
 
     os.chdir(ROOT)
+    if args.workload == "llama7b":
+        from bench import build_config as headline_config
+
+        tp = args.tp or world
+        if world % tp:
+            raise SystemExit(f"--tp {tp} does not divide {world} GPUs")
+        c = headline_config(tp, args.steps)
+        c.trainer(tensor_model_parallel_size=tp, cuda_graph=tp > 1)
+        c.parallel(world_size=world, sequence_parallel=tp > 1, zero_stage=1)
+        c.trainer.gradient_accumulation_steps = None
+        if args.layers:
+            c.model.num_layers = args.layers
+        if args.global_batch:
+            c.trainer.train_batch_size = args.global_batch
+        apply_env_ranks(c)
+        validate_config(c)
+        return c
     c = default_config()
     apply_yaml(c, PRESET[args.workload])
     c.trainer(log_interval=10 ** 9, model_path="")
@@ -74,6 +93,7 @@ def main(argv=None):
                     help="sequences per optimizer step (0 = the preset's: strong scaling over --gpus)")
     ap.add_argument("--prompts", type=int, default=0, help="GRPO: prompts per rollout batch (0 = preset scaled by GPUs)")
     ap.add_argument("--new-tokens", dest="new_tokens", type=int, default=0, help="GRPO: generated tokens per sample")
+    ap.add_argument("--tp", type=int, default=0, help="llama7b: tensor-parallel size (0 = all GPUs); the rest is DP")
     args = ap.parse_args(argv)
     import torch
     import torch.distributed as dist
@@ -143,7 +163,7 @@ def main(argv=None):
             "metric": metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "dtype": m.precision,
             "data": "synthetic", "impl": "ironcore_b200", "workload": args.workload,
-            "config": {"preset": PRESET[args.workload], "model": m.name, "layers": m.num_layers,
+            "config": {"preset": PRESET[args.workload] or "bench.py model", "model": m.name, "layers": m.num_layers,
                        "layers_overridden": bool(args.layers), "d_model": m.d_model,
                        "global_batch": cfg.trainer.train_batch_size, "micro_batch": cfg.trainer.micro_batch_size,
                        "seq_len": m.max_seq_len, "tp": cfg.trainer.tensor_model_parallel_size,

@@ -52,14 +52,16 @@ __device__ __forceinline__ void st8(uint16_t* p, const float (&f)[8]) {
 template <bool BF16>
 __global__ void rope_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, const int* __restrict__ pos_ids,
                             int T, int nheads, int hd, long long row_stride, long long out_stride, int seq_len,
-                            float base, float scale, int offset, int interleaved, int inverse) {
-  const int half = hd >> 1;
+                            float base, float scale, int offset, int interleaved, int inverse, int rot_dim) {
+  // partial rotary: only the first rot_dim elements of every head rotate (frequencies over rot_dim); the rest
+  // of the head is left as it is, so rot_dim < hd is an in-place operation (out == x)
+  const int half = rot_dim >> 1;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)T * half) return;
   const int t = (int)(idx / half);
   const int i = (int)(idx - (long long)t * half);
   const int pos = (pos_ids != nullptr) ? pos_ids[t] : (t % seq_len);
-  const float inv_freq = powf(base, -2.0f * (float)i / (float)hd);
+  const float inv_freq = powf(base, -2.0f * (float)i / (float)rot_dim);
   float s, c;
   sincosf((float)(pos + offset) * scale * inv_freq, &s, &c);
   if (inverse) s = -s;
@@ -440,18 +442,22 @@ using namespace icb;
 
 ICB_API int icb_rope(const void* x, void* out, const int* pos_ids, int T, int nheads, int hd, long long row_stride,
                      long long out_stride, int seq_len, float base, float scale, int offset, int interleaved,
-                     int inverse, int dtype, void* stream) {
+                     int inverse, int dtype, void* stream, int rot_dim) {
   if (T <= 0 || nheads <= 0) return 0;
-  if (hd % 2) return -2;
-  const long long n = (long long)T * (hd / 2);
+  if (rot_dim <= 0) rot_dim = hd;
+  if (hd % 2 || rot_dim % 2 || rot_dim > hd) return -2;
+  if (rot_dim < hd && x != out) return -3;       // partial rotary leaves the tail of each head in place
+  const long long n = (long long)T * (rot_dim / 2);
   const int th = 256;
   const int bl = (int)((n + th - 1) / th);
   if (dtype == kBF16)
     rope_kernel<true><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(x), ICB_U16M(out), pos_ids, T, nheads, hd, row_stride,
-                                                     out_stride, seq_len, base, scale, offset, interleaved, inverse);
+                                                     out_stride, seq_len, base, scale, offset, interleaved, inverse,
+                                                     rot_dim);
   else
     rope_kernel<false><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(x), ICB_U16M(out), pos_ids, T, nheads, hd, row_stride,
-                                                      out_stride, seq_len, base, scale, offset, interleaved, inverse);
+                                                      out_stride, seq_len, base, scale, offset, interleaved, inverse,
+                                                      rot_dim);
   return check_launch("rope");
 }
 

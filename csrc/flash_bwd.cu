@@ -36,6 +36,9 @@ struct FlashBwdArgs {
   int causal;
   int in_fmt;
   int* status;
+  const unsigned long long* drop_seed;  // the device word the forward pass was given
+  int drop_thr;
+  float drop_scale;
 };
 
 template <int HD>
@@ -218,6 +221,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int row = q * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
     const float log2e = 1.4426950408889634f;
+    const bool dropout = args.drop_thr > 0;
+    const unsigned long long drop_key = dropout ? *args.drop_seed : 0ull;
     for (int it = 0; it < n_iters; ++it) {
       const uint32_t ph = it & 1;
       const int head = kv_head * group + it / iters_per_head;
@@ -231,6 +236,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         dlt = args.delta[(size_t)head * args.total_tokens + tok];
       }
       const bool need_mask = (args.causal && it_q == jt) || (kv0 + 128 > seq_len);
+      const unsigned long long drop_row = dropout_row_counter(b, args.hq, head, args.seq_len, q_idx);
       mbar_wait(sdp_full, ph, abort_flag, args.status, kTimeoutTmemFull);
       tc_fence_after();
       uint8_t* prow = sP + row * 128;
@@ -244,6 +250,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           float p[8], ds[8];
+          // dropout: dV takes the masked, rescaled P; dP arrives as d(masked P) and is masked the same way
+          // before dS = P (dP - delta) scale, where delta = rowsum(dO O) already includes the mask
+          unsigned long long h = ~0ull;
+          if (dropout) h = dropout_hash(drop_key, drop_row + (unsigned)((kv0 + c * 32 + g * 8) >> 3));
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int col = c * 32 + g * 8 + i;
@@ -254,8 +264,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               if (kv_idx >= seq_len || (args.causal && kv_idx > q_idx)) keep = false;
             }
             pv = keep ? pv : 0.f;
-            p[i] = pv;
-            ds[i] = pv * (__uint_as_float(dr[g * 8 + i]) - dlt) * args.scale;
+            const float mr = (int)((h >> (8 * i)) & 0xffull) >= args.drop_thr ? args.drop_scale : 0.f;
+            p[i] = pv * mr;
+            ds[i] = pv * (__uint_as_float(dr[g * 8 + i]) * mr - dlt) * args.scale;
           }
           uint4 up, ud;
           if (args.in_fmt == 1) {
@@ -417,11 +428,13 @@ using namespace icb;
 
 // Scratch: delta fp32 [hq * T] and dq_acc fp32 [T * hq * hd] (zeroed here). dq/dk/dv point at the
 // first element of each gradient inside rows of dqkv_stride elements (packed layout or separate).
+// dropout_p / dropout_seed: the values the forward pass was given (the mask is recomputed, never stored).
 ICB_API int icb_flash_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out,
                           const float* lse, void* dq, void* dk, void* dv, float* delta, float* dq_acc, int batch,
                           int seq_len, long long total_tokens, int hq, int hkv, int hd, long long q_stride,
                           long long kv_stride, long long dq_stride, long long dkv_stride, const int* cu_seqlens,
-                          int causal, float scale, int dtype, int* status, void* stream_) {
+                          int causal, float scale, int dtype, int* status, void* stream_, float dropout_p,
+                          const unsigned long long* dropout_seed) {
   if (hd != 64 && hd != 128) return -2;
   if (hq % hkv != 0) return -3;
   if (batch <= 0 || seq_len <= 0) return 0;
@@ -465,6 +478,10 @@ ICB_API int icb_flash_bwd(const void* dout, const void* q, const void* k, const 
   a.causal = causal;
   a.in_fmt = bf16 ? 1 : 0;
   a.status = status;
+  a.drop_thr = icb_dropout_threshold(dropout_p);
+  if (a.drop_thr > 0 && dropout_seed == nullptr) return -4;
+  a.drop_seed = dropout_seed;
+  a.drop_scale = 256.0f / (256 - a.drop_thr);
   dim3 grid((seq_len + 127) / 128, hkv, batch);
   rc = (hd == 64) ? launch_flash_bwd<64>(tmQ, tmK, tmV, tmDO, a, grid, stream)
                   : launch_flash_bwd<128>(tmQ, tmK, tmV, tmDO, a, grid, stream);

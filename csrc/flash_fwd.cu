@@ -16,8 +16,6 @@
 // give every warp scheduler two softmax warps, which hides the latency of the row-wise exp / max / sum
 // chain that one warp per scheduler cannot.
 // Every wait is bounded; on timeout the status word is set and the CTA drains.
-#include <cstdlib>
-
 #include "host_common.h"
 #include "ptx.cuh"
 
@@ -35,6 +33,9 @@ struct FlashFwdArgs {
   int causal;
   int in_fmt;                         // 1 bf16, 0 fp16
   int* status;
+  const unsigned long long* drop_seed;  // device word; read when drop_thr > 0
+  int drop_thr;                       // keep a probability when its hash byte >= drop_thr (0: no dropout)
+  float drop_scale;                   // 256 / (256 - drop_thr)
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -224,6 +225,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int q_idx = q0 + row;  // position inside the sequence
     float m_ref = -INFINITY;     // reference max (log2 domain, scaled)
     float l_sum = 0.f;
+    const bool dropout = args.drop_thr > 0;
+    const unsigned long long drop_key = dropout ? *args.drop_seed : 0ull;
+    const unsigned long long drop_row = dropout_row_counter(b, args.hq, head, args.seq_len, q_idx);
     for (int j = 0; j < n_kv; ++j) {
       const int s = j & 1;
       const uint32_t ph = (j >> 1) & 1;
@@ -295,6 +299,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           for (int i = 0; i < 8; ++i) {
             p[i] = fast_exp2(__uint_as_float(r[c][g * 8 + i]) - m_ref);
             lsum_tile += p[i];
+          }
+          if (dropout) {
+            // the row sum keeps every probability (softmax first, dropout second); only P V sees the mask
+            const unsigned long long h = dropout_hash(drop_key, drop_row + (unsigned)((kv0 + c * 32 + g * 8) >> 3));
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              p[i] = (int)((h >> (8 * i)) & 0xffull) >= args.drop_thr ? p[i] * args.drop_scale : 0.f;
           }
           uint4 u;
           if (args.in_fmt == 1) {
@@ -390,16 +401,9 @@ int make_head_tmap(CUtensorMap* tm, const void* base, int hd, int heads, long lo
   return make_head_tmap_rows(tm, base, hd, heads, tokens, row_stride, dtype, 128);
 }
 
-// Key rows per step: 64 (two CTAs per SM, the default) or 128 (one CTA per SM). ICB_FLASH_BN overrides it.
-static int flash_fwd_bn() {
-  static int bn = 0;
-  if (bn == 0) {
-    const char* e = getenv("ICB_FLASH_BN");
-    const int v = e != nullptr ? atoi(e) : 0;
-    bn = (v == 64 || v == 128) ? v : 64;   // measured: 0.270 ms vs 0.452 ms at s=4096, 32 heads x 128
-  }
-  return bn;
-}
+// Key rows per step: 64 (two CTAs per SM; measured 0.270 ms against 0.452 ms for 128 rows with one CTA per SM
+// at s = 4096, 32 heads x 128). `wide` selects the 128-row tiling.
+static int flash_fwd_bn(int wide) { return wide ? 128 : 64; }
 
 }  // namespace icb
 
@@ -408,9 +412,12 @@ using namespace icb;
 // q/k/v: first element of each operand inside rows of `row_stride` elements (packed qkv or separate
 // tensors). out: [T, hq, hd] contiguous. lse: [hq, T] fp32. cu_seqlens (optional, device int32
 // [batch + 1]) gives document boundaries in the flat token stream; seq_len is then the maximum length.
+// dropout_p > 0 drops attention probabilities with probability round(256 p) / 256 under the mask that the
+// device word *dropout_seed selects (the backward pass must be given the same word).
 ICB_API int icb_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int seq_len,
                           long long total_tokens, int hq, int hkv, int hd, long long q_stride, long long kv_stride,
-                          const int* cu_seqlens, int causal, float scale, int dtype, int* status, void* stream_) {
+                          const int* cu_seqlens, int causal, float scale, int dtype, int* status, void* stream_,
+                          float dropout_p, const unsigned long long* dropout_seed, int wide) {
   if (hd != 64 && hd != 128) return -2;
   if (hq % hkv != 0) return -3;
   if (batch <= 0 || seq_len <= 0) return 0;
@@ -418,7 +425,7 @@ ICB_API int icb_flash_fwd(const void* q, const void* k, const void* v, void* out
   CUtensorMap tmQ, tmK, tmV;
   int rc = make_head_tmap(&tmQ, q, hd, hq, total_tokens, q_stride, dtype);
   if (rc) return rc;
-  const int bn = flash_fwd_bn();
+  const int bn = flash_fwd_bn(wide);
   rc = make_head_tmap_rows(&tmK, k, hd, hkv, total_tokens, kv_stride, dtype, bn);
   if (rc) return rc;
   rc = make_head_tmap_rows(&tmV, v, hd, hkv, total_tokens, kv_stride, dtype, bn);
@@ -431,6 +438,10 @@ ICB_API int icb_flash_fwd(const void* q, const void* k, const void* v, void* out
   a.causal = causal;
   a.in_fmt = (dtype == kBF16) ? 1 : 0;
   a.status = status;
+  a.drop_thr = icb_dropout_threshold(dropout_p);
+  if (a.drop_thr > 0 && dropout_seed == nullptr) return -4;
+  a.drop_seed = dropout_seed;
+  a.drop_scale = 256.0f / (256 - a.drop_thr);
   dim3 grid((seq_len + 127) / 128, hq, batch);
   if (bn == 64) {
     if (hd == 64) return launch_flash_fwd<64, 64>(tmQ, tmK, tmV, a, grid, stream);

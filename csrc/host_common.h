@@ -19,6 +19,12 @@ namespace icb {
 enum DType : int { kBF16 = 0, kF16 = 1, kF32 = 2 };
 
 inline int dtype_bytes(int dt) { return dt == kF32 ? 4 : 2; }
+// 8-bit threshold of the attention dropout mask: a probability is dropped when its hash byte is below it.
+inline int icb_dropout_threshold(float p) {
+  if (!(p > 0.f)) return 0;
+  int t = (int)(p * 256.0f + 0.5f);
+  return t < 1 ? 1 : (t > 255 ? 255 : t);
+}
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,

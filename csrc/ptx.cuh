@@ -445,4 +445,20 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Dropout of attention probabilities. One 64-bit hash (splitmix64 finaliser of key + counter) decides eight
+// neighbouring key columns of one query row: byte i of the hash keeps column i when it is >= the 8-bit
+// threshold, so the drop probability is threshold / 256 and kept values are scaled by 256 / (256 - threshold).
+// The counter is ((sequence * heads + head) * max_len + query) * ceil(max_len / 8) + key / 8, which forward and
+// backward kernels compute the same way whatever their tiling.
+__device__ __forceinline__ unsigned long long dropout_hash(unsigned long long key, unsigned long long counter) {
+  unsigned long long z = key + (counter + 1ull) * 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+__device__ __forceinline__ unsigned long long dropout_row_counter(int seq, int heads, int head, int max_len, int q_idx) {
+  return ((unsigned long long)((long long)seq * heads + head) * (unsigned long long)max_len + (unsigned long long)q_idx) *
+         (unsigned long long)((max_len + 7) >> 3);
+}
+
 }  // namespace icb

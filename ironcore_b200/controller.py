@@ -1,5 +1,13 @@
 """Cadence predicates of the training loop.
-``now``  : step > 0 and step % every == 0      ``next`` : (step + 1) % every == 0
+
+Steps are counted from 0, and every periodic action (log, checkpoint, evaluation, exit, norm logging) fires
+after the ``every``-th completed step: ``(step + 1) % every == 0``, i.e. at steps ``every - 1``,
+``2 * every - 1``, ... A checkpoint written at that moment is named for the 0-based step it completes and
+a run resumed from it continues at ``step + 1``. The reference uses this form for some actions and
+``step > 0 and step % every == 0`` for others (logging and saving one step later, never at step
+``every - 1``: ironcore/controller.py:43-70); here one rule serves all of them, so "every N steps" always
+means "N optimizer steps have finished since the last time". ``cadence_now`` is the reference's other
+predicate, kept for scripts that want its behaviour.
 (Behavioural reference: ironcore/controller.py:12-78.)"""
 
 from __future__ import annotations
@@ -18,8 +26,10 @@ class TrainingControl:
         self.profiling = config.utils.profile_torch or config.utils.profile_nsys
 
     @staticmethod
-    def _cadence_now(step: int, every) -> bool:
+    def cadence_now(step: int, every) -> bool:
         return bool(every) and step > 0 and step % every == 0
+
+    _cadence_now = cadence_now
 
     @staticmethod
     def _cadence_next(step: int, every) -> bool:

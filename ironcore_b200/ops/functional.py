@@ -325,34 +325,39 @@ class _RopeAttention(torch.autograd.Function):
     """RoPE (in place on the packed projection output) + causal flash attention."""
 
     @staticmethod
-    def forward(ctx, qkv, hq, hkv, hd, seq_len, rope, cu_seqlens, causal, scale):
+    def forward(ctx, qkv, hq, hkv, hd, seq_len, rope, cu_seqlens, causal, scale, rot_dim=None, dropout_p=0.0):
         from . import attention as attn
 
         t = qkv.shape[0]
+        rot_dim = hd if rot_dim is None else rot_dim
         if rope is not None:
             base, rscale, offset, interleaved, pos_ids = rope
             kernels.rope(qkv, qkv, nheads=hq + hkv, head_dim=hd, tokens=t, seq_len=seq_len, base=base, scale=rscale,
                          offset=offset, interleaved=interleaved, pos_ids=pos_ids, row_stride=qkv.stride(0),
-                         out_stride=qkv.stride(0))
-        out, lse = attn.flash_fwd(qkv, hq, hkv, hd, seq_len, cu_seqlens=cu_seqlens, causal=causal, scale=scale)
-        ctx.save_for_backward(qkv, out, lse, cu_seqlens if cu_seqlens is not None else lse)
-        ctx.meta = (hq, hkv, hd, seq_len, rope, cu_seqlens is not None, causal, scale)
+                         out_stride=qkv.stride(0), rot_dim=rot_dim)
+        seed = attn.next_dropout_seed(qkv.device) if dropout_p > 0 else None
+        out, lse = attn.flash_fwd(qkv, hq, hkv, hd, seq_len, cu_seqlens=cu_seqlens, causal=causal, scale=scale,
+                                  dropout_p=dropout_p, dropout_seed=seed)
+        ctx.save_for_backward(qkv, out, lse, cu_seqlens if cu_seqlens is not None else lse,
+                              seed if seed is not None else lse)
+        ctx.meta = (hq, hkv, hd, seq_len, rope, cu_seqlens is not None, causal, scale, rot_dim, dropout_p)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         from . import attention as attn
 
-        qkv, out, lse, cu = ctx.saved_tensors
-        hq, hkv, hd, seq_len, rope, has_cu, causal, scale = ctx.meta
+        qkv, out, lse, cu, seed = ctx.saved_tensors
+        hq, hkv, hd, seq_len, rope, has_cu, causal, scale, rot_dim, dropout_p = ctx.meta
         dqkv = attn.flash_bwd(dout.contiguous(), qkv, out, lse, hq, hkv, hd, seq_len,
-                              cu_seqlens=cu if has_cu else None, causal=causal, scale=scale)
+                              cu_seqlens=cu if has_cu else None, causal=causal, scale=scale, dropout_p=dropout_p,
+                              dropout_seed=seed if dropout_p > 0 else None)
         if rope is not None:
             base, rscale, offset, interleaved, pos_ids = rope
             kernels.rope(dqkv, dqkv, nheads=hq + hkv, head_dim=hd, tokens=dqkv.shape[0], seq_len=seq_len, base=base,
                          scale=rscale, offset=offset, interleaved=interleaved, inverse=True, pos_ids=pos_ids,
-                         row_stride=dqkv.stride(0), out_stride=dqkv.stride(0))
-        return dqkv, None, None, None, None, None, None, None, None
+                         row_stride=dqkv.stride(0), out_stride=dqkv.stride(0), rot_dim=rot_dim)
+        return dqkv, None, None, None, None, None, None, None, None, None, None
 
 
 def rope_attention(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int, seq_len: int,
@@ -363,20 +368,21 @@ def rope_attention(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int, head
     """Self attention on a packed projection ``qkv`` [T, (Hq + 2 Hkv) * hd] (T = batch * seq_len,
     batch-major). ``rope`` = (base, scale, offset, interleaved, pos_ids or None). Returns [T, Hq*hd].
 
-    ``fused`` selects the flash kernel (causal, optional document boundaries via cu_seqlens);
-    otherwise scores are materialised (supports an arbitrary boolean mask and dropout)."""
+    ``fused`` selects the flash kernel (causal or full, document boundaries via cu_seqlens, partial rotary and
+    attention dropout inside the kernel); scores are materialised only for an arbitrary boolean mask, for head
+    sizes other than 64 / 128, on CPU and in fp32."""
     t = qkv.shape[0]
     scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
     rot_dim = head_dim if rot_dim is None else rot_dim
-    native_ok = (use_native(qkv) and fused and head_dim in (64, 128) and rot_dim == head_dim
-                 and attn_mask is None and (dropout_p == 0.0 or not training))
+    native_ok = (use_native(qkv) and fused and head_dim in (64, 128) and rot_dim % 2 == 0 and 0 < rot_dim <= head_dim
+                 and attn_mask is None)
     if native_ok:
         from . import attention as attn
 
         if attn.available():
             q = qkv if qkv.is_contiguous() else qkv.contiguous()
             return _RopeAttention.apply(q, num_heads, num_kv_heads, head_dim, seq_len, rope, cu_seqlens, causal,
-                                        scale)
+                                        scale, rot_dim, float(dropout_p) if training else 0.0)
     if rope is not None:
         base, rscale, offset, interleaved, pos_ids = rope
         qkv = rope_reference_packed(qkv, num_heads, num_kv_heads, head_dim, seq_len, base, rscale, offset,

@@ -238,14 +238,15 @@ def norm_bwd(dy, x, weight, mean, rstd, rms: bool, has_bias: bool, dres_in=None,
 def rope(x: torch.Tensor, out: torch.Tensor, *, nheads: int, head_dim: int, tokens: int, seq_len: int,
          base: float, scale: float = 1.0, offset: int = 0, interleaved: bool = True, inverse: bool = False,
          pos_ids: Optional[torch.Tensor] = None, row_stride: Optional[int] = None,
-         out_stride: Optional[int] = None) -> torch.Tensor:
-    """Rotate ``nheads`` heads starting at x's data pointer in rows of pitch ``row_stride`` elements."""
+         out_stride: Optional[int] = None, rot_dim: Optional[int] = None) -> torch.Tensor:
+    """Rotate ``nheads`` heads starting at x's data pointer in rows of pitch ``row_stride`` elements.
+    ``rot_dim`` < ``head_dim`` (partial rotary, in place only) rotates the first ``rot_dim`` elements of each head."""
     rs = row_stride if row_stride is not None else nheads * head_dim
     os_ = out_stride if out_stride is not None else rs
     call(
         "icb_rope", ptr(x), ptr(out), ptr(pos_ids), int(tokens), int(nheads), int(head_dim), int(rs), int(os_),
         int(seq_len), float(base), float(scale), int(offset), 1 if interleaved else 0, 1 if inverse else 0,
-        dtype_code(x.dtype), stream_ptr(),
+        dtype_code(x.dtype), stream_ptr(), int(rot_dim or head_dim),
     )
     return out
 

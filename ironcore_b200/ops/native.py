@@ -29,7 +29,7 @@ _SIGNATURES = {
     "icb_norm_bwd_parts": [I],
     "icb_norm_fwd": [P, P, P, P, P, P, P, P, I, I, F, F, I, I, P],
     "icb_norm_bwd": [P, P, P, P, P, P, P, P, P, P, I, I, F, I, I, I, I, P],
-    "icb_rope": [P, P, P, I, I, I, L, L, I, F, F, I, I, I, I, P],
+    "icb_rope": [P, P, P, I, I, I, L, L, I, F, F, I, I, I, I, P, I],
     "icb_glu_fwd": [P, P, L, I, I, I, I, P],
     "icb_glu_bwd": [P, P, P, L, I, I, I, I, P],
     "icb_act_fwd": [P, P, L, I, I, P],

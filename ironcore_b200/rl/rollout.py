@@ -107,10 +107,10 @@ class RolloutEngine:
         rot = layer.rotary_pos_emb
         if rot is None:
             return qkv
-        if OF.use_native(qkv) and rot.rot_dim == self.hd:
+        if OF.use_native(qkv) and rot.rot_dim % 2 == 0:
             kernels.rope(qkv, qkv, nheads=self.hq + self.hkv, head_dim=self.hd, tokens=tokens, seq_len=seq_len,
                          base=rot.base, scale=rot.scaling_factor, offset=rot.offset, interleaved=rot.interleaved,
-                         pos_ids=pos_ids, row_stride=qkv.stride(0), out_stride=qkv.stride(0))
+                         pos_ids=pos_ids, row_stride=qkv.stride(0), out_stride=qkv.stride(0), rot_dim=rot.rot_dim)
             return qkv
         return OF.rope_reference_packed(qkv, self.hq, self.hkv, self.hd, seq_len, rot.base, rot.scaling_factor,
                                         rot.offset, rot.interleaved, rot.rot_dim, pos_ids)

@@ -87,3 +87,68 @@ def test_rope_attention_autograd_matches_reference():
     y1.backward(dy.to(BF))
     y2.backward(dy)
     assert _err(x1.grad, x2.grad) < 3e-2 * max(x2.grad.abs().max().item(), 1.0)
+
+
+@pytest.mark.parametrize("b,s,hq,hkv,hd,causal,p", [
+    (2, 256, 4, 2, 128, True, 0.1), (1, 200, 2, 2, 64, True, 0.25), (1, 384, 2, 1, 128, False, 0.1),
+])
+def test_flash_dropout_matches_masked_reference(b, s, hq, hkv, hd, causal, p):
+    """Dropout inside the kernels: forward and backward recompute the same hash mask; the oracle applies that
+    mask (built on the host from the published definition) to an fp32 softmax."""
+    from ironcore_b200.ops import attention, native
+
+    torch.manual_seed(5)
+    t = b * s
+    qkv = torch.randn(t, (hq + 2 * hkv) * hd, device="cuda").to(BF)
+    dout = torch.randn(t, hq * hd, device="cuda").to(BF)
+    seed = torch.tensor([0x1234_5678_9ABC], dtype=torch.int64, device="cuda")
+    out, lse = attention.flash_fwd(qkv, hq, hkv, hd, s, causal=causal, dropout_p=p, dropout_seed=seed)
+    out_nodrop, lse_nodrop = attention.flash_fwd(qkv, hq, hkv, hd, s, causal=causal)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert torch.equal(lse, lse_nodrop)                      # the row statistics ignore the mask
+    assert not torch.equal(out, out_nodrop)
+
+    thr = attention.dropout_threshold(p)
+    keep = attention.dropout_keep_mask(int(seed.item()), b, hq, s, p).cuda()
+    frac = keep.float().mean().item()
+    assert abs(frac - (1 - thr / 256)) < 0.01
+    leaf = qkv.float().requires_grad_(True)
+    x = leaf.view(b, s, hq + 2 * hkv, hd)
+    q, k, v = x[:, :, :hq].transpose(1, 2), x[:, :, hq:hq + hkv].transpose(1, 2), x[:, :, hq + hkv:].transpose(1, 2)
+    k, v = k.repeat_interleave(hq // hkv, dim=1), v.repeat_interleave(hq // hkv, dim=1)
+    scores = q @ k.transpose(-1, -2) * hd ** -0.5
+    if causal:
+        scores = scores.masked_fill(~torch.ones(s, s, dtype=torch.bool, device="cuda").tril(), float("-inf"))
+    probs = torch.softmax(scores, dim=-1) * keep * (256.0 / (256 - thr))
+    ref = (probs @ v).transpose(1, 2).reshape(t, hq * hd)
+    assert _err(out, ref) < 3e-2, f"fwd err {_err(out, ref)}"
+    ref.backward(dout.float())
+    dqkv = attention.flash_bwd(dout, qkv, out, lse, hq, hkv, hd, s, causal=causal, dropout_p=p, dropout_seed=seed)
+    torch.cuda.synchronize()
+    native.check_status()
+    g = leaf.grad
+    nq, nk = hq * hd, hkv * hd
+    scale = g.abs().max().item()
+    for name, lo, hi in (("dq", 0, nq), ("dk", nq, nq + nk), ("dv", nq + nk, nq + 2 * nk)):
+        e = _err(dqkv[:, lo:hi], g[:, lo:hi])
+        assert e < 3e-2 * max(scale, 1.0), f"{name} err {e} (grad scale {scale})"
+
+
+def test_rope_attention_dropout_uses_flash_and_advances_the_mask():
+    """The public op keeps dropout on the flash path in training (no score matrix), draws a new mask per call
+    and none in evaluation."""
+    from ironcore_b200.ops import functional as OF
+
+    torch.manual_seed(6)
+    s, hq, hkv, hd = 256, 4, 2, 128
+    qkv = torch.randn(s, (hq + 2 * hkv) * hd, device="cuda").to(BF).requires_grad_(True)
+    kw = dict(num_heads=hq, num_kv_heads=hkv, head_dim=hd, seq_len=s)
+    base = OF.rope_attention(qkv, dropout_p=0.2, training=False, **kw)
+    a = OF.rope_attention(qkv, dropout_p=0.2, training=True, **kw)
+    b2 = OF.rope_attention(qkv, dropout_p=0.2, training=True, **kw)
+    assert type(a.grad_fn).__name__.startswith("_RopeAttention")
+    assert torch.equal(base, OF.rope_attention(qkv, **kw))
+    assert not torch.equal(a, b2) and not torch.equal(a, base)
+    a.float().square().mean().backward()
+    assert torch.isfinite(qkv.grad).all() and qkv.grad.abs().max().item() > 0

@@ -75,6 +75,36 @@ def test_rope_roundtrip_and_reference(interleaved):
     _close(back, xf, 3e-2)
 
 
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_partial_rotary_in_place_and_attention(interleaved):
+    """Phi-style partial rotary: the first rot_dim elements of every head rotate (frequencies over rot_dim), the
+    rest stays; and the attention op keeps such models on the flash kernel."""
+    from ironcore_b200.ops import functional as OF
+    from ironcore_b200.ops import kernels, reference
+
+    torch.manual_seed(2)
+    b, s, h, hd, rot = 2, 64, 4, 64, 32
+    x = torch.randn(b * s, h, hd, device="cuda").to(BF)
+    ref = x.clone()
+    pos = torch.arange(s, device="cuda").repeat(b)
+    ref[..., :rot] = reference.rope_reference(x[..., :rot], pos, 10000.0, 1.0, 0, interleaved)
+    y = x.clone()
+    kernels.rope(y, y, nheads=h, head_dim=hd, tokens=b * s, seq_len=s, base=10000.0, interleaved=interleaved, rot_dim=rot)
+    _close(y, ref.float(), 2e-2)
+    assert torch.equal(y[..., rot:], x[..., rot:])
+    qkv = (0.5 * torch.randn(b * s, 3 * h * hd, device="cuda")).to(BF).requires_grad_(True)
+    rope = (10000.0, 1.0, 0, interleaved, None)
+    qf = qkv.detach().float().requires_grad_(True)
+    # the op rotates its input in place (it owns the projection output), so it is given a copy of the leaf
+    out = OF.rope_attention(qkv * 1.0, num_heads=h, num_kv_heads=h, head_dim=hd, seq_len=s, rope=rope, rot_dim=rot)
+    want = OF.rope_attention(qf, num_heads=h, num_kv_heads=h, head_dim=hd, seq_len=s, rope=rope, rot_dim=rot, fused=False)
+    _close(out, want, 3e-2)
+    g = torch.randn_like(out)
+    out.backward(g)
+    want.backward(g.float())
+    _close(qkv.grad, qf.grad, 6e-2)
+
+
 @pytest.mark.parametrize("name", ["swiglu", "geglu", "geglu_erf", "reglu", "glu"])
 def test_glu(name):
     from ironcore_b200.ops import kernels
