@@ -90,8 +90,8 @@ __device__ __forceinline__ float act_f(int kind, float x) {
       const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
       return 0.5f * x * (1.f + tanhf(u));
     }
-    case 3: return x / (1.f + __expf(-x));
-    default: return 1.f / (1.f + __expf(-x));
+    case 3: return __fdividef(x, 1.f + __expf(-x));
+    default: return __fdividef(1.f, 1.f + __expf(-x));
   }
 }
 __device__ __forceinline__ float act_df(int kind, float x) {
@@ -109,55 +109,107 @@ __device__ __forceinline__ float act_df(int kind, float x) {
       return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
     }
     case 3: {
-      const float sg = 1.f / (1.f + __expf(-x));
+      const float sg = __fdividef(1.f, 1.f + __expf(-x));
       return sg * (1.f + x * (1.f - sg));
     }
     default: {
-      const float sg = 1.f / (1.f + __expf(-x));
+      const float sg = __fdividef(1.f, 1.f + __expf(-x));
       return sg * (1.f - sg);
     }
   }
 }
 
-template <bool BF16>
-__global__ void glu_fwd_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, long long M, int F, int kind,
-                               int gate_is_act) {
+// KIND >= 0 fixes the activation at compile time (3 = silu: the SwiGLU of every Llama-style model); KIND = -1
+// reads it from the argument. Every thread owns two 8-element vectors half the problem apart and issues the
+// loads of both before it computes, which doubles the bytes each SM keeps in flight.
+template <bool BF16, int KIND>
+__global__ void __launch_bounds__(256) glu_fwd_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
+                                                      long long M, int F, int kind_arg, int gate_is_act,
+                                                      const int* __restrict__ row_limit) {
+  const int kind = KIND >= 0 ? KIND : kind_arg;
   const int vecs = F >> 3;
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= M * vecs) return;
-  const long long m = idx / vecs;
-  const int v = (int)(idx - m * vecs);
-  float f[8], g[8], o[8];
-  ld8<BF16>(x + (size_t)m * 2 * F + v * 8, f);
-  ld8<BF16>(x + (size_t)m * 2 * F + F + v * 8, g);
+  const long long total = M * vecs;
+  const long long half = (total + 1) >> 1;
+  const long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i0 >= half) return;
+  // rows from *row_limit on hold nothing (unused capacity of a padded expert layout): zeros are written for them
+  const long long live = row_limit != nullptr ? (long long)*row_limit : M;
+  const long long i1 = i0 + half;
+  const bool two = i1 < total;
+  const long long m0 = i0 / vecs, m1 = two ? i1 / vecs : m0;
+  const int v0 = (int)(i0 - m0 * vecs), v1 = two ? (int)(i1 - m1 * vecs) : v0;
+  const uint16_t* r0 = x + (size_t)m0 * 2 * F + v0 * 8;
+  const uint16_t* r1 = x + (size_t)m1 * 2 * F + v1 * 8;
+  float f0[8], g0[8], f1[8], g1[8], o[8];
+  const bool live0 = m0 < live, live1 = two && m1 < live;
+  if (live0) {
+    ld8<BF16>(r0, f0);
+    ld8<BF16>(r0 + F, g0);
+  }
+  if (live1) {
+    ld8<BF16>(r1, f1);
+    ld8<BF16>(r1 + F, g1);
+  }
 #pragma unroll
-  for (int j = 0; j < 8; ++j) o[j] = gate_is_act ? f[j] * act_f(kind, g[j]) : act_f(kind, f[j]) * g[j];
-  st8<BF16>(y + (size_t)m * F + v * 8, o);
+  for (int j = 0; j < 8; ++j)
+    o[j] = !live0 ? 0.f : (gate_is_act ? f0[j] * act_f(kind, g0[j]) : act_f(kind, f0[j]) * g0[j]);
+  st8<BF16>(y + (size_t)m0 * F + v0 * 8, o);
+  if (two) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      o[j] = !live1 ? 0.f : (gate_is_act ? f1[j] * act_f(kind, g1[j]) : act_f(kind, f1[j]) * g1[j]);
+    st8<BF16>(y + (size_t)m1 * F + v1 * 8, o);
+  }
 }
-template <bool BF16>
-__global__ void glu_bwd_kernel(const uint16_t* __restrict__ dy, const uint16_t* __restrict__ x,
-                               uint16_t* __restrict__ dx, long long M, int F, int kind, int gate_is_act) {
+template <bool BF16, int KIND>
+__global__ void __launch_bounds__(256) glu_bwd_kernel(const uint16_t* __restrict__ dy, const uint16_t* __restrict__ x,
+                                                      uint16_t* __restrict__ dx, long long M, int F, int kind_arg,
+                                                      int gate_is_act, const int* __restrict__ row_limit) {
+  const int kind = KIND >= 0 ? KIND : kind_arg;
+  const long long live = row_limit != nullptr ? (long long)*row_limit : M;
   const int vecs = F >> 3;
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= M * vecs) return;
-  const long long m = idx / vecs;
-  const int v = (int)(idx - m * vecs);
-  float f[8], g[8], d[8], df[8], dg[8];
-  ld8<BF16>(x + (size_t)m * 2 * F + v * 8, f);
-  ld8<BF16>(x + (size_t)m * 2 * F + F + v * 8, g);
-  ld8<BF16>(dy + (size_t)m * F + v * 8, d);
+  const long long total = M * vecs;
+  const long long half = (total + 1) >> 1;
+  const long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i0 >= half) return;
+  const long long i1 = i0 + half;
+  const int n = i1 < total ? 2 : 1;
+  long long mm[2];
+  int vv[2];
+  float f[2][8], g[2][8], d[2][8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    if (gate_is_act) {
-      df[j] = d[j] * act_f(kind, g[j]);
-      dg[j] = d[j] * f[j] * act_df(kind, g[j]);
-    } else {
-      df[j] = d[j] * g[j] * act_df(kind, f[j]);
-      dg[j] = d[j] * act_f(kind, f[j]);
+  for (int u = 0; u < 2; ++u) {
+    const long long idx = (u == 0 || n == 2) ? (u == 0 ? i0 : i1) : i0;
+    mm[u] = idx / vecs;
+    vv[u] = (int)(idx - mm[u] * vecs);
+    if (mm[u] < live) {
+      ld8<BF16>(x + (size_t)mm[u] * 2 * F + vv[u] * 8, f[u]);
+      ld8<BF16>(x + (size_t)mm[u] * 2 * F + F + vv[u] * 8, g[u]);
+      ld8<BF16>(dy + (size_t)mm[u] * F + vv[u] * 8, d[u]);
     }
   }
-  st8<BF16>(dx + (size_t)m * 2 * F + v * 8, df);
-  st8<BF16>(dx + (size_t)m * 2 * F + F + v * 8, dg);
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    if (u < n) {
+      float df[8], dg[8];
+      const bool dead = mm[u] >= live;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (dead) {
+          df[j] = 0.f;
+          dg[j] = 0.f;
+        } else if (gate_is_act) {
+          df[j] = d[u][j] * act_f(kind, g[u][j]);
+          dg[j] = d[u][j] * f[u][j] * act_df(kind, g[u][j]);
+        } else {
+          df[j] = d[u][j] * g[u][j] * act_df(kind, f[u][j]);
+          dg[j] = d[u][j] * act_f(kind, f[u][j]);
+        }
+      }
+      st8<BF16>(dx + (size_t)mm[u] * 2 * F + vv[u] * 8, df);
+      st8<BF16>(dx + (size_t)mm[u] * 2 * F + F + vv[u] * 8, dg);
+    }
+  }
 }
 template <bool BF16>
 __global__ void act_fwd_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, long long nvec, int kind) {
@@ -350,6 +402,75 @@ __global__ void adam_kernel(void* __restrict__ p_, const void* __restrict__ g_, 
   }
 }
 
+// Four elements per thread and step (16-byte loads of the fp32 streams, two steps in flight): the form that runs
+// whenever the four pointers are aligned for it; the element-wise kernel above takes the ragged tail.
+template <int T>
+__device__ __forceinline__ void adam_load4(const void* base, long long i4, float (&f)[4]) {
+  if (T == 2) {
+    const float4 t = reinterpret_cast<const float4*>(base)[i4];
+    f[0] = t.x; f[1] = t.y; f[2] = t.z; f[3] = t.w;
+  } else {
+    const uint2 u = reinterpret_cast<const uint2*>(base)[i4];
+    if (T == 0) {
+      const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
+      f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+    } else {
+      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+      f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+    }
+  }
+}
+template <int T>
+__device__ __forceinline__ void adam_store4(void* base, long long i4, const float (&f)[4]) {
+  if (T == 2) {
+    reinterpret_cast<float4*>(base)[i4] = make_float4(f[0], f[1], f[2], f[3]);
+  } else {
+    uint2 u;
+    if (T == 0) { u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]); }
+    else { u.x = pack_f16x2(f[0], f[1]); u.y = pack_f16x2(f[2], f[3]); }
+    reinterpret_cast<uint2*>(base)[i4] = u;
+  }
+}
+template <int PT, int GT>
+__global__ void __launch_bounds__(256)
+adam_vec4_kernel(void* __restrict__ p_, const void* __restrict__ g_, float* __restrict__ m, float* __restrict__ v,
+                 long long n4, float lr, float b1, float b2, float eps, float wd, float step_size, float gscale,
+                 const float* __restrict__ gscale_dev) {
+  const float gs = gscale * (gscale_dev != nullptr ? *gscale_dev : 1.f);
+  const float decay = 1.f - lr * wd;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += 2 * stride) {
+    const long long idx[2] = {i, i + stride};
+    const int cnt = idx[1] < n4 ? 2 : 1;
+    float g[2][4], p[2][4], mm[2][4], vv[2][4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (u < cnt) {
+        adam_load4<GT>(g_, idx[u], g[u]);
+        adam_load4<PT>(p_, idx[u], p[u]);
+        adam_load4<2>(m, idx[u], mm[u]);
+        adam_load4<2>(v, idx[u], vv[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (u < cnt) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float gj = g[u][j] * gs;
+          mm[u][j] = b1 * mm[u][j] + (1.f - b1) * gj;
+          vv[u][j] = b2 * vv[u][j] + (1.f - b2) * gj * gj;
+          p[u][j] = p[u][j] * decay - step_size * mm[u][j] / (sqrtf(vv[u][j]) + eps);
+        }
+        adam_store4<2>(m, idx[u], mm[u]);
+        adam_store4<2>(v, idx[u], vv[u]);
+        adam_store4<PT>(p_, idx[u], p[u]);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Sum of squares of a flat range: per-CTA partials in scratch, then one CTA
 // folds them (optionally adding to what `out` already holds).
@@ -461,28 +582,39 @@ ICB_API int icb_rope(const void* x, void* out, const int* pos_ids, int T, int nh
   return check_launch("rope");
 }
 
+// row_limit (optional, device int32): rows from *row_limit on are not read and get zeros.
 ICB_API int icb_glu_fwd(const void* x, void* y, long long M, int F, int kind, int gate_is_act, int dtype,
-                        void* stream) {
+                        void* stream, const int* row_limit) {
   if (M <= 0) return 0;
   if (F % 8) return -2;
-  const long long n = M * (F / 8);
+  const long long n = (M * (F / 8) + 1) / 2;
   const int th = 256;
   const int bl = (int)((n + th - 1) / th);
-  if (dtype == kBF16) glu_fwd_kernel<true><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(x), ICB_U16M(y), M, F, kind, gate_is_act);
-  else glu_fwd_kernel<false><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(x), ICB_U16M(y), M, F, kind, gate_is_act);
+  const bool silu = kind == 3 && !gate_is_act;
+  if (dtype == kBF16) {
+    if (silu) glu_fwd_kernel<true, 3><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(x), ICB_U16M(y), M, F, kind, 0, row_limit);
+    else glu_fwd_kernel<true, -1><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(x), ICB_U16M(y), M, F, kind, gate_is_act, row_limit);
+  } else {
+    if (silu) glu_fwd_kernel<false, 3><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(x), ICB_U16M(y), M, F, kind, 0, row_limit);
+    else glu_fwd_kernel<false, -1><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(x), ICB_U16M(y), M, F, kind, gate_is_act, row_limit);
+  }
   return check_launch("glu_fwd");
 }
 ICB_API int icb_glu_bwd(const void* dy, const void* x, void* dx, long long M, int F, int kind, int gate_is_act,
-                        int dtype, void* stream) {
+                        int dtype, void* stream, const int* row_limit) {
   if (M <= 0) return 0;
   if (F % 8) return -2;
-  const long long n = M * (F / 8);
+  const long long n = (M * (F / 8) + 1) / 2;
   const int th = 256;
   const int bl = (int)((n + th - 1) / th);
-  if (dtype == kBF16)
-    glu_bwd_kernel<true><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(dy), ICB_U16(x), ICB_U16M(dx), M, F, kind, gate_is_act);
-  else
-    glu_bwd_kernel<false><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(dy), ICB_U16(x), ICB_U16M(dx), M, F, kind, gate_is_act);
+  const bool silu = kind == 3 && !gate_is_act;
+  if (dtype == kBF16) {
+    if (silu) glu_bwd_kernel<true, 3><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(dy), ICB_U16(x), ICB_U16M(dx), M, F, kind, 0, row_limit);
+    else glu_bwd_kernel<true, -1><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(dy), ICB_U16(x), ICB_U16M(dx), M, F, kind, gate_is_act, row_limit);
+  } else {
+    if (silu) glu_bwd_kernel<false, 3><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(dy), ICB_U16(x), ICB_U16M(dx), M, F, kind, 0, row_limit);
+    else glu_bwd_kernel<false, -1><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(dy), ICB_U16(x), ICB_U16M(dx), M, F, kind, gate_is_act, row_limit);
+  }
   return check_launch("glu_bwd");
 }
 // out[M, N] (16-bit, pitch ldo) = acc[M, N] (fp32, contiguous) (+ residual[M, N], 16-bit, pitch ldr): the closing
@@ -584,11 +716,28 @@ ICB_API int icb_adam(void* p, const void* g, float* m, float* v, long long n, fl
                      void* stream) {
   if (n <= 0) return 0;
   const int th = 256;
-  long long blocks = (n + th - 1) / th;
   const long long cap = (long long)num_sms() * 16;
-  const int bl = (int)(blocks < cap ? blocks : cap);
-#define ICB_ADAM(PT, GT) \
-  adam_kernel<PT, GT><<<bl, th, 0, ICB_ST(stream)>>>(p, g, m, v, n, lr, b1, b2, eps, wd, step_size, gscale, gscale_dev)
+  const size_t psz = p_dtype == 2 ? 4 : 2, gsz = g_dtype == 2 ? 4 : 2;
+  const bool aligned = reinterpret_cast<uintptr_t>(p) % (4 * psz) == 0 && reinterpret_cast<uintptr_t>(g) % (4 * gsz) == 0 &&
+                       reinterpret_cast<uintptr_t>(m) % 16 == 0 && reinterpret_cast<uintptr_t>(v) % 16 == 0;
+  const long long n4 = aligned ? n / 4 : 0;        // vectors of four elements for the wide kernel
+  const long long done = n4 * 4;
+  const long long tail = n - done;
+  const long long vblocks = (n4 + 2 * th - 1) / (2 * th);
+  const int vbl = (int)(vblocks < cap ? vblocks : cap);
+  const long long tblocks = (tail + th - 1) / th;
+  const int bl = (int)(tblocks < cap ? tblocks : cap);
+  void* pt = reinterpret_cast<char*>(p) + done * psz;
+  const void* gt = reinterpret_cast<const char*>(g) + done * gsz;
+#define ICB_ADAM(PT, GT)                                                                                            \
+  do {                                                                                                              \
+    if (n4 > 0)                                                                                                     \
+      adam_vec4_kernel<PT, GT><<<vbl, th, 0, ICB_ST(stream)>>>(p, g, m, v, n4, lr, b1, b2, eps, wd, step_size,      \
+                                                               gscale, gscale_dev);                                 \
+    if (tail > 0)                                                                                                   \
+      adam_kernel<PT, GT><<<bl, th, 0, ICB_ST(stream)>>>(pt, gt, m + done, v + done, tail, lr, b1, b2, eps, wd,     \
+                                                         step_size, gscale, gscale_dev);                            \
+  } while (0)
   if (p_dtype == 0 && g_dtype == 0) ICB_ADAM(0, 0);
   else if (p_dtype == 0 && g_dtype == 2) ICB_ADAM(0, 2);
   else if (p_dtype == 1 && g_dtype == 1) ICB_ADAM(1, 1);

@@ -6,17 +6,20 @@
 // and dQ = dS K, which read the *same* shared-memory bytes through MN-major descriptors,
 // so nothing is transposed or copied. TMEM holds S, dP, dV and dK (4 x 128 columns for
 // head_dim 128); dQ reuses the S columns once the softmax warps have consumed S.
-// Warps 2-5 own one query row each: P = exp2(S*scale - lse), dS = P (dP - delta) scale,
+// Warps 2-9 are two groups of four; a thread owns one query row (TMEM lane) and its group one half of
+// the columns, so every warp scheduler has two softmax warps whose TMEM loads, exponentials and shared-memory
+// stores interleave: P = exp2(S*scale - lse), dS = P (dP - delta) scale,
 // written as bf16 into 128-byte-swizzled tiles; the same threads drain dQ with fp32 vector
 // atomics into a zeroed scratch (converted to 16-bit by a follow-up kernel) and, at the
-// end, dK / dV (TMEM lane == kv row). dK/dV need no atomics: the group's heads are
+// end, dK (first group) / dV (second group; TMEM lane == kv row). dK/dV need no atomics: the group's heads are
 // accumulated in place. Every wait is bounded (status word + drain on timeout).
 #include "host_common.h"
 #include "ptx.cuh"
 
 namespace icb {
 
-constexpr int kFbThreads = 192;
+constexpr int kFbThreads = 320;           // TMA warp, MMA warp, 2 x 4 softmax warps
+constexpr int kFbSoftmaxThreads = 256;
 constexpr int kFbTmemCols = 512;
 
 int make_head_tmap(CUtensorMap* tm, const void* base, int hd, int heads, long long tokens, long long row_stride,
@@ -118,9 +121,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(do_full, 1);
     mbar_init(do_empty, 1);
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 128);
+    mbar_init(pds_full, kFbSoftmaxThreads);
     mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 128);
+    mbar_init(dq_empty, kFbSoftmaxThreads);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmQ);
@@ -217,7 +220,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     __syncwarp();
   } else {
-    const int q = warp & 3;
+    const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;       // column half of this warp's group
     const int row = q * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
     const float log2e = 1.4426950408889634f;
@@ -242,7 +246,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       uint8_t* prow = sP + row * 128;
       uint8_t* dsrow = sDS + row * 128;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t sr[32], dr[32];
         tmem_ld_32x32(tm_s + lane_off + c * 32, sr);
         tmem_ld_32x32(tm_dp + lane_off + c * 32, dr);
@@ -294,7 +298,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_after();
       float* dqrow = args.dq_acc + ((size_t)tok * args.hq + head) * HD;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); ++c) {
         uint32_t o[32];
         tmem_ld_32x32(tm_s + lane_off + c * 32, o);
         tmem_ld_wait();
@@ -318,8 +322,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       uint8_t* dkrow = reinterpret_cast<uint8_t*>(args.dk) + ((size_t)tok * args.dkv_stride + (size_t)kv_head * HD) * 2;
       uint8_t* dvrow = reinterpret_cast<uint8_t*>(args.dv) + ((size_t)tok * args.dkv_stride + (size_t)kv_head * HD) * 2;
       tc_fence_after();
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
+      {
+        const int which = half;
         const uint32_t tm = which == 0 ? tm_dk : tm_dv;
         uint8_t* orow = which == 0 ? dkrow : dvrow;
 #pragma unroll 1

@@ -47,44 +47,93 @@ __device__ __forceinline__ float block_sum_128(float v, float* sh) {
   return sh[0] + sh[1] + sh[2] + sh[3];
 }
 
+template <bool BF16>
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t;
+    if (BF16) t = unpack_bf16x2(w[i]);
+    else t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 ldg16(const uint16_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
 // VPT = 16-byte vectors per thread; D == VPT*128*8 is not required: tail vectors are masked.
+// The loads of the CTA's next row are issued (as packed 16-byte registers) before the current row is reduced and
+// stored, so that every CTA has a row in flight while it sits in the block-wide reduction.
 template <bool BF16, int VPT, bool RMS>
-__global__ void __launch_bounds__(kNormThreads)
+__global__ void __launch_bounds__(kNormThreads, VPT <= 4 ? 4 : 2)
 norm_fwd_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ res, const uint16_t* __restrict__ w,
                 const uint16_t* __restrict__ b, uint16_t* __restrict__ y, uint16_t* __restrict__ h_out,
                 float* __restrict__ mean_out, float* __restrict__ rstd_out, int M, int D, float eps, float w_offset) {
   __shared__ float sh[4];
   const int nvec = D >> 3;
-  float wv[VPT][8], bv[VPT][8];
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  uint4 wraw[VPT], braw[VPT], nx[VPT], nr[VPT];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int vi = threadIdx.x + i * kNormThreads;
+    wraw[i] = braw[i] = nx[i] = nr[i] = zero4;
     if (vi < nvec) {
-      load8<BF16>(w + vi * 8, wv[i]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) wv[i][j] += w_offset;
-      if (b != nullptr) load8<BF16>(b + vi * 8, bv[i]);
+      wraw[i] = ldg16(w + vi * 8);
+      if (b != nullptr) braw[i] = ldg16(b + vi * 8);
     }
   }
-  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+  int row = blockIdx.x;
+  if (row < M) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = threadIdx.x + i * kNormThreads;
+      if (vi < nvec) {
+        nx[i] = ldg16(x + (size_t)row * D + vi * 8);
+        if (res != nullptr) nr[i] = ldg16(res + (size_t)row * D + vi * 8);
+      }
+    }
+  }
+  for (; row < M; row += gridDim.x) {
     const size_t base = (size_t)row * D;
     float xv[VPT][8];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      unpack8<BF16>(nx[i], xv[i]);
+      if (res != nullptr) {
+        float rv[8];
+        unpack8<BF16>(nr[i], rv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) xv[i][j] += rv[j];
+      }
+    }
+    const int next = row + gridDim.x;
+    if (next < M) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int vi = threadIdx.x + i * kNormThreads;
+        if (vi < nvec) {
+          nx[i] = ldg16(x + (size_t)next * D + vi * 8);
+          if (res != nullptr) nr[i] = ldg16(res + (size_t)next * D + vi * 8);
+        }
+      }
+    }
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int vi = threadIdx.x + i * kNormThreads;
       if (vi < nvec) {
-        load8<BF16>(x + base + vi * 8, xv[i]);
-        if (res != nullptr) {
-          float rv[8];
-          load8<BF16>(res + base + vi * 8, rv);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) xv[i][j] += rv[j];
-          if (h_out != nullptr) {
-            store8<BF16>(h_out + base + vi * 8, xv[i]);
-            // keep the statistics consistent with the rounded value that backward will re-read
-            load8<BF16>(h_out + base + vi * 8, xv[i]);
+        if (res != nullptr && h_out != nullptr) {
+          // keep the statistics consistent with the rounded value that backward will re-read
+          uint4 u;
+          if (BF16) {
+            u.x = pack_bf16x2(xv[i][0], xv[i][1]); u.y = pack_bf16x2(xv[i][2], xv[i][3]);
+            u.z = pack_bf16x2(xv[i][4], xv[i][5]); u.w = pack_bf16x2(xv[i][6], xv[i][7]);
+          } else {
+            u.x = pack_f16x2(xv[i][0], xv[i][1]); u.y = pack_f16x2(xv[i][2], xv[i][3]);
+            u.z = pack_f16x2(xv[i][4], xv[i][5]); u.w = pack_f16x2(xv[i][6], xv[i][7]);
           }
+          *reinterpret_cast<uint4*>(h_out + base + vi * 8) = u;
+          unpack8<BF16>(u, xv[i]);
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) s += RMS ? xv[i][j] * xv[i][j] : xv[i][j];
@@ -115,11 +164,13 @@ norm_fwd_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ res
     for (int i = 0; i < VPT; ++i) {
       const int vi = threadIdx.x + i * kNormThreads;
       if (vi < nvec) {
-        float o[8];
+        float o[8], wv[8], bv[8];
+        unpack8<BF16>(wraw[i], wv);
+        unpack8<BF16>(braw[i], bv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          o[j] = (xv[i][j] - mean) * rstd * wv[i][j];
-          if (b != nullptr) o[j] += bv[i][j];
+          o[j] = (xv[i][j] - mean) * rstd * (wv[j] + w_offset);
+          if (b != nullptr) o[j] += bv[j];
         }
         store8<BF16>(y + base + vi * 8, o);
       }
@@ -127,65 +178,112 @@ norm_fwd_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ res
   }
 }
 
-template <bool BF16, int VPT, bool RMS>
-__global__ void __launch_bounds__(kNormThreads)
+// DB: the bias gradient is wanted (LayerNorm with bias). The current row is kept packed and unpacked twice
+// (before and after the reduction), which leaves the registers for the prefetched next row.
+template <bool BF16, int VPT, bool RMS, bool DB>
+__global__ void __launch_bounds__(kNormThreads, VPT <= 4 ? 3 : 1)
 norm_bwd_kernel(const uint16_t* __restrict__ dy, const uint16_t* __restrict__ x, const uint16_t* __restrict__ w,
                 const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                 const uint16_t* __restrict__ dres_in, uint16_t* __restrict__ dx, float* __restrict__ dw_part,
                 float* __restrict__ db_part, int M, int D, float w_offset) {
   __shared__ float sh[4];
   const int nvec = D >> 3;
-  float wv[VPT][8], dwv[VPT][8], dbv[VPT][8];
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  uint4 wraw[VPT], ndy[VPT], nx[VPT];
+  float dwv[VPT][8], dbv[DB ? VPT : 1][8];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int vi = threadIdx.x + i * kNormThreads;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { dwv[i][j] = 0.f; dbv[i][j] = 0.f; wv[i][j] = 0.f; }
-    if (vi < nvec) {
-      load8<BF16>(w + vi * 8, wv[i]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) wv[i][j] += w_offset;
+    for (int j = 0; j < 8; ++j) {
+      dwv[i][j] = 0.f;
+      if (DB) dbv[i][j] = 0.f;
     }
+    wraw[i] = ndy[i] = nx[i] = zero4;
+    if (vi < nvec) wraw[i] = ldg16(w + vi * 8);
   }
-  for (int row = blockIdx.x; row < M; row += gridDim.x) {
-    const size_t base = (size_t)row * D;
-    const float mean = RMS ? 0.f : mean_in[row];
-    const float rstd = rstd_in[row];
-    float xh[VPT][8], g[VPT][8];
-    float s1 = 0.f, s2 = 0.f;
+  int row = blockIdx.x;
+  float n_mean = 0.f, n_rstd = 0.f;
+  if (row < M) {
+    n_mean = RMS ? 0.f : mean_in[row];
+    n_rstd = rstd_in[row];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int vi = threadIdx.x + i * kNormThreads;
       if (vi < nvec) {
-        float dyv[8];
-        load8<BF16>(dy + base + vi * 8, dyv);
-        load8<BF16>(x + base + vi * 8, xh[i]);
+        ndy[i] = ldg16(dy + (size_t)row * D + vi * 8);
+        nx[i] = ldg16(x + (size_t)row * D + vi * 8);
+      }
+    }
+  }
+  for (; row < M; row += gridDim.x) {
+    const size_t base = (size_t)row * D;
+    const float mean = n_mean, rstd = n_rstd;
+    uint4 cdy[VPT], cx[VPT], cres[VPT];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          xh[i][j] = (xh[i][j] - mean) * rstd;
-          g[i][j] = dyv[j] * wv[i][j];
-          s1 += g[i][j] * xh[i][j];
-          if (!RMS) s2 += g[i][j];
-          dwv[i][j] += dyv[j] * xh[i][j];
-          dbv[i][j] += dyv[j];
+    for (int i = 0; i < VPT; ++i) {
+      cdy[i] = ndy[i]; cx[i] = nx[i]; cres[i] = zero4;
+      // the weights stay packed: unpacking them once outside the row loop would cost 8 registers per vector
+      asm volatile("" : "+r"(wraw[i].x), "+r"(wraw[i].y), "+r"(wraw[i].z), "+r"(wraw[i].w));
+    }
+    const int next = row + gridDim.x;
+    if (next < M) {
+      n_mean = RMS ? 0.f : mean_in[next];
+      n_rstd = rstd_in[next];
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int vi = threadIdx.x + i * kNormThreads;
+        if (vi < nvec) {
+          ndy[i] = ldg16(dy + (size_t)next * D + vi * 8);
+          nx[i] = ldg16(x + (size_t)next * D + vi * 8);
         }
+      }
+    }
+    if (dres_in != nullptr) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int vi = threadIdx.x + i * kNormThreads;
+        if (vi < nvec) cres[i] = ldg16(dres_in + base + vi * 8);
+      }
+    }
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      float dyv[8], xh[8], wv[8];
+      unpack8<BF16>(cdy[i], dyv);
+      unpack8<BF16>(cx[i], xh);
+      unpack8<BF16>(wraw[i], wv);
+      const bool live = threadIdx.x + i * kNormThreads < nvec;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xn = live ? (xh[j] - mean) * rstd : 0.f;
+        const float g = dyv[j] * (wv[j] + w_offset);
+        s1 += g * xn;
+        if (!RMS) s2 += g;
+        dwv[i][j] += dyv[j] * xn;
+        if (DB) dbv[i][j] += dyv[j];
       }
     }
     const float c1 = block_sum_128(s1, sh) / D;
     const float c2 = RMS ? 0.f : block_sum_128(s2, sh) / D;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
+      // opaque to the compiler, so that the unpacked floats of the first phase are not kept across the reduction
+      asm volatile("" : "+r"(cdy[i].x), "+r"(cdy[i].y), "+r"(cdy[i].z), "+r"(cdy[i].w));
+      asm volatile("" : "+r"(cx[i].x), "+r"(cx[i].y), "+r"(cx[i].z), "+r"(cx[i].w));
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
       const int vi = threadIdx.x + i * kNormThreads;
       if (vi < nvec) {
-        float o[8];
+        float dyv[8], xh[8], wv[8], a[8], o[8];
+        unpack8<BF16>(cdy[i], dyv);
+        unpack8<BF16>(cx[i], xh);
+        unpack8<BF16>(wraw[i], wv);
+        unpack8<BF16>(cres[i], a);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - c2 - xh[i][j] * c1);
-        if (dres_in != nullptr) {
-          float a[8];
-          load8<BF16>(dres_in + base + vi * 8, a);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += a[j];
-        }
+        for (int j = 0; j < 8; ++j)
+          o[j] = rstd * (dyv[j] * (wv[j] + w_offset) - c2 - (xh[j] - mean) * rstd * c1) + a[j];
         store8<BF16>(dx + base + vi * 8, o);
       }
     }
@@ -197,7 +295,7 @@ norm_bwd_kernel(const uint16_t* __restrict__ dy, const uint16_t* __restrict__ x,
       float* p = dw_part + (size_t)blockIdx.x * D + vi * 8;
       *reinterpret_cast<float4*>(p) = make_float4(dwv[i][0], dwv[i][1], dwv[i][2], dwv[i][3]);
       *reinterpret_cast<float4*>(p + 4) = make_float4(dwv[i][4], dwv[i][5], dwv[i][6], dwv[i][7]);
-      if (db_part != nullptr) {
+      if (DB) {
         float* q = db_part + (size_t)blockIdx.x * D + vi * 8;
         *reinterpret_cast<float4*>(q) = make_float4(dbv[i][0], dbv[i][1], dbv[i][2], dbv[i][3]);
         *reinterpret_cast<float4*>(q + 4) = make_float4(dbv[i][4], dbv[i][5], dbv[i][6], dbv[i][7]);
@@ -264,8 +362,15 @@ template <bool BF16, bool RMS>
 static int norm_bwd_dispatch(int vpt, int grid, cudaStream_t st, const uint16_t* dy, const uint16_t* x,
                              const uint16_t* w, const float* mean, const float* rstd, const uint16_t* dres,
                              uint16_t* dx, float* dwp, float* dbp, int M, int D, float woff) {
-#define ICB_NB(V) \
-  norm_bwd_kernel<BF16, V, RMS><<<grid, kNormThreads, 0, st>>>(dy, x, w, mean, rstd, dres, dx, dwp, dbp, M, D, woff)
+#define ICB_NB(V)                                                                                                   \
+  do {                                                                                                              \
+    if (dbp != nullptr)                                                                                             \
+      norm_bwd_kernel<BF16, V, RMS, true><<<grid, kNormThreads, 0, st>>>(dy, x, w, mean, rstd, dres, dx, dwp, dbp,  \
+                                                                         M, D, woff);                               \
+    else                                                                                                            \
+      norm_bwd_kernel<BF16, V, RMS, false><<<grid, kNormThreads, 0, st>>>(dy, x, w, mean, rstd, dres, dx, dwp, dbp, \
+                                                                          M, D, woff);                              \
+  } while (0)
   switch (vpt) {
     case 1: ICB_NB(1); break;
     case 2: ICB_NB(2); break;

@@ -29,8 +29,8 @@ class Activation(nn.Module):
         self.name = canonical_activation(name)
         self.gated = OF.is_gated(self.name)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return OF.activation(x, self.name)
+    def forward(self, x: torch.Tensor, row_limit=None) -> torch.Tensor:
+        return OF.activation(x, self.name, row_limit)
 
     def extra_repr(self):
         return self.name

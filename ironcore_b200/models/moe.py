@@ -213,22 +213,15 @@ class MoEBlock(nn.Module):
         xp = torch.zeros((cap, xs.shape[1]), dtype=xs.dtype, device=xs.device)
         xp = xp.index_copy(0, dest, xs)
         h = grouped_linear(xp, self.experts_up, tile_expert, seg_offsets)
-        if OF.use_native(h):
-            # rows of unused tiles are never written by the grouped GEMM: define them for the activation
-            used = seg_offsets[-1].to(torch.long)
-            row = torch.arange(cap, device=h.device)
-            h = torch.where((row < used)[:, None], h, torch.zeros((), dtype=h.dtype, device=h.device))
-        h = self.activation(h)
+        # rows of unused tiles are never written by the grouped GEMM: the activation is told where they start
+        h = self.activation(h, seg_offsets[-1:] if OF.use_native(h) else None)
         yp = grouped_linear(h, self.experts_down, tile_expert, seg_offsets)
         return yp.index_select(0, dest)
 
     def _experts_on_layout(self, xp, seg_offsets, tile_expert):
         """Expert MLPs on rows that already sit in the padded, expert-sorted layout."""
         h = grouped_linear(xp, self.experts_up, tile_expert, seg_offsets)
-        used = seg_offsets[-1].to(torch.long)
-        row = torch.arange(xp.shape[0], device=h.device)
-        h = torch.where((row < used)[:, None], h, torch.zeros((), dtype=h.dtype, device=h.device))
-        h = self.activation(h)
+        h = self.activation(h, seg_offsets[-1:])
         return grouped_linear(h, self.experts_down, tile_expert, seg_offsets)
 
     def _fused_workspace(self, x):

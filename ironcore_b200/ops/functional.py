@@ -135,15 +135,16 @@ def norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], ep
 # --------------------------------------------------------------------------- activations
 class _Glu(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, name):
-        ctx.save_for_backward(x)
+    def forward(ctx, x, name, row_limit=None):
+        ctx.save_for_backward(x, row_limit if row_limit is not None else x)
         ctx.name = name
-        return kernels.glu_fwd(x, name)
+        ctx.limited = row_limit is not None
+        return kernels.glu_fwd(x, name, row_limit)
 
     @staticmethod
     def backward(ctx, dy):
-        (x,) = ctx.saved_tensors
-        return kernels.glu_bwd(dy.contiguous(), x, ctx.name), None
+        x, limit = ctx.saved_tensors
+        return kernels.glu_bwd(dy.contiguous(), x, ctx.name, limit if ctx.limited else None), None, None
 
 
 class _Act(torch.autograd.Function):
@@ -163,12 +164,25 @@ def is_gated(name: str) -> bool:
     return name in GLU_KINDS
 
 
-def activation(x: torch.Tensor, name: str) -> torch.Tensor:
-    """Plain (relu/gelu/gelu_tanh/silu) or gated (swiglu/geglu/reglu/glu on [f|g] halves) activation."""
+def _mask_rows(x: torch.Tensor, row_limit: torch.Tensor) -> torch.Tensor:
+    row = torch.arange(x.shape[0], device=x.device)
+    return torch.where((row < row_limit.to(torch.long))[:, None], x, torch.zeros((), dtype=x.dtype, device=x.device))
+
+
+def activation(x: torch.Tensor, name: str, row_limit: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Plain (relu/gelu/gelu_tanh/silu) or gated (swiglu/geglu/reglu/glu on [f|g] halves) activation.
+
+    ``row_limit`` (int32 device tensor with one element) declares the rows of a 2-D ``x`` from that index on as
+    holding nothing: they come out as zeros and receive a zero gradient. The gated kernels neither read nor
+    compute them; the other paths mask."""
     if name in GLU_KINDS:
         if use_native(x) and (x.shape[-1] // 2) % 8 == 0:
-            return _Glu.apply(x.contiguous(), name)
+            return _Glu.apply(x.contiguous(), name, row_limit)
+        if row_limit is not None:
+            x = _mask_rows(x, row_limit)
         return reference.glu_reference(x, name)
+    if row_limit is not None:
+        x = _mask_rows(x, row_limit)
     if name not in ACT_KINDS:
         raise ValueError(f"unknown activation type {name}")
     if use_native(x) and x.numel() % 8 == 0:

@@ -254,16 +254,19 @@ def rope(x: torch.Tensor, out: torch.Tensor, *, nheads: int, head_dim: int, toke
 # ---------------------------------------------------------------------------
 # activations
 # ---------------------------------------------------------------------------
-def glu_fwd(x: torch.Tensor, name: str) -> torch.Tensor:
+def glu_fwd(x: torch.Tensor, name: str, row_limit: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``row_limit`` (int32 device tensor, one element): rows from that index on are not read and come out as
+    zeros (the unused capacity of a padded expert layout, which no kernel has written)."""
     kind, gate_is_act = GLU_KINDS[name]
     f = x.shape[-1] // 2
     x2 = x.reshape(-1, 2 * f)
     y = torch.empty((x2.shape[0], f), dtype=x.dtype, device=x.device)
-    call("icb_glu_fwd", ptr(x2), ptr(y), x2.shape[0], f, kind, gate_is_act, dtype_code(x.dtype), stream_ptr())
+    call("icb_glu_fwd", ptr(x2), ptr(y), x2.shape[0], f, kind, gate_is_act, dtype_code(x.dtype), stream_ptr(),
+         ptr(row_limit))
     return y.view(*x.shape[:-1], f)
 
 
-def glu_bwd(dy: torch.Tensor, x: torch.Tensor, name: str) -> torch.Tensor:
+def glu_bwd(dy: torch.Tensor, x: torch.Tensor, name: str, row_limit: Optional[torch.Tensor] = None) -> torch.Tensor:
     kind, gate_is_act = GLU_KINDS[name]
     f = x.shape[-1] // 2
     x2 = x.reshape(-1, 2 * f)
@@ -271,7 +274,8 @@ def glu_bwd(dy: torch.Tensor, x: torch.Tensor, name: str) -> torch.Tensor:
     if not dy2.is_contiguous():
         dy2 = dy2.contiguous()
     dx = torch.empty_like(x2)
-    call("icb_glu_bwd", ptr(dy2), ptr(x2), ptr(dx), x2.shape[0], f, kind, gate_is_act, dtype_code(x.dtype), stream_ptr())
+    call("icb_glu_bwd", ptr(dy2), ptr(x2), ptr(dx), x2.shape[0], f, kind, gate_is_act, dtype_code(x.dtype), stream_ptr(),
+         ptr(row_limit))
     return dx.view(x.shape)
 
 

@@ -30,8 +30,8 @@ _SIGNATURES = {
     "icb_norm_fwd": [P, P, P, P, P, P, P, P, I, I, F, F, I, I, P],
     "icb_norm_bwd": [P, P, P, P, P, P, P, P, P, P, I, I, F, I, I, I, I, P],
     "icb_rope": [P, P, P, I, I, I, L, L, I, F, F, I, I, I, I, P, I],
-    "icb_glu_fwd": [P, P, L, I, I, I, I, P],
-    "icb_glu_bwd": [P, P, P, L, I, I, I, I, P],
+    "icb_glu_fwd": [P, P, L, I, I, I, I, P, P],
+    "icb_glu_bwd": [P, P, P, L, I, I, I, I, P, P],
     "icb_act_fwd": [P, P, L, I, I, P],
     "icb_act_bwd": [P, P, P, L, I, I, P],
     "icb_embedding_fwd": [P, P, P, P, P, I, I, I, I, I, I, P],

@@ -121,6 +121,14 @@ def test_glu(name):
     ref.backward(dy.float())
     dx = kernels.glu_bwd(dy, x, name)
     _close(dx, xf.grad, 3e-2)
+    # a row limit: rows from it on may hold anything (NaN here); they come out as zeros, the others unchanged
+    limit = torch.tensor([77], dtype=torch.int32, device="cuda")
+    xn = x.clone()
+    xn[77:] = float("nan")
+    y2 = kernels.glu_fwd(xn, name, limit)
+    dx2 = kernels.glu_bwd(dy, xn, name, limit)
+    assert torch.equal(y2[:77], y[:77]) and torch.equal(dx2[:77], dx[:77])
+    assert not y2[77:].any() and not dx2[77:].any()
 
 
 @pytest.mark.parametrize("name", ["relu", "gelu", "gelu_tanh", "silu"])
@@ -178,15 +186,18 @@ def test_cross_entropy(t, v, valid):
     assert float(g[:, valid:].float().abs().max() if valid < v else 0.0) == 0.0
 
 
-def test_adam_and_norms():
+@pytest.mark.parametrize("skew", [0, 1])
+def test_adam_and_norms(skew):
+    """skew = 0: aligned buffers (four-element kernel plus a three-element tail); skew = 1: views that start one
+    element into their buffers, which only the element-wise kernel can take."""
     from ironcore_b200.ops import kernels
 
     torch.manual_seed(6)
     n = 100_003
-    p = torch.randn(n, device="cuda").to(BF)
-    g = (0.1 * torch.randn(n, device="cuda")).to(BF)
-    m = torch.zeros(n, device="cuda")
-    v = torch.zeros(n, device="cuda")
+    p = torch.randn(n + skew, device="cuda").to(BF)[skew:]
+    g = (0.1 * torch.randn(n + skew, device="cuda")).to(BF)[skew:]
+    m = torch.zeros(n + skew, device="cuda")[skew:]
+    v = torch.zeros(n + skew, device="cuda")[skew:]
     total = torch.zeros(1, device="cuda")
     kernels.sumsq(g, total)
     assert abs(total.item() - g.float().pow(2).sum().item()) < 1e-3 * total.item()
