@@ -5,12 +5,15 @@
 // loaded once: S = Q K^T and dP = dO V^T (K-major reads), then dV += P^T dO, dK += dS^T Q
 // and dQ = dS K, which read the *same* shared-memory bytes through MN-major descriptors,
 // so nothing is transposed or copied. TMEM holds S, dP, dV and dK (4 x 128 columns for
-// head_dim 128); dQ reuses the S columns once the softmax warps have consumed S.
+// head_dim 128); dQ reuses the dP columns once the softmax warps have consumed dP. Q is double buffered:
+// the next step's Q tile is loaded while this step runs and its S = Q K^T is issued right behind this step's
+// dQ, so that it executes while dQ is drained.
 // Warps 2-9 are two groups of four; a thread owns one query row (TMEM lane) and its group one half of
 // the columns, so every warp scheduler has two softmax warps whose TMEM loads, exponentials and shared-memory
 // stores interleave: P = exp2(S*scale - lse), dS = P (dP - delta) scale,
-// written as bf16 into 128-byte-swizzled tiles; the same threads drain dQ with fp32 vector
-// atomics into a zeroed scratch (converted to 16-bit by a follow-up kernel) and, at the
+// written as bf16 into 128-byte-swizzled tiles; the same threads copy dQ from TMEM into an fp32 staging tile
+// (the P / dS buffers, free by then) that one thread adds to a zeroed fp32 scratch with TMA bulk reduce-adds
+// (converted to 16-bit by a follow-up kernel) and, at the
 // end, dK (first group) / dV (second group; TMEM lane == kv row). dK/dV need no atomics: the group's heads are
 // accumulated in place. Every wait is bounded (status word + drain on timeout).
 #include "host_common.h"
@@ -51,8 +54,8 @@ struct FbSmem {
   static constexpr int p_bytes = 128 * 128 * 2;
   static constexpr int k_off = 0;
   static constexpr int v_off = k_off + tile_bytes;
-  static constexpr int q_off = v_off + tile_bytes;
-  static constexpr int do_off = q_off + tile_bytes;
+  static constexpr int q_off = v_off + tile_bytes;          // two Q buffers
+  static constexpr int do_off = q_off + 2 * tile_bytes;
   static constexpr int p_off = do_off + tile_bytes;
   static constexpr int ds_off = p_off + p_bytes;
   static constexpr int bar_off = ds_off + p_bytes;
@@ -65,11 +68,64 @@ __device__ __forceinline__ float fast_exp2_b(float x) {
   return y;
 }
 
+// One 32-column chunk of the softmax / dS phase for one query row: P = exp2(S*scale - lse) (masked), written for
+// dV = P^T dO, and dS' = P (dP - delta) written for dK and dQ; the softmax scale that dS carries is applied where
+// dK and dQ leave the chip. MASK: the tile crosses the diagonal, the end of the sequence or holds rows past it.
+// DROP: attention dropout (dV takes the masked, rescaled P; dP arrives as d(masked P) and is masked the same way;
+// delta = rowsum(dO O) already includes the mask).
+template <bool MASK, bool DROP>
+__device__ __forceinline__ void fb_softmax_chunk(const uint32_t (&sr)[32], const uint32_t (&dr)[32], int col_base,
+                                                 uint8_t* prow, uint8_t* dsrow, int row7, float scale_log2, float lse2,
+                                                 float dlt, bool q_valid, int kv0, int q_idx, int seq_len, int causal,
+                                                 int in_fmt, unsigned long long drop_key, unsigned long long drop_row,
+                                                 int drop_thr, float drop_scale) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    float p[8], ds[8];
+    unsigned long long h = 0ull;
+    if (DROP) h = dropout_hash(drop_key, drop_row + (unsigned)((kv0 + col_base + g * 8) >> 3));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float pv = fast_exp2_b(__uint_as_float(sr[g * 8 + i]) * scale_log2 - lse2);
+      if (MASK) {
+        const int kv_idx = kv0 + col_base + g * 8 + i;
+        const bool keep = q_valid && kv_idx < seq_len && !(causal && kv_idx > q_idx);
+        pv = keep ? pv : 0.f;
+      }
+      float dp = __uint_as_float(dr[g * 8 + i]);
+      if (DROP) {
+        const float mr = (int)((h >> (8 * i)) & 0xffull) >= drop_thr ? drop_scale : 0.f;
+        dp *= mr;
+        p[i] = pv * mr;
+      } else {
+        p[i] = pv;
+      }
+      ds[i] = pv * (dp - dlt);
+    }
+    uint4 up, ud;
+    if (in_fmt == 1) {
+      up.x = pack_bf16x2(p[0], p[1]); up.y = pack_bf16x2(p[2], p[3]);
+      up.z = pack_bf16x2(p[4], p[5]); up.w = pack_bf16x2(p[6], p[7]);
+      ud.x = pack_bf16x2(ds[0], ds[1]); ud.y = pack_bf16x2(ds[2], ds[3]);
+      ud.z = pack_bf16x2(ds[4], ds[5]); ud.w = pack_bf16x2(ds[6], ds[7]);
+    } else {
+      up.x = pack_f16x2(p[0], p[1]); up.y = pack_f16x2(p[2], p[3]);
+      up.z = pack_f16x2(p[4], p[5]); up.w = pack_f16x2(p[6], p[7]);
+      ud.x = pack_f16x2(ds[0], ds[1]); ud.y = pack_f16x2(ds[2], ds[3]);
+      ud.z = pack_f16x2(ds[4], ds[5]); ud.w = pack_f16x2(ds[6], ds[7]);
+    }
+    const int col0 = col_base + g * 8;          // col_base is a multiple of 32: (col0 & 63) >> 3 is its piece index
+    const int off = (col0 >> 6) * 16384 + ((((col0 & 63) >> 3) ^ row7) << 4);
+    *reinterpret_cast<uint4*>(prow + off) = up;
+    *reinterpret_cast<uint4*>(dsrow + off) = ud;
+  }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(kFbThreads, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
-                 const FlashBwdArgs args) {
+                 const __grid_constant__ CUtensorMap tmDQ, const FlashBwdArgs args) {
   using L = FbSmem<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -81,15 +137,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sDS = smem + L::ds_off;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::bar_off);
   uint64_t* kv_full = bars;
-  uint64_t* q_full = bars + 1;
-  uint64_t* q_empty = bars + 2;
-  uint64_t* do_full = bars + 3;
-  uint64_t* do_empty = bars + 4;
-  uint64_t* sdp_full = bars + 5;
-  uint64_t* pds_full = bars + 6;
-  uint64_t* dq_full = bars + 7;
-  uint64_t* dq_empty = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* q_full = bars + 1;        // 2
+  uint64_t* q_empty = bars + 3;       // 2
+  uint64_t* do_full = bars + 5;
+  uint64_t* do_empty = bars + 6;
+  uint64_t* sdp_full = bars + 7;
+  uint64_t* pds_full = bars + 8;
+  uint64_t* dq_full = bars + 9;
+  uint64_t* dq_empty = bars + 10;
+  uint64_t* stage_free = bars + 11;   // 2: the dQ staging that borrowed Q buffer i has been read by its reduce
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -116,20 +173,25 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+    }
     mbar_init(do_full, 1);
     mbar_init(do_empty, 1);
     mbar_init(sdp_full, 1);
     mbar_init(pds_full, kFbSoftmaxThreads);
     mbar_init(dq_full, 1);
     mbar_init(dq_empty, kFbSoftmaxThreads);
+    mbar_init(&stage_free[0], 1);
+    mbar_init(&stage_free[1], 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
     tma_prefetch_desc(&tmDO);
+    tma_prefetch_desc(&tmDQ);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kFbTmemCols);
@@ -139,8 +201,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tm_s = tmem_base;          // also dQ
-  const uint32_t tm_dp = tmem_base + 128;
+  const uint32_t tm_s = tmem_base;
+  const uint32_t tm_dp = tmem_base + 128;   // also dQ, once the softmax warps have consumed dP
   const uint32_t tm_dv = tmem_base + 256;
   const uint32_t tm_dk = tmem_base + 384;
 
@@ -156,10 +218,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t ph = it & 1;
         const int head = kv_head * group + it / iters_per_head;
         const int t0 = seq_start + (i_begin + it % iters_per_head) * 128;
-        mbar_wait(q_empty, ph ^ 1, abort_flag, args.status, kTimeoutSmemEmpty);
-        mbar_expect_tx(q_full, L::tile_bytes);
+        const int qb = it & 1;
+        mbar_wait(&q_empty[qb], ((it >> 1) & 1) ^ 1, abort_flag, args.status, kTimeoutSmemEmpty);
+        mbar_wait(&stage_free[qb], ((it >> 1) & 1) ^ 1, abort_flag, args.status, kTimeoutSmemEmpty);
+        mbar_expect_tx(&q_full[qb], L::tile_bytes);
 #pragma unroll
-        for (int c = 0; c < L::kChunks; ++c) tma_load_3d(sQ + c * 16384, &tmQ, q_full, c * 64, head, t0);
+        for (int c = 0; c < L::kChunks; ++c)
+          tma_load_3d(sQ + qb * L::tile_bytes + c * 16384, &tmQ, &q_full[qb], c * 64, head, t0);
         mbar_wait(do_empty, ph ^ 1, abort_flag, args.status, kTimeoutSmemEmpty);
         mbar_expect_tx(do_full, L::tile_bytes);
 #pragma unroll
@@ -175,18 +240,26 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aDO = smem_u32(sDO);
       const uint32_t aP = smem_u32(sP), aDS = smem_u32(sDS);
       mbar_wait(kv_full, 0, abort_flag, args.status, kTimeoutSmemFull);
-      for (int it = 0; it < n_iters; ++it) {
-        const uint32_t ph = it & 1;
-        mbar_wait(q_full, ph, abort_flag, args.status, kTimeoutSmemFull);
-        mbar_wait(dq_empty, ph ^ 1, abort_flag, args.status, kTimeoutTmemEmpty);
+      // S of step it + 1 is issued right behind dQ of step it (Q is double buffered and the S columns were
+      // consumed before P / dS were published), so the tensor core works on it while dQ is drained; dP has to
+      // wait for that drain because dQ uses its columns.
+      auto issue_s = [&](int it) {
+        const uint32_t q_addr = aQ + (it & 1) * L::tile_bytes;
+        mbar_wait(&q_full[it & 1], (it >> 1) & 1, abort_flag, args.status, kTimeoutSmemFull);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-          umma_ss(tm_s, umma_desc_sw128(aQ + off, 16, 1024), umma_desc_sw128(aK + off, 16, 1024), idesc_kk,
+          umma_ss(tm_s, umma_desc_sw128(q_addr + off, 16, 1024), umma_desc_sw128(aK + off, 16, 1024), idesc_kk,
                   k > 0 ? 1u : 0u);
         }
+      };
+      if (n_iters > 0) issue_s(0);
+      for (int it = 0; it < n_iters; ++it) {
+        const uint32_t ph = it & 1;
+        const uint32_t q_addr = aQ + (it & 1) * L::tile_bytes;
         mbar_wait(do_full, ph, abort_flag, args.status, kTimeoutSmemFull);
+        mbar_wait(dq_empty, ph ^ 1, abort_flag, args.status, kTimeoutTmemEmpty);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
@@ -207,15 +280,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // dK += dS^T Q
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ss(tm_dk, umma_desc_sw128(aDS + k * 2048, 16384, 1024), umma_desc_sw128(aQ + k * 2048, 16384, 1024),
+          umma_ss(tm_dk, umma_desc_sw128(aDS + k * 2048, 16384, 1024), umma_desc_sw128(q_addr + k * 2048, 16384, 1024),
                   idesc_mm, (acc | (k > 0 ? 1u : 0u)));
-        umma_commit(q_empty);
+        umma_commit(&q_empty[it & 1]);
         // dQ = dS K   (A = dS read K-major: M = q rows, K = kv; B = K tile read MN-major)
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ss(tm_s, umma_desc_sw128(aDS + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+          umma_ss(tm_dp, umma_desc_sw128(aDS + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
                   umma_desc_sw128(aK + k * 2048, 16384, 1024), idesc_km, k > 0 ? 1u : 0u);
         umma_commit(dq_full);
+        if (it + 1 < n_iters) issue_s(it + 1);
       }
     }
     __syncwarp();
@@ -239,81 +313,77 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         lse2 = args.lse[(size_t)head * args.total_tokens + tok] * log2e;
         dlt = args.delta[(size_t)head * args.total_tokens + tok];
       }
-      const bool need_mask = (args.causal && it_q == jt) || (kv0 + 128 > seq_len);
+      const bool need_mask = (args.causal && it_q == jt) || (kv0 + 128 > seq_len) || (it_q * 128 + 128 > seq_len);
       const unsigned long long drop_row = dropout_row_counter(b, args.hq, head, args.seq_len, q_idx);
       mbar_wait(sdp_full, ph, abort_flag, args.status, kTimeoutTmemFull);
       tc_fence_after();
+      if (it > 0) {
+        // the P tile staged the first half of the previous step's dQ: that bulk reduce (the older of the two
+        // groups) must have read it
+        if (threadIdx.x == 64) tma_store_wait_read<1>();
+        named_barrier(1, kFbSoftmaxThreads);
+      }
       uint8_t* prow = sP + row * 128;
       uint8_t* dsrow = sDS + row * 128;
-#pragma unroll 1
-      for (int c = half * 2; c < half * 2 + 2; ++c) {
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int col_base = half * 64 + cc * 32;
         uint32_t sr[32], dr[32];
-        tmem_ld_32x32(tm_s + lane_off + c * 32, sr);
-        tmem_ld_32x32(tm_dp + lane_off + c * 32, dr);
+        tmem_ld_32x32(tm_s + lane_off + col_base, sr);
+        tmem_ld_32x32(tm_dp + lane_off + col_base, dr);
         tmem_ld_wait();
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float p[8], ds[8];
-          // dropout: dV takes the masked, rescaled P; dP arrives as d(masked P) and is masked the same way
-          // before dS = P (dP - delta) scale, where delta = rowsum(dO O) already includes the mask
-          unsigned long long h = ~0ull;
-          if (dropout) h = dropout_hash(drop_key, drop_row + (unsigned)((kv0 + c * 32 + g * 8) >> 3));
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int col = c * 32 + g * 8 + i;
-            float pv = fast_exp2_b(__uint_as_float(sr[g * 8 + i]) * args.scale_log2 - lse2);
-            bool keep = q_valid;
-            if (need_mask) {
-              const int kv_idx = kv0 + col;
-              if (kv_idx >= seq_len || (args.causal && kv_idx > q_idx)) keep = false;
-            }
-            pv = keep ? pv : 0.f;
-            const float mr = (int)((h >> (8 * i)) & 0xffull) >= args.drop_thr ? args.drop_scale : 0.f;
-            p[i] = pv * mr;
-            ds[i] = pv * (__uint_as_float(dr[g * 8 + i]) * mr - dlt) * args.scale;
-          }
-          uint4 up, ud;
-          if (args.in_fmt == 1) {
-            up.x = pack_bf16x2(p[0], p[1]); up.y = pack_bf16x2(p[2], p[3]);
-            up.z = pack_bf16x2(p[4], p[5]); up.w = pack_bf16x2(p[6], p[7]);
-            ud.x = pack_bf16x2(ds[0], ds[1]); ud.y = pack_bf16x2(ds[2], ds[3]);
-            ud.z = pack_bf16x2(ds[4], ds[5]); ud.w = pack_bf16x2(ds[6], ds[7]);
-          } else {
-            up.x = pack_f16x2(p[0], p[1]); up.y = pack_f16x2(p[2], p[3]);
-            up.z = pack_f16x2(p[4], p[5]); up.w = pack_f16x2(p[6], p[7]);
-            ud.x = pack_f16x2(ds[0], ds[1]); ud.y = pack_f16x2(ds[2], ds[3]);
-            ud.z = pack_f16x2(ds[4], ds[5]); ud.w = pack_f16x2(ds[6], ds[7]);
-          }
-          const int col0 = c * 32 + g * 8;
-          const int off = (col0 >> 6) * 16384 + ((((col0 & 63) >> 3) ^ (row & 7)) << 4);
-          *reinterpret_cast<uint4*>(prow + off) = up;
-          *reinterpret_cast<uint4*>(dsrow + off) = ud;
+#define ICB_FB_CHUNK(M, D)                                                                                          \
+  fb_softmax_chunk<M, D>(sr, dr, col_base, prow, dsrow, row & 7, args.scale_log2, lse2, dlt, q_valid, kv0, q_idx,   \
+                         seq_len, args.causal, args.in_fmt, drop_key, drop_row, args.drop_thr, args.drop_scale)
+        if (dropout) {
+          if (need_mask) ICB_FB_CHUNK(true, true);
+          else ICB_FB_CHUNK(false, true);
+        } else {
+          if (need_mask) ICB_FB_CHUNK(true, false);
+          else ICB_FB_CHUNK(false, false);
         }
+#undef ICB_FB_CHUNK
       }
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(pds_full);
-      // drain dQ
+      // drain dQ: TMEM -> fp32 staging in the 128-byte swizzle of the tensor map, then one thread adds the tile to
+      // the fp32 accumulator in global memory with bulk reduce-adds: whole 128-byte lines instead of one 16-byte
+      // atomic per thread and row. The first 64 columns are staged in the P tile and the rest in this step's Q
+      // buffer (both free once dq_full fired): the next softmax only has to wait for the reduce of the first half,
+      // the second half may take until the Q buffer is loaded again a step later.
+      if (it > 0 && threadIdx.x == 64) {
+        tma_store_wait_read<0>();                      // both groups of the previous step: long done by now
+        mbar_arrive(&stage_free[(it - 1) & 1]);
+      }
       mbar_wait(dq_full, ph, abort_flag, args.status, kTimeoutTmemFull);
       tc_fence_after();
-      float* dqrow = args.dq_acc + ((size_t)tok * args.hq + head) * HD;
+      uint8_t* stage_hi = sQ + (it & 1) * L::tile_bytes;
 #pragma unroll 1
       for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); ++c) {
         uint32_t o[32];
-        tmem_ld_32x32(tm_s + lane_off + c * 32, o);
+        tmem_ld_32x32(tm_dp + lane_off + c * 32, o);
         tmem_ld_wait();
-        if (q_valid) {
+        uint8_t* brow = (c < 2 ? sP + c * 16384 : stage_hi + (c - 2) * 16384) + row * 128;
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            float4 v4 = make_float4(__uint_as_float(o[g * 4]), __uint_as_float(o[g * 4 + 1]),
-                                    __uint_as_float(o[g * 4 + 2]), __uint_as_float(o[g * 4 + 3]));
-            atomicAdd(reinterpret_cast<float4*>(dqrow + c * 32 + g * 4), v4);
-          }
-        }
+        for (int g = 0; g < 8; ++g)
+          *reinterpret_cast<uint4*>(brow + ((g ^ (row & 7)) << 4)) = make_uint4(o[g * 4], o[g * 4 + 1], o[g * 4 + 2], o[g * 4 + 3]);
       }
       tc_fence_before();
-      mbar_arrive(dq_empty);
+      mbar_arrive(dq_empty);              // the dP columns are free: the next step's dP = dO V^T may be issued
+      fence_proxy_async_smem();
+      named_barrier(1, kFbSoftmaxThreads);
+      if (threadIdx.x == 64) {
+        const int t0 = seq_start + it_q * 128;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) tma_reduce_add_3d(&tmDQ, sP + c * 16384, c * 32, head, t0);
+        tma_store_commit();
+#pragma unroll
+        for (int c = 2; c < HD / 32; ++c) tma_reduce_add_3d(&tmDQ, stage_hi + (c - 2) * 16384, c * 32, head, t0);
+        tma_store_commit();                              // (an empty group for head_dim 64)
+      }
     }
+    if (threadIdx.x == 64) tma_store_wait<0>();
     // ---- epilogue: dK, dV (lane == kv row). The last dq_full wait implies every MMA finished.
     {
       const int kv_idx = kv0 + row;
@@ -324,6 +394,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_after();
       {
         const int which = half;
+        const float out_scale = which == 0 ? args.scale : 1.0f;   // dK = scale * dS'^T Q
         const uint32_t tm = which == 0 ? tm_dk : tm_dv;
         uint8_t* orow = which == 0 ? dkrow : dvrow;
 #pragma unroll 1
@@ -336,7 +407,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (int g = 0; g < 4; ++g) {
               float f[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(o[g * 8 + i]);
+              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(o[g * 8 + i]) * out_scale;
               uint4 u;
               if (args.in_fmt == 1) {
                 u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
@@ -392,17 +463,19 @@ __global__ void flash_delta_kernel(const uint16_t* __restrict__ dO, const uint16
   if (lane == 0) delta[(size_t)h * T + t] = s;
 }
 
-// fp32 [T, width] -> 16-bit rows of pitch out_stride
+// fp32 [T, width] * scale -> 16-bit rows of pitch out_stride
 template <bool BF16>
 __global__ void flash_dq_convert_kernel(const float* __restrict__ acc, uint16_t* __restrict__ out, long long T,
-                                        int width, long long out_stride) {
+                                        int width, long long out_stride, float scale) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int vecs = width >> 3;
   if (idx >= T * vecs) return;
   const long long t = idx / vecs;
   const int v = (int)(idx - t * vecs);
-  const float4 a = *reinterpret_cast<const float4*>(acc + (size_t)t * width + v * 8);
-  const float4 b = *reinterpret_cast<const float4*>(acc + (size_t)t * width + v * 8 + 4);
+  float4 a = *reinterpret_cast<const float4*>(acc + (size_t)t * width + v * 8);
+  float4 b = *reinterpret_cast<const float4*>(acc + (size_t)t * width + v * 8 + 4);
+  a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;     // dQ = scale * dS' K
+  b.x *= scale; b.y *= scale; b.z *= scale; b.w *= scale;
   uint4 u;
   if (BF16) {
     u.x = pack_bf16x2(a.x, a.y); u.y = pack_bf16x2(a.z, a.w); u.z = pack_bf16x2(b.x, b.y); u.w = pack_bf16x2(b.z, b.w);
@@ -414,7 +487,8 @@ __global__ void flash_dq_convert_kernel(const float* __restrict__ acc, uint16_t*
 
 template <int HD>
 static int launch_flash_bwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
-                            const CUtensorMap& tmDO, const FlashBwdArgs& args, dim3 grid, cudaStream_t stream) {
+                            const CUtensorMap& tmDO, const CUtensorMap& tmDQ, const FlashBwdArgs& args, dim3 grid,
+                            cudaStream_t stream) {
   static bool configured = false;
   auto kern = flash_bwd_kernel<HD>;
   if (!configured) {
@@ -422,7 +496,7 @@ static int launch_flash_bwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, cons
     if (e != cudaSuccess) return -(int)e;
     configured = true;
   }
-  kern<<<grid, kFbThreads, FbSmem<HD>::total, stream>>>(tmQ, tmK, tmV, tmDO, args);
+  kern<<<grid, kFbThreads, FbSmem<HD>::total, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, args);
   return check_launch("flash_bwd_kernel");
 }
 
@@ -462,7 +536,7 @@ ICB_API int icb_flash_bwd(const void* dout, const void* q, const void* k, const 
   cudaError_t e = cudaMemsetAsync(dq_acc, 0, (size_t)total_tokens * hq * hd * sizeof(float), stream);
   if (e != cudaSuccess) return -(int)e;
 
-  CUtensorMap tmQ, tmK, tmV, tmDO;
+  CUtensorMap tmQ, tmK, tmV, tmDO, tmDQ;
   int rc = make_head_tmap(&tmQ, q, hd, hq, total_tokens, q_stride, dtype);
   if (rc) return rc;
   rc = make_head_tmap(&tmK, k, hd, hkv, total_tokens, kv_stride, dtype);
@@ -471,6 +545,14 @@ ICB_API int icb_flash_bwd(const void* dout, const void* q, const void* k, const 
   if (rc) return rc;
   rc = make_head_tmap(&tmDO, dout, hd, hq, total_tokens, (long long)hq * hd, dtype);
   if (rc) return rc;
+  {
+    // fp32 accumulator [T, hq, hd] seen as (hd, hq, T); boxes of 32 floats (one 128-byte swizzle row) x 128 tokens
+    uint64_t dims[3] = {(uint64_t)hd, (uint64_t)hq, (uint64_t)total_tokens};
+    uint64_t str[2] = {(uint64_t)hd * 4, (uint64_t)hq * hd * 4};
+    uint32_t box[3] = {32, 1, 128};
+    rc = make_tmap(&tmDQ, kF32, 3, dq_acc, dims, str, box, true);
+    if (rc) return rc;
+  }
   FlashBwdArgs a;
   a.batch = batch; a.seq_len = seq_len; a.hq = hq; a.hkv = hkv;
   a.cu_seqlens = cu_seqlens;
@@ -487,8 +569,8 @@ ICB_API int icb_flash_bwd(const void* dout, const void* q, const void* k, const 
   a.drop_seed = dropout_seed;
   a.drop_scale = 256.0f / (256 - a.drop_thr);
   dim3 grid((seq_len + 127) / 128, hkv, batch);
-  rc = (hd == 64) ? launch_flash_bwd<64>(tmQ, tmK, tmV, tmDO, a, grid, stream)
-                  : launch_flash_bwd<128>(tmQ, tmK, tmV, tmDO, a, grid, stream);
+  rc = (hd == 64) ? launch_flash_bwd<64>(tmQ, tmK, tmV, tmDO, tmDQ, a, grid, stream)
+                  : launch_flash_bwd<128>(tmQ, tmK, tmV, tmDO, tmDQ, a, grid, stream);
   if (rc) return rc;
   {
     const int width = hq * hd;
@@ -497,10 +579,10 @@ ICB_API int icb_flash_bwd(const void* dout, const void* q, const void* k, const 
     const long long blocks = (n + th - 1) / th;
     if (bf16)
       flash_dq_convert_kernel<true><<<(unsigned)blocks, th, 0, stream>>>(dq_acc, reinterpret_cast<uint16_t*>(dq),
-                                                                        total_tokens, width, dq_stride);
+                                                                        total_tokens, width, dq_stride, scale);
     else
       flash_dq_convert_kernel<false><<<(unsigned)blocks, th, 0, stream>>>(dq_acc, reinterpret_cast<uint16_t*>(dq),
-                                                                         total_tokens, width, dq_stride);
+                                                                         total_tokens, width, dq_stride, scale);
   }
   return check_launch("flash_dq_convert");
 }
