@@ -9,13 +9,15 @@
 // the next step's Q tile is loaded while this step runs and its S = Q K^T is issued right behind this step's
 // dQ, so that it executes while dQ is drained.
 // Warps 2-9 are two groups of four; a thread owns one query row (TMEM lane) and its group one half of
-// the columns, so every warp scheduler has two softmax warps whose TMEM loads, exponentials and shared-memory
-// stores interleave: P = exp2(S*scale - lse), dS = P (dP - delta) scale,
-// written as bf16 into 128-byte-swizzled tiles; the same threads copy dQ from TMEM into an fp32 staging tile
-// (the P / dS buffers, free by then) that one thread adds to a zeroed fp32 scratch with TMA bulk reduce-adds
-// (converted to 16-bit by a follow-up kernel) and, at the
-// end, dK (first group) / dV (second group; TMEM lane == kv row). dK/dV need no atomics: the group's heads are
-// accumulated in place. Every wait is bounded (status word + drain on timeout).
+// the columns. Per step they first turn S into P = exp2(S*scale - lse) (kept in registers, written as bf16 into a
+// 128-byte-swizzled tile) and publish it, so that dV = P^T dO runs while they wait for dP and form
+// dS' = P (dP - delta); then they copy dQ from TMEM into an fp32 staging tile (the P tile and the step's Q buffer,
+// both free by then) that one thread adds to a zeroed fp32 scratch with TMA bulk reduce-adds (converted to 16-bit
+// and scaled by a follow-up kernel) and, at the end, dK (first group) / dV (second group; TMEM lane == kv row).
+// dK/dV need no atomics: the group's heads are accumulated in place.
+// Barriers of one step: s_full (S done) -> p_full (P written) -> dV; dp_full (dP done) -> pds_full (dS written)
+// -> dK, dQ -> dq_full -> drain -> dq_empty (dP columns free). Every wait is bounded (status word + drain on
+// timeout).
 #include "host_common.h"
 #include "ptx.cuh"
 
@@ -68,56 +70,72 @@ __device__ __forceinline__ float fast_exp2_b(float x) {
   return y;
 }
 
-// One 32-column chunk of the softmax / dS phase for one query row: P = exp2(S*scale - lse) (masked), written for
-// dV = P^T dO, and dS' = P (dP - delta) written for dK and dQ; the softmax scale that dS carries is applied where
-// dK and dQ leave the chip. MASK: the tile crosses the diagonal, the end of the sequence or holds rows past it.
-// DROP: attention dropout (dV takes the masked, rescaled P; dP arrives as d(masked P) and is masked the same way;
-// delta = rowsum(dO O) already includes the mask).
+__device__ __forceinline__ uint4 fb_pack8(const float (&f)[8], int in_fmt) {
+  uint4 u;
+  if (in_fmt == 1) {
+    u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
+    u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+  } else {
+    u.x = pack_f16x2(f[0], f[1]); u.y = pack_f16x2(f[2], f[3]);
+    u.z = pack_f16x2(f[4], f[5]); u.w = pack_f16x2(f[6], f[7]);
+  }
+  return u;
+}
+// byte offset of the 16-byte piece that holds columns col0 .. col0 + 7 of a row in a 128-byte-swizzled tile of
+// 64-column (16 KiB) chunks; row7 = row & 7
+__device__ __forceinline__ int fb_piece_off(int col0, int row7) {
+  return (col0 >> 6) * 16384 + ((((col0 & 63) >> 3) ^ row7) << 4);
+}
+
+// The softmax / dS phase of one query row, in two parts per 32-column chunk so that P can be published (and
+// dV = P^T dO started) before dP has even arrived:
+//   part 1: P = exp2(S*scale - lse) (masked), kept in registers and written for the dV product;
+//   part 2: dS' = P (dP - delta), written for dK and dQ (the softmax scale that dS carries is applied where dK
+//           and dQ leave the chip).
+// MASK: the tile crosses the diagonal, the end of the sequence or holds rows past it. DROP: attention dropout
+// (dV takes the masked, rescaled P; dP arrives as d(masked P) and is masked the same way; delta = rowsum(dO O)
+// already includes the mask).
 template <bool MASK, bool DROP>
-__device__ __forceinline__ void fb_softmax_chunk(const uint32_t (&sr)[32], const uint32_t (&dr)[32], int col_base,
-                                                 uint8_t* prow, uint8_t* dsrow, int row7, float scale_log2, float lse2,
-                                                 float dlt, bool q_valid, int kv0, int q_idx, int seq_len, int causal,
-                                                 int in_fmt, unsigned long long drop_key, unsigned long long drop_row,
-                                                 int drop_thr, float drop_scale) {
+__device__ __forceinline__ void fb_p_chunk(const uint32_t (&sr)[32], float (&pv)[32], int col_base, uint8_t* prow,
+                                           int row7, float scale_log2, float lse2, bool q_valid, int kv0, int q_idx,
+                                           int seq_len, int causal, int in_fmt, unsigned long long drop_key,
+                                           unsigned long long drop_row, int drop_thr, float drop_scale) {
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
-    float p[8], ds[8];
+    float p[8];
     unsigned long long h = 0ull;
     if (DROP) h = dropout_hash(drop_key, drop_row + (unsigned)((kv0 + col_base + g * 8) >> 3));
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      float pv = fast_exp2_b(__uint_as_float(sr[g * 8 + i]) * scale_log2 - lse2);
+      float v = fast_exp2_b(__uint_as_float(sr[g * 8 + i]) * scale_log2 - lse2);
       if (MASK) {
         const int kv_idx = kv0 + col_base + g * 8 + i;
         const bool keep = q_valid && kv_idx < seq_len && !(causal && kv_idx > q_idx);
-        pv = keep ? pv : 0.f;
+        v = keep ? v : 0.f;
       }
+      pv[g * 8 + i] = v;
+      p[i] = DROP ? ((int)((h >> (8 * i)) & 0xffull) >= drop_thr ? v * drop_scale : 0.f) : v;
+    }
+    *reinterpret_cast<uint4*>(prow + fb_piece_off(col_base + g * 8, row7)) = fb_pack8(p, in_fmt);
+  }
+}
+template <bool DROP>
+__device__ __forceinline__ void fb_ds_chunk(const uint32_t (&dr)[32], const float (&pv)[32], int col_base,
+                                            uint8_t* dsrow, int row7, float dlt, int kv0, int in_fmt,
+                                            unsigned long long drop_key, unsigned long long drop_row, int drop_thr,
+                                            float drop_scale) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    float ds[8];
+    unsigned long long h = 0ull;
+    if (DROP) h = dropout_hash(drop_key, drop_row + (unsigned)((kv0 + col_base + g * 8) >> 3));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
       float dp = __uint_as_float(dr[g * 8 + i]);
-      if (DROP) {
-        const float mr = (int)((h >> (8 * i)) & 0xffull) >= drop_thr ? drop_scale : 0.f;
-        dp *= mr;
-        p[i] = pv * mr;
-      } else {
-        p[i] = pv;
-      }
-      ds[i] = pv * (dp - dlt);
+      if (DROP) dp = (int)((h >> (8 * i)) & 0xffull) >= drop_thr ? dp * drop_scale : 0.f;
+      ds[i] = pv[g * 8 + i] * (dp - dlt);
     }
-    uint4 up, ud;
-    if (in_fmt == 1) {
-      up.x = pack_bf16x2(p[0], p[1]); up.y = pack_bf16x2(p[2], p[3]);
-      up.z = pack_bf16x2(p[4], p[5]); up.w = pack_bf16x2(p[6], p[7]);
-      ud.x = pack_bf16x2(ds[0], ds[1]); ud.y = pack_bf16x2(ds[2], ds[3]);
-      ud.z = pack_bf16x2(ds[4], ds[5]); ud.w = pack_bf16x2(ds[6], ds[7]);
-    } else {
-      up.x = pack_f16x2(p[0], p[1]); up.y = pack_f16x2(p[2], p[3]);
-      up.z = pack_f16x2(p[4], p[5]); up.w = pack_f16x2(p[6], p[7]);
-      ud.x = pack_f16x2(ds[0], ds[1]); ud.y = pack_f16x2(ds[2], ds[3]);
-      ud.z = pack_f16x2(ds[4], ds[5]); ud.w = pack_f16x2(ds[6], ds[7]);
-    }
-    const int col0 = col_base + g * 8;          // col_base is a multiple of 32: (col0 & 63) >> 3 is its piece index
-    const int off = (col0 >> 6) * 16384 + ((((col0 & 63) >> 3) ^ row7) << 4);
-    *reinterpret_cast<uint4*>(prow + off) = up;
-    *reinterpret_cast<uint4*>(dsrow + off) = ud;
+    *reinterpret_cast<uint4*>(dsrow + fb_piece_off(col_base + g * 8, row7)) = fb_pack8(ds, in_fmt);
   }
 }
 
@@ -141,12 +159,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* q_empty = bars + 3;       // 2
   uint64_t* do_full = bars + 5;
   uint64_t* do_empty = bars + 6;
-  uint64_t* sdp_full = bars + 7;
+  uint64_t* dp_full = bars + 7;
   uint64_t* pds_full = bars + 8;
   uint64_t* dq_full = bars + 9;
   uint64_t* dq_empty = bars + 10;
   uint64_t* stage_free = bars + 11;   // 2: the dQ staging that borrowed Q buffer i has been read by its reduce
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* s_full = bars + 13;
+  uint64_t* p_full = bars + 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -179,7 +199,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     mbar_init(do_full, 1);
     mbar_init(do_empty, 1);
-    mbar_init(sdp_full, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_full, kFbSoftmaxThreads);
     mbar_init(pds_full, kFbSoftmaxThreads);
     mbar_init(dq_full, 1);
     mbar_init(dq_empty, kFbSoftmaxThreads);
@@ -253,6 +275,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           umma_ss(tm_s, umma_desc_sw128(q_addr + off, 16, 1024), umma_desc_sw128(aK + off, 16, 1024), idesc_kk,
                   k > 0 ? 1u : 0u);
         }
+        umma_commit(s_full);
       };
       if (n_iters > 0) issue_s(0);
       for (int it = 0; it < n_iters; ++it) {
@@ -267,8 +290,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           umma_ss(tm_dp, umma_desc_sw128(aDO + off, 16, 1024), umma_desc_sw128(aV + off, 16, 1024), idesc_kk,
                   k > 0 ? 1u : 0u);
         }
-        umma_commit(sdp_full);
-        mbar_wait(pds_full, ph, abort_flag, args.status, kTimeoutLocalFlag);
+        umma_commit(dp_full);
+        mbar_wait(p_full, ph, abort_flag, args.status, kTimeoutLocalFlag);
         tc_fence_after();
         const uint32_t acc = it > 0 ? 1u : 0u;
         // dV += P^T dO   (A = P read MN-major: M = kv, K = q rows; B = dO read MN-major)
@@ -277,6 +300,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           umma_ss(tm_dv, umma_desc_sw128(aP + k * 2048, 16384, 1024), umma_desc_sw128(aDO + k * 2048, 16384, 1024),
                   idesc_mm, (acc | (k > 0 ? 1u : 0u)));
         umma_commit(do_empty);
+        mbar_wait(pds_full, ph, abort_flag, args.status, kTimeoutLocalFlag);
+        tc_fence_after();
         // dK += dS^T Q
 #pragma unroll
         for (int k = 0; k < 8; ++k)
@@ -315,7 +340,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       const bool need_mask = (args.causal && it_q == jt) || (kv0 + 128 > seq_len) || (it_q * 128 + 128 > seq_len);
       const unsigned long long drop_row = dropout_row_counter(b, args.hq, head, args.seq_len, q_idx);
-      mbar_wait(sdp_full, ph, abort_flag, args.status, kTimeoutTmemFull);
+      mbar_wait(s_full, ph, abort_flag, args.status, kTimeoutTmemFull);
       tc_fence_after();
       if (it > 0) {
         // the P tile staged the first half of the previous step's dQ: that bulk reduce (the older of the two
@@ -325,24 +350,43 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       uint8_t* prow = sP + row * 128;
       uint8_t* dsrow = sDS + row * 128;
+      const int row7 = row & 7;
+      float pv[2][32];
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int col_base = half * 64 + cc * 32;
-        uint32_t sr[32], dr[32];
+        uint32_t sr[32];
         tmem_ld_32x32(tm_s + lane_off + col_base, sr);
+        tmem_ld_wait();
+#define ICB_FB_P(M, D)                                                                                               \
+  fb_p_chunk<M, D>(sr, pv[cc], col_base, prow, row7, args.scale_log2, lse2, q_valid, kv0, q_idx, seq_len,            \
+                   args.causal, args.in_fmt, drop_key, drop_row, args.drop_thr, args.drop_scale)
+        if (dropout) {
+          if (need_mask) ICB_FB_P(true, true);
+          else ICB_FB_P(false, true);
+        } else {
+          if (need_mask) ICB_FB_P(true, false);
+          else ICB_FB_P(false, false);
+        }
+#undef ICB_FB_P
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(p_full);                // dV = P^T dO may start
+      mbar_wait(dp_full, ph, abort_flag, args.status, kTimeoutTmemFull);
+      tc_fence_after();
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int col_base = half * 64 + cc * 32;
+        uint32_t dr[32];
         tmem_ld_32x32(tm_dp + lane_off + col_base, dr);
         tmem_ld_wait();
-#define ICB_FB_CHUNK(M, D)                                                                                          \
-  fb_softmax_chunk<M, D>(sr, dr, col_base, prow, dsrow, row & 7, args.scale_log2, lse2, dlt, q_valid, kv0, q_idx,   \
-                         seq_len, args.causal, args.in_fmt, drop_key, drop_row, args.drop_thr, args.drop_scale)
-        if (dropout) {
-          if (need_mask) ICB_FB_CHUNK(true, true);
-          else ICB_FB_CHUNK(false, true);
-        } else {
-          if (need_mask) ICB_FB_CHUNK(true, false);
-          else ICB_FB_CHUNK(false, false);
-        }
-#undef ICB_FB_CHUNK
+        if (dropout)
+          fb_ds_chunk<true>(dr, pv[cc], col_base, dsrow, row7, dlt, kv0, args.in_fmt, drop_key, drop_row,
+                            args.drop_thr, args.drop_scale);
+        else
+          fb_ds_chunk<false>(dr, pv[cc], col_base, dsrow, row7, dlt, kv0, args.in_fmt, drop_key, drop_row,
+                             args.drop_thr, args.drop_scale);
       }
       tc_fence_before();
       fence_proxy_async_smem();

@@ -50,8 +50,12 @@ __global__ void __launch_bounds__(256) moe_count_kernel(const MoeCountArgs a) {
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long s0 = (long long)blockIdx.x * blockDim.x; s0 < a.S; s0 += stride) {
     const long long s = s0 + threadIdx.x;
-    const bool valid = s < a.S;
+    bool valid = s < a.S;
     const int e = valid ? a.expert[s] : -1;
+    if (valid && (unsigned)e >= (unsigned)a.E) {   // not an expert id: the slot is dropped (moe_push reports it)
+      a.pos[s] = -1;
+      valid = false;
+    }
     // warp-aggregated atomics: lanes with the same expert take consecutive positions
     const unsigned active = __ballot_sync(0xffffffffu, valid);
     if (valid) {
@@ -201,6 +205,11 @@ __global__ void __launch_bounds__(256) moe_push_kernel(const MoePushArgs a) {
     const int n_gw = gridDim.x * (blockDim.x >> 5);
     for (int s = gw; s < a.S; s += n_gw) {
       const int e = a.expert[s];
+      if ((unsigned)e >= (unsigned)a.E) {
+        if (lane == 0 && a.dest_out != nullptr) a.dest_out[s] = -1;
+        if (lane == 0 && a.status != nullptr) atomicCAS(a.status, 0, kBadArgument);
+        continue;
+      }
       const int owner = e / a.e_local;
       const int dest = a.dest_in != nullptr ? a.dest_in[s] : base_sh[e] + a.pos[s];
       if (lane == 0 && a.dest_out != nullptr) a.dest_out[s] = dest;
@@ -274,6 +283,7 @@ __global__ void __launch_bounds__(256) moe_pull_kernel(const MoePullArgs a) {
           const int dest = a.dest[s];
           if (dest < 0 || dest >= a.cap) continue;
           const int owner = a.expert[s] / a.e_local;
+          if ((unsigned)owner >= (unsigned)a.ep) continue;
           const uint4 u = __ldcv(reinterpret_cast<const uint4*>(a.peer_y[owner] + (size_t)dest * a.d * 2) + c);
           if (a.gathered != nullptr)
             reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.gathered) + (size_t)s * a.d * 2)[c] = u;

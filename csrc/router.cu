@@ -51,6 +51,9 @@ router_fwd_kernel(const float* __restrict__ logits, int T, int E, int K, int nor
         probs[(size_t)t * E + e] = v[j];
         atomicAdd(&sh_p[e], v[j]);
       }
+      // a row of NaN logits (a diverged run) still has to select K valid experts: the probabilities written
+      // above carry the NaN to the loss, the selection below sees zeros
+      if (!(v[j] >= 0.f)) v[j] = 0.f;
     }
     // top-k by k rounds of warp arg-max (ties: lowest expert index, like torch.topk on distinct values)
     float taken_w[kRouterMaxK];
@@ -70,6 +73,7 @@ router_fwd_kernel(const float* __restrict__ logits, int T, int E, int K, int nor
         const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
         if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
       }
+      best_e = min(best_e, E - 1);     // (unreachable for K <= E: every round finds an expert)
       taken_w[r] = best;
       taken_e[r] = best_e;
       wsum += best;

@@ -307,7 +307,7 @@ class ParallelConfig(BaseConfig):
     zero_stage: int = opt(0, "0 = replicated optimizer, 1 = optimizer state sharded over DP")
     fused_comm: bool = opt(True, "use the in-kernel P2P collectives when symmetric memory is available")
     fused_norm_gather: Literal["auto", "on", "off"] = opt(
-        "auto", "row-parallel GEMM -> reduce-scatter -> RMSNorm -> all-gather in one kernel (auto: TP >= 4)")
+        "auto", "row-parallel GEMM -> reduce-scatter -> RMSNorm -> all-gather in one kernel (auto: separate kernels)")
     fused_zero: bool = opt(True, "gradient reduce-scatter + Adam + parameter broadcast as in-kernel collectives")
     fused_moe: bool = opt(True, "expert-parallel dispatch / combine as in-kernel P2P copies")
     nvls: Literal["auto", "on", "off"] = opt("auto", "NVSwitch multicast (multimem) forms of the in-kernel collectives")

@@ -498,10 +498,10 @@ def attach_fused_tp(model, config) -> Optional[FusedTP]:
         mod.fused = ws
     link = getattr(model, "link_fused_norm_gather", None)
     want = str(getattr(config.parallel, "fused_norm_gather", "auto")).lower()
-    # "auto": from 4 ranks up. At 2 ranks half of the consumer's tiles are local and hide its own push, and
-    # the separate kernels measured 11 % faster on the Llama-7B layer shapes; from 4 ranks up little of the
-    # push can hide behind local tiles and the producer form removes it together with the norm kernel.
-    on = want in ("on", "true", "1") or (want == "auto" and t >= 4)
+    # "auto" keeps the separate kernels: on the Llama-7B layer shapes the linked form measured 11 % slower at
+    # 2 ranks (half of the consumer's tiles are local and hide its own push) and level at 4 ranks (0.358 ms
+    # against 0.354 ms per boundary; 61.1 k against 62.2 k tokens/s for the whole step), so it stays opt-in.
+    on = want in ("on", "true", "1")
     if link is not None and on and ws.norm_fusable:
         link()
     return ws

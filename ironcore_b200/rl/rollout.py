@@ -204,6 +204,19 @@ class RolloutEngine:
         self._graph.replay()
         return self._static_logits
 
+    def release_graph(self):
+        """Drop the captured decode step (and its static buffers); the next ``decode_step`` captures again."""
+        if self._graph is not None:
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+            self._graph = None
+            self._static_logits = None
+            self._static_tokens = None
+            self._graph_seqs = 0
+            import gc
+
+            gc.collect()
+
     # ------------------------------------------------------------------ generation
     @torch.no_grad()
     def generate(self, prompts: torch.Tensor, max_new_tokens: int, temperature: float = 1.0, top_k: int = 0,

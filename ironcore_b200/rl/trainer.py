@@ -63,6 +63,13 @@ class GRPOTrainer(Trainer):
             self.sample_gen.manual_seed(int(config.init.seed) + 17 * mesh.get_rank())
         self.update_micro_batch = max(1, config.trainer.micro_batch_size)
 
+    def finalize(self):
+        # the decode step's captured graph holds the tensor-parallel all-reduces: it has to go before the
+        # process group does, or tearing the group down waits on work that is never replayed again
+        if getattr(self, "engine", None) is not None:
+            self.engine.release_graph()
+        super().finalize()
+
     def _prompts(self) -> torch.Tensor:
         rl = self.config.rl
         base = torch.randint(0, self.model.vocab_size, (self.prompts_per_replica, rl.prompt_len), generator=self.prompt_gen)

@@ -182,3 +182,25 @@ def test_gemm_2sm_epilogue_and_policy():
     native.check_status()
     assert out.data_ptr() == acc.data_ptr()
     _check(out, ref2, m, tol=1e-2)
+
+
+def test_gemm_accumulate_in_place_splits_k():
+    """C += A^T B with an fp32 C (the weight-gradient form): shapes whose whole-K tiles fill the machine badly
+    split the K range over several CTAs that add into C with TMA reduce-adds; same result as the unsplit kernels."""
+    from ironcore_b200.ops import kernels, native
+
+    torch.manual_seed(9)
+    m, n, k = 512, 4096, 4096          # an 8-way shard of the attention output projection's gradient
+    assert kernels._accumulate_split(m, n, k) > 1 and kernels._accumulate_split(4096, 4096, 4096) == 1
+    x, dy = _mk(k, m), _mk(k, n)
+    start = torch.randn(m, n, device="cuda")
+    ref = start + x.float().t() @ dy.float()
+    acc = start.clone()
+    out = kernels.mm_tn(x, dy, out=acc, residual=acc, out_dtype=torch.float32)          # policy: split
+    pair = start.clone()
+    kernels.mm_tn(x, dy, out=pair, residual=pair, out_dtype=torch.float32, two_sm=True)  # forced: CTA pairs
+    torch.cuda.synchronize()
+    native.check_status()
+    assert out.data_ptr() == acc.data_ptr()
+    _check(acc, ref, k, tol=1e-2)
+    assert (acc - pair).abs().max().item() <= 1e-3 * ref.abs().max().item()

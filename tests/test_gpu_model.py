@@ -130,6 +130,30 @@ def test_cuda_graph_micro_batch_matches_eager():
         assert abs(x - y) < 2e-2, (a, b)
 
 
+def test_router_kernel_selects_valid_experts_for_nan_rows():
+    """A diverged run feeds NaN logits to the router: the kernel must still name K experts in range for every
+    token (the downstream kernels index tables with them) while the probabilities keep the NaN for the loss."""
+    from ironcore_b200.models import moe  # noqa: F401  (registers the router entry points)
+    from ironcore_b200.ops import native
+
+    t, e, k = 64, 64, 6
+    logits = torch.randn(t, e, device="cuda")
+    logits[5] = float("nan")
+    logits[17, 3] = float("nan")
+    probs = torch.empty_like(logits)
+    w = torch.empty(t, k, device="cuda")
+    idx = torch.full((t, k), -7, dtype=torch.int32, device="cuda")
+    counts = torch.zeros(e, dtype=torch.int32, device="cuda")
+    psum = torch.zeros(e, device="cuda")
+    native.call("icb_router_fwd", native.ptr(logits), t, e, k, 1, native.ptr(probs), native.ptr(w), native.ptr(idx),
+                native.ptr(counts), native.ptr(psum), native.stream_ptr())
+    torch.cuda.synchronize()
+    assert int(idx.min()) >= 0 and int(idx.max()) < e
+    assert all(len(set(row.tolist())) == k for row in idx.cpu())
+    assert int(counts.sum()) == t * k
+    assert torch.isnan(probs[5]).all() and torch.isfinite(probs[0]).all()
+
+
 @pytest.mark.parametrize("experts,top_k,normalize", [(64, 6, False), (8, 2, True), (16, 1, False)])
 def test_router_kernel_matches_eager(experts, top_k, normalize):
     """Router kernels (GEMM logits -> softmax / top-k / histogram / aux loss, and the backward) against the same
