@@ -23,6 +23,21 @@
 
 namespace icb {
 
+// Cycle counters for `python -m benchmarks.flash_bwd_trace` (a separate build with -DICB_FB_TRACE; the product
+// library compiles these macros away): where each role of the kernel spends a step, summed over all CTAs.
+#ifdef ICB_FB_TRACE
+__device__ unsigned long long g_fb_trace[16];
+#define FB_T0(v) long long v = clock64()
+#define FB_TSET(v) v = clock64()
+#define FB_TADD(i, v) atomicAdd(&g_fb_trace[i], (unsigned long long)(clock64() - (v)))
+#define FB_TCOUNT(i) atomicAdd(&g_fb_trace[i], 1ull)
+#else
+#define FB_T0(v)
+#define FB_TSET(v)
+#define FB_TADD(i, v)
+#define FB_TCOUNT(i)
+#endif
+
 constexpr int kFbThreads = 320;           // TMA warp, MMA warp, 2 x 4 softmax warps
 constexpr int kFbSoftmaxThreads = 256;
 constexpr int kFbTmemCols = 512;
@@ -169,6 +184,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  FB_T0(t_cta);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int kv_head = blockIdx.y;
@@ -241,13 +257,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int head = kv_head * group + it / iters_per_head;
         const int t0 = seq_start + (i_begin + it % iters_per_head) * 128;
         const int qb = it & 1;
+        FB_T0(tt);
         mbar_wait(&q_empty[qb], ((it >> 1) & 1) ^ 1, abort_flag, args.status, kTimeoutSmemEmpty);
+        FB_TADD(0, tt);
+        FB_TSET(tt);
         mbar_wait(&stage_free[qb], ((it >> 1) & 1) ^ 1, abort_flag, args.status, kTimeoutSmemEmpty);
+        FB_TADD(12, tt);
         mbar_expect_tx(&q_full[qb], L::tile_bytes);
 #pragma unroll
         for (int c = 0; c < L::kChunks; ++c)
           tma_load_3d(sQ + qb * L::tile_bytes + c * 16384, &tmQ, &q_full[qb], c * 64, head, t0);
+        FB_TSET(tt);
         mbar_wait(do_empty, ph ^ 1, abort_flag, args.status, kTimeoutSmemEmpty);
+        FB_TADD(1, tt);
         mbar_expect_tx(do_full, L::tile_bytes);
 #pragma unroll
         for (int c = 0; c < L::kChunks; ++c) tma_load_3d(sDO + c * 16384, &tmDO, do_full, c * 64, head, t0);
@@ -267,7 +289,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // wait for that drain because dQ uses its columns.
       auto issue_s = [&](int it) {
         const uint32_t q_addr = aQ + (it & 1) * L::tile_bytes;
+        FB_T0(tq);
         mbar_wait(&q_full[it & 1], (it >> 1) & 1, abort_flag, args.status, kTimeoutSmemFull);
+        FB_TADD(2, tq);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
@@ -281,8 +305,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int it = 0; it < n_iters; ++it) {
         const uint32_t ph = it & 1;
         const uint32_t q_addr = aQ + (it & 1) * L::tile_bytes;
+        FB_T0(tm);
         mbar_wait(do_full, ph, abort_flag, args.status, kTimeoutSmemFull);
+        FB_TADD(3, tm);
+        FB_TSET(tm);
         mbar_wait(dq_empty, ph ^ 1, abort_flag, args.status, kTimeoutTmemEmpty);
+        FB_TADD(4, tm);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
@@ -291,7 +319,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                   k > 0 ? 1u : 0u);
         }
         umma_commit(dp_full);
+        FB_TSET(tm);
         mbar_wait(p_full, ph, abort_flag, args.status, kTimeoutLocalFlag);
+        FB_TADD(5, tm);
         tc_fence_after();
         const uint32_t acc = it > 0 ? 1u : 0u;
         // dV += P^T dO   (A = P read MN-major: M = kv, K = q rows; B = dO read MN-major)
@@ -340,7 +370,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       const bool need_mask = (args.causal && it_q == jt) || (kv0 + 128 > seq_len) || (it_q * 128 + 128 > seq_len);
       const unsigned long long drop_row = dropout_row_counter(b, args.hq, head, args.seq_len, q_idx);
+      FB_T0(ts);
       mbar_wait(s_full, ph, abort_flag, args.status, kTimeoutTmemFull);
+      if (threadIdx.x == 64) {
+        FB_TADD(6, ts);
+        FB_TCOUNT(15);
+      }
+      FB_TSET(ts);
       tc_fence_after();
       if (it > 0) {
         // the P tile staged the first half of the previous step's dQ: that bulk reduce (the older of the two
@@ -348,6 +384,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (threadIdx.x == 64) tma_store_wait_read<1>();
         named_barrier(1, kFbSoftmaxThreads);
       }
+      if (threadIdx.x == 64) FB_TADD(11, ts);
       uint8_t* prow = sP + row * 128;
       uint8_t* dsrow = sDS + row * 128;
       const int row7 = row & 7;
@@ -373,7 +410,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(p_full);                // dV = P^T dO may start
+      FB_T0(t2);
       mbar_wait(dp_full, ph, abort_flag, args.status, kTimeoutTmemFull);
+      if (threadIdx.x == 64) FB_TADD(13, t2);
       tc_fence_after();
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
@@ -391,6 +430,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(pds_full);
+      if (threadIdx.x == 64) FB_TADD(7, ts);
+      FB_TSET(ts);
       // drain dQ: TMEM -> fp32 staging in the 128-byte swizzle of the tensor map, then one thread adds the tile to
       // the fp32 accumulator in global memory with bulk reduce-adds: whole 128-byte lines instead of one 16-byte
       // atomic per thread and row. The first 64 columns are staged in the P tile and the rest in this step's Q
@@ -401,6 +442,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_arrive(&stage_free[(it - 1) & 1]);
       }
       mbar_wait(dq_full, ph, abort_flag, args.status, kTimeoutTmemFull);
+      if (threadIdx.x == 64) FB_TADD(8, ts);
+      FB_TSET(ts);
       tc_fence_after();
       uint8_t* stage_hi = sQ + (it & 1) * L::tile_bytes;
 #pragma unroll 1
@@ -426,6 +469,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int c = 2; c < HD / 32; ++c) tma_reduce_add_3d(&tmDQ, stage_hi + (c - 2) * 16384, c * 32, head, t0);
         tma_store_commit();                              // (an empty group for head_dim 64)
       }
+      if (threadIdx.x == 64) FB_TADD(9, ts);
     }
     if (threadIdx.x == 64) tma_store_wait<0>();
     // ---- epilogue: dK, dV (lane == kv row). The last dq_full wait implies every MMA finished.
@@ -478,6 +522,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kFbTmemCols);
+  }
+  if (threadIdx.x == 0) {
+    FB_TADD(10, t_cta);
+    FB_TCOUNT(14);
   }
 }
 
@@ -547,6 +595,21 @@ static int launch_flash_bwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, cons
 }  // namespace icb
 
 using namespace icb;
+
+#ifdef ICB_FB_TRACE
+// Copies the 16 counters out (and clears them): [0] tma: q_empty, [1] tma: do_empty, [2] mma: q_full, [3] mma: do_full,
+// [4] mma: dq_empty, [5] mma: p_full, [6] softmax: s_full, [7] softmax: s_full .. dS published, [8] softmax: dq_full,
+// [9] softmax: dQ drain, [10] whole CTA, [11] of [7]: wait for the staging tile, [12] tma: stage_free,
+// [13] of [7]: dp_full, [14] CTAs, [15] steps.
+ICB_API int icb_flash_bwd_trace_read(unsigned long long* out, int reset) {
+  if (cudaMemcpyFromSymbol(out, icb::g_fb_trace, sizeof(unsigned long long) * 16) != cudaSuccess) return -1;
+  if (reset) {
+    unsigned long long z[16] = {0};
+    if (cudaMemcpyToSymbol(icb::g_fb_trace, z, sizeof(z)) != cudaSuccess) return -1;
+  }
+  return 0;
+}
+#endif
 
 // Scratch: delta fp32 [hq * T] and dq_acc fp32 [T * hq * hd] (zeroed here). dq/dk/dv point at the
 // first element of each gradient inside rows of dqkv_stride elements (packed layout or separate).

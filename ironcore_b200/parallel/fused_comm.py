@@ -134,6 +134,9 @@ class FusedTP:
             dist.all_reduce(have, op=dist.ReduceOp.MIN, group=group)
         have = self.world > 1 and int(have.item()) == 1
         self.nvls_ag = bool(have and (nvls_requested(self.world, "ag") if nvls is None else nvls))
+        # The gather push is bound by what one warp keeps in flight towards the link (about 8 KiB per 12 us), not
+        # by the link: the four epilogue warps of every CTA, idle until the first accumulator is ready, push too.
+        self.push_helpers = True
         self.nvls_rs = bool(have and (nvls_requested(self.world, "rs") if nvls is None else nvls))
         self.nvls = self.nvls_ag or self.nvls_rs
         self.norm_fusable = row_width_supported(width)
@@ -172,7 +175,7 @@ class FusedTP:
              self.rows, self.width, ptr(epoch_dev), ptr(b), ptr(out), ptr(bias), ptr(residual), int(n), b.stride(0),
              out.stride(0), ldr, int(a_major), int(b_major), dtype_code(self.dtype),
              1 if out_dtype == torch.float32 else 0, ptr(native.status_tensor(x_shard.device)), stream_ptr(), mc,
-             1 if pushed else 0)
+             1 if pushed else (2 if self.push_helpers else 0))
         epoch_dev.add_(1)
         self.last_gathered = gathered
         return out
