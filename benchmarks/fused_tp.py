@@ -27,8 +27,8 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--trace", action="store_true", help="per-CTA timestamps of the fused all-gather kernel")
     ap.add_argument("--cases", default="", help="comma-separated case names to run (default: all)")
-    ap.add_argument("--no-helpers", action="store_true",
-                    help="only the two copy warps of every CTA push the gather shard (default: the epilogue warps help)")
+    ap.add_argument("--helpers", action="store_true",
+                    help="the epilogue warps of every CTA push chunks of the gather shard too (default: two copy warps)")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -39,8 +39,8 @@ def main():
     t, d, f = args.tokens, args.width, args.ffn
     ws = FusedTP(t, d, dist.group.WORLD, num_slots=1)    # NVLS form when the fabric offers multicast
     ws_p2p = FusedTP(t, d, dist.group.WORLD, nvls=False, num_slots=1) if ws.nvls else ws   # plain P2P stores / loads
-    if args.no_helpers:
-        ws.push_helpers = ws_p2p.push_helpers = False
+    if args.helpers:
+        ws.push_helpers = ws_p2p.push_helpers = True
     rows = t // world
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     peak_tflops, link_gbs = 1414.0, 770.0
