@@ -72,16 +72,21 @@ def bench_elementwise(results, quick: bool):
     from ironcore_b200.ops import kernels
 
     flush = _flush_buffer()
-    m, d = 16384, 4096
-    x = torch.randn(m, d, device="cuda").bfloat16()
+    d = 4096
     w = torch.ones(d, device="cuda").bfloat16()
-    ms = time_cuda(lambda: kernels.norm_fwd(x, w, None, 1e-5, True), flush=flush)
-    results.append({"kernel": "rmsnorm_fwd", "ms": ms, "gbs": 2 * x.numel() * 2 / ms / 1e6})
-    print(json.dumps(results[-1]), flush=True)
-    y, h, mean, rstd = kernels.norm_fwd(x, w, None, 1e-5, True)
-    ms = time_cuda(lambda: kernels.norm_bwd(x, x, w, mean, rstd, True, False), flush=flush)
-    results.append({"kernel": "rmsnorm_bwd", "ms": ms, "gbs": 3 * x.numel() * 2 / ms / 1e6})
-    print(json.dumps(results[-1]), flush=True)
+    # two row counts: at 16384 rows (0.13 GB per tensor) a launch takes 50-80 us and the few microseconds of launch
+    # and event overhead are a tenth of it; 65536 rows show the kernel's own rate
+    for m in (16384, 65536):
+        x = torch.randn(m, d, device="cuda").bfloat16()
+        ms = time_cuda(lambda: kernels.norm_fwd(x, w, None, 1e-5, True), flush=flush)
+        results.append({"kernel": "rmsnorm_fwd", "rows": m, "d": d, "ms": ms, "gbs": 2 * x.numel() * 2 / ms / 1e6})
+        print(json.dumps(results[-1]), flush=True)
+        y, h, mean, rstd = kernels.norm_fwd(x, w, None, 1e-5, True)
+        ms = time_cuda(lambda: kernels.norm_bwd(x, x, w, mean, rstd, True, False), flush=flush)
+        results.append({"kernel": "rmsnorm_bwd", "rows": m, "d": d, "ms": ms, "gbs": 3 * x.numel() * 2 / ms / 1e6})
+        print(json.dumps(results[-1]), flush=True)
+        del x, y, h
+    m = 16384
     g = torch.randn(m, 2 * 11008, device="cuda").bfloat16()
     ms = time_cuda(lambda: kernels.glu_fwd(g, "swiglu"), flush=flush)
     results.append({"kernel": "swiglu_fwd", "ms": ms, "gbs": 1.5 * g.numel() * 2 / ms / 1e6})

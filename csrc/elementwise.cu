@@ -122,7 +122,7 @@ __device__ __forceinline__ float act_df(int kind, float x) {
 // KIND >= 0 fixes the activation at compile time (3 = silu: the SwiGLU of every Llama-style model); KIND = -1
 // reads it from the argument. Every thread owns two 8-element vectors half the problem apart and issues the
 // loads of both before it computes, which doubles the bytes each SM keeps in flight.
-template <bool BF16, int KIND>
+template <bool BF16, int KIND, bool LIMIT>
 __global__ void __launch_bounds__(256) glu_fwd_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
                                                       long long M, int F, int kind_arg, int gate_is_act,
                                                       const int* __restrict__ row_limit) {
@@ -133,23 +133,21 @@ __global__ void __launch_bounds__(256) glu_fwd_kernel(const uint16_t* __restrict
   const long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i0 >= half) return;
   // rows from *row_limit on hold nothing (unused capacity of a padded expert layout): zeros are written for them
-  const long long live = row_limit != nullptr ? (long long)*row_limit : M;
+  const long long live = LIMIT ? (long long)*row_limit : M;
   const long long i1 = i0 + half;
   const bool two = i1 < total;
   const long long m0 = i0 / vecs, m1 = two ? i1 / vecs : m0;
   const int v0 = (int)(i0 - m0 * vecs), v1 = two ? (int)(i1 - m1 * vecs) : v0;
-  const uint16_t* r0 = x + (size_t)m0 * 2 * F + v0 * 8;
-  const uint16_t* r1 = x + (size_t)m1 * 2 * F + v1 * 8;
+  // dead rows are not read: their loads go to row 0 instead (always inside the buffer), unconditionally, so that
+  // the four loads are issued back to back; the select below discards what they return
+  const bool live0 = !LIMIT || m0 < live, live1 = two && (!LIMIT || m1 < live);
+  const uint16_t* r0 = x + (size_t)(live0 ? m0 : 0) * 2 * F + v0 * 8;
+  const uint16_t* r1 = x + (size_t)(live1 ? m1 : 0) * 2 * F + v1 * 8;
   float f0[8], g0[8], f1[8], g1[8], o[8];
-  const bool live0 = m0 < live, live1 = two && m1 < live;
-  if (live0) {
-    ld8<BF16>(r0, f0);
-    ld8<BF16>(r0 + F, g0);
-  }
-  if (live1) {
-    ld8<BF16>(r1, f1);
-    ld8<BF16>(r1 + F, g1);
-  }
+  ld8<BF16>(r0, f0);
+  ld8<BF16>(r0 + F, g0);
+  ld8<BF16>(r1, f1);
+  ld8<BF16>(r1 + F, g1);
 #pragma unroll
   for (int j = 0; j < 8; ++j)
     o[j] = !live0 ? 0.f : (gate_is_act ? f0[j] * act_f(kind, g0[j]) : act_f(kind, f0[j]) * g0[j]);
@@ -161,12 +159,12 @@ __global__ void __launch_bounds__(256) glu_fwd_kernel(const uint16_t* __restrict
     st8<BF16>(y + (size_t)m1 * F + v1 * 8, o);
   }
 }
-template <bool BF16, int KIND>
+template <bool BF16, int KIND, bool LIMIT>
 __global__ void __launch_bounds__(256) glu_bwd_kernel(const uint16_t* __restrict__ dy, const uint16_t* __restrict__ x,
                                                       uint16_t* __restrict__ dx, long long M, int F, int kind_arg,
                                                       int gate_is_act, const int* __restrict__ row_limit) {
   const int kind = KIND >= 0 ? KIND : kind_arg;
-  const long long live = row_limit != nullptr ? (long long)*row_limit : M;
+  const long long live = LIMIT ? (long long)*row_limit : M;
   const int vecs = F >> 3;
   const long long total = M * vecs;
   const long long half = (total + 1) >> 1;
@@ -182,17 +180,16 @@ __global__ void __launch_bounds__(256) glu_bwd_kernel(const uint16_t* __restrict
     const long long idx = (u == 0 || n == 2) ? (u == 0 ? i0 : i1) : i0;
     mm[u] = idx / vecs;
     vv[u] = (int)(idx - mm[u] * vecs);
-    if (mm[u] < live) {
-      ld8<BF16>(x + (size_t)mm[u] * 2 * F + vv[u] * 8, f[u]);
-      ld8<BF16>(x + (size_t)mm[u] * 2 * F + F + vv[u] * 8, g[u]);
-      ld8<BF16>(dy + (size_t)mm[u] * F + vv[u] * 8, d[u]);
-    }
+    const long long src = (!LIMIT || mm[u] < live) ? mm[u] : 0;   // dead rows: loads from row 0, discarded
+    ld8<BF16>(x + (size_t)src * 2 * F + vv[u] * 8, f[u]);
+    ld8<BF16>(x + (size_t)src * 2 * F + F + vv[u] * 8, g[u]);
+    ld8<BF16>(dy + (size_t)src * F + vv[u] * 8, d[u]);
   }
 #pragma unroll
   for (int u = 0; u < 2; ++u) {
     if (u < n) {
       float df[8], dg[8];
-      const bool dead = mm[u] >= live;
+      const bool dead = LIMIT && mm[u] >= live;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         if (dead) {
@@ -591,13 +588,22 @@ ICB_API int icb_glu_fwd(const void* x, void* y, long long M, int F, int kind, in
   const int th = 256;
   const int bl = (int)((n + th - 1) / th);
   const bool silu = kind == 3 && !gate_is_act;
+#define ICB_GLU_FWD(B16, K, L) \
+  glu_fwd_kernel<B16, K, L><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(x), ICB_U16M(y), M, F, kind, gate_is_act, row_limit)
+#define ICB_GLU_FWD_L(B16, K)            \
+  do {                                   \
+    if (row_limit != nullptr) ICB_GLU_FWD(B16, K, true); \
+    else ICB_GLU_FWD(B16, K, false);     \
+  } while (0)
   if (dtype == kBF16) {
-    if (silu) glu_fwd_kernel<true, 3><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(x), ICB_U16M(y), M, F, kind, 0, row_limit);
-    else glu_fwd_kernel<true, -1><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(x), ICB_U16M(y), M, F, kind, gate_is_act, row_limit);
+    if (silu) ICB_GLU_FWD_L(true, 3);
+    else ICB_GLU_FWD_L(true, -1);
   } else {
-    if (silu) glu_fwd_kernel<false, 3><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(x), ICB_U16M(y), M, F, kind, 0, row_limit);
-    else glu_fwd_kernel<false, -1><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(x), ICB_U16M(y), M, F, kind, gate_is_act, row_limit);
+    if (silu) ICB_GLU_FWD_L(false, 3);
+    else ICB_GLU_FWD_L(false, -1);
   }
+#undef ICB_GLU_FWD_L
+#undef ICB_GLU_FWD
   return check_launch("glu_fwd");
 }
 ICB_API int icb_glu_bwd(const void* dy, const void* x, void* dx, long long M, int F, int kind, int gate_is_act,
@@ -608,13 +614,23 @@ ICB_API int icb_glu_bwd(const void* dy, const void* x, void* dx, long long M, in
   const int th = 256;
   const int bl = (int)((n + th - 1) / th);
   const bool silu = kind == 3 && !gate_is_act;
+#define ICB_GLU_BWD(B16, K, L)                                                                                     \
+  glu_bwd_kernel<B16, K, L><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(dy), ICB_U16(x), ICB_U16M(dx), M, F, kind,      \
+                                                           gate_is_act, row_limit)
+#define ICB_GLU_BWD_L(B16, K)            \
+  do {                                   \
+    if (row_limit != nullptr) ICB_GLU_BWD(B16, K, true); \
+    else ICB_GLU_BWD(B16, K, false);     \
+  } while (0)
   if (dtype == kBF16) {
-    if (silu) glu_bwd_kernel<true, 3><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(dy), ICB_U16(x), ICB_U16M(dx), M, F, kind, 0, row_limit);
-    else glu_bwd_kernel<true, -1><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(dy), ICB_U16(x), ICB_U16M(dx), M, F, kind, gate_is_act, row_limit);
+    if (silu) ICB_GLU_BWD_L(true, 3);
+    else ICB_GLU_BWD_L(true, -1);
   } else {
-    if (silu) glu_bwd_kernel<false, 3><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(dy), ICB_U16(x), ICB_U16M(dx), M, F, kind, 0, row_limit);
-    else glu_bwd_kernel<false, -1><<<bl, th, 0, ICB_ST(stream)>>>(ICB_U16(dy), ICB_U16(x), ICB_U16M(dx), M, F, kind, gate_is_act, row_limit);
+    if (silu) ICB_GLU_BWD_L(false, 3);
+    else ICB_GLU_BWD_L(false, -1);
   }
+#undef ICB_GLU_BWD_L
+#undef ICB_GLU_BWD
   return check_launch("glu_bwd");
 }
 // out[M, N] (16-bit, pitch ldo) = acc[M, N] (fp32, contiguous) (+ residual[M, N], 16-bit, pitch ldr): the closing

@@ -195,6 +195,14 @@ __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* tm, const v
                "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
+// Untiled bulk copy global -> shared memory (this CTA), completion counted in bytes on an mbarrier. Both addresses
+// and the size must be multiples of 16 bytes.
+__device__ __forceinline__ void bulk_load_g2s(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst_smem)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {

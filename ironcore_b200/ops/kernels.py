@@ -249,6 +249,7 @@ def norm_fwd(x, weight, bias, eps: float, rms: bool, residual=None, w_offset: fl
     call(
         "icb_norm_fwd", ptr(x2), ptr(r2), ptr(weight), ptr(bias), ptr(y), ptr(h), ptr(mean), ptr(rstd),
         m, d, float(eps), float(w_offset), 1 if rms else 0, dtype_code(x.dtype), stream_ptr(),
+        ptr(native.status_tensor(x.device)),
     )
     return y.view(x.shape), (h.view(x.shape) if h is not None else x), mean, rstd
 
@@ -268,6 +269,7 @@ def norm_bwd(dy, x, weight, mean, rstd, rms: bool, has_bias: bool, dres_in=None,
     call(
         "icb_norm_bwd", ptr(dy2), ptr(x2), ptr(weight), ptr(mean), ptr(rstd), ptr(dr2), ptr(dx), ptr(dw), ptr(db),
         ptr(scratch), m, d, float(w_offset), 1 if rms else 0, dtype_code(x.dtype), 1, 0, stream_ptr(),
+        ptr(native.status_tensor(x.device)),
     )
     return dx.view(x.shape), dw, db
 

@@ -27,8 +27,8 @@ F = C.c_float
 _SIGNATURES = {
     "icb_gemm": [P, P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, I, I, P, L, P, I, P],
     "icb_norm_bwd_parts": [I],
-    "icb_norm_fwd": [P, P, P, P, P, P, P, P, I, I, F, F, I, I, P],
-    "icb_norm_bwd": [P, P, P, P, P, P, P, P, P, P, I, I, F, I, I, I, I, P],
+    "icb_norm_fwd": [P, P, P, P, P, P, P, P, I, I, F, F, I, I, P, P],
+    "icb_norm_bwd": [P, P, P, P, P, P, P, P, P, P, I, I, F, I, I, I, I, P, P],
     "icb_rope": [P, P, P, I, I, I, L, L, I, F, F, I, I, I, I, P, I],
     "icb_glu_fwd": [P, P, L, I, I, I, I, P, P],
     "icb_glu_bwd": [P, P, P, L, I, I, I, I, P, P],
