@@ -195,6 +195,8 @@ class ModelConfig(BaseConfig):
     parallel_block: Optional[bool] = opt(None, "attention and MLP read the same norm output (None = family default; Phi)")
     embed_scale: Optional[float] = opt(None, "multiply embeddings (None = family default; Gemma: sqrt(d_model))")
     lm_head_bias: Optional[bool] = opt(None, "bias on the LM head (None = family default; Phi)")
+    lm_head_chunk: int = opt(0, "vocabulary columns per step of the chunked LM head + cross entropy (multiple of "
+                                "128; 0 = materialise the logits, chunked by itself without gradients above 64 k)")
     activation_type: str = opt("gelu", "relu|gelu|gelu_tanh|silu|swiglu|geglu|reglu|glu")
     seq_len_q: Optional[int] = opt(None, "unused")
     seq_len_kv: Optional[int] = opt(None, "unused")
@@ -313,6 +315,8 @@ class ParallelConfig(BaseConfig):
     nvls: Literal["auto", "on", "off"] = opt("auto", "NVSwitch multicast (multimem) forms of the in-kernel collectives")
     grad_bucket_mb: int = opt(64, "gradient reduction bucket size")
     use_fsdp: bool = opt(False, "fully sharded data parallel")
+    fsdp_fused_gather: bool = opt(False, "FSDP parameter gathers as P2P / NVSwitch-multicast kernels into "
+                                         "symmetric slots instead of NCCL all-gathers")
     fsdp_offload_params: bool = opt(False, "keep FSDP shards in pinned host memory")
     fsdp_mixed_precision: Literal["fp16", "float16", "bf16", "bfloat16", "fp32", "float32", "mixed"] = opt(
         "mixed", "FSDP reduce precision")

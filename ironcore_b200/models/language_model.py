@@ -223,6 +223,40 @@ class LanguageModel(BaseModule):
             x = C.gather_from_sp(x, self.tp_group) if self.sequence_parallel else C.copy_to_tp(x, self.tp_group)
         return linear_t(x, self.embedding.word_embeddings.weight)
 
+    def _head_chunk(self) -> int:
+        """Vocabulary columns per step of the chunked LM head + cross entropy, or 0 for materialised logits:
+        ``model.lm_head_chunk`` when set; without gradients (reference / old-policy log-probs, evaluation) the
+        chunked form is chosen by itself for local vocabularies above 64 k entries, where the [tokens, vocab]
+        matrix is the largest tensor of the pass and nothing needs it afterwards."""
+        chunk = int(getattr(self.config.model, "lm_head_chunk", 0) or 0)
+        if chunk > 0:
+            return chunk
+        v_local = self.padded_vocab_size // self.tp_size
+        if not torch.is_grad_enabled() and v_local > 65536:
+            return 8192
+        return 0
+
+    def per_token_loss(self, x: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """Cross entropy of every token of the normalised final hidden states ``x`` (token-major, the
+        sequence-parallel shard when enabled) against ``targets`` [T] (global ids, negative = ignored), fp32 [T].
+        Chunked over the vocabulary when ``_head_chunk`` says so, through the logits otherwise."""
+        chunk = self._head_chunk()
+        if chunk <= 0:
+            logits = self.logits_from_hidden(x)
+            return vocab_parallel_cross_entropy(logits, targets, self.vocab_size, tp_group=self.tp_group)
+        if self.tp_size > 1:
+            x = C.gather_from_sp(x, self.tp_group) if self.sequence_parallel else C.copy_to_tp(x, self.tp_group)
+        v_local = self.padded_vocab_size // self.tp_size
+        start = mesh.get_tensor_model_parallel_rank() * v_local
+        valid = max(0, min(v_local, self.vocab_size - start))
+        if self.untied:
+            weight, bias, tied = self.output_layer.weight, self.output_layer.bias, False
+        else:
+            weight, bias, tied = self.embedding.word_embeddings.weight, None, True
+        return OF.chunked_head_cross_entropy(x, weight, targets, tied=tied, bias=bias, vocab_start=start,
+                                             vocab_valid=valid, group=self.tp_group if self.tp_size > 1 else None,
+                                             chunk=chunk)
+
     def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None,
                 position_ids: Optional[torch.Tensor] = None, cu_seqlens: Optional[torch.Tensor] = None,
                 loss_mask: Optional[torch.Tensor] = None, attn_mask: Optional[torch.Tensor] = None):
@@ -233,11 +267,9 @@ class LanguageModel(BaseModule):
             labels = labels.to(dev, non_blocking=True)
         b, s = input_ids.shape
         x, aux = self.hidden_states(input_ids, position_ids, cu_seqlens, attn_mask)
-        logits = self.logits_from_hidden(x)
         if labels is None:
-            return logits.view(b, s, -1)
-        per_token = vocab_parallel_cross_entropy(logits, labels.reshape(-1).clamp_min(-1), self.vocab_size,
-                                                 tp_group=self.tp_group)
+            return self.logits_from_hidden(x).view(b, s, -1)
+        per_token = self.per_token_loss(x, labels.reshape(-1).clamp_min(-1))
         mask = self._loss_mask(input_ids, labels, loss_mask)
         loss = self.loss_fn(per_token.view(b, s), mask)
         if aux is not None:
@@ -252,9 +284,7 @@ class LanguageModel(BaseModule):
         input_ids, labels = input_ids.to(dev), labels.to(dev)
         b, s = input_ids.shape
         x, _aux = self.hidden_states(input_ids)
-        logits = self.logits_from_hidden(x)
-        ce = vocab_parallel_cross_entropy(logits, labels.reshape(-1).clamp_min(-1), self.vocab_size,
-                                          tp_group=self.tp_group)
+        ce = self.per_token_loss(x, labels.reshape(-1).clamp_min(-1))
         return -ce.view(b, s)
 
     def link_fused_norm_gather(self) -> int:

@@ -302,15 +302,164 @@ def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, *, vocab_start: i
         from ..parallel.collectives import all_reduce_sum
 
         sumexp = all_reduce_sum(torch.exp(lf - gmax[:, None]).sum(-1), group)
-        tgt = lf.gather(1, local_t.clamp(0, v - 1)[:, None]).squeeze(1) * mine.to(lf.dtype)
+        tgt = lf.gather(1, local_t.clamp(0, max(vv - 1, 0))[:, None]).squeeze(1).masked_fill(~mine, 0.0)
         tgt = all_reduce_sum(tgt, group)
         loss = torch.log(sumexp) + gmax - tgt
     else:
         gmax = rmax.detach()
         sumexp = torch.exp(lf - gmax[:, None]).sum(-1)
-        tgt = lf.gather(1, local_t.clamp(0, v - 1)[:, None]).squeeze(1) * mine.to(lf.dtype)
+        tgt = lf.gather(1, local_t.clamp(0, max(vv - 1, 0))[:, None]).squeeze(1).masked_fill(~mine, 0.0)
         loss = torch.log(sumexp) + gmax - tgt
     return loss.masked_fill(targets < 0, 0.0)
+
+
+# --------------------------------------------------------------------------- LM head + cross entropy, chunked
+def _head_chunk_logits(x, weight, bias, tied, c0, c1, buf, native_path):
+    """logits of vocabulary columns [c0, c1): x [T, d] times the head's slice, into ``buf[:, :c1 - c0]``."""
+    n = c1 - c0
+    b = bias[c0:c1] if bias is not None else None
+    if native_path:
+        out = buf[:, :n]
+        if tied:     # weight [V, d]: rows are vocabulary entries
+            kernels.gemm(x, weight[c0:c1], a_major=0, b_major=0, m=x.shape[0], n=n, k=x.shape[1], out=out, bias=b)
+        else:        # weight [d, V]
+            kernels.gemm(x, weight[:, c0:c1], a_major=0, b_major=1, m=x.shape[0], n=n, k=x.shape[1], out=out, bias=b)
+        return out
+    w = weight[c0:c1].t() if tied else weight[:, c0:c1]
+    y = x @ w
+    return y + b if b is not None else y
+
+
+def _head_chunk_stats(logits, targets, start, valid, native_path):
+    """(row max, sum of exp(logit - max), target logit or 0) over the chunk's first ``valid`` columns; ``start`` is
+    the global id of its first column."""
+    if native_path:
+        return kernels.ce_stats(logits, targets, vocab_start=start, vocab_valid=valid)
+    lf = logits.float()[:, :valid]
+    cm = lf.max(dim=-1).values
+    cs = torch.exp(lf - cm[:, None]).sum(-1)
+    local = targets - start
+    mine = (local >= 0) & (local < valid)
+    ct = lf.gather(1, local.clamp(0, valid - 1)[:, None]).squeeze(1) * mine.to(lf.dtype)
+    return cm, cs, ct
+
+
+def _head_chunk_grad_(logits, targets, lse, gs, start, valid, native_path):
+    """d loss / d logits of the chunk: gs * (softmax - one_hot(target)); zero for padding columns."""
+    if native_path:
+        return kernels.ce_grad_(logits, targets, lse, gs, vocab_start=start, vocab_valid=valid)
+    lf = logits.float()
+    g = torch.exp(lf - lse[:, None])
+    g[:, valid:] = 0.0
+    local = targets - start
+    mine = (local >= 0) & (local < valid)
+    rows = torch.nonzero(mine).squeeze(1)
+    g[rows, local[rows]] -= 1.0
+    return (g * gs[:, None]).to(logits.dtype)
+
+
+class _ChunkedHeadCE(torch.autograd.Function):
+    """LM head and cross entropy over chunks of the (local) vocabulary. Logits exist only as one [T, chunk] block at a
+    time: the forward pass runs GEMM + row statistics per chunk and merges the statistics the way vocabulary shards
+    of a tensor-parallel group are merged; the backward pass recomputes a chunk's logits, turns them into their
+    gradient in place and feeds the dX and dW GEMMs from it. One more GEMM than the materialised form, no
+    [T, V] tensor."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, targets, tied, vocab_start, vocab_valid, group, chunk):
+        native_path = use_native(x)
+        t = x.shape[0]
+        v_local = weight.shape[0] if tied else weight.shape[1]
+        x = x.contiguous()
+        targets = targets.contiguous()
+        rmax = torch.full((t,), float("-inf"), dtype=torch.float32, device=x.device)
+        rsum = torch.zeros(t, dtype=torch.float32, device=x.device)
+        rtgt = torch.zeros(t, dtype=torch.float32, device=x.device)
+        buf = torch.empty((t, chunk), dtype=x.dtype, device=x.device) if native_path else None
+        for c0 in range(0, v_local, chunk):
+            c1 = min(c0 + chunk, v_local)
+            valid = max(0, min(c1 - c0, vocab_valid - c0))
+            if valid == 0:
+                break
+            logits = _head_chunk_logits(x, weight, bias, tied, c0, c1, buf, native_path)
+            cm, cs, ct = _head_chunk_stats(logits, targets, vocab_start + c0, valid, native_path)
+            new = torch.maximum(rmax, cm)
+            rsum = rsum * torch.exp(rmax - new) + cs * torch.exp(cm - new)
+            rtgt = rtgt + ct
+            rmax = new
+        if group is not None and torch.distributed.get_world_size(group) > 1:
+            import torch.distributed as dist
+
+            gmax = rmax.clone()
+            dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
+            packed = torch.stack([rsum * torch.exp(rmax - gmax), rtgt])
+            dist.all_reduce(packed, group=group)
+            rsum, rtgt, rmax = packed[0], packed[1], gmax
+        lse = rmax + torch.log(rsum)
+        loss = (lse - rtgt).masked_fill(targets < 0, 0.0)
+        ctx.save_for_backward(x, weight, bias if bias is not None else lse, targets, lse)
+        ctx.meta = (tied, vocab_start, vocab_valid, chunk, bias is not None, native_path)
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        x, weight, bias, targets, lse = ctx.saved_tensors
+        tied, vocab_start, vocab_valid, chunk, has_bias, native_path = ctx.meta
+        bias = bias if has_bias else None
+        t, d = x.shape
+        v_local = weight.shape[0] if tied else weight.shape[1]
+        gs = dloss.float().masked_fill(targets < 0, 0.0).contiguous()
+        need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        main_grad = getattr(weight, "main_grad", None) if need_dw else None
+        dx_acc = torch.zeros((t, d), dtype=torch.float32, device=x.device) if need_dx else None
+        dw = torch.zeros_like(weight) if (need_dw and main_grad is None) else None
+        db = torch.zeros_like(bias) if (has_bias and ctx.needs_input_grad[2]) else None
+        buf = torch.empty((t, chunk), dtype=x.dtype, device=x.device) if native_path else None
+        for c0 in range(0, v_local, chunk):
+            c1 = min(c0 + chunk, v_local)
+            n = c1 - c0
+            valid = max(0, min(n, vocab_valid - c0))
+            if valid == 0:
+                break
+            logits = _head_chunk_logits(x, weight, bias, tied, c0, c1, buf, native_path)
+            dl = _head_chunk_grad_(logits, targets, lse, gs, vocab_start + c0, valid, native_path)
+            w_c = weight[c0:c1] if tied else weight[:, c0:c1]
+            if need_dx:
+                if native_path:     # dx += dl @ W_c (tied: [n, d]) or dl @ W_c^T (untied: [d, n])
+                    kernels.gemm(dl, w_c, a_major=0, b_major=1 if tied else 0, m=t, n=d, k=n, out=dx_acc,
+                                 residual=dx_acc, out_dtype=torch.float32)
+                else:
+                    dx_acc += (dl.float() @ (w_c.float() if tied else w_c.float().t()))
+            if need_dw:
+                target = main_grad if main_grad is not None else dw
+                tgt_c = target[c0:c1] if tied else target[:, c0:c1]
+                if native_path:     # tied: dW_c [n, d] = dl^T x; untied: dW_c [d, n] = x^T dl
+                    a, b_ = (dl, x) if tied else (x, dl)
+                    kernels.gemm(a, b_, a_major=1, b_major=1, m=tgt_c.shape[0], n=tgt_c.shape[1], k=t, out=tgt_c,
+                                 residual=tgt_c if main_grad is not None else None, out_dtype=tgt_c.dtype)
+                else:
+                    upd = (dl.float().t() @ x.float()) if tied else (x.float().t() @ dl.float())
+                    tgt_c += upd.to(tgt_c.dtype)
+            if db is not None:
+                db[c0:c1] = dl.sum(0, dtype=torch.float32).to(db.dtype)
+        if main_grad is not None:
+            weight.grad_ready = True
+        dx = dx_acc.to(x.dtype) if need_dx else None
+        return dx, dw, db, None, None, None, None, None, None
+
+
+def chunked_head_cross_entropy(x: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, *, tied: bool,
+                               bias: Optional[torch.Tensor] = None, vocab_start: int = 0,
+                               vocab_valid: Optional[int] = None, group=None, chunk: int = 8192) -> torch.Tensor:
+    """Per-token cross entropy of ``x`` [T, d] under the LM head ``weight`` ([V_local, d] when ``tied``: the
+    embedding table; [d, V_local] otherwise) without the [T, V_local] logits: see ``_ChunkedHeadCE``. ``targets``
+    [T] are global ids (negative = ignored); ``vocab_start`` is the first id of this rank's shard, columns from
+    ``vocab_valid`` on are padding; ``chunk`` (a multiple of 128) columns are live at a time. Returns fp32 [T]."""
+    v_local = weight.shape[0] if tied else weight.shape[1]
+    if chunk % 128 or chunk <= 0:
+        raise ValueError("chunk must be a positive multiple of 128")
+    vv = v_local if vocab_valid is None else vocab_valid
+    return _ChunkedHeadCE.apply(x, weight, bias, targets, bool(tied), int(vocab_start), int(vv), group, int(chunk))
 
 
 # --------------------------------------------------------------------------- rope + attention

@@ -114,6 +114,13 @@ class FSDPUnit:
         self._flat_grad: Optional[torch.Tensor] = None
         self._pending = 0
         self.gather_event = None
+        # in-kernel parameter gather (``parallel.fsdp_fused_gather``): set by ``FullyShardedModel``
+        self.pool = None            # FsdpCommPool shared by all units
+        self.pool_slot = 0          # this unit's slot: fixed, so its parameters always live at the same address
+        self.pool_stream = None     # stream the gather kernels run on
+        self.use_pool = False
+        self._pool_full: Optional[torch.Tensor] = None
+        self._points_at = full.data_ptr()
         if self.shard_params:
             self.release()
 
@@ -123,14 +130,45 @@ class FSDPUnit:
             return self.shard_host.to(self.device, non_blocking=True)
         return self.shard
 
+    def _point_params(self, buf: torch.Tensor):
+        if self._points_at == buf.data_ptr():
+            return
+        for p, o in zip(self.params, self.offsets):
+            p.data = buf[o:o + p.numel()].view(p.shape)
+        self._points_at = buf.data_ptr()
+
+    def _gather_in_kernel(self, async_op: bool):
+        """Gather into this unit's slot of the symmetric pool with the P2P / multicast kernel, on the pool's
+        stream. The kernel starts once everything the compute stream has been given so far is done (the slot's
+        previous tenant included) and runs beside what the compute stream is given next."""
+        comm = self.pool_stream
+        comm.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(comm):
+            shard = self._local_shard()
+            full = self.pool.gather(shard, self.pool_slot)
+            event = torch.cuda.Event()
+            event.record(comm)
+        self._gather_event = event
+        self._gather_src = shard
+        self._pool_full = full
+        self._point_params(full)
+        self.materialised = True
+        if not async_op:
+            self.wait_gather()
+
     def gather(self, async_op: bool = False):
         """Re-materialise the full buffer. With ``async_op`` the all-gather is only enqueued (it runs on the
         communication stream of the backend, overlapping whatever the compute stream does next); ``wait_gather``
         makes the compute stream wait for it right before the unit's parameters are used."""
         if self.materialised or not self.shard_params:
             return
+        if self.use_pool and self.pool is not None:
+            self._gather_in_kernel(async_op)
+            return
         nbytes = self.total * self.full.element_size()
         self.full.untyped_storage().resize_(nbytes)
+        if self.pool is not None:
+            self._point_params(self.full)     # the parameters may still be views of a pool slot
         shard = self._local_shard()
         if self.device.type == "cpu":
             parts = [torch.empty_like(shard) for _ in range(self.dp)]
@@ -143,6 +181,11 @@ class FSDPUnit:
         self.materialised = True
 
     def wait_gather(self):
+        event = getattr(self, "_gather_event", None)
+        if event is not None:
+            torch.cuda.current_stream().wait_event(event)
+            self._gather_event = None
+            self._gather_src = None
         work = getattr(self, "_gather_work", None)
         if work is not None:
             work.wait()
@@ -153,7 +196,11 @@ class FSDPUnit:
         if not self.shard_params or not self.materialised:
             return
         self.wait_gather()
-        self.full.untyped_storage().resize_(0)
+        if self._pool_full is not None:
+            # the slot keeps the bytes until its next tenant's gather, which waits for this stream first
+            self._pool_full = None
+        else:
+            self.full.untyped_storage().resize_(0)
         self.materialised = False
 
     def write_back_shard(self, new_shard: torch.Tensor):
@@ -270,6 +317,29 @@ class FullyShardedModel(nn.Module):
                 if prm.requires_grad:
                     prm.register_post_accumulate_grad_hook(self._grad_hook(u, idx))
         self.comm_stream = torch.cuda.Stream() if torch.cuda.is_available() else None
+        self.pool = None
+        if getattr(p, "fsdp_fused_gather", False) and shard and self.dp > 1 and self.comm_stream is not None \
+                and self.units[0].device.type == "cuda":
+            self._attach_gather_pool(dtype, reduce_dtype)
+
+    def _attach_gather_pool(self, dtype, reduce_dtype):
+        """Parameter gathers as P2P / NVSwitch-multicast kernels (``csrc/fsdp_comm.cu``) into three symmetric
+        slots: one for the root unit, two that the layers alternate between (a layer's slot is fixed, so its
+        parameters keep their addresses from gather to gather)."""
+        from .fsdp_comm import FsdpCommPool
+        from .symmetric import symmetric_memory_available
+
+        if not symmetric_memory_available() or dtype not in (torch.bfloat16, torch.float16):
+            return
+        quantum = 8 * self.dp
+        biggest = max(u.total for u in self.units)
+        biggest = (biggest + quantum - 1) // quantum * quantum
+        if any(u.total % quantum for u in self.units):
+            return
+        self.pool = FsdpCommPool(self.group, biggest, dtype, reduce_dtype, slots=3, flat_slots=0)
+        for i, u in enumerate(self.units):
+            u.pool, u.pool_stream, u.use_pool = self.pool, self.comm_stream, True
+            u.pool_slot = 0 if i == 0 else 1 + (i % 2)
 
     # ---- hooks ----
     def _prefetch(self, idx: int):
@@ -328,14 +398,19 @@ class FullyShardedModel(nn.Module):
         return self.module(*a, **k)
 
     def gather_all(self):
+        """Every unit materialised at once (state dicts): through private buffers, never the shared slots."""
         for u in self.units:
+            if u.use_pool:
+                u.release()
+                u.use_pool = False
             u.gather()
             u.wait_gather()
 
     def release_all(self):
         for u in self.units:
-            if u is not self.root_unit:
+            if u is not self.root_unit or u.pool is not None:
                 u.release()
+            u.use_pool = u.pool is not None
 
     def canonical_state_dict(self):
         self.gather_all()

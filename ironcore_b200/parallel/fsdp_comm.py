@@ -30,7 +30,7 @@ native.register("icb_fsdp_reduce_scatter", [P, P, P, L, F, I, I, I, P, P, P, P, 
 
 class FsdpCommPool:
     def __init__(self, group, max_unit_elems: int, param_dtype=torch.bfloat16, reduce_dtype=torch.float32,
-                 slots: int = 2):
+                 slots: int = 2, flat_slots=None):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -42,14 +42,16 @@ class FsdpCommPool:
         res = torch.empty((), dtype=reduce_dtype).element_size()
         self._full_bytes = (max_unit_elems * pes + 255) // 256 * 256
         self._flat_bytes = (max_unit_elems * res + 255) // 256 * 256
+        flat_slots = slots if flat_slots is None else flat_slots     # 0: gather only, no gradient buffers
+        self.flat_slots = flat_slots
         self._flat_off = slots * self._full_bytes
-        self._ctr_off = self._flat_off + slots * self._flat_bytes
+        self._ctr_off = self._flat_off + flat_slots * self._flat_bytes
         self.buf = SymmetricBuffer(self._ctr_off + 256, group)
         dev = self.buf.local.device
         self.ctr = self.buf.view(self._ctr_off, (4,), torch.int32)
         self.peer_ctr = self.buf.peer_table(self._ctr_off)
         self.peer_full = [self.buf.peer_table(s * self._full_bytes) for s in range(slots)]
-        self.peer_flat = [self.buf.peer_table(self._flat_off + s * self._flat_bytes) for s in range(slots)]
+        self.peer_flat = [self.buf.peer_table(self._flat_off + s * self._flat_bytes) for s in range(flat_slots)]
         self.gather_epoch = torch.zeros(1, dtype=torch.int32, device=dev)
         self.reduce_epoch = torch.zeros(1, dtype=torch.int32, device=dev)
         self.ticket = torch.zeros(2, dtype=torch.int32, device=dev)

@@ -190,3 +190,54 @@ def test_router_kernel_matches_eager(experts, top_k, normalize):
     dw_ref = dl.t() @ x.detach().float()
     assert (x.grad.float() - dx_ref).abs().max().item() < 2e-2 * max(1.0, dx_ref.abs().max().item())
     assert (wr.grad.float() - dw_ref).abs().max().item() < 2e-2 * max(1.0, dw_ref.abs().max().item())
+
+
+@pytest.mark.parametrize("tied", [True, False])
+def test_chunked_head_cross_entropy_native(tied):
+    """LM head + cross entropy over vocabulary chunks on the kernels (GEMM into a [T, chunk] block, row statistics,
+    in-place gradient, dX / dW GEMMs accumulating in fp32) against the materialised-logits loss in fp32: values and
+    gradients; padding columns, ignored and off-shard targets, a weight with a main_grad buffer."""
+    from ironcore_b200.ops import functional as OF
+    from ironcore_b200.ops import native
+
+    torch.manual_seed(12)
+    t, d, v_local, valid, start, chunk = 300, 256, 1536, 1500, 3072, 512
+    targets = torch.randint(start - 200, start + valid + 200, (t,), device="cuda")
+    targets[7] = -1
+    shape = (v_local, d) if tied else (d, v_local)
+    x = torch.randn(t, d, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(*shape, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    b = None if tied else (torch.randn(v_local, device="cuda") * 0.1).bfloat16().requires_grad_(True)
+    xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    bf = b.detach().float().requires_grad_(True) if b is not None else None
+    logits = xf @ (wf.t() if tied else wf)
+    if bf is not None:
+        logits = logits + bf
+    ref = OF.cross_entropy(logits, targets, vocab_start=start, vocab_valid=valid)
+    got = OF.chunked_head_cross_entropy(x, w, targets, tied=tied, bias=b, vocab_start=start, vocab_valid=valid,
+                                        chunk=chunk)
+    assert type(got.grad_fn).__name__.startswith("_ChunkedHeadCE")
+    assert (got - ref).abs().max().item() < 3e-2
+    gw = torch.rand(t, device="cuda")
+    (ref * gw).sum().backward()
+    (got * gw).sum().backward()
+    torch.cuda.synchronize()
+    native.check_status()
+    for name, a, r in (("dx", x.grad, xf.grad), ("dw", w.grad, wf.grad)) + ((("db", b.grad, bf.grad),) if b is not None else ()):
+        scale = r.abs().max().item()
+        assert (a.float() - r).abs().max().item() < 2e-2 * max(scale, 1.0), (name, scale)
+    # accumulation into the optimizer's fp32 gradient buffer
+    w2 = w.detach().clone().requires_grad_(True)
+    w2.main_grad = torch.ones(*shape, device="cuda")
+    got2 = OF.chunked_head_cross_entropy(x.detach(), w2, targets, tied=tied, bias=None if b is None else b.detach(),
+                                         vocab_start=start, vocab_valid=valid, chunk=chunk)
+    (got2 * gw).sum().backward()
+    torch.cuda.synchronize()
+    assert w2.grad is None and w2.grad_ready
+    assert (w2.main_grad - 1.0 - wf.grad).abs().max().item() < 2e-2 * max(wf.grad.abs().max().item(), 1.0)
+    # without gradients nothing of size [t, v_local] is allocated
+    torch.cuda.reset_peak_memory_stats()
+    before = torch.cuda.memory_allocated()
+    with torch.no_grad():
+        OF.chunked_head_cross_entropy(x, w, targets, tied=tied, bias=b, vocab_start=start, vocab_valid=valid, chunk=chunk)
+    assert torch.cuda.max_memory_allocated() - before < t * v_local * 2

@@ -324,11 +324,12 @@ def check_fsdp2_matches_dp2(rank, world):
     """Full-shard FSDP on 2 GPUs (asynchronous parameter gathers and gradient reduce-scatters) against the
     replicated data-parallel run, with Adam and with Muon."""
     from ironcore_b200.config import validate_config
+    from ironcore_b200.ops import native
     from ironcore_b200.parallel import mesh
     from ironcore_b200.trainer import Trainer
     from helpers import tiny_config
 
-    def run(fsdp, optimizer):
+    def run(fsdp, optimizer, fused_gather=False):
         mesh.destroy_model_parallel()
         cfg = tiny_config("llama", d_model=256, d_ffn=512, num_layers=3, num_attention_heads=4, head_dim=64,
                           max_seq_len=128, max_position_embeddings=128, precision="bf16", vocab_size=1024)
@@ -336,22 +337,28 @@ def check_fsdp2_matches_dp2(rank, world):
         cfg.model(reset_position_ids=False, reset_attention_mask=False)
         cfg.trainer(micro_batch_size=2, train_batch_size=8, gradient_accumulation_steps=None,
                     tensor_model_parallel_size=1)
-        cfg.parallel(world_size=world, rank=rank, local_rank=rank, use_fsdp=fsdp, fsdp_mixed_precision="mixed")
+        cfg.parallel(world_size=world, rank=rank, local_rank=rank, use_fsdp=fsdp, fsdp_mixed_precision="mixed",
+                     fsdp_fused_gather=fused_gather)
         cfg.optim(optimizer=optimizer, muon_lr=0.02, max_lr=1e-3, clip_grad=1.0)
         cfg.operation.train_steps = 3
         validate_config(cfg)
         tr = Trainer(cfg)
+        if fused_gather:
+            assert tr.model.pool is not None, "the in-kernel gather was asked for and must be in use"
         losses = [float(tr.train_step(s)[0]) for s in range(3)]
         sd = {k: v.float().clone() for k, v in tr.model.canonical_state_dict().items()}
+        losses.append(float(tr.train_step(3)[0]))         # and on after a state dict went through private buffers
+        native.check_status()
         return losses, sd
 
     for optimizer in ("adam", "muon"):
         la, sa = run(False, optimizer)
-        lb, sb = run(True, optimizer)
-        for x, y in zip(la, lb):
-            assert abs(x - y) < 3e-2, (optimizer, la, lb)
-        worst = max((sa[k] - sb[k]).abs().max().item() for k in sa)
-        assert worst < 3e-2, (optimizer, worst)
+        for fused_gather in (False, True):
+            lb, sb = run(True, optimizer, fused_gather)
+            for x, y in zip(la, lb):
+                assert abs(x - y) < 3e-2, (optimizer, fused_gather, la, lb)
+            worst = max((sa[k] - sb[k]).abs().max().item() for k in sa)
+            assert worst < 3e-2, (optimizer, fused_gather, worst)
 
 
 def check_fsdp_comm_kernels(rank, world):

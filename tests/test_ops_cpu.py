@@ -18,3 +18,46 @@ def test_attention_dropout_mask_definition():
     other = dropout_keep_mask(12346, 2, 3, 200, 0.1).float()
     agree = (other == keep).float().mean().item()
     assert abs(agree - ((1 - 26 / 256) ** 2 + (26 / 256) ** 2)) < 0.01       # independent masks
+
+
+def _full_head_ce(x, weight, bias, targets, tied, vocab_start, vocab_valid):
+    from ironcore_b200.ops import functional as OF
+
+    logits = x @ (weight.t() if tied else weight)
+    if bias is not None:
+        logits = logits + bias
+    return OF.cross_entropy(logits, targets, vocab_start=vocab_start, vocab_valid=vocab_valid)
+
+
+def test_chunked_head_cross_entropy_matches_materialised():
+    """LM head + cross entropy over vocabulary chunks (the logits never exist as a whole) against the same loss
+    on materialised logits: values and the gradients of x, the head weight and its bias; tied and untied layouts,
+    padding columns, ignored targets, a vocabulary shard that does not start at 0."""
+    from ironcore_b200.ops import functional as OF
+
+    torch.manual_seed(3)
+    t, d, v_local, valid, start = 37, 48, 640, 600, 1280
+    targets = torch.randint(start - 100, start + valid + 100, (t,))      # some targets live on other shards
+    targets[5] = -1
+    for tied in (True, False):
+        shape = (v_local, d) if tied else (d, v_local)
+        for with_bias in (False, True):
+            leaves = []
+            for _ in range(2):
+                torch.manual_seed(4)
+                x = torch.randn(t, d, dtype=torch.float64, requires_grad=True)
+                w = (torch.randn(*shape, dtype=torch.float64) * 0.2).requires_grad_(True)
+                b = torch.randn(v_local, dtype=torch.float64, requires_grad=True) if with_bias else None
+                leaves.append((x, w, b))
+            (x1, w1, b1), (x2, w2, b2) = leaves
+            ref = _full_head_ce(x1, w1, b1, targets, tied, start, valid)
+            got = OF.chunked_head_cross_entropy(x2, w2, targets, tied=tied, bias=b2, vocab_start=start,
+                                                vocab_valid=valid, chunk=256)
+            assert torch.allclose(got.double(), ref.double(), atol=1e-5, rtol=1e-5)
+            weights = torch.randn(t, dtype=torch.float64)
+            (ref.double() * weights).sum().backward()
+            (got.double() * weights).sum().backward()
+            assert torch.allclose(x2.grad, x1.grad, atol=1e-5, rtol=1e-4)
+            assert torch.allclose(w2.grad, w1.grad, atol=1e-5, rtol=1e-4)
+            if with_bias:
+                assert torch.allclose(b2.grad, b1.grad, atol=1e-5, rtol=1e-4)

@@ -98,3 +98,33 @@ def test_param_norm_over_flat_buffers_matches_per_tensor_loop():
     want = torch.sqrt(sum(p.detach().float().pow(2).sum() for p in tr.model.parameters()))
     got = tr._param_norm()
     assert torch.allclose(got, want, rtol=1e-5), (float(got), float(want))
+
+
+def test_lm_head_chunk_gives_the_same_loss_and_gradients():
+    """``model.lm_head_chunk``: the loss and every gradient of a small model equal the materialised-logits path,
+    tied and untied heads."""
+    from helpers import tiny_config
+    from ironcore_b200.models.language_model import LanguageModel
+    from ironcore_b200.parallel import mesh
+
+    for untie in (False, True):
+        grads = []
+        for chunk in (0, 128):
+            mesh.destroy_model_parallel()
+            cfg = tiny_config("llama", d_model=64, d_ffn=128, num_layers=2, num_attention_heads=4, head_dim=16,
+                              max_seq_len=32, max_position_embeddings=32, vocab_size=300)
+            cfg.data.vocab_size = 300
+            cfg.model(untie_embed=untie, lm_head_chunk=chunk)
+            torch.manual_seed(11)
+            model = LanguageModel(cfg)
+            ids = torch.randint(0, 300, (2, 32))
+            labels = torch.roll(ids, -1, dims=1)
+            labels[0, -1] = -100
+            loss = model(ids, labels)
+            loss.backward()
+            grads.append((loss.detach(), {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None}))
+        (la, ga), (lb, gb) = grads
+        assert torch.allclose(la, lb, atol=1e-5), (untie, la, lb)
+        assert ga.keys() == gb.keys()
+        for n in ga:
+            assert torch.allclose(ga[n], gb[n], atol=2e-5, rtol=1e-4), (untie, n)
