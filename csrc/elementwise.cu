@@ -353,14 +353,14 @@ ce_grad_kernel(uint16_t* __restrict__ logits, const long long* __restrict__ targ
     for (int j = 0; j < 8; ++j) {
       const int col = v * 8 + j;
       float p = (col < vocab_valid) ? __expf(f[j] - l) : 0.f;
-      if (col == tg) p -= 1.f;
+      if (col == tg && col < vocab_valid) p -= 1.f;   // a target that names a padding column is not on this shard
       f[j] = p * gs;
     }
     st8<BF16>(lr + v * 8, f);
   }
   for (int col = nvec * 8 + threadIdx.x; col < V; col += blockDim.x) {
     float p = (col < vocab_valid) ? __expf(ld16<BF16>(lr + col) - l) : 0.f;
-    if (col == tg) p -= 1.f;
+    if (col == tg && col < vocab_valid) p -= 1.f;
     st16<BF16>(lr + col, p * gs);
   }
 }
