@@ -61,6 +61,7 @@ def build_config(args, world: int):
         c.parallel.expert_model_parallel_size = min(8, world)
     elif args.workload == "fsdp_muon":
         c.parallel.use_fsdp = world > 1
+        c.parallel.fsdp_fused_gather = bool(args.fsdp_fused_gather) and world > 1
     elif args.workload == "grpo":
         tp = 2 if world >= 2 else 1
         c.trainer.tensor_model_parallel_size = tp
@@ -94,6 +95,8 @@ def main(argv=None):
     ap.add_argument("--prompts", type=int, default=0, help="GRPO: prompts per rollout batch (0 = preset scaled by GPUs)")
     ap.add_argument("--new-tokens", dest="new_tokens", type=int, default=0, help="GRPO: generated tokens per sample")
     ap.add_argument("--tp", type=int, default=0, help="llama7b: tensor-parallel size (0 = all GPUs); the rest is DP")
+    ap.add_argument("--fsdp-fused-gather", dest="fsdp_fused_gather", action="store_true",
+                    help="fsdp_muon: parameter gathers as P2P / multicast kernels instead of NCCL all-gathers")
     args = ap.parse_args(argv)
     import torch
     import torch.distributed as dist
@@ -168,6 +171,7 @@ def main(argv=None):
                        "global_batch": cfg.trainer.train_batch_size, "micro_batch": cfg.trainer.micro_batch_size,
                        "seq_len": m.max_seq_len, "tp": cfg.trainer.tensor_model_parallel_size,
                        "ep": cfg.parallel.expert_model_parallel_size, "fsdp": cfg.parallel.use_fsdp,
+                       "fsdp_fused_gather": bool(getattr(cfg.parallel, "fsdp_fused_gather", False)),
                        "optimizer": cfg.optim.optimizer, "zero_stage": cfg.parallel.zero_stage},
             "clocks": clocks, "gpu_launches": native.launches(),
             "memory_gib": torch.cuda.max_memory_allocated() / 2 ** 30, **extra}), flush=True)

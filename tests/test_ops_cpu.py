@@ -61,3 +61,22 @@ def test_chunked_head_cross_entropy_matches_materialised():
             assert torch.allclose(w2.grad, w1.grad, atol=1e-5, rtol=1e-4)
             if with_bias:
                 assert torch.allclose(b2.grad, b1.grad, atol=1e-5, rtol=1e-4)
+
+
+def test_accumulate_split_policy():
+    """Split of K for in-place fp32 accumulation: only where whole-K tiles fill 148 SMs badly (8-way tensor-parallel
+    weight-gradient shards), never for the unsharded layer shapes, and never below 8 k-blocks per work item."""
+    from ironcore_b200.ops import kernels
+
+    old = kernels._NUM_SMS
+    kernels._NUM_SMS = 148
+    try:
+        assert kernels._accumulate_split(4096, 1536, 4096) > 1        # qkv shard, 8 ranks
+        assert kernels._accumulate_split(512, 4096, 4096) > 1         # attention output shard, 8 ranks
+        assert kernels._accumulate_split(1376, 4096, 4096) > 1        # down projection shard, 8 ranks
+        for shape in [(4096, 12288, 4096), (4096, 4096, 4096), (11008, 4096, 4096), (4096, 22016, 4096),
+                      (4096, 3072, 4096), (4096, 5504, 4096)]:
+            assert kernels._accumulate_split(*shape) == 1, shape
+        assert kernels._accumulate_split(512, 4096, 512) == 1         # 8 k-blocks: nothing to split
+    finally:
+        kernels._NUM_SMS = old
