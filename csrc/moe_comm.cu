@@ -193,7 +193,8 @@ __global__ void __launch_bounds__(256) moe_push_kernel(const MoePushArgs a) {
       for (int j = 0; j < a.e_local; ++j) {
         const int s0 = seg_start_sh[e0 + j] + total_sh[e0 + j];
         const int s1 = seg_start_sh[e0 + j] + ((total_sh[e0 + j] + 127) & ~127);
-        for (int row = s0 + gw; row < s1 && row < a.cap; row += n_gw) {
+        // (counts are trusted to be non-negative; a corrupted matrix must still not produce a row below 0)
+        for (int row = max(s0, 0) + gw; row < s1 && row < a.cap; row += n_gw) {
           uint4* dst = reinterpret_cast<uint4*>(a.recv + (size_t)row * a.d * 2);
           for (int c = lane; c < row_u4; c += 32) dst[c] = make_uint4(0u, 0u, 0u, 0u);
         }
@@ -218,6 +219,24 @@ __global__ void __launch_bounds__(256) moe_push_kernel(const MoePushArgs a) {
       const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.rows) + (size_t)src_row * a.d * 2);
       uint4* dst = reinterpret_cast<uint4*>(a.peer_recv[owner] + (size_t)dest * a.d * 2);
       for (int c = lane; c < row_u4; c += 32) dst[c] = src[c];
+    }
+  }
+  if (!ok) {
+    // The counts never arrived (the wait ran out or the status block already reports a failure): nothing was
+    // pushed. Leave defined tables behind - no slot has a destination, no tile an expert, every count is zero -
+    // so that the kernels downstream of this one (grouped GEMMs, combine, the backward pass) do nothing instead
+    // of working from uninitialised memory.
+    const int gt = blockIdx.x * blockDim.x + threadIdx.x;
+    const int nt = gridDim.x * blockDim.x;
+    if (a.dest_out != nullptr)
+      for (int s = gt; s < a.S; s += nt) a.dest_out[s] = -1;
+    if (blockIdx.x == 0) {
+      if (a.seg_offsets != nullptr)
+        for (int j = threadIdx.x; j <= a.e_local; j += blockDim.x) a.seg_offsets[j] = 0;
+      if (a.tile_expert != nullptr)
+        for (int t = threadIdx.x; t < (a.cap >> 7); t += blockDim.x) a.tile_expert[t] = -1;
+      if (a.counts_out != nullptr)
+        for (int i = threadIdx.x; i < a.ep * a.E; i += blockDim.x) a.counts_out[i] = 0;
     }
   }
   // ---- all of this rank's rows are out: tell every rank, wait for every rank ----
@@ -281,9 +300,15 @@ __global__ void __launch_bounds__(256) moe_pull_kernel(const MoePullArgs a) {
         for (int k = 0; k < a.top_k; ++k) {
           const int s = t * a.top_k + k;
           const int dest = a.dest[s];
-          if (dest < 0 || dest >= a.cap) continue;
           const int owner = a.expert[s] / a.e_local;
-          if ((unsigned)owner >= (unsigned)a.ep) continue;
+          if (dest < 0 || dest >= a.cap || (unsigned)owner >= (unsigned)a.ep) {
+            // a slot without a row (dropped for capacity, or never dispatched): it contributes nothing, and the
+            // copy kept for the router-weight gradient is zero rather than uninitialised
+            if (a.gathered != nullptr)
+              reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.gathered) + (size_t)s * a.d * 2)[c] =
+                  make_uint4(0u, 0u, 0u, 0u);
+            continue;
+          }
           const uint4 u = __ldcv(reinterpret_cast<const uint4*>(a.peer_y[owner] + (size_t)dest * a.d * 2) + c);
           if (a.gathered != nullptr)
             reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.gathered) + (size_t)s * a.d * 2)[c] = u;

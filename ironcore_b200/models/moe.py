@@ -163,6 +163,7 @@ class MoEBlock(nn.Module):
         self.num_experts = moe.num_experts
         self.top_k = moe.top_k
         self.aux_coeff = moe.aux_loss_coeff
+        self.capacity_factor = float(getattr(moe, "capacity_factor", 0.0) or 0.0)   # 0 = dropless
         self.normalize = moe.normalize_topk
         self.ffn = moe.expert_d_ffn or m.d_ffn
         self.ep_group = mesh.get_expert_model_parallel_group()
@@ -231,7 +232,8 @@ class MoEBlock(nn.Module):
                 from ..parallel.fused_moe import get_fused_ep
 
                 self.fused_ep = get_fused_ep(self.ep_group, self.num_experts, self.top_k,
-                                             max(self._max_tokens, x.shape[0]), self.d_model, x.dtype)
+                                             max(self._max_tokens, x.shape[0]), self.d_model, x.dtype,
+                                             factor=float(getattr(self, "capacity_factor", 0.0) or 0.0))
         return self.fused_ep
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None):

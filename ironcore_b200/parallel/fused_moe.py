@@ -165,14 +165,22 @@ def fused_combine(yp, w, expert, dest, counts, ws: FusedEP):
 _WORKSPACES = {}
 # Largest expert-parallel group the in-kernel exchange is used for. Two ranks pass the numerics tests and full-size
 # training runs. A full-size run on four ranks (64 experts, top-6, 8192 tokens per micro-batch, 16 layers) ended
-# twice with an illegal memory access in its fourth step; reading the kernels (every peer access is bounded by the
-# buffer capacity, expert ids are checked) did not show the cause, so larger groups take the all-to-all
-# composition until it is found.
+# twice with an illegal memory access in its fourth step. The likeliest chain, found by reading afterwards: the
+# receive buffers held 2 x the mean load (the worst case only for 2 ranks), an overflow set the status block, the
+# flag waits of later kernels then returned at once, a dispatch that never saw its counts left its tables
+# uninitialised, and the backward push derived a negative row from them. Each link is closed now (worst-case
+# buffers up to 4 ranks, defined tables when the counts do not arrive, a guard on the row), but none of it has run
+# on 4 GPUs since, so larger groups keep taking the all-to-all composition until it has.
 MAX_VERIFIED_EP = 2
 
 
-def get_fused_ep(group, num_experts, top_k, max_tokens, d_model, dtype, factor: float = 2.0) -> Optional[FusedEP]:
-    """Shared workspace for all MoE layers with the same geometry; None when the fused path cannot run."""
+def get_fused_ep(group, num_experts, top_k, max_tokens, d_model, dtype, factor: float = 0.0) -> Optional[FusedEP]:
+    """Shared workspace for all MoE layers with the same geometry; None when the fused path cannot run.
+
+    ``factor``: rows of every receive buffer as a multiple of one rank's slots (tokens x top_k). 0 = dropless up to
+    4 ranks (the worst case, every slot of every rank on one owner) and 4 x the mean load beyond, where the worst
+    case would multiply the expert activations by the group size; a positive value is a capacity factor. Rows that
+    do not fit are dropped (they contribute nothing, forward and backward) and the status block reports it."""
     from .symmetric import POLICY
 
     if not POLICY.fused_moe:
@@ -184,7 +192,9 @@ def get_fused_ep(group, num_experts, top_k, max_tokens, d_model, dtype, factor: 
         return None
     if ep > MAX_VERIFIED_EP:
         return None
-    key = (id(group), num_experts, top_k, max_tokens, d_model, dtype)
+    if factor <= 0:
+        factor = float(min(ep, 4))
+    key = (id(group), num_experts, top_k, max_tokens, d_model, dtype, float(factor))
     ws = _WORKSPACES.get(key)
     if ws is None:
         ws = FusedEP(group, num_experts, top_k, max_tokens, d_model, dtype, factor)
