@@ -34,6 +34,18 @@ def test_reference_names_resolve(compat_path):
     from ironcore.config import MainConfig, _config_validation, load_trainer_config  # noqa: F401
     from ironcore.dataloader import get_data_iterator  # noqa: F401
     from ironcore.language_model import LanguageModel  # noqa: F401
+    # the submodule paths that the reference's own examples and tests import from
+    from ironcore.checkpointing.hf_interop import _generate_hf_config, load_hf_config, load_hf_state_dict  # noqa: F401
+    from ironcore.checkpointing.weight_mapping import ARCHITECTURE_ALIASES, get_architecture  # noqa: F401
+    from ironcore.eval.tasks.hellaswag import HellaSwag  # noqa: F401
+    from ironcore.layers.attention import Attention  # noqa: F401
+    from ironcore.layers.positional_embedding.rotary import RotaryPositionalEmbedding  # noqa: F401
+    from ironcore.models.transformer import TransformerLayer  # noqa: F401
+    from ironcore.preprocessing import DataSerializer  # noqa: F401
+    from ironcore.tokenizer.tokenizer import build_tokenizer  # noqa: F401
+    from ironcore.utils import get_device, get_model_dtype, is_first_rank, profile_context  # noqa: F401
+    from ironcore.training_utils import forward_step, loss_func  # noqa: F401
+    assert get_architecture("llama-3").value == "llama" and "gpt2" in ARCHITECTURE_ALIASES
     from ironcore.optimizer import AdamWOptimizer, CosineAnnealingLR, get_lr_scheduler, get_optimizer  # noqa: F401
     from ironcore.parallel import initialize_parallelism, initialize_process  # noqa: F401
     from ironcore.parallel.parallel_states import (get_data_parallel_group, get_data_parallel_group_rank,  # noqa: F401
