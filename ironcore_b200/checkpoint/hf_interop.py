@@ -32,7 +32,7 @@ class Architecture(Enum):
     LLAMA = "llama"
 
 
-_ALIASES = {"gpt2": Architecture.GPT2, "gpt-2": Architecture.GPT2, "llama": Architecture.LLAMA,
+_ALIASES = {"gpt2": Architecture.GPT2, "gpt-2": Architecture.GPT2, "gpt": Architecture.GPT2, "llama": Architecture.LLAMA,
             "llama2": Architecture.LLAMA, "llama3": Architecture.LLAMA, "mistral": Architecture.LLAMA,
             "mixtral": Architecture.LLAMA, "qwen": Architecture.LLAMA, "qwen2": Architecture.LLAMA,
             "qwen3": Architecture.LLAMA, "gemma": Architecture.LLAMA, "gemma2": Architecture.LLAMA}
