@@ -104,3 +104,33 @@ def test_inspect_subcommand(tmp_path, capsys):
     out = capsys.readouterr().out
     assert "[pre]" in out and "OK" in out
     assert (tmp_path / "out" / "inspection_report.json").exists()
+
+
+def test_reference_style_evaluation_script(compat_path, tmp_path):
+    """The way the reference's evaluation / generation scripts set a model up (tests/test_eval.py:28-60,
+    examples/generate_text.py): global states, process and model-parallel initialisation, LanguageModel(config),
+    initialize_parallelism, load_checkpoint (-1 without a checkpoint), then a forward pass for logits."""
+    from helpers import tiny_config
+    from ironcore import get_logger, set_global_states
+    from ironcore.checkpointing import load_checkpoint
+    from ironcore.language_model import LanguageModel
+    from ironcore.parallel import initialize_parallelism, initialize_process
+    from ironcore.parallel.parallel_states import initialize_model_parallel
+    from ironcore.utils import get_device, get_model_dtype, is_first_rank
+    from ironcore_b200.parallel import mesh
+
+    mesh.destroy_model_parallel()
+    cfg = tiny_config("llama")
+    cfg.trainer.model_path = str(tmp_path / "ckpt")
+    set_global_states(cfg)
+    initialize_process(cfg)
+    assert get_logger() is not None and is_first_rank()
+    device, dtype = get_device(), get_model_dtype(cfg)
+    initialize_model_parallel(cfg.trainer.tensor_model_parallel_size, timeout=cfg.parallel.timeout_minute)
+    model = LanguageModel(cfg).to(device=device, dtype=dtype)
+    model = initialize_parallelism(cfg, model)
+    assert load_checkpoint(cfg, model) == -1
+    ids = torch.randint(0, cfg.model.vocab_size or cfg.data.vocab_size, (2, 16))
+    with torch.no_grad():
+        logits = model(ids)
+    assert logits.shape[:2] == (2, 16) and torch.isfinite(logits).all()
