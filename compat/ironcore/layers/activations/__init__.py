@@ -1,3 +1,3 @@
-"""Activations (reference: ironcore/layers/activations/activations.py:15-60)."""
+"""Activation registry (reference: ironcore/layers/activations/__init__.py)."""
 
-from ironcore_b200.layers.activations import Activation, get_activation  # noqa: F401
+from .activations import Activation, GLUActivation, get_activation  # noqa: F401

@@ -1,7 +1,7 @@
 """Tensor-parallel layers, collectives and loss (reference: ironcore/parallel/tensor_parallel/__init__.py)."""
 
-from ironcore_b200.parallel.tensor_parallel import (ColumnParallelLinear, RowParallelLinear,  # noqa: F401
-                                                    VocabParallelEmbedding, vocab_parallel_cross_entropy)
+from .cross_entropy import vocab_parallel_cross_entropy  # noqa: F401
+from .layers import ColumnParallelLinear, ParallelLinear, RowParallelLinear, VocabParallelEmbedding  # noqa: F401
 
 from .comm import (copy_inputs_to_model_parallel_workers, gather_from_model_parallel_workers,  # noqa: F401
                    reduce_inputs_from_model_parallel_workers, scatter_input_to_model_parallel_workers,

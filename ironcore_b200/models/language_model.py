@@ -20,13 +20,12 @@ import torch
 import torch.nn as nn
 
 from ..layers.embedding import LanguageModelEmbedding
-from ..layers.module import BaseModule
+from ..layers.module import BaseModule, init_parameters
 from ..layers.norm import get_norm
 from ..ops import functional as OF
 from ..parallel import collectives as C
 from ..parallel import mesh
-from ..parallel.tensor_parallel import (ColumnParallelLinear, init_linear_weight_, shard_tensor,
-                                        vocab_parallel_cross_entropy)
+from ..parallel.tensor_parallel import ColumnParallelLinear, shard_tensor, vocab_parallel_cross_entropy
 from .families import resolve_family_defaults
 
 IGNORE_INDEX = -100
@@ -122,41 +121,8 @@ class LanguageModel(BaseModule):
         vocabulary rows zero. Sharded weights are slices of the TP=1 tensor, drawn from a
         CPU generator so every TP size sees the same full matrices.
         (Behavioural reference: ironcore/layers/module.py:43-163.)"""
-        cfg = self.config
-        std = cfg.init.init_std
-        resid_std = std / math.sqrt(2.0 * max(cfg.model.num_layers, 1))
-        gen = torch.Generator(device="cpu")
-        gen.manual_seed(int(cfg.init.seed))
-        tp_rank, tp_size = mesh.get_tensor_model_parallel_rank(), self.tp_size
-        ep_rank = mesh.get_expert_model_parallel_rank()
-        ep_size = mesh.get_expert_model_parallel_world_size()
-        for name, p in self.named_parameters():
-            if name.endswith("bias"):
-                nn.init.zeros_(p)
-                continue
-            if "layernorm" in name:
-                continue  # gains were set at construction
-            shard_dim = getattr(p, "tp_shard_dim", None)
-            parts = getattr(p, "tp_parts", 1)
-            is_resid = name.endswith("attn_output.weight") or name.endswith("down_proj.weight") \
-                or name.endswith("experts_down")
-            s = resid_std if is_resid else std
-            if getattr(p, "expert_parallel", False):
-                # [E_local, in, out]: draw all experts, keep this rank's slice of the expert dim
-                e_local = p.shape[0]
-                full = torch.empty((e_local * ep_size,) + tuple(p.shape[1:]), dtype=torch.float32)
-                full.normal_(0.0, s, generator=gen)
-                with torch.no_grad():
-                    p.copy_(full[ep_rank * e_local:(ep_rank + 1) * e_local].to(p.dtype))
-                continue
-            full_shape = list(p.shape)
-            if shard_dim is not None and tp_size > 1:
-                full_shape[shard_dim] *= tp_size
-            if p.dim() < 2:
-                with torch.no_grad():
-                    p.copy_(torch.empty(full_shape).normal_(0.0, s, generator=gen).to(p.dtype))
-                continue
-            init_linear_weight_(p, full_shape, s, shard_dim, parts, tp_rank, tp_size, bool(cfg.init.xavier_init), gen)
+        init_parameters(self, self.config)
+        tp_rank = mesh.get_tensor_model_parallel_rank()
         # zero the padded vocabulary rows / columns
         with torch.no_grad():
             w = self.embedding.word_embeddings

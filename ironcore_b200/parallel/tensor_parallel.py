@@ -38,6 +38,28 @@ def divide(a: int, b: int) -> int:
     return a // b
 
 
+def _accept_full_tensors(module: nn.Module) -> None:
+    """Let ``load_state_dict`` take the unsharded (tensor-parallel size 1) tensor for a sharded parameter of
+    ``module``: an entry whose shape is the full shape is replaced by this rank's slice before it is copied, so a
+    plain ``state_dict()`` of a single-rank model loads into any tensor-parallel size."""
+
+    def hook(state_dict, prefix, *_unused):
+        if module.tp_size == 1:
+            return
+        for name, p in module._parameters.items():   # pylint: disable=protected-access
+            dim = getattr(p, "tp_shard_dim", None) if p is not None else None
+            t = state_dict.get(prefix + name)
+            if dim is None or t is None or t.dim() != p.dim() or t.shape == p.shape or p.numel() == 0:
+                continue
+            full = list(p.shape)
+            full[dim] *= module.tp_size
+            if list(t.shape) == full:
+                state_dict[prefix + name] = shard_tensor(t, dim, getattr(p, "tp_parts", 1), C._rank(module.tp_group),
+                                                         module.tp_size)
+
+    module._register_load_state_dict_pre_hook(hook)   # pylint: disable=protected-access
+
+
 class ColumnParallelLinear(nn.Module):
     """y_local = gather(x) @ W[:, shard] + b[shard].
 
@@ -67,6 +89,7 @@ class ColumnParallelLinear(nn.Module):
             self.bias.tp_parts = concatenated_weights
         self.fused = None        # optional fused gather+GEMM workspace
         self.gather_slot = None  # this call site's persistent gathered buffer inside that workspace
+        _accept_full_tensors(self)
 
     def gather_target(self, x: torch.Tensor) -> Optional[torch.Tensor]:
         """This rank's rows of the gather slot, when ``self(x')`` for an ``x'`` shaped like ``x`` will run the
@@ -122,6 +145,7 @@ class RowParallelLinear(nn.Module):
             # replicated parameter that sees different tokens per rank under sequence parallelism
             self.bias.sp_replicated = True
         self.fused = None
+        _accept_full_tensors(self)
 
     def can_fuse_norm(self, x: torch.Tensor, norm, consumer) -> bool:
         """Whether ``forward_norm`` can run as one kernel: fused workspace on both ends, RMSNorm without
@@ -192,6 +216,7 @@ class VocabParallelEmbedding(nn.Module):
         self.weight = nn.Parameter(torch.empty(self.rows_per_partition, embedding_dim, dtype=dtype, device=device))
         self.weight.tp_shard_dim = 0
         self.weight.tp_parts = 1
+        _accept_full_tensors(self)
 
     def forward(self, ids: torch.Tensor, pos_table: Optional[torch.Tensor] = None,
                 pos_ids: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -134,3 +134,114 @@ def test_reference_style_evaluation_script(compat_path, tmp_path):
     with torch.no_grad():
         logits = model(ids)
     assert logits.shape[:2] == (2, 16) and torch.isfinite(logits).all()
+
+
+def _layer_config(heads=4, groups=2, flash=False, rope=False):
+    from ironcore.config import (DataConfig, InitConfig, MainConfig, ModelConfig, OperationConfig, OptimConfig,
+                                 ParallelConfig, TrainerConfig, UtilsConfig)
+
+    model = ModelConfig(d_model=64, num_attention_heads=heads, num_attention_groups=groups, head_dim=16, max_seq_len=32,
+                        max_position_embeddings=32, dropout_attn=0.0, dropout_mlp=0.0, dropout_embd=0.0, no_bias=False,
+                        num_layers=2, d_ffn=128)
+    if rope:
+        model.positional_embedding.type = "rope"
+    return MainConfig(model=model, trainer=TrainerConfig(tensor_model_parallel_size=1, use_flash_attn=flash),
+                      init=InitConfig(seed=5, init_std=0.02), optim=OptimConfig(max_lr=1e-3), data=DataConfig(),
+                      parallel=ParallelConfig(), operation=OperationConfig(train_steps=1), utils=UtilsConfig())
+
+
+def test_layer_level_call_conventions(compat_path):
+    """The reference's layer classes: built from the configuration, ``[b, s, ...]`` tensors in and out."""
+    from ironcore.layers import MLP, LanguageModelEmbedding, get_norm
+    from ironcore.layers.attention import Attention
+    from ironcore.layers.positional_embedding import PositionalEncoding, RotaryPositionalEmbedding
+    from ironcore.models.transformer import TransformerLayer, TransformerModel
+    from ironcore.parallel import parallel_states
+    from ironcore.parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear
+
+    parallel_states.initialize_model_parallel(tensor_model_parallel_size=1, timeout_in_minutes=1.0)
+    cfg = _layer_config()
+    torch.manual_seed(0)
+    b, s, hq, hkv, hd = 2, 12, 4, 2, 16
+    q, k, v = torch.randn(b, s, hq, hd), torch.randn(b, s, hkv, hd), torch.randn(b, s, hkv, hd)
+    mask = torch.tril(torch.ones(s, s)).expand(b, 1, s, s)
+    att = Attention(cfg)
+    assert att.num_attention_heads == 4 and att.head_dimension == 16
+
+    def oracle(masked):
+        kk, vv = k.repeat_interleave(hq // hkv, 2), v.repeat_interleave(hq // hkv, 2)
+        sc = torch.einsum("bqhd,bkhd->bhqk", q, kk) / hd ** 0.5
+        if masked:
+            sc = sc.masked_fill(mask == 0, float("-inf"))
+        return torch.einsum("bhqk,bkhd->bqhd", sc.softmax(-1), vv).reshape(b, s, hq * hd)
+
+    assert torch.allclose(att(q, k, v, mask), oracle(True), atol=1e-5)
+    assert torch.allclose(att(q, k, v, attention_mask=None), oracle(False), atol=1e-5)   # no mask: bidirectional
+
+    x = torch.randn(b, s, 64, requires_grad=True)
+    layer = TransformerLayer(cfg)
+    layer.init_weights()
+    assert layer.self_attention is layer.attention
+    assert layer.linear_q.weight.shape == (64, 64) and layer.linear_kv.weight.shape == (64, 2 * hkv * hd)
+    y = layer(x, mask, rotary_pos_emb=None)
+    assert y.shape == x.shape
+    y.sum().backward()
+    assert x.grad is not None and all(p.grad is not None for p in layer.parameters())
+    rope = RotaryPositionalEmbedding(head_dim=hd, max_seq_len=32)
+    y_rope = layer(x, mask, rotary_pos_emb=rope)
+    assert y_rope.shape == x.shape and not torch.allclose(y_rope, y)
+    assert torch.allclose(layer(x, mask, None), y)   # the rotary module of one call does not stick to the layer
+    stack = TransformerModel(cfg)
+    stack.init_weights()
+    assert stack(x, mask, None).shape == x.shape and len(stack.layers) == 2
+
+    col, row = ColumnParallelLinear(cfg, 64, 96, bias=True, concatenated_weights=2), RowParallelLinear(cfg, 96, 64)
+    torch.nn.init.normal_(col.weight, std=0.1)
+    torch.nn.init.normal_(row.weight, std=0.1)
+    h = col(x)
+    assert h.shape == (b, s, 96) and torch.allclose(h, x @ col.weight + col.bias, atol=1e-5)
+    assert row(h).shape == (b, s, 64)
+    mlp = MLP(cfg)
+    assert mlp(x).shape == x.shape
+    assert get_norm(cfg)(x).shape == x.shape
+    emb = LanguageModelEmbedding(cfg)
+    ids = torch.randint(0, 100, (b, s))
+    assert emb(ids, torch.arange(s).expand(b, s)).shape == (b, s, 64)
+    pe = PositionalEncoding(64, max_len=32)
+    assert torch.allclose(pe(torch.zeros(b, s, 64))[0], pe(torch.zeros(1, s, 64))[0])
+    parallel_states.destroy_model_parallel()
+
+
+def test_weight_mapper_reference_dialect(compat_path):
+    """``WeightMapper(architecture, num_layers)``: the reference's mapper names and ``[out, in]`` weights, and the
+    conversion to the live parameter names."""
+    from ironcore.checkpointing import Architecture, WeightMapper
+    from ironcore.checkpointing.weight_mapping import from_live, to_live
+
+    torch.manual_seed(1)
+    d, f, L = 16, 64, 2
+    hf = {"transformer.wte.weight": torch.randn(50, d), "transformer.wpe.weight": torch.randn(8, d),
+          "transformer.ln_f.weight": torch.randn(d), "transformer.ln_f.bias": torch.randn(d)}
+    for i in range(L):
+        p = f"transformer.h.{i}."
+        hf.update({p + "ln_1.weight": torch.randn(d), p + "ln_1.bias": torch.randn(d), p + "ln_2.weight": torch.randn(d),
+                   p + "ln_2.bias": torch.randn(d), p + "attn.c_attn.weight": torch.randn(d, 3 * d),
+                   p + "attn.c_attn.bias": torch.randn(3 * d), p + "attn.c_proj.weight": torch.randn(d, d),
+                   p + "attn.c_proj.bias": torch.randn(d), p + "mlp.c_fc.weight": torch.randn(d, f),
+                   p + "mlp.c_fc.bias": torch.randn(f), p + "mlp.c_proj.weight": torch.randn(f, d),
+                   p + "mlp.c_proj.bias": torch.randn(d)})
+    mapper = WeightMapper(Architecture.GPT2, num_layers=L)
+    ic = mapper.hf_to_ironcore(hf, strict=False)
+    assert ic["model.layers.0.self_attention.linear_q.weight"].shape == (d, d)
+    assert ic["model.layers.1.self_attention.linear_kv.weight"].shape == (2 * d, d)
+    assert ic["model.layers.0.mlp.up_proj.weight"].shape == (f, d) and "output_layernorm.weight" in ic
+    back = mapper.ironcore_to_hf(ic, strict=False)
+    for k, v in hf.items():
+        assert torch.equal(back[k], v), k
+    live = to_live(ic)
+    assert live["model.layers.0.linear_q.weight"].shape == (d, d) and "output_layernorm.layernorm.weight" in live
+    assert live["model.layers.0.mlp.up_proj.weight"].shape == (d, f)
+    again = from_live(live)
+    assert set(again) == set(ic) and all(torch.equal(again[k], ic[k]) for k in ic)
+    assert torch.equal(mapper.ironcore_to_hf(live)["transformer.h.1.attn.c_attn.weight"],
+                       hf["transformer.h.1.attn.c_attn.weight"])

@@ -69,6 +69,48 @@ def test_tp2_matches_tp1(tmp_path, family, sp):
         assert torch.allclose(v, got["sd"][k], atol=2e-4, rtol=1e-3), k
 
 
+def _full_load_worker(rank, world, family, path):
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.models.language_model import LanguageModel
+    from ironcore_b200.parallel import mesh
+
+    saved = torch.load(path)
+    cfg = tiny_config(family)
+    cfg.trainer(tensor_model_parallel_size=world)
+    cfg.parallel(world_size=world, rank=rank)
+    cfg.init.seed = 99          # different weights until the state dict is loaded
+    validate_config(cfg)
+    mesh.initialize_model_parallel(world)
+    model = LanguageModel(cfg)
+    model.load_state_dict(saved["sd"])
+    with torch.no_grad():
+        loss = float(model(saved["ids"], saved["labels"]))
+    assert abs(loss - saved["loss"]) < 1e-4, (loss, saved["loss"])
+
+
+@pytest.mark.parametrize("family", ["gpt2", "llama"])
+def test_single_rank_state_dict_loads_into_tp2(tmp_path, family):
+    """``load_state_dict`` slices unsharded tensors: a TP=1 ``state_dict()`` drives a TP=2 model to the same loss."""
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.models.language_model import LanguageModel
+    from ironcore_b200.parallel import mesh
+
+    mesh.destroy_model_parallel()
+    cfg = tiny_config(family)
+    validate_config(cfg)
+    mesh.initialize_model_parallel(1)
+    model = LanguageModel(cfg)
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 512, (2, 32), generator=g)
+    labels = torch.randint(0, 512, (2, 32), generator=g)
+    with torch.no_grad():
+        loss = float(model(ids, labels))
+    path = str(tmp_path / "full.pt")
+    torch.save({"sd": model.state_dict(), "ids": ids, "labels": labels, "loss": loss}, path)
+    mesh.destroy_model_parallel()
+    run_distributed(_full_load_worker, 2, family, path)
+
+
 def _zero_worker(rank, world, zero, steps, out_path):
     from ironcore_b200.config import validate_config
     from ironcore_b200.trainer import Trainer
