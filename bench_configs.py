@@ -37,8 +37,10 @@ def build_config(args, world: int):
         if world % tp:
             raise SystemExit(f"--tp {tp} does not divide {world} GPUs")
         c = headline_config(tp, args.steps)
-        c.trainer(tensor_model_parallel_size=tp, cuda_graph=tp > 1)
-        c.parallel(world_size=world, sequence_parallel=tp > 1, zero_stage=1)
+        overlap = bool(args.overlap_grad_reduce) and world > tp
+        # (the overlapped reduction needs the autograd hooks of an eager backward pass: no graph replay)
+        c.trainer(tensor_model_parallel_size=tp, cuda_graph=tp > 1 and not overlap)
+        c.parallel(world_size=world, sequence_parallel=tp > 1, zero_stage=1, overlap_grad_reduce=overlap)
         c.trainer.gradient_accumulation_steps = None
         if args.layers:
             c.model.num_layers = args.layers
@@ -97,6 +99,8 @@ def main(argv=None):
     ap.add_argument("--tp", type=int, default=0, help="llama7b: tensor-parallel size (0 = all GPUs); the rest is DP")
     ap.add_argument("--fsdp-fused-gather", dest="fsdp_fused_gather", action="store_true",
                     help="fsdp_muon: parameter gathers as P2P / multicast kernels instead of NCCL all-gathers")
+    ap.add_argument("--overlap-grad-reduce", dest="overlap_grad_reduce", action="store_true",
+                    help="llama7b with --tp below the GPU count: all-reduce gradient buckets behind the last backward pass")
     args = ap.parse_args(argv)
     import torch
     import torch.distributed as dist
@@ -172,6 +176,7 @@ def main(argv=None):
                        "seq_len": m.max_seq_len, "tp": cfg.trainer.tensor_model_parallel_size,
                        "ep": cfg.parallel.expert_model_parallel_size, "fsdp": cfg.parallel.use_fsdp,
                        "fsdp_fused_gather": bool(getattr(cfg.parallel, "fsdp_fused_gather", False)),
+                       "overlap_grad_reduce": bool(getattr(cfg.parallel, "overlap_grad_reduce", False)),
                        "optimizer": cfg.optim.optimizer, "zero_stage": cfg.parallel.zero_stage},
             "clocks": clocks, "gpu_launches": native.launches(),
             "memory_gib": torch.cuda.max_memory_allocated() / 2 ** 30, **extra}), flush=True)

@@ -313,7 +313,10 @@ class ParallelConfig(BaseConfig):
     fused_zero: bool = opt(True, "gradient reduce-scatter + Adam + parameter broadcast as in-kernel collectives")
     fused_moe: bool = opt(True, "expert-parallel dispatch / combine as in-kernel P2P copies")
     nvls: Literal["auto", "on", "off"] = opt("auto", "NVSwitch multicast (multimem) forms of the in-kernel collectives")
-    grad_bucket_mb: int = opt(64, "gradient reduction bucket size")
+    grad_bucket_mb: float = opt(64.0, "gradient reduction bucket size in MiB (overlap_grad_reduce)")
+    overlap_grad_reduce: bool = opt(False, "reduce gradient buckets over the data-parallel group while the last "
+                                           "micro-batch's backward pass still runs (instead of one reduction of "
+                                           "the whole buffer inside the optimizer step)")
     use_fsdp: bool = opt(False, "fully sharded data parallel")
     fsdp_fused_gather: bool = opt(False, "FSDP parameter gathers as P2P / NVSwitch-multicast kernels into "
                                          "symmetric slots instead of NCCL all-gathers")

@@ -21,7 +21,7 @@ The update rule is the reference's (see :mod:`ironcore_b200.optim.adam`).
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List
+from typing import Dict, List, Tuple
 
 import torch
 import torch.distributed as dist
@@ -142,6 +142,21 @@ class FlatGroup:
             s.param.main_grad = self.grad_buf[s.offset:s.offset + s.numel].view(s.param.shape)
             s.param.grad_ready = False
         self.shard_size = self.total // self.dp if self.dp > 0 else self.total
+        self.buckets: List[Tuple[int, int, int]] = []   # (start, end, number of slots) of every reduction bucket
+        self.slot_bucket: List[int] = []                 # bucket of slot i
+
+    def make_buckets(self, bucket_elems: int) -> None:
+        """Cut the flat buffer into contiguous ranges of about ``bucket_elems`` elements that begin and end on
+        parameter boundaries (the last one takes the padding at the end of the buffer)."""
+        self.buckets, self.slot_bucket = [], []
+        start, count = 0, 0
+        for i, s in enumerate(self.slots):
+            self.slot_bucket.append(len(self.buckets))
+            count += 1
+            end = self.slots[i + 1].offset if i + 1 < len(self.slots) else self.total
+            if end - start >= bucket_elems or i + 1 == len(self.slots):
+                self.buckets.append((start, end, count))
+                start, count = end, 0
 
     def shard_range(self, sharded: bool):
         if not sharded:
@@ -198,7 +213,8 @@ class DistributedOptimizer:
         if self.zero and not expert and not self.use_muon and not self.offload and self.tp_size == 1 \
                 and _gsize(self.dp_group) > 1 and getattr(config.parallel, "fused_comm", True) \
                 and grad_dtype == torch.float32 and dense and dense[0][3].is_cuda \
-                and dense[0][3].dtype in (torch.bfloat16, torch.float16):
+                and dense[0][3].dtype in (torch.bfloat16, torch.float16) \
+                and not getattr(config.parallel, "overlap_grad_reduce", False):
             from .fused_zero import FusedZeroStep
 
             self.fused_zero = FusedZeroStep.create(self.dp_group)
@@ -221,10 +237,23 @@ class DistributedOptimizer:
             if self.offload and torch.cuda.is_available():
                 kw["pin_memory"] = True
             self.moments.append({"exp_avg": torch.zeros(n, **kw), "exp_avg_sq": torch.zeros(n, **kw)})
+        # Overlapped reduction: during the last micro-batch of a step every bucket of the gradient buffer is
+        # all-reduced (asynchronously, on the collective library's own stream) as soon as the last of its
+        # parameters has its gradient; the step waits for the buckets instead of reducing the whole buffer.
+        # (Reference: the bucketed all-reduce of DistributedDataParallel, ironcore/parallel/parallel.py:76-81.)
+        self.overlap = bool(getattr(config.parallel, "overlap_grad_reduce", False)) and self.fused_zero is None
+        self._overlap_active = False
+        self._bucket_left: List[List[int]] = []
+        self._bucket_work = []
+        if self.overlap:
+            for g in self.groups:
+                esize = g.grad_buf.element_size() if g.total > 0 else 4
+                g.make_buckets(max(int(float(config.parallel.grad_bucket_mb) * (1 << 20)) // esize, 1))
         self._hooks = []
-        for g in self.groups:
-            for s in g.slots:
-                self._hooks.append(s.param.register_post_accumulate_grad_hook(self._make_hook()))
+        for gi, g in enumerate(self.groups):
+            for si, s in enumerate(g.slots):
+                bi = g.slot_bucket[si] if self.overlap and g.dp > 1 else -1
+                self._hooks.append(s.param.register_post_accumulate_grad_hook(self._make_hook(gi, bi)))
         self.muon = muon
         if self.use_muon and self.muon is None:
             from .muon import MuonState
@@ -233,13 +262,45 @@ class DistributedOptimizer:
         self._norm = None
         self._side_stream = None
 
-    @staticmethod
-    def _make_hook():
+    def _make_hook(self, group_index: int, bucket_index: int):
         def hook(p):
             if p.grad is not None:
                 p.main_grad.add_(p.grad.to(p.main_grad.dtype))
                 p.grad = None
+            if bucket_index >= 0 and self._overlap_active:
+                left = self._bucket_left[group_index]
+                left[bucket_index] -= 1
+                if left[bucket_index] == 0:
+                    self._launch_bucket(group_index, bucket_index)
         return hook
+
+    def _launch_bucket(self, group_index: int, bucket_index: int):
+        g = self.groups[group_index]
+        a, b, _ = g.buckets[bucket_index]
+        self._bucket_left[group_index][bucket_index] = -1     # launched
+        if b > a:
+            self._bucket_work.append(dist.all_reduce(g.grad_buf[a:b], group=g.reduce_group, async_op=True))
+
+    def start_grad_reduce_overlap(self) -> bool:
+        """Call before the backward pass of the step's last micro-batch. Returns whether buckets will be reduced
+        behind that pass (``parallel.overlap_grad_reduce`` and a data-parallel group of more than one rank)."""
+        if not self.overlap or not any(g.dp > 1 for g in self.groups):
+            return False
+        self._bucket_left = [[n for _, _, n in g.buckets] if g.dp > 1 else [] for g in self.groups]
+        self._bucket_work = []
+        self._overlap_active = True
+        return True
+
+    def _finish_grad_reduce_overlap(self):
+        """Reduce the buckets whose parameters received no gradient in the last micro-batch, then wait for all."""
+        self._overlap_active = False
+        for gi, left in enumerate(self._bucket_left):
+            for bi, n in enumerate(left):
+                if n >= 0:
+                    self._launch_bucket(gi, bi)
+        for w in self._bucket_work:
+            w.wait()
+        self._bucket_work = []
 
     # ------------------------------------------------------------------ API
     def zero_grad(self, set_to_none: bool = False):
@@ -427,9 +488,13 @@ class DistributedOptimizer:
         if self.fused_zero is not None and self.fused_zero.ready:
             self._norm = self._fused_zero_step()
             return self._norm
+        overlapped = self._overlap_active
+        if overlapped:
+            self._finish_grad_reduce_overlap()
         for g in self.groups:
             self._tp_sync_replicated(g)
-            self._reduce_grads(g)
+            if not (overlapped and g.dp > 1):
+                self._reduce_grads(g)
         norm, coef = self._global_norm_and_coef()
         self._norm = norm
         lr = self.param_groups[0]["lr"]

@@ -236,7 +236,10 @@ class Trainer:
                     total = loss.detach().clone() if total is None else total + loss.detach()
             main.wait_stream(self._graph_stream)
         else:
-            for _ in range(accum):
+            overlap = getattr(self.optimizer, "start_grad_reduce_overlap", None)
+            for i in range(accum):
+                if i == accum - 1 and overlap is not None:
+                    overlap()   # gradient buckets are reduced behind this micro-batch's backward pass
                 loss = self.forward_step_func(self.model, self.data_iterator["train"])
                 (loss / accum).backward()
                 total = loss.detach() if total is None else total + loss.detach()

@@ -389,6 +389,47 @@ def check_fsdp_comm_kernels(rank, world):
             assert (acc - (1.0 + 0.5 * want)).abs().max().item() < 2e-2
 
 
+def check_dp2_overlapped_reduction_matches_whole_buffer(rank, world):
+    """ZeRO-1 over two ranks with two micro-batches per step: gradient buckets all-reduced behind the last
+    backward pass against one reduce-scatter of the whole buffer inside the step (both on NCCL)."""
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.trainer import Trainer
+    from helpers import tiny_config
+
+    def run(overlap):
+        mesh.destroy_model_parallel()
+        cfg = tiny_config("llama", d_model=256, d_ffn=512, num_layers=2, num_attention_heads=4, head_dim=64,
+                          max_seq_len=128, max_position_embeddings=128, precision="bf16", vocab_size=1024)
+        cfg.data.vocab_size = 1024
+        cfg.model(reset_position_ids=False, reset_attention_mask=False)
+        cfg.trainer(micro_batch_size=2, train_batch_size=8, gradient_accumulation_steps=None,
+                    tensor_model_parallel_size=1, cuda_graph=False)
+        cfg.parallel(world_size=world, rank=rank, local_rank=rank, zero_stage=1, fused_zero=False,
+                     overlap_grad_reduce=overlap, grad_bucket_mb=1.0)
+        cfg.optim(max_lr=1e-3, clip_grad=0.5, weight_decay=0.1)
+        cfg.operation.train_steps = 3
+        validate_config(cfg)
+        tr = Trainer(cfg)
+        assert tr.optimizer.fused_zero is None and tr.optimizer.overlap == overlap
+        launched = []
+        if overlap:
+            real = tr.optimizer._launch_bucket
+            tr.optimizer._launch_bucket = lambda gi, bi: (launched.append(tr.optimizer._overlap_active), real(gi, bi))
+        out = [tr.train_step(s) for s in range(3)]
+        if overlap:
+            assert len(launched) == 3 * len(tr.optimizer.groups[0].buckets) > 3 and all(launched), launched
+        return [float(o[0]) for o in out], [float(o[1]) for o in out], tr.optimizer.groups[0].param_buf.float().clone()
+
+    la, na, pa = run(False)
+    lb, nb, pb = run(True)
+    for x, y in zip(la, lb):
+        assert abs(x - y) < 2e-2, (la, lb)
+    for x, y in zip(na, nb):
+        assert abs(x - y) < 2e-2 * max(1.0, abs(x)), (na, nb)
+    assert (pa - pb).abs().max().item() < 2e-2, (pa - pb).abs().max().item()
+
+
 def test_fused_tp_kernels_two_gpus():
     _need_two()
     for world in _worlds():
@@ -398,6 +439,11 @@ def test_fused_tp_kernels_two_gpus():
 def test_dp2_fused_zero_step_vs_nccl():
     _need_two()
     _spawn("check_dp2_fused_zero_matches_nccl")
+
+
+def test_dp2_overlapped_bucket_reduction():
+    _need_two()
+    _spawn("check_dp2_overlapped_reduction_matches_whole_buffer")
 
 
 def test_fsdp2_matches_dp2():

@@ -111,17 +111,25 @@ def test_single_rank_state_dict_loads_into_tp2(tmp_path, family):
     run_distributed(_full_load_worker, 2, family, path)
 
 
-def _zero_worker(rank, world, zero, steps, out_path):
+def _zero_worker(rank, world, zero, steps, out_path, overlap=False, accum=1):
     from ironcore_b200.config import validate_config
     from ironcore_b200.trainer import Trainer
 
     cfg = tiny_config("llama")
-    cfg.trainer(micro_batch_size=2, train_batch_size=4, gradient_accumulation_steps=None)
-    cfg.parallel(world_size=world, rank=rank, zero_stage=zero)
+    cfg.trainer(micro_batch_size=2, train_batch_size=4 * accum, gradient_accumulation_steps=None)
+    cfg.parallel(world_size=world, rank=rank, zero_stage=zero, overlap_grad_reduce=overlap, grad_bucket_mb=0.05)
     cfg.operation.train_steps = steps
     validate_config(cfg)
     tr = Trainer(cfg)
+    if overlap:
+        launched = []
+        real = tr.optimizer._launch_bucket
+        tr.optimizer._launch_bucket = lambda gi, bi: (launched.append((gi, bi, tr.optimizer._overlap_active)), real(gi, bi))
     losses = [float(tr.train_step(s)[0]) for s in range(steps)]
+    if overlap:
+        nb = len(tr.optimizer.groups[0].buckets)
+        # every bucket once per step, and all of them from inside the backward pass
+        assert nb > 2 and len(launched) == nb * steps and all(active for _, _, active in launched), (nb, launched)
     sd = {k: v.clone() for k, v in tr.model.canonical_state_dict().items()}
     opt = tr.optimizer.state_dict()
     if rank == 0:
@@ -137,6 +145,46 @@ def test_zero1_matches_replicated_optimizer(tmp_path):
         assert torch.allclose(r0["sd"][k], r1["sd"][k], atol=1e-6), k
     for k in r0["opt"]:
         assert torch.allclose(r0["opt"][k]["exp_avg"], r1["opt"][k]["exp_avg"], atol=1e-7), k
+
+
+@pytest.mark.parametrize("zero", [0, 1])
+def test_overlapped_bucket_reduction_matches_whole_buffer_reduction(tmp_path, zero):
+    a, b = str(tmp_path / "plain.pt"), str(tmp_path / "overlap.pt")
+    run_distributed(_zero_worker, 2, zero, 3, a, False, 2)
+    run_distributed(_zero_worker, 2, zero, 3, b, True, 2)
+    r0, r1 = torch.load(a), torch.load(b)
+    assert r0["losses"] == pytest.approx(r1["losses"], abs=1e-6)
+    for k in r0["sd"]:
+        assert torch.allclose(r0["sd"][k], r1["sd"][k], atol=1e-6), k
+
+
+def _tp_dp_worker(rank, world, overlap, out_path):
+    from ironcore_b200.checkpoint.native import merge_model_parallel_state
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.trainer import Trainer
+
+    cfg = tiny_config("llama")
+    cfg.trainer(micro_batch_size=2, train_batch_size=8, gradient_accumulation_steps=None, tensor_model_parallel_size=2)
+    cfg.parallel(world_size=world, rank=rank, sequence_parallel=True, zero_stage=1, overlap_grad_reduce=overlap,
+                 grad_bucket_mb=0.02)
+    validate_config(cfg)
+    tr = Trainer(cfg)
+    losses = [float(tr.train_step(s)[0]) for s in range(2)]
+    merged = merge_model_parallel_state(dict(tr.model.canonical_state_dict()), tr.model.canonical_shard_info())
+    if rank == 0:
+        torch.save({"losses": losses, "sd": merged}, out_path)
+
+
+def test_overlapped_reduction_on_a_tp_by_dp_mesh(tmp_path):
+    """TP2 x DP2 with sequence parallelism: the bucket all-reduces over the data-parallel group and the
+    tensor-parallel sum of the replicated parameters' gradients commute."""
+    a, b = str(tmp_path / "plain.pt"), str(tmp_path / "overlap.pt")
+    run_distributed(_tp_dp_worker, 4, False, a)
+    run_distributed(_tp_dp_worker, 4, True, b)
+    r0, r1 = torch.load(a), torch.load(b)
+    assert r0["losses"] == pytest.approx(r1["losses"], abs=1e-6)
+    for k in r0["sd"]:
+        assert torch.allclose(r0["sd"][k], r1["sd"][k], atol=1e-6), k
 
 
 def _ckpt_save_worker(rank, world, path):
