@@ -8,9 +8,12 @@ wide orientation):  A = X X^T ; B = b A + c A A ; X <- a X + B X   with
 Fused tensors (q|k|v, gate|up) and stacked expert weights are orthogonalised per logical
 matrix. Distribution: every logical matrix has an owner rank in the data-parallel group
 (greedy balance by Newton-Schulz FLOPs); the owner keeps the momentum, runs the iteration
-on the (TP-gathered) matrix and publishes the update through a summed update buffer, so
-momentum memory and Newton-Schulz time divide by the number of ranks. On CUDA the three
-matrix products per iteration are the tcgen05 GEMM.
+on the (TP-gathered) matrix and publishes the update once: every owner packs the updates of
+its matrices into one send buffer, one all-gather over the data-parallel group delivers the
+packs, and every rank adds each matrix's update from its owner's pack (wire bytes: one copy
+of the Muon parameters per rank and step, against two for an all-reduce of a dense update
+buffer). Momentum memory and Newton-Schulz time divide by the number of ranks. On CUDA the
+three matrix products per iteration are the tcgen05 GEMM.
 (No counterpart in the reference; semantics follow the published Muon optimizer.)
 """
 
@@ -63,7 +66,7 @@ def newton_schulz(g: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.T
 
 class _Matrix:
     __slots__ = ("slot", "group_idx", "expert", "col_lo", "col_hi", "full_shape", "owner", "momentum", "tp_dim",
-                 "part", "key")
+                 "part", "key", "pack_off", "pack_numel")
 
 
 class MuonState:
@@ -124,6 +127,18 @@ class MuonState:
                 r = min(range(len(load)), key=lambda i: load[i])
                 m.owner = r
                 load[r] += self._cost(m.full_shape)
+        # position of every matrix's (local, TP-sliced) update inside its owner's pack
+        self.pack_size: List[int] = []
+        for gi, g in enumerate(engine.groups):
+            used = [0] * max(g.dp, 1)
+            for m in self.matrices:
+                if m.group_idx != gi:
+                    continue
+                rows = m.slot.param.shape[-2]
+                m.pack_numel = rows * (m.col_hi - m.col_lo)
+                m.pack_off = used[m.owner]
+                used[m.owner] += (m.pack_numel + 127) // 128 * 128
+            self.pack_size.append(max(used) if used else 0)
 
     @staticmethod
     def _cost(shape) -> float:
@@ -153,9 +168,11 @@ class MuonState:
     @torch.no_grad()
     def step(self, coef: torch.Tensor, lr: float):
         eng = self.engine
-        upd_bufs = []
-        for g in eng.groups:
-            upd_bufs.append(torch.zeros_like(g.param_buf) if g.dp > 1 else None)
+        send = []
+        for gi, g in enumerate(eng.groups):
+            # (zeros: the tail of a pack that is shorter than the longest one is sent but never read)
+            send.append(torch.zeros(self.pack_size[gi], dtype=g.dtype, device=g.device)
+                        if g.dp > 1 and self.pack_size[gi] > 0 else None)
         for m in self.matrices:
             g = eng.groups[m.group_idx]
             mine = (m.owner == g.dp_rank)
@@ -177,24 +194,33 @@ class MuonState:
             fan_in, fan_out = m.full_shape
             scale = math.sqrt(max(1.0, fan_out / fan_in))
             delta = self._slice_tp((-lr * scale) * x.float(), m)
-            target = upd_bufs[m.group_idx]
+            target = send[m.group_idx]
             if target is None:
                 w = self._view(g.param_buf, m)
                 if self.weight_decay:
                     w.mul_(1 - lr * self.weight_decay)
                 w.add_(delta.to(w.dtype))
             else:
-                self._view(target, m).copy_(delta.to(target.dtype))
-        for g, upd in zip(eng.groups, upd_bufs):
-            if upd is None:
+                target[m.pack_off:m.pack_off + m.pack_numel].view(delta.shape).copy_(delta.to(target.dtype))
+        for gi, (g, pack) in enumerate(zip(eng.groups, send)):
+            if pack is None:
                 continue
-            for r in g.regions:
-                if r.kind == "muon" and r.end > r.start:
-                    dist.all_reduce(upd[r.start:r.end], group=g.reduce_group)
-                    w = g.param_buf[r.start:r.end]
-                    if self.weight_decay:
-                        w.mul_(1 - lr * self.weight_decay)
-                    w.add_(upd[r.start:r.end])
+            if g.device.type == "cpu":
+                parts = [torch.empty_like(pack) for _ in range(g.dp)]
+                dist.all_gather(parts, pack, group=g.reduce_group)
+                recv = torch.stack(parts)
+            else:
+                recv = torch.empty(g.dp, pack.numel(), dtype=pack.dtype, device=pack.device)
+                dist.all_gather_into_tensor(recv.view(-1), pack, group=g.reduce_group)
+            if self.weight_decay:
+                for r in g.regions:
+                    if r.kind == "muon" and r.end > r.start:
+                        g.param_buf[r.start:r.end].mul_(1 - lr * self.weight_decay)
+            for m in self.matrices:
+                if m.group_idx != gi:
+                    continue
+                w = self._view(g.param_buf, m)
+                w.add_(recv[m.owner, m.pack_off:m.pack_off + m.pack_numel].view(w.shape))
 
     def state_dict(self) -> Dict[str, torch.Tensor]:
         """Momentum of every logical matrix by layout-independent key. Collective: each momentum lives on

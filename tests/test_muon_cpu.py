@@ -86,3 +86,33 @@ def _resume_worker(rank, world, fsdp, ckpt_dir):
 @pytest.mark.parametrize("fsdp", [False, True])
 def test_muon_momentum_survives_resume_on_two_ranks(tmp_path, fsdp):
     run_distributed(_resume_worker, 2, fsdp, str(tmp_path / "ckpt"))
+
+
+def _mesh_worker(rank, world, tp, out_path):
+    from ironcore_b200.checkpoint.native import merge_model_parallel_state
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.trainer import Trainer
+
+    cfg = _muon_config(muon_weight_decay=0.01)
+    cfg.trainer(micro_batch_size=2, train_batch_size=4, gradient_accumulation_steps=None,
+                tensor_model_parallel_size=tp)
+    cfg.parallel(world_size=world, rank=rank, zero_stage=1, sequence_parallel=tp > 1)
+    validate_config(cfg)
+    tr = Trainer(cfg)
+    losses = [float(tr.train_step(s)[0]) for s in range(3)]
+    merged = merge_model_parallel_state(dict(tr.model.canonical_state_dict()), tr.model.canonical_shard_info())
+    if rank == 0:
+        torch.save({"losses": losses, "sd": merged}, out_path)
+
+
+def test_muon_update_packs_on_tp_by_dp_mesh_match_dp(tmp_path):
+    """Owners publish their matrices' updates through one all-gather of per-owner packs; on a TP2 x DP2 mesh the
+    packs hold the tensor-parallel slices. Same data-parallel size, same data: the merged weights must agree.
+    (DP2 itself is checked against the FSDP implementation of Muon in test_fsdp_cpu.)"""
+    a, b = str(tmp_path / "dp2.pt"), str(tmp_path / "tp2dp2.pt")
+    run_distributed(_mesh_worker, 2, 1, a)
+    run_distributed(_mesh_worker, 4, 2, b)
+    r0, r1 = torch.load(a), torch.load(b)
+    assert r0["losses"] == pytest.approx(r1["losses"], abs=3e-4)
+    for k, v in r0["sd"].items():
+        assert torch.allclose(v, r1["sd"][k], atol=3e-4, rtol=1e-3), k
