@@ -3,7 +3,9 @@
 Every rank publishes ``(step, beat counter)`` to the process group's key-value store on a background
 thread; each rank watches the others and declares a peer dead when that peer's counter has not moved
 for longer than the timeout, measured on the watcher's own clock (clocks of different hosts are never
-compared, and a key that is not there yet is probed with ``check`` instead of a blocking ``get``). The trainer asks between steps (never while kernels or collectives are in flight), so a
+compared, and a key that is not there yet is probed with ``check`` instead of a blocking ``get``). A rank that
+leaves on purpose (an exception in its training loop) publishes a tombstone first, which its peers read as a
+failure at once, without waiting for the timeout. The trainer asks between steps (never while kernels or collectives are in flight), so a
 lost rank surfaces as a Python exception before the next launch instead of a collective that
 blocks until the process-group timeout. Recovery is restart-from-latest-checkpoint, driven by the
 launcher. Device-side waits are bounded separately (status word written by the kernels).
@@ -52,6 +54,8 @@ class Heartbeat:
         return f"{self.prefix}/{rank}"
 
     def _publish(self):
+        if getattr(self, "_left", False):
+            return
         self._seq += 1
         self.store.set(self._key(self.rank), f"{self.step}:{self._seq}")
 
@@ -66,6 +70,16 @@ class Heartbeat:
     def beat(self, step: int):
         self.step = step
         self._publish()
+
+    def leave(self, reason: str = "") -> None:
+        """Tell the peers that this rank stops taking part (call between steps, with nothing of this rank in
+        flight): its record becomes a tombstone that ``raise_if_peer_dead`` on the other ranks reports at once."""
+        self._stop.set()
+        self._left = True
+        try:
+            self.store.set(self._key(self.rank), f"{self.step}:left:{reason[:200]}")
+        except Exception:   # the store lives on rank 0: if that is gone there is nobody left to tell
+            pass
 
     def _read(self, rank: int) -> Optional[str]:
         """The peer's record, or None when it has not published yet. Never blocks on a missing key."""
@@ -99,6 +113,9 @@ class Heartbeat:
             now = self.clock()
             if raw is None:
                 ages[r] = now - self._born
+                continue
+            if raw.split(":")[1:2] == ["left"]:
+                ages[r] = float("inf")
                 continue
             with self._lock:
                 seen = self._seen.get(r)

@@ -187,7 +187,12 @@ class Trainer:
             if self.heartbeat is not None:
                 self.heartbeat.beat(step)
                 self.heartbeat.raise_if_peer_dead()
-            loss, grad_norm, param_norm = self.train_step(step)
+            try:
+                loss, grad_norm, param_norm = self.train_step(step)
+            except BaseException as e:
+                if self.heartbeat is not None:     # the peers stop before their next step instead of waiting for us
+                    self.heartbeat.leave(f"{type(e).__name__}: {e}")
+                raise
             pending.append(loss)
             if self.control.do_log(step):
                 self.log_training(step, pending, grad_norm, param_norm)

@@ -74,6 +74,46 @@ def test_heartbeat_over_real_store_two_ranks():
     run_distributed(_hb_worker, 2)
 
 
+def _leave_worker(rank, world):
+    """Three ranks train with heartbeats; after step 0, between steps and with nothing in flight, rank 2 leaves
+    (a host-side exception in its loop). The others read its tombstone before their next step and stop with a
+    ``RankFailure`` at once, long before the heartbeat timeout, instead of entering a collective."""
+    import time
+
+    import torch.distributed as dist
+
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.parallel.fault import RankFailure
+    from ironcore_b200.trainer import Trainer
+
+    cfg = tiny_config("gpt2")
+    cfg.trainer(micro_batch_size=1, train_batch_size=3, gradient_accumulation_steps=None)
+    cfg.parallel(world_size=world, rank=rank)
+    cfg.utils(heartbeat_interval_s=0.1, heartbeat_timeout_s=120.0)
+    validate_config(cfg)
+    tr = Trainer(cfg)
+    hb = tr.heartbeat
+    assert hb is not None
+    hb.beat(0)
+    hb.raise_if_peer_dead()
+    tr.train_step(0)
+    if rank == 2:
+        hb.leave("injected failure")
+    dist.barrier()          # (test only) orders the tombstone before the others' next question
+    if rank == 2:
+        return
+    t0 = time.time()
+    with pytest.raises(RankFailure) as info:
+        hb.beat(1)
+        hb.raise_if_peer_dead()
+    assert info.value.ranks == [2] and time.time() - t0 < 5.0
+    hb.stop()
+
+
+def test_rank_that_leaves_between_steps_stops_its_peers():
+    run_distributed(_leave_worker, 3)
+
+
 def _timeout_worker(rank, world):
     """A rank that never joins a collective: the short process-group timeout ends the others' wait
     with an error instead of a hang (Gloo ranks, nothing on a GPU)."""
