@@ -1,3 +1,3 @@
-"""Packing collator (reference: ironcore/dataloader/collator.py)."""
+"""Packing collator (reference: ironcore/dataloader/collator.py:17-255)."""
 
-from ironcore_b200.data.collator import UniversalCollator  # noqa: F401
+from ironcore_b200.data.collator import UniversalCollator, create_collator, first_fit_decreasing  # noqa: F401

@@ -2,4 +2,5 @@
 
 from ironcore_b200.optim import get_lr_scheduler, get_optimizer  # noqa: F401
 from ironcore_b200.optim.adam import AdamWOptimizer  # noqa: F401
-from ironcore_b200.optim.lr_scheduler import CosineAnnealingLR  # noqa: F401
+
+from .lr_scheduler import CosineAnnealingLR, LinearDecayLRScheduler  # noqa: F401

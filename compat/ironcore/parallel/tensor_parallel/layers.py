@@ -15,7 +15,19 @@ def _flat(x: torch.Tensor):
 
 
 class ParallelLinear(torch.nn.Module):
-    """Common base of the two linear layers (reference: layers.py:27-60); it carries no behaviour here."""
+    """Common base of the two linear layers (reference: layers.py:27-60). On its own,
+    ``ParallelLinear(config, input_size, output_size, bias)`` is an unsharded ``[in, out]`` weight (and bias)
+    without a forward pass, as in the reference."""
+
+    def __init__(self, config=None, input_size: int = None, output_size: int = None, bias: bool = True):
+        super().__init__()
+        if input_size is None:       # reached through a subclass, which sets everything up itself
+            return
+        self.config, self.input_size, self.output_size, self.use_bias = config, input_size, output_size, bias
+        self.weight = torch.nn.Parameter(torch.empty(input_size, output_size))
+        self.bias = torch.nn.Parameter(torch.zeros(output_size)) if bias else None
+        self.column_parallel = self.row_parallel = False
+        self.concatenated_weights = 1
 
 
 class ColumnParallelLinear(_tp.ColumnParallelLinear, ParallelLinear):
@@ -52,6 +64,15 @@ class VocabParallelEmbedding(_tp.VocabParallelEmbedding):
         super().__init__(input_dim, embedding_dim, padding_start_idx=padding_start_idx)
         self.config = config
         self.parallel_input, self.parallel_output = parallel_input, parallel_output
+
+    def init_weight(self):
+        """normal(0, init_std) rows, zeros from ``padding_start_idx`` on (this rank's part of them)."""
+        std = self.config.init.init_std if self.config is not None else 0.02
+        with torch.no_grad():
+            self.weight.normal_(0.0, std)
+            lo = max(self.padding_start_idx - self.vocab_start, 0)
+            if lo < self.rows_per_partition:
+                self.weight[lo:].zero_()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:   # pylint: disable=arguments-differ
         ids = x if x.dim() == 2 else x.reshape(1, -1)

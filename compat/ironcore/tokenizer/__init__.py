@@ -1,3 +1,3 @@
-"""Tokenizer construction (reference: ironcore/tokenizer/tokenizer.py:26-220)."""
+"""Tokenizers (reference: ironcore/tokenizer/__init__.py)."""
 
-from ironcore_b200.tokenizer import Tokenizer, build_tokenizer  # noqa: F401
+from .tokenizer import BbpeTokenizer, SentencePieceTokenizer, Tokenizer, build_tokenizer  # noqa: F401

@@ -180,7 +180,7 @@ class ModelConfig(BaseConfig):
     precision: str = opt("bfloat16", "parameter / compute dtype")
     reset_position_ids: bool = opt(True, "restart positions after an end-of-document token")
     reset_attention_mask: bool = opt(True, "block attention across documents")
-    eod_mask_loss: bool = opt(False, "mask the loss on end-of-document tokens")
+    eod_mask_loss: bool = opt(False, "leave positions whose target is the end-of-document or padding token out of the loss")
     positional_embedding: PositionalEmbeddingConfig = field(default_factory=PositionalEmbeddingConfig)
     add_pooler: bool = opt(True, "unused, kept for compatibility")
     untie_embed: bool = opt(False, "separate LM head")

@@ -63,5 +63,14 @@ class TrainingControl:
     def do_param_norm(self, step: int) -> bool:
         return self._norm_cadence(self.config.trainer.param_norm_log_interval, step)
 
-    def do_final_checkpoint(self) -> bool:
-        return (not self.no_save) and not self.profiling
+    def do_final_checkpoint(self, step=None, last_step=None) -> bool:
+        """Whether to save when training ends. Never while profiling or with saving off; with ``step`` (the step
+        training ended on) not when the cadence saved that step already; with ``last_step`` (the step the run
+        resumed from) as well only when more than one step lies between them, which is the reference's call
+        ``do_final_checkpoint(step, last_step)`` (ironcore/controller.py:71-78)."""
+        ok = (not self.no_save) and not self.profiling
+        if step is not None:
+            ok = ok and not self.do_checkpoint(step)
+            if last_step is not None:
+                ok = ok and step - last_step > 1
+        return ok

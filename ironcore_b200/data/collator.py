@@ -37,8 +37,16 @@ def first_fit_decreasing(lengths: List[int], capacity: int) -> List[List[int]]:
 
 
 class UniversalCollator:
-    def __init__(self, mode: str, max_seq_len: int, pad_token_id: int = 0, pack: bool = True):
+    """``use_flash_attention`` keeps ``cu_seqlens`` in SFT batches (the sample boundaries the attention kernel
+    masks by); ``return_full_attention_mask`` adds ``attention_mask`` ``[rows, S, S]`` (bool, block-diagonal over
+    the packed samples, padding excluded) for attention paths that take a materialised mask."""
+
+    def __init__(self, mode: str, max_seq_len: int, pad_token_id: int = 0, pack: bool = True,
+                 use_flash_attention: bool = True, return_full_attention_mask: bool = False):
         self.mode, self.max_seq_len, self.pad, self.pack = mode, max_seq_len, pad_token_id, pack
+        self.pad_token_id = pad_token_id
+        self.use_flash_attention = use_flash_attention
+        self.return_full_attention_mask = return_full_attention_mask
 
     def __call__(self, samples: List[Dict]) -> Dict[str, torch.Tensor]:
         if self.mode == "pretrain":
@@ -66,6 +74,7 @@ class UniversalCollator:
         labels_full = torch.full((rows, cap), IGNORE_INDEX, dtype=torch.long)
         pos = torch.zeros((rows, cap), dtype=torch.long)
         boundaries = [0]
+        full_mask = torch.zeros((rows, cap, cap), dtype=torch.bool) if self.return_full_attention_mask else None
         for r, members in enumerate(bins):
             col = 0
             for i in members:
@@ -80,11 +89,21 @@ class UniversalCollator:
                 labels_full[r, col:col + n] = lab
                 labels_full[r, col] = IGNORE_INDEX          # never predict a sample's first token from the previous one
                 pos[r, col:col + n] = torch.arange(n)
+                if full_mask is not None:
+                    full_mask[r, col:col + n, col:col + n] = True
                 col += n
                 boundaries.append(r * self.max_seq_len + min(col, self.max_seq_len))
             if boundaries[-1] != (r + 1) * self.max_seq_len:
                 boundaries.append((r + 1) * self.max_seq_len)
         cu = torch.tensor(sorted(set(boundaries)), dtype=torch.int32)
-        return {"input_ids": tokens[:, :-1].contiguous(), "labels": labels_full[:, 1:].contiguous(),
-                "position_ids": pos[:, :-1].contiguous(), "cu_seqlens": cu,
-                "loss_mask": (labels_full[:, 1:] != IGNORE_INDEX)}
+        out = {"input_ids": tokens[:, :-1].contiguous(), "labels": labels_full[:, 1:].contiguous(),
+               "position_ids": pos[:, :-1].contiguous(), "loss_mask": (labels_full[:, 1:] != IGNORE_INDEX)}
+        if self.use_flash_attention:
+            out["cu_seqlens"] = cu
+        if full_mask is not None:
+            out["attention_mask"] = full_mask[:, :-1, :-1].contiguous()
+        return out
+
+
+def create_collator(mode: str, max_seq_len: int, pad_token_id: int = 0, **kwargs) -> UniversalCollator:
+    return UniversalCollator(mode=mode, max_seq_len=max_seq_len, pad_token_id=pad_token_id, **kwargs)

@@ -81,9 +81,18 @@ class UniversalDataConfig:
     def output_dir(self, ds: DatasetConfig) -> Path:
         return self.preprocessed_dir / ds.name / ds.task_type
 
+    def get_dataset_output_path(self, dataset: DatasetConfig) -> Path:
+        """Directory of a dataset's ``data.bin`` / ``data.idx.npy`` (created when missing)."""
+        out = Path(dataset.output_path) if dataset.output_path else self.output_dir(dataset)
+        out.mkdir(parents=True, exist_ok=True)
+        return out
+
     @classmethod
     def from_yaml(cls, path: Union[str, Path]) -> "UniversalDataConfig":
-        doc = load_yaml_config(path, merge_lists=False)
+        return cls.from_dict(load_yaml_config(path, merge_lists=False))
+
+    @classmethod
+    def from_dict(cls, doc: Dict) -> "UniversalDataConfig":
         def parse(key_a, key_b=None):
             raw = doc.get(key_a) or (doc.get(key_b) if key_b else None) or []
             if isinstance(raw, dict):  # list of single-key dicts was merged by the YAML helper
@@ -95,3 +104,10 @@ class UniversalDataConfig:
               if k in doc}
         return cls(datasets=parse("train_datasets", "datasets"), eval_datasets=parse("eval_datasets"),
                    test_datasets=parse("test_datasets"), **kw)
+
+
+def load_data_config(config_path: Union[str, Path]) -> UniversalDataConfig:
+    return UniversalDataConfig.from_yaml(config_path)
+
+
+DataConfig = UniversalDataConfig     # the reference's alias (ironcore/dataloader/data_config.py:231)

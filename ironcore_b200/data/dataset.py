@@ -84,6 +84,24 @@ class WeightedMixingDataset(IterableDataset):
         self.epochs = epochs
         self.cursor = 0          # samples yielded so far on this rank (saved in checkpoints)
 
+    @classmethod
+    def from_data_config(cls, data_config, mode: str = "pretrain", seed: int = 1337, split: str = "train",
+                         dp_rank: int = 0, dp_size: int = 1, epochs: Optional[int] = None, seq_len: Optional[int] = None):
+        """The mixing dataset of one split of a dataset YAML (``UniversalDataConfig``): the split's own dataset
+        list when it has one (used whole), else the split's share of the training datasets; only datasets of
+        task type ``mode`` take part."""
+        own = {"train": data_config.datasets, "eval": data_config.eval_datasets, "test": data_config.test_datasets}
+        if split not in own:
+            raise ValueError(f"Invalid split: {split}")
+        separate = split != "train" and bool(own[split])
+        sources = [d for d in (own[split] if separate or split == "train" else data_config.datasets)
+                   if d.task_type == mode]
+        if not sources:
+            raise ValueError(f"no {mode} dataset for split {split}")
+        return cls([d.output_path for d in sources], [d.ratio for d in sources], mode, "train" if separate else split,
+                   seq_len or data_config.max_seq_len, [1.0, 0.0, 0.0] if separate else data_config.splits, seed=seed,
+                   dp_rank=dp_rank, dp_size=dp_size, epochs=epochs)
+
     def _pretrain_positions(self):
         items = []
         for si, ds in enumerate(self.sets):

@@ -27,12 +27,8 @@ def build_file_iterators(config, dp_rank: int, dp_size: int) -> Dict[str, object
         if not enabled or not sources:
             out[split] = None
             continue
-        own_split = split if (split == "train" or not {"eval": dcfg.eval_datasets, "test": dcfg.test_datasets}[split]) \
-            else "train"
-        splits = dcfg.splits if own_split == split else [1.0, 0.0, 0.0]
-        ds = WeightedMixingDataset([s.output_path for s in sources], [s.ratio for s in sources], task, own_split,
-                                   seq_len, splits, seed=1337, dp_rank=dp_rank, dp_size=dp_size,
-                                   epochs=None if split == "train" else 1)
+        ds = WeightedMixingDataset.from_data_config(dcfg, task, 1337, split, dp_rank, dp_size,
+                                                    epochs=None if split == "train" else 1, seq_len=seq_len)
         bs = {"train": config.trainer.micro_batch_size,
               "eval": config.trainer.eval_batch_size or config.trainer.micro_batch_size,
               "test": config.trainer.test_batch_size or config.trainer.micro_batch_size}[split]

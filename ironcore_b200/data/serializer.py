@@ -94,9 +94,10 @@ def load_rows(ds: DatasetConfig, cache_dir: Optional[Path] = None) -> Iterable[D
 
 
 class DataSerializer:
-    def __init__(self, config: UniversalDataConfig, tokenizer):
+    def __init__(self, config: UniversalDataConfig, tokenizer, verbose: bool = False):
         self.config = config
         self.tok = tokenizer
+        self.verbose = verbose
 
     # ---- per-task tokenisation: yields (tokens, type, group_id, mask_ranges) ----
     def _pretrain(self, ds, rows):
@@ -237,5 +238,14 @@ class DataSerializer:
                                                    "name": ds.name}))
         return out
 
+    def serialize_dataset(self, dataset_config: DatasetConfig, force: bool = False) -> Path:
+        """One dataset -> its ``data.bin`` / ``data.idx.npy`` directory (skipped when already there)."""
+        if self.verbose:
+            print(f"[{dataset_config.name}] task {dataset_config.task_type}, source {dataset_config.source}")
+        out = self.serialize(dataset_config, force)
+        if self.verbose:
+            print(f"[{dataset_config.name}] -> {out}")
+        return out
+
     def serialize_all(self, force: bool = False) -> List[Path]:
-        return [self.serialize(ds, force) for ds in self.config.all_datasets()]
+        return [self.serialize_dataset(ds, force) for ds in self.config.all_datasets()]

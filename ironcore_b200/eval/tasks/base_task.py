@@ -18,6 +18,10 @@ class Task:
         self.cache_dir = cache_dir
         self._examples = examples
 
+    @property
+    def task_name(self) -> str:
+        return self.name
+
     def load_examples(self) -> Iterable[dict]:
         raise NotImplementedError
 

@@ -11,13 +11,48 @@ from .utils.timers import Timer
 
 
 class GlobalStates:
-    def __init__(self):
+    def __init__(self, config=None, tokenizer=None):
         self.config = None
         self.logger: Optional[IronCoreLogger] = None
         self.tb: Optional[TensorboardLogger] = None
         self.mlflow: Optional[MLFlowLogger] = None
         self.timer: Optional[Timer] = None
         self.tokenizer = None
+        if config is not None:
+            self.setup(config, tokenizer)
+
+    def setup(self, config, tokenizer=None) -> "GlobalStates":
+        """Create the logger, timer, tokenizer and metric sinks for ``config``; records the tokenizer's vocabulary
+        sizes and special ids in the model config."""
+        self.config = config
+        self.logger = IronCoreLogger(level=config.utils.log_level, rank=max(config.parallel.rank, 0))
+        self.timer = Timer()
+        self.tokenizer = tokenizer if tokenizer is not None else build_tokenizer(config)
+        m = config.model
+        m.vocab_size = self.tokenizer.vocab_size
+        m.padded_vocab_size = self.tokenizer.padded_vocab_size
+        m.eod_token_id = self.tokenizer.eod_token_id
+        m.pad_token_id = self.tokenizer.pad_token_id
+        rank0 = max(config.parallel.rank, 0) == 0
+        if rank0 and config.utils.tensorboard_dir:
+            self.tb = TensorboardLogger(config.utils.tensorboard_dir, config.trainer.model_name)
+        if rank0 and config.utils.mlflow_tracking_uri:
+            self.mlflow = MLFlowLogger(config.utils.mlflow_tracking_uri, config.utils.mlflow_experiment_name,
+                                       config.trainer.model_path, config.trainer.model_name)
+        return self
+
+    # accessors under the reference's method names (ironcore/global_vars.py:41-57)
+    def get_config(self):
+        return self.config
+
+    def get_logger(self):
+        return get_logger()
+
+    def get_tokenizer(self):
+        return self.tokenizer
+
+    def cleanup(self):
+        global_states_cleanup()
 
 
 _G = GlobalStates()
@@ -25,21 +60,10 @@ _G = GlobalStates()
 
 def set_global_states(config, tokenizer=None) -> GlobalStates:
     """Create the singletons once; records the tokenizer's vocabulary sizes in the model config."""
-    _G.config = config
-    _G.logger = IronCoreLogger(level=config.utils.log_level, rank=max(config.parallel.rank, 0))
-    _G.timer = Timer()
-    _G.tokenizer = tokenizer if tokenizer is not None else build_tokenizer(config)
-    m = config.model
-    m.vocab_size = _G.tokenizer.vocab_size
-    m.padded_vocab_size = _G.tokenizer.padded_vocab_size
-    m.eod_token_id = _G.tokenizer.eod_token_id
-    m.pad_token_id = _G.tokenizer.pad_token_id
-    rank0 = max(config.parallel.rank, 0) == 0
-    if rank0 and config.utils.tensorboard_dir:
-        _G.tb = TensorboardLogger(config.utils.tensorboard_dir, config.trainer.model_name)
-    if rank0 and config.utils.mlflow_tracking_uri:
-        _G.mlflow = MLFlowLogger(config.utils.mlflow_tracking_uri, config.utils.mlflow_experiment_name,
-                                 config.trainer.model_path, config.trainer.model_name)
+    return _G.setup(config, tokenizer)
+
+
+def get_global_states() -> GlobalStates:
     return _G
 
 

@@ -74,7 +74,17 @@ class BaseModule(nn.Module):
         return next(self.parameters()).dtype
 
     # -- NVTX / torch.profiler ranges around every submodule's forward and backward --
-    def register_profile_hooks(self, use_nvtx: bool = True, use_record_function: bool = True):
+    def save_to_state_dict(self, destination, prefix, keep_vars):
+        return super()._save_to_state_dict(destination, prefix, keep_vars)
+
+    def register_profile_hooks(self, use_nvtx: bool = True, use_record_function: bool = True,
+                               profile_torch=None, profile_nsys=None):
+        """``profile_torch`` / ``profile_nsys`` are the reference's names for ``use_record_function`` /
+        ``use_nvtx`` (ironcore/layers/module.py:208-232)."""
+        if profile_torch is not None:
+            use_record_function = bool(profile_torch)
+        if profile_nsys is not None:
+            use_nvtx = bool(profile_nsys)
         if self._profile_handles:
             return
         nvtx_ok = use_nvtx and torch.cuda.is_available()

@@ -166,8 +166,12 @@ class LanguageModel(BaseModule):
         if loss_mask is not None:
             mask = mask & (loss_mask.to(torch.bool))
         m = self.config.model
-        if self.eod_mask_loss and m.eod_token_id is not None:
-            mask = mask & (input_ids != m.eod_token_id)
+        if self.eod_mask_loss:
+            # the masked positions are those whose *target* is the end-of-document or the padding token
+            # (ironcore/language_model.py:118-125), not those whose input is
+            for tok in (m.eod_token_id, m.pad_token_id):
+                if tok is not None:
+                    mask = mask & (labels != tok)
         return mask
 
     def hidden_states(self, input_ids, position_ids=None, cu_seqlens=None, attn_mask=None):
@@ -252,6 +256,58 @@ class LanguageModel(BaseModule):
         x, _aux = self.hidden_states(input_ids)
         ce = self.per_token_loss(x, labels.reshape(-1).clamp_min(-1))
         return -ce.view(b, s)
+
+    # ------------------------------------------------------------------ the reference's helper methods
+    def get_masks_and_position_ids(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None):
+        """``(attention_mask [B, 1, S, S] bool, position_ids [B, S], loss_mask [B, S] float)`` as the reference
+        builds them for every batch (ironcore/language_model.py:102-161): causal mask, cut at document boundaries
+        with ``reset_attention_mask``; positions restarting after an end-of-document token with
+        ``reset_position_ids``; loss mask zero where the *label* is the end-of-document or padding token with
+        ``eod_mask_loss``. ``forward`` does not need them (it hands document boundaries to the attention kernel);
+        they serve callers that want the explicit tensors."""
+        b, s = input_ids.shape
+        dev = input_ids.device
+        mask = torch.ones(s, s, dtype=torch.bool, device=dev).tril().expand(b, 1, s, s)
+        pos, cu = self._document_layout(input_ids)
+        if cu is not None:
+            mask = mask & OF.document_mask(cu, b, s, dev)
+        if pos is None:
+            pos = torch.arange(s, device=dev).expand(b, s)
+        loss_mask = torch.ones(b, s, dtype=torch.float, device=dev)
+        m = self.config.model
+        if self.eod_mask_loss and labels is not None:
+            for tok in (m.eod_token_id, m.pad_token_id):
+                if tok is not None:
+                    loss_mask = loss_mask.masked_fill(labels == tok, 0.0)
+        return mask, pos, loss_mask
+
+    def compute_loss_from_logits(self, logits: torch.Tensor, labels: torch.Tensor, loss_mask: torch.Tensor,
+                                 fp16_lm_cross_entropy: bool = False, padding_start_idx: Optional[int] = None):
+        """Loss of (vocabulary-sharded) ``logits`` [B, S, V/t] against ``labels`` [B, S] through the
+        vocab-parallel cross entropy and the model's loss function; labels of ``-100`` are left out.
+        ``padding_start_idx`` defaults to the real vocabulary size. (ironcore/language_model.py:163-201)"""
+        if not fp16_lm_cross_entropy:
+            logits = logits.float()
+        vocab = self.vocab_size if padding_start_idx is None else padding_start_idx
+        per_token = vocab_parallel_cross_entropy(logits, labels.contiguous().clamp_min(-1), vocab,
+                                                 tp_group=self.tp_group)
+        mask = loss_mask.to(per_token.dtype) * (labels != IGNORE_INDEX).to(per_token.dtype)
+        return self.loss_fn(per_token.view(labels.shape), mask)
+
+    def post_lm_processing(self, lm_output: torch.Tensor, labels: Optional[torch.Tensor] = None,
+                           loss_mask: Optional[torch.Tensor] = None, fp16_lm_cross_entropy: bool = False,
+                           padding_start_idx: Optional[int] = None):
+        """LM head on normalised hidden states ``[B, S, d]``: the (vocabulary-sharded) logits without labels, the
+        loss with them. (ironcore/language_model.py:203-234)"""
+        lead = lm_output.shape[:-1]
+        logits = self.logits_from_hidden(lm_output.reshape(-1, lm_output.shape[-1]))
+        logits = logits.view(*lead, -1) if logits.shape[0] == lead.numel() else logits
+        if labels is None:
+            return logits
+        if loss_mask is None:
+            loss_mask = torch.ones(labels.shape, dtype=torch.float, device=labels.device)
+        return self.compute_loss_from_logits(logits.view(*labels.shape, -1), labels, loss_mask,
+                                             fp16_lm_cross_entropy, padding_start_idx)
 
     def link_fused_norm_gather(self) -> int:
         """See ``TransformerModel.link_fused_norm_gather``; called once the fused tensor-parallel

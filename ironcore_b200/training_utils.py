@@ -39,13 +39,18 @@ def forward_step(model, data_iterator):
     for key in ("position_ids", "cu_seqlens", "loss_mask"):
         if key in batch and batch[key] is not None:
             kwargs[key] = batch[key]
+    if batch.get("attention_mask") is not None and "cu_seqlens" not in kwargs:
+        m = batch["attention_mask"]           # [rows, S, S] block mask of the packed samples
+        kwargs["attn_mask"] = m.unsqueeze(1) if m.dim() == 3 else m
     return model(batch["input_ids"], batch["labels"], **kwargs)
 
 
 @torch.no_grad()
-def compute_token_accuracy(logits: torch.Tensor, labels: torch.Tensor, tp_group="default") -> float:
-    """Fraction of unmasked positions whose arg-max (over the full, possibly sharded, vocab)
-    equals the label."""
+def compute_token_accuracy(logits: torch.Tensor, labels: torch.Tensor, loss_mask=None, tp_group="default") -> float:
+    """Fraction of counted positions whose arg-max (over the full, possibly sharded, vocab) equals the
+    label. Counted: labels other than -100, and where ``loss_mask`` (optional, [B, S]) is non-zero."""
+    if isinstance(loss_mask, str) or (loss_mask is not None and not torch.is_tensor(loss_mask)):
+        loss_mask, tp_group = None, loss_mask      # (logits, labels, tp_group) positional form
     group = mesh.get_tensor_model_parallel_group() if tp_group == "default" else tp_group
     v_local = logits.shape[-1]
     vals, idx = logits.float().max(dim=-1)
@@ -59,5 +64,7 @@ def compute_token_accuracy(logits: torch.Tensor, labels: torch.Tensor, tp_group=
         best = torch.stack(all_vals).argmax(dim=0, keepdim=True)
         idx = torch.stack(all_idx).gather(0, best).squeeze(0)
     mask = labels != IGNORE_INDEX
+    if loss_mask is not None:
+        mask = mask & (loss_mask > 0)
     correct = ((idx == labels) & mask).sum().item()
     return correct / max(int(mask.sum().item()), 1)

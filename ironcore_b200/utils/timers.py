@@ -71,6 +71,32 @@ class Timer:
         for n in ([name] if name else list(self.timers)):
             self(n).reset()
 
+    # -- the reference's remaining timer calls (ironcore/utils.py:153-216) --
+    def register(self, name):
+        if name in self.timers:
+            raise KeyError(f"Requested timer ({name}) is already registered")
+        self.timers[name] = _HostTimer(name)
+
+    def get(self, name) -> float:
+        """Mean lap time of ``name`` in seconds; a running timer is stopped first."""
+        if name not in self.timers:
+            raise KeyError(f"Not initialized timer ({name}) is requested")
+        t = self.timers[name]
+        if t._t0 is not None:
+            t.stop()
+        return t.elapsed()
+
+    def get_summary(self) -> Dict[str, float]:
+        return {n: t.elapsed() for n, t in self.timers.items() if t.laps}
+
+    def reset_all(self):
+        self.reset()
+
+    def stop_all(self):
+        for t in self.timers.values():
+            if t._t0 is not None:
+                t.stop()
+
 
 class DeviceTimer:
     """CUDA-event timer on the current stream; ``elapsed_ms`` synchronises on the end event."""

@@ -245,3 +245,171 @@ def test_weight_mapper_reference_dialect(compat_path):
     assert set(again) == set(ic) and all(torch.equal(again[k], ic[k]) for k in ic)
     assert torch.equal(mapper.ironcore_to_hf(live)["transformer.h.1.attn.c_attn.weight"],
                        hf["transformer.h.1.attn.c_attn.weight"])
+
+
+def test_reference_signatures_of_helpers(compat_path, tmp_path):
+    """Constructors and helpers under the reference's signatures: loggers, timers, tokenizer wrapper, schedules,
+    gradient clipping, configuration module paths."""
+    import logging
+
+    from ironcore.config.config_trainer import InitConfig, OperationConfig, TrainerConfig  # noqa: F401
+    from ironcore.config.config_model import ModelConfig, PositionalEmbeddingConfig  # noqa: F401
+    from ironcore.config import print_args
+    from ironcore.logger import IronCoreLogger, LevelFormatter, TensorboardLogger
+    from ironcore.optimizer.lr_scheduler import CosineAnnealingLR
+    from ironcore.optimizer.optimizer import AdamWOptimizer
+    from ironcore.tokenizer.tokenizer import Tokenizer
+    from ironcore.utils import Timer, bytes_to_mib, clip_grad_norm_tp, get_memory_usage, profile_context
+
+    cfg = _layer_config()
+    cfg.utils.tensorboard_dir = str(tmp_path / "tb")
+    cfg.trainer.model_name = "m"
+    cfg.parallel.rank = 0
+    print_args(cfg)
+    log = IronCoreLogger(config=cfg, name="compat-test", level=logging.WARNING)
+    log.set_log_level(logging.INFO)
+    log.info("plain %s", "message")
+    log.log_metrics({"hellaswag": {"accuracy": 25.0, "samples": 4}}, msg="evaluation score")
+    assert LevelFormatter("%(message)s", level_formats={logging.ERROR: "E %(message)s"}).format(
+        logging.LogRecord("x", logging.ERROR, "f", 1, "boom", None, None)) == "E boom"
+    tb = TensorboardLogger(cfg)
+    tb.add_scalar("loss", 1.0, 0)
+    tb.close()
+    assert (tmp_path / "tb" / "m").is_dir()
+
+    t = Timer()
+    t.register("a")
+    with pytest.raises(KeyError):
+        t.register("a")
+    t.start("a")
+    assert t.get("a") >= 0.0 and "a" in t.get_summary()
+    t.start("a")
+    t.stop_all()
+    t.reset_all()
+    assert t.get_summary() == {} and bytes_to_mib(3 << 20) == 3 and isinstance(get_memory_usage(in_mib=True), dict)
+    with profile_context("tag"):
+        pass
+
+    class _Backend:                                  # the surface of a HuggingFace tokenizer that the wrapper reads
+        eos_token, eos_token_id, pad_token, pad_token_id, vocab_size = "<eos>", 9, None, None, 10
+
+        def __len__(self):
+            return 12
+
+        def encode(self, text):
+            return [1, 2]
+
+        def decode(self, ids):
+            return "ab"
+
+        def __call__(self, text):
+            return {"input_ids": self.encode(text)}
+
+    tok = Tokenizer(_Backend(), "somewhere", vocab_padding_unit=8)
+    assert (tok.vocab_size, tok.padded_vocab_size, tok.eos_token_id, tok.eod_token_id, tok.pad_token_id) == (12, 16, 9, 9, 9)
+    assert tok("x")["input_ids"] == [1, 2] and tok.decode([1, 2]) == "ab" and tok.decode([]) == "" and tok.pad_token == "<eos>"
+
+    p = torch.nn.Parameter(torch.ones(4))
+    opt = AdamWOptimizer([p], lr=1.0, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, amsgrad=False)
+    sched = CosineAnnealingLR(opt, 2, 4, 10, max_lr=1.0, min_lr=0.1)
+    assert opt.param_groups[0]["lr"] == pytest.approx(0.5)
+    sched.step()
+    assert opt.param_groups[0]["lr"] == pytest.approx(1.0)
+    p.grad = torch.full((4,), 3.0)
+    norm = clip_grad_norm_tp([p], max_norm=3.0)
+    assert norm.item() == pytest.approx(6.0) and p.grad.norm().item() == pytest.approx(3.0, rel=1e-4)
+
+
+def test_reference_style_huggingface_directory_round_trip(compat_path, tmp_path):
+    """``load_from_huggingface(path, model)`` / ``export_to_huggingface(model, path, architecture=...)`` on a
+    directory written by ``transformers``: same logits, same tensors back."""
+    transformers = pytest.importorskip("transformers")
+    from ironcore.checkpointing import export_to_huggingface, load_from_huggingface
+    from ironcore.checkpointing.hf_interop import detect_checkpoint_format, load_hf_config, load_hf_state_dict
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.models.language_model import LanguageModel
+    from ironcore_b200.parallel import mesh
+    from helpers import tiny_config
+
+    hcfg = transformers.LlamaConfig(vocab_size=96, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                                    num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=32,
+                                    rms_norm_eps=1e-5, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    hf = transformers.LlamaForCausalLM(hcfg).eval()
+    src = tmp_path / "hf_in"
+    hf.save_pretrained(src, safe_serialization=True)
+    assert load_hf_config(src)["model_type"] == "llama" and detect_checkpoint_format(src)
+    assert "model.embed_tokens.weight" in load_hf_state_dict(src, device="cpu")
+
+    mesh.destroy_model_parallel()
+    cfg = tiny_config("llama", d_model=32, d_ffn=64, num_attention_heads=4, num_attention_groups=2, head_dim=8,
+                      vocab_size=96, ln_eps=1e-5, hf_model_type="llama")
+    cfg.data.vocab_size = 96
+    validate_config(cfg)
+    model = LanguageModel(cfg).eval()
+    info = load_from_huggingface(src, model)
+    assert info["missing_keys"] == [] and "embedding.word_embeddings.weight" in info["loaded_keys"]
+    ids = torch.randint(0, 96, (2, 16))
+    with torch.no_grad():
+        assert torch.allclose(model(ids)[..., :96], hf(ids).logits, atol=2e-4)
+    out = export_to_huggingface(model, tmp_path / "hf_out", architecture="llama")
+    assert out["config_file"] and out["files"]
+    back = load_hf_state_dict(tmp_path / "hf_out")
+    for k, v in hf.state_dict().items():
+        assert torch.allclose(back[k], v, atol=1e-6), k
+
+
+def test_reference_helper_methods_of_the_language_model(compat_path):
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.models.language_model import LanguageModel
+    from ironcore_b200.parallel import mesh
+    from helpers import tiny_config
+
+    mesh.destroy_model_parallel()
+    cfg = tiny_config("gpt2")
+    cfg.model(reset_position_ids=True, reset_attention_mask=True, eod_mask_loss=True, eod_token_id=7, pad_token_id=0)
+    validate_config(cfg)
+    model = LanguageModel(cfg).eval()
+    ids = torch.tensor([[3, 4, 7, 5, 6, 7, 8, 9]])
+    labels = torch.tensor([[4, 7, 5, 6, 7, 8, 9, 0]])
+    mask, pos, lmask = model.get_masks_and_position_ids(ids, labels)
+    assert pos.tolist() == [[0, 1, 2, 0, 1, 2, 0, 1]]
+    assert mask.shape == (1, 1, 8, 8) and bool(mask[0, 0, 4, 3]) and not bool(mask[0, 0, 3, 2]) and not bool(mask[0, 0, 1, 2])
+    assert lmask.tolist() == [[1, 0, 1, 1, 0, 1, 1, 0]]
+    with torch.no_grad():
+        logits = model(ids)
+        loss = model(ids, labels)
+        again = model.compute_loss_from_logits(logits, labels, lmask)
+        hidden, _ = model.hidden_states(ids)
+        assert torch.allclose(model.post_lm_processing(hidden.view(1, 8, -1)), logits, atol=1e-5)
+        assert torch.allclose(model.post_lm_processing(hidden.view(1, 8, -1), labels, lmask), again, atol=1e-6)
+    assert loss.item() == pytest.approx(again.item(), rel=1e-5)
+
+
+def test_reference_data_constructors(compat_path, tmp_path):
+    import numpy as np
+
+    from ironcore.dataloader import BinaryDataset, DataConfig, WeightedMixingDataset, create_collator, load_data_config
+    from ironcore_b200.data.serializer import BIN_NAME, IDX_DTYPE, IDX_NAME
+
+    d = tmp_path / "pre" / "toy" / "pretrain"
+    d.mkdir(parents=True)
+    toks = (np.arange(400) % 50).astype(np.uint16)
+    toks.tofile(d / BIN_NAME)
+    idx = np.zeros(4, dtype=IDX_DTYPE)
+    idx["offset"], idx["length"], idx["type"] = [0, 100, 200, 300], 100, "pretrain"
+    np.save(d / IDX_NAME, idx)
+    y = tmp_path / "data.yaml"
+    y.write_text(f"train_datasets:\n  - name: toy\n    source: none\n    task_type: pretrain\n    ratio: 1.0\n"
+                 f"seq_length: 16\nsplits: [1.0, 0.0, 0.0]\npreprocessed_dir: {tmp_path / 'pre'}\n")
+    dcfg = load_data_config(y)
+    assert isinstance(dcfg, DataConfig) and dcfg.get_dataset_output_path(dcfg.datasets[0]) == d
+    ds = BinaryDataset(d / BIN_NAME, d / IDX_NAME)
+    assert ds.total_tokens() == 400 and len(ds) == 4 and len(ds[1]["token_ids"]) == 100
+    mix = WeightedMixingDataset(dcfg, mode="pretrain", seed=1, split="train")
+    first = next(iter(mix))
+    assert len(first["tokens"]) == 17
+    coll = create_collator("sft", 8, pad_token_id=0, return_full_attention_mask=True, use_flash_attention=False)
+    batch = coll([{"tokens": np.arange(1, 6), "mask_ranges": [[0, 2]]}, {"tokens": np.arange(1, 4), "mask_ranges": []}])
+    m = batch["attention_mask"]
+    assert "cu_seqlens" not in batch and m.shape == (1, 8, 8) and bool(m[0, 4, 0]) and not bool(m[0, 5, 4]) and bool(m[0, 6, 5])
