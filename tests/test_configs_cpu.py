@@ -94,3 +94,32 @@ def test_data_preset_parses(path):
 
     cfg = UniversalDataConfig.from_yaml(path) if hasattr(UniversalDataConfig, "from_yaml") else UniversalDataConfig(**y)
     assert cfg.datasets and cfg.seq_length > 0 and abs(sum(d.ratio for d in cfg.datasets) - 1.0) < 1e-6
+
+
+def test_every_configuration_field_is_documented():
+    """configs/README.md lists every field of every configuration group (name in the group's table)."""
+    from dataclasses import fields, is_dataclass
+
+    from ironcore_b200.config import default_config
+
+    text = open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs", "README.md")).read()
+    sections = {}
+    current = None
+    for line in text.split("\n"):
+        if line.startswith("###"):
+            current = line.lstrip("# ").strip()
+            sections[current] = []
+        elif current is not None and line.startswith("| `"):
+            sections[current].append(line.split("`")[1])
+
+    def check(node, title):
+        assert title in sections, f"group {title} has no table"
+        for f in fields(node):
+            assert f.name in sections[title], f"{title}.{f.name} is not documented"
+            v = getattr(node, f.name)
+            if is_dataclass(v):
+                check(v, f"{title}.{f.name}")
+
+    cfg = default_config()
+    for f in fields(cfg):
+        check(getattr(cfg, f.name), f.name)
