@@ -334,3 +334,49 @@ def test_constructed_baselines_run_tiny_on_cpu():
         assert out.returncode == 0, out.stderr[-1500:]
         line = json.loads(out.stdout.strip().splitlines()[-1])
         assert line["workload"] == workload and line["value"] > 0
+
+
+# ------------------------------------------------------------------ tracing
+def test_torch_profiler_window_stops_training_and_writes_a_trace(tmp_path):
+    """``utils.profile_torch``: the profiler runs over [profile_step_start, profile_step_end), training stops when
+    the window ends, a trace lands under ``utils.tensorboard_dir`` and no final checkpoint is written."""
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.trainer import Trainer
+
+    mesh.destroy_model_parallel()
+    cfg = tiny_config("gpt2")
+    cfg.trainer.model_path = str(tmp_path / "ck")
+    cfg.operation.train_steps = 10
+    cfg.utils(profile_torch=True, profile_step_start=1, profile_step_end=3, tensorboard_dir=str(tmp_path / "tb"),
+              profile_ranks=[0])
+    validate_config(cfg)
+    tr = Trainer(cfg)
+    last = tr.train()
+    assert last == 2                                   # steps 0, 1, 2 ran; the window ended at step 3
+    traces = [p for p in (tmp_path / "tb").rglob("*") if p.is_file() and "trace" in p.name]
+    assert traces, list((tmp_path / "tb").rglob("*"))
+    assert not (tmp_path / "ck").exists() or not any((tmp_path / "ck").glob("step_*"))
+
+
+def test_module_profile_hooks_put_ranges_into_a_trace():
+    """``BaseModule.register_profile_hooks``: every submodule's forward and backward appear as named ranges."""
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.models.language_model import LanguageModel
+    from ironcore_b200.parallel import mesh
+
+    mesh.destroy_model_parallel()
+    cfg = tiny_config("gpt2")
+    validate_config(cfg)
+    model = LanguageModel(cfg)
+    model.register_profile_hooks(profile_torch=True, profile_nsys=False)
+    ids = torch.randint(0, 512, (2, 16))
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU]) as prof:
+        model(ids, ids).backward()
+    names = {e.key for e in prof.key_averages()}
+    assert any(n.startswith("Forward TransformerLayer") for n in names), sorted(names)[:20]
+    assert any(n.startswith("Forward MLP") for n in names)
+    model.remove_profile_hooks()
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU]) as prof:
+        model(ids, ids)
+    assert not any(e.key.startswith("Forward TransformerLayer") for e in prof.key_averages())
