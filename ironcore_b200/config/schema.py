@@ -9,7 +9,6 @@ expert parallelism, ZeRO, MoE, Muon, RL rollouts, CPU offload) are added here.
 
 from __future__ import annotations
 
-import dataclasses
 import typing
 from dataclasses import dataclass, field, fields, is_dataclass
 from typing import Any, Dict, List, Literal, Optional, Union

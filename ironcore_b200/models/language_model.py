@@ -17,7 +17,6 @@ from collections import OrderedDict
 from typing import Callable, Dict, Optional
 
 import torch
-import torch.nn as nn
 
 from ..layers.embedding import LanguageModelEmbedding
 from ..layers.module import BaseModule, init_parameters
@@ -25,7 +24,7 @@ from ..layers.norm import get_norm
 from ..ops import functional as OF
 from ..parallel import collectives as C
 from ..parallel import mesh
-from ..parallel.tensor_parallel import ColumnParallelLinear, shard_tensor, vocab_parallel_cross_entropy
+from ..parallel.tensor_parallel import ColumnParallelLinear, vocab_parallel_cross_entropy
 from .families import resolve_family_defaults
 
 IGNORE_INDEX = -100

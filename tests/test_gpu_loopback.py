@@ -3,7 +3,6 @@ reduce-scatter + norm + gather producer (the peer tables point at the GPU's own 
 "two-rank" call whose second rank does not exist makes the bounded waits run out: the kernels must
 return by themselves with a status code, and the device must stay usable."""
 
-import ctypes as C
 
 import pytest
 import torch

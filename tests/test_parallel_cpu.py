@@ -2,8 +2,6 @@
 single-rank model, ZeRO-1 equivalence with the replicated optimizer, universal checkpoints
 across TP sizes."""
 
-import os
-
 import pytest
 import torch
 
