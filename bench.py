@@ -253,6 +253,9 @@ def run_ours(args):
             "config": {"model": "llama-7b-shape (32L, d4096, 32h x 128, ffn 11008 swiglu, vocab 32000)",
                        "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN, "micro_batch": 1,
                        "parallelism": f"tp{world}" + ("+sp" if world > 1 else "") + "+zero1",
+                       # tensor parallel over every GPU leaves one data-parallel replica: ZeRO-1 is configured
+                       # (flat buffers, sharded-state code path) but has nothing to shard at this layout
+                       "data_parallel_size": 1,
                        "tp_comm": ("fused in-kernel (all-gather->GEMM: "
                                    + ("NVLS multimem.st" if getattr(fused_ws, "nvls_ag", False) else "P2P stores")
                                    + ", GEMM->reduce-scatter: "
