@@ -278,4 +278,12 @@ def validate_config(config: MainConfig) -> MainConfig:
         raise ValueError(f"unknown optimizer {config.optim.optimizer}")
     if not torch.cuda.is_available() and p.dist_backend == "nccl":
         p.dist_backend = "gloo"
+    import warnings
+
+    if m.fp32_residual_connection:
+        warnings.warn("model.fp32_residual_connection has no effect: the residual stream stays in the parameter "
+                      "dtype (residual adds run in fp32 inside the GEMM and norm kernels)", stacklevel=2)
+    if t.compile_model:
+        warnings.warn("trainer.compile_model has no effect: the training step launches hand-written kernels; "
+                      "trainer.cuda_graph removes the launch overhead that torch.compile would", stacklevel=2)
     return config

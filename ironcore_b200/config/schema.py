@@ -185,7 +185,7 @@ class ModelConfig(BaseConfig):
     untie_embed: bool = opt(False, "separate LM head")
     no_bias: bool = opt(False, "no bias in linear layers and norms")
     qkv_bias: Optional[bool] = opt(None, "bias on q/k/v projections only (Qwen); None = follow no_bias")
-    fp32_residual_connection: bool = opt(False, "keep the residual stream in fp32")
+    fp32_residual_connection: bool = opt(False, "accepted for compatibility: the residual stream stays in the parameter dtype (sums inside the kernels are fp32); a warning is issued when set")
     fp16_lm_cross_entropy: bool = opt(False, "cross entropy in 16-bit")
     ln_type: str = opt("layernorm", "layernorm | rmsnorm")
     ln_eps: float = opt(1e-5, "norm epsilon")
@@ -335,7 +335,7 @@ class UtilsConfig(BaseConfig):
     profile_step_start: Optional[int] = opt(10, "first profiled step")
     profile_step_end: Optional[int] = opt(12, "last profiled step")
     profile_ranks: Optional[List[int]] = opt([0], "ranks that profile")
-    stop_on_profile_end: bool = opt(False, "stop training when profiling ends")
+    stop_on_profile_end: bool = opt(False, "accepted for compatibility: training always stops when a profiling window ends, as in the reference")
     deterministic: bool = opt(False, "deterministic algorithms")
     report_memory_usage: bool = opt(True, "memory report at the first log step")
     tensorboard_dir: Optional[str] = opt(None, "tensorboard directory")
