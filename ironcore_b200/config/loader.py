@@ -176,11 +176,23 @@ def apply_env_ranks(config: MainConfig) -> MainConfig:
 
 
 def _load_special_tokens(config: MainConfig) -> None:
+    """Read ``trainer.special_tokens_config_path`` (JSON or YAML: token attribute -> value, e.g. ``eos_token``,
+    ``pad_token``, ``eod_token``, or ``*_token_id`` integers) into ``config.data.special_tokens``; the tokenizer
+    applies it. A relative path is looked up under ``model.vocab_name_or_path``, then ``trainer.model_path``, then
+    the working directory. (Reference: ironcore/config/__init__.py:492-511, ironcore/tokenizer/tokenizer.py:38-40.)"""
     path = config.trainer.special_tokens_config_path
-    if not path:
+    if not path or getattr(config.data, "special_tokens", None):
         return
-    doc = load_yaml_config(path)
-    setattr(config.data, "special_tokens", doc)
+    candidates = [Path(path)]
+    if not Path(path).is_absolute():
+        for base in (config.model.vocab_name_or_path, config.trainer.model_path):
+            if base:
+                candidates.insert(len(candidates) - 1, Path(base) / path)
+    for cand in candidates:
+        if cand.exists():
+            setattr(config.data, "special_tokens", load_yaml_config(cand))    # (JSON is a subset of YAML)
+            return
+    raise FileNotFoundError(f"Could not find special token config file: {candidates[0]}")
 
 
 def load_trainer_config(argv: Optional[Sequence[str]] = None) -> MainConfig:
@@ -194,7 +206,6 @@ def load_trainer_config(argv: Optional[Sequence[str]] = None) -> MainConfig:
     apply_env_ranks(config)
     if ns.cli_local_rank is not None:
         config.parallel.local_rank = ns.cli_local_rank
-    _load_special_tokens(config)
     validate_config(config)
     return config
 
@@ -278,6 +289,7 @@ def validate_config(config: MainConfig) -> MainConfig:
         raise ValueError(f"unknown optimizer {config.optim.optimizer}")
     if not torch.cuda.is_available() and p.dist_backend == "nccl":
         p.dist_backend = "gloo"
+    _load_special_tokens(config)
     import warnings
 
     if m.fp32_residual_connection:

@@ -77,12 +77,24 @@ def build_tokenizer(config) -> Tokenizer:
     hf = None
     if getattr(config.data, "task_type", "pretrain") != "synthetic":
         hf = _try_hf(m.vocab_name_or_path, ttype)
+    special = dict(getattr(config.data, "special_tokens", None) or {})
     if hf is not None:
+        for name, value in special.items():      # token strings (eos_token, pad_token, ...) of the backend
+            if not name.endswith("_id"):
+                setattr(hf, name, value)
         eos = hf.eos_token_id if hf.eos_token_id is not None else len(hf) - 1
         tok = Tokenizer(len(hf), eos, hf.pad_token_id, unit, tp, backend=hf, eos_token=hf.eos_token or "")
+        eod = getattr(hf, "eod_token", None)
+        if eod is not None:
+            tok.eod_token_id = int(hf.convert_tokens_to_ids(eod))
     else:
         vocab = m.vocab_size or _KNOWN_VOCAB.get(ttype) or config.data.vocab_size
         eos = vocab - 1
         pad = config.data.pad_token_id
-        tok = Tokenizer(vocab, eos, pad, unit, tp)
+        tok = Tokenizer(vocab, eos, pad, unit, tp, eos_token=special.get("eos_token", "<|endoftext|>"))
+    for name in ("eos_token_id", "eod_token_id", "pad_token_id"):    # explicit ids win on either path
+        if special.get(name) is not None:
+            setattr(tok, name, int(special[name]))
+    if "eos_token_id" in special and "eod_token_id" not in special:
+        tok.eod_token_id = tok.eos_token_id
     return tok

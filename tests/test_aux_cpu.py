@@ -380,3 +380,25 @@ def test_module_profile_hooks_put_ranges_into_a_trace():
     with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU]) as prof:
         model(ids, ids)
     assert not any(e.key.startswith("Forward TransformerLayer") for e in prof.key_averages())
+
+
+def test_special_tokens_file_reaches_the_tokenizer(tmp_path):
+    """``trainer.special_tokens_config_path`` (looked up under the vocabulary / model path) overrides the special
+    ids the model and the data pipeline use."""
+    import json
+
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.global_vars import set_global_states
+
+    (tmp_path / "special_tokens.json").write_text(json.dumps({"eos_token": "</s>", "eos_token_id": 2, "pad_token_id": 1}))
+    cfg = tiny_config("gpt2")
+    cfg.trainer(special_tokens_config_path="special_tokens.json", model_path=str(tmp_path))
+    validate_config(cfg)
+    assert cfg.data.special_tokens["eos_token_id"] == 2
+    tok = set_global_states(cfg).tokenizer
+    assert (tok.eos_token_id, tok.eod_token_id, tok.pad_token_id, tok.eos_token) == (2, 2, 1, "</s>")
+    assert (cfg.model.eod_token_id, cfg.model.pad_token_id) == (2, 1)
+    cfg2 = tiny_config("gpt2")
+    cfg2.trainer(special_tokens_config_path="missing.json", model_path=str(tmp_path))
+    with pytest.raises(FileNotFoundError):
+        validate_config(cfg2)
