@@ -237,7 +237,7 @@ class TrainerConfig(BaseConfig):
     tensor_model_parallel_size: int = opt(1, "tensor parallel size")
     pipeline_model_parallel_size: int = opt(1, "pipeline parallel size (must be 1)")
     vocab_padding_unit: int = opt(128, "vocab padding unit")
-    special_tokens_config_path: Optional[str] = opt(None, "special token file")
+    special_tokens_config_path: Optional[str] = opt(None, "JSON / YAML file of special tokens (eos_token, pad_token, eod_token, *_token_id), looked up under model.vocab_name_or_path, then trainer.model_path")
     use_flash_attn: bool = opt(True, "fused attention kernel")
     cuda_graph: bool = opt(False, "capture one micro-batch forward+backward in a CUDA graph and replay it")
     compile_model: bool = opt(False, "accepted for compatibility; the hot path is hand-written kernels")
