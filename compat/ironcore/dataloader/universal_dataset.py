@@ -29,12 +29,13 @@ class WeightedMixingDataset(_ds.WeightedMixingDataset):
     """``WeightedMixingDataset(data_config, mode, seed, split)``; this rank's share of the data follows the
     data-parallel layout of the initialised mesh (rank 0 of 1 without one)."""
 
-    def __init__(self, data_config, mode: str = "pretrain", seed: int = 1337, split: str = "train", **kw):
+    def __init__(self, data_config, mode: str = "pretrain", seed: int = 1337, split: str = "train", dp_rank=None,
+                 dp_size=None, epochs=None, seq_len=None):
         from ironcore_b200.parallel import mesh
 
-        made = _ds.WeightedMixingDataset.from_data_config(
-            data_config, mode, seed, split, kw.pop("dp_rank", mesh.get_data_parallel_rank()),
-            kw.pop("dp_size", mesh.get_data_parallel_world_size()), **kw)
-        self.__dict__.update(made.__dict__)
-        self.config, self.max_seq_len = data_config, made.seq_len
+        super().__init__(seq_len=seq_len or data_config.max_seq_len, seed=seed, epochs=epochs,
+                         dp_rank=mesh.get_data_parallel_rank() if dp_rank is None else dp_rank,
+                         dp_size=mesh.get_data_parallel_world_size() if dp_size is None else dp_size,
+                         **self.sources_of(data_config, mode, split))
+        self.config, self.max_seq_len = data_config, self.seq_len
         self.datasets = self.sets

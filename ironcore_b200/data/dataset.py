@@ -84,12 +84,11 @@ class WeightedMixingDataset(IterableDataset):
         self.epochs = epochs
         self.cursor = 0          # samples yielded so far on this rank (saved in checkpoints)
 
-    @classmethod
-    def from_data_config(cls, data_config, mode: str = "pretrain", seed: int = 1337, split: str = "train",
-                         dp_rank: int = 0, dp_size: int = 1, epochs: Optional[int] = None, seq_len: Optional[int] = None):
-        """The mixing dataset of one split of a dataset YAML (``UniversalDataConfig``): the split's own dataset
-        list when it has one (used whole), else the split's share of the training datasets; only datasets of
-        task type ``mode`` take part."""
+    @staticmethod
+    def sources_of(data_config, mode: str, split: str) -> Dict:
+        """Directories, ratios and split ratios of one split of a dataset YAML (``UniversalDataConfig``): the
+        split's own dataset list when it has one (used whole), else the split's share of the training datasets;
+        only datasets of task type ``mode`` take part."""
         own = {"train": data_config.datasets, "eval": data_config.eval_datasets, "test": data_config.test_datasets}
         if split not in own:
             raise ValueError(f"Invalid split: {split}")
@@ -98,9 +97,15 @@ class WeightedMixingDataset(IterableDataset):
                    if d.task_type == mode]
         if not sources:
             raise ValueError(f"no {mode} dataset for split {split}")
-        return cls([d.output_path for d in sources], [d.ratio for d in sources], mode, "train" if separate else split,
-                   seq_len or data_config.max_seq_len, [1.0, 0.0, 0.0] if separate else data_config.splits, seed=seed,
-                   dp_rank=dp_rank, dp_size=dp_size, epochs=epochs)
+        return dict(directories=[d.output_path for d in sources], ratios=[d.ratio for d in sources], mode=mode,
+                    split="train" if separate else split,
+                    splits=[1.0, 0.0, 0.0] if separate else list(data_config.splits))
+
+    @classmethod
+    def from_data_config(cls, data_config, mode: str = "pretrain", seed: int = 1337, split: str = "train",
+                         dp_rank: int = 0, dp_size: int = 1, epochs: Optional[int] = None, seq_len: Optional[int] = None):
+        return cls(seq_len=seq_len or data_config.max_seq_len, seed=seed, dp_rank=dp_rank, dp_size=dp_size,
+                   epochs=epochs, **cls.sources_of(data_config, mode, split))
 
     def _pretrain_positions(self):
         items = []
