@@ -35,7 +35,12 @@ def run_train(args, extra_argv=None) -> int:
         with GRPOTrainer(config) as trainer:
             trainer.train()
         return 0
-    trainer = Trainer(config, forward_step_func=forward_step, loss_fn=loss_fn)
+    if str(task_type).lower() == "dpo":
+        from ..rl.dpo import DPOTrainer
+
+        trainer = DPOTrainer(config, loss_fn=loss_fn)
+    else:
+        trainer = Trainer(config, forward_step_func=forward_step, loss_fn=loss_fn)
     try:
         trainer.train()
         print("\nTraining completed successfully!")

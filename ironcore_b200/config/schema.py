@@ -375,7 +375,7 @@ class DataConfig(BaseConfig):
 # --------------------------------------------------------------------------- rl
 @dataclass
 class RLConfig(BaseConfig):
-    algorithm: str = opt("grpo", "grpo")
+    algorithm: str = opt("grpo", "grpo (rollouts + clipped policy gradient); preference pairs train with data.task_type: dpo")
     num_prompts: int = opt(64, "prompts per rollout batch")
     prompt_len: int = opt(256, "synthetic prompt length")
     group_size: int = opt(8, "samples per prompt")
@@ -389,6 +389,8 @@ class RLConfig(BaseConfig):
     reward_vocab_subset: int = opt(1024, "size of the seeded rewarded-token subset")
     reward_seed: int = opt(7, "seed of the rewarded subset / prompts")
     adv_eps: float = opt(1e-6, "epsilon in the group advantage normalisation")
+    dpo_beta: float = opt(0.1, "DPO: scale of the policy / reference log-ratio difference (data.task_type: dpo)")
+    dpo_label_smoothing: float = opt(0.0, "DPO: weight of the flipped pair's loss (conservative DPO)")
 
 
 @dataclass

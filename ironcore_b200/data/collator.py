@@ -54,8 +54,9 @@ class UniversalCollator:
         if self.mode == "sft":
             return self._sft(samples)
         if self.mode == "dpo":
-            chosen = self._sft([s["chosen"] for s in samples])
-            rejected = self._sft([s["rejected"] for s in samples])
+            # one sample per row, in order: row i of the chosen half pairs with row i of the rejected half
+            chosen = self._sft([s["chosen"] for s in samples], pack=False)
+            rejected = self._sft([s["rejected"] for s in samples], pack=False)
             out = {f"chosen_{k}": v for k, v in chosen.items()}
             out.update({f"rejected_{k}": v for k, v in rejected.items()})
             return out
@@ -65,10 +66,11 @@ class UniversalCollator:
         t = torch.from_numpy(np.stack([s["tokens"] for s in samples])).long()
         return {"input_ids": t[:, :-1].contiguous(), "labels": t[:, 1:].contiguous()}
 
-    def _sft(self, samples):
+    def _sft(self, samples, pack=None):
         cap = self.max_seq_len + 1
         lengths = [len(s["tokens"]) for s in samples]
-        bins = first_fit_decreasing(lengths, cap) if self.pack else [[i] for i in range(len(samples))]
+        pack = self.pack if pack is None else pack
+        bins = first_fit_decreasing(lengths, cap) if pack else [[i] for i in range(len(samples))]
         rows = len(bins)
         tokens = torch.full((rows, cap), self.pad, dtype=torch.long)
         labels_full = torch.full((rows, cap), IGNORE_INDEX, dtype=torch.long)

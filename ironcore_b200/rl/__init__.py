@@ -1,4 +1,5 @@
-"""Rollouts and RL: block KV cache, paged decode attention, sampling, rollout engine, GRPO."""
+"""Rollouts and RL: block KV cache, paged decode attention, sampling, rollout engine, GRPO; DPO on preference
+pairs (``rl.dpo``: imported on demand, it pulls in the trainer)."""
 
 from .grpo import VocabSubsetReward, group_advantages, grpo_loss
 from .kv_cache import BlockKVCache

@@ -36,24 +36,9 @@ class GRPOTrainer(Trainer):
         # frozen reference policy: same weights at construction time, never updated
         self.ref_model = None
         if rl.kl_beta > 0:
-            # a second model of the same layout with the policy's initial weights (modules hold
-            # process-group handles, so the policy object itself cannot be deep-copied)
-            from ..models.language_model import LanguageModel
+            from .reference_policy import frozen_copy
 
-            rng_cpu = torch.get_rng_state()
-            rng_dev = torch.cuda.get_rng_state() if self.device.type == "cuda" else None
-            self.ref_model = LanguageModel(config, self.loss_fn, device=self.device)
-            torch.set_rng_state(rng_cpu)
-            if rng_dev is not None:
-                torch.cuda.set_rng_state(rng_dev)
-            with torch.no_grad():
-                for dst, src in zip(self.ref_model.parameters(), self.model.parameters()):
-                    dst.copy_(src)
-                for dst, src in zip(self.ref_model.buffers(), self.model.buffers()):
-                    dst.copy_(src)
-            for p in self.ref_model.parameters():
-                p.requires_grad_(False)
-            self.ref_model.eval()
+            self.ref_model = frozen_copy(self.model, config, self.loss_fn, self.device)
         self.prompt_gen = torch.Generator(device="cpu").manual_seed(int(rl.reward_seed) + 1000 * mesh.get_data_parallel_rank())
         self.sample_gen = None
         if self.device.type == "cuda":

@@ -195,3 +195,30 @@ def test_pretrain_mixing_follows_the_ratios(tmp_path):
     r0 = list(WeightedMixingDataset(dirs, [0.9, 0.1], "pretrain", "train", 16, [1.0, 0.0, 0.0], dp_rank=0, dp_size=2, epochs=1))
     r1 = list(WeightedMixingDataset(dirs, [0.9, 0.1], "pretrain", "train", 16, [1.0, 0.0, 0.0], dp_rank=1, dp_size=2, epochs=1))
     assert len(r0) + len(r1) == 800 and abs(len(r0) - len(r1)) <= 1
+
+
+def test_preference_pairs_from_files_train_with_dpo(tmp_path, capsys):
+    """``ironcore preprocess`` on a file of (prompt, chosen, rejected) rows, then ``ironcore train`` with
+    ``data.task_type: dpo``: the command-line path picks the DPO trainer and runs its steps."""
+    from ironcore_b200.__main__ import main
+    from ironcore_b200.parallel import mesh
+
+    mesh.destroy_model_parallel()
+    cfg_path = _write_sources(tmp_path)
+    assert main(["preprocess", "--config", str(cfg_path)]) == 0
+    run = {"trainer": {"micro_batch_size": 2, "train_batch_size": 2, "log_interval": 1, "model_path": "",
+                       "use_flash_attn": False, "vocab_padding_unit": 8},
+           "operation": {"train_steps": 3, "no_save": True},
+           "model": {"name": "gpt2", "d_model": 32, "d_ffn": 64, "num_layers": 2, "num_attention_heads": 4,
+                     "max_seq_len": 64, "max_position_embeddings": 64, "precision": "fp32", "dropout_embd": 0.0,
+                     "dropout_attn": 0.0, "dropout_mlp": 0.0},
+           "data": {"task_type": "dpo", "config_path": str(cfg_path)},
+           "optim": {"max_lr": 1e-3, "warmup_steps": 0}, "rl": {"dpo_beta": 0.2}}
+    run_path = tmp_path / "run.yaml"
+    run_path.write_text(yaml.safe_dump(run))
+    assert main(["train", "--config", str(run_path)]) == 0
+    out = capsys.readouterr().out
+    assert "Task type: dpo" in out and "Training completed successfully" in out
+    first = [ln for ln in out.splitlines() if "step" in ln and "loss" in ln][0]
+    assert "0.693" in first           # the first step sees policy == reference: ln 2
+    mesh.destroy_model_parallel()

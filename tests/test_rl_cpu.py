@@ -1,6 +1,9 @@
 """Rollout engine and GRPO on CPU: the paged-cache decode path must reproduce the cache-less
 full-prefix forward, sampling must be exact, the loss must match its formula."""
 
+import math
+
+import pytest
 import torch
 
 from helpers import tiny_config
@@ -108,3 +111,63 @@ def test_grpo_trainer_runs_and_improves_reward_signal():
     assert st["rollout_tokens_per_s"] > 0 and abs(st["ratio_mean"] - 1.0) < 1e-3
     st2 = tr.train_step(1)
     assert st2["kl_mean"] >= 0.0
+
+
+def test_dpo_loss_against_a_plain_restatement():
+    from ironcore_b200.rl.dpo import dpo_loss
+
+    torch.manual_seed(0)
+    pc, pr, rc, rr = (torch.randn(6, dtype=torch.float64) for _ in range(4))
+    loss, stats = dpo_loss(pc, pr, rc, rr, beta=0.3, label_smoothing=0.1)
+    z = 0.3 * ((pc - rc) - (pr - rr))
+    want = (-(0.9) * torch.log(torch.sigmoid(z)) - 0.1 * torch.log(torch.sigmoid(-z))).mean()
+    assert torch.allclose(loss, want, atol=1e-12)
+    assert float(stats["reward_accuracy"]) == pytest.approx(float((z > 0).double().mean()))
+    same, _ = dpo_loss(pc, pr, pc, pr, beta=0.3)
+    assert float(same) == pytest.approx(math.log(2.0))       # policy == reference: every pair is a coin flip
+
+
+def test_dpo_trainer_learns_the_preference():
+    """Pairs that share a prompt and differ in the answer (chosen answers from one token range, rejected ones from
+    another): the loss starts at ln 2 (the reference is the policy's own copy) and falls, the implied reward of the
+    chosen answers overtakes the rejected ones, and the frozen reference does not move."""
+    import numpy as np
+
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.data.collator import UniversalCollator
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.rl.dpo import DPOTrainer
+
+    mesh.destroy_model_parallel()
+    cfg = tiny_config("llama")
+    cfg.data.task_type = "dpo"
+    cfg.trainer(micro_batch_size=4, train_batch_size=4, gradient_accumulation_steps=None)
+    cfg.optim(max_lr=3e-3, warmup_steps=0, clip_grad=1.0, lr_scheduler="constant")
+    cfg.operation.train_steps = 100
+    cfg.rl(dpo_beta=0.5)
+    validate_config(cfg)
+    rng = np.random.default_rng(0)
+    coll = UniversalCollator("dpo", cfg.model.max_seq_len, pad_token_id=0)
+
+    def batches():
+        while True:
+            rows = []
+            for _ in range(4):
+                prompt = rng.integers(300, 500, size=6)
+                good, bad = rng.integers(10, 60, size=5), rng.integers(100, 150, size=7)
+                rows.append({"chosen": {"tokens": np.concatenate([prompt, good]), "mask_ranges": [[0, 6]]},
+                             "rejected": {"tokens": np.concatenate([prompt, bad]), "mask_ranges": [[0, 6]]}})
+            yield coll(rows)
+
+    tr = DPOTrainer(cfg)
+    tr.data_iterator = {"train": batches(), "eval": None, "test": None}
+    ref_before = [p.clone() for p in tr.ref_model.parameters()]
+    losses, acc = [], []
+    for s in range(30):
+        losses.append(float(tr.train_step(s)[0]))
+        acc.append(tr.last_stats["reward_accuracy"])
+    assert losses[0] == pytest.approx(math.log(2.0), abs=1e-5)
+    assert losses[-1] < 0.5 * losses[0] and acc[-1] == 1.0, (losses, acc)
+    assert tr.last_stats["reward_chosen"] > tr.last_stats["reward_rejected"]
+    assert all(torch.equal(a, b) for a, b in zip(ref_before, tr.ref_model.parameters()))
+    assert all(not p.requires_grad for p in tr.ref_model.parameters())
