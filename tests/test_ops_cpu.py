@@ -80,3 +80,61 @@ def test_accumulate_split_policy():
         assert kernels._accumulate_split(512, 4096, 512) == 1         # 8 k-blocks: nothing to split
     finally:
         kernels._NUM_SMS = old
+
+
+def test_op_oracles_agree_with_torch_and_with_each_other():
+    """The plain restatements in ``ops/reference.py`` are the oracles of the GPU numerics tests: check them
+    against PyTorch's own operators (and the two rotary layouts against each other) in fp64-free fp32."""
+    import math
+
+    import torch.nn.functional as F
+
+    from ironcore_b200.ops import functional as OF
+    from ironcore_b200.ops import reference as R
+
+    torch.manual_seed(0)
+    x = torch.randn(5, 7, 48)
+    w, b = torch.randn(48), torch.randn(48)
+    assert torch.allclose(R.rms_norm_reference(x, w, 1e-6), torch.nn.functional.rms_norm(x, (48,), w, 1e-6), atol=1e-5)
+    assert torch.allclose(R.rms_norm_reference(x, w, 1e-6, w_offset=1.0),
+                          torch.nn.functional.rms_norm(x, (48,), w + 1.0, 1e-6), atol=1e-5)
+    assert torch.allclose(R.layer_norm_reference(x, w, b, 1e-5), F.layer_norm(x, (48,), w, b, 1e-5), atol=1e-5)
+    f, g = x.chunk(2, -1)
+    assert torch.allclose(R.glu_reference(x, "swiglu"), F.silu(f) * g)
+    assert torch.allclose(R.glu_reference(x, "glu"), F.glu(x, dim=-1))
+    assert torch.allclose(R.glu_reference(x, "geglu"), F.gelu(f, approximate="tanh") * g)
+
+    # attention against scaled_dot_product_attention, causal and with grouped keys / values
+    q, k, v = torch.randn(2, 9, 4, 16), torch.randn(2, 9, 2, 16), torch.randn(2, 9, 2, 16)
+    want = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2).repeat_interleave(2, 1),
+                                          v.transpose(1, 2).repeat_interleave(2, 1), is_causal=True).transpose(1, 2)
+    assert torch.allclose(R.attention_reference(q, k, v, causal=True), want, atol=1e-5)
+
+    # rotary: a rotation (norm preserving, invertible); dot products depend on the position difference only;
+    # the interleaved and the half-split layouts are the same map up to the permutation of the head dimension
+    pos = torch.arange(9).expand(2, 9)
+    r = R.rope_reference(q, pos, 10000.0)
+    assert torch.allclose(r.norm(dim=-1), q.norm(dim=-1), atol=1e-5)
+    assert torch.allclose(R.rope_reference(r, pos, 10000.0, inverse=True), q, atol=1e-5)
+    q1 = q[:, :1].expand(2, 9, 4, 16).contiguous()          # the same vector at every position
+    rq, rk = R.rope_reference(q1, pos, 10000.0), R.rope_reference(q1, pos + 3, 10000.0)
+    dots = (rq * rk).sum(-1)                                  # offset 3 everywhere -> the same value everywhere
+    assert torch.allclose(dots, dots[:, :1].expand_as(dots), atol=1e-4)
+    perm = torch.cat([torch.arange(0, 16, 2), torch.arange(1, 16, 2)])
+    assert torch.allclose(R.rope_reference(q, pos, 10000.0)[..., perm],
+                          R.rope_reference(q[..., perm], pos, 10000.0, interleaved=False), atol=1e-5)
+
+    # vocabulary-sharded cross entropy against F.cross_entropy, with padding columns and ignored targets
+    logits = torch.randn(12, 40)
+    tgt = torch.randint(0, 37, (12,))
+    tgt[3] = -1
+    got = OF.cross_entropy(logits, tgt, vocab_start=0, vocab_valid=37)
+    want = F.cross_entropy(logits[:, :37], tgt.clamp_min(0), reduction="none")
+    keep = tgt >= 0
+    assert torch.allclose(got[keep], want[keep], atol=1e-5) and float(got[3]) == 0.0
+    # embedding with a position table
+    table, ptab = torch.randn(30, 8), torch.randn(16, 8)
+    ids = torch.randint(0, 30, (2, 5))
+    pid = torch.arange(5).expand(2, 5)
+    assert torch.allclose(OF.embedding(ids, table, pos_table=ptab, pos_ids=pid).view(2, 5, 8), table[ids] + ptab[pid])
+    assert math.isfinite(float(got.sum()))
