@@ -30,12 +30,14 @@ from .native import merge_model_parallel_state, split_model_parallel_tensor
 class Architecture(Enum):
     GPT2 = "gpt2"
     LLAMA = "llama"
+    PHI = "phi"
 
 
 _ALIASES = {"gpt2": Architecture.GPT2, "gpt-2": Architecture.GPT2, "gpt": Architecture.GPT2, "llama": Architecture.LLAMA,
             "llama2": Architecture.LLAMA, "llama3": Architecture.LLAMA, "mistral": Architecture.LLAMA,
             "mixtral": Architecture.LLAMA, "qwen": Architecture.LLAMA, "qwen2": Architecture.LLAMA,
-            "qwen3": Architecture.LLAMA, "gemma": Architecture.LLAMA, "gemma2": Architecture.LLAMA}
+            "qwen3": Architecture.LLAMA, "gemma": Architecture.LLAMA, "gemma2": Architecture.LLAMA,
+            "phi": Architecture.PHI, "phi1": Architecture.PHI, "phi15": Architecture.PHI, "phi2": Architecture.PHI}
 
 
 def detect_architecture(model_type: Optional[str]) -> Architecture:
@@ -47,13 +49,15 @@ def detect_architecture(model_type: Optional[str]) -> Architecture:
     return _ALIASES.get(key, Architecture.GPT2 if key.startswith("gpt2") else Architecture.LLAMA)
 
 
-def _rope_perm(head_dim: int, to_interleaved: bool) -> torch.Tensor:
+def _rope_perm(head_dim: int, to_interleaved: bool, rot_dim: Optional[int] = None) -> torch.Tensor:
     """Index permutation of one head's output features between HF rotate-half order
-    (pairs (j, j + hd/2)) and interleaved order (pairs (2j, 2j + 1))."""
-    half = head_dim // 2
-    inter_from_hf = torch.empty(head_dim, dtype=torch.long)
-    inter_from_hf[0::2] = torch.arange(half)
-    inter_from_hf[1::2] = torch.arange(half) + half
+    (pairs (j, j + rot/2)) and interleaved order (pairs (2j, 2j + 1)) over the first ``rot_dim`` features (all of
+    them by default); features beyond ``rot_dim`` (partial rotary) keep their place."""
+    rot = head_dim if rot_dim is None else rot_dim
+    half = rot // 2
+    inter_from_hf = torch.arange(head_dim)
+    inter_from_hf[0:rot:2] = torch.arange(half)
+    inter_from_hf[1:rot:2] = torch.arange(half) + half
     if to_interleaved:
         return inter_from_hf
     inv = torch.empty_like(inter_from_hf)
@@ -61,9 +65,10 @@ def _rope_perm(head_dim: int, to_interleaved: bool) -> torch.Tensor:
     return inv
 
 
-def _permute_heads(w_in_out: torch.Tensor, heads: int, head_dim: int, to_interleaved: bool) -> torch.Tensor:
+def _permute_heads(w_in_out: torch.Tensor, heads: int, head_dim: int, to_interleaved: bool,
+                   rot_dim: Optional[int] = None) -> torch.Tensor:
     """Permute the output features (last dim) of a [in, heads*hd] weight or a [heads*hd] bias."""
-    perm = _rope_perm(head_dim, to_interleaved)
+    perm = _rope_perm(head_dim, to_interleaved, rot_dim)
     shape = w_in_out.shape
     x = w_in_out.reshape(*shape[:-1], heads, head_dim)
     return x[..., perm].reshape(shape)
@@ -73,10 +78,12 @@ class WeightMapper:
     """Name and layout mapping between HF state dicts and the canonical native state dict."""
 
     def __init__(self, architecture: Architecture, num_layers: int, num_heads: int, num_kv_heads: int, head_dim: int,
-                 gated_mlp: bool = True, interleaved_rope: bool = True, tie_embeddings: bool = False):
+                 gated_mlp: bool = True, interleaved_rope: bool = True, tie_embeddings: bool = False,
+                 rot_dim: Optional[int] = None):
         self.arch, self.L = architecture, num_layers
         self.h, self.g, self.hd = num_heads, num_kv_heads, head_dim
         self.gated, self.interleaved, self.tied = gated_mlp, interleaved_rope, tie_embeddings
+        self.rot = rot_dim if rot_dim is not None else head_dim     # rotated features per head (partial rotary)
 
     @classmethod
     def from_config(cls, config, architecture: Optional[Architecture] = None):
@@ -85,13 +92,70 @@ class WeightMapper:
 
         arch = architecture or detect_architecture(m.hf_model_type or m.name)
         rope = m.positional_embedding.type.lower() == "rope"
+        hd = m.head_dim or m.d_model // m.num_attention_heads
+        rot = int(hd * float(m.positional_embedding.rotary_fraction or 1.0))
         return cls(arch, m.num_layers, m.num_attention_heads, m.num_attention_groups or m.num_attention_heads,
-                   m.head_dim or m.d_model // m.num_attention_heads, is_glu(m.activation_type),
-                   bool(m.positional_embedding.interleaved) and rope, not m.untie_embed)
+                   hd, is_glu(m.activation_type), bool(m.positional_embedding.interleaved) and rope,
+                   not m.untie_embed, rot_dim=rot - rot % 2)
 
     # ------------------------------------------------------------------ HF -> native
     def hf_to_native(self, hf: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        if self.arch == Architecture.PHI:
+            return self._phi_in(hf)
         return self._gpt2_in(hf) if self.arch == Architecture.GPT2 else self._llama_in(hf)
+
+    # Phi-1 / 1.5 / 2: one LayerNorm feeding attention and MLP in parallel, biases everywhere, a plain (ungated)
+    # MLP ``fc1`` / ``fc2``, the attention output projection called ``dense``, ``final_layernorm`` and an LM head
+    # with a bias; rotary on the first ``rot_dim`` features of every head.
+    def _phi_in(self, hf):
+        pre = "model." if any(k.startswith("model.") for k in hf) else ""
+        out = {"embedding.word_embeddings.weight": hf[pre + "embed_tokens.weight"],
+               "output_layernorm.layernorm.weight": hf[pre + "final_layernorm.weight"],
+               "output_layernorm.layernorm.bias": hf[pre + "final_layernorm.bias"]}
+        for i in range(self.L):
+            p, q = f"{pre}layers.{i}.", f"model.layers.{i}."
+            w = {n: hf[p + f"self_attn.{n}_proj.weight"].t() for n in "qkv"}
+            b = {n: hf[p + f"self_attn.{n}_proj.bias"] for n in "qkv"}
+            if self.interleaved:
+                w["q"], b["q"] = (_permute_heads(t, self.h, self.hd, True, self.rot) for t in (w["q"], b["q"]))
+                w["k"], b["k"] = (_permute_heads(t, self.g, self.hd, True, self.rot) for t in (w["k"], b["k"]))
+            out[q + "linear_q.weight"], out[q + "linear_q.bias"] = w["q"], b["q"]
+            out[q + "linear_kv.weight"] = torch.cat([w["k"], w["v"]], dim=1)
+            out[q + "linear_kv.bias"] = torch.cat([b["k"], b["v"]])
+            out[q + "attn_output.weight"], out[q + "attn_output.bias"] = hf[p + "self_attn.dense.weight"].t(), hf[p + "self_attn.dense.bias"]
+            out[q + "input_layernorm.layernorm.weight"] = hf[p + "input_layernorm.weight"]
+            out[q + "input_layernorm.layernorm.bias"] = hf[p + "input_layernorm.bias"]
+            out[q + "mlp.up_proj.weight"], out[q + "mlp.up_proj.bias"] = hf[p + "mlp.fc1.weight"].t(), hf[p + "mlp.fc1.bias"]
+            out[q + "mlp.down_proj.weight"], out[q + "mlp.down_proj.bias"] = hf[p + "mlp.fc2.weight"].t(), hf[p + "mlp.fc2.bias"]
+        if not self.tied:
+            out["output_layer.weight"] = hf["lm_head.weight"].t()
+            if "lm_head.bias" in hf:
+                out["output_layer.bias"] = hf["lm_head.bias"]
+        return {k: v.contiguous() for k, v in out.items()}
+
+    def _phi_out(self, sd):
+        out = {"model.embed_tokens.weight": sd["embedding.word_embeddings.weight"],
+               "model.final_layernorm.weight": sd["output_layernorm.layernorm.weight"],
+               "model.final_layernorm.bias": sd["output_layernorm.layernorm.bias"]}
+        for i in range(self.L):
+            p, q = f"model.layers.{i}.", f"model.layers.{i}."
+            wq, bq = sd[q + "linear_q.weight"], sd[q + "linear_q.bias"]
+            (wk, wv), (bk, bv) = sd[q + "linear_kv.weight"].chunk(2, dim=1), sd[q + "linear_kv.bias"].chunk(2)
+            if self.interleaved:
+                wq, bq = (_permute_heads(t, self.h, self.hd, False, self.rot) for t in (wq, bq))
+                wk, bk = (_permute_heads(t, self.g, self.hd, False, self.rot) for t in (wk, bk))
+            for n, w_, b_ in (("q", wq, bq), ("k", wk, bk), ("v", wv, bv)):
+                out[p + f"self_attn.{n}_proj.weight"], out[p + f"self_attn.{n}_proj.bias"] = w_.t(), b_
+            out[p + "self_attn.dense.weight"], out[p + "self_attn.dense.bias"] = sd[q + "attn_output.weight"].t(), sd[q + "attn_output.bias"]
+            out[p + "input_layernorm.weight"] = sd[q + "input_layernorm.layernorm.weight"]
+            out[p + "input_layernorm.bias"] = sd[q + "input_layernorm.layernorm.bias"]
+            out[p + "mlp.fc1.weight"], out[p + "mlp.fc1.bias"] = sd[q + "mlp.up_proj.weight"].t(), sd[q + "mlp.up_proj.bias"]
+            out[p + "mlp.fc2.weight"], out[p + "mlp.fc2.bias"] = sd[q + "mlp.down_proj.weight"].t(), sd[q + "mlp.down_proj.bias"]
+        out["lm_head.weight"] = sd["output_layer.weight"].t() if "output_layer.weight" in sd \
+            else sd["embedding.word_embeddings.weight"]
+        if "output_layer.bias" in sd:
+            out["lm_head.bias"] = sd["output_layer.bias"]
+        return {k: v.contiguous() for k, v in out.items()}
 
     def _gpt2_in(self, hf):
         g = lambda k: hf[k] if k in hf else hf["transformer." + k]
@@ -124,15 +188,15 @@ class WeightMapper:
             wk = hf[p + "self_attn.k_proj.weight"].t()
             wv = hf[p + "self_attn.v_proj.weight"].t()
             if self.interleaved:
-                wq = _permute_heads(wq, self.h, self.hd, True)
-                wk = _permute_heads(wk, self.g, self.hd, True)
+                wq = _permute_heads(wq, self.h, self.hd, True, self.rot)
+                wk = _permute_heads(wk, self.g, self.hd, True, self.rot)
             out[q + "linear_q.weight"] = wq
             out[q + "linear_kv.weight"] = torch.cat([wk, wv], dim=1)
             if p + "self_attn.q_proj.bias" in hf:
                 bq, bk, bv = (hf[p + f"self_attn.{n}_proj.bias"] for n in "qkv")
                 if self.interleaved:
-                    bq = _permute_heads(bq, self.h, self.hd, True)
-                    bk = _permute_heads(bk, self.g, self.hd, True)
+                    bq = _permute_heads(bq, self.h, self.hd, True, self.rot)
+                    bk = _permute_heads(bk, self.g, self.hd, True, self.rot)
                 out[q + "linear_q.bias"] = bq
                 out[q + "linear_kv.bias"] = torch.cat([bk, bv])
             out[q + "attn_output.weight"] = hf[p + "self_attn.o_proj.weight"].t()
@@ -150,6 +214,8 @@ class WeightMapper:
 
     # ------------------------------------------------------------------ native -> HF
     def native_to_hf(self, sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        if self.arch == Architecture.PHI:
+            return self._phi_out(sd)
         return self._gpt2_out(sd) if self.arch == Architecture.GPT2 else self._llama_out(sd)
 
     def _gpt2_out(self, sd):
@@ -178,16 +244,16 @@ class WeightMapper:
             wq = sd[q + "linear_q.weight"]
             wk, wv = sd[q + "linear_kv.weight"].chunk(2, dim=1)
             if self.interleaved:
-                wq = _permute_heads(wq, self.h, self.hd, False)
-                wk = _permute_heads(wk, self.g, self.hd, False)
+                wq = _permute_heads(wq, self.h, self.hd, False, self.rot)
+                wk = _permute_heads(wk, self.g, self.hd, False, self.rot)
             out[p + "self_attn.q_proj.weight"], out[p + "self_attn.k_proj.weight"] = wq.t(), wk.t()
             out[p + "self_attn.v_proj.weight"] = wv.t()
             if q + "linear_q.bias" in sd:
                 bq = sd[q + "linear_q.bias"]
                 bk, bv = sd[q + "linear_kv.bias"].chunk(2)
                 if self.interleaved:
-                    bq = _permute_heads(bq, self.h, self.hd, False)
-                    bk = _permute_heads(bk, self.g, self.hd, False)
+                    bq = _permute_heads(bq, self.h, self.hd, False, self.rot)
+                    bk = _permute_heads(bk, self.g, self.hd, False, self.rot)
                 out[p + "self_attn.q_proj.bias"], out[p + "self_attn.k_proj.bias"], out[p + "self_attn.v_proj.bias"] = bq, bk, bv
             out[p + "self_attn.o_proj.weight"] = sd[q + "attn_output.weight"].t()
             out[p + "input_layernorm.weight"] = sd[q + "input_layernorm.layernorm.weight"]
@@ -274,6 +340,16 @@ def generate_hf_config(config) -> dict:
                 "n_positions": m.max_position_embeddings, "n_embd": m.d_model, "n_layer": m.num_layers,
                 "n_head": m.num_attention_heads, "n_inner": m.d_ffn, "activation_function": "gelu",
                 "layer_norm_epsilon": m.ln_eps, "resid_pdrop": 0.0, "embd_pdrop": 0.0, "attn_pdrop": 0.0,
+                "tie_word_embeddings": not m.untie_embed}
+    if arch == Architecture.PHI:
+        return {"model_type": "phi", "architectures": [m.hf_architecture or "PhiForCausalLM"], "vocab_size": vocab,
+                "hidden_size": m.d_model, "intermediate_size": m.d_ffn, "num_hidden_layers": m.num_layers,
+                "num_attention_heads": m.num_attention_heads,
+                "num_key_value_heads": m.num_attention_groups or m.num_attention_heads, "hidden_act": "gelu_new",
+                "max_position_embeddings": m.max_position_embeddings, "layer_norm_eps": m.ln_eps,
+                "rope_theta": float(m.positional_embedding.base),
+                "partial_rotary_factor": float(m.positional_embedding.rotary_fraction or 1.0),
+                "resid_pdrop": 0.0, "embd_pdrop": 0.0, "attention_dropout": 0.0, "qk_layernorm": False,
                 "tie_word_embeddings": not m.untie_embed}
     return {"model_type": m.hf_model_type or "llama", "architectures": [m.hf_architecture or "LlamaForCausalLM"],
             "vocab_size": vocab, "hidden_size": m.d_model, "intermediate_size": m.d_ffn,

@@ -27,6 +27,8 @@ def test_architecture_aliases():
     assert detect_architecture("gpt2-small") == Architecture.GPT2
     for name in ("llama", "llama3", "mistral", "qwen2", "gemma", "something-new"):
         assert detect_architecture(name) == Architecture.LLAMA
+    for name in ("phi", "phi-2", "phi1"):
+        assert detect_architecture(name) == Architecture.PHI
 
 
 def test_gpt2_forward_equivalence_and_roundtrip(tmp_path):
@@ -73,3 +75,64 @@ def test_llama_forward_equivalence_and_roundtrip(tmp_path, interleaved):
     sd = read_hf_state_dict(out)
     for k, v in hf.state_dict().items():
         assert torch.allclose(v, sd[k], atol=1e-6), k
+
+
+def _logits_match(hf, model, cfg, vocab=512, atol=3e-4):
+    from ironcore_b200.checkpoint.hf_interop import load_from_huggingface
+
+    load_from_huggingface(model, cfg, dict(hf.state_dict()))
+    ids = torch.randint(0, vocab, (2, 32))
+    with torch.no_grad():
+        ref, got = hf(ids).logits, model(ids)[..., :vocab]
+    assert torch.allclose(ref, got, atol=atol), (ref - got).abs().max()
+    return ids, ref
+
+
+def test_qwen2_forward_equivalence():
+    """Qwen family: biases on q / k / v only, RMSNorm eps 1e-6, rotary base 1e6, grouped keys / values."""
+    torch.manual_seed(2)
+    hcfg = transformers.Qwen2Config(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                    num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=32,
+                                    rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+    hf = transformers.Qwen2ForCausalLM(hcfg).eval()
+    cfg, model = _native("qwen", hf_model_type="qwen2", ln_eps=1e-6, positional_embedding={"type": "rope", "base": 1e6})
+    assert cfg.model.qkv_bias and model.model.layers[0].attn_output.bias is None
+    _logits_match(hf, model, cfg)
+
+
+def test_gemma_forward_equivalence():
+    """Gemma-1 family: (1 + w) norm gains, sqrt(d) embedding scale, GeGLU, one key / value head, tied head."""
+    torch.manual_seed(3)
+    hcfg = transformers.GemmaConfig(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                    num_attention_heads=4, num_key_value_heads=1, head_dim=16,
+                                    max_position_embeddings=32, rms_norm_eps=1e-6, rope_theta=10000.0,
+                                    hidden_act="gelu_pytorch_tanh", hidden_activation="gelu_pytorch_tanh")
+    hf = transformers.GemmaForCausalLM(hcfg).eval()
+    cfg, model = _native("gemma1", hf_model_type="gemma", ln_eps=1e-6, no_bias=True, ln_type="rmsnorm",
+                         num_attention_groups=1, activation_type="geglu", untie_embed=False,
+                         positional_embedding={"type": "rope", "base": 10000.0})
+    assert cfg.model.norm_weight_offset == 1.0 and cfg.model.embed_scale == 8.0
+    _logits_match(hf, model, cfg)
+
+
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_phi_forward_equivalence_and_roundtrip(tmp_path, interleaved):
+    """Phi family: attention and MLP in parallel behind one LayerNorm, rotary on half of every head, biases
+    everywhere including the LM head; export reloads into ``transformers``."""
+    from ironcore_b200.checkpoint.hf_interop import export_to_huggingface
+
+    torch.manual_seed(4)
+    hcfg = transformers.PhiConfig(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                  num_attention_heads=4, max_position_embeddings=32, layer_norm_eps=1e-5,
+                                  rope_theta=10000.0, partial_rotary_factor=0.5, hidden_act="gelu_new",
+                                  resid_pdrop=0.0, embd_pdrop=0.0, attention_dropout=0.0)
+    hf = transformers.PhiForCausalLM(hcfg).eval()
+    cfg, model = _native("phi2", hf_model_type="phi", ln_eps=1e-5, activation_type="gelu_new", untie_embed=True,
+                         positional_embedding={"type": "rope", "base": 10000.0, "rotary_fraction": 0.5,
+                                               "interleaved": interleaved})
+    assert cfg.model.parallel_block and cfg.model.lm_head_bias
+    ids, ref = _logits_match(hf, model, cfg)
+    out = export_to_huggingface(model, cfg, tmp_path / "hf_phi")
+    back = transformers.PhiForCausalLM.from_pretrained(out).eval()
+    with torch.no_grad():
+        assert torch.allclose(ref, back(ids).logits, atol=2e-4)
