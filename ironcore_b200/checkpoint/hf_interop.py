@@ -178,6 +178,25 @@ class WeightMapper:
             out["output_layer.weight"] = hf["lm_head.weight"].t()
         return {k: v.contiguous() for k, v in out.items()}
 
+    @staticmethod
+    def _moe_in(hf, p: str):
+        """Router and stacked expert weights of a Mixtral-style layer (``(router [E, d], up [E, d, 2f] with the
+        activated half first, down [E, f, d])``), or None for a dense layer. Reads the per-expert names of
+        checkpoints on disk (``block_sparse_moe.gate``, ``experts.N.w1 / w3 / w2``) and the stacked form that
+        ``transformers`` keeps in memory (``mlp.gate``, ``mlp.experts.gate_up_proj`` / ``down_proj``)."""
+        if p + "mlp.experts.gate_up_proj" in hf:
+            return (hf[p + "mlp.gate.weight"], hf[p + "mlp.experts.gate_up_proj"].transpose(1, 2),
+                    hf[p + "mlp.experts.down_proj"].transpose(1, 2))
+        if p + "block_sparse_moe.gate.weight" in hf:
+            ups, downs, e = [], [], 0
+            while p + f"block_sparse_moe.experts.{e}.w1.weight" in hf:
+                ep = p + f"block_sparse_moe.experts.{e}."
+                ups.append(torch.cat([hf[ep + "w1.weight"].t(), hf[ep + "w3.weight"].t()], dim=1))
+                downs.append(hf[ep + "w2.weight"].t())
+                e += 1
+            return hf[p + "block_sparse_moe.gate.weight"], torch.stack(ups), torch.stack(downs)
+        return None
+
     def _llama_in(self, hf):
         pre = "model." if any(k.startswith("model.") for k in hf) else ""
         out = {"embedding.word_embeddings.weight": hf[pre + "embed_tokens.weight"],
@@ -202,6 +221,10 @@ class WeightMapper:
             out[q + "attn_output.weight"] = hf[p + "self_attn.o_proj.weight"].t()
             out[q + "input_layernorm.layernorm.weight"] = hf[p + "input_layernorm.weight"]
             out[q + "post_attn_layernorm.layernorm.weight"] = hf[p + "post_attention_layernorm.weight"]
+            moe = self._moe_in(hf, p)
+            if moe is not None:
+                out[q + "mlp.router.weight"], out[q + "mlp.experts_up"], out[q + "mlp.experts_down"] = moe
+                continue
             up = hf[p + "mlp.up_proj.weight"].t()
             if self.gated:
                 up = torch.cat([hf[p + "mlp.gate_proj.weight"].t(), up], dim=1)   # (f | g): act(f) * g, f = gate
@@ -258,6 +281,15 @@ class WeightMapper:
             out[p + "self_attn.o_proj.weight"] = sd[q + "attn_output.weight"].t()
             out[p + "input_layernorm.weight"] = sd[q + "input_layernorm.layernorm.weight"]
             out[p + "post_attention_layernorm.weight"] = sd[q + "post_attn_layernorm.layernorm.weight"]
+            if q + "mlp.experts_up" in sd:
+                # Mixtral names on disk: one gate, w1 (activated) / w3 / w2 per expert
+                out[p + "block_sparse_moe.gate.weight"] = sd[q + "mlp.router.weight"]
+                ups, downs = sd[q + "mlp.experts_up"], sd[q + "mlp.experts_down"]
+                for e in range(ups.shape[0]):
+                    w1, w3 = ups[e].chunk(2, dim=1)
+                    ep = p + f"block_sparse_moe.experts.{e}."
+                    out[ep + "w1.weight"], out[ep + "w3.weight"], out[ep + "w2.weight"] = w1.t(), w3.t(), downs[e].t()
+                continue
             up = sd[q + "mlp.up_proj.weight"]
             if self.gated:
                 gate, up = up.chunk(2, dim=1)
@@ -318,12 +350,13 @@ def load_from_huggingface(model, config, path, architecture: Optional[Architectu
         native["output_layer.weight"] = _fit_vocab(native["output_layer.weight"], padded, 1)
     info = model.canonical_shard_info()
     own = model.canonical_state_dict()
+    experts = [n for n in own if n.endswith(("experts_up", "experts_down"))]    # split over the expert-parallel group
     sd = {}
     for name, t in native.items():
         if name not in own:
             continue
         dim, parts = info.get(name, (None, 1))
-        t = split_model_parallel_tensor(t, dim, parts, name)
+        t = split_model_parallel_tensor(t, dim, parts, name, expert_names=experts)
         sd[name] = t.to(own[name].dtype).reshape(own[name].shape)
     missing = [k for k in own if k not in sd and not k.endswith(".theta")]
     if missing:
@@ -351,6 +384,18 @@ def generate_hf_config(config) -> dict:
                 "partial_rotary_factor": float(m.positional_embedding.rotary_fraction or 1.0),
                 "resid_pdrop": 0.0, "embd_pdrop": 0.0, "attention_dropout": 0.0, "qk_layernorm": False,
                 "tie_word_embeddings": not m.untie_embed}
+    if m.moe.num_experts > 0:
+        if m.moe.num_shared_experts or not m.moe.normalize_topk or m.moe.layer_freq != 1:
+            raise ValueError("only the Mixtral layout exports to HuggingFace: every layer a mixture of experts, "
+                             "no shared experts, model.moe.normalize_topk on")
+        return {"model_type": "mixtral", "architectures": [m.hf_architecture or "MixtralForCausalLM"],
+                "vocab_size": vocab, "hidden_size": m.d_model, "intermediate_size": m.moe.expert_d_ffn or m.d_ffn,
+                "num_hidden_layers": m.num_layers, "num_attention_heads": m.num_attention_heads,
+                "num_key_value_heads": m.num_attention_groups or m.num_attention_heads, "head_dim": m.head_dim,
+                "hidden_act": "silu", "max_position_embeddings": m.max_position_embeddings, "rms_norm_eps": m.ln_eps,
+                "rope_theta": float(m.positional_embedding.base), "num_local_experts": m.moe.num_experts,
+                "num_experts_per_tok": m.moe.top_k, "router_aux_loss_coef": m.moe.aux_loss_coeff,
+                "sliding_window": None, "tie_word_embeddings": not m.untie_embed}
     return {"model_type": m.hf_model_type or "llama", "architectures": [m.hf_architecture or "LlamaForCausalLM"],
             "vocab_size": vocab, "hidden_size": m.d_model, "intermediate_size": m.d_ffn,
             "num_hidden_layers": m.num_layers, "num_attention_heads": m.num_attention_heads,

@@ -136,3 +136,31 @@ def test_phi_forward_equivalence_and_roundtrip(tmp_path, interleaved):
     back = transformers.PhiForCausalLM.from_pretrained(out).eval()
     with torch.no_grad():
         assert torch.allclose(ref, back(ids).logits, atol=2e-4)
+
+
+def test_mixtral_forward_equivalence_and_roundtrip(tmp_path):
+    """Mixture of experts in the Mixtral layout (every layer: softmax router, top-2 renormalised, SwiGLU experts, no
+    shared expert): the native block reproduces ``transformers``' logits, and the export (per-expert names, as
+    checkpoints on disk carry them) reloads into ``transformers``."""
+    from ironcore_b200.checkpoint.hf_interop import export_to_huggingface
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.models import LanguageModel
+    from ironcore_b200.parallel import mesh
+
+    torch.manual_seed(5)
+    hcfg = transformers.MixtralConfig(vocab_size=512, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=32,
+                                      rms_norm_eps=1e-5, rope_theta=10000.0, num_local_experts=4, num_experts_per_tok=2,
+                                      sliding_window=None, tie_word_embeddings=False, router_aux_loss_coef=0.0)
+    hf = transformers.MixtralForCausalLM(hcfg).eval()
+    mesh.destroy_model_parallel()
+    cfg = tiny_config("llama", d_ffn=96, hf_model_type="mixtral", ln_eps=1e-5,
+                      positional_embedding={"type": "rope", "base": 10000.0})
+    cfg.model.moe(num_experts=4, top_k=2, expert_d_ffn=96, normalize_topk=True, aux_loss_coeff=0.0)
+    validate_config(cfg)
+    model = LanguageModel(cfg).eval()
+    ids, ref = _logits_match(hf, model, cfg)
+    out = export_to_huggingface(model, cfg, tmp_path / "hf_mixtral")
+    back = transformers.MixtralForCausalLM.from_pretrained(out).eval()
+    with torch.no_grad():
+        assert torch.allclose(ref, back(ids).logits, atol=2e-4)
