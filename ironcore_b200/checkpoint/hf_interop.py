@@ -180,22 +180,39 @@ class WeightMapper:
 
     @staticmethod
     def _moe_in(hf, p: str):
-        """Router and stacked expert weights of a Mixtral-style layer (``(router [E, d], up [E, d, 2f] with the
-        activated half first, down [E, f, d])``), or None for a dense layer. Reads the per-expert names of
-        checkpoints on disk (``block_sparse_moe.gate``, ``experts.N.w1 / w3 / w2``) and the stacked form that
-        ``transformers`` keeps in memory (``mlp.gate``, ``mlp.experts.gate_up_proj`` / ``down_proj``)."""
+        """Tensors of a mixture-of-experts layer under the native names (without the layer prefix): ``mlp.router.weight``
+        [E, d], ``mlp.experts_up`` [E, d, 2f] (activated half first), ``mlp.experts_down`` [E, f, d] and, for the
+        Qwen-MoE layout, the shared expert and its gate; None for a dense layer. Reads the per-expert names of
+        checkpoints on disk (Mixtral: ``block_sparse_moe.gate``, ``experts.N.w1 / w3 / w2``; Qwen-MoE:
+        ``mlp.experts.N.gate_proj / up_proj / down_proj``) and the stacked form that ``transformers`` keeps in
+        memory (``mlp.gate``, ``mlp.experts.gate_up_proj`` / ``down_proj``)."""
+        out = {}
         if p + "mlp.experts.gate_up_proj" in hf:
-            return (hf[p + "mlp.gate.weight"], hf[p + "mlp.experts.gate_up_proj"].transpose(1, 2),
-                    hf[p + "mlp.experts.down_proj"].transpose(1, 2))
-        if p + "block_sparse_moe.gate.weight" in hf:
-            ups, downs, e = [], [], 0
-            while p + f"block_sparse_moe.experts.{e}.w1.weight" in hf:
-                ep = p + f"block_sparse_moe.experts.{e}."
-                ups.append(torch.cat([hf[ep + "w1.weight"].t(), hf[ep + "w3.weight"].t()], dim=1))
-                downs.append(hf[ep + "w2.weight"].t())
-                e += 1
-            return hf[p + "block_sparse_moe.gate.weight"], torch.stack(ups), torch.stack(downs)
-        return None
+            out["mlp.router.weight"] = hf[p + "mlp.gate.weight"]
+            out["mlp.experts_up"] = hf[p + "mlp.experts.gate_up_proj"].transpose(1, 2)
+            out["mlp.experts_down"] = hf[p + "mlp.experts.down_proj"].transpose(1, 2)
+        else:
+            for gate, fmt, (n1, n3, n2) in (("block_sparse_moe.gate.weight", "block_sparse_moe.experts.{}.", ("w1", "w3", "w2")),
+                                            ("mlp.gate.weight", "mlp.experts.{}.", ("gate_proj", "up_proj", "down_proj"))):
+                if p + gate in hf and p + fmt.format(0) + n1 + ".weight" in hf:
+                    ups, downs, e = [], [], 0
+                    while p + fmt.format(e) + n1 + ".weight" in hf:
+                        ep = p + fmt.format(e)
+                        ups.append(torch.cat([hf[ep + n1 + ".weight"].t(), hf[ep + n3 + ".weight"].t()], dim=1))
+                        downs.append(hf[ep + n2 + ".weight"].t())
+                        e += 1
+                    out["mlp.router.weight"] = hf[p + gate]
+                    out["mlp.experts_up"], out["mlp.experts_down"] = torch.stack(ups), torch.stack(downs)
+                    break
+        if not out:
+            return None
+        if p + "mlp.shared_expert.up_proj.weight" in hf:
+            out["mlp.shared.up_proj.weight"] = torch.cat([hf[p + "mlp.shared_expert.gate_proj.weight"].t(),
+                                                          hf[p + "mlp.shared_expert.up_proj.weight"].t()], dim=1)
+            out["mlp.shared.down_proj.weight"] = hf[p + "mlp.shared_expert.down_proj.weight"].t()
+            if p + "mlp.shared_expert_gate.weight" in hf:
+                out["mlp.shared_gate.weight"] = hf[p + "mlp.shared_expert_gate.weight"]
+        return out
 
     def _llama_in(self, hf):
         pre = "model." if any(k.startswith("model.") for k in hf) else ""
@@ -223,7 +240,7 @@ class WeightMapper:
             out[q + "post_attn_layernorm.layernorm.weight"] = hf[p + "post_attention_layernorm.weight"]
             moe = self._moe_in(hf, p)
             if moe is not None:
-                out[q + "mlp.router.weight"], out[q + "mlp.experts_up"], out[q + "mlp.experts_down"] = moe
+                out.update({q + name: t for name, t in moe.items()})
                 continue
             up = hf[p + "mlp.up_proj.weight"].t()
             if self.gated:
@@ -282,13 +299,25 @@ class WeightMapper:
             out[p + "input_layernorm.weight"] = sd[q + "input_layernorm.layernorm.weight"]
             out[p + "post_attention_layernorm.weight"] = sd[q + "post_attn_layernorm.layernorm.weight"]
             if q + "mlp.experts_up" in sd:
-                # Mixtral names on disk: one gate, w1 (activated) / w3 / w2 per expert
-                out[p + "block_sparse_moe.gate.weight"] = sd[q + "mlp.router.weight"]
                 ups, downs = sd[q + "mlp.experts_up"], sd[q + "mlp.experts_down"]
+                if q + "mlp.shared.up_proj.weight" in sd:
+                    # Qwen-MoE names on disk: gate / up / down per expert, one shared expert and its gate
+                    out[p + "mlp.gate.weight"] = sd[q + "mlp.router.weight"]
+                    names, fmt = ("gate_proj", "up_proj", "down_proj"), p + "mlp.experts.{}."
+                    g, u = sd[q + "mlp.shared.up_proj.weight"].chunk(2, dim=1)
+                    out[p + "mlp.shared_expert.gate_proj.weight"], out[p + "mlp.shared_expert.up_proj.weight"] = g.t(), u.t()
+                    out[p + "mlp.shared_expert.down_proj.weight"] = sd[q + "mlp.shared.down_proj.weight"].t()
+                    if q + "mlp.shared_gate.weight" in sd:
+                        out[p + "mlp.shared_expert_gate.weight"] = sd[q + "mlp.shared_gate.weight"]
+                else:
+                    # Mixtral names on disk: one gate, w1 (activated) / w3 / w2 per expert
+                    out[p + "block_sparse_moe.gate.weight"] = sd[q + "mlp.router.weight"]
+                    names, fmt = ("w1", "w3", "w2"), p + "block_sparse_moe.experts.{}."
                 for e in range(ups.shape[0]):
                     w1, w3 = ups[e].chunk(2, dim=1)
-                    ep = p + f"block_sparse_moe.experts.{e}."
-                    out[ep + "w1.weight"], out[ep + "w3.weight"], out[ep + "w2.weight"] = w1.t(), w3.t(), downs[e].t()
+                    ep = fmt.format(e)
+                    out[ep + names[0] + ".weight"], out[ep + names[1] + ".weight"] = w1.t(), w3.t()
+                    out[ep + names[2] + ".weight"] = downs[e].t()
                 continue
             up = sd[q + "mlp.up_proj.weight"]
             if self.gated:
@@ -384,10 +413,26 @@ def generate_hf_config(config) -> dict:
                 "partial_rotary_factor": float(m.positional_embedding.rotary_fraction or 1.0),
                 "resid_pdrop": 0.0, "embd_pdrop": 0.0, "attention_dropout": 0.0, "qk_layernorm": False,
                 "tie_word_embeddings": not m.untie_embed}
+    if m.moe.num_experts > 0 and m.moe.num_shared_experts:
+        if not m.moe.shared_expert_gate or m.moe.layer_freq != 1 or not m.qkv_bias:
+            raise ValueError("a model with shared experts exports in the Qwen-MoE layout: every layer a mixture of "
+                             "experts, model.moe.shared_expert_gate on, biases on q / k / v")
+        return {"model_type": "qwen2_moe", "architectures": [m.hf_architecture or "Qwen2MoeForCausalLM"],
+                "vocab_size": vocab, "hidden_size": m.d_model, "intermediate_size": m.d_ffn,
+                "moe_intermediate_size": m.moe.expert_d_ffn or m.d_ffn,
+                "shared_expert_intermediate_size": (m.moe.shared_expert_d_ffn or m.moe.expert_d_ffn or m.d_ffn)
+                * m.moe.num_shared_experts,
+                "num_hidden_layers": m.num_layers, "num_attention_heads": m.num_attention_heads,
+                "num_key_value_heads": m.num_attention_groups or m.num_attention_heads, "hidden_act": "silu",
+                "max_position_embeddings": m.max_position_embeddings, "rms_norm_eps": m.ln_eps,
+                "rope_theta": float(m.positional_embedding.base), "num_experts": m.moe.num_experts,
+                "num_experts_per_tok": m.moe.top_k, "norm_topk_prob": bool(m.moe.normalize_topk),
+                "decoder_sparse_step": 1, "mlp_only_layers": [], "router_aux_loss_coef": m.moe.aux_loss_coeff,
+                "use_sliding_window": False, "tie_word_embeddings": not m.untie_embed}
     if m.moe.num_experts > 0:
-        if m.moe.num_shared_experts or not m.moe.normalize_topk or m.moe.layer_freq != 1:
-            raise ValueError("only the Mixtral layout exports to HuggingFace: every layer a mixture of experts, "
-                             "no shared experts, model.moe.normalize_topk on")
+        if not m.moe.normalize_topk or m.moe.layer_freq != 1:
+            raise ValueError("a model without shared experts exports in the Mixtral layout: every layer a mixture "
+                             "of experts, model.moe.normalize_topk on")
         return {"model_type": "mixtral", "architectures": [m.hf_architecture or "MixtralForCausalLM"],
                 "vocab_size": vocab, "hidden_size": m.d_model, "intermediate_size": m.moe.expert_d_ffn or m.d_ffn,
                 "num_hidden_layers": m.num_layers, "num_attention_heads": m.num_attention_heads,

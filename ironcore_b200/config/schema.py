@@ -152,6 +152,7 @@ class MoEConfig(BaseConfig):
     expert_d_ffn: int = opt(0, "hidden size of one routed expert")
     num_shared_experts: int = opt(0, "always-on experts applied to every token")
     shared_expert_d_ffn: int = opt(0, "hidden size of one shared expert (0 = expert_d_ffn)")
+    shared_expert_gate: bool = opt(False, "scale the shared experts' output per token by sigmoid(x . g) (Qwen-MoE)")
     aux_loss_coeff: float = opt(0.01, "load-balance loss coefficient")
     router: str = opt("softmax_topk", "router type")
     normalize_topk: bool = opt(False, "renormalise the selected probabilities to sum to 1")

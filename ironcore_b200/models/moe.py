@@ -187,6 +187,10 @@ class MoEBlock(nn.Module):
         if moe.num_shared_experts > 0:
             s_ffn = (moe.shared_expert_d_ffn or self.ffn) * moe.num_shared_experts
             self.shared = MLP(m.d_model, s_ffn, m.activation_type, bias=False, dropout=0.0, dtype=dtype, device=device)
+        # Qwen-MoE layout: the shared expert's output is scaled per token by sigmoid(x . g)
+        self.shared_gate = None
+        if self.shared is not None and getattr(moe, "shared_expert_gate", False):
+            self.shared_gate = nn.Linear(m.d_model, 1, bias=False, dtype=dtype, device=device)
 
     # ------------------------------------------------------------------ routing
     def route(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
@@ -250,7 +254,7 @@ class MoEBlock(nn.Module):
             yp = self._experts_on_layout(xp, seg, tile_expert)
             out = fused_combine(yp, w, expert, dest, counts, ws)
             if self.shared is not None:
-                out = out + self.shared(x)
+                out = out + self._shared_out(x)
             if residual is not None:
                 out = out + residual
             return out, aux
@@ -281,10 +285,16 @@ class MoEBlock(nn.Module):
             ys = ys.index_copy(0, order, ys_sorted)
         out = (ys.view(t, self.top_k, d) * w.to(ys.dtype).unsqueeze(-1)).sum(1)
         if self.shared is not None:
-            out = out + self.shared(x)
+            out = out + self._shared_out(x)
         if residual is not None:
             out = out + residual
         return out, aux
+
+    def _shared_out(self, x: torch.Tensor) -> torch.Tensor:
+        y = self.shared(x)
+        if self.shared_gate is not None:
+            y = y * torch.sigmoid(self.shared_gate(x))
+        return y
 
     def _exchange_counts(self, send_counts, recv_counts):
         gathered = [torch.empty_like(send_counts) for _ in range(self.ep)]

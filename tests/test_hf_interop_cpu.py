@@ -164,3 +164,33 @@ def test_mixtral_forward_equivalence_and_roundtrip(tmp_path):
     back = transformers.MixtralForCausalLM.from_pretrained(out).eval()
     with torch.no_grad():
         assert torch.allclose(ref, back(ids).logits, atol=2e-4)
+
+
+def test_qwen2_moe_forward_equivalence_and_roundtrip(tmp_path):
+    """Routed experts plus an always-on shared expert (the Qwen-MoE layout: top-k of the softmax without
+    renormalisation, the shared expert scaled by a sigmoid gate): native logits equal ``transformers``', and the
+    export reloads into ``transformers``."""
+    from ironcore_b200.checkpoint.hf_interop import export_to_huggingface
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.models import LanguageModel
+    from ironcore_b200.parallel import mesh
+
+    torch.manual_seed(6)
+    hcfg = transformers.Qwen2MoeConfig(vocab_size=512, hidden_size=64, intermediate_size=128, moe_intermediate_size=48,
+                                       shared_expert_intermediate_size=80, num_hidden_layers=2, num_attention_heads=4,
+                                       num_key_value_heads=2, max_position_embeddings=32, rms_norm_eps=1e-6,
+                                       rope_theta=1e6, num_experts=8, num_experts_per_tok=3, norm_topk_prob=False,
+                                       decoder_sparse_step=1, mlp_only_layers=[], tie_word_embeddings=False,
+                                       router_aux_loss_coef=0.0, use_sliding_window=False)
+    hf = transformers.Qwen2MoeForCausalLM(hcfg).eval()
+    mesh.destroy_model_parallel()
+    cfg = tiny_config("qwen", hf_model_type="qwen2_moe", ln_eps=1e-6, positional_embedding={"type": "rope", "base": 1e6})
+    cfg.model.moe(num_experts=8, top_k=3, expert_d_ffn=48, num_shared_experts=1, shared_expert_d_ffn=80,
+                  shared_expert_gate=True, normalize_topk=False, aux_loss_coeff=0.0)
+    validate_config(cfg)
+    model = LanguageModel(cfg).eval()
+    ids, ref = _logits_match(hf, model, cfg)
+    out = export_to_huggingface(model, cfg, tmp_path / "hf_qwen2_moe")
+    back = transformers.Qwen2MoeForCausalLM.from_pretrained(out).eval()
+    with torch.no_grad():
+        assert torch.allclose(ref, back(ids).logits, atol=2e-4)
