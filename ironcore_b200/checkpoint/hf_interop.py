@@ -441,11 +441,16 @@ def generate_hf_config(config) -> dict:
                 "rope_theta": float(m.positional_embedding.base), "num_local_experts": m.moe.num_experts,
                 "num_experts_per_tok": m.moe.top_k, "router_aux_loss_coef": m.moe.aux_loss_coeff,
                 "sliding_window": None, "tie_word_embeddings": not m.untie_embed}
+    from ..layers.activations import canonical_activation
+
+    act = {"swiglu": "silu", "geglu": "gelu_pytorch_tanh", "geglu_erf": "gelu", "reglu": "relu"}.get(
+        canonical_activation(m.activation_type), "silu")
     return {"model_type": m.hf_model_type or "llama", "architectures": [m.hf_architecture or "LlamaForCausalLM"],
             "vocab_size": vocab, "hidden_size": m.d_model, "intermediate_size": m.d_ffn,
             "num_hidden_layers": m.num_layers, "num_attention_heads": m.num_attention_heads,
             "num_key_value_heads": m.num_attention_groups or m.num_attention_heads, "head_dim": m.head_dim,
-            "hidden_act": "silu", "max_position_embeddings": m.max_position_embeddings, "rms_norm_eps": m.ln_eps,
+            "hidden_act": act, "hidden_activation": act,     # (Gemma reads the second name)
+            "max_position_embeddings": m.max_position_embeddings, "rms_norm_eps": m.ln_eps,
             "rope_theta": float(m.positional_embedding.base), "tie_word_embeddings": not m.untie_embed,
             "attention_bias": bool(m.qkv_bias), "mlp_bias": False}
 

@@ -88,7 +88,15 @@ def _logits_match(hf, model, cfg, vocab=512, atol=3e-4):
     return ids, ref
 
 
-def test_qwen2_forward_equivalence():
+def _export_reloads(model, cfg, hf_cls, out_dir, ids, ref):
+    from ironcore_b200.checkpoint.hf_interop import export_to_huggingface
+
+    back = hf_cls.from_pretrained(export_to_huggingface(model, cfg, out_dir)).eval()
+    with torch.no_grad():
+        assert torch.allclose(ref, back(ids).logits, atol=2e-4), (ref - back(ids).logits).abs().max()
+
+
+def test_qwen2_forward_equivalence_and_roundtrip(tmp_path):
     """Qwen family: biases on q / k / v only, RMSNorm eps 1e-6, rotary base 1e6, grouped keys / values."""
     torch.manual_seed(2)
     hcfg = transformers.Qwen2Config(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
@@ -97,10 +105,11 @@ def test_qwen2_forward_equivalence():
     hf = transformers.Qwen2ForCausalLM(hcfg).eval()
     cfg, model = _native("qwen", hf_model_type="qwen2", ln_eps=1e-6, positional_embedding={"type": "rope", "base": 1e6})
     assert cfg.model.qkv_bias and model.model.layers[0].attn_output.bias is None
-    _logits_match(hf, model, cfg)
+    ids, ref = _logits_match(hf, model, cfg)
+    _export_reloads(model, cfg, transformers.Qwen2ForCausalLM, tmp_path / "hf_qwen2", ids, ref)
 
 
-def test_gemma_forward_equivalence():
+def test_gemma_forward_equivalence_and_roundtrip(tmp_path):
     """Gemma-1 family: (1 + w) norm gains, sqrt(d) embedding scale, GeGLU, one key / value head, tied head."""
     torch.manual_seed(3)
     hcfg = transformers.GemmaConfig(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
@@ -112,7 +121,8 @@ def test_gemma_forward_equivalence():
                          num_attention_groups=1, activation_type="geglu", untie_embed=False,
                          positional_embedding={"type": "rope", "base": 10000.0})
     assert cfg.model.norm_weight_offset == 1.0 and cfg.model.embed_scale == 8.0
-    _logits_match(hf, model, cfg)
+    ids, ref = _logits_match(hf, model, cfg)
+    _export_reloads(model, cfg, transformers.GemmaForCausalLM, tmp_path / "hf_gemma", ids, ref)
 
 
 @pytest.mark.parametrize("interleaved", [True, False])
