@@ -23,6 +23,25 @@ def use_native(t: torch.Tensor) -> bool:
     return t.is_cuda and t.dtype in _NATIVE_DTYPES
 
 
+_FALLBACKS_SEEN = set()
+
+
+def note_fallback(op: str, reason: str, t: Optional[torch.Tensor] = None) -> None:
+    """A 16-bit CUDA tensor is about to run ``op`` through PyTorch operators instead of the native kernel because
+    its shape is outside the kernel's range: say so, once per (op, reason), so that the slow path never runs
+    unnoticed. Tensors for which the native path was never an option (CPU, fp32) are not reported."""
+    if t is not None and not use_native(t):
+        return
+    key = (op, reason)
+    if key in _FALLBACKS_SEEN:
+        return
+    _FALLBACKS_SEEN.add(key)
+    import warnings
+
+    warnings.warn(f"{op}: {reason}; this call runs on PyTorch operators, not on the native sm_100a kernel",
+                  RuntimeWarning, stacklevel=3)
+
+
 # --------------------------------------------------------------------------- linear
 class _Linear(torch.autograd.Function):
     """y = x @ W (+ b) (+ residual) with W stored [in, out]."""
@@ -124,6 +143,7 @@ def norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], ep
         if out is not None and (xc.dim() != 2 or out.shape != xc.shape or out.dtype != xc.dtype):
             out = None
         return _Norm.apply(xc, weight, bias, rc, eps, rms, w_offset, out)
+    note_fallback("norm", f"row length {x.shape[-1]} is not a multiple of 8 up to 8192", x)
     h = x if residual is None else x + residual
     if rms:
         y = reference.rms_norm_reference(h, weight, eps, w_offset)
@@ -178,6 +198,7 @@ def activation(x: torch.Tensor, name: str, row_limit: Optional[torch.Tensor] = N
     if name in GLU_KINDS:
         if use_native(x) and (x.shape[-1] // 2) % 8 == 0:
             return _Glu.apply(x.contiguous(), name, row_limit)
+        note_fallback("gated activation", f"half width {x.shape[-1] // 2} is not a multiple of 8", x)
         if row_limit is not None:
             x = _mask_rows(x, row_limit)
         return reference.glu_reference(x, name)
@@ -187,6 +208,7 @@ def activation(x: torch.Tensor, name: str, row_limit: Optional[torch.Tensor] = N
         raise ValueError(f"unknown activation type {name}")
     if use_native(x) and x.numel() % 8 == 0:
         return _Act.apply(x.contiguous(), name)
+    note_fallback("activation", f"element count {x.numel()} is not a multiple of 8", x)
     return reference.act_reference(x, name)
 
 
@@ -546,6 +568,12 @@ def rope_attention(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int, head
             q = qkv if qkv.is_contiguous() else qkv.contiguous()
             return _RopeAttention.apply(q, num_heads, num_kv_heads, head_dim, seq_len, rope, cu_seqlens, causal,
                                         scale, rot_dim, float(dropout_p) if training else 0.0)
+    if attn_mask is not None:
+        note_fallback("attention", "an explicit boolean mask materialises the scores (document boundaries go "
+                                   "through cu_seqlens on the flash kernel)", qkv)
+    elif fused:
+        note_fallback("attention", f"head size {head_dim} (rotary width {rot_dim}) is outside the flash kernel's "
+                                   "64 / 128", qkv)
     if rope is not None:
         base, rscale, offset, interleaved, pos_ids = rope
         qkv = rope_reference_packed(qkv, num_heads, num_kv_heads, head_dim, seq_len, base, rscale, offset,

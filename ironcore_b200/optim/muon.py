@@ -49,6 +49,10 @@ def newton_schulz_reference(g: torch.Tensor, steps: int = 5, eps: float = 1e-7, 
 def newton_schulz(g: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.Tensor:
     """Newton-Schulz on the native GEMM (CUDA, dims multiples of 8) or the reference path."""
     if not (g.is_cuda and g.shape[0] % 8 == 0 and g.shape[1] % 8 == 0):
+        if g.is_cuda:
+            from ..ops.functional import note_fallback
+
+            note_fallback("Newton-Schulz", f"matrix {tuple(g.shape)} has a side that is not a multiple of 8")
         return newton_schulz_reference(g, steps, eps, torch.bfloat16 if g.is_cuda else torch.float32).to(g.dtype)
     a, b, c = NS_COEFFS
     x = g.to(torch.bfloat16)

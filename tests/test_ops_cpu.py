@@ -138,3 +138,20 @@ def test_op_oracles_agree_with_torch_and_with_each_other():
     pid = torch.arange(5).expand(2, 5)
     assert torch.allclose(OF.embedding(ids, table, pos_table=ptab, pos_ids=pid).view(2, 5, 8), table[ids] + ptab[pid])
     assert math.isfinite(float(got.sum()))
+
+
+def test_fallbacks_are_reported_once_and_only_for_native_candidates(monkeypatch):
+    """``note_fallback`` warns once per (op, reason) and stays silent for tensors that never had a native path."""
+    import warnings
+
+    from ironcore_b200.ops import functional as OF
+
+    monkeypatch.setattr(OF, "_FALLBACKS_SEEN", set())
+    with warnings.catch_warnings(record=True) as seen:
+        warnings.simplefilter("always")
+        OF.norm(torch.randn(4, 12), torch.ones(12), None, 1e-5, True)          # CPU fp32: nothing to report
+        OF.note_fallback("norm", "row length 12 is not a multiple of 8 up to 8192", torch.randn(2))
+        assert not seen
+        OF.note_fallback("norm", "row length 12 is not a multiple of 8 up to 8192")
+        OF.note_fallback("norm", "row length 12 is not a multiple of 8 up to 8192")
+        assert len(seen) == 1 and "native sm_100a kernel" in str(seen[0].message)
