@@ -171,3 +171,35 @@ def test_dpo_trainer_learns_the_preference():
     assert tr.last_stats["reward_chosen"] > tr.last_stats["reward_rejected"]
     assert all(torch.equal(a, b) for a, b in zip(ref_before, tr.ref_model.parameters()))
     assert all(not p.requires_grad for p in tr.ref_model.parameters())
+
+
+def test_paged_decode_reproduces_transformers_greedy_generation():
+    """A tiny Qwen2 model from ``transformers`` loaded into the native model: greedy decoding on the block KV cache
+    yields the same tokens as ``generate(do_sample=False)``, and the recorded log-probs are those of the full
+    softmax."""
+    transformers = pytest.importorskip("transformers")
+    from ironcore_b200.checkpoint.hf_interop import load_from_huggingface
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.models import LanguageModel
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.rl.rollout import RolloutEngine
+
+    torch.manual_seed(0)
+    hcfg = transformers.Qwen2Config(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                    num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64,
+                                    rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+    hf = transformers.Qwen2ForCausalLM(hcfg).eval()
+    mesh.destroy_model_parallel()
+    cfg = tiny_config("qwen", hf_model_type="qwen2", ln_eps=1e-6, max_seq_len=64, max_position_embeddings=64,
+                      positional_embedding={"type": "rope", "base": 1e6})
+    validate_config(cfg)
+    model = LanguageModel(cfg).eval()
+    load_from_huggingface(model, cfg, dict(hf.state_dict()))
+    prompts = torch.randint(0, 512, (3, 7))
+    engine = RolloutEngine(model, cfg, max_seqs=3, max_seq_len=40)
+    tokens, logps = engine.generate(prompts, 20, temperature=1.0, top_k=1)
+    ref = hf.generate(prompts, max_new_tokens=20, do_sample=False, pad_token_id=0)
+    assert torch.equal(tokens, ref)
+    with torch.no_grad():
+        want = torch.log_softmax(hf(ref).logits.float(), -1)[:, 6:-1].gather(-1, ref[:, 7:, None]).squeeze(-1)
+    assert torch.allclose(logps, want, atol=1e-5)
