@@ -204,3 +204,45 @@ def test_qwen2_moe_forward_equivalence_and_roundtrip(tmp_path):
     back = transformers.Qwen2MoeForCausalLM.from_pretrained(out).eval()
     with torch.no_grad():
         assert torch.allclose(ref, back(ids).logits, atol=2e-4)
+
+
+def _tp_import_worker(rank, world, path):
+    import torch.distributed as dist
+
+    from ironcore_b200.checkpoint.hf_interop import load_from_huggingface
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.models import LanguageModel
+    from ironcore_b200.parallel import mesh
+
+    saved = torch.load(path)
+    cfg = tiny_config("qwen", hf_model_type="qwen2", ln_eps=1e-6, positional_embedding={"type": "rope", "base": 1e6})
+    cfg.trainer(tensor_model_parallel_size=world)
+    cfg.parallel(world_size=world, rank=rank, sequence_parallel=True)
+    validate_config(cfg)
+    mesh.initialize_model_parallel(world, sequence_parallel=True)
+    model = LanguageModel(cfg).eval()
+    load_from_huggingface(model, cfg, saved["sd"])
+    with torch.no_grad():
+        local = model(saved["ids"])                                   # [B, S, V / world]
+    parts = [torch.empty_like(local) for _ in range(world)]
+    dist.all_gather(parts, local.contiguous())
+    full = torch.cat(parts, dim=-1)[..., :512]
+    assert torch.allclose(full, saved["logits"], atol=3e-4), (full - saved["logits"]).abs().max()
+
+
+def test_import_into_two_tensor_parallel_ranks_matches_transformers(tmp_path):
+    """The HuggingFace import splits q | k | v, gate | up, the row-parallel projections and the vocabulary over the
+    tensor-parallel group (with sequence parallelism on): the gathered logits equal ``transformers``'."""
+    from helpers import run_distributed
+
+    torch.manual_seed(7)
+    hcfg = transformers.Qwen2Config(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                    num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=32,
+                                    rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+    hf = transformers.Qwen2ForCausalLM(hcfg).eval()
+    ids = torch.randint(0, 512, (2, 32))
+    with torch.no_grad():
+        logits = hf(ids).logits
+    path = str(tmp_path / "hf.pt")
+    torch.save({"sd": {k: v.clone() for k, v in hf.state_dict().items()}, "ids": ids, "logits": logits}, path)
+    run_distributed(_tp_import_worker, 2, path)
