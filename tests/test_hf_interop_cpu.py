@@ -246,3 +246,44 @@ def test_import_into_two_tensor_parallel_ranks_matches_transformers(tmp_path):
     path = str(tmp_path / "hf.pt")
     torch.save({"sd": {k: v.clone() for k, v in hf.state_dict().items()}, "ids": ids, "logits": logits}, path)
     run_distributed(_tp_import_worker, 2, path)
+
+
+def _ep_import_worker(rank, world, path):
+    from ironcore_b200.checkpoint.hf_interop import load_from_huggingface
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.models import LanguageModel
+    from ironcore_b200.parallel import mesh
+
+    saved = torch.load(path)
+    cfg = tiny_config("llama", d_ffn=96, hf_model_type="mixtral", ln_eps=1e-5,
+                      positional_embedding={"type": "rope", "base": 10000.0})
+    cfg.model.moe(num_experts=4, top_k=2, expert_d_ffn=96, normalize_topk=True, aux_loss_coeff=0.0)
+    cfg.trainer(micro_batch_size=2, train_batch_size=4, gradient_accumulation_steps=None)
+    cfg.parallel(world_size=world, rank=rank, expert_model_parallel_size=world)
+    validate_config(cfg)
+    mesh.initialize_model_parallel(1, expert_model_parallel_size=world)
+    model = LanguageModel(cfg).eval()
+    assert model.model.layers[0].mlp.experts_up.shape[0] == 4 // world
+    load_from_huggingface(model, cfg, saved["sd"])
+    with torch.no_grad():
+        got = model(saved["ids"])[..., :512]
+    assert torch.allclose(got, saved["logits"], atol=3e-4), (got - saved["logits"]).abs().max()
+
+
+def test_import_of_a_mixture_of_experts_over_two_expert_parallel_ranks(tmp_path):
+    """Each expert-parallel rank keeps its experts of a Mixtral checkpoint; with the token exchange between the
+    ranks the logits equal ``transformers``'."""
+    from helpers import run_distributed
+
+    torch.manual_seed(8)
+    hcfg = transformers.MixtralConfig(vocab_size=512, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=32,
+                                      rms_norm_eps=1e-5, rope_theta=10000.0, num_local_experts=4, num_experts_per_tok=2,
+                                      sliding_window=None, tie_word_embeddings=False, router_aux_loss_coef=0.0)
+    hf = transformers.MixtralForCausalLM(hcfg).eval()
+    ids = torch.randint(0, 512, (2, 32))
+    with torch.no_grad():
+        logits = hf(ids).logits
+    path = str(tmp_path / "hf.pt")
+    torch.save({"sd": {k: v.clone() for k, v in hf.state_dict().items()}, "ids": ids, "logits": logits}, path)
+    run_distributed(_ep_import_worker, 2, path)
