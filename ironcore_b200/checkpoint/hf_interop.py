@@ -461,7 +461,8 @@ def export_to_huggingface(model, config, out_dir, safe_serialization: bool = Tru
     Collective over the TP group; rank 0 writes."""
     base = model
     local = {k: v.detach() for k, v in base.canonical_state_dict().items()}
-    merged = merge_model_parallel_state(local, base.canonical_shard_info())
+    experts = [n for n in local if n.endswith(("experts_up", "experts_down"))]   # gathered over the expert-parallel group
+    merged = merge_model_parallel_state(local, base.canonical_shard_info(), expert_names=experts)
     vocab = config.model.vocab_size or config.data.vocab_size
     merged["embedding.word_embeddings.weight"] = _fit_vocab(merged["embedding.word_embeddings.weight"], vocab, 0)
     if "output_layer.weight" in merged:

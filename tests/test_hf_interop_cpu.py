@@ -268,6 +268,17 @@ def _ep_import_worker(rank, world, path):
     with torch.no_grad():
         got = model(saved["ids"])[..., :512]
     assert torch.allclose(got, saved["logits"], atol=3e-4), (got - saved["logits"]).abs().max()
+    # the export gathers the experts of both ranks again (collective; rank 0 writes)
+    from ironcore_b200.checkpoint.hf_interop import export_to_huggingface, read_hf_state_dict
+
+    out = export_to_huggingface(model, cfg, saved["out_dir"])
+    import torch.distributed as dist
+
+    dist.barrier()
+    if rank == 0:
+        back = read_hf_state_dict(out)
+        w1 = back["model.layers.1.block_sparse_moe.experts.3.w1.weight"]
+        assert torch.allclose(w1, saved["sd"]["model.layers.1.mlp.experts.gate_up_proj"][3, :96], atol=1e-6)
 
 
 def test_import_of_a_mixture_of_experts_over_two_expert_parallel_ranks(tmp_path):
@@ -285,5 +296,9 @@ def test_import_of_a_mixture_of_experts_over_two_expert_parallel_ranks(tmp_path)
     with torch.no_grad():
         logits = hf(ids).logits
     path = str(tmp_path / "hf.pt")
-    torch.save({"sd": {k: v.clone() for k, v in hf.state_dict().items()}, "ids": ids, "logits": logits}, path)
+    torch.save({"sd": {k: v.clone() for k, v in hf.state_dict().items()}, "ids": ids, "logits": logits,
+                "out_dir": str(tmp_path / "hf_out")}, path)
     run_distributed(_ep_import_worker, 2, path)
+    back = transformers.MixtralForCausalLM.from_pretrained(tmp_path / "hf_out").eval()
+    with torch.no_grad():
+        assert torch.allclose(back(ids).logits, logits, atol=2e-4)
