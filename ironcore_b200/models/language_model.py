@@ -285,8 +285,8 @@ class LanguageModel(BaseModule):
         """Loss of (vocabulary-sharded) ``logits`` [B, S, V/t] against ``labels`` [B, S] through the
         vocab-parallel cross entropy and the model's loss function; labels of ``-100`` are left out.
         ``padding_start_idx`` defaults to the real vocabulary size. (ironcore/language_model.py:163-201)"""
-        if not fp16_lm_cross_entropy:
-            logits = logits.float()
+        if not fp16_lm_cross_entropy and not OF.use_native(logits):
+            logits = logits.float()      # (the native kernel reads 16-bit logits and computes in fp32 by itself)
         vocab = self.vocab_size if padding_start_idx is None else padding_start_idx
         per_token = vocab_parallel_cross_entropy(logits, labels.contiguous().clamp_min(-1), vocab,
                                                  tp_group=self.tp_group)

@@ -371,10 +371,18 @@ class Trainer:
             if i >= max_batches:
                 break
             ids, labels = batch["input_ids"], batch["labels"]
-            losses.append(self.model(ids, labels).float())
-            logits = self.model(ids)
-            accs.append(compute_token_accuracy(logits.reshape(-1, logits.shape[-1]),
-                                               labels.reshape(-1).to(logits.device)))
+            extra = {k: batch[k] for k in ("position_ids", "cu_seqlens") if batch.get(k) is not None}
+            if hasattr(self.model, "compute_loss_from_logits"):
+                # one forward pass: loss and accuracy from the same logits, on the positions the training loss counts
+                logits = self.model(ids, **extra)
+                ids, labels = ids.to(logits.device), labels.to(logits.device)
+                mask = self.model._loss_mask(ids, labels, batch.get("loss_mask"))   # pylint: disable=protected-access
+                losses.append(self.model.compute_loss_from_logits(logits, labels, mask).float())
+            else:   # a wrapper that only exposes forward (FSDP): loss and logits from two passes
+                losses.append(self.model(ids, labels, **extra).float())
+                logits = self.model(ids, **extra)
+                mask = None
+            accs.append(compute_token_accuracy(logits, labels.to(logits.device), mask))
         self.model.train()
         if not losses:
             return None

@@ -1,5 +1,6 @@
 """End-to-end trainer on CPU (fp32): the loss falls, checkpoints resume, config derivation works."""
 
+import pytest
 import torch
 
 from helpers import tiny_config
@@ -128,3 +129,42 @@ def test_lm_head_chunk_gives_the_same_loss_and_gradients():
         assert ga.keys() == gb.keys()
         for n in ga:
             assert torch.allclose(ga[n], gb[n], atol=2e-5, rtol=1e-4), (untie, n)
+
+
+def test_evaluation_reports_the_loss_of_the_counted_positions():
+    """``Trainer.evaluate`` / ``test``: one forward pass per batch; loss, perplexity and arg-max accuracy over the
+    positions the training loss counts (SFT masks and sample boundaries included)."""
+    import math
+
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.trainer import Trainer
+
+    mesh.destroy_model_parallel()
+    cfg = tiny_config("llama")
+    cfg.trainer(do_eval=True, do_test=True, eval_batch_size=2, test_batch_size=2)
+    cfg.operation(eval_samples=4, test_samples=2)
+    validate_config(cfg)
+    tr = Trainer(cfg)
+    m = tr.evaluate(0)
+    assert set(m) == {"eval_loss", "eval_ppl", "eval_accuracy"}
+    assert m["eval_ppl"] == pytest.approx(math.exp(m["eval_loss"]), rel=1e-6) and 0.0 <= m["eval_accuracy"] <= 1.0
+    assert abs(m["eval_loss"] - math.log(512)) < 0.5                    # an untrained model on uniform tokens
+    assert set(tr.test(0)) == {"test_loss", "test_ppl", "test_accuracy"}
+
+    # a packed SFT batch: only unmasked answer tokens count, attention stays inside each sample
+    ids = torch.randint(1, 500, (1, 32))
+    labels = torch.roll(ids, -1, dims=1)
+    labels[:, :10] = -100
+    labels[:, 20:] = -100
+    batch = {"input_ids": ids, "labels": labels, "position_ids": torch.cat([torch.arange(16), torch.arange(16)])[None],
+             "cu_seqlens": torch.tensor([0, 16, 32], dtype=torch.int32), "loss_mask": labels != -100}
+    got = tr._eval_loop(iter([batch]), 1, "eval", 0)
+    tr.model.eval()
+    with torch.no_grad():
+        want = float(tr.model(ids, labels, position_ids=batch["position_ids"], cu_seqlens=batch["cu_seqlens"],
+                              loss_mask=batch["loss_mask"]))
+        logits = tr.model(ids, position_ids=batch["position_ids"], cu_seqlens=batch["cu_seqlens"])
+    keep = labels != -100
+    acc = float(((logits.argmax(-1) == labels) & keep).sum()) / float(keep.sum())
+    assert got["eval_loss"] == pytest.approx(want, rel=1e-5) and got["eval_accuracy"] == pytest.approx(acc)
