@@ -222,6 +222,8 @@ class TrainerConfig(BaseConfig):
     model_name: str = opt("model", "run name")
     config_path: Optional[str] = opt(None, "config file path")
     model_path: str = opt("", "checkpoint directory")
+    init_from_hf: Optional[str] = opt(None, "HuggingFace checkpoint directory to initialise the weights from when "
+                                            "model_path holds no checkpoint to resume (fine-tuning)")
     micro_batch_size: Optional[int] = opt(2, "micro batch size")
     train_batch_size: Optional[int] = opt(None, "global batch size")
     gradient_accumulation_steps: Optional[int] = opt(None, "gradient accumulation steps")

@@ -171,13 +171,29 @@ class Trainer:
         self.logger.info("model %s: %.1fM parameters on this rank (%s)", cfg.model.name, n_params / 1e6, dtype)
         return model, optimizer
 
+    def load_or_init_weights(self) -> int:
+        """Resume from the latest checkpoint under ``trainer.model_path`` (weights, optimizer, schedule) and return
+        the step to continue at; without one start at step 0, from the HuggingFace checkpoint named by
+        ``trainer.init_from_hf`` when that is set, else from the random initialisation."""
+        from .checkpoint import load_checkpoint
+
+        cfg = self.config
+        last = load_checkpoint(cfg, self.model, self.optimizer, self.lr_scheduler)
+        if last is not None and last >= 0:
+            return last + 1
+        if cfg.trainer.init_from_hf:
+            from .checkpoint.hf_interop import load_from_huggingface
+
+            load_from_huggingface(self.model, cfg, cfg.trainer.init_from_hf)
+            self.logger.info("initialised the weights from the HuggingFace checkpoint %s", cfg.trainer.init_from_hf)
+        return 0
+
     # ------------------------------------------------------------------ training
     def train(self):
         cfg = self.config
-        from .checkpoint import load_checkpoint, save_checkpoint
+        from .checkpoint import save_checkpoint
 
-        last = load_checkpoint(cfg, self.model, self.optimizer, self.lr_scheduler)
-        step = last + 1 if last is not None and last >= 0 else 0
+        step = self.load_or_init_weights()
         self._start_profiler()
         loss_acc, n_acc = 0.0, 0
         pending = []

@@ -302,3 +302,43 @@ def test_import_of_a_mixture_of_experts_over_two_expert_parallel_ranks(tmp_path)
     back = transformers.MixtralForCausalLM.from_pretrained(tmp_path / "hf_out").eval()
     with torch.no_grad():
         assert torch.allclose(back(ids).logits, logits, atol=2e-4)
+
+
+def test_trainer_starts_from_a_huggingface_checkpoint(tmp_path):
+    """``trainer.init_from_hf``: without a checkpoint to resume, training starts from the HuggingFace weights (through
+    the flat parameter buffer of the optimizer engine); with one, the resume wins."""
+    from ironcore_b200.checkpoint import save_checkpoint
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.trainer import Trainer
+
+    torch.manual_seed(9)
+    hcfg = transformers.LlamaConfig(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                    num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=32,
+                                    rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False)
+    hf = transformers.LlamaForCausalLM(hcfg).eval()
+    hf.save_pretrained(tmp_path / "hf", safe_serialization=True)
+    ids = torch.randint(0, 512, (2, 32))
+    with torch.no_grad():
+        ref = hf(ids).logits
+
+    def trainer():
+        mesh.destroy_model_parallel()
+        cfg = tiny_config("llama", hf_model_type="llama")
+        cfg.trainer(init_from_hf=str(tmp_path / "hf"), model_path=str(tmp_path / "ck"))
+        validate_config(cfg)
+        return cfg, Trainer(cfg)
+
+    cfg, tr = trainer()
+    assert tr.load_or_init_weights() == 0
+    tr.model.eval()
+    with torch.no_grad():
+        assert torch.allclose(tr.model(ids)[..., :512], ref, atol=3e-4)
+    tr.model.train()
+    tr.train_step(0)                                       # the optimizer engine updates the loaded weights
+    save_checkpoint(cfg, tr.model, tr.optimizer, tr.lr_scheduler, 0)
+    after = {k: v.clone() for k, v in tr.model.canonical_state_dict().items()}
+    cfg2, tr2 = trainer()
+    assert tr2.load_or_init_weights() == 1                 # resumes the native checkpoint, not the HuggingFace one
+    for k, v in tr2.model.canonical_state_dict().items():
+        assert torch.equal(v, after[k]), k
