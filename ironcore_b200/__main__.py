@@ -1,4 +1,4 @@
-"""Command-line entry: ``ironcore {train,preprocess,inspect,rollout} ...`` (also ``python -m ironcore_b200``).
+"""Command-line entry: ``ironcore {train,preprocess,inspect,rollout,export} ...`` (also ``python -m ironcore_b200``).
 (Behavioural reference: ironcore/__main__.py:16-89.)"""
 
 from __future__ import annotations
@@ -30,6 +30,13 @@ def main(argv=None) -> int:
     p_roll.add_argument("--prompt", default=None)
     p_roll.add_argument("--max-new-tokens", type=int, default=64)
 
+    p_exp = sub.add_parser("export", help="write a native checkpoint as a HuggingFace directory")
+    p_exp.add_argument("--config", required=True, help="training YAML of the run that wrote the checkpoint")
+    p_exp.add_argument("--output", required=True, help="directory to write")
+    p_exp.add_argument("--step", type=int, default=None, help="checkpoint step (default: the latest)")
+    p_exp.add_argument("--pytorch", action="store_true", help="pytorch_model.bin instead of safetensors")
+    p_exp.add_argument("--shard-bytes", dest="shard_bytes", type=int, default=0, help="maximum bytes per weight file")
+
     args, extra = parser.parse_known_args(argv)
     if args.command == "preprocess":
         from .cli.preprocess import run_preprocess
@@ -48,6 +55,10 @@ def main(argv=None) -> int:
         from .cli.rollout import run_rollout
 
         return run_rollout(args, extra)
+    if args.command == "export":
+        from .cli.export import run_export
+
+        return run_export(args, extra)
     parser.print_help()
     return 1
 

@@ -342,3 +342,37 @@ def test_trainer_starts_from_a_huggingface_checkpoint(tmp_path):
     assert tr2.load_or_init_weights() == 1                 # resumes the native checkpoint, not the HuggingFace one
     for k, v in tr2.model.canonical_state_dict().items():
         assert torch.equal(v, after[k]), k
+
+
+def test_export_subcommand_writes_a_loadable_directory(tmp_path, capsys):
+    """``ironcore train`` then ``ironcore export``: the written directory loads into ``transformers`` and holds the
+    trained weights."""
+    import yaml
+
+    from ironcore_b200.__main__ import main
+    from ironcore_b200.checkpoint.hf_interop import read_hf_state_dict
+    from ironcore_b200.parallel import mesh
+
+    mesh.destroy_model_parallel()
+    run = {"trainer": {"micro_batch_size": 2, "train_batch_size": 2, "log_interval": 1, "save_checkpoint_steps": 2,
+                       "model_path": str(tmp_path / "ck"), "use_flash_attn": False, "vocab_padding_unit": 8},
+           "operation": {"train_steps": 2},
+           "model": {"name": "llama", "hf_model_type": "llama", "d_model": 32, "d_ffn": 64, "num_layers": 2,
+                     "num_attention_heads": 4, "num_attention_groups": 2, "max_seq_len": 32,
+                     "max_position_embeddings": 32, "precision": "fp32", "ln_type": "rmsnorm",
+                     "activation_type": "swiglu", "no_bias": True, "untie_embed": True, "vocab_size": 300,
+                     "dropout_embd": 0.0, "dropout_attn": 0.0, "dropout_mlp": 0.0,
+                     "positional_embedding": {"type": "rope"}},
+           "data": {"task_type": "synthetic", "vocab_size": 300}, "optim": {"max_lr": 1e-3, "warmup_steps": 0}}
+    path = tmp_path / "run.yaml"
+    path.write_text(yaml.safe_dump(run))
+    assert main(["train", "--config", str(path)]) == 0
+    mesh.destroy_model_parallel()
+    assert main(["export", "--config", str(path), "--output", str(tmp_path / "hf")]) == 0
+    assert "exported step 1" in capsys.readouterr().out
+    back = transformers.LlamaForCausalLM.from_pretrained(tmp_path / "hf").eval()
+    sd = read_hf_state_dict(tmp_path / "hf")
+    assert back.config.num_key_value_heads == 2 and sd["model.embed_tokens.weight"].shape[1] == 32
+    with torch.no_grad():
+        assert torch.isfinite(back(torch.randint(0, 300, (1, 8))).logits).all()
+    mesh.destroy_model_parallel()
