@@ -203,3 +203,54 @@ def test_paged_decode_reproduces_transformers_greedy_generation():
     with torch.no_grad():
         want = torch.log_softmax(hf(ref).logits.float(), -1)[:, 6:-1].gather(-1, ref[:, 7:, None]).squeeze(-1)
     assert torch.allclose(logps, want, atol=1e-5)
+
+
+def _dpo_batches(seed=0):
+    import numpy as np
+
+    from ironcore_b200.data.collator import UniversalCollator
+
+    rng = np.random.default_rng(seed)
+    coll = UniversalCollator("dpo", 32, pad_token_id=0)
+    while True:
+        rows = []
+        for _ in range(2):
+            prompt = rng.integers(300, 500, size=6)
+            good, bad = rng.integers(10, 60, size=5), rng.integers(100, 150, size=7)
+            rows.append({"chosen": {"tokens": np.concatenate([prompt, good]), "mask_ranges": [[0, 6]]},
+                         "rejected": {"tokens": np.concatenate([prompt, bad]), "mask_ranges": [[0, 6]]}})
+        yield coll(rows)
+
+
+def _dpo_tp_worker(rank, world, out_path):
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.rl.dpo import DPOTrainer
+
+    cfg = tiny_config("llama")
+    cfg.data.task_type = "dpo"
+    cfg.trainer(micro_batch_size=2, train_batch_size=2, gradient_accumulation_steps=None,
+                tensor_model_parallel_size=world)
+    cfg.parallel(world_size=world, rank=rank, sequence_parallel=world > 1)
+    cfg.optim(max_lr=2e-3, warmup_steps=0, lr_scheduler="constant")
+    cfg.operation.train_steps = 50
+    validate_config(cfg)
+    tr = DPOTrainer(cfg)
+    tr.data_iterator = {"train": _dpo_batches(), "eval": None, "test": None}
+    losses = [float(tr.train_step(s)[0]) for s in range(4)]
+    if rank == 0:
+        torch.save(losses, out_path)
+
+
+def test_dpo_on_two_tensor_parallel_ranks_matches_one(tmp_path):
+    """The DPO step under tensor + sequence parallelism (sharded vocabulary in the sequence log-probs, policy and
+    frozen reference both sharded) follows the single-rank losses."""
+    from helpers import run_distributed
+    from ironcore_b200.parallel import mesh
+
+    a, b = str(tmp_path / "tp1.pt"), str(tmp_path / "tp2.pt")
+    mesh.destroy_model_parallel()
+    run_distributed(_dpo_tp_worker, 1, a)
+    run_distributed(_dpo_tp_worker, 2, b)
+    l1, l2 = torch.load(a), torch.load(b)
+    assert l1[0] == pytest.approx(math.log(2.0), abs=1e-5)
+    assert l1 == pytest.approx(l2, abs=2e-4), (l1, l2)
