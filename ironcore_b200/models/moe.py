@@ -7,7 +7,9 @@ Semantics (no counterpart in the reference; standard top-k softmax routing):
   ``num_shared * shared_d_ffn`` applied to every token;
   out = shared(x) + sum_k w_k * expert_k(x) (+ residual);
   aux = coeff * E * sum_e f_e * P_e with f_e the fraction of token slots routed to e and P_e the
-  mean router probability of e.
+  mean router probability of e, taken over the tokens this rank routes: the micro-batch of a data-parallel
+  rank, and under sequence parallelism this rank's token shard of it (the layer's loss is then the mean of
+  the shards' losses, identical on every tensor-parallel rank).
 
 Execution. Token slots are sorted by expert into a buffer whose per-expert segments are padded
 to the GEMM's 128-row tile, so the grouped tcgen05 GEMM picks the expert weight per M tile
@@ -166,6 +168,9 @@ class MoEBlock(nn.Module):
         self.capacity_factor = float(getattr(moe, "capacity_factor", 0.0) or 0.0)   # 0 = dropless
         self.normalize = moe.normalize_topk
         self.ffn = moe.expert_d_ffn or m.d_ffn
+        self.tp_group = mesh.get_tensor_model_parallel_group()
+        tp = mesh.get_tensor_model_parallel_world_size()
+        self.sp_size = tp if (tp > 1 and mesh.sequence_parallel_enabled()) else 1
         self.ep_group = mesh.get_expert_model_parallel_group()
         self.ep = mesh.get_expert_model_parallel_world_size()
         self.ep_rank = mesh.get_expert_model_parallel_rank()
@@ -244,6 +249,12 @@ class MoEBlock(nn.Module):
         """x: [T, d] -> ([T, d], aux loss)."""
         t, d = x.shape
         w, idx, aux = self.route(x)
+        if self.sp_size > 1:
+            # Under sequence parallelism this rank routes its token shard only: the layer's balance loss is the
+            # mean of the shards' losses. The sum over the tensor-parallel group makes the value the same on
+            # every rank; its backward pass is the identity, and the gradients of the replicated router weight
+            # are summed over the group by the optimizer engine, so each shard's loss counts once, not tp times.
+            aux = C.reduce_from_tp(aux / self.sp_size, self.tp_group)
         ws = self._fused_workspace(x) if self.ep > 1 else None
         if ws is not None and t <= ws.max_tokens:
             # dispatch, expert GEMMs and combine without leaving the device: the exchange runs inside kernels

@@ -104,7 +104,9 @@ class FlatGroup:
         buckets: Dict[tuple, list] = {}
         order = []
         for name, mod, pname, p in named_params:
-            repl = getattr(p, "tp_shard_dim", None) is None and not getattr(p, "expert_parallel", False)
+            # not sharded over the tensor-parallel group: every TP rank holds a copy (norms, biases of row-parallel
+            # layers, the router, and the expert weights, which are split over the expert-parallel group only)
+            repl = getattr(p, "tp_shard_dim", None) is None
             kind = "muon" if muon_fn(name, p) else "adam"
             wd = 0.0 if decay_fn(mod, pname) else weight_decay
             key = (repl, kind, wd)

@@ -1,5 +1,6 @@
 """Mixture-of-experts block: dense restatement equivalence, padded layout, EP=2 == EP=1."""
 
+import pytest
 import torch
 
 from helpers import run_distributed, tiny_config
@@ -79,5 +80,40 @@ def test_ep2_matches_ep1(tmp_path):
     r1, r2 = torch.load(a), torch.load(b)
     for x, y in zip(r1["losses"], r2["losses"]):
         assert abs(x - y) < 1e-4, (r1["losses"], r2["losses"])
+    for k in r1["sd"]:
+        assert torch.allclose(r1["sd"][k], r2["sd"][k], atol=1e-4, rtol=1e-3), k
+
+
+def _tp_ep_worker(rank, world, tp, sp, out_path):
+    from ironcore_b200.checkpoint.native import merge_model_parallel_state
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.trainer import Trainer
+
+    cfg = _moe_cfg(expert_model_parallel_size=2)
+    cfg.model.moe.aux_loss_coeff = 0.0     # (under sequence parallelism the balance loss is per token shard)
+    cfg.trainer(micro_batch_size=2, train_batch_size=2 * (world // tp), gradient_accumulation_steps=None,
+                tensor_model_parallel_size=tp)
+    cfg.parallel(world_size=world, rank=rank, sequence_parallel=sp)
+    cfg.operation.train_steps = 3
+    validate_config(cfg)
+    tr = Trainer(cfg)
+    out = [tr.train_step(s) for s in range(3)]
+    local = dict(tr.model.canonical_state_dict())
+    merged = merge_model_parallel_state(local, tr.model.canonical_shard_info(), {n for n in local if ".experts_" in n})
+    if rank == 0:
+        torch.save({"losses": [float(o[0]) for o in out], "norms": [float(o[1]) for o in out], "sd": merged}, out_path)
+
+
+@pytest.mark.parametrize("sp", [False, True])
+def test_tensor_parallel_times_expert_parallel_matches_expert_parallel(tmp_path, sp):
+    """TP2 x EP2 on four ranks against EP2 on two: the expert weights are copies on the tensor-parallel ranks, so
+    under sequence parallelism (each rank routes its token shard) their gradients are summed over the group, and
+    the gradient norm counts them once."""
+    a, b = str(tmp_path / "ep2.pt"), str(tmp_path / "tp2ep2.pt")
+    run_distributed(_tp_ep_worker, 2, 1, False, a)
+    run_distributed(_tp_ep_worker, 4, 2, sp, b)
+    r1, r2 = torch.load(a), torch.load(b)
+    assert r1["losses"] == pytest.approx(r2["losses"], abs=2e-5)
+    assert r1["norms"] == pytest.approx(r2["norms"], rel=1e-4)
     for k in r1["sd"]:
         assert torch.allclose(r1["sd"][k], r2["sd"][k], atol=1e-4, rtol=1e-3), k
