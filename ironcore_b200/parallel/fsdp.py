@@ -456,6 +456,30 @@ class FSDPOptimizer:
         self._muon_plans: Dict[str, dict] = {}
         self._norm = None
         self._owners: Dict[str, int] = {}
+        # Tensor parallelism next to the shard group: a parameter without a tensor-parallel shard dimension is a
+        # copy on every TP rank. Its squares count once in a norm summed over the TP group, and under sequence
+        # parallelism (each rank sees its token shard) its gradient is the sum over that group.
+        self.tp_group = mesh.get_tensor_model_parallel_group()
+        self.tp_size = mesh.get_tensor_model_parallel_world_size()
+        self.sequence_parallel = mesh.sequence_parallel_enabled() and self.tp_size > 1
+        self._tp_copies: Dict[str, list] = {}
+        if self.tp_size > 1:
+            if self.use_muon:
+                raise NotImplementedError("Muon on FSDP shards needs tensor_model_parallel_size 1 (a matrix is "
+                                          "orthogonalised from the shards of one group); use the ZeRO-1 engine "
+                                          "for tensor-parallel Muon")
+            for u in fsdp.units:
+                lo, hi = u.shard_range()
+                ranges = []
+                for p, o in zip(u.params, u.offsets):
+                    if getattr(p, "tp_shard_dim", None) is None:
+                        a, b = max(o, lo), min(o + p.numel(), hi)
+                        if b > a:
+                            if ranges and ranges[-1][1] == a - lo:
+                                ranges[-1][1] = b - lo          # adjacent copies: one range
+                            else:
+                                ranges.append([a - lo, b - lo])
+                self._tp_copies[u.name] = ranges
         if self.use_muon:
             load = [0.0] * max(fsdp.dp, 1)
             mats = []
@@ -492,6 +516,23 @@ class FSDPOptimizer:
     def grad_norm(self):
         return self._norm
 
+    def _unit_sumsq(self, u, t: torch.Tensor, total: torch.Tensor) -> None:
+        """Add the squares of ``t`` (this rank's flat range of unit ``u``) to ``total``; ranges that are copies on
+        every tensor-parallel rank are weighted 1 / tp, so that the sum over that group counts them once."""
+        def add(x, w):
+            if x.numel() == 0:
+                return
+            if x.is_cuda:
+                tmp = torch.zeros(1, dtype=torch.float32, device=total.device)
+                kernels.sumsq(x, tmp)
+                total.add_(tmp * w)
+            else:
+                total.add_(x.float().pow(2).sum() * w)
+
+        add(t, 1.0)
+        for a, b in self._tp_copies.get(u.name, ()):
+            add(t[a:b], 1.0 / self.tp_size - 1.0)
+
     @torch.no_grad()
     def param_norm(self) -> torch.Tensor:
         """L2 norm of all parameters: one sum-of-squares kernel per unit shard, summed over the shard group."""
@@ -502,14 +543,11 @@ class FSDPOptimizer:
         for u in fs.units:
             t = (u._local_shard() if u.shard_params else u.full)
             sharded = sharded or u.shard_params
-            if t.is_cuda:
-                tmp = torch.zeros(1, dtype=torch.float32, device=dev)
-                kernels.sumsq(t, tmp)
-                total += tmp
-            else:
-                total += t.float().pow(2).sum()
+            self._unit_sumsq(u, t, total)
         if sharded and fs.dp > 1:
             dist.all_reduce(total, group=fs.group)
+        if self.tp_size > 1:
+            dist.all_reduce(total, group=self.tp_group)
         return total.sqrt().squeeze(0)
 
     @torch.no_grad()
@@ -523,15 +561,15 @@ class FSDPOptimizer:
         dev = fs.units[0].device
         total = torch.zeros(1, dtype=torch.float32, device=dev)
         for u in fs.units:
-            if u.device.type == "cuda":
-                tmp = torch.zeros(1, dtype=torch.float32, device=dev)
-                kernels.sumsq(u.grad_shard, tmp)
-                total += tmp
-            else:
-                total += u.grad_shard.pow(2).sum()
+            if self.sequence_parallel:
+                for a, b in self._tp_copies.get(u.name, ()):
+                    dist.all_reduce(u.grad_shard[a:b], group=self.tp_group)
+            self._unit_sumsq(u, u.grad_shard, total)
         total = total / (dp * dp)
         if fs.dp > 1 and any(u.shard_params for u in fs.units):
             dist.all_reduce(total, group=fs.group)
+        if self.tp_size > 1:
+            dist.all_reduce(total, group=self.tp_group)
         norm = total.sqrt()
         coef = torch.clamp(self.clip / (norm + 1e-6), max=1.0) if self.clip > 0 else torch.ones_like(norm)
         self._norm = norm

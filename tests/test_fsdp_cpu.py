@@ -49,3 +49,38 @@ def test_newton_schulz_orthogonalises():
     gt = torch.randn(96, 48)
     xt = newton_schulz_reference(gt, steps=5, dtype=torch.float32)
     assert xt.shape == gt.shape
+
+
+def _tp_worker(rank, world, fsdp, sp, out_path):
+    from ironcore_b200.checkpoint.native import merge_model_parallel_state
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.trainer import Trainer
+
+    cfg = tiny_config("llama")
+    cfg.trainer(micro_batch_size=2, train_batch_size=4, gradient_accumulation_steps=None, tensor_model_parallel_size=2)
+    cfg.parallel(world_size=world, rank=rank, use_fsdp=fsdp, fsdp_mixed_precision="fp32", sequence_parallel=sp)
+    cfg.optim(max_lr=1e-3, clip_grad=0.5)          # (the clip is active: the norm enters the update)
+    cfg.operation.train_steps = 3
+    validate_config(cfg)
+    tr = Trainer(cfg)
+    out = [tr.train_step(s) for s in range(3)]
+    merged = merge_model_parallel_state(dict(tr.model.canonical_state_dict()), tr.model.canonical_shard_info())
+    pn = float(tr.optimizer.param_norm())
+    if rank == 0:
+        torch.save({"losses": [float(o[0]) for o in out], "norms": [float(o[1]) for o in out], "sd": merged,
+                    "param_norm": pn}, out_path)
+
+
+@pytest.mark.parametrize("sp", [False, True])
+def test_fsdp_next_to_tensor_parallelism_matches_data_parallel(tmp_path, sp):
+    """FSDP over the data-parallel group of a TP2 x DP2 mesh: the gradient norm sums the tensor-parallel shards and
+    counts the copies once, and with sequence parallelism the copies' gradients are summed over the TP group."""
+    a, b = str(tmp_path / "dp.pt"), str(tmp_path / "fsdp.pt")
+    run_distributed(_tp_worker, 4, False, sp, a)
+    run_distributed(_tp_worker, 4, True, sp, b)
+    r0, r1 = torch.load(a), torch.load(b)
+    assert r0["losses"] == pytest.approx(r1["losses"], abs=1e-4)
+    assert r0["norms"] == pytest.approx(r1["norms"], rel=1e-4)
+    assert r0["param_norm"] == pytest.approx(r1["param_norm"], rel=1e-5)
+    for k in r0["sd"]:
+        assert torch.allclose(r0["sd"][k], r1["sd"][k], atol=1e-5, rtol=1e-3), k
