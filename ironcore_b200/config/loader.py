@@ -283,6 +283,10 @@ def validate_config(config: MainConfig) -> MainConfig:
             raise ValueError("num_experts should be divisible by expert_model_parallel_size")
         if dp % ep != 0:
             raise ValueError("expert_model_parallel_size must divide the data-parallel size")
+    if ep > 1 and p.use_fsdp:
+        # the shard group of an FSDP unit is the data-parallel group, whose ranks hold *different* experts
+        raise ValueError("parallel.use_fsdp with expert_model_parallel_size > 1 is not implemented: shard the "
+                         "optimizer state of an expert-parallel model with parallel.zero_stage: 1 instead")
     if p.zero_stage not in (0, 1):
         raise ValueError("zero_stage must be 0 or 1 (use parallel.use_fsdp for full sharding)")
     if config.optim.optimizer.lower() not in ("adam", "adamw", "muon"):

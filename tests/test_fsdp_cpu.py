@@ -84,3 +84,14 @@ def test_fsdp_next_to_tensor_parallelism_matches_data_parallel(tmp_path, sp):
     assert r0["param_norm"] == pytest.approx(r1["param_norm"], rel=1e-5)
     for k in r0["sd"]:
         assert torch.allclose(r0["sd"][k], r1["sd"][k], atol=1e-5, rtol=1e-3), k
+
+
+def test_layouts_the_shard_engine_does_not_serve_are_refused():
+    from ironcore_b200.config import validate_config
+
+    cfg = tiny_config("llama")
+    cfg.model.moe(num_experts=4, top_k=2, expert_d_ffn=32)
+    cfg.trainer(micro_batch_size=2, train_batch_size=4, gradient_accumulation_steps=None)
+    cfg.parallel(world_size=2, rank=0, use_fsdp=True, expert_model_parallel_size=2)
+    with pytest.raises(ValueError, match="zero_stage"):
+        validate_config(cfg)
