@@ -259,6 +259,9 @@ class OperationConfig(BaseConfig):
     activation_recompute: bool = opt(False, "recompute layer activations in backward")
     recompute_strategy: Optional[str] = opt("default", "default | optimized")
     no_save: bool = opt(False, "never write checkpoints")
+    resume_data_position: bool = opt(True, "after a resume, continue the training data stream where the checkpoint "
+                                           "left it (skips the micro-batches of the completed steps) instead of "
+                                           "replaying it from the start")
     exit_interval: Optional[int] = opt(None, "stop after this many steps")
     save_dist_ckpt: bool = opt(False, "one checkpoint shard per TP rank")
 

@@ -180,6 +180,9 @@ class Trainer:
         cfg = self.config
         last = load_checkpoint(cfg, self.model, self.optimizer, self.lr_scheduler)
         if last is not None and last >= 0:
+            if cfg.operation.resume_data_position:
+                # the stream is seeded and deterministic: the completed steps consumed this many micro-batches
+                self._skip_training_batches((last + 1) * int(cfg.trainer.gradient_accumulation_steps))
             return last + 1
         if cfg.trainer.init_from_hf:
             from .checkpoint.hf_interop import load_from_huggingface
@@ -187,6 +190,16 @@ class Trainer:
             load_from_huggingface(self.model, cfg, cfg.trainer.init_from_hf)
             self.logger.info("initialised the weights from the HuggingFace checkpoint %s", cfg.trainer.init_from_hf)
         return 0
+
+    def _skip_training_batches(self, n: int) -> None:
+        it = self.data_iterator.get("train") if isinstance(self.data_iterator, dict) else None
+        if it is None or n <= 0:
+            return
+        for _ in range(n):
+            try:
+                next(it)
+            except StopIteration:
+                break
 
     # ------------------------------------------------------------------ training
     def train(self):

@@ -168,3 +168,32 @@ def test_evaluation_reports_the_loss_of_the_counted_positions():
     keep = labels != -100
     acc = float(((logits.argmax(-1) == labels) & keep).sum()) / float(keep.sum())
     assert got["eval_loss"] == pytest.approx(want, rel=1e-5) and got["eval_accuracy"] == pytest.approx(acc)
+
+
+def test_interrupted_run_continues_as_if_uninterrupted(tmp_path):
+    """Two steps, a checkpoint, a new process-worth of objects, two more steps: the same weights as four steps in
+    one go. Weights, optimizer state, schedule and the position in the data stream all come back."""
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.trainer import Trainer
+
+    def run(steps, path, accum=2):
+        mesh.destroy_model_parallel()
+        cfg = tiny_config("llama")
+        cfg.trainer(micro_batch_size=2, train_batch_size=2 * accum, gradient_accumulation_steps=None, model_path=path,
+                    save_checkpoint_steps=100)
+        cfg.optim(lr_scheduler="cosine", warmup_steps=1, annealing_steps=10, max_lr=1e-3)
+        cfg.operation(train_steps=steps)
+        validate_config(cfg)
+        tr = Trainer(cfg)
+        last = tr.train()
+        return last, {k: v.clone() for k, v in tr.model.canonical_state_dict().items()}
+
+    last, whole = run(4, str(tmp_path / "a"))
+    assert last == 3
+    last, _ = run(2, str(tmp_path / "b"))            # ends with the final checkpoint of step 1
+    assert last == 1
+    last, resumed = run(4, str(tmp_path / "b"))      # picks it up and goes on to step 3
+    assert last == 3
+    for k, v in whole.items():
+        assert torch.equal(v, resumed[k]), k
