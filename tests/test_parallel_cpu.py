@@ -2,6 +2,8 @@
 single-rank model, ZeRO-1 equivalence with the replicated optimizer, universal checkpoints
 across TP sizes."""
 
+import os
+
 import pytest
 import torch
 
@@ -221,3 +223,54 @@ def test_universal_checkpoint_tp2_to_tp1(tmp_path):
     for k, v in tr.model.canonical_state_dict().items():
         assert torch.allclose(v, ref_sd[k], atol=2e-4, rtol=1e-3), k
     assert tr.optimizer.step_count == 2
+
+
+_RESUME_LAYOUTS = {
+    "zero1_dp2": dict(parallel=dict(zero_stage=1)),
+    "tp2_sp": dict(tp=2, parallel=dict(sequence_parallel=True)),
+    "tp2_sp_per_rank_files": dict(tp=2, parallel=dict(sequence_parallel=True), operation=dict(save_dist_ckpt=True)),
+    "ep2_zero1": dict(moe=dict(num_experts=4, top_k=2, expert_d_ffn=32, num_shared_experts=1),
+                      parallel=dict(expert_model_parallel_size=2, zero_stage=1)),
+    "fsdp2": dict(parallel=dict(use_fsdp=True, fsdp_mixed_precision="fp32")),
+}
+
+
+def _resume_worker(rank, world, layout, root, out_path):
+    from ironcore_b200.checkpoint.native import merge_model_parallel_state
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.parallel import mesh
+    from ironcore_b200.trainer import Trainer
+
+    spec = _RESUME_LAYOUTS[layout]
+
+    def run(steps, path):
+        mesh.destroy_model_parallel()
+        cfg = tiny_config("llama")
+        if spec.get("moe"):
+            cfg.model.moe(**spec["moe"])
+        tp = spec.get("tp", 1)
+        cfg.trainer(micro_batch_size=2, train_batch_size=2 * (world // tp), gradient_accumulation_steps=None,
+                    tensor_model_parallel_size=tp, model_path=path, save_checkpoint_steps=100)
+        cfg.parallel(world_size=world, rank=rank, **spec.get("parallel", {}))
+        cfg.optim(lr_scheduler="cosine", warmup_steps=1, annealing_steps=10, max_lr=1e-3)
+        cfg.operation(train_steps=steps, **spec.get("operation", {}))
+        validate_config(cfg)
+        tr = Trainer(cfg)
+        assert tr.train() == steps - 1
+        local = dict(tr.model.canonical_state_dict())
+        return merge_model_parallel_state(local, tr.model.canonical_shard_info(), {n for n in local if ".experts_" in n})
+
+    whole = run(4, os.path.join(root, "a"))
+    run(2, os.path.join(root, "b"))
+    resumed = run(4, os.path.join(root, "b"))
+    if rank == 0:
+        torch.save(max((whole[k].float() - resumed[k].float()).abs().max().item() for k in whole), out_path)
+
+
+@pytest.mark.parametrize("layout", sorted(_RESUME_LAYOUTS))
+def test_interrupted_run_on_two_ranks_continues_as_if_uninterrupted(tmp_path, layout):
+    """Save after two steps, start over with new objects, train to step four: bit-identical to four steps in one go
+    for every parallel layout and checkpoint form."""
+    out = str(tmp_path / "diff.pt")
+    run_distributed(_resume_worker, 2, layout, str(tmp_path), out)
+    assert torch.load(out) == 0.0
