@@ -274,3 +274,49 @@ def test_interrupted_run_on_two_ranks_continues_as_if_uninterrupted(tmp_path, la
     out = str(tmp_path / "diff.pt")
     run_distributed(_resume_worker, 2, layout, str(tmp_path), out)
     assert torch.load(out) == 0.0
+
+
+_MOE4 = dict(num_experts=4, top_k=2, expert_d_ffn=32, num_shared_experts=1)
+_CROSS = {      # name: ((world, layout) that writes the checkpoint, (world, layout) that resumes it)
+    "tp2_to_tp1": ((2, dict(tp=2, gb=2, parallel=dict(sequence_parallel=True))), (1, dict(gb=2))),
+    "tp1_to_tp2": ((1, dict(gb=2)), (2, dict(tp=2, gb=2, parallel=dict(sequence_parallel=True)))),
+    "ep2_to_ep1": ((2, dict(moe=True, gb=4, parallel=dict(expert_model_parallel_size=2))), (2, dict(moe=True, gb=4))),
+    "fsdp_to_zero1": ((2, dict(gb=4, parallel=dict(use_fsdp=True, fsdp_mixed_precision="fp32"))),
+                      (2, dict(gb=4, parallel=dict(zero_stage=1)))),
+}
+
+
+def _cross_worker(rank, world, spec, steps, path, out_path):
+    from ironcore_b200.checkpoint.native import merge_model_parallel_state
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.trainer import Trainer
+
+    cfg = tiny_config("llama")
+    if spec.get("moe"):
+        cfg.model.moe(**_MOE4)
+    cfg.trainer(micro_batch_size=2, train_batch_size=spec["gb"], gradient_accumulation_steps=None,
+                tensor_model_parallel_size=spec.get("tp", 1), model_path=path, save_checkpoint_steps=100)
+    cfg.parallel(world_size=world, rank=rank, **spec.get("parallel", {}))
+    cfg.optim(lr_scheduler="cosine", warmup_steps=1, annealing_steps=10, max_lr=1e-3)
+    cfg.operation(train_steps=steps)
+    validate_config(cfg)
+    tr = Trainer(cfg)
+    tr.train()
+    local = dict(tr.model.canonical_state_dict())
+    merged = merge_model_parallel_state(local, tr.model.canonical_shard_info(), {n for n in local if ".experts_" in n})
+    if rank == 0 and out_path:
+        torch.save(merged, out_path)
+
+
+@pytest.mark.parametrize("case", sorted(_CROSS))
+def test_checkpoint_resumes_under_another_layout(tmp_path, case):
+    """A merged checkpoint (weights and optimizer state) written under one parallel layout continues under another
+    as the uninterrupted run of that other layout would (same data-parallel size, so the same data)."""
+    (wa, sa), (wb, sb) = _CROSS[case]
+    whole, ck = str(tmp_path / "whole"), str(tmp_path / "ck")
+    run_distributed(_cross_worker, wb, sb, 4, whole, str(tmp_path / "whole.pt"))
+    run_distributed(_cross_worker, wa, sa, 2, ck, None)
+    run_distributed(_cross_worker, wb, sb, 4, ck, str(tmp_path / "resumed.pt"))
+    a, b = torch.load(str(tmp_path / "whole.pt")), torch.load(str(tmp_path / "resumed.pt"))
+    for k in a:
+        assert torch.allclose(a[k], b[k], atol=1e-5, rtol=1e-4), k
