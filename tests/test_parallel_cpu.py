@@ -21,6 +21,14 @@ def test_mesh_layout_matches_documented_example():
     assert lay["edp"] == [[0, 4], [1, 5], [2, 6], [3, 7]]
 
 
+# architecture switches of the families that ``tiny_config`` does not know by itself
+_FAMILY_KW = {
+    "phi2": dict(activation_type="gelu_new", untie_embed=True, positional_embedding={"type": "rope", "rotary_fraction": 0.5}),
+    "gemma1": dict(no_bias=True, ln_type="rmsnorm", activation_type="geglu", untie_embed=False, num_attention_groups=2,
+                   positional_embedding={"type": "rope"}),
+}
+
+
 def _reference_run(family, steps, accum=1):
     """Single-process TP=1 run: returns losses and the final canonical state dict."""
     from ironcore_b200.config import validate_config
@@ -28,7 +36,7 @@ def _reference_run(family, steps, accum=1):
     from ironcore_b200.trainer import Trainer
 
     mesh.destroy_model_parallel()
-    cfg = tiny_config(family)
+    cfg = tiny_config(family, **_FAMILY_KW.get(family, {}))
     cfg.trainer(micro_batch_size=2, train_batch_size=2 * accum, gradient_accumulation_steps=None)
     cfg.operation.train_steps = steps
     validate_config(cfg)
@@ -43,7 +51,7 @@ def _tp_worker(rank, world, family, sp, steps, out_path):
     from ironcore_b200.config import validate_config
     from ironcore_b200.trainer import Trainer
 
-    cfg = tiny_config(family)
+    cfg = tiny_config(family, **_FAMILY_KW.get(family, {}))
     cfg.trainer(micro_batch_size=2, train_batch_size=2, gradient_accumulation_steps=None,
                 tensor_model_parallel_size=world)
     cfg.parallel(world_size=world, rank=rank, sequence_parallel=sp)
@@ -56,7 +64,8 @@ def _tp_worker(rank, world, family, sp, steps, out_path):
         torch.save({"losses": losses, "sd": merged}, out_path)
 
 
-@pytest.mark.parametrize("family,sp", [("gpt2", False), ("llama", False), ("llama", True), ("gpt2", True)])
+@pytest.mark.parametrize("family,sp", [("gpt2", False), ("llama", False), ("llama", True), ("gpt2", True),
+                                       ("qwen", True), ("phi2", True), ("gemma1", True)])
 def test_tp2_matches_tp1(tmp_path, family, sp):
     steps = 3
     ref_losses, ref_sd = _reference_run(family, steps)
@@ -75,7 +84,7 @@ def _full_load_worker(rank, world, family, path):
     from ironcore_b200.parallel import mesh
 
     saved = torch.load(path)
-    cfg = tiny_config(family)
+    cfg = tiny_config(family, **_FAMILY_KW.get(family, {}))
     cfg.trainer(tensor_model_parallel_size=world)
     cfg.parallel(world_size=world, rank=rank)
     cfg.init.seed = 99          # different weights until the state dict is loaded
@@ -96,7 +105,7 @@ def test_single_rank_state_dict_loads_into_tp2(tmp_path, family):
     from ironcore_b200.parallel import mesh
 
     mesh.destroy_model_parallel()
-    cfg = tiny_config(family)
+    cfg = tiny_config(family, **_FAMILY_KW.get(family, {}))
     validate_config(cfg)
     mesh.initialize_model_parallel(1)
     model = LanguageModel(cfg)
