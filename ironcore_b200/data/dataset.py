@@ -83,6 +83,7 @@ class WeightedMixingDataset(IterableDataset):
         self.seed, self.dp_rank, self.dp_size = seed, dp_rank, dp_size
         self.epochs = epochs
         self.cursor = 0          # samples yielded so far on this rank (saved in checkpoints)
+        self.start_sample = 0    # samples of this rank's stream to pass over before the first one is read (resume)
 
     @staticmethod
     def sources_of(data_config, mode: str, split: str) -> Dict:
@@ -145,8 +146,17 @@ class WeightedMixingDataset(IterableDataset):
                 probs.append(self.weights[si] / max(n, 1))
         return items, np.asarray(probs)
 
+    def _passed_over(self) -> bool:
+        """Whether the next sample of the stream is one to pass over without reading it (``start_sample``)."""
+        if self._to_skip > 0:
+            self._to_skip -= 1
+            self.cursor += 1
+            return True
+        return False
+
     def __iter__(self) -> Iterator[Dict]:
         epoch = 0
+        self._to_skip = int(self.start_sample)
         while self.epochs is None or epoch < self.epochs:
             rng = np.random.default_rng(self.seed + epoch)
             if self.mode == "pretrain":
@@ -156,6 +166,8 @@ class WeightedMixingDataset(IterableDataset):
                 order = self._weighted_pretrain_order(items, rng)
                 for j, k in enumerate(order):
                     if j % self.dp_size != self.dp_rank:
+                        continue
+                    if self._passed_over():
                         continue
                     si, start = items[k]
                     self.cursor += 1
@@ -180,12 +192,17 @@ class WeightedMixingDataset(IterableDataset):
                             grp = [x for x in range(len(self.sets[si])) if int(self.sets[si].index[x]["group_id"]) == gid[1]]
                             pair = {str(self.sets[si].index[x]["type"]): self.sets[si].sample(x) for x in grp}
                             if "dpo_chosen" in pair and "dpo_rejected" in pair:
+                                if self._passed_over():
+                                    j += 1
+                                    continue
                                 self.cursor += 1
                                 yield {"chosen": pair["dpo_chosen"], "rejected": pair["dpo_rejected"], "type": "dpo"}
                         j += 1
                 else:
                     for j, k in enumerate(order):
                         if j % self.dp_size != self.dp_rank:
+                            continue
+                        if self._passed_over():
                             continue
                         si, i = items[k]
                         self.cursor += 1

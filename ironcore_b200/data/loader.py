@@ -34,5 +34,31 @@ def build_file_iterators(config, dp_rank: int, dp_size: int) -> Dict[str, object
               "test": config.trainer.test_batch_size or config.trainer.micro_batch_size}[split]
         loader = DataLoader(ds, batch_size=bs, collate_fn=UniversalCollator(task, seq_len, pad), num_workers=0,
                             pin_memory=torch.cuda.is_available(), drop_last=(split == "train"))
-        out[split] = iter(loader)
+        out[split] = _BatchIterator(loader, ds, bs)
     return out
+
+
+class _BatchIterator:
+    """Iterator over a loader's batches that can pass over its first batches without reading their tokens."""
+
+    def __init__(self, loader, dataset, batch_size: int):
+        self.loader, self.dataset, self.batch_size = loader, dataset, batch_size
+        self._it = None
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        if self._it is None:
+            self._it = iter(self.loader)
+        return next(self._it)
+
+    def skip_batches(self, n: int) -> None:
+        """Advance the stream by ``n`` batches. Before the first batch was drawn this only moves the dataset's
+        starting point (fixed-size samples per batch: pretrain windows, one pair or conversation per sample);
+        afterwards the batches are drawn and dropped."""
+        if self._it is None:
+            self.dataset.start_sample += int(n) * self.batch_size
+            return
+        for _ in range(int(n)):
+            next(self)

@@ -195,6 +195,9 @@ class Trainer:
         it = self.data_iterator.get("train") if isinstance(self.data_iterator, dict) else None
         if it is None or n <= 0:
             return
+        if hasattr(it, "skip_batches"):      # file-backed streams move their starting point without reading tokens
+            it.skip_batches(n)
+            return
         for _ in range(n):
             try:
                 next(it)

@@ -3,6 +3,7 @@
 import json
 
 import numpy as np
+import pytest
 import torch
 import yaml
 
@@ -220,3 +221,37 @@ def test_preference_pairs_from_files_train_with_dpo(tmp_path, capsys):
     out = capsys.readouterr().out
     assert "Task type: dpo" in out and "Training completed successfully" in out
     mesh.destroy_model_parallel()
+
+
+@pytest.mark.parametrize("task", ["pretrain", "sft", "dpo"])
+def test_file_backed_stream_can_start_further_in(tmp_path, task):
+    """``skip_batches`` before the first batch moves the dataset's starting point (no tokens are read for the part
+    passed over); the batches that follow are the ones an iterator that drew and dropped would have produced."""
+    from helpers import tiny_config
+    from ironcore_b200.__main__ import main
+    from ironcore_b200.config import validate_config
+    from ironcore_b200.data import get_data_iterator
+
+    cfg_path = _write_sources(tmp_path)
+    assert main(["preprocess", "--config", str(cfg_path)]) == 0
+
+    def stream():
+        cfg = tiny_config("gpt2", vocab_size=50257)
+        cfg.data(task_type=task, config_path=str(cfg_path), vocab_size=50257)
+        cfg.trainer(micro_batch_size=2, train_batch_size=2, gradient_accumulation_steps=None)
+        validate_config(cfg)
+        return get_data_iterator(cfg, dp_rank=0, dp_size=1)["train"]
+
+    plain, moved = stream(), stream()
+    for _ in range(2):
+        next(plain)
+    moved.skip_batches(2)
+    for _ in range(2):
+        a, b = next(plain), next(moved)
+        assert a.keys() == b.keys()
+        for k in a:
+            assert torch.equal(a[k], b[k]), k
+    moved.skip_batches(1)                 # after the first draw: batches are drawn and dropped
+    next(plain)
+    a, b = next(plain), next(moved)
+    assert all(torch.equal(a[k], b[k]) for k in a)
