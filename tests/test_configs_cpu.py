@@ -19,7 +19,8 @@ def test_run_preset_loads(path, monkeypatch):
     from ironcore_b200.config import load_config
 
     world = {"baseline_llama7b_tp8.yaml": 8, "baseline_moe_ep8.yaml": 8, "baseline_llama13b_fsdp_muon.yaml": 8,
-             "baseline_grpo_qwen.yaml": 8, "example.yaml": 2}.get(os.path.basename(path), 1)
+             "baseline_grpo_qwen.yaml": 8, "example.yaml": 2, "dpo_example.yaml": 2,
+             "finetune_from_hf_example.yaml": 8}.get(os.path.basename(path), 1)
     monkeypatch.setenv("WORLD_SIZE", str(world))
     monkeypatch.setenv("RANK", "0")
     monkeypatch.chdir(ROOT)
