@@ -68,3 +68,14 @@ class DPOTrainer(Trainer):
         loss, stats = dpo_loss(pol_c, pol_r, ref_c, ref_r, rl.dpo_beta, rl.dpo_label_smoothing)
         self.last_stats = {k: float(v) for k, v in stats.items()}
         return loss
+
+    def log_training(self, step, losses, grad_norm, param_norm):
+        metrics = super().log_training(step, losses, grad_norm, param_norm)
+        if self.last_stats:
+            from .. import global_vars as G
+
+            s = self.last_stats
+            self.logger.info("          dpo | reward accuracy %.2f | chosen %.4f | rejected %.4f | margin %.3f",
+                             s["reward_accuracy"], s["reward_chosen"], s["reward_rejected"], s["margin"])
+            G.log_metrics({f"dpo/{k}": v for k, v in s.items()}, step + 1)
+        return metrics
