@@ -79,3 +79,30 @@ class DPOTrainer(Trainer):
                              s["reward_accuracy"], s["reward_chosen"], s["reward_rejected"], s["margin"])
             G.log_metrics({f"dpo/{k}": v for k, v in s.items()}, step + 1)
         return metrics
+
+    @torch.no_grad()
+    def _eval_loop(self, iterator, max_batches: int, tag: str, step: int):
+        """Preference loss and reward accuracy over held-out pairs."""
+        if iterator is None:
+            return None
+        from .. import global_vars as G
+
+        rl = self.config.rl
+        self.model.eval()
+        losses, accs = [], []
+        for i, batch in enumerate(iterator):
+            if i >= max_batches:
+                break
+            lp = {(m, h): sequence_logprobs(model, batch, h) for m, model in (("p", self.model), ("r", self.ref_model))
+                  for h in ("chosen_", "rejected_")}
+            loss, stats = dpo_loss(lp["p", "chosen_"], lp["p", "rejected_"], lp["r", "chosen_"], lp["r", "rejected_"],
+                                   rl.dpo_beta, rl.dpo_label_smoothing)
+            losses.append(loss.float())
+            accs.append(float(stats["reward_accuracy"]))
+        self.model.train()
+        if not losses:
+            return None
+        metrics = {f"{tag}_loss": self.average_loss(losses), f"{tag}_reward_accuracy": sum(accs) / len(accs)}
+        self.logger.log_metrics(metrics, title=f"{tag} @ step {step + 1}")
+        G.log_metrics(metrics, step + 1)
+        return metrics

@@ -171,6 +171,8 @@ def test_dpo_trainer_learns_the_preference():
     assert tr.last_stats["reward_chosen"] > tr.last_stats["reward_rejected"]
     assert all(torch.equal(a, b) for a, b in zip(ref_before, tr.ref_model.parameters()))
     assert all(not p.requires_grad for p in tr.ref_model.parameters())
+    held_out = tr._eval_loop(batches(), 3, "eval", 29)        # fresh pairs of the same kind
+    assert held_out["eval_reward_accuracy"] == 1.0 and held_out["eval_loss"] < 0.5 * math.log(2.0)
 
 
 def test_paged_decode_reproduces_transformers_greedy_generation():
