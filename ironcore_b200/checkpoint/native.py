@@ -116,6 +116,23 @@ def split_model_parallel_tensor(full: torch.Tensor, dim, parts, name: str, exper
     return full
 
 
+_VOCAB_DIM = {"embedding.word_embeddings.weight": 0, "output_layer.weight": 1, "output_layer.bias": 0}
+
+
+def fit_padded_vocab(name: str, full: torch.Tensor, padded_vocab: int) -> torch.Tensor:
+    """The padded vocabulary size is a multiple of ``vocab_padding_unit`` x the tensor-parallel size, so a merged
+    checkpoint written under one TP size can carry more or fewer padding rows than the model that resumes it.
+    Padding rows hold zeros and are never addressed: cut them off or add zeros along the vocabulary dimension."""
+    dim = _VOCAB_DIM.get(name)
+    if dim is None or padded_vocab <= 0 or full.dim() <= dim or full.shape[dim] == padded_vocab:
+        return full
+    if full.shape[dim] > padded_vocab:
+        return full.narrow(dim, 0, padded_vocab).contiguous()
+    pad = list(full.shape)
+    pad[dim] = padded_vocab - full.shape[dim]
+    return torch.cat([full, full.new_zeros(pad)], dim=dim)
+
+
 def _ckpt_dir(config, step: int, dist_ckpt: bool) -> Path:
     base = Path(config.trainer.model_path) / f"step_{step}"
     if dist_ckpt:
@@ -279,6 +296,8 @@ def load_checkpoint(config, model, optimizer=None, lr_scheduler=None, step: int 
     own = base.canonical_state_dict()
     expert_names = {n for n in own if ".experts_" in n}
     saved_tp = int(ckpt.get("tp_size", 1))
+    padded_vocab = int(getattr(base, "padded_vocab_size", None) or getattr(getattr(base, "module", None),
+                                                                           "padded_vocab_size", 0) or 0)
     sharded_file = path.parent != base_dir
     if sharded_file and saved_tp != mesh.get_tensor_model_parallel_world_size():
         raise ValueError(f"distributed checkpoint was written with TP={saved_tp}, "
@@ -290,6 +309,7 @@ def load_checkpoint(config, model, optimizer=None, lr_scheduler=None, step: int 
             continue
         if not sharded_file:
             dim, parts = info.get(name, (None, 1))
+            t = fit_padded_vocab(name, t, padded_vocab)
             t = split_model_parallel_tensor(t, dim, parts, name, expert_names)
         if t.numel() != own[name].numel():
             raise ValueError(f"checkpoint tensor {name} has {t.numel()} elements, model expects {own[name].numel()}")
@@ -303,8 +323,10 @@ def load_checkpoint(config, model, optimizer=None, lr_scheduler=None, step: int 
             if not sharded_file:
                 dim, parts = info.get(name, (None, 1))
                 st = {"step": st["step"],
-                      "exp_avg": split_model_parallel_tensor(st["exp_avg"], dim, parts, name, expert_names),
-                      "exp_avg_sq": split_model_parallel_tensor(st["exp_avg_sq"], dim, parts, name, expert_names)}
+                      "exp_avg": split_model_parallel_tensor(fit_padded_vocab(name, st["exp_avg"], padded_vocab),
+                                                             dim, parts, name, expert_names),
+                      "exp_avg_sq": split_model_parallel_tensor(fit_padded_vocab(name, st["exp_avg_sq"], padded_vocab),
+                                                                dim, parts, name, expert_names)}
             state[name] = st
         osd["state"] = _internal_optimizer_state(state)
         optimizer.load_state_dict(osd)

@@ -53,7 +53,8 @@ def init_parameters(module: nn.Module, config, generator: torch.Generator = None
             with torch.no_grad():
                 p.copy_(torch.empty(full_shape).normal_(0.0, s, generator=gen).to(p.dtype))
             continue
-        init_linear_weight_(p, full_shape, s, shard_dim, parts, tp_rank, tp_size, bool(config.init.xavier_init), gen)
+        init_linear_weight_(p, full_shape, s, shard_dim, parts, tp_rank, tp_size, bool(config.init.xavier_init), gen,
+                            valid=getattr(p, "vocab_valid", None))
 
 
 class BaseModule(nn.Module):

@@ -120,6 +120,10 @@ class LanguageModel(BaseModule):
         vocabulary rows zero. Sharded weights are slices of the TP=1 tensor, drawn from a
         CPU generator so every TP size sees the same full matrices.
         (Behavioural reference: ironcore/layers/module.py:43-163.)"""
+        # (dim, real vocabulary size) of the tensors that carry vocabulary padding: their padding is not drawn
+        self.embedding.word_embeddings.weight.vocab_valid = (0, self.vocab_size)
+        if self.untied:
+            self.output_layer.weight.vocab_valid = (1, self.vocab_size)
         init_parameters(self, self.config)
         tp_rank = mesh.get_tensor_model_parallel_rank()
         # zero the padded vocabulary rows / columns

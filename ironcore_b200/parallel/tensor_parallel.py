@@ -253,15 +253,25 @@ def vocab_parallel_cross_entropy(logits: torch.Tensor, targets: torch.Tensor, vo
 
 
 def init_linear_weight_(param: torch.Tensor, full_shape, std: float, shard_dim: Optional[int], parts: int,
-                        tp_rank: int, tp_size: int, xavier: bool = False, generator=None) -> None:
+                        tp_rank: int, tp_size: int, xavier: bool = False, generator=None,
+                        valid: Optional[tuple] = None) -> None:
     """Initialise a (possibly TP-sharded) weight so that TP=k equals the shards of the TP=1
-    tensor: draw the full matrix from the shared RNG stream, keep this rank's slice."""
-    full = torch.empty(full_shape, dtype=torch.float32)
+    tensor: draw the full matrix from the shared RNG stream, keep this rank's slice.
+    ``valid`` = (dim, n): only the first ``n`` entries along ``dim`` are drawn, the rest (vocabulary padding, whose
+    amount depends on the TP size) are zeros, so that the stream of random numbers does not depend on the padding."""
+    drawn = list(full_shape)
+    if valid is not None:
+        drawn[valid[0]] = min(int(valid[1]), drawn[valid[0]])
+    full = torch.empty(drawn, dtype=torch.float32)
     if xavier:
-        bound = math.sqrt(6.0 / (full_shape[0] + full_shape[1]))
+        bound = math.sqrt(6.0 / (drawn[0] + drawn[1]))
         full.uniform_(-bound, bound, generator=generator)
     else:
         full.normal_(mean=0.0, std=std, generator=generator)
+    if drawn != list(full_shape):
+        pad = list(full_shape)
+        pad[valid[0]] = full_shape[valid[0]] - drawn[valid[0]]
+        full = torch.cat([full, full.new_zeros(pad)], dim=valid[0])
     with torch.no_grad():
         param.copy_(shard_tensor(full, shard_dim, parts, tp_rank, tp_size).to(param.dtype))
 

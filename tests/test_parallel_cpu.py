@@ -300,7 +300,9 @@ def _cross_worker(rank, world, spec, steps, path, out_path):
     from ironcore_b200.config import validate_config
     from ironcore_b200.trainer import Trainer
 
-    cfg = tiny_config("llama")
+    # 500 entries: padded to 504 on one tensor-parallel rank and to 512 on two (unit 8 x TP size)
+    cfg = tiny_config("llama", vocab_size=500)
+    cfg.data.vocab_size = 500
     if spec.get("moe"):
         cfg.model.moe(**_MOE4)
     cfg.trainer(micro_batch_size=2, train_batch_size=spec["gb"], gradient_accumulation_steps=None,
@@ -328,4 +330,4 @@ def test_checkpoint_resumes_under_another_layout(tmp_path, case):
     run_distributed(_cross_worker, wb, sb, 4, ck, str(tmp_path / "resumed.pt"))
     a, b = torch.load(str(tmp_path / "whole.pt")), torch.load(str(tmp_path / "resumed.pt"))
     for k in a:
-        assert torch.allclose(a[k], b[k], atol=1e-5, rtol=1e-4), k
+        assert a[k].shape == b[k].shape and torch.allclose(a[k], b[k], atol=1e-5, rtol=1e-4), k
